@@ -1,0 +1,249 @@
+"""Public façade: runtimes, generation, training steps.
+
+Same call surface and reset/carry semantics as the reference's
+src/rwkv7m/api.py:38-326.  ``rng_key`` arguments are integer seeds (or anything
+``torch.as_tensor`` can read; the last element is used), since there is no JAX
+key type here.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .config import ModelConfig, load_model_config, tiny_config
+from .data import BinIdxBatchDataset, create_binidx_dataset
+from .infer.generate import decode_one, generate, prefill
+from .io.safetensors_io import load_params_into_model
+from .models.model import ScreenedRWKVModel, initialize_model
+from .state import init_rwkv_state, init_screen_state
+from .tokenizer import RWKVTokenizer
+from .train.train_step import initialize_train_state, train_step
+
+
+@dataclass
+class RWKV7MRuntime:
+    model: ScreenedRWKVModel
+    variables: dict
+    rwkv_state: tuple
+    screen_state: object
+    config: ModelConfig
+    batch_size: int
+    initial_rwkv_state: tuple
+    initial_screen_state: object
+
+    @property
+    def device(self):
+        return next(self.model.parameters()).device
+
+
+def _seed(rng_key) -> int:
+    if rng_key is None:
+        return 0
+    if isinstance(rng_key, int):
+        return rng_key
+    return int(torch.as_tensor(rng_key).flatten()[-1].item())
+
+
+def _default_device(device):
+    if device is not None:
+        return torch.device(device)
+    return torch.device("cpu")
+
+
+def _make_runtime(model, config, batch_size):
+    device = next(model.parameters()).device
+    rwkv_state = init_rwkv_state(batch_size, config, device=device)
+    screen_state = init_screen_state(batch_size, config.screening if config.use_screening else _no_screen(config),
+                                     device=device)
+    return RWKV7MRuntime(
+        model=model,
+        variables={"params": dict(model.named_parameters())},
+        rwkv_state=rwkv_state,
+        screen_state=screen_state,
+        config=config,
+        batch_size=batch_size,
+        initial_rwkv_state=rwkv_state,
+        initial_screen_state=screen_state,
+    )
+
+
+def _no_screen(config):
+    import copy
+
+    scr = copy.copy(config.screening)
+    scr.screened_layers = ()
+    return scr
+
+
+def create_runtime(rng_key, config, *, batch_size: int = 1, device=None) -> RWKV7MRuntime:
+    config = load_model_config(config)
+    model = initialize_model(_seed(rng_key), config, device=_default_device(device))
+    model.eval()
+    return _make_runtime(model, config, batch_size)
+
+
+def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, device=None,
+                         shard_multiple: int = 1):
+    config = load_model_config(config)
+    train_state = initialize_train_state(
+        _seed(rng_key) + 1, config, total_steps=total_steps, device=_default_device(device),
+        shard_multiple=shard_multiple,
+    )
+    return _make_runtime(train_state.model, config, batch_size), train_state
+
+
+def load_runtime_params(runtime: RWKV7MRuntime, params):
+    """Load a portable parameter tree (nested or ``/``-joined flat) into the runtime's model."""
+    load_params_into_model(runtime.model, params)
+    runtime.variables = {"params": dict(runtime.model.named_parameters())}
+    return runtime
+
+
+def _ids(runtime, ids):
+    t = torch.as_tensor(ids)
+    if t.ndim == 1:
+        t = t[None, :]
+    return t.to(device=runtime.device, dtype=torch.int32)
+
+
+def _match_state_batch(runtime, ids):
+    """A prompt whose batch size differs from the held state starts from a fresh zero state."""
+    if int(ids.shape[0]) != int(runtime.rwkv_state[0].wkv.shape[0]):
+        reset_runtime_state(runtime, batch_size=int(ids.shape[0]))
+
+
+def infer_prefill(runtime: RWKV7MRuntime, prompt_ids, *, phase="read_screening_only"):
+    _match_state_batch(runtime, _ids(runtime, prompt_ids))
+    logits, runtime.rwkv_state, runtime.screen_state, stats = prefill(
+        runtime.model, _ids(runtime, prompt_ids), runtime.rwkv_state, runtime.screen_state, phase=phase
+    )
+    return logits, stats
+
+
+def infer_next(runtime: RWKV7MRuntime, token_ids, *, phase="read_screening_only"):
+    tok = torch.as_tensor(token_ids).to(device=runtime.device, dtype=torch.int32)
+    logits, runtime.rwkv_state, runtime.screen_state, stats = decode_one(
+        runtime.model, tok, runtime.rwkv_state, runtime.screen_state, phase=phase
+    )
+    return logits, stats
+
+
+def generate_ids(runtime: RWKV7MRuntime, prompt_ids, *, max_new_tokens=50, temperature=1.0, top_p=0.9,
+                 rng_key=None, phase="read_screening_only"):
+    _match_state_batch(runtime, _ids(runtime, prompt_ids))
+    ids, runtime.rwkv_state, runtime.screen_state = generate(
+        runtime.model, _ids(runtime, prompt_ids), runtime.rwkv_state, runtime.screen_state,
+        max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p, rng_key=rng_key, phase=phase,
+    )
+    return ids
+
+
+def generate_text(runtime: RWKV7MRuntime, prompt: str, *, tokenizer: RWKVTokenizer | None = None,
+                  max_new_tokens=50, temperature=1.0, top_p=0.9, rng_key=None,
+                  phase="read_screening_only", include_prompt: bool = True):
+    tokenizer = tokenizer or RWKVTokenizer()
+    prompt_ids = tokenizer.encode(prompt)
+    if not prompt_ids:
+        raise ValueError("prompt must encode to at least one token")
+    new_ids = generate_ids(
+        runtime, [prompt_ids], max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p,
+        rng_key=rng_key, phase=phase,
+    )
+    generated = [int(x) for x in new_ids[0].tolist()]
+    return tokenizer.decode(prompt_ids + generated if include_prompt else generated)
+
+
+def _batch_to_device(batch, device):
+    out = {}
+    for k, v in batch.items():
+        t = torch.as_tensor(v)
+        out[k] = t.to(device, non_blocking=True) if t.device != device else t
+    return out
+
+
+def train_batch(train_state, batch, runtime: RWKV7MRuntime, *, phase="read_screening_only",
+                carry_state: bool = False, gradient_accumulation_steps: int = 1):
+    """One optimizer update on ``batch`` (host or device tensors).
+
+    ``carry_state=False`` starts from the zero state (the runtime's reusable
+    initial state when the batch size matches); ``carry_state=True`` starts
+    from and writes back ``runtime.rwkv_state`` / ``runtime.screen_state``.
+    """
+    device = runtime.device
+    batch = _batch_to_device(batch, device)
+    if carry_state:
+        rwkv_state, screen_state = runtime.rwkv_state, runtime.screen_state
+    else:
+        bsz = int(batch["input_ids"].shape[0])
+        if bsz == runtime.batch_size:
+            rwkv_state, screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
+        else:
+            rwkv_state = init_rwkv_state(bsz, runtime.config, device=device)
+            screen_state = init_screen_state(
+                bsz, runtime.config.screening if runtime.config.use_screening else _no_screen(runtime.config),
+                device=device,
+            )
+    step_fn = train_state.extras.get("train_step", train_step)
+    train_state, rwkv_state, screen_state, metrics = step_fn(
+        train_state, batch, rwkv_state, screen_state, phase=phase,
+        gradient_accumulation_steps=gradient_accumulation_steps,
+    )
+    if carry_state:
+        runtime.rwkv_state, runtime.screen_state = rwkv_state, screen_state
+    return train_state, metrics
+
+
+def train_binidx(rng_key, config: ModelConfig, data_file, *, ctx_len: int, batch_size: int, num_steps: int,
+                 magic_prime: int | None = None, phase="read_screening_only", carry_state: bool = False,
+                 sampling_mode: str = "magic", print_every: int | None = None,
+                 gradient_accumulation_steps: int = 1, device=None):
+    if carry_state and sampling_mode != "sequential":
+        raise ValueError("carry_state training requires sampling_mode='sequential'")
+    dataset = create_binidx_dataset(
+        data_file, ctx_len=ctx_len, batch_size=batch_size, magic_prime=magic_prime,
+        epoch_steps=num_steps, sampling_mode=sampling_mode,
+    )
+    runtime, train_state = create_train_runtime(rng_key, config, batch_size=batch_size, total_steps=num_steps,
+                                                device=device)
+    losses = []
+    try:
+        for step in range(num_steps):
+            if carry_state and dataset.should_reset_state_before_step(step):
+                runtime.rwkv_state = runtime.initial_rwkv_state
+                runtime.screen_state = runtime.initial_screen_state
+            batch = dataset.get_batch(step)
+            train_state, metrics = train_batch(
+                train_state, batch, runtime, phase=phase, carry_state=carry_state,
+                gradient_accumulation_steps=gradient_accumulation_steps,
+            )
+            loss = float(metrics["loss"])
+            losses.append(loss)
+            if print_every and (step % print_every == 0 or step == num_steps - 1):
+                print(f"step={step} loss={loss:.6f}")
+    finally:
+        dataset.close()
+    return losses, runtime, train_state
+
+
+def reset_runtime_state(runtime: RWKV7MRuntime, config: ModelConfig | None = None, *, batch_size: int | None = None):
+    config = config or runtime.config
+    batch_size = batch_size or runtime.batch_size
+    device = runtime.device
+    runtime.rwkv_state = init_rwkv_state(batch_size, config, device=device)
+    runtime.screen_state = init_screen_state(
+        batch_size, config.screening if config.use_screening else _no_screen(config), device=device
+    )
+    runtime.config = config
+    runtime.batch_size = batch_size
+    runtime.initial_rwkv_state = runtime.rwkv_state
+    runtime.initial_screen_state = runtime.screen_state
+    return runtime
+
+
+__all__ = [
+    "RWKV7MRuntime", "create_runtime", "create_train_runtime", "load_runtime_params", "infer_prefill",
+    "infer_next", "generate_ids", "generate_text", "train_batch", "train_binidx", "reset_runtime_state",
+    "tiny_config", "BinIdxBatchDataset", "create_binidx_dataset",
+]

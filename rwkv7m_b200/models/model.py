@@ -1,0 +1,180 @@
+"""Complete screened RWKV-7 language model.
+
+Skeleton per src/rwkv7m/model/nnx_model.py:1310-1442 of the reference:
+embedding -> per-layer (block, optional screening that reads the layer input
+and the block output) -> final LayerNorm -> LM head.  The recurrent part and
+the head are separate entry points so the training loss can chunk them
+independently.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+from .. import ops
+from ..config import ModelConfig, normalize_phase
+from ..state import LayerRWKVState, LayerScreenState, ModelScreenState
+from .rwkv7 import LayerNorm, Linear, RWKV7Block, _orthogonal, _uniform
+from .screening import StateLevelScreening
+
+
+def torch_dtype(name: str) -> torch.dtype:
+    return {"float32": torch.float32, "bfloat16": torch.bfloat16}[name]
+
+
+class ScreenedRWKVLayer(nn.Module):
+    def __init__(self, config: ModelConfig, layer_idx: int):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.block = RWKV7Block(config, layer_idx)
+        self.has_screening = bool(config.use_screening and layer_idx in config.screening.screened_layers)
+        self.screening = StateLevelScreening(config.screening) if self.has_screening else None
+
+    def forward(self, x, v_first, rwkv_state, screen_state, phase):
+        h_base, v_first, new_rwkv = self.block(x, v_first, rwkv_state)
+        if self.has_screening:
+            h, new_screen, stats = self.screening(x, h_base, screen_state, phase=phase)
+        else:
+            h, new_screen, stats = h_base, screen_state, {}
+        return h, v_first, new_rwkv, new_screen, stats
+
+
+class ScreenedRWKVModel(nn.Module):
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        self.config = config
+        C, V = config.d_model, config.vocab_size
+        self.emb = nn.Embedding(V, C)
+        with torch.no_grad():
+            self.emb.weight.copy_(_uniform((V, C), 1e-4))
+        self.layers = nn.ModuleList(ScreenedRWKVLayer(config, i) for i in range(config.n_layers))
+        self.ln_out = LayerNorm(C)
+        gain = 0.5 * math.sqrt(V / C) if V > C else 0.5
+        if config.lm_head_init == "orthogonal":
+            head = _orthogonal(V, C, gain)
+        else:
+            std = gain / math.sqrt(C) / 0.87962566
+            head = torch.empty(V, C)
+            nn.init.trunc_normal_(head, std=std, a=-2 * std, b=2 * std)
+        self.head = Linear(C, V, init=head)
+        param_dtype = torch_dtype(config.param_dtype)
+        if param_dtype != torch.float32:
+            self.to(param_dtype)
+
+    @property
+    def compute_dtype(self) -> torch.dtype:
+        return torch_dtype(self.config.dtype)
+
+    # ------------------------------------------------------------------
+    def compute_recurrent_hidden(self, input_ids, rwkv_state, screen_state, *, phase="read_screening_only"):
+        cfg = self.config
+        phase = normalize_phase(phase)
+        x = ops.embedding(input_ids, self.emb.weight, self.compute_dtype)
+        screened_idx = {layer: i for i, layer in enumerate(cfg.screening.screened_layers)} if cfg.use_screening else {}
+        v_first = torch.zeros_like(x)
+        new_rwkv = list(rwkv_state)
+        new_screen = list(screen_state.layers) if screen_state is not None else []
+        all_stats = []
+        for idx, layer in enumerate(self.layers):
+            scr = screen_state.layers[screened_idx[idx]] if idx in screened_idx else None
+            if cfg.remat_blocks and torch.is_grad_enabled():
+                x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
+            else:
+                x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)
+            new_rwkv[idx] = rwkv_l
+            if idx in screened_idx:
+                new_screen[screened_idx[idx]] = scr_l
+            if stats:
+                all_stats.append(stats)
+        agg = {}
+        if all_stats:
+            for key in all_stats[0]:
+                agg[key] = torch.stack([torch.as_tensor(s[key]).float() for s in all_stats]).mean()
+        return x, tuple(new_rwkv), ModelScreenState(layers=tuple(new_screen)), agg
+
+    def compute_logits(self, hidden):
+        if hidden.shape[-1] != self.config.d_model:
+            raise ValueError(
+                f"hidden final dimension must equal config.d_model, got {hidden.shape[-1]} and {self.config.d_model}"
+            )
+        return ops.linear(self.ln_out(hidden), self.head.weight)
+
+    def compute_training_loss(self, hidden, targets, mask=None, *, chunk=None):
+        """CE / L2Wrap numerators and denominators without exposing the logits."""
+        ce_total, ce_count, l2_total, l2_count = ops.head_loss(
+            hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, targets, mask, chunk, self.ln_out.eps
+        )
+        return {"ce_total": ce_total, "ce_count": ce_count, "l2_total": l2_total, "l2_count": l2_count}
+
+    def forward(self, input_ids, rwkv_state, screen_state, *, phase="read_screening_only"):
+        hidden, new_rwkv, new_screen, stats = self.compute_recurrent_hidden(
+            input_ids, rwkv_state, screen_state, phase=phase
+        )
+        return self.compute_logits(hidden), new_rwkv, new_screen, stats
+
+
+def _remat_layer(layer, x, v_first, rwkv_state, scr_state, phase):
+    """Per-layer activation recompute (reference: nnx.remat per layer,
+    src/rwkv7m/model/nnx_model.py:1234-1237)."""
+    has_scr = scr_state is not None
+    flat = [x, v_first, rwkv_state.time_mix_x, rwkv_state.channel_mix_x, rwkv_state.wkv]
+    if has_scr:
+        flat += [scr_state.slots, scr_state.ages, scr_state.usage_ema]
+    stat_keys = []
+
+    def run(*args):
+        rs = LayerRWKVState(args[2], args[3], args[4])
+        ss = LayerScreenState(args[5], args[6], args[7]) if has_scr else None
+        h, vf, nr, ns, stats = layer(args[0], args[1], rs, ss, phase)
+        out = [h, vf, nr.time_mix_x, nr.channel_mix_x, nr.wkv]
+        if has_scr:
+            out += [ns.slots, ns.ages, ns.usage_ema]
+        stat_keys[:] = list(stats.keys())
+        out += [torch.as_tensor(stats[k]).float().to(h.device) for k in stat_keys]
+        return tuple(out)
+
+    out = checkpoint(run, *flat, use_reentrant=False)
+    h, vf = out[0], out[1]
+    nr = LayerRWKVState(out[2], out[3], out[4])
+    pos = 5
+    ns = None
+    if has_scr:
+        ns = LayerScreenState(out[5], out[6], out[7])
+        pos = 8
+    stats = {k: out[pos + i] for i, k in enumerate(stat_keys)}
+    return h, vf, nr, ns, stats
+
+
+def initialize_model(seed_or_generator, config: ModelConfig, device=None) -> ScreenedRWKVModel:
+    """Build a model with the reference's initialisation scheme
+    (src/rwkv7m/model/nnx_model.py:449-590,1259-1294) from an integer seed."""
+    if isinstance(seed_or_generator, int):
+        seed = seed_or_generator
+    else:
+        seed = int(torch.as_tensor(seed_or_generator).flatten()[-1].item())
+    with torch.random.fork_rng(devices=[]):
+        torch.manual_seed(seed)
+        model = ScreenedRWKVModel(config)
+    if device is not None:
+        model = model.to(device)
+    return model
+
+
+def count_parameters(model_or_config) -> dict:
+    """Parameter totals split into core and screening."""
+    if isinstance(model_or_config, ModelConfig):
+        with torch.device("meta"):
+            model = ScreenedRWKVModel(model_or_config)
+    else:
+        model = model_or_config
+    core = screening = 0
+    for name, p in model.named_parameters():
+        if ".screening." in name:
+            screening += p.numel()
+        else:
+            core += p.numel()
+    return {"total": core + screening, "core": core, "screening": screening}

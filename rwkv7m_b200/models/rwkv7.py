@@ -1,0 +1,175 @@
+"""RWKV-7 time-mix, channel-mix and block as torch modules.
+
+The math is the reference's (src/rwkv7m/model/nnx_model.py:592-798,841-882);
+the module layout is this framework's own: every matmul weight is stored
+``[out, in]`` (K-major for the TN GEMM kernel), the six token-shift mixes live
+in one ``[6, C]`` parameter, and per-channel vectors are ``[C]``.  The portable
+checkpoint layout (``[in, out]`` kernels, ``[1,1,C]`` vectors) is produced by
+``rwkv7m_b200.io``.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..config import ModelConfig
+from ..state import LayerRWKVState
+
+
+def _uniform(shape, scale):
+    return (torch.rand(shape) * 2.0 - 1.0) * scale
+
+
+def _orthogonal(rows, cols, gain):
+    w = torch.empty(rows, cols)
+    nn.init.orthogonal_(w, gain=gain)
+    return w
+
+
+class LayerNorm(nn.Module):
+    """Affine LayerNorm whose statistics are always fp32."""
+
+    def __init__(self, dim, eps=1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.bias = nn.Parameter(torch.zeros(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class Linear(nn.Module):
+    """Bias-free (by default) projection with ``weight`` stored [out, in]."""
+
+    def __init__(self, d_in, d_out, bias=False, init=None):
+        super().__init__()
+        w = init if init is not None else torch.zeros(d_out, d_in)
+        assert tuple(w.shape) == (d_out, d_in)
+        self.weight = nn.Parameter(w)
+        self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
+
+    def forward(self, x):
+        y = ops.linear(x, self.weight)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y
+
+
+class RWKV7TimeMix(nn.Module):
+    def __init__(self, config: ModelConfig, layer_idx: int):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        C, H, N, L = config.d_model, config.n_heads, config.head_size, config.n_layers
+        ranks = config.lora_ranks()
+        ratio_0_to_1 = layer_idx / max(1, L - 1)
+        ratio_1_to_almost0 = 1.0 - layer_idx / max(1, L)
+        idx = torch.arange(C, dtype=torch.float32)
+        ddd = idx / C
+        powers = (0.2, 0.9, 0.7, 0.7, 0.9, 0.2)  # r, w, k, v, a, g
+        self.x_mix = nn.Parameter(
+            torch.stack([1.0 - torch.pow(ddd, p * ratio_1_to_almost0) for p in powers])
+        )
+        self.receptance = Linear(C, C, init=_uniform((C, C), 0.5 / math.sqrt(C)))
+        self.key = Linear(C, C, init=_uniform((C, C), 0.05 / math.sqrt(C)))
+        self.value = Linear(C, C, init=_uniform((C, C), 0.5 / math.sqrt(C)))
+        self.output = Linear(C, C)
+
+        linear = idx / max(1, C - 1) - 0.5
+        zigzag = ((idx % N) - (N - 1) / 2) / ((N - 1) / 2)
+        zigzag = zigzag * zigzag.abs()
+        www = -6.0 + 6.0 * torch.pow(idx / max(1, C - 1), 1 + ratio_0_to_1**0.3)
+        self.w0 = nn.Parameter(www + 0.5 + zigzag * 2.5)
+        self.w1 = nn.Parameter(torch.zeros(ranks["decay"], C))
+        self.w2 = nn.Parameter(_orthogonal(C, ranks["decay"], 0.1))
+        self.a0 = nn.Parameter(-0.19 + zigzag * 0.3 + linear * 0.4)
+        self.a1 = nn.Parameter(torch.zeros(ranks["aaa"], C))
+        self.a2 = nn.Parameter(_orthogonal(C, ranks["aaa"], 0.1))
+        if layer_idx > 0:
+            self.v0 = nn.Parameter(0.73 - linear * 0.4)
+            self.v1 = nn.Parameter(torch.zeros(ranks["mv"], C))
+            self.v2 = nn.Parameter(_orthogonal(C, ranks["mv"], 0.1))
+        else:
+            self.v0 = self.v1 = self.v2 = None
+        self.g1 = nn.Parameter(torch.zeros(ranks["gate"], C))
+        self.g2 = nn.Parameter(_orthogonal(C, ranks["gate"], 0.1))
+        self.k_k = nn.Parameter(0.71 - linear * 0.1)
+        self.k_a = nn.Parameter(torch.full((C,), 1.02))
+        self.r_k = nn.Parameter(torch.full((H, N), -0.04))
+        self.ln_x = LayerNorm(C, eps=64e-5)  # used as per-head GroupNorm affine
+        with torch.no_grad():
+            self.ln_x.weight.fill_(((1 + layer_idx) / L) ** 0.7)
+
+    def forward(self, x, v_first, prev_x, wkv_state):
+        """x: [B,T,C] (already LN1'd).  Returns (out, v_first, last_x fp32, final wkv state)."""
+        cfg = self.config
+        B, T, C = x.shape
+        H, N = cfg.n_heads, cfg.head_size
+        x_r, x_w, x_k, x_v, x_a, x_g = ops.shift_mix(x, prev_x, self.x_mix)
+        r = ops.linear(x_r, self.receptance.weight)
+        w = ops.decay_lora(x_w, self.w1, self.w2, self.w0)
+        k = ops.linear(x_k, self.key.weight)
+        v = ops.linear(x_v, self.value.weight)
+        if self.layer_idx == 0:
+            v_first = v
+        else:
+            v = ops.value_residual(v, v_first, x_v, self.v1, self.v2, self.v0)
+        a = ops.sigmoid_lora(x_a, self.a1, self.a2, self.a0)
+        g = ops.gate_lora(x_g, self.g1, self.g2)
+        k_mod, neg_kk, kka = ops.kk_pre(k, a, self.k_k, self.k_a, H)
+        y, final_state = ops.wkv7(
+            r.view(B, T, H, N),
+            w.view(B, T, H, N),
+            k_mod.view(B, T, H, N),
+            v.view(B, T, H, N),
+            neg_kk.view(B, T, H, N),
+            kka.view(B, T, H, N),
+            wkv_state,
+        )
+        y = ops.gn_bonus_gate(
+            y.reshape(B, T, C), r, k_mod, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps
+        )
+        out = ops.linear(y, self.output.weight)
+        return out, v_first, x[:, -1].float(), final_state
+
+
+class RWKV7ChannelMix(nn.Module):
+    def __init__(self, config: ModelConfig, layer_idx: int):
+        super().__init__()
+        C, F = config.d_model, config.ffn_dim
+        ratio = 1.0 - layer_idx / max(1, config.n_layers)
+        ddd = torch.arange(C, dtype=torch.float32) / C
+        self.x_k = nn.Parameter(1.0 - torch.pow(ddd, ratio**4))
+        self.key = Linear(C, F, init=_uniform((F, C), 0.5 / math.sqrt(C)))
+        self.value = Linear(F, C)
+
+    def forward(self, x, prev_x):
+        (xk,) = ops.shift_mix(x, prev_x, self.x_k.unsqueeze(0))
+        h = ops.linear_relu_sq(xk, self.key.weight)
+        return ops.linear(h, self.value.weight), x[:, -1].float()
+
+
+class RWKV7Block(nn.Module):
+    def __init__(self, config: ModelConfig, layer_idx: int):
+        super().__init__()
+        self.layer_idx = layer_idx
+        C = config.d_model
+        self.ln0 = LayerNorm(C) if layer_idx == 0 else None
+        self.ln1 = LayerNorm(C)
+        self.ln2 = LayerNorm(C)
+        self.att = RWKV7TimeMix(config, layer_idx)
+        self.ffn = RWKV7ChannelMix(config, layer_idx)
+
+    def forward(self, x, v_first, state: LayerRWKVState):
+        if self.ln0 is not None:
+            x = self.ln0(x)
+        att_out, v_first, tm_x, wkv = self.att(self.ln1(x), v_first, state.time_mix_x, state.wkv)
+        x = x + att_out
+        ffn_out, cm_x = self.ffn(self.ln2(x), state.channel_mix_x)
+        x = x + ffn_out
+        return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)

@@ -1,0 +1,171 @@
+"""Hot-path operators.
+
+Every function here has two bodies: the sm_100a CUDA kernels in
+``rwkv7m_b200.ops.cuda`` (used for every CUDA tensor) and the plain PyTorch
+statement in ``rwkv7m_b200.ops.reference`` (used on CPU, and as the oracle the
+kernels are tested against).  A CUDA tensor never silently falls back: if the
+compiled extension is missing the call raises.  ``reference_mode()`` forces the
+PyTorch bodies on any device and exists for the numerics tests.
+"""
+
+from __future__ import annotations
+
+import contextlib
+
+import torch
+
+from . import reference
+
+_FORCE_REFERENCE = False
+
+
+@contextlib.contextmanager
+def reference_mode(enabled: bool = True):
+    """Run every op through its PyTorch statement (numerics oracle)."""
+    global _FORCE_REFERENCE
+    previous = _FORCE_REFERENCE
+    _FORCE_REFERENCE = enabled
+    try:
+        yield
+    finally:
+        _FORCE_REFERENCE = previous
+
+
+def use_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_REFERENCE
+
+
+def _cuda():
+    from . import cuda  # noqa: WPS433 (deferred: loads the compiled extension)
+
+    return cuda
+
+
+def embedding(ids, weight, dtype):
+    """Row gather from the embedding table, cast to the compute dtype."""
+    if use_cuda(weight):
+        return _cuda().embedding(ids, weight, dtype)
+    return torch.nn.functional.embedding(ids.long(), weight).to(dtype)
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    if use_cuda(x):
+        return _cuda().layer_norm(x, weight, bias, eps)
+    return reference.layer_norm(x, weight, bias, eps)
+
+
+def shift_mix(x, prev, mix):
+    if use_cuda(x):
+        return _cuda().shift_mix(x, prev, mix)
+    return reference.shift_mix(x, prev, mix)
+
+
+def linear(x, weight):
+    if use_cuda(x):
+        return _cuda().linear(x, weight)
+    return reference.linear(x, weight)
+
+
+def linear_relu_sq(x, weight):
+    """relu(x @ W.T)**2 (the GEMM epilogue applies the activation on CUDA)."""
+    if use_cuda(x):
+        return _cuda().linear_relu_sq(x, weight)
+    return reference.relu_sq(reference.linear(x, weight))
+
+
+def decay_lora(x_w, w1, w2, w0):
+    """w = -softplus(-(w0 + tanh(x_w @ w1.T) @ w2.T)) - 0.5."""
+    if use_cuda(x_w):
+        return _cuda().decay_lora(x_w, w1, w2, w0)
+    return reference.decay_clamp(reference.lora(x_w, w1, w2, w0, mid="tanh"))
+
+
+def sigmoid_lora(x_a, a1, a2, a0):
+    """a = sigmoid(a0 + (x_a @ a1.T) @ a2.T)."""
+    if use_cuda(x_a):
+        return _cuda().sigmoid_lora(x_a, a1, a2, a0)
+    return torch.sigmoid(reference.lora(x_a, a1, a2, a0))
+
+
+def gate_lora(x_g, g1, g2):
+    """g = sigmoid(x_g @ g1.T) @ g2.T."""
+    if use_cuda(x_g):
+        return _cuda().gate_lora(x_g, g1, g2)
+    return reference.lora(x_g, g1, g2, None, mid="sigmoid")
+
+
+def value_residual(v, v_first, x_v, v1, v2, v0):
+    """v + (v_first - v) * sigmoid(v0 + (x_v @ v1.T) @ v2.T)."""
+    if use_cuda(v):
+        return _cuda().value_residual(v, v_first, x_v, v1, v2, v0)
+    return v + (v_first - v) * torch.sigmoid(reference.lora(x_v, v1, v2, v0))
+
+
+def kk_pre(k, a, k_k, k_a, n_heads):
+    if use_cuda(k):
+        return _cuda().kk_pre(k, a, k_k, k_a, n_heads)
+    return reference.kk_pre(k, a, k_k, k_a, n_heads)
+
+
+def wkv7(r, w, k, v, a, b, state0):
+    """WKV7 recurrence on [B,T,H,N] vectors with an fp32 [B,H,N,N] initial state."""
+    if use_cuda(r):
+        return _cuda().wkv7(r, w, k, v, a, b, state0)
+    return reference.wkv7(r, w, k, v, a, b, state0)
+
+
+def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+    if use_cuda(y):
+        return _cuda().gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps)
+    return reference.gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps)
+
+
+def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
+    """final LN -> LM head -> (ce_total, ce_count, l2_total, l2_count).
+
+    The [tokens, V] logits are produced chunk by chunk over tokens so the full
+    matrix never exists (reference: head chunks, src/rwkv7m/train/nnx_train.py:278-332).
+    """
+    if use_cuda(hidden):
+        return _cuda().head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk, eps)
+    B, T, C = hidden.shape
+    chunk = chunk or T
+    totals = None
+    for start in range(0, T, chunk):
+        h = reference.layer_norm(hidden[:, start : start + chunk], ln_w, ln_b, eps)
+        logits = reference.linear(h, head_w)
+        part = reference.cross_entropy_l2wrap(
+            logits, targets[:, start : start + chunk], None if mask is None else mask[:, start : start + chunk]
+        )
+        totals = part if totals is None else tuple(a + b for a, b in zip(totals, part))
+    return totals
+
+
+def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars):
+    """Slot-dependent part of the screening memory, sequential over time."""
+    if use_cuda(h_base):
+        return _cuda().screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars)
+    from ..models.screening import screening_scan_reference
+
+    return screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars)
+
+
+__all__ = [
+    "screening_scan",
+    "embedding",
+    "reference",
+    "reference_mode",
+    "use_cuda",
+    "layer_norm",
+    "shift_mix",
+    "linear",
+    "linear_relu_sq",
+    "decay_lora",
+    "sigmoid_lora",
+    "gate_lora",
+    "value_residual",
+    "kk_pre",
+    "wkv7",
+    "gn_bonus_gate",
+    "head_loss",
+]

@@ -1,0 +1,190 @@
+"""Plain PyTorch statements of every hot op.
+
+These are the numerical oracle for the CUDA kernels and the execution path on
+CPU.  Everything here is differentiable through autograd; nothing is fused.
+Math follows the reference's Linen/NNX model (src/rwkv7m/model/rwkv_core.py:54-86,
+src/rwkv7m/model/nnx_model.py:592-798) and losses (src/rwkv7m/model/losses.py:21-69).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    """LayerNorm with fp32 statistics; output in the dtype of ``x``."""
+    y = F.layer_norm(x.float(), (x.shape[-1],), weight.float(), bias.float(), eps)
+    return y.to(x.dtype)
+
+
+def time_shift(x, prev):
+    """``[prev, x[:, :-1]]`` along time.  x: [B,T,C], prev: [B,C]."""
+    return torch.cat([prev.to(x.dtype).unsqueeze(1), x[:, :-1]], dim=1)
+
+
+def shift_mix(x, prev, mix):
+    """Token-shift lerp.  mix: [K,C] -> tuple of K tensors ``x + (shift(x)-x)*mix[k]``."""
+    xx = time_shift(x, prev) - x
+    return tuple(x + xx * mix[i].to(x.dtype) for i in range(mix.shape[0]))
+
+
+def linear(x, weight):
+    """``x @ weight.T`` with ``weight`` stored [out, in]; computed in x's dtype."""
+    return F.linear(x, weight.to(x.dtype))
+
+
+def lora(x, down, up, bias=None, mid="none"):
+    """Low-rank path ``act(x @ down.T) @ up.T (+ bias)``; weights stored [out,in]."""
+    h = F.linear(x, down.to(x.dtype))
+    if mid == "tanh":
+        h = torch.tanh(h)
+    elif mid == "sigmoid":
+        h = torch.sigmoid(h)
+    y = F.linear(h, up.to(x.dtype))
+    if bias is not None:
+        y = y + bias.to(x.dtype)
+    return y
+
+
+def decay_clamp(w_raw):
+    """Soft clamp of the log-log decay into (-inf, -0.5)."""
+    return -F.softplus(-w_raw) - 0.5
+
+
+def kk_pre(k, a, k_k, k_a, n_heads):
+    """Returns (k_mod, neg_kk, kka) from raw k and in-context rate a.
+
+    kk = normalize_per_head(k*k_k) with norm sqrt(sum + 1e-24); the key itself
+    is rescaled *after* kk was formed (nnx_model.py:683-687).
+    """
+    B, T, C = k.shape
+    kk = (k * k_k.to(k.dtype)).view(B, T, n_heads, C // n_heads)
+    kkf = kk.float()
+    kkf = kkf / torch.sqrt((kkf * kkf).sum(-1, keepdim=True) + 1e-24)
+    kk = kkf.to(k.dtype).view(B, T, C)
+    k_mod = k * (1.0 + (a - 1.0) * k_a.to(k.dtype))
+    return k_mod, -kk, kk * a
+
+
+def wkv7(r, w, k, v, a, b, state0):
+    """Sequential WKV7 generalised delta rule.
+
+    Vectors are [B,T,H,N] (any float dtype), ``state0`` is [B,H,N,N] fp32 with
+    index order [value row i, key column j].  ``a`` is the removal key
+    (``-kk``) and ``b`` the replacement key (``kk*a``).  All math is fp32.
+    Returns (y [B,T,H,N] in the vector dtype, final state fp32).
+    """
+    B, T, H, N = r.shape
+    S = state0.float()
+    rf, wf, kf, vf, af, bf = (t.float() for t in (r, w, k, v, a, b))
+    decay = torch.exp(-torch.exp(wf))
+    ys = []
+    for t in range(T):
+        sa = torch.einsum("bhij,bhj->bhi", S, af[:, t])
+        S = (
+            S * decay[:, t].unsqueeze(-2)
+            + sa.unsqueeze(-1) * bf[:, t].unsqueeze(-2)
+            + vf[:, t].unsqueeze(-1) * kf[:, t].unsqueeze(-2)
+        )
+        ys.append(torch.einsum("bhij,bhj->bhi", S, rf[:, t]))
+    y = torch.stack(ys, dim=1).to(r.dtype)
+    return y, S
+
+
+def group_norm_heads(y, weight, bias, n_heads, eps=64e-5):
+    """GroupNorm with one group per head over [.., C]; fp32 statistics."""
+    shape = y.shape
+    C = shape[-1]
+    yf = y.float().reshape(-1, n_heads, C // n_heads)
+    mean = yf.mean(-1, keepdim=True)
+    var = yf.var(-1, unbiased=False, keepdim=True)
+    yn = ((yf - mean) * torch.rsqrt(var + eps)).reshape(-1, C)
+    yn = yn * weight.float() + bias.float()
+    return yn.to(y.dtype).reshape(shape)
+
+
+def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+    """GroupNorm(y) + (sum_n r*k*r_k per head) * v, then times the gate g."""
+    B, T, C = y.shape
+    N = C // n_heads
+    yn = group_norm_heads(y, ln_w, ln_b, n_heads, eps)
+    rk = (r.view(B, T, n_heads, N) * k.view(B, T, n_heads, N) * r_k.to(r.dtype)).sum(-1, keepdim=True)
+    bonus = (rk * v.view(B, T, n_heads, N)).view(B, T, C)
+    return (yn + bonus) * g
+
+
+def relu_sq(x):
+    return torch.relu(x) ** 2
+
+
+def cross_entropy_l2wrap(logits, targets, mask=None):
+    """Returns (ce_total, ce_count, l2_total, l2_count) as fp32 scalars.
+
+    ce_total = sum(mask * nll), l2_total = 0.5e-4 * sum_positions(max_v logit^2)
+    (src/rwkv7m/model/losses.py:21-69).  Log-softmax is taken in fp32.
+    """
+    lf = logits.float()
+    logp = torch.log_softmax(lf, dim=-1)
+    nll = -logp.gather(-1, targets.long().unsqueeze(-1)).squeeze(-1)
+    if mask is None:
+        mask = torch.ones_like(nll)
+    mask = mask.float()
+    ce_total = (nll * mask).sum()
+    ce_count = mask.sum()
+    max_logit = lf.max(dim=-1).values
+    l2_total = 0.5 * 1e-4 * (max_logit * max_logit).sum()
+    l2_count = torch.tensor(float(max_logit.numel()), device=logits.device)
+    return ce_total, ce_count, l2_total, l2_count
+
+
+# ---- screening helpers (src/rwkv7m/model/screening.py:21-88) -----------------
+
+
+def unit_norm(x, eps=1e-6):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps * eps)
+
+
+def bounded_tau(theta):
+    return 2.0 * torch.sigmoid(theta) - 1.0
+
+
+def theta_from_tau(tau):
+    p = torch.clamp((torch.as_tensor(tau, dtype=torch.float32) + 1.0) / 2.0, 1e-4, 1.0 - 1e-4)
+    return torch.log(p) - torch.log1p(-p)
+
+
+def trim_square(sim, tau, eps=1e-6):
+    return torch.relu((sim - tau) / (1.0 - tau + eps)) ** 2
+
+
+def relevance_with_warmup(sim, tau, alpha, gamma=8.0):
+    return (1.0 - alpha) * trim_square(sim, tau) + alpha * torch.sigmoid(gamma * (sim - tau))
+
+
+def tanh_norm(z, cap=1.0, eps=1e-6):
+    norm = torch.sqrt((z * z).sum(-1, keepdim=True) + eps * eps)
+    return cap * torch.tanh(norm / cap) / norm * z
+
+
+def update_rate_from_half_life(half_life_tokens):
+    """EMA rate whose retained weight halves after ``half_life_tokens`` updates."""
+    h = torch.as_tensor(half_life_tokens, dtype=torch.float32)
+    return -torch.expm1(-torch.log(torch.tensor(2.0)) / h)
+
+
+def compute_slot_delta(x, h, slot_embed, kernel, bias):
+    """tanh of the concatenated delta projection, evaluated split by input block.
+
+    kernel is [2C+ds, ds] in [in,out] order as in the portable checkpoint.
+    """
+    C = x.shape[-1]
+    ds = slot_embed.shape[-1]
+    if h.shape[-1] != C:
+        raise ValueError("x and h must have the same final dimension")
+    if kernel.shape[0] != 2 * C + ds:
+        raise ValueError("delta kernel input dimension does not match x/h/slot dimensions")
+    x_term = x @ kernel[:C]
+    h_term = h @ kernel[C : 2 * C]
+    slot_term = slot_embed @ kernel[2 * C :]
+    return torch.tanh(x_term.unsqueeze(-2) + h_term.unsqueeze(-2) + slot_term + bias)

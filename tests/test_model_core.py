@@ -1,0 +1,121 @@
+"""Model semantics on CPU: shapes, prefill == stepwise decode, zero read-out,
+state handling, parameter counts."""
+
+import pytest
+import torch
+
+import rwkv7m_b200 as R
+from rwkv7m_b200.models import count_parameters
+from rwkv7m_b200.train import generate_toy_batch
+
+
+def _runtime(use_screening=True, write=False, batch=2, seed=0):
+    cfg = R.tiny_config(use_screening=use_screening)
+    cfg.screening.use_write_screening = write
+    return R.create_runtime(seed, cfg, batch_size=batch), cfg
+
+
+def test_logits_shape_and_state_shapes():
+    rt, cfg = _runtime()
+    ids = torch.randint(0, 256, (2, 6), dtype=torch.int32)
+    logits, stats = R.infer_prefill(rt, ids)
+    assert logits.shape == (2, 6, 256)
+    assert rt.rwkv_state[0].wkv.shape == (2, 4, 16, 16)
+    assert rt.rwkv_state[0].wkv.dtype == torch.float32
+    assert rt.screen_state.layers[0].slots.shape == (2, 4, 32)
+    assert "rel_read_mean" in stats
+
+
+@pytest.mark.parametrize("phase,write", [("read_screening_only", False), ("read_write", True)])
+def test_prefill_equals_stepwise_decode(phase, write):
+    rt, cfg = _runtime(write=write)
+    _randomize(rt.model)
+    ids = torch.randint(0, 256, (2, 7), dtype=torch.int32)
+    full, _ = R.infer_prefill(rt, ids, phase=phase)
+    R.reset_runtime_state(rt)
+    steps = []
+    for t in range(7):
+        logit, _ = R.infer_next(rt, ids[:, t], phase=phase)
+        steps.append(logit)
+    stepwise = torch.stack(steps, dim=1)
+    assert torch.allclose(full, stepwise, atol=1e-4, rtol=1e-4)
+
+
+def _randomize(model, scale=0.05):
+    gen = torch.Generator().manual_seed(7)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.ndim >= 2 and float(p.abs().max()) == 0.0:
+                p.copy_(torch.randn(p.shape, generator=gen) * scale)
+
+
+def test_all_irrelevant_slots_give_zero_readout():
+    rt, cfg = _runtime()
+    _randomize(rt.model)
+    scr = rt.model.layers[1].screening
+    with torch.no_grad():
+        scr.tau_r_raw.fill_(20.0)  # tau -> 1: nothing passes the trim
+    ids = torch.randint(0, 256, (2, 5), dtype=torch.int32)
+    x = torch.randn(2, 5, cfg.d_model)
+    h_base = torch.randn(2, 5, cfg.d_model)
+    h, _, stats = scr(x, h_base, rt.screen_state.layers[0])
+    assert torch.allclose(h, h_base, atol=1e-6)
+    assert float(stats["rel_read_max"]) == 0.0
+
+
+def test_phase_alias_and_rejection():
+    assert R.normalize_phase("read_only") == "read_screening_only"
+    with pytest.raises(ValueError):
+        R.normalize_phase("write_only")
+
+
+def test_ages_accumulate_only_in_write_phase():
+    rt, cfg = _runtime(write=True)
+    ids = torch.randint(0, 256, (2, 5), dtype=torch.int32)
+    R.infer_prefill(rt, ids, phase="read_screening_only")
+    assert float(rt.screen_state.layers[0].ages.abs().sum()) == 0.0
+    R.infer_prefill(rt, ids, phase="read_write")
+    assert float(rt.screen_state.layers[0].ages.sum()) > 0.0
+
+
+def test_config_validation_errors():
+    with pytest.raises(ValueError):
+        R.ModelConfig(d_model=64, n_heads=3, head_size=16)
+    with pytest.raises(ValueError):
+        R.ModelConfig(d_model=64, n_heads=4, head_size=16, dtype="float16")
+    with pytest.raises(ValueError):
+        R.ScreeningConfig(n_slots=4, bank_ids=(0, 1))
+    with pytest.raises(ValueError):
+        R.ScreeningConfig(write_rel_floor=-1.0)
+
+
+def test_preset_parameter_counts_exact():
+    for name in R.MODEL_PRESET_NAMES:
+        assert count_parameters(R.model_preset(name))["total"] == R.MODEL_PRESET_PARAMETER_COUNTS[name]
+    assert count_parameters(R.bench_config("1.5b"))["total"] == 1_530_550_272
+    assert count_parameters(R.bench_config("0.19b"))["total"] == 191_034_624
+
+
+def test_train_reset_vs_carry_semantics():
+    cfg = R.tiny_config()
+    rt, ts = R.create_train_runtime(0, cfg, batch_size=2, total_steps=10)
+    batch = generate_toy_batch(2, 2, 8, 256)
+    ts, _ = R.train_batch(ts, batch, rt)
+    assert float(rt.rwkv_state[0].wkv.abs().sum()) == 0.0  # reset mode leaves runtime state alone
+    ts, _ = R.train_batch(ts, batch, rt, carry_state=True)
+    assert float(rt.rwkv_state[0].wkv.abs().sum()) > 0.0
+    assert not rt.rwkv_state[0].wkv.requires_grad
+
+
+def test_tiny_train_then_greedy_generate():
+    cfg = R.tiny_config()
+    rt, ts = R.create_train_runtime(0, cfg, batch_size=2, total_steps=10)
+    batch = generate_toy_batch(2, 2, 8, 256)
+    losses = []
+    for _ in range(4):
+        ts, m = R.train_batch(ts, batch, rt)
+        losses.append(float(m["loss"]))
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
+    ids = R.generate_ids(rt, [[1, 2, 3]], max_new_tokens=8, temperature=0.0)
+    again = R.generate_ids(R.reset_runtime_state(rt, batch_size=1), [[1, 2, 3]], max_new_tokens=8, temperature=0.0)
+    assert ids.shape == (1, 8) and torch.equal(ids, again)
