@@ -1,0 +1,383 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with
+// the fp32 accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+// Persistent, warp-specialised CTA of 192 threads (one CTA per SM):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one elected lane)
+//   warps 2..5  epilogue: each reads its 32-lane quarter of the accumulator
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue
+// of tile i overlaps the main loop of tile i+1.  Operands may be K-major or
+// MN-major in global memory; the three layouts cover y = x W^T, dx = dy W and
+// dW = dy^T x without any transposition pass.  Every wait is bounded: when a
+// limit runs out the CTA records an error code, drains and frees TMEM.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rk {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded mbarrier wait with an explicit suspend hint; gives up after ~2 s or when
+// another role of this CTA already gave up.
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(2000u)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+
+template <int BN>
+struct Tile {
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = BN == 256 ? 512 : (BN == 128 ? 256 : 128);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, int A_MN, int B_MN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 void* __restrict__ Dptr, int M, int N, int K, int ldd, int* __restrict__ err) {
+  using TL = Tile<BN>;
+  constexpr int kStages = TL::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * TL::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tfull_bar = bars + 2 * kStages;
+  uint64_t* tempty_bar = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull_bar[s], 1); mbar_init(&tempty_bar[s], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc(tmem_slot, TL::kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM;
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * TL::kStageBytes;
+          uint8_t* sb = sa + TL::kABytes;
+          mbar_expect_tx(&full_bar[stage], TL::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * c, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * c, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x10000 | 1); }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!wait_bar(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * TL::kStageBytes);
+          const uint32_t sb = sa + TL::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN == 0 ? umma_smem_desc_sw128(sa + k * 32, 16, 1024)
+                                          : umma_smem_desc_sw128(sa + k * 2048, BK * 128, 1024);
+            const uint64_t db = B_MN == 0 ? umma_smem_desc_sw128(sb + k * 32, 16, 1024)
+                                          : umma_smem_desc_sw128(sb + k * 2048, BK * 128, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x10000 | 2); }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * BM;
+      const int n0 = (tile / tiles_m) * BN;
+      if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          if (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + (size_t)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1; }
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                pk[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float x0 = __uint_as_float(v[j]);
+                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; }
+                out[j] = f2bf(x0);
+              }
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(Dptr) + (size_t)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              float4* o4 = reinterpret_cast<float4*>(out);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 t = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                if (EPI == kEpiAccumF32) { float4 o = o4[j]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
+                o4[j] = t;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float t = __uint_as_float(v[j]);
+                if (EPI == kEpiAccumF32) t += out[j];
+                out[j] = t;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x10000 | 3); }
+  }
+
+  // ---------------- teardown ----------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // give copies and MMAs that were already issued time to land before TMEM/smem are released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) { }
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TL::kTmemCols); }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.cols * 0xC2B2AE3D27D4EB4Full;
+    h ^= ((size_t)k.ld << 20) ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+// Row-major bf16 matrix [rows, cols] with leading dimension ld; box = 64 columns x box_rows rows, 128B swizzle.
+bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int A_MN, int B_MN, int EPI>
+int launch(const GemmArgs& p, cudaStream_t st) {
+  using TL = Tile<BN>;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (A_MN == 0) ok = make_map(&ta, p.A, p.M, p.K, p.lda, BM); else ok = make_map(&ta, p.A, p.K, p.M, p.lda, BK);
+  if (!ok) return 2;
+  if (B_MN == 0) ok = make_map(&tb, p.B, p.N, p.K, p.ldb, BN); else ok = make_map(&tb, p.B, p.K, p.N, p.ldb, BK);
+  if (!ok) return 2;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::kSmemBytes) != cudaSuccess) return 3;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, p.error_flag);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+template <int BN, int A_MN, int B_MN>
+int launch_epi(const GemmArgs& p, cudaStream_t st) {
+  switch (p.epilogue) {
+    case kEpiStoreBf16: return launch<BN, A_MN, B_MN, kEpiStoreBf16>(p, st);
+    case kEpiReluSqBf16: return launch<BN, A_MN, B_MN, kEpiReluSqBf16>(p, st);
+    case kEpiStoreF32: return launch<BN, A_MN, B_MN, kEpiStoreF32>(p, st);
+    case kEpiAccumF32: return launch<BN, A_MN, B_MN, kEpiAccumF32>(p, st);
+  }
+  return 5;
+}
+
+template <int BN>
+int launch_layout(const GemmArgs& p, cudaStream_t st) {
+  switch (p.layout) {
+    case kGemmTN: return launch_epi<BN, 0, 0>(p, st);
+    case kGemmNN: return launch_epi<BN, 0, 1>(p, st);
+    case kGemmNT_wgrad: return launch_epi<BN, 1, 1>(p, st);
+  }
+  return 5;
+}
+
+}  // namespace
+
+int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return 1;
+  // TMA needs 16-byte aligned bases and row pitches.
+  if ((reinterpret_cast<uintptr_t>(p.A) & 15) || (reinterpret_cast<uintptr_t>(p.B) & 15) ||
+      (reinterpret_cast<uintptr_t>(p.D) & 15) || (p.lda & 7) || (p.ldb & 7))
+    return 6;
+  const bool out_bf16 = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16;
+  if (p.ldd & (out_bf16 ? 7 : 3)) return 6;
+  if (p.error_flag == nullptr) return 7;
+  if (p.N > 128) return launch_layout<256>(p, st);
+  return launch_layout<128>(p, st);
+}
+
+}  // namespace rk

@@ -1,0 +1,64 @@
+// Host-callable launchers of the sm_100a kernels.  Nothing here depends on
+// PyTorch: arguments are raw device pointers plus a CUDA stream, so the same
+// entry points serve the Python bindings and C callers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rk {
+
+// ---- WKV7 ---------------------------------------------------------------------
+struct WkvArgs {
+  int B, T, H, N;
+  int interval;     // checkpoint interval in steps (training forward / backward)
+  bool is_bf16;     // vector dtype: bf16 (true) or fp32 (false)
+  const void *r, *w, *k, *v, *a, *b;   // [B,T,H,N]
+  const float* s0;                      // [B,H,N,N]
+  void* y;                              // [B,T,H,N]
+  float* sT;                            // [B,H,N,N]
+  float* sa;                            // [B,T,H,N] fp32, nullptr = inference forward
+  float* ckpt;                          // [ceil(T/interval), B*H, N, N]
+  // backward only
+  const void* dy;
+  const float* dsT;                     // may be nullptr
+  void *dr, *dw, *dk, *dv, *da, *db;
+  float* ds0;
+};
+int wkv7_forward(const WkvArgs& p, cudaStream_t st);
+int wkv7_backward(const WkvArgs& p, cudaStream_t st);
+
+// ---- optimizer ------------------------------------------------------------------
+// out[0] += sum(g^2) over n elements (out must be zeroed by the caller).
+void grad_norm_sq(const void* g, bool g_is_bf16, int64_t n, float* out, cudaStream_t st);
+
+struct AdamWArgs {
+  void* param; bool param_bf16;          // master parameters (fp32 or bf16)
+  void* grad; bool grad_bf16;            // gradients; zeroed after use when zero_grad
+  void* m; void* v; bool state_bf16;     // Adam moments
+  void* shadow;                          // optional bf16 compute copy (nullptr = none)
+  const float* norm_sq;                  // device scalar: global sum of squared grads
+  int64_t begin, end;                    // element range to update
+  int64_t n_decay, n_nodecay_end;        // group boundaries: [0,n_decay) decayed, [n_nodecay_end, ...) is w0 (x2)
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2, max_norm, grad_scale;
+  bool zero_grad;
+};
+void adamw_flat(const AdamWArgs& p, cudaStream_t st);
+
+// ---- GEMM (tcgen05) -------------------------------------------------------------
+enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
+enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3 };
+struct GemmArgs {
+  // D[M,N] = A (M x K) * B (K x N) with fp32 accumulation.
+  //  layout kGemmTN      : A stored [M,K] row-major, B stored [N,K] row-major      (y = x W^T)
+  //  layout kGemmNN      : A stored [M,K] row-major, B stored [K,N] row-major      (dx = dy W)
+  //  layout kGemmNT_wgrad: A stored [K,M] row-major, B stored [K,N] row-major      (dW = dy^T x)
+  const void* A; const void* B; void* D;
+  int M, N, K;
+  int lda, ldb, ldd;   // leading dimensions in elements of the stored matrices
+  int layout, epilogue;
+  int* error_flag;     // device int, set non-zero if a bounded wait ran out
+};
+int gemm_bf16(const GemmArgs& p, cudaStream_t st);
+
+}  // namespace rk

@@ -125,6 +125,8 @@ class FlatParams:
             p.data = self.master[off : off + numel].view(p.shape)
             if self.bound:
                 p.grad = self.grad[off : off + numel].view(p.shape)
+                # GEMM epilogues accumulate weight gradients straight into this view
+                p._main_grad = p.grad
             if self.compute is not None:
                 p._compute = self.compute[off : off + numel].view(p.shape)
         self.sync_compute()

@@ -1,0 +1,97 @@
+"""tcgen05 GEMM against torch.matmul in fp32."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _K():
+    from rwkv7m_b200.ops import cuda as K
+
+    return K
+
+
+def _rand(*shape, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * 0.5).to(device="cuda", dtype=torch.bfloat16)
+
+
+SHAPES = [(128, 256, 64), (256, 512, 128), (384, 256, 512), (200, 136, 72), (64, 32, 2048), (1000, 768, 320),
+          (4096, 2048, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_tn_forward_layout(M, N, K):
+    kk = _K()
+    a, b = _rand(M, K, seed=1), _rand(N, K, seed=2)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    kk.gemm_error_reset(a)
+    kk.gemm(a, b, out, kk.GEMM_TN, kk.EPI_BF16)
+    ref = a.float() @ b.float().t()
+    assert kk.gemm_error_code(a) == 0
+    assert torch.allclose(out.float(), ref, atol=0.05 + 0.01 * K**0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_nn_dgrad_layout(M, N, K):
+    kk = _K()
+    a, b = _rand(M, K, seed=3), _rand(K, N, seed=4)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    kk.gemm_error_reset(a)
+    kk.gemm(a, b, out, kk.GEMM_NN, kk.EPI_BF16)
+    ref = a.float() @ b.float()
+    assert kk.gemm_error_code(a) == 0
+    assert torch.allclose(out.float(), ref, atol=0.05 + 0.01 * K**0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_wgrad_layout_store_and_accumulate(M, N, K):
+    kk = _K()
+    a, b = _rand(K, M, seed=5), _rand(K, N, seed=6)
+    out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    kk.gemm_error_reset(a)
+    kk.gemm(a, b, out, kk.GEMM_WGRAD, kk.EPI_F32)
+    ref = a.float().t() @ b.float()
+    assert kk.gemm_error_code(a) == 0
+    assert torch.allclose(out, ref, atol=1e-2 + 1e-3 * K**0.5, rtol=1e-3)
+    kk.gemm(a, b, out, kk.GEMM_WGRAD, kk.EPI_ACC_F32)
+    assert torch.allclose(out, 2 * ref, atol=2e-2 + 2e-3 * K**0.5, rtol=1e-3)
+
+
+def test_relu_sq_epilogue():
+    kk = _K()
+    a, b = _rand(300, 256, seed=7), _rand(520, 256, seed=8)
+    out = torch.empty(300, 520, dtype=torch.bfloat16, device="cuda")
+    kk.gemm(a, b, out, kk.GEMM_TN, kk.EPI_RELUSQ)
+    ref = torch.relu(a.float() @ b.float().t()) ** 2
+    assert torch.allclose(out.float(), ref, atol=0.5, rtol=3e-2)
+
+
+def test_strided_views_as_operands():
+    kk = _K()
+    big = _rand(256, 1024, seed=9)
+    w = _rand(128, 1024 + 64, seed=10)
+    a, b = big[:, 256:768], w[:, 64:576]  # column slices: leading dimension > width
+    out = torch.empty(256, 128, dtype=torch.bfloat16, device="cuda")
+    kk.gemm(a, b, out, kk.GEMM_TN, kk.EPI_BF16)
+    ref = a.float() @ b.float().t()
+    assert torch.allclose(out.float(), ref, atol=0.3, rtol=2e-2)
+
+
+def test_linear_function_gradients_match_autograd():
+    from rwkv7m_b200 import ops
+
+    x = _rand(4, 96, 256, seed=11).requires_grad_(True)
+    w = _rand(384, 256, seed=12).requires_grad_(True)
+    go = _rand(4, 96, 384, seed=13)
+    y = ops.linear(x, w)
+    y.backward(go)
+    gx, gw = x.grad.clone(), w.grad.clone()
+    x.grad = w.grad = None
+    with ops.reference_mode():
+        y_ref = ops.linear(x, w)
+        y_ref.backward(go)
+    assert torch.allclose(y.float(), y_ref.float(), atol=0.2, rtol=2e-2)
+    assert torch.allclose(gx.float(), x.grad.float(), atol=0.3, rtol=3e-2)
+    assert torch.allclose(gw.float(), w.grad.float(), atol=1.0, rtol=3e-2)

@@ -1,0 +1,96 @@
+"""WKV7 CUDA kernels against the fp32 PyTorch recurrence."""
+
+import pytest
+import torch
+
+from rwkv7m_b200 import ops
+from rwkv7m_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, T, H, N, dtype, seed=0, device="cuda"):
+    g = torch.Generator().manual_seed(seed)
+    r = torch.randn(B, T, H, N, generator=g) * 0.5
+    w = -torch.nn.functional.softplus(-torch.randn(B, T, H, N, generator=g)) - 0.5
+    k = torch.randn(B, T, H, N, generator=g) * 0.5
+    v = torch.randn(B, T, H, N, generator=g) * 0.5
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N, generator=g), dim=-1)
+    a_lr = torch.sigmoid(torch.randn(B, T, H, N, generator=g))
+    a, b = -kk, kk * a_lr
+    s0 = torch.randn(B, H, N, N, generator=g) * 0.1
+    vecs = [t.to(device=device, dtype=dtype) for t in (r, w, k, v, a, b)]
+    return vecs, s0.to(device)
+
+
+@pytest.mark.parametrize("N", [16, 32, 64])
+@pytest.mark.parametrize("T", [1, 5, 16, 37])
+def test_forward_fp32(N, T):
+    vecs, s0 = _inputs(2, T, 3, N, torch.float32)
+    y, sT = ops.wkv7(*vecs, s0)
+    y_ref, sT_ref = R.wkv7(*vecs, s0)
+    assert torch.allclose(y, y_ref, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(sT, sT_ref, atol=2e-5, rtol=1e-4)
+
+
+def test_forward_bf16():
+    vecs, s0 = _inputs(2, 64, 2, 64, torch.bfloat16)
+    y, sT = ops.wkv7(*vecs, s0)
+    y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
+    assert torch.allclose(y.float(), y_ref, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(sT, sT_ref, atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("N,T", [(16, 7), (64, 16), (64, 45), (32, 33)])
+def test_all_gradients_fp32(N, T):
+    vecs, s0 = _inputs(2, T, 2, N, torch.float32, seed=3)
+    g = torch.Generator().manual_seed(9)
+    wy = torch.randn(2, T, 2, N, generator=g).cuda()
+    ws = torch.randn(2, 2, N, N, generator=g).cuda()
+
+    def run(fn):
+        leaves = [t.clone().requires_grad_(True) for t in vecs] + [s0.clone().requires_grad_(True)]
+        y, sT = fn(*leaves)
+        loss = (y * wy).sum() + (sT * ws).sum()
+        loss.backward()
+        return [l.grad for l in leaves]
+
+    got = run(ops.wkv7)
+    want = run(R.wkv7)
+    for name, a, b in zip("r w k v a b s0".split(), got, want):
+        scale = float(b.abs().max()) + 1e-6
+        assert float((a - b).abs().max()) / scale < 2e-3, name
+
+
+def test_gradients_bf16_tolerance():
+    vecs, s0 = _inputs(1, 48, 2, 64, torch.bfloat16, seed=5)
+    wy = torch.randn(1, 48, 2, 64, device="cuda")
+
+    def run(fn, cast):
+        leaves = [cast(t).clone().requires_grad_(True) for t in vecs]
+        y, _ = fn(*leaves, s0)
+        (y.float() * wy).sum().backward()
+        return [l.grad.float() for l in leaves]
+
+    got = run(ops.wkv7, lambda t: t)
+    want = run(R.wkv7, lambda t: t.float())
+    for name, a, b in zip("r w k v a b".split(), got, want):
+        rel = float((a - b).norm() / (b.norm() + 1e-9))
+        assert rel < 3e-2, (name, rel)
+
+
+def test_chunked_call_equals_single_call():
+    vecs, s0 = _inputs(2, 40, 2, 64, torch.float32, seed=11)
+    y_full, s_full = ops.wkv7(*vecs, s0)
+    y1, s1 = ops.wkv7(*[t[:, :23].contiguous() for t in vecs], s0)
+    y2, s2 = ops.wkv7(*[t[:, 23:].contiguous() for t in vecs], s1)
+    assert torch.allclose(torch.cat([y1, y2], 1), y_full, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(s2, s_full, atol=1e-5, rtol=1e-5)
+
+
+def test_rejects_bad_state_dtype():
+    vecs, s0 = _inputs(1, 4, 1, 64, torch.bfloat16)
+    from rwkv7m_b200.ops.build import load_extension
+
+    with pytest.raises(RuntimeError):
+        load_extension().wkv7_fwd(*vecs, s0.double(), False, 16)
