@@ -1,0 +1,134 @@
+"""Kernel microbenchmarks: WKV7 forward / forward+backward and the tcgen05 GEMM.
+
+Counterpart of the reference's scripts/benchmark_wkv_accelerator.py:63-97,167-169
+(synchronised per call, warm-up, percentile summary, JSON output), timed here
+with CUDA events and an L2 flush between iterations.  WKV FLOPs use the
+"useful" count 9*N^2 per token and head forward, 2.5x that for backward.
+
+    python -m rwkv7m_b200.cli.bench_kernels --what wkv,gemm --json-out out.json
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return {"median_ms": statistics.median(times), "min_ms": min(times), "max_ms": max(times), "iters": iters}
+
+
+def bench_wkv(shapes, dtype=torch.bfloat16, iters=10):
+    from rwkv7m_b200 import ops
+
+    out = []
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for (T, B, H, N) in shapes:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        mk = lambda s=0.5: (torch.randn(B, T, H, N, device="cuda", generator=g) * s)
+        r, k, v = mk(), mk(), mk()
+        w = -torch.nn.functional.softplus(-mk(1.0)) - 0.5
+        kk = torch.nn.functional.normalize(mk(1.0), dim=-1)
+        a, b = -kk, kk * torch.sigmoid(mk(1.0))
+        vecs = [t.to(dtype).contiguous() for t in (r, w, k, v, a, b)]
+        s0 = torch.zeros(B, H, N, N, device="cuda")
+
+        def fwd():
+            with torch.no_grad():
+                ops.wkv7(*vecs, s0)
+
+        leaves = [t.clone().requires_grad_(True) for t in vecs]
+        dy = torch.randn(B, T, H, N, device="cuda").to(dtype)
+
+        def fwdbwd():
+            y, _ = ops.wkv7(*leaves, s0)
+            y.backward(dy)
+            for l in leaves:
+                l.grad = None
+
+        tf = _time(fwd, iters, flush=flush)
+        tb = _time(fwdbwd, iters, flush=flush)
+        flops_f = 9.0 * N * N * T * B * H
+        out.append({
+            "kernel": "wkv7", "T": T, "B": B, "H": H, "N": N, "dtype": str(dtype).split(".")[-1],
+            "fwd_ms": tf["median_ms"], "fwd_bwd_ms": tb["median_ms"],
+            "fwd_tflops": flops_f / tf["median_ms"] / 1e9,
+            "fwd_bwd_tflops": 3.5 * flops_f / tb["median_ms"] / 1e9,
+        })
+    return out
+
+
+def bench_gemm(shapes, iters=10):
+    from rwkv7m_b200.ops import cuda as K
+
+    out = []
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for (M, N, Kd) in shapes:
+        a = torch.randn(M, Kd, device="cuda").bfloat16()
+        b = torch.randn(N, Kd, device="cuda").bfloat16()
+        bt = b.t().contiguous()
+        at = a.t().contiguous()
+        d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        d32 = torch.empty(M, N, device="cuda", dtype=torch.float32)
+        row = {"kernel": "gemm_bf16", "M": M, "N": N, "K": Kd}
+        flops = 2.0 * M * N * Kd
+        K.gemm_error_reset(a)
+        for name, fn in (
+            ("tn", lambda: K.gemm(a, b, d, K.GEMM_TN, K.EPI_BF16)),
+            ("nn", lambda: K.gemm(a, bt, d, K.GEMM_NN, K.EPI_BF16)),
+            ("wgrad_f32acc", lambda: K.gemm(at, bt, d32, K.GEMM_WGRAD, K.EPI_ACC_F32)),
+            ("cublas_tn", lambda: torch.matmul(a, b.t(), out=d)),
+        ):
+            t = _time(fn, iters, flush=flush)
+            row[f"{name}_ms"] = t["median_ms"]
+            row[f"{name}_tflops"] = flops / t["median_ms"] / 1e9
+        row["error_flag"] = K.gemm_error_code(a)
+        out.append(row)
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="wkv,gemm")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json-out", default=None)
+    ap.add_argument("--small", action="store_true", help="small shapes only (profiling captures)")
+    args = ap.parse_args(argv)
+    results = []
+    if "wkv" in args.what:
+        shapes = [(128, 1, 12, 64), (512, 4, 12, 64)] if args.small else [
+            (128, 1, 12, 64), (128, 4, 12, 64), (512, 1, 12, 64), (512, 4, 12, 64), (4096, 8, 12, 64), (4096, 8, 32, 64)]
+        results += bench_wkv(shapes, iters=args.iters)
+    if "gemm" in args.what:
+        shapes = [(4096, 2048, 2048)] if args.small else [
+            (32768, 2048, 2048), (32768, 8192, 2048), (32768, 2048, 8192), (8192, 65536, 2048), (32768, 128, 2048),
+            (32768, 768, 768), (8192, 8192, 8192)]
+        results += bench_gemm(shapes, iters=args.iters)
+    for r in results:
+        print(json.dumps(r))
+    if args.json_out:
+        with open(args.json_out, "w") as f:
+            json.dump(results, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

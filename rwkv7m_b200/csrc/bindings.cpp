@@ -166,6 +166,221 @@ int64_t gemm_error(const Tensor& like) {
 
 void gemm_error_reset(const Tensor& like) { gemm_error_flag(like.device()).zero_(); }
 
+// ---- fused memory-bound kernels -------------------------------------------------------
+
+void check_act(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kBFloat16, name,
+              " must be a contiguous bf16 CUDA tensor");
+}
+void check_par(const Tensor& t, int64_t n, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kFloat && t.numel() == n, name,
+              " must be a contiguous fp32 CUDA tensor with ", n, " elements");
+}
+
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_act(x, "x");
+  const int64_t C = x.size(-1), M = x.numel() / C;
+  TORCH_CHECK(C % 2 == 0, "layernorm: width must be even");
+  check_par(w, C, "weight"); check_par(b, C, "bias");
+  Tensor y = torch::empty_like(x);
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor mean = torch::empty({M}, f32), rstd = torch::empty({M}, f32);
+  rk::layernorm_fwd(x.data_ptr(), w.data_ptr<float>(), b.data_ptr<float>(), y.data_ptr(), mean.data_ptr<float>(),
+                    rstd.data_ptr<float>(), (int)M, (int)C, (float)eps, stream());
+  return {y, mean, rstd};
+}
+
+std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
+                                  const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_act(dy, "dy"); check_act(x, "x");
+  const int64_t C = x.size(-1), M = x.numel() / C;
+  check_par(w, C, "weight"); check_par(mean, M, "mean"); check_par(rstd, M, "rstd");
+  TORCH_CHECK(dy.numel() == x.numel());
+  Tensor dx = torch::empty_like(x);
+  int parts = (int)std::min<int64_t>(64, std::max<int64_t>(1, M / 256));
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dwp = torch::empty({parts, C}, f32), dbp = torch::empty({parts, C}, f32);
+  rk::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                    dx.data_ptr(), dwp.data_ptr<float>(), dbp.data_ptr<float>(), parts, (int)M, (int)C, stream());
+  return {dx, dwp.sum(0), dbp.sum(0)};
+}
+
+Tensor shift_mix_fwd(const Tensor& x, const Tensor& prev, const Tensor& mix) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_act(x, "x");
+  TORCH_CHECK(x.dim() == 3, "shift_mix: x must be [B,T,C]");
+  const int64_t B = x.size(0), T = x.size(1), C = x.size(2), K = mix.size(0);
+  TORCH_CHECK(K == 1 || K == 6, "shift_mix supports 1 or 6 mixes");
+  TORCH_CHECK(C % 2 == 0);
+  check_par(prev, B * C, "prev"); check_par(mix, K * C, "mix");
+  Tensor out = torch::empty({K, B, T, C}, x.options());
+  rk::shift_mix_fwd(x.data_ptr(), prev.data_ptr<float>(), mix.data_ptr<float>(), out.data_ptr(), (int)K, (int)B,
+                    (int)T, (int)C, stream());
+  return out;
+}
+
+std::vector<Tensor> shift_mix_bwd(const std::vector<Tensor>& dout, const Tensor& x, const Tensor& prev,
+                                  const Tensor& mix) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_act(x, "x");
+  const int64_t B = x.size(0), T = x.size(1), C = x.size(2), K = mix.size(0);
+  TORCH_CHECK((int64_t)dout.size() == K, "shift_mix_bwd: one gradient per mix");
+  const void* gp[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int64_t z = 0; z < K; ++z) {
+    check_act(dout[z], "dout");
+    TORCH_CHECK(dout[z].numel() == x.numel(), "shift_mix_bwd: gradient shape mismatch");
+    gp[z] = dout[z].data_ptr();
+  }
+  check_par(prev, B * C, "prev"); check_par(mix, K * C, "mix");
+  Tensor dx = torch::empty_like(x);
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dprev = torch::empty({B, C}, f32);
+  const int parts = rk::shift_mix_parts((int)B, (int)T);
+  Tensor dmp = torch::empty({parts, K, C}, f32);
+  rk::shift_mix_bwd(gp, x.data_ptr(), prev.data_ptr<float>(), mix.data_ptr<float>(), dx.data_ptr(),
+                    dprev.data_ptr<float>(), dmp.data_ptr<float>(), (int)K, (int)B, (int)T, (int)C, stream());
+  return {dx, dprev, dmp.sum(0)};
+}
+
+// tmix_pre: acts = [k_raw, v_raw, w_lora, a_lora] (+ [vg_lora, v_first] past layer 0); pars = [w0, a0, k_k, k_a] (+ [v0])
+Tensor tmix_pre_fwd(const std::vector<Tensor>& acts, const std::vector<Tensor>& pars) {
+  TORCH_CHECK(acts.size() == 4 || acts.size() == 6, "tmix_pre: 4 or 6 activations");
+  const bool has_v = acts.size() == 6;
+  TORCH_CHECK(pars.size() == (has_v ? 5u : 4u), "tmix_pre: parameter count mismatch");
+  c10::cuda::CUDAGuard guard(acts[0].device());
+  const int64_t C = acts[0].size(-1), M = acts[0].numel() / C;
+  TORCH_CHECK(C % 64 == 0, "tmix_pre needs head size 64");
+  for (auto& t : acts) { check_act(t, "activation"); TORCH_CHECK(t.numel() == M * C); }
+  for (auto& t : pars) check_par(t, C, "parameter");
+  Tensor out = torch::empty({5, M, C}, acts[0].options());
+  const void* in[6] = {acts[0].data_ptr(), acts[1].data_ptr(), acts[2].data_ptr(), acts[3].data_ptr(),
+                       has_v ? acts[4].data_ptr() : nullptr, has_v ? acts[5].data_ptr() : nullptr};
+  const float* par[5] = {pars[0].data_ptr<float>(), pars[1].data_ptr<float>(),
+                         has_v ? pars[4].data_ptr<float>() : nullptr, pars[2].data_ptr<float>(),
+                         pars[3].data_ptr<float>()};
+  char* o = (char*)out.data_ptr();
+  const size_t plane = (size_t)M * C * 2;
+  void* outs[5] = {o, o + plane, o + 2 * plane, o + 3 * plane, o + 4 * plane};
+  rk::tmix_pre_fwd(in, par, outs, (int)M, (int)C, stream());
+  return out;
+}
+
+// gouts = five [M,C] gradients (dw, dk_mod, dv, dneg_kk, dkka).
+// Returns {gin [6 or 4 planes: dk_raw, dv_raw, dw_lora, da_lora, (dvg_lora, dv_first)], dw0, da0, dk_k, dk_a, (dv0)}
+std::vector<Tensor> tmix_pre_bwd(const std::vector<Tensor>& acts, const std::vector<Tensor>& pars,
+                                 const std::vector<Tensor>& gouts) {
+  const bool has_v = acts.size() == 6;
+  c10::cuda::CUDAGuard guard(acts[0].device());
+  const int64_t C = acts[0].size(-1), M = acts[0].numel() / C;
+  for (auto& t : acts) check_act(t, "activation");
+  for (auto& t : pars) check_par(t, C, "parameter");
+  TORCH_CHECK(gouts.size() == 5, "tmix_pre_bwd: five output gradients");
+  for (auto& t : gouts) { check_act(t, "grad output"); TORCH_CHECK(t.numel() == M * C); }
+  const int nplanes = has_v ? 6 : 4;
+  Tensor gin = torch::empty({nplanes, M, C}, acts[0].options());
+  const int parts = rk::row_parts((int)M);
+  auto f32 = acts[0].options().dtype(at::kFloat);
+  Tensor gp = torch::empty({5, parts, C}, f32);
+  const void* in[6] = {acts[0].data_ptr(), acts[1].data_ptr(), acts[2].data_ptr(), acts[3].data_ptr(),
+                       has_v ? acts[4].data_ptr() : nullptr, has_v ? acts[5].data_ptr() : nullptr};
+  const float* par[5] = {pars[0].data_ptr<float>(), pars[1].data_ptr<float>(),
+                         has_v ? pars[4].data_ptr<float>() : nullptr, pars[2].data_ptr<float>(),
+                         pars[3].data_ptr<float>()};
+  const size_t plane = (size_t)M * C * 2;
+  const void* gout[5] = {gouts[0].data_ptr(), gouts[1].data_ptr(), gouts[2].data_ptr(), gouts[3].data_ptr(),
+                         gouts[4].data_ptr()};
+  char* gi = (char*)gin.data_ptr();
+  void* gins[6] = {gi, gi + plane, gi + 2 * plane, gi + 3 * plane, has_v ? gi + 4 * plane : nullptr,
+                   has_v ? gi + 5 * plane : nullptr};
+  float* gpp = gp.data_ptr<float>();
+  const size_t pp = (size_t)parts * C;
+  // kernel order: dw0, da0, dv0, dk_k, dk_a
+  float* gpar[5] = {gpp, gpp + pp, gpp + 4 * pp, gpp + 2 * pp, gpp + 3 * pp};
+  rk::tmix_pre_bwd(in, par, gout, gins, gpar, (int)M, (int)C, stream());
+  Tensor sums = gp.sum(1);  // [5, C]: dw0, da0, dk_k, dk_a, dv0
+  std::vector<Tensor> out = {gin, sums[0], sums[1], sums[2], sums[3]};
+  if (has_v) out.push_back(sums[4]);
+  return out;
+}
+
+Tensor gn_bonus_gate_fwd(const std::vector<Tensor>& acts, const std::vector<Tensor>& pars, double eps) {
+  TORCH_CHECK(acts.size() == 5 && pars.size() == 3);
+  c10::cuda::CUDAGuard guard(acts[0].device());
+  const int64_t C = acts[0].size(-1), M = acts[0].numel() / C;
+  TORCH_CHECK(C % 64 == 0, "gn_bonus_gate needs head size 64");
+  for (auto& t : acts) { check_act(t, "activation"); TORCH_CHECK(t.numel() == M * C); }
+  for (auto& t : pars) check_par(t, C, "parameter");
+  Tensor out = torch::empty_like(acts[0]);
+  const void* in[5] = {acts[0].data_ptr(), acts[1].data_ptr(), acts[2].data_ptr(), acts[3].data_ptr(), acts[4].data_ptr()};
+  const float* par[3] = {pars[0].data_ptr<float>(), pars[1].data_ptr<float>(), pars[2].data_ptr<float>()};
+  rk::gn_bonus_gate_fwd(in, par, out.data_ptr(), (int)M, (int)C, (float)eps, stream());
+  return out;
+}
+
+// Returns {gin [5,M,C]: dy, dr, dk, dv, dg; dln_w, dln_b, dr_k}
+std::vector<Tensor> gn_bonus_gate_bwd(const std::vector<Tensor>& acts, const std::vector<Tensor>& pars,
+                                      const Tensor& dout, double eps) {
+  c10::cuda::CUDAGuard guard(acts[0].device());
+  const int64_t C = acts[0].size(-1), M = acts[0].numel() / C;
+  for (auto& t : acts) check_act(t, "activation");
+  for (auto& t : pars) check_par(t, C, "parameter");
+  check_act(dout, "dout");
+  TORCH_CHECK(dout.numel() == M * C);
+  Tensor gin = torch::empty({5, M, C}, acts[0].options());
+  const int parts = rk::row_parts((int)M);
+  Tensor gp = torch::empty({3, parts, C}, acts[0].options().dtype(at::kFloat));
+  const void* in[5] = {acts[0].data_ptr(), acts[1].data_ptr(), acts[2].data_ptr(), acts[3].data_ptr(), acts[4].data_ptr()};
+  const float* par[3] = {pars[0].data_ptr<float>(), pars[1].data_ptr<float>(), pars[2].data_ptr<float>()};
+  const size_t plane = (size_t)M * C * 2;
+  char* gi = (char*)gin.data_ptr();
+  void* gins[5] = {gi, gi + plane, gi + 2 * plane, gi + 3 * plane, gi + 4 * plane};
+  float* gpp = gp.data_ptr<float>();
+  const size_t pp = (size_t)parts * C;
+  float* gpar[3] = {gpp, gpp + pp, gpp + 2 * pp};
+  rk::gn_bonus_gate_bwd(in, par, dout.data_ptr(), gins, gpar, (int)M, (int)C, (float)eps, stream());
+  Tensor sums = gp.sum(1);
+  return {gin, sums[0], sums[1], sums[2]};
+}
+
+Tensor relusq_bwd(const Tensor& dh, const Tensor& h) {
+  c10::cuda::CUDAGuard guard(dh.device());
+  check_act(dh, "dh"); check_act(h, "h");
+  TORCH_CHECK(dh.numel() == h.numel() && dh.numel() % 8 == 0);
+  Tensor out = torch::empty_like(dh);
+  rk::relusq_bwd(dh.data_ptr(), h.data_ptr(), out.data_ptr(), dh.numel(), stream());
+  return out;
+}
+
+std::vector<Tensor> ce_fwd(const Tensor& logits, const Tensor& targets) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_act(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2);
+  const int64_t M = logits.size(0), V = logits.size(1);
+  TORCH_CHECK(V % 8 == 0, "vocabulary must be a multiple of 8");
+  TORCH_CHECK(targets.is_cuda() && targets.is_contiguous() && targets.scalar_type() == at::kInt && targets.numel() == M);
+  auto f32 = logits.options().dtype(at::kFloat);
+  Tensor lse = torch::empty({M}, f32), maxv = torch::empty({M}, f32), nll = torch::empty({M}, f32);
+  Tensor am = torch::empty({M}, logits.options().dtype(at::kInt));
+  rk::ce_fwd(logits.data_ptr(), targets.data_ptr<int>(), lse.data_ptr<float>(), maxv.data_ptr<float>(),
+             am.data_ptr<int>(), nll.data_ptr<float>(), (int)M, (int)V, stream());
+  return {lse, maxv, am, nll};
+}
+
+void ce_bwd(Tensor logits, const Tensor& targets, const c10::optional<Tensor>& mask, const Tensor& lse,
+            const Tensor& maxv, const Tensor& am, const Tensor& g_ce, const Tensor& g_l2) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_act(logits, "logits");
+  const int64_t M = logits.size(0), V = logits.size(1);
+  check_par(lse, M, "lse"); check_par(maxv, M, "max"); check_par(g_ce, 1, "g_ce"); check_par(g_l2, 1, "g_l2");
+  TORCH_CHECK(targets.scalar_type() == at::kInt && targets.numel() == M && am.scalar_type() == at::kInt);
+  const float* mp = nullptr;
+  if (mask.has_value() && mask->defined()) { check_par(*mask, M, "mask"); mp = mask->data_ptr<float>(); }
+  rk::ce_bwd(logits.data_ptr(), targets.data_ptr<int>(), mp, lse.data_ptr<float>(), maxv.data_ptr<float>(),
+             am.data_ptr<int>(), g_ce.data_ptr<float>(), g_l2.data_ptr<float>(), (int)M, (int)V, stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -176,4 +391,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_error", &gemm_error);
   m.def("gemm_error_reset", &gemm_error_reset);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("shift_mix_fwd", &shift_mix_fwd);
+  m.def("shift_mix_bwd", &shift_mix_bwd);
+  m.def("tmix_pre_fwd", &tmix_pre_fwd);
+  m.def("tmix_pre_bwd", &tmix_pre_bwd);
+  m.def("gn_bonus_gate_fwd", &gn_bonus_gate_fwd);
+  m.def("gn_bonus_gate_bwd", &gn_bonus_gate_bwd);
+  m.def("relusq_bwd", &relusq_bwd);
+  m.def("ce_fwd", &ce_fwd);
+  m.def("ce_bwd", &ce_bwd);
 }

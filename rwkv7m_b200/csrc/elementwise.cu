@@ -1,0 +1,503 @@
+// Memory-bound fused kernels around the GEMMs of an RWKV-7 block (bf16 activations,
+// fp32 parameters and statistics).  Each forward has an explicit backward; per-channel
+// parameter gradients are produced as partial sums [parts, C] that the caller reduces.
+//
+//   layernorm            fp32 statistics, saves mean / rstd
+//   shift_mix            K token-shift lerps of one input in one pass
+//   tmix_pre             decay clamp, in-context rate, value residual, per-head key normalisation
+//   gn_bonus_gate        per-head GroupNorm + (r.k.r_k) v bonus + output gate
+//   relusq_bwd           derivative of relu(x)^2 from the saved output
+//
+// Math: src/rwkv7m/model/nnx_model.py:592-798 of the reference.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rk {
+
+using bf16 = __nv_bfloat16;
+using bf162 = __nv_bfloat162;
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+__device__ __forceinline__ float2 ld2(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const bf162*>(p)); }
+__device__ __forceinline__ void st2(bf16* p, float a, float b) { *reinterpret_cast<bf162*>(p) = __floats2bfloat162_rn(a, b); }
+
+// ---------------------------------------------------------------------------------
+// LayerNorm: one warp per row.
+// ---------------------------------------------------------------------------------
+__global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
+                                     const float* __restrict__ b, bf16* __restrict__ y, float* __restrict__ mean,
+                                     float* __restrict__ rstd, int M, int C, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < M; row += gridDim.x * warps_per_block) {
+    const bf16* xr = x + (size_t)row * C;
+    float s = 0.f, ss = 0.f;
+    for (int c = lane * 2; c < C; c += 64) {
+      float2 v = ld2(xr + c);
+      s += v.x + v.y;
+      ss += v.x * v.x + v.y * v.y;
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mu = s / C;
+    const float var = fmaxf(ss / C - mu * mu, 0.f);
+    const float rs = rsqrtf(var + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+    bf16* yr = y + (size_t)row * C;
+    for (int c = lane * 2; c < C; c += 64) {
+      float2 v = ld2(xr + c);
+      st2(yr + c, (v.x - mu) * rs * w[c] + b[c], (v.y - mu) * rs * w[c + 1] + b[c + 1]);
+    }
+  }
+}
+
+__global__ void layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                        const float* __restrict__ w, const float* __restrict__ mean,
+                                        const float* __restrict__ rstd, bf16* __restrict__ dx, int M, int C) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < M; row += gridDim.x * warps_per_block) {
+    const bf16* xr = x + (size_t)row * C;
+    const bf16* gr = dy + (size_t)row * C;
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane * 2; c < C; c += 64) {
+      float2 v = ld2(xr + c), g = ld2(gr + c);
+      const float g0 = g.x * w[c], g1 = g.y * w[c + 1];
+      s1 += g0 + g1;
+      s2 += g0 * (v.x - mu) * rs + g1 * (v.y - mu) * rs;
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+    bf16* dr = dx + (size_t)row * C;
+    for (int c = lane * 2; c < C; c += 64) {
+      float2 v = ld2(xr + c), g = ld2(gr + c);
+      const float xh0 = (v.x - mu) * rs, xh1 = (v.y - mu) * rs;
+      st2(dr + c, rs * (g.x * w[c] - s1 - xh0 * s2), rs * (g.y * w[c + 1] - s1 - xh1 * s2));
+    }
+  }
+}
+
+// Column sums for dw/db: block (32 columns x 8 row lanes), grid (C/32, parts).
+__global__ void layernorm_bwd_wb_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                                        float* __restrict__ dw_part, float* __restrict__ db_part, int M, int C) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int parts = gridDim.y;
+  const int rows_per = (M + parts - 1) / parts;
+  const int r0 = blockIdx.y * rows_per;
+  const int r1 = min(M, r0 + rows_per);
+  float aw = 0.f, ab = 0.f;
+  if (c < C) {
+    for (int r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+      const float g = bf2f(dy[(size_t)r * C + c]);
+      const float xh = (bf2f(x[(size_t)r * C + c]) - mean[r]) * rstd[r];
+      aw += g * xh;
+      ab += g;
+    }
+  }
+  __shared__ float sw[8][33], sb[8][33];
+  sw[threadIdx.y][threadIdx.x] = aw;
+  sb[threadIdx.y][threadIdx.x] = ab;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    for (int j = 1; j < 8; ++j) { aw += sw[j][threadIdx.x]; ab += sb[j][threadIdx.x]; }
+    dw_part[(size_t)blockIdx.y * C + c] = aw;
+    db_part[(size_t)blockIdx.y * C + c] = ab;
+  }
+}
+
+void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int M, int C,
+                   float eps, cudaStream_t st) {
+  int blocks = (M + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  layernorm_fwd_kernel<<<blocks, 256, 0, st>>>((const bf16*)x, w, b, (bf16*)y, mean, rstd, M, C, eps);
+}
+
+void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                   float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st) {
+  int blocks = (M + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  layernorm_bwd_dx_kernel<<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, M, C);
+  dim3 grid((C + 31) / 32, parts), block(32, 8);
+  layernorm_bwd_wb_kernel<<<grid, block, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
+}
+
+// ---------------------------------------------------------------------------------
+// shift_mix: out[z][b,t,c] = x[b,t,c] + (xprev - x[b,t,c]) * mix[z][c], xprev = x[b,t-1,c] or prev[b,c] at t = 0.
+// Thread = one column pair; block walks a segment of SEG consecutive tokens of one batch row.
+// ---------------------------------------------------------------------------------
+constexpr int kShiftSeg = 64;
+
+template <int K>
+__global__ void shift_mix_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ prev,
+                                     const float* __restrict__ mix, bf16* __restrict__ out, int B, int T, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * kShiftSeg;
+  const int t1 = min(T, t0 + kShiftSeg);
+  float m0[K], m1[K];
+#pragma unroll
+  for (int z = 0; z < K; ++z) { m0[z] = mix[z * C + c]; m1[z] = mix[z * C + c + 1]; }
+  float2 p;
+  if (t0 == 0) p = make_float2(prev[(size_t)b * C + c], prev[(size_t)b * C + c + 1]);
+  else p = ld2(x + ((size_t)b * T + t0 - 1) * C + c);
+  const size_t plane = (size_t)B * T * C;
+  for (int t = t0; t < t1; ++t) {
+    const size_t o = ((size_t)b * T + t) * C + c;
+    const float2 v = ld2(x + o);
+    const float d0 = p.x - v.x, d1 = p.y - v.y;
+#pragma unroll
+    for (int z = 0; z < K; ++z) st2(out + z * plane + o, v.x + d0 * m0[z], v.y + d1 * m1[z]);
+    p = v;
+  }
+}
+
+// dx[t] = sum_z dout_z[t] (1 - mix_z) + sum_z dout_z[t+1] mix_z ;  dmix_z = sum_t dout_z[t] (xprev_t - x_t) ;
+// dprev = sum_z dout_z[0] mix_z.  Segment walked backwards in time.
+template <int K> struct ShiftGrads { const bf16* p[K]; };
+
+template <int K>
+__global__ void shift_mix_bwd_kernel(ShiftGrads<K> dout, const bf16* __restrict__ x,
+                                     const float* __restrict__ prev, const float* __restrict__ mix,
+                                     bf16* __restrict__ dx, float* __restrict__ dprev, float* __restrict__ dmix_part,
+                                     int B, int T, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * kShiftSeg;
+  const int t1 = min(T, t0 + kShiftSeg);
+  float m0[K], m1[K], a0[K], a1[K];
+#pragma unroll
+  for (int z = 0; z < K; ++z) { m0[z] = mix[z * C + c]; m1[z] = mix[z * C + c + 1]; a0[z] = 0.f; a1[z] = 0.f; }
+  // carry = sum_z dout_z[t+1] * mix_z
+  float c0 = 0.f, c1 = 0.f;
+  if (t1 < T) {
+    const size_t o = ((size_t)b * T + t1) * C + c;
+#pragma unroll
+    for (int z = 0; z < K; ++z) { float2 g = ld2(dout.p[z] + o); c0 += g.x * m0[z]; c1 += g.y * m1[z]; }
+  }
+  float2 cur = ld2(x + ((size_t)b * T + t1 - 1) * C + c);
+  for (int t = t1 - 1; t >= t0; --t) {
+    const size_t o = ((size_t)b * T + t) * C + c;
+    float2 pv;
+    if (t == 0) pv = make_float2(prev[(size_t)b * C + c], prev[(size_t)b * C + c + 1]);
+    else pv = ld2(x + o - C);
+    const float d0 = pv.x - cur.x, d1 = pv.y - cur.y;
+    float s0 = 0.f, s1 = 0.f, n0 = 0.f, n1 = 0.f;
+#pragma unroll
+    for (int z = 0; z < K; ++z) {
+      float2 g = ld2(dout.p[z] + o);
+      s0 += g.x * (1.f - m0[z]); s1 += g.y * (1.f - m1[z]);
+      n0 += g.x * m0[z]; n1 += g.y * m1[z];
+      a0[z] += g.x * d0; a1[z] += g.y * d1;
+    }
+    st2(dx + o, s0 + c0, s1 + c1);
+    c0 = n0; c1 = n1;
+    cur = pv;
+  }
+  if (t0 == 0) { dprev[(size_t)b * C + c] = c0; dprev[(size_t)b * C + c + 1] = c1; }
+  const int part = blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+  for (int z = 0; z < K; ++z) {
+    dmix_part[((size_t)part * K + z) * C + c] = a0[z];
+    dmix_part[((size_t)part * K + z) * C + c + 1] = a1[z];
+  }
+}
+
+int shift_mix_parts(int B, int T) { return B * ((T + kShiftSeg - 1) / kShiftSeg); }
+
+void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out, int K, int B, int T, int C,
+                   cudaStream_t st) {
+  dim3 block(128), grid((C / 2 + 127) / 128, (T + kShiftSeg - 1) / kShiftSeg, B);
+  if (K == 6) shift_mix_fwd_kernel<6><<<grid, block, 0, st>>>((const bf16*)x, prev, mix, (bf16*)out, B, T, C);
+  else shift_mix_fwd_kernel<1><<<grid, block, 0, st>>>((const bf16*)x, prev, mix, (bf16*)out, B, T, C);
+}
+
+void shift_mix_bwd(const void* const* dout, const void* x, const float* prev, const float* mix, void* dx,
+                   float* dprev, float* dmix_part, int K, int B, int T, int C, cudaStream_t st) {
+  dim3 block(128), grid((C / 2 + 127) / 128, (T + kShiftSeg - 1) / kShiftSeg, B);
+  if (K == 6) {
+    ShiftGrads<6> g;
+    for (int z = 0; z < 6; ++z) g.p[z] = (const bf16*)dout[z];
+    shift_mix_bwd_kernel<6><<<grid, block, 0, st>>>(g, (const bf16*)x, prev, mix, (bf16*)dx, dprev, dmix_part, B, T, C);
+  } else {
+    ShiftGrads<1> g;
+    g.p[0] = (const bf16*)dout[0];
+    shift_mix_bwd_kernel<1><<<grid, block, 0, st>>>(g, (const bf16*)x, prev, mix, (bf16*)dx, dprev, dmix_part, B, T, C);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// tmix_pre: one warp per (row, head), head size 64 (two channels per lane).  A block of
+// 8 warps covers 8 heads; blocks walk kRowsPerBlock rows so per-channel parameter
+// gradients accumulate in registers before the partial write.
+// ---------------------------------------------------------------------------------
+constexpr int kRowsPerPart = 128;
+
+struct TmixPreParams {
+  const bf16 *k_raw, *v_raw, *w_lora, *a_lora, *vg_lora, *v_first;  // vg_lora / v_first null on layer 0
+  const float *w0, *a0, *v0, *k_k, *k_a;
+  bf16 *w, *k_mod, *v, *neg_kk, *kka;
+  // backward
+  const bf16 *dw, *dk_mod, *dv, *dneg_kk, *dkka;
+  bf16 *dk_raw, *dv_raw, *dw_lora, *da_lora, *dvg_lora, *dv_first;
+  float *dw0_part, *da0_part, *dv0_part, *dkk_part, *dka_part;  // [parts, C]
+  int M, C;
+};
+
+__global__ void tmix_pre_fwd_kernel(TmixPreParams p) {
+  const int H = p.C / 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * 8 + warp;
+  if (head >= H) return;
+  const int c = head * 64 + lane * 2;
+  const float w0a = p.w0[c], w0b = p.w0[c + 1], a0a = p.a0[c], a0b = p.a0[c + 1];
+  const float kka_ = p.k_k[c], kkb_ = p.k_k[c + 1], kaa = p.k_a[c], kab = p.k_a[c + 1];
+  const bool has_v = p.vg_lora != nullptr;
+  float v0a = 0.f, v0b = 0.f;
+  if (has_v) { v0a = p.v0[c]; v0b = p.v0[c + 1]; }
+  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    const float2 k = ld2(p.k_raw + o), v = ld2(p.v_raw + o), wl = ld2(p.w_lora + o), al = ld2(p.a_lora + o);
+    const float wa = -softplusf_(-(w0a + wl.x)) - 0.5f, wb = -softplusf_(-(w0b + wl.y)) - 0.5f;
+    const float aa = sigmoidf_(a0a + al.x), ab = sigmoidf_(a0b + al.y);
+    float va = v.x, vb = v.y;
+    if (has_v) {
+      const float2 vg = ld2(p.vg_lora + o), vf = ld2(p.v_first + o);
+      va = v.x + (vf.x - v.x) * sigmoidf_(v0a + vg.x);
+      vb = v.y + (vf.y - v.y) * sigmoidf_(v0b + vg.y);
+    }
+    const float x0 = k.x * kka_, x1 = k.y * kkb_;
+    const float inv = rsqrtf(warp_sum(x0 * x0 + x1 * x1) + 1e-24f);
+    const float kk0 = x0 * inv, kk1 = x1 * inv;
+    st2(p.w + o, wa, wb);
+    st2(p.k_mod + o, k.x * (1.f + (aa - 1.f) * kaa), k.y * (1.f + (ab - 1.f) * kab));
+    st2(p.v + o, va, vb);
+    st2(p.neg_kk + o, -kk0, -kk1);
+    st2(p.kka + o, kk0 * aa, kk1 * ab);
+  }
+}
+
+__global__ void tmix_pre_bwd_kernel(TmixPreParams p) {
+  const int H = p.C / 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * 8 + warp;
+  if (head >= H) return;
+  const int c = head * 64 + lane * 2;
+  const float w0a = p.w0[c], w0b = p.w0[c + 1], a0a = p.a0[c], a0b = p.a0[c + 1];
+  const float kka_ = p.k_k[c], kkb_ = p.k_k[c + 1], kaa = p.k_a[c], kab = p.k_a[c + 1];
+  const bool has_v = p.vg_lora != nullptr;
+  float v0a = 0.f, v0b = 0.f;
+  if (has_v) { v0a = p.v0[c]; v0b = p.v0[c + 1]; }
+  float gw0a = 0.f, gw0b = 0.f, ga0a = 0.f, ga0b = 0.f, gv0a = 0.f, gv0b = 0.f, gkka = 0.f, gkkb = 0.f, gkaa = 0.f,
+        gkab = 0.f;
+  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    const float2 k = ld2(p.k_raw + o), v = ld2(p.v_raw + o), wl = ld2(p.w_lora + o), al = ld2(p.a_lora + o);
+    const float2 gw = ld2(p.dw + o), gk = ld2(p.dk_mod + o), gv = ld2(p.dv + o), gn = ld2(p.dneg_kk + o),
+                 gb = ld2(p.dkka + o);
+    // decay
+    const float dwa = gw.x * sigmoidf_(-(w0a + wl.x)), dwb = gw.y * sigmoidf_(-(w0b + wl.y));
+    st2(p.dw_lora + o, dwa, dwb);
+    gw0a += dwa; gw0b += dwb;
+    // key normalisation
+    const float aa = sigmoidf_(a0a + al.x), ab = sigmoidf_(a0b + al.y);
+    const float x0 = k.x * kka_, x1 = k.y * kkb_;
+    const float inv = rsqrtf(warp_sum(x0 * x0 + x1 * x1) + 1e-24f);
+    const float kk0 = x0 * inv, kk1 = x1 * inv;
+    const float dkk0 = -gn.x + gb.x * aa, dkk1 = -gn.y + gb.y * ab;
+    const float dot = warp_sum(dkk0 * kk0 + dkk1 * kk1);
+    const float dx0 = (dkk0 - kk0 * dot) * inv, dx1 = (dkk1 - kk1 * dot) * inv;
+    gkka += dx0 * k.x; gkkb += dx1 * k.y;
+    // in-context rate
+    const float da0 = gk.x * k.x * kaa + gb.x * kk0, da1 = gk.y * k.y * kab + gb.y * kk1;
+    const float dar0 = da0 * aa * (1.f - aa), dar1 = da1 * ab * (1.f - ab);
+    st2(p.da_lora + o, dar0, dar1);
+    ga0a += dar0; ga0b += dar1;
+    gkaa += gk.x * k.x * (aa - 1.f); gkab += gk.y * k.y * (ab - 1.f);
+    st2(p.dk_raw + o, dx0 * kka_ + gk.x * (1.f + (aa - 1.f) * kaa), dx1 * kkb_ + gk.y * (1.f + (ab - 1.f) * kab));
+    // value residual
+    if (has_v) {
+      const float2 vg = ld2(p.vg_lora + o), vf = ld2(p.v_first + o);
+      const float g0 = sigmoidf_(v0a + vg.x), g1 = sigmoidf_(v0b + vg.y);
+      st2(p.dv_raw + o, gv.x * (1.f - g0), gv.y * (1.f - g1));
+      st2(p.dv_first + o, gv.x * g0, gv.y * g1);
+      const float dg0 = gv.x * (vf.x - v.x) * g0 * (1.f - g0), dg1 = gv.y * (vf.y - v.y) * g1 * (1.f - g1);
+      st2(p.dvg_lora + o, dg0, dg1);
+      gv0a += dg0; gv0b += dg1;
+    } else {
+      st2(p.dv_raw + o, gv.x, gv.y);
+    }
+  }
+  const size_t po = (size_t)blockIdx.y * p.C + c;
+  p.dw0_part[po] = gw0a; p.dw0_part[po + 1] = gw0b;
+  p.da0_part[po] = ga0a; p.da0_part[po + 1] = ga0b;
+  p.dkk_part[po] = gkka; p.dkk_part[po + 1] = gkkb;
+  p.dka_part[po] = gkaa; p.dka_part[po + 1] = gkab;
+  if (has_v) { p.dv0_part[po] = gv0a; p.dv0_part[po + 1] = gv0b; }
+}
+
+int row_parts(int M) { return (M + kRowsPerPart - 1) / kRowsPerPart; }
+
+void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* out, int M, int C, cudaStream_t st) {
+  TmixPreParams p{};
+  p.k_raw = (const bf16*)in[0]; p.v_raw = (const bf16*)in[1]; p.w_lora = (const bf16*)in[2];
+  p.a_lora = (const bf16*)in[3]; p.vg_lora = (const bf16*)in[4]; p.v_first = (const bf16*)in[5];
+  p.w0 = par[0]; p.a0 = par[1]; p.v0 = par[2]; p.k_k = par[3]; p.k_a = par[4];
+  p.w = (bf16*)out[0]; p.k_mod = (bf16*)out[1]; p.v = (bf16*)out[2]; p.neg_kk = (bf16*)out[3]; p.kka = (bf16*)out[4];
+  p.M = M; p.C = C;
+  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  tmix_pre_fwd_kernel<<<grid, 256, 0, st>>>(p);
+}
+
+void tmix_pre_bwd(const void* const* in, const float* const* par, const void* const* gout, void* const* gin,
+                  float* const* gpar_part, int M, int C, cudaStream_t st) {
+  TmixPreParams p{};
+  p.k_raw = (const bf16*)in[0]; p.v_raw = (const bf16*)in[1]; p.w_lora = (const bf16*)in[2];
+  p.a_lora = (const bf16*)in[3]; p.vg_lora = (const bf16*)in[4]; p.v_first = (const bf16*)in[5];
+  p.w0 = par[0]; p.a0 = par[1]; p.v0 = par[2]; p.k_k = par[3]; p.k_a = par[4];
+  p.dw = (const bf16*)gout[0]; p.dk_mod = (const bf16*)gout[1]; p.dv = (const bf16*)gout[2];
+  p.dneg_kk = (const bf16*)gout[3]; p.dkka = (const bf16*)gout[4];
+  p.dk_raw = (bf16*)gin[0]; p.dv_raw = (bf16*)gin[1]; p.dw_lora = (bf16*)gin[2]; p.da_lora = (bf16*)gin[3];
+  p.dvg_lora = (bf16*)gin[4]; p.dv_first = (bf16*)gin[5];
+  p.dw0_part = gpar_part[0]; p.da0_part = gpar_part[1]; p.dv0_part = gpar_part[2]; p.dkk_part = gpar_part[3];
+  p.dka_part = gpar_part[4];
+  p.M = M; p.C = C;
+  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  tmix_pre_bwd_kernel<<<grid, 256, 0, st>>>(p);
+}
+
+// ---------------------------------------------------------------------------------
+// gn_bonus_gate: out = (GroupNorm_head(y) * ln_w + ln_b + (sum_head r k r_k) v) * g
+// ---------------------------------------------------------------------------------
+struct GnParams {
+  const bf16 *y, *r, *k, *v, *g;
+  const float *ln_w, *ln_b, *r_k;
+  bf16* out;
+  const bf16* dout;
+  bf16 *dy, *dr, *dk, *dv, *dg;
+  float *dlnw_part, *dlnb_part, *drk_part;
+  int M, C;
+  float eps;
+};
+
+__global__ void gn_bonus_gate_fwd_kernel(GnParams p) {
+  const int H = p.C / 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * 8 + warp;
+  if (head >= H) return;
+  const int c = head * 64 + lane * 2;
+  const float lw0 = p.ln_w[c], lw1 = p.ln_w[c + 1], lb0 = p.ln_b[c], lb1 = p.ln_b[c + 1];
+  const float rk0 = p.r_k[c], rk1 = p.r_k[c + 1];
+  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    const float2 y = ld2(p.y + o), r = ld2(p.r + o), k = ld2(p.k + o), v = ld2(p.v + o), g = ld2(p.g + o);
+    const float mu = warp_sum(y.x + y.y) * (1.f / 64.f);
+    const float d0 = y.x - mu, d1 = y.y - mu;
+    const float rs = rsqrtf(warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f) + p.eps);
+    const float s = warp_sum(r.x * k.x * rk0 + r.y * k.y * rk1);
+    st2(p.out + o, (d0 * rs * lw0 + lb0 + s * v.x) * g.x, (d1 * rs * lw1 + lb1 + s * v.y) * g.y);
+  }
+}
+
+__global__ void gn_bonus_gate_bwd_kernel(GnParams p) {
+  const int H = p.C / 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * 8 + warp;
+  if (head >= H) return;
+  const int c = head * 64 + lane * 2;
+  const float lw0 = p.ln_w[c], lw1 = p.ln_w[c + 1], lb0 = p.ln_b[c], lb1 = p.ln_b[c + 1];
+  const float rk0 = p.r_k[c], rk1 = p.r_k[c + 1];
+  float aw0 = 0.f, aw1 = 0.f, ab0 = 0.f, ab1 = 0.f, ar0 = 0.f, ar1 = 0.f;
+  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    const float2 y = ld2(p.y + o), r = ld2(p.r + o), k = ld2(p.k + o), v = ld2(p.v + o), g = ld2(p.g + o),
+                 go = ld2(p.dout + o);
+    const float mu = warp_sum(y.x + y.y) * (1.f / 64.f);
+    const float d0 = y.x - mu, d1 = y.y - mu;
+    const float rs = rsqrtf(warp_sum(d0 * d0 + d1 * d1) * (1.f / 64.f) + p.eps);
+    const float xh0 = d0 * rs, xh1 = d1 * rs;
+    const float s = warp_sum(r.x * k.x * rk0 + r.y * k.y * rk1);
+    const float pre0 = xh0 * lw0 + lb0 + s * v.x, pre1 = xh1 * lw1 + lb1 + s * v.y;
+    st2(p.dg + o, go.x * pre0, go.y * pre1);
+    const float dp0 = go.x * g.x, dp1 = go.y * g.y;
+    st2(p.dv + o, dp0 * s, dp1 * s);
+    const float ds = warp_sum(dp0 * v.x + dp1 * v.y);
+    st2(p.dr + o, ds * k.x * rk0, ds * k.y * rk1);
+    st2(p.dk + o, ds * r.x * rk0, ds * r.y * rk1);
+    ar0 += ds * r.x * k.x; ar1 += ds * r.y * k.y;
+    aw0 += dp0 * xh0; aw1 += dp1 * xh1;
+    ab0 += dp0; ab1 += dp1;
+    const float dx0 = dp0 * lw0, dx1 = dp1 * lw1;
+    const float m1 = warp_sum(dx0 + dx1) * (1.f / 64.f);
+    const float m2 = warp_sum(dx0 * xh0 + dx1 * xh1) * (1.f / 64.f);
+    st2(p.dy + o, rs * (dx0 - m1 - xh0 * m2), rs * (dx1 - m1 - xh1 * m2));
+  }
+  const size_t po = (size_t)blockIdx.y * p.C + c;
+  p.dlnw_part[po] = aw0; p.dlnw_part[po + 1] = aw1;
+  p.dlnb_part[po] = ab0; p.dlnb_part[po + 1] = ab1;
+  p.drk_part[po] = ar0; p.drk_part[po + 1] = ar1;
+}
+
+void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out, int M, int C, float eps,
+                       cudaStream_t st) {
+  GnParams p{};
+  p.y = (const bf16*)in[0]; p.r = (const bf16*)in[1]; p.k = (const bf16*)in[2]; p.v = (const bf16*)in[3];
+  p.g = (const bf16*)in[4];
+  p.ln_w = par[0]; p.ln_b = par[1]; p.r_k = par[2];
+  p.out = (bf16*)out; p.M = M; p.C = C; p.eps = eps;
+  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  gn_bonus_gate_fwd_kernel<<<grid, 256, 0, st>>>(p);
+}
+
+void gn_bonus_gate_bwd(const void* const* in, const float* const* par, const void* dout, void* const* gin,
+                       float* const* gpar_part, int M, int C, float eps, cudaStream_t st) {
+  GnParams p{};
+  p.y = (const bf16*)in[0]; p.r = (const bf16*)in[1]; p.k = (const bf16*)in[2]; p.v = (const bf16*)in[3];
+  p.g = (const bf16*)in[4];
+  p.ln_w = par[0]; p.ln_b = par[1]; p.r_k = par[2];
+  p.dout = (const bf16*)dout;
+  p.dy = (bf16*)gin[0]; p.dr = (bf16*)gin[1]; p.dk = (bf16*)gin[2]; p.dv = (bf16*)gin[3]; p.dg = (bf16*)gin[4];
+  p.dlnw_part = gpar_part[0]; p.dlnb_part = gpar_part[1]; p.drk_part = gpar_part[2];
+  p.M = M; p.C = C; p.eps = eps;
+  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  gn_bonus_gate_bwd_kernel<<<grid, 256, 0, st>>>(p);
+}
+
+// ---------------------------------------------------------------------------------
+// relu(x)^2 backward from the saved output h: dpre = dh * 2 sqrt(h)
+// ---------------------------------------------------------------------------------
+__global__ void relusq_bwd_kernel(const bf16* __restrict__ dh, const bf16* __restrict__ h, bf16* __restrict__ out,
+                                  int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x * 8;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    uint4 a = *reinterpret_cast<const uint4*>(dh + i);
+    uint4 b = *reinterpret_cast<const uint4*>(h + i);
+    const bf162* pa = reinterpret_cast<const bf162*>(&a);
+    const bf162* pb = reinterpret_cast<const bf162*>(&b);
+    uint4 o;
+    bf162* po = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 g = __bfloat1622float2(pa[j]), hh = __bfloat1622float2(pb[j]);
+      po[j] = __floats2bfloat162_rn(g.x * 2.f * sqrtf(hh.x), g.y * 2.f * sqrtf(hh.y));
+    }
+    *reinterpret_cast<uint4*>(out + i) = o;
+  }
+}
+
+void relusq_bwd(const void* dh, const void* h, void* out, int64_t n, cudaStream_t st) {
+  int64_t want = (n / 8 + 255) / 256;
+  int blocks = (int)(want > 148 * 32 ? 148 * 32 : (want < 1 ? 1 : want));
+  relusq_bwd_kernel<<<blocks, 256, 0, st>>>((const bf16*)dh, (const bf16*)h, (bf16*)out, n);
+}
+
+}  // namespace rk

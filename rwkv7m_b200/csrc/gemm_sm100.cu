@@ -12,6 +12,7 @@
 // limit runs out the CTA records an error code, drains and frees TMEM.
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -287,14 +288,18 @@ struct MapKeyHash {
 };
 
 // Row-major bf16 matrix [rows, cols] with leading dimension ld; box = 64 columns x box_rows rows, 128B swizzle.
+// The cache stores the 128 descriptor bytes as a plain byte array: CUtensorMap is 64-byte aligned and
+// node-based containers do not honour that alignment under every host compiler configuration.
+struct MapBytes { unsigned char raw[sizeof(CUtensorMap)]; };
+
 bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::unordered_map<MapKey, MapBytes, MapKeyHash> cache;
   static std::mutex mu;
   MapKey key{ptr, rows, cols, ld, box_rows};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return true; }
+    if (it != cache.end()) { memcpy(out, it->second.raw, sizeof(CUtensorMap)); return true; }
   }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
@@ -306,9 +311,11 @@ bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
+  MapBytes mb;
+  memcpy(mb.raw, out, sizeof(CUtensorMap));
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 8192) cache.clear();
-  cache.emplace(key, *out);
+  cache[key] = mb;
   return true;
 }
 
@@ -326,7 +333,8 @@ int sm_count() {
 template <int BN, int A_MN, int B_MN, int EPI>
 int launch(const GemmArgs& p, cudaStream_t st) {
   using TL = Tile<BN>;
-  CUtensorMap ta, tb;
+  alignas(64) CUtensorMap ta;
+  alignas(64) CUtensorMap tb;
   bool ok;
   if (A_MN == 0) ok = make_map(&ta, p.A, p.M, p.K, p.lda, BM); else ok = make_map(&ta, p.A, p.K, p.M, p.lda, BK);
   if (!ok) return 2;

@@ -45,6 +45,39 @@ struct AdamWArgs {
 };
 void adamw_flat(const AdamWArgs& p, cudaStream_t st);
 
+// ---- fused memory-bound kernels (bf16 activations, fp32 parameters) ---------------
+void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int M, int C,
+                   float eps, cudaStream_t st);
+void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                   float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st);
+int shift_mix_parts(int B, int T);
+void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out, int K, int B, int T, int C,
+                   cudaStream_t st);
+// dout: K separate [B,T,C] gradient tensors
+void shift_mix_bwd(const void* const* dout, const void* x, const float* prev, const float* mix, void* dx,
+                   float* dprev, float* dmix_part, int K, int B, int T, int C, cudaStream_t st);
+int row_parts(int M);
+// in: k_raw, v_raw, w_lora, a_lora, vg_lora, v_first (last two null on layer 0); par: w0, a0, v0, k_k, k_a;
+// out: w, k_mod, v, neg_kk, kka
+void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* out, int M, int C, cudaStream_t st);
+// gout: dw, dk_mod, dv, dneg_kk, dkka; gin: dk_raw, dv_raw, dw_lora, da_lora, dvg_lora, dv_first;
+// gpar_part: dw0, da0, dv0, dk_k, dk_a as [row_parts(M), C]
+void tmix_pre_bwd(const void* const* in, const float* const* par, const void* const* gout, void* const* gin,
+                  float* const* gpar_part, int M, int C, cudaStream_t st);
+// in: y, r, k, v, g; par: ln_w, ln_b, r_k
+void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out, int M, int C, float eps,
+                       cudaStream_t st);
+// gin: dy, dr, dk, dv, dg; gpar_part: dln_w, dln_b, dr_k as [row_parts(M), C]
+void gn_bonus_gate_bwd(const void* const* in, const float* const* par, const void* dout, void* const* gin,
+                       float* const* gpar_part, int M, int C, float eps, cudaStream_t st);
+void relusq_bwd(const void* dh, const void* h, void* out, int64_t n, cudaStream_t st);
+
+// ---- loss ---------------------------------------------------------------------------
+void ce_fwd(const void* logits, const int* targets, float* lse, float* maxv, int* argmax, float* nll, int rows, int V,
+            cudaStream_t st);
+void ce_bwd(void* logits, const int* targets, const float* mask, const float* lse, const float* maxv,
+            const int* argmax, const float* g_ce, const float* g_l2, int rows, int V, cudaStream_t st);
+
 // ---- GEMM (tcgen05) -------------------------------------------------------------
 enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
 enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3 };

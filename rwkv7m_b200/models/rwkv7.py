@@ -112,16 +112,20 @@ class RWKV7TimeMix(nn.Module):
         H, N = cfg.n_heads, cfg.head_size
         x_r, x_w, x_k, x_v, x_a, x_g = ops.shift_mix(x, prev_x, self.x_mix)
         r = ops.linear(x_r, self.receptance.weight)
-        w = ops.decay_lora(x_w, self.w1, self.w2, self.w0)
         k = ops.linear(x_k, self.key.weight)
         v = ops.linear(x_v, self.value.weight)
+        w_lora = ops.lora(x_w, self.w1, self.w2, "tanh")
+        a_lora = ops.lora(x_a, self.a1, self.a2, "none")
+        g = ops.lora(x_g, self.g1, self.g2, "sigmoid")
+        if self.layer_idx == 0:
+            vg_lora, v_src, v0 = None, None, None
+        else:
+            vg_lora, v_src, v0 = ops.lora(x_v, self.v1, self.v2, "none"), v_first, self.v0
+        w, k_mod, v, neg_kk, kka = ops.tmix_pre(
+            k, v, w_lora, a_lora, vg_lora, v_src, self.w0, self.a0, v0, self.k_k, self.k_a, H
+        )
         if self.layer_idx == 0:
             v_first = v
-        else:
-            v = ops.value_residual(v, v_first, x_v, self.v1, self.v2, self.v0)
-        a = ops.sigmoid_lora(x_a, self.a1, self.a2, self.a0)
-        g = ops.gate_lora(x_g, self.g1, self.g2)
-        k_mod, neg_kk, kka = ops.kk_pre(k, a, self.k_k, self.k_a, H)
         y, final_state = ops.wkv7(
             r.view(B, T, H, N),
             w.view(B, T, H, N),

@@ -73,38 +73,24 @@ def linear_relu_sq(x, weight):
     return reference.relu_sq(reference.linear(x, weight))
 
 
-def decay_lora(x_w, w1, w2, w0):
-    """w = -softplus(-(w0 + tanh(x_w @ w1.T) @ w2.T)) - 0.5."""
-    if use_cuda(x_w):
-        return _cuda().decay_lora(x_w, w1, w2, w0)
-    return reference.decay_clamp(reference.lora(x_w, w1, w2, w0, mid="tanh"))
+def lora(x, down, up, mid="none"):
+    """Low-rank path act(x @ down.T) @ up.T with weights stored [out,in]; no bias."""
+    if use_cuda(x):
+        return _cuda().lora(x, down, up, mid)
+    return reference.lora(x, down, up, None, mid=mid)
 
 
-def sigmoid_lora(x_a, a1, a2, a0):
-    """a = sigmoid(a0 + (x_a @ a1.T) @ a2.T)."""
-    if use_cuda(x_a):
-        return _cuda().sigmoid_lora(x_a, a1, a2, a0)
-    return torch.sigmoid(reference.lora(x_a, a1, a2, a0))
+def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads):
+    """Everything between the projections and the recurrence, in one pass:
 
-
-def gate_lora(x_g, g1, g2):
-    """g = sigmoid(x_g @ g1.T) @ g2.T."""
-    if use_cuda(x_g):
-        return _cuda().gate_lora(x_g, g1, g2)
-    return reference.lora(x_g, g1, g2, None, mid="sigmoid")
-
-
-def value_residual(v, v_first, x_v, v1, v2, v0):
-    """v + (v_first - v) * sigmoid(v0 + (x_v @ v1.T) @ v2.T)."""
-    if use_cuda(v):
-        return _cuda().value_residual(v, v_first, x_v, v1, v2, v0)
-    return v + (v_first - v) * torch.sigmoid(reference.lora(x_v, v1, v2, v0))
-
-
-def kk_pre(k, a, k_k, k_a, n_heads):
+    w = -softplus(-(w0 + w_lora)) - 0.5;  a = sigmoid(a0 + a_lora);
+    v = v + (v_first - v) * sigmoid(v0 + vg_lora)   (skipped when ``vg_lora`` is None: layer 0);
+    kk = normalize_per_head(k * k_k);  k_mod = k * (1 + (a - 1) * k_a).
+    Returns (w, k_mod, v, -kk, kk * a).
+    """
     if use_cuda(k):
-        return _cuda().kk_pre(k, a, k_k, k_a, n_heads)
-    return reference.kk_pre(k, a, k_k, k_a, n_heads)
+        return _cuda().tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
+    return reference.tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
 
 
 def wkv7(r, w, k, v, a, b, state0):
@@ -160,11 +146,8 @@ __all__ = [
     "shift_mix",
     "linear",
     "linear_relu_sq",
-    "decay_lora",
-    "sigmoid_lora",
-    "gate_lora",
-    "value_residual",
-    "kk_pre",
+    "lora",
+    "tmix_pre",
     "wkv7",
     "gn_bonus_gate",
     "head_loss",

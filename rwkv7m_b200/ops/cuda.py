@@ -143,10 +143,11 @@ class LinearFn(torch.autograd.Function):
         w = ctx.weight
         N, K = wc.shape
         dy2 = dy.reshape(-1, N)
-        if ctx.relu_sq:
-            dy2 = dy2 * (2.0 * torch.sqrt(h.float())).to(dy2.dtype)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        if ctx.relu_sq:
+            dy2 = _C.relusq_bwd(dy2, h)
+            _count()
         dx = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty(x2.shape[0], K, dtype=torch.bfloat16, device=dy.device)
@@ -183,63 +184,261 @@ def linear_relu_sq(x, weight):
 
 
 # ---------------------------------------------------------------------------
-# Ops whose CUDA statement is still the PyTorch one
+# Fused memory-bound ops (bf16 activations, head size 64)
 # ---------------------------------------------------------------------------
 
 
+def _par(p):
+    """Per-channel parameter as a flat fp32 tensor (no copy for fp32 parameters)."""
+    return p.detach().float().contiguous().view(-1)
+
+
+def _like_param(g, p):
+    return g.view(p.shape).to(p.dtype)
+
+
+def _bf16(x):
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+class EmbeddingFn(torch.autograd.Function):
+    """Row gather from the bf16 shadow of the table; backward scatters into the fp32 main gradient."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, dtype):
+        src = getattr(weight, "_compute", None)
+        if src is None or src.dtype != dtype:
+            src = weight.detach()
+        out = torch.nn.functional.embedding(ids.long(), src)
+        ctx.weight = weight
+        ctx.save_for_backward(ids)
+        return out if out.dtype == dtype else out.to(dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        w = ctx.weight
+        main = getattr(w, "_main_grad", None)
+        flat_ids = ids.reshape(-1).long()
+        d2 = dout.reshape(-1, dout.shape[-1])
+        if main is not None:
+            main.index_add_(0, flat_ids, d2.to(main.dtype))
+            return None, None, None
+        g = torch.zeros_like(w, dtype=torch.float32)
+        g.index_add_(0, flat_ids, d2.float())
+        return None, g.to(w.dtype), None
+
+
 def embedding(ids, weight, dtype):
-    shadow = getattr(weight, "_compute", None)
-    if shadow is not None and shadow.dtype == dtype and not torch.is_grad_enabled():
-        return torch.nn.functional.embedding(ids.long(), shadow)
-    return torch.nn.functional.embedding(ids.long(), weight).to(dtype)
+    return EmbeddingFn.apply(ids, weight, dtype)
+
+
+class LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        xc = x.contiguous()
+        y, mean, rstd = _C.layernorm_fwd(xc, _par(w), _par(b), eps)
+        _count()
+        ctx.save_for_backward(xc, w, b, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, b, mean, rstd = ctx.saved_tensors
+        dx, dw, db = _C.layernorm_bwd(dy.contiguous(), x, _par(w), mean, rstd)
+        _count(2)
+        return dx, _like_param(dw, w), _like_param(db, b), None
 
 
 def layer_norm(x, weight, bias, eps=1e-5):
+    if _bf16(x) and x.shape[-1] % 2 == 0:
+        return LayerNormFn.apply(x, weight, bias, eps)
     return R.layer_norm(x, weight, bias, eps)
 
 
+class ShiftMixFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, prev, mix):
+        xc = x.contiguous()
+        prev32 = prev.detach().float().contiguous()
+        out = _C.shift_mix_fwd(xc, prev32, _par(mix))
+        _count()
+        ctx.save_for_backward(xc, prev32, mix)
+        ctx.prev_dtype = prev.dtype
+        return tuple(out.unbind(0))
+
+    @staticmethod
+    def backward(ctx, *douts):
+        x, prev32, mix = ctx.saved_tensors
+        gs = [torch.zeros_like(x) if g is None else g.contiguous() for g in douts]
+        dx, dprev, dmix = _C.shift_mix_bwd(gs, x, prev32, _par(mix))
+        _count()
+        return dx, dprev.to(ctx.prev_dtype), _like_param(dmix, mix)
+
+
 def shift_mix(x, prev, mix):
+    if _bf16(x) and x.dim() == 3 and mix.shape[0] in (1, 6) and x.shape[-1] % 2 == 0:
+        return ShiftMixFn.apply(x, prev, mix)
     return R.shift_mix(x, prev, mix)
 
 
-def _lora(x, down, up, bias, mid):
+def lora(x, down, up, mid="none"):
     h = linear(x, down)
     if mid == "tanh":
         h = torch.tanh(h)
     elif mid == "sigmoid":
         h = torch.sigmoid(h)
-    y = linear(h, up)
-    if bias is not None:
-        y = y + bias.to(y.dtype)
-    return y
+    return linear(h, up)
 
 
-def decay_lora(x_w, w1, w2, w0):
-    return R.decay_clamp(_lora(x_w, w1, w2, w0, "tanh"))
+class TmixPreFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a):
+        has_v = vg_lora is not None
+        acts = [k.contiguous(), v.contiguous(), w_lora.contiguous(), a_lora.contiguous()]
+        pars = [w0, a0, k_k, k_a]
+        if has_v:
+            acts += [vg_lora.contiguous(), v_first.contiguous()]
+            pars.append(v0)
+        out = _C.tmix_pre_fwd(acts, [_par(p) for p in pars])
+        _count()
+        ctx.has_v = has_v
+        ctx.n_acts = len(acts)
+        ctx.save_for_backward(*acts, *pars)
+        shape = k.shape
+        return tuple(o.view(shape) for o in out.unbind(0))
+
+    @staticmethod
+    def backward(ctx, dw, dk_mod, dv, dneg_kk, dkka):
+        saved = ctx.saved_tensors
+        acts, pars = list(saved[: ctx.n_acts]), list(saved[ctx.n_acts :])
+        ref = acts[0]
+        gouts = [torch.zeros_like(ref) if g is None else g.contiguous() for g in (dw, dk_mod, dv, dneg_kk, dkka)]
+        res = _C.tmix_pre_bwd(acts, [_par(p) for p in pars], gouts)
+        _count()
+        gin = res[0]
+        shape = ref.shape
+        planes = [g.view(shape) for g in gin.unbind(0)]
+        dk_raw, dv_raw, dwl, dal = planes[:4]
+        dvg = planes[4] if ctx.has_v else None
+        dvf = planes[5] if ctx.has_v else None
+        w0, a0, k_k, k_a = pars[:4]
+        gw0, ga0, gkk, gka = (_like_param(res[i + 1], p) for i, p in enumerate((w0, a0, k_k, k_a)))
+        gv0 = _like_param(res[5], pars[4]) if ctx.has_v else None
+        return dk_raw, dv_raw, dwl, dal, dvg, dvf, gw0, ga0, gv0, gkk, gka
 
 
-def sigmoid_lora(x_a, a1, a2, a0):
-    return torch.sigmoid(_lora(x_a, a1, a2, a0, "none"))
+def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads):
+    if _bf16(k) and k.shape[-1] == 64 * n_heads:
+        return TmixPreFn.apply(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a)
+    return R.tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
 
 
-def gate_lora(x_g, g1, g2):
-    return _lora(x_g, g1, g2, None, "sigmoid")
+class GnBonusGateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, r, k, v, g, ln_w, ln_b, r_k, eps):
+        acts = [t.contiguous() for t in (y, r, k, v, g)]
+        out = _C.gn_bonus_gate_fwd(acts, [_par(ln_w), _par(ln_b), _par(r_k)], eps)
+        _count()
+        ctx.eps = eps
+        ctx.save_for_backward(*acts, ln_w, ln_b, r_k)
+        return out
 
-
-def value_residual(v, v_first, x_v, v1, v2, v0):
-    return v + (v_first - v) * torch.sigmoid(_lora(x_v, v1, v2, v0, "none"))
-
-
-def kk_pre(k, a, k_k, k_a, n_heads):
-    return R.kk_pre(k, a, k_k, k_a, n_heads)
+    @staticmethod
+    def backward(ctx, dout):
+        *acts, ln_w, ln_b, r_k = ctx.saved_tensors
+        gin, dlw, dlb, drk = _C.gn_bonus_gate_bwd(
+            list(acts), [_par(ln_w), _par(ln_b), _par(r_k)], dout.contiguous(), ctx.eps
+        )
+        _count()
+        shape = acts[0].shape
+        dy, dr, dk, dv, dg = (t.view(shape) for t in gin.unbind(0))
+        return dy, dr, dk, dv, dg, _like_param(dlw, ln_w), _like_param(dlb, ln_b), _like_param(drk, r_k), None
 
 
 def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+    if _bf16(y) and y.shape[-1] == 64 * n_heads:
+        return GnBonusGateFn.apply(y, r, k, v, g, ln_w, ln_b, r_k, eps)
     return R.gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps)
+
+
+class HeadLossFn(torch.autograd.Function):
+    """LM head + cross-entropy + L2Wrap without keeping the logits.
+
+    Forward runs the head GEMM chunk by chunk into one reusable [rows, V] bf16
+    buffer and keeps only per-row log-sum-exp / max / argmax.  Backward
+    recomputes each logits chunk, turns it into its own gradient in place and
+    feeds the two gradient GEMMs.
+    """
+
+    @staticmethod
+    def forward(ctx, h, head_w, targets, mask, chunk_rows):
+        wc = _compute_weight(head_w)
+        C = h.shape[-1]
+        h2 = h.reshape(-1, C)
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        M, V = h2.shape[0], wc.shape[0]
+        tgt = targets.reshape(-1).to(torch.int32).contiguous()
+        msk = None if mask is None else mask.reshape(-1).float().contiguous()
+        chunk_rows = min(chunk_rows, M)
+        buf = torch.empty(chunk_rows, V, dtype=torch.bfloat16, device=h.device)
+        lse = torch.empty(M, dtype=torch.float32, device=h.device)
+        mx = torch.empty_like(lse)
+        nll = torch.empty_like(lse)
+        am = torch.empty(M, dtype=torch.int32, device=h.device)
+        for s in range(0, M, chunk_rows):
+            e = min(M, s + chunk_rows)
+            logits = buf[: e - s]
+            gemm(h2[s:e], wc, logits, GEMM_TN, EPI_BF16)
+            l, m, a, n = _C.ce_fwd(logits, tgt[s:e])
+            _count()
+            lse[s:e], mx[s:e], am[s:e], nll[s:e] = l, m, a, n
+        ce_total = (nll * msk).sum() if msk is not None else nll.sum()
+        ce_count = msk.sum() if msk is not None else torch.tensor(float(M), device=h.device)
+        l2_total = 0.5e-4 * (mx * mx).sum()
+        l2_count = torch.tensor(float(M), device=h.device)
+        ctx.weight = head_w
+        ctx.chunk_rows = chunk_rows
+        ctx.h_shape = h.shape
+        ctx.save_for_backward(h2, wc, tgt, msk, lse, mx, am)
+        ctx.mark_non_differentiable(ce_count, l2_count)
+        return ce_total, ce_count, l2_total, l2_count
+
+    @staticmethod
+    def backward(ctx, g_ce, _g1, g_l2, _g2):
+        h2, wc, tgt, msk, lse, mx, am = ctx.saved_tensors
+        w = ctx.weight
+        M, C = h2.shape
+        V = wc.shape[0]
+        dev = h2.device
+        g_ce = torch.zeros(1, device=dev) if g_ce is None else g_ce.float().reshape(1).contiguous()
+        g_l2 = torch.zeros(1, device=dev) if g_l2 is None else g_l2.float().reshape(1).contiguous()
+        buf = torch.empty(ctx.chunk_rows, V, dtype=torch.bfloat16, device=dev)
+        dh = torch.empty(M, C, dtype=torch.bfloat16, device=dev)
+        main = getattr(w, "_main_grad", None)
+        dw32 = None
+        if main is None or main.dtype != torch.float32:
+            dw32 = torch.zeros(V, C, dtype=torch.float32, device=dev)
+        acc = main if dw32 is None else dw32
+        for s in range(0, M, ctx.chunk_rows):
+            e = min(M, s + ctx.chunk_rows)
+            logits = buf[: e - s]
+            gemm(h2[s:e], wc, logits, GEMM_TN, EPI_BF16)
+            _C.ce_bwd(logits, tgt[s:e], None if msk is None else msk[s:e], lse[s:e], mx[s:e], am[s:e], g_ce, g_l2)
+            _count()
+            gemm(logits, wc, dh[s:e], GEMM_NN, EPI_BF16)
+            gemm(logits, h2[s:e], acc, GEMM_WGRAD, EPI_ACC_F32)
+        dw = None if dw32 is None else dw32.to(w.dtype)
+        return dh.view(ctx.h_shape), dw, None, None, None
 
 
 def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
     B, T, C = hidden.shape
+    if _bf16(hidden) and GEMM_BACKEND == "tcgen05" and head_w.shape[0] % 8 == 0 and C % 8 == 0:
+        h = layer_norm(hidden, ln_w, ln_b, eps)
+        rows = 8192 if chunk is None else max(1, int(chunk)) * B
+        return HeadLossFn.apply(h, head_w, targets, mask, min(rows, 8192))
     chunk = chunk or min(T, max(1, 8192 // max(B, 1)))
     totals = None
     for start in range(0, T, chunk):

@@ -67,6 +67,17 @@ def kk_pre(k, a, k_k, k_a, n_heads):
     return k_mod, -kk, kk * a
 
 
+def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads):
+    """Decay clamp, in-context rate, value residual and key normalisation (nnx_model.py:616-687)."""
+    dt = k.dtype
+    w = decay_clamp(w0.to(dt) + w_lora)
+    a = torch.sigmoid(a0.to(dt) + a_lora)
+    if vg_lora is not None:
+        v = v + (v_first - v) * torch.sigmoid(v0.to(dt) + vg_lora)
+    k_mod, neg_kk, kka = kk_pre(k, a, k_k, k_a, n_heads)
+    return w, k_mod, v, neg_kk, kka
+
+
 def wkv7(r, w, k, v, a, b, state0):
     """Sequential WKV7 generalised delta rule.
 
