@@ -41,6 +41,7 @@ def parse_args(argv=None):
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
     return ap.parse_args(argv)
 
 
@@ -149,8 +150,11 @@ def main(argv=None):
         cfg.dtype = "bfloat16"
     else:
         cfg = bench_config(args.model)
+    if args.layers > 0:
+        cfg.n_layers = args.layers
     cfg.head_chunk_size = max(1, 8192 // args.batch)
-    remat_modes = {"on": [True], "off": [False], "auto": [False, True]}[args.remat]
+    L = cfg.n_layers
+    remat_modes = {"on": [L], "off": [0], "auto": [0, L // 3, (2 * L) // 3, L]}[args.remat]
 
     B, T, V = args.batch, args.seq, cfg.vocab_size
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -169,11 +173,12 @@ def main(argv=None):
     trainer = None
     used_remat = None
     for remat in remat_modes:
-        cfg.remat_blocks = remat
+        cfg.remat_blocks = False
         try:
             runtime, train_state = R.create_train_runtime(
                 rank * 0 + 7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8
             )
+            train_state.model.remat_layer_count = remat
             trainer = DataParallelTrainer(train_state, mode=args.dp if world > 1 else "single")
             dev_batches = [make_batch(False) for _ in range(2)]
             for i in range(args.warmup):
@@ -183,7 +188,10 @@ def main(argv=None):
             break
         except torch.cuda.OutOfMemoryError:
             trainer = None
-            del runtime, train_state
+            runtime = train_state = metrics = dev_batches = None
+            import gc
+
+            gc.collect()
             torch.cuda.empty_cache()
             if remat == remat_modes[-1]:
                 raise
@@ -250,11 +258,12 @@ def main(argv=None):
             "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": {
-                "model": f"rwkv7-{args.model} (d_model {cfg.d_model}, layers {cfg.n_layers}, d_ffn {cfg.ffn_dim}, vocab {V})",
+                "model": ("REDUCED-LAYERS " if args.layers > 0 else "") + f"rwkv7-{args.model} (d_model {cfg.d_model}, layers {cfg.n_layers}, d_ffn {cfg.ffn_dim}, vocab {V})",
                 "global_batch": B * world,
                 "seq_len": T,
                 "parallelism": f"dp{world}" + ("" if world == 1 else f"-{args.dp}"),
-                "remat_blocks": bool(used_remat),
+                "remat_layers": int(used_remat),
+                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                 "gemm": args.gemm,
                 "master_weights": "fp32", "adam_moments": "fp32",
                 "l2": "per-step working set (>=3 GB bf16 weights plus activations) exceeds the 126 MB L2",

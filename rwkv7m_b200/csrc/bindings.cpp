@@ -4,6 +4,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace {
@@ -133,6 +136,8 @@ Tensor& gemm_error_flag(const at::Device& dev) {
 
 // D = op(A) op(B); see kernels.h for the three layouts.  D must be preallocated.
 void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue) {
+  static const bool trace = [] { const char* e = getenv("RWKV7M_B200_TRACE"); return e != nullptr && e[0] == '1'; }();
+  if (trace) { fprintf(stderr, "[gemm-bind] enter layout=%d epi=%d\n", (int)layout, (int)epilogue); fflush(stderr); }
   c10::cuda::CUDAGuard guard(A.device());
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && D.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: A and B must be bf16");
@@ -155,7 +160,9 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   TORCH_CHECK(D.size(0) == p.M && D.size(1) == p.N, "gemm: output shape mismatch");
   const bool out_bf16 = epilogue == rk::kEpiStoreBf16 || epilogue == rk::kEpiReluSqBf16;
   TORCH_CHECK(D.scalar_type() == (out_bf16 ? at::kBFloat16 : at::kFloat), "gemm: output dtype mismatch");
+  if (trace) { fprintf(stderr, "[gemm-bind] checks ok\n"); fflush(stderr); }
   p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();
+  if (trace) { fprintf(stderr, "[gemm-bind] flag ok\n"); fflush(stderr); }
   const int rc = rk::gemm_bf16(p, stream());
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
 }

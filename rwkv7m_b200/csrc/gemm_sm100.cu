@@ -12,6 +12,8 @@
 // limit runs out the CTA records an error code, drains and frees TMEM.
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -303,6 +305,13 @@ bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int
   }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
+  // The driver entry point needs the primary context bound to the calling thread.  A worker
+  // thread (e.g. an autograd thread) whose first CUDA action is this call has none yet.
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess)
+      return false;
+  }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
@@ -330,9 +339,18 @@ int sm_count() {
   return n;
 }
 
+#define RK_TRACE(...) do { if (trace_on()) { fprintf(stderr, "[gemm] " __VA_ARGS__); fflush(stderr); } } while (0)
+bool trace_on() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("RWKV7M_B200_TRACE"); on = (e != nullptr && e[0] == '1') ? 1 : 0; }
+  return on == 1;
+}
+
 template <int BN, int A_MN, int B_MN, int EPI>
 int launch(const GemmArgs& p, cudaStream_t st) {
   using TL = Tile<BN>;
+  RK_TRACE("launch BN=%d A_MN=%d B_MN=%d EPI=%d M=%d N=%d K=%d lda=%d ldb=%d ldd=%d A=%p B=%p D=%p err=%p\n", BN, A_MN,
+           B_MN, EPI, p.M, p.N, p.K, p.lda, p.ldb, p.ldd, p.A, p.B, p.D, (void*)p.error_flag);
   alignas(64) CUtensorMap ta;
   alignas(64) CUtensorMap tb;
   bool ok;
@@ -340,6 +358,7 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   if (!ok) return 2;
   if (B_MN == 0) ok = make_map(&tb, p.B, p.N, p.K, p.ldb, BN); else ok = make_map(&tb, p.B, p.K, p.N, p.ldb, BK);
   if (!ok) return 2;
+  RK_TRACE("maps ok\n");
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -348,7 +367,9 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  RK_TRACE("attr ok grid=%d smem=%d\n", grid, TL::kSmemBytes);
   kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, p.error_flag);
+  RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -47,6 +47,8 @@ class ScreenedRWKVModel(nn.Module):
     def __init__(self, config: ModelConfig):
         super().__init__()
         self.config = config
+        # execution control: recompute the first k layers in backward even when remat_blocks is off
+        self.remat_layer_count = 0
         C, V = config.d_model, config.vocab_size
         self.emb = nn.Embedding(V, C)
         with torch.no_grad():
@@ -81,7 +83,7 @@ class ScreenedRWKVModel(nn.Module):
         all_stats = []
         for idx, layer in enumerate(self.layers):
             scr = screen_state.layers[screened_idx[idx]] if idx in screened_idx else None
-            if cfg.remat_blocks and torch.is_grad_enabled():
+            if (cfg.remat_blocks or idx < self.remat_layer_count) and torch.is_grad_enabled():
                 x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
             else:
                 x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)

@@ -261,7 +261,7 @@ class ShiftMixFn(torch.autograd.Function):
     def forward(ctx, x, prev, mix):
         xc = x.contiguous()
         prev32 = prev.detach().float().contiguous()
-        out = _C.shift_mix_fwd(xc, prev32, _par(mix))
+        out = _C.shift_mix_fwd(xc, prev32, mix.detach().float().contiguous())
         _count()
         ctx.save_for_backward(xc, prev32, mix)
         ctx.prev_dtype = prev.dtype
@@ -271,7 +271,7 @@ class ShiftMixFn(torch.autograd.Function):
     def backward(ctx, *douts):
         x, prev32, mix = ctx.saved_tensors
         gs = [torch.zeros_like(x) if g is None else g.contiguous() for g in douts]
-        dx, dprev, dmix = _C.shift_mix_bwd(gs, x, prev32, _par(mix))
+        dx, dprev, dmix = _C.shift_mix_bwd(gs, x, prev32, mix.detach().float().contiguous())
         _count()
         return dx, dprev.to(ctx.prev_dtype), _like_param(dmix, mix)
 
