@@ -175,11 +175,18 @@ def main(argv=None):
     for remat in remat_modes:
         cfg.remat_blocks = False
         try:
+            alloc = None
+            if world > 1 and args.dp == "fused":
+                from rwkv7m_b200.parallel.fused_dp import SymmetricFlatBuffers
+
+                alloc = SymmetricFlatBuffers()
             runtime, train_state = R.create_train_runtime(
-                rank * 0 + 7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8
+                7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8,
+                buffer_allocator=alloc,
             )
             train_state.model.remat_layer_count = remat
-            trainer = DataParallelTrainer(train_state, mode=args.dp if world > 1 else "single")
+            mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
+            trainer = DataParallelTrainer(train_state, mode=mode)
             dev_batches = [make_batch(False) for _ in range(2)]
             for i in range(args.warmup):
                 train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime)

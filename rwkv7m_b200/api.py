@@ -85,11 +85,11 @@ def create_runtime(rng_key, config, *, batch_size: int = 1, device=None) -> RWKV
 
 
 def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, device=None,
-                         shard_multiple: int = 1):
+                         shard_multiple: int = 1, buffer_allocator=None):
     config = load_model_config(config)
     train_state = initialize_train_state(
         _seed(rng_key) + 1, config, total_steps=total_steps, device=_default_device(device),
-        shard_multiple=shard_multiple,
+        shard_multiple=shard_multiple, buffer_allocator=buffer_allocator,
     )
     return _make_runtime(train_state.model, config, batch_size), train_state
 

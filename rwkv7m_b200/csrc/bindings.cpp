@@ -388,6 +388,62 @@ void ce_bwd(Tensor logits, const Tensor& targets, const c10::optional<Tensor>& m
              am.data_ptr<int>(), g_ce.data_ptr<float>(), g_l2.data_ptr<float>(), (int)M, (int)V, stream());
 }
 
+// ---- data-parallel optimizer step -------------------------------------------------------
+
+rk::DpPeers make_peers(const std::vector<int64_t>& grad, const std::vector<int64_t>& master,
+                       const std::vector<int64_t>& shadow, const std::vector<int64_t>& aux, int64_t grad_mc,
+                       int64_t master_mc, int64_t shadow_mc) {
+  const size_t world = grad.size();
+  TORCH_CHECK(world >= 1 && world <= (size_t)rk::kMaxRanks, "data-parallel world size must be 1..", rk::kMaxRanks);
+  TORCH_CHECK(master.size() == world && aux.size() == world && (shadow.empty() || shadow.size() == world));
+  rk::DpPeers p{};
+  for (size_t i = 0; i < world; ++i) {
+    p.grad[i] = reinterpret_cast<void*>(grad[i]);
+    p.master[i] = reinterpret_cast<void*>(master[i]);
+    p.shadow[i] = shadow.empty() ? nullptr : reinterpret_cast<void*>(shadow[i]);
+    p.aux[i] = reinterpret_cast<void*>(aux[i]);
+  }
+  p.grad_mc = reinterpret_cast<void*>(grad_mc);
+  p.master_mc = reinterpret_cast<void*>(master_mc);
+  p.shadow_mc = reinterpret_cast<void*>(shadow_mc);
+  return p;
+}
+
+// One optimizer step.  Pointer lists are raw device addresses of the symmetric buffers of every rank.
+// Returns the number of barriers issued so far.
+int64_t dp_step(const std::vector<int64_t>& grad, const std::vector<int64_t>& master, const std::vector<int64_t>& shadow,
+                const std::vector<int64_t>& aux, int64_t grad_mc, int64_t master_mc, int64_t shadow_mc, Tensor m,
+                Tensor v, Tensor norm_out, int64_t rank, int64_t begin, int64_t end, int64_t n_decay,
+                int64_t n_nodecay_end, int64_t barriers_done, int64_t step_index, double lr, double beta1, double beta2,
+                double eps, double weight_decay, double bc1, double bc2, double max_norm) {
+  c10::cuda::CUDAGuard guard(m.device());
+  const int world = (int)grad.size();
+  TORCH_CHECK(m.is_cuda() && m.is_contiguous() && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(m.numel() == end - begin && v.numel() == end - begin, "moment shards must match the owned range");
+  TORCH_CHECK(begin % 4 == 0 && end % 4 == 0, "shard bounds must be multiples of 4 elements");
+  const bool has_mc = grad_mc != 0 && master_mc != 0;
+  rk::DpPeers peers = make_peers(grad, master, shadow, aux, has_mc ? grad_mc : 0, has_mc ? master_mc : 0,
+                                 has_mc ? shadow_mc : 0);
+  cudaStream_t st = stream();
+  uint32_t b = (uint32_t)barriers_done;
+  const int parity = (int)(step_index & 1);
+  rk::dp_barrier(peers, (int)rank, world, ++b, -1, st);
+  rk::dp_reduce_shard(peers, (int)rank, world, begin, end, st);
+  rk::dp_barrier(peers, (int)rank, world, ++b, parity, st);
+  rk::DpAdamW a{};
+  a.rank = (int)rank; a.world = world; a.parity = parity; a.begin = begin; a.end = end;
+  a.n_decay = n_decay; a.n_nodecay_end = n_nodecay_end;
+  a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>(); a.norm_out = norm_out.data_ptr<float>();
+  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2; a.eps = (float)eps;
+  a.weight_decay = (float)weight_decay; a.bc1 = (float)bc1; a.bc2 = (float)bc2; a.max_norm = (float)max_norm;
+  rk::dp_adamw_allgather(peers, a, st);
+  rk::dp_barrier(peers, (int)rank, world, ++b, -1, st);
+  return (int64_t)b;
+}
+
+int64_t dp_aux_error_word() { return rk::dp_aux_error_word(); }
+int64_t dp_aux_words() { return rk::dp_aux_words(); }
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -409,4 +465,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relusq_bwd", &relusq_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
+  m.def("dp_step", &dp_step);
+  m.def("dp_aux_error_word", &dp_aux_error_word);
+  m.def("dp_aux_words", &dp_aux_words);
 }

@@ -78,6 +78,33 @@ void ce_fwd(const void* logits, const int* targets, float* lse, float* maxv, int
 void ce_bwd(void* logits, const int* targets, const float* mask, const float* lse, const float* maxv,
             const int* argmax, const float* g_ce, const float* g_l2, int rows, int V, cudaStream_t st);
 
+// ---- data-parallel optimizer step over symmetric memory -------------------------------
+constexpr int kMaxRanks = 8;
+struct DpPeers {
+  void* grad[kMaxRanks];     // fp32 flat gradient buffer of every rank (peer-mapped)
+  void* master[kMaxRanks];   // fp32 flat master parameters of every rank
+  void* shadow[kMaxRanks];   // bf16 compute copy of every rank (entries may be null)
+  void* aux[kMaxRanks];      // small scratch: barrier counters, norm partials, error word
+  void* grad_mc;             // multicast addresses of the same buffers, or null without NVSwitch multicast
+  void* master_mc;
+  void* shadow_mc;
+};
+struct DpAdamW {
+  int rank, world, parity;
+  int64_t begin, end;              // owned element range in the flat buffers
+  int64_t n_decay, n_nodecay_end;  // group boundaries
+  float* m; float* v;              // Adam moments of the owned shard (local index = i - begin)
+  float* norm_out;                 // receives the global gradient norm
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2, max_norm;
+};
+// target = number of barriers issued so far on this buffer (same on every rank);
+// publish_parity >= 0 also stores this rank's partial sum of squares to every peer first.
+void dp_barrier(const DpPeers& peers, int rank, int world, uint32_t target, int publish_parity, cudaStream_t st);
+void dp_reduce_shard(const DpPeers& peers, int rank, int world, int64_t begin, int64_t end, cudaStream_t st);
+void dp_adamw_allgather(const DpPeers& peers, const DpAdamW& a, cudaStream_t st);
+int dp_aux_error_word();
+int dp_aux_words();
+
 // ---- GEMM (tcgen05) -------------------------------------------------------------
 enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
 enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3 };

@@ -7,12 +7,13 @@
 //
 // One CTA per (batch, head).  The per-step vectors are streamed through shared
 // memory in chunks of 16 time steps with cp.async, double-buffered, so global
-// latency is paid once per chunk and never inside the recurrence.  Forward: four
-// threads share row i of S (16 columns each for N = 64); a mat-vec product is a
-// short thread-local dot plus two shuffles and no block barrier is needed inside a
-// chunk.  Backward: 8N threads; the first 4N own rows of the state cotangent, the
-// other 4N own columns of both the state and its cotangent, exchanging one vector
-// per step through shared memory.  The previous state is re-derived by undoing one
+// latency is paid once per chunk and never inside the recurrence.  Forward: each
+// thread holds a 2 x 16 register tile of S (two rows, a quarter of the columns), so
+// a mat-vec product is a short thread-local dot plus two shuffles, each broadcast
+// value read from shared memory feeds two rows, and no block barrier is needed
+// inside a chunk.  Backward: half of the threads own rows of the state cotangent,
+// the other half own columns of both the state and its cotangent, exchanging one
+// vector per step through shared memory.  The previous state is re-derived by undoing one
 // step (division by the decay, which the soft clamp keeps above 0.545) and is
 // re-anchored from an exact checkpoint at every chunk boundary.
 //
@@ -73,28 +74,34 @@ __device__ __forceinline__ void stage_chunk(T* tile, const VecPtrs<T, NV>& src, 
   }
 }
 
+constexpr int RPT = 2;  // state rows (forward) / rows-or-columns (backward) held by one thread
+
+// Forward: 2N threads.  Thread (g, p) holds rows 2g, 2g+1 of S restricted to the 16 columns of part p, so
+// every broadcast vector value it loads from shared memory feeds two rows.
 template <typename T, int N, bool SAVE>
-__global__ void __launch_bounds__(4 * N) wkv7_fwd_kernel(VecPtrs<T, 6> src, const float* __restrict__ s0,
-                                                         T* __restrict__ y, float* __restrict__ sT,
-                                                         float* __restrict__ sa_out, float* __restrict__ ckpt,
-                                                         int Tlen, int H) {
+__global__ void __launch_bounds__(4 * N / RPT) wkv7_fwd_kernel(VecPtrs<T, 6> src, const float* __restrict__ s0,
+                                                               T* __restrict__ y, float* __restrict__ sT,
+                                                               float* __restrict__ sa_out, float* __restrict__ ckpt,
+                                                               int Tlen, int H) {
   constexpr int NQ = N / 16;
-  constexpr int NT = 4 * N;
+  constexpr int NT = 4 * N / RPT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* tiles = reinterpret_cast<T*>(smem_raw);                                   // [2][6][CH][N]: r,w,k,v,a,b (raw)
   float* work = reinterpret_cast<float*>(smem_raw + 2 * 6 * CH * N * sizeof(T));  // [6][CH][N] fp32, slot 1 = decay
   const int bh = blockIdx.x;
   const int bidx = bh / H, h = bh % H;
   const int tid = threadIdx.x;
-  const int i = tid >> 2, p = tid & 3;
+  const int i0 = (tid >> 2) * RPT, p = tid & 3;
   const int BH = gridDim.x;
 
-  float S[4 * NQ];
+  float S[RPT][4 * NQ];
 #pragma unroll
-  for (int q = 0; q < NQ; ++q) {
-    const float4 t4 = load4(s0 + ((size_t)bh * N + i) * N + pos_of(q, p, 0));
-    S[4 * q] = t4.x; S[4 * q + 1] = t4.y; S[4 * q + 2] = t4.z; S[4 * q + 3] = t4.w;
-  }
+  for (int rr = 0; rr < RPT; ++rr)
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      const float4 t4 = load4(s0 + ((size_t)bh * N + i0 + rr) * N + pos_of(q, p, 0));
+      S[rr][4 * q] = t4.x; S[rr][4 * q + 1] = t4.y; S[rr][4 * q + 2] = t4.z; S[rr][4 * q + 3] = t4.w;
+    }
   const size_t stride_t = (size_t)H * N;
   const size_t base = ((size_t)bidx * Tlen * H + h) * N;
   const int nch = (Tlen + CH - 1) / CH;
@@ -123,85 +130,110 @@ __global__ void __launch_bounds__(4 * N) wkv7_fwd_kernel(VecPtrs<T, 6> src, cons
       const float* vv = work + (3 * CH + s) * N;
       const float* va = work + (4 * CH + s) * N;
       const float* vb = work + (5 * CH + s) * N;
-      const float vi = vv[i];
-      float sa0 = 0.f, sa1 = 0.f;
+      float vi[RPT], sa[RPT], yy[RPT];
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) { vi[rr] = vv[i0 + rr]; sa[rr] = 0.f; yy[rr] = 0.f; }
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
         const float4 aa = load4(va + pos_of(q, p, 0));
-        sa0 += S[4 * q] * aa.x + S[4 * q + 2] * aa.z;
-        sa1 += S[4 * q + 1] * aa.y + S[4 * q + 3] * aa.w;
+#pragma unroll
+        for (int rr = 0; rr < RPT; ++rr)
+          sa[rr] += (S[rr][4 * q] * aa.x + S[rr][4 * q + 2] * aa.z) + (S[rr][4 * q + 1] * aa.y + S[rr][4 * q + 3] * aa.w);
       }
-      const float sa = quad_sum(sa0 + sa1);
-      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) sa[rr] = quad_sum(sa[rr]);
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
         const int o = pos_of(q, p, 0);
-        const float4 dd = load4(vd + o), bb = load4(vb + o), kk = load4(vk + o), rr = load4(vr + o);
-        S[4 * q] = S[4 * q] * dd.x + sa * bb.x + vi * kk.x;
-        S[4 * q + 1] = S[4 * q + 1] * dd.y + sa * bb.y + vi * kk.y;
-        S[4 * q + 2] = S[4 * q + 2] * dd.z + sa * bb.z + vi * kk.z;
-        S[4 * q + 3] = S[4 * q + 3] * dd.w + sa * bb.w + vi * kk.w;
-        y0 += S[4 * q] * rr.x + S[4 * q + 2] * rr.z;
-        y1 += S[4 * q + 1] * rr.y + S[4 * q + 3] * rr.w;
+        const float4 dd = load4(vd + o), bb = load4(vb + o), kk = load4(vk + o), rv = load4(vr + o);
+#pragma unroll
+        for (int rr = 0; rr < RPT; ++rr) {
+          float* Sr = S[rr];
+          Sr[4 * q] = Sr[4 * q] * dd.x + sa[rr] * bb.x + vi[rr] * kk.x;
+          Sr[4 * q + 1] = Sr[4 * q + 1] * dd.y + sa[rr] * bb.y + vi[rr] * kk.y;
+          Sr[4 * q + 2] = Sr[4 * q + 2] * dd.z + sa[rr] * bb.z + vi[rr] * kk.z;
+          Sr[4 * q + 3] = Sr[4 * q + 3] * dd.w + sa[rr] * bb.w + vi[rr] * kk.w;
+          yy[rr] += (Sr[4 * q] * rv.x + Sr[4 * q + 2] * rv.z) + (Sr[4 * q + 1] * rv.y + Sr[4 * q + 3] * rv.w);
+        }
       }
-      const float yy = quad_sum(y0 + y1);
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) yy[rr] = quad_sum(yy[rr]);
       if (p == 0) {
-        const size_t o = base + (size_t)(c * CH + s) * stride_t + i;
-        y[o] = from_float<T>(yy);
-        if (SAVE) sa_out[o] = sa;
+        const size_t o = base + (size_t)(c * CH + s) * stride_t + i0;
+#pragma unroll
+        for (int rr = 0; rr < RPT; ++rr) {
+          y[o + rr] = from_float<T>(yy[rr]);
+          if (SAVE) sa_out[o + rr] = sa[rr];
+        }
       }
     }
     if (SAVE) {
-      float* dst = ckpt + (((size_t)c * BH + bh) * N + i) * N;
 #pragma unroll
-      for (int q = 0; q < NQ; ++q)
-        *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+      for (int rr = 0; rr < RPT; ++rr) {
+        float* dst = ckpt + (((size_t)c * BH + bh) * N + i0 + rr) * N;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q)
+          *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) =
+              make_float4(S[rr][4 * q], S[rr][4 * q + 1], S[rr][4 * q + 2], S[rr][4 * q + 3]);
+      }
     }
   }
-  float* dst = sT + ((size_t)bh * N + i) * N;
 #pragma unroll
-  for (int q = 0; q < NQ; ++q)
-    *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+  for (int rr = 0; rr < RPT; ++rr) {
+    float* dst = sT + ((size_t)bh * N + i0 + rr) * N;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+      *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) =
+          make_float4(S[rr][4 * q], S[rr][4 * q + 1], S[rr][4 * q + 2], S[rr][4 * q + 3]);
+  }
 }
 
 template <typename T, int N>
 constexpr size_t fwd_smem_bytes() { return 2 * 6 * CH * N * sizeof(T) + 6 * CH * N * sizeof(float); }
 
-// Backward.  Tile vectors: r,w,k,v,a,b,dy (type T) and sa (fp32).
+// Backward.  Tile vectors: r,w,k,v,a,b,dy (type T) and sa (fp32).  4N threads: the first 2N own two rows
+// each of the state cotangent G (16 columns per thread), the other 2N own two columns each of both the
+// state S and G (16 rows per thread).
 template <typename T, int N>
-__global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
+__global__ void __launch_bounds__(8 * N / RPT, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
     VecPtrs<T, 7> src, const float* __restrict__ sa, const float* __restrict__ ckpt, const float* __restrict__ s0,
     const float* __restrict__ dsT, T* __restrict__ dr, T* __restrict__ dw, T* __restrict__ dk, T* __restrict__ dv,
     T* __restrict__ da, T* __restrict__ db, float* __restrict__ ds0, int Tlen, int H) {
   constexpr int NQ = N / 16;
-  constexpr int NT = 8 * N;
+  constexpr int NE = 4 * NQ;
+  constexpr int HALF = 4 * N / RPT;
+  constexpr int NT = 2 * HALF;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* tiles = reinterpret_cast<T*>(smem_raw);                                         // [2][7][CH][N]
   float* sa_tiles = reinterpret_cast<float*>(smem_raw + 2 * 7 * CH * N * sizeof(T));  // [2][CH][N]
   float* work = sa_tiles + 2 * CH * N;                                                // [7][CH][N] fp32, slot 1 = decay
   float* ewd = work + 7 * CH * N;                                                     // [CH][N]  -exp(w) * d
   float* sdsa = ewd + CH * N;                                                         // [2][N]
+  float* anc = sdsa + 2 * N;                                                          // [2][N][N] exact chunk-start state
   const int bh = blockIdx.x;
   const int bidx = bh / H, h = bh % H;
   const int tid = threadIdx.x;
-  const bool is_col = tid >= 4 * N;
-  const int idx = (is_col ? tid - 4 * N : tid) >> 2;  // row i or column j
+  const bool is_col = tid >= HALF;
+  const int idx0 = ((is_col ? tid - HALF : tid) >> 2) * RPT;  // first row i (row threads) or column j (column threads)
   const int p = tid & 3;
   const int BH = gridDim.x;
 
-  float G[4 * NQ];
-  float S[4 * NQ];
-  float A[4 * NQ];  // prefetched anchor (exact S at the start of the chunk), column threads only
+  float G[RPT][NE];
+  float S[RPT][NE];
 #pragma unroll
-  for (int e = 0; e < 4 * NQ; ++e) { G[e] = 0.f; S[e] = 0.f; A[e] = 0.f; }
+  for (int u = 0; u < RPT; ++u)
+#pragma unroll
+    for (int e = 0; e < NE; ++e) { G[u][e] = 0.f; S[u][e] = 0.f; }
   if (dsT != nullptr) {
 #pragma unroll
-    for (int q = 0; q < NQ; ++q)
+    for (int u = 0; u < RPT; ++u)
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int o = pos_of(q, p, x);
-        G[4 * q + x] = is_col ? dsT[((size_t)bh * N + o) * N + idx] : dsT[((size_t)bh * N + idx) * N + o];
-      }
+      for (int q = 0; q < NQ; ++q)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int o = pos_of(q, p, x);
+          G[u][4 * q + x] = is_col ? dsT[((size_t)bh * N + o) * N + idx0 + u] : dsT[((size_t)bh * N + idx0 + u) * N + o];
+        }
   }
   const int nch = (Tlen + CH - 1) / CH;
   if (is_col) {
@@ -209,7 +241,10 @@ __global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
 #pragma unroll
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
-      for (int x = 0; x < 4; ++x) S[4 * q + x] = srcS[pos_of(q, p, x) * N + idx];
+      for (int x = 0; x < 4; ++x) {
+        const float2 t2 = *reinterpret_cast<const float2*>(srcS + pos_of(q, p, x) * N + idx0);
+        S[0][4 * q + x] = t2.x; S[1][4 * q + x] = t2.y;
+      }
   }
 
   const size_t stride_t = (size_t)H * N;
@@ -219,6 +254,10 @@ __global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
   auto stage = [&](int c, int buf) {
     stage_chunk<T, N, 7>(tiles + (size_t)buf * 7 * CH * N, src, base, stride_t, c, Tlen, tid, NT);
     stage_chunk<float, N, 1>(sa_tiles + (size_t)buf * CH * N, sa_src, base, stride_t, c, Tlen, tid, NT);
+    // exact state before the first step of chunk c (initial state for chunk 0)
+    const float* prev = (c == 0) ? (s0 + (size_t)bh * N * N) : (ckpt + ((size_t)(c - 1) * BH + bh) * N * N);
+    float* dst = anc + (size_t)buf * N * N;
+    for (int pc = tid; pc < N * N / 4; pc += NT) cp_async16(dst + pc * 4, prev + pc * 4);
     cp_async_commit();
   };
   stage(nch - 1, (nch - 1) & 1);
@@ -240,20 +279,13 @@ __global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
         work[e] = x;
       }
     }
-    if (is_col) {
-      // exact state before the first step of this chunk; its latency hides behind the chunk's steps
-      const float* prev = (c == 0) ? (s0 + (size_t)bh * N * N) : (ckpt + ((size_t)(c - 1) * BH + bh) * N * N);
-#pragma unroll
-      for (int q = 0; q < NQ; ++q)
-#pragma unroll
-        for (int x = 0; x < 4; ++x) A[4 * q + x] = prev[pos_of(q, p, x) * N + idx];
-    }
+    const float* anchor_tile = anc + (size_t)buf * N * N;
     __syncthreads();
     const int steps = min(CH, Tlen - c * CH);
     for (int s = steps - 1; s >= 0; --s) {
       const int t = c * CH + s;
       const int sb = t & 1;
-      const size_t o = base + (size_t)t * stride_t + idx;
+      const size_t o = base + (size_t)t * stride_t + idx0;
       const float* vr = work + (0 * CH + s) * N;
       const float* vd = work + (1 * CH + s) * N;
       const float* vk = work + (2 * CH + s) * N;
@@ -263,33 +295,48 @@ __global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
       const float* vdy = work + (6 * CH + s) * N;
       const float* vsa = sat + s * N;
       if (!is_col) {
-        const float dyi = vdy[idx];
-        float dsa = 0.f, dvi = 0.f;
+        float dyi[RPT], dsa[RPT], dvi[RPT];
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) { dyi[u] = vdy[idx0 + u]; dsa[u] = 0.f; dvi[u] = 0.f; }
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const int po = pos_of(q, p, 0);
           const float4 rr = load4(vr + po), bb = load4(vb + po), kk = load4(vk + po);
-          G[4 * q] += dyi * rr.x; G[4 * q + 1] += dyi * rr.y; G[4 * q + 2] += dyi * rr.z; G[4 * q + 3] += dyi * rr.w;
-          dsa += G[4 * q] * bb.x + G[4 * q + 1] * bb.y + G[4 * q + 2] * bb.z + G[4 * q + 3] * bb.w;
-          dvi += G[4 * q] * kk.x + G[4 * q + 1] * kk.y + G[4 * q + 2] * kk.z + G[4 * q + 3] * kk.w;
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) {
+            float* g = G[u] + 4 * q;
+            g[0] += dyi[u] * rr.x; g[1] += dyi[u] * rr.y; g[2] += dyi[u] * rr.z; g[3] += dyi[u] * rr.w;
+            dsa[u] += (g[0] * bb.x + g[2] * bb.z) + (g[1] * bb.y + g[3] * bb.w);
+            dvi[u] += (g[0] * kk.x + g[2] * kk.z) + (g[1] * kk.y + g[3] * kk.w);
+          }
         }
-        dsa = quad_sum(dsa);
-        dvi = quad_sum(dvi);
-        if (p == 0) { sdsa[sb * N + idx] = dsa; dv[o] = from_float<T>(dvi); }
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) { dsa[u] = quad_sum(dsa[u]); dvi[u] = quad_sum(dvi[u]); }
+        if (p == 0) {
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) { sdsa[sb * N + idx0 + u] = dsa[u]; dv[o + u] = from_float<T>(dvi[u]); }
+        }
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const int po = pos_of(q, p, 0);
           const float4 dd = load4(vd + po), aa = load4(va + po);
-          G[4 * q] = G[4 * q] * dd.x + dsa * aa.x;
-          G[4 * q + 1] = G[4 * q + 1] * dd.y + dsa * aa.y;
-          G[4 * q + 2] = G[4 * q + 2] * dd.z + dsa * aa.z;
-          G[4 * q + 3] = G[4 * q + 3] * dd.w + dsa * aa.w;
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) {
+            float* g = G[u] + 4 * q;
+            g[0] = g[0] * dd.x + dsa[u] * aa.x;
+            g[1] = g[1] * dd.y + dsa[u] * aa.y;
+            g[2] = g[2] * dd.z + dsa[u] * aa.z;
+            g[3] = g[3] * dd.w + dsa[u] * aa.w;
+          }
         }
       } else {
         const bool anchor = s == 0;
-        const float rj = vr[idx], bj = vb[idx], kj = vk[idx], dj = vd[idx];
-        const float inv_d = 1.0f / dj;
-        float drj = 0.f, ddj = 0.f, dbj = 0.f, dkj = 0.f;
+        float rj[RPT], bj[RPT], kj[RPT], inv_d[RPT], drj[RPT], ddj[RPT], dbj[RPT], dkj[RPT];
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) {
+          rj[u] = vr[idx0 + u]; bj[u] = vb[idx0 + u]; kj[u] = vk[idx0 + u]; inv_d[u] = 1.0f / vd[idx0 + u];
+          drj[u] = 0.f; ddj[u] = 0.f; dbj[u] = 0.f; dkj[u] = 0.f;
+        }
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const int po = pos_of(q, p, 0);
@@ -298,55 +345,78 @@ __global__ void __launch_bounds__(8 * N, (N == 64 ? 2 : 1)) wkv7_bwd_kernel(
           const float sav[4] = {sa4.x, sa4.y, sa4.z, sa4.w};
           const float vvv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int e = 4 * q + x;
-            drj += S[e] * dyv[x];
-            G[e] += dyv[x] * rj;
-            const float sp = anchor ? A[e] : (S[e] - sav[x] * bj - vvv[x] * kj) * inv_d;
-            ddj += G[e] * sp;
-            dbj += G[e] * sav[x];
-            dkj += G[e] * vvv[x];
-            S[e] = sp;
-          }
+          for (int u = 0; u < RPT; ++u)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int e = 4 * q + x;
+              drj[u] += S[u][e] * dyv[x];
+              G[u][e] += dyv[x] * rj[u];
+              const float sp = anchor ? anchor_tile[pos_of(q, p, x) * N + idx0 + u]
+                                      : (S[u][e] - sav[x] * bj[u] - vvv[x] * kj[u]) * inv_d[u];
+              ddj[u] += G[u][e] * sp;
+              dbj[u] += G[u][e] * sav[x];
+              dkj[u] += G[u][e] * vvv[x];
+              S[u][e] = sp;
+            }
         }
-        drj = quad_sum(drj); ddj = quad_sum(ddj); dbj = quad_sum(dbj); dkj = quad_sum(dkj);
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) {
+          drj[u] = quad_sum(drj[u]); ddj[u] = quad_sum(ddj[u]); dbj[u] = quad_sum(dbj[u]); dkj[u] = quad_sum(dkj[u]);
+        }
         if (p == 0) {
-          dr[o] = from_float<T>(drj);
-          dw[o] = from_float<T>(ddj * ewd[s * N + idx]);
-          dk[o] = from_float<T>(dkj);
-          db[o] = from_float<T>(dbj);
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) {
+            dr[o + u] = from_float<T>(drj[u]);
+            dw[o + u] = from_float<T>(ddj[u] * ewd[s * N + idx0 + u]);
+            dk[o + u] = from_float<T>(dkj[u]);
+            db[o + u] = from_float<T>(dbj[u]);
+          }
         }
       }
       __syncthreads();  // dsa of this step is visible; sdsa[sb] is rewritten two steps later
       if (is_col) {
-        const float aj = va[idx], dj = vd[idx];
         const float* ds = sdsa + sb * N;
-        float daj = 0.f;
+        float aj[RPT], dj[RPT], daj[RPT];
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) { aj[u] = va[idx0 + u]; dj[u] = vd[idx0 + u]; daj[u] = 0.f; }
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const float4 d4 = load4(ds + pos_of(q, p, 0));
-          daj += S[4 * q] * d4.x + S[4 * q + 1] * d4.y + S[4 * q + 2] * d4.z + S[4 * q + 3] * d4.w;
-          G[4 * q] = G[4 * q] * dj + d4.x * aj;
-          G[4 * q + 1] = G[4 * q + 1] * dj + d4.y * aj;
-          G[4 * q + 2] = G[4 * q + 2] * dj + d4.z * aj;
-          G[4 * q + 3] = G[4 * q + 3] * dj + d4.w * aj;
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) {
+            float* g = G[u] + 4 * q;
+            const float* sv = S[u] + 4 * q;
+            daj[u] += (sv[0] * d4.x + sv[2] * d4.z) + (sv[1] * d4.y + sv[3] * d4.w);
+            g[0] = g[0] * dj[u] + d4.x * aj[u];
+            g[1] = g[1] * dj[u] + d4.y * aj[u];
+            g[2] = g[2] * dj[u] + d4.z * aj[u];
+            g[3] = g[3] * dj[u] + d4.w * aj[u];
+          }
         }
-        daj = quad_sum(daj);
-        if (p == 0) da[o] = from_float<T>(daj);
+#pragma unroll
+        for (int u = 0; u < RPT; ++u) daj[u] = quad_sum(daj[u]);
+        if (p == 0) {
+#pragma unroll
+          for (int u = 0; u < RPT; ++u) da[o + u] = from_float<T>(daj[u]);
+        }
       }
     }
   }
   if (!is_col) {
-    float* dst = ds0 + ((size_t)bh * N + idx) * N;
 #pragma unroll
-    for (int q = 0; q < NQ; ++q)
-      *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) = make_float4(G[4 * q], G[4 * q + 1], G[4 * q + 2], G[4 * q + 3]);
+    for (int u = 0; u < RPT; ++u) {
+      float* dst = ds0 + ((size_t)bh * N + idx0 + u) * N;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q)
+        *reinterpret_cast<float4*>(dst + pos_of(q, p, 0)) =
+            make_float4(G[u][4 * q], G[u][4 * q + 1], G[u][4 * q + 2], G[u][4 * q + 3]);
+    }
   }
 }
 
 template <typename T, int N>
 constexpr size_t bwd_smem_bytes() {
-  return 2 * 7 * CH * N * sizeof(T) + (2 * CH * N + 7 * CH * N + CH * N + 2 * N) * sizeof(float);
+  return 2 * 7 * CH * N * sizeof(T) + (2 * CH * N + 7 * CH * N + CH * N + 2 * N + 2 * N * N) * sizeof(float);
 }
 
 template <typename T, int N>
@@ -359,11 +429,11 @@ static int launch_fwd_n(const WkvArgs& p, cudaStream_t st) {
   if (p.sa != nullptr) {
     auto kern = wkv7_fwd_kernel<T, N, true>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, 4 * N, smem, st>>>(src, p.s0, (T*)p.y, p.sT, p.sa, p.ckpt, p.T, p.H);
+    kern<<<grid, 4 * N / RPT, smem, st>>>(src, p.s0, (T*)p.y, p.sT, p.sa, p.ckpt, p.T, p.H);
   } else {
     auto kern = wkv7_fwd_kernel<T, N, false>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, 4 * N, smem, st>>>(src, p.s0, (T*)p.y, p.sT, nullptr, nullptr, p.T, p.H);
+    kern<<<grid, 4 * N / RPT, smem, st>>>(src, p.s0, (T*)p.y, p.sT, nullptr, nullptr, p.T, p.H);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
@@ -377,7 +447,7 @@ static int launch_bwd_n(const WkvArgs& p, cudaStream_t st) {
   auto kern = wkv7_bwd_kernel<T, N>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(p.B * p.H);
-  kern<<<grid, 8 * N, smem, st>>>(src, p.sa, p.ckpt, p.s0, p.dsT, (T*)p.dr, (T*)p.dw, (T*)p.dk, (T*)p.dv, (T*)p.da,
+  kern<<<grid, 8 * N / RPT, smem, st>>>(src, p.sa, p.ckpt, p.s0, p.dsT, (T*)p.dr, (T*)p.dw, (T*)p.dk, (T*)p.dv, (T*)p.da,
                                  (T*)p.db, p.ds0, p.T, p.H);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

@@ -1,0 +1,129 @@
+"""Sharded AdamW whose collectives run inside the optimizer kernels.
+
+The flat gradient, master-parameter and bf16 compute buffers live in NVLink
+symmetric memory (``torch.distributed._symmetric_memory``: one allocation per
+rank, mapped into every peer and, when NVSwitch multicast is available, bound to
+a multicast address).  Each rank keeps Adam moments only for its 1/world slice.
+``step()`` launches the kernels of ``csrc/dp_fused.cu``: barrier -> reduce the
+owned gradient shard (``multimem.ld_reduce`` or peer loads) -> publish partial
+norms + barrier -> clip + AdamW + store fp32 master and bf16 copy to every rank
+(``multimem.st`` or peer stores) -> barrier.  NCCL is used only for the
+rendezvous and the initial parameter broadcast.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..models.model import torch_dtype
+
+
+def shard_bounds(total: int, world: int, rank: int, multiple: int = 8):
+    """Contiguous equal split of [0, total); ``total`` must divide by world*multiple."""
+    if total % (world * multiple) != 0:
+        raise ValueError(f"flat buffer length {total} is not a multiple of world*{multiple}")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+class SymmetricFlatBuffers:
+    """Allocator handed to ``FlatParams``: places master / grad / compute buffers in symmetric memory."""
+
+    def __init__(self, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.symm = symm
+        self.group = group if group is not None else dist.group.WORLD
+        enable = getattr(symm, "enable_symm_mem_for_group", None)
+        if enable is not None:
+            try:
+                enable(self.group.group_name)
+            except Exception:  # newer torch releases enable every group implicitly
+                pass
+        self.handles = {}
+        self.tensors = {}
+
+    def __call__(self, name, numel, dtype, device):
+        t = self.symm.empty(numel, dtype=dtype, device=device)
+        t.zero_()
+        self.tensors[name] = t
+        return t
+
+    def rendezvous(self):
+        for name, t in self.tensors.items():
+            self.handles[name] = self.symm.rendezvous(t, self.group)
+        return self.handles
+
+
+class FusedShardedAdamW:
+    def __init__(self, optimizer, group=None, use_multicast: bool = True):
+        from ..ops.build import load_extension
+
+        self._C = load_extension()
+        self.opt = optimizer
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        flat = optimizer.flat
+        alloc = getattr(flat, "allocator", None)
+        if not isinstance(alloc, SymmetricFlatBuffers):
+            raise RuntimeError(
+                "fused data parallelism needs the flat buffers in symmetric memory: create the train state "
+                "with buffer_allocator=SymmetricFlatBuffers(group)"
+            )
+        cfg = optimizer.config
+        if torch_dtype(cfg.param_dtype) != torch.float32 or torch_dtype(cfg.gradient_accum_dtype) != torch.float32:
+            raise ValueError("fused data parallelism expects fp32 master parameters and fp32 gradient accumulation")
+        self.alloc = alloc
+        dev = flat.master.device
+        self.aux = alloc("aux", self._C.dp_aux_words(), torch.int32, dev)
+        handles = alloc.rendezvous()
+        self.h_grad, self.h_master, self.h_aux = handles["grad"], handles["master"], handles["aux"]
+        self.h_shadow = handles.get("compute")
+        self.begin, self.end = shard_bounds(flat.master.numel(), self.world, self.rank)
+        n = self.end - self.begin
+        # Adam moments only for the owned slice; drop the replicated ones the base optimizer allocated
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        optimizer.exp_avg = optimizer.exp_avg_sq = None
+        self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.barriers = 0
+        self.use_multicast = bool(use_multicast) and all(
+            int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in (self.h_grad, self.h_master)
+        ) and (self.h_shadow is None or int(self.h_shadow.multicast_ptr or 0) != 0)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def _ptrs(self, handle):
+        return [int(p) for p in handle.buffer_ptrs]
+
+    def step(self):
+        opt, cfg, flat = self.opt, self.opt.config, self.opt.flat
+        flat.collect_grads()
+        lr = opt.current_lr()
+        t = opt.count + 1
+        mc = self.use_multicast
+        self.barriers = self._C.dp_step(
+            self._ptrs(self.h_grad), self._ptrs(self.h_master),
+            self._ptrs(self.h_shadow) if self.h_shadow is not None else [],
+            self._ptrs(self.h_aux),
+            int(self.h_grad.multicast_ptr) if mc else 0,
+            int(self.h_master.multicast_ptr) if mc else 0,
+            int(self.h_shadow.multicast_ptr) if (mc and self.h_shadow is not None) else 0,
+            self.exp_avg, self.exp_avg_sq, self.norm, self.rank, self.begin, self.end,
+            int(flat.bounds[0]), int(flat.bounds[1]), self.barriers, opt.count,
+            lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, cfg.weight_decay,
+            1.0 - cfg.adam_beta1**t, 1.0 - cfg.adam_beta2**t, cfg.max_grad_norm,
+        )
+        from ..ops import cuda as K
+
+        K._count(5)
+        # every peer has finished reading this rank's gradients (second barrier): clear them for the next step
+        flat.grad.zero_()
+        opt.grad_norm = self.norm.reshape(())
+        opt.count += 1
+
+    def error_code(self) -> int:
+        """Non-zero when a bounded wait on a peer ran out (host sync)."""
+        return int(self.aux[self._C.dp_aux_error_word()].item())

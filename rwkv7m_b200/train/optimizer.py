@@ -92,7 +92,7 @@ class FlatParams:
     are the group boundaries inside the buffers.
     """
 
-    def __init__(self, model, config: ModelConfig, shard_multiple: int = 1):
+    def __init__(self, model, config: ModelConfig, shard_multiple: int = 1, allocator=None):
         named = [(n, p) for n, p in model.named_parameters()]
         groups = ([], [], [])
         for n, p in named:
@@ -111,11 +111,15 @@ class FlatParams:
         pdtype = torch_dtype(config.param_dtype)
         gdtype = torch_dtype(config.gradient_accum_dtype)
         cdtype = torch_dtype(config.dtype)
-        self.master = torch.zeros(total, dtype=pdtype, device=device)
-        self.grad = torch.zeros(total, dtype=gdtype, device=device)
+        # ``allocator(name, numel, dtype, device)`` lets a caller place the buffers elsewhere
+        # (e.g. NVLink symmetric memory for the fused data-parallel step)
+        self.allocator = allocator
+        alloc = allocator or (lambda name, numel, dtype, dev: torch.zeros(numel, dtype=dtype, device=dev))
+        self.master = alloc("master", total, pdtype, device)
+        self.grad = alloc("grad", total, gdtype, device)
         self.compute = None
         if device.type == "cuda" and cdtype != pdtype:
-            self.compute = torch.zeros(total, dtype=cdtype, device=device)
+            self.compute = alloc("compute", total, cdtype, device)
         # autograd only accepts a .grad of the parameter's own dtype; with bf16
         # parameters and fp32 accumulation the per-parameter grads are folded
         # into the flat buffer by collect_grads() instead.
@@ -157,9 +161,10 @@ class FlatParams:
 class AdamWChain:
     """clip -> AdamW -> x2(w0) over a :class:`FlatParams` buffer set."""
 
-    def __init__(self, model, config: ModelConfig, total_steps: int = 10000, shard_multiple: int = 1):
+    def __init__(self, model, config: ModelConfig, total_steps: int = 10000, shard_multiple: int = 1,
+                 buffer_allocator=None):
         self.config = config
-        self.flat = FlatParams(model, config, shard_multiple)
+        self.flat = FlatParams(model, config, shard_multiple, buffer_allocator)
         self.schedule = make_schedule(config, total_steps)
         self.total_steps = int(total_steps)
         sdtype = torch_dtype(config.optimizer_state_dtype)
@@ -239,5 +244,6 @@ class AdamWChain:
             self.exp_avg_sq[off : off + numel].copy_(state[f"exp_avg_sq/{name}"].reshape(-1))
 
 
-def create_optimizer(model, config: ModelConfig, total_steps: int = 10000, shard_multiple: int = 1) -> AdamWChain:
-    return AdamWChain(model, config, total_steps, shard_multiple)
+def create_optimizer(model, config: ModelConfig, total_steps: int = 10000, shard_multiple: int = 1,
+                     buffer_allocator=None) -> AdamWChain:
+    return AdamWChain(model, config, total_steps, shard_multiple, buffer_allocator)

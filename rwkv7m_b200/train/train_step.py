@@ -49,9 +49,9 @@ class TrainState:
 
 
 def initialize_train_state(seed, config: ModelConfig, *, total_steps: int = 10000, device=None,
-                           shard_multiple: int = 1) -> TrainState:
+                           shard_multiple: int = 1, buffer_allocator=None) -> TrainState:
     model = initialize_model(seed, config, device=device)
-    optimizer = create_optimizer(model, config, total_steps, shard_multiple)
+    optimizer = create_optimizer(model, config, total_steps, shard_multiple, buffer_allocator)
     return TrainState(model=model, optimizer=optimizer, config=config)
 
 

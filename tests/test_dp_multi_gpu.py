@@ -1,0 +1,34 @@
+"""Fused data-parallel optimizer step (symmetric memory) against the all-reduce baseline on >= 2 GPUs."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(world, multicast):
+    env = dict(os.environ, RWKV7M_B200_DP_MULTICAST="1" if multicast else "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29531", str(Path(__file__).with_name("dp_worker.py"))]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
+    return json.loads(line)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("multicast", [False, True])
+def test_fused_step_matches_allreduce(multicast):
+    res = _run(2, multicast)
+    assert res["error_code"] == 0
+    assert res["rank_spread"] == 0.0
+    assert res["max_master_diff"] < 2e-4, res
+    assert abs(res["norm_ref"] - res["norm_fused"]) < 1e-3 * max(res["norm_ref"], 1e-6)
+    for a, b in zip(res["loss_ref"], res["loss_fused"]):
+        assert abs(a - b) < 5e-3 * abs(a)
