@@ -1,0 +1,37 @@
+"""``rwkv7m-plan-scale``: print the training-memory estimate as JSON
+(reference: src/rwkv7m/cli/plan_scale.py)."""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+from ..config import MODEL_PRESET_NAMES, load_model_config, model_preset
+from ..parallel.scaling import DTypePolicy, estimate_training_memory
+
+
+def parse_args(argv=None):
+    p = argparse.ArgumentParser(description="Estimate parameter-related training memory.")
+    src = p.add_mutually_exclusive_group(required=True)
+    src.add_argument("--model-config")
+    src.add_argument("--model-preset", choices=MODEL_PRESET_NAMES)
+    p.add_argument("--model-axis-size", type=int, required=True)
+    p.add_argument("--dtype-policy", choices=["config", "stability", "memory"], default="config")
+    p.add_argument("--optimizer-shards", type=int, default=1)
+    p.add_argument("--tokens-per-device", type=int, default=0)
+    return p.parse_args(argv)
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    cfg = load_model_config(args.model_config) if args.model_config else model_preset(args.model_preset)
+    policy = {"config": DTypePolicy.from_config(cfg), "stability": DTypePolicy.stability(),
+              "memory": DTypePolicy.memory()}[args.dtype_policy]
+    est = estimate_training_memory(cfg, policy, model_axis_size=args.model_axis_size,
+                                   optimizer_shards=args.optimizer_shards, tokens_per_device=args.tokens_per_device)
+    print(json.dumps(est.to_dict(), indent=2, sort_keys=True))
+    return est
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,389 @@
+"""``rwkv7m-train-binidx-dp``: multi-GPU trainer (one process per GPU, launch with torchrun).
+
+Run artefacts, flags and semantics follow src/rwkv7m/cli/train_binidx_distributed.py:41-761
+of the reference: ``run_config.json``, ``run_summary.json`` (status running /
+completed / failed), ``metrics.jsonl`` + ``metrics.csv``, ``best_eval.json``,
+``ckpt-%08d`` directories with rotation that never deletes the best-eval
+checkpoint, ``--resume`` (``--steps`` = additional updates), carry-state only
+with sequential sampling, lane-wrap resets, optional Python GC disabling.
+Throughput is device time per step (CUDA events), not host wall clock.
+``--mesh-axis-names data`` selects data parallelism (``--dp-mode fused`` runs the
+reduce-scatter + AdamW + all-gather inside the optimizer kernels over NVLink).
+"""
+
+from __future__ import annotations
+
+import argparse
+import gc
+import json
+import math
+import time
+from datetime import datetime, timezone
+from pathlib import Path
+
+import torch
+
+from ..api import create_train_runtime, train_batch
+from ..config import model_config_to_dict
+from ..parallel.checkpoint import (
+    checkpoint_path,
+    load_distributed_checkpoint_metadata,
+    restore_distributed_runtime_state,
+    restore_distributed_train_state,
+    rotate_checkpoints,
+    save_data_parallel_checkpoint,
+)
+from ..parallel.dp import DataParallelTrainer
+from ..parallel.environment import environment_manifest
+from ..parallel.input_pipeline import create_host_binidx_dataset, iter_prefetched_global_batches
+from ..parallel.mesh import initialize_distributed, make_mesh
+from ..parallel.metrics import mean_metric_dict, metrics_to_host_dict, write_metric_record
+from ..state import init_rwkv_state, init_screen_state
+from ..train.train_step import model_loss
+from .common import (
+    add_architecture_args,
+    add_execution_args,
+    add_model_source_args,
+    build_config,
+    parse_args_with_config,
+    pick_device,
+)
+
+
+def parse_args(argv=None):
+    p = argparse.ArgumentParser(description="Distributed rwkv7m trainer on .bin/.idx data.")
+    p.add_argument("--data-file", required=True)
+    add_model_source_args(p)
+    p.add_argument("--ctx-len", type=int, required=True)
+    p.add_argument("--global-batch-size", type=int, default=1)
+    p.add_argument("--steps", type=int, default=100)
+    p.add_argument("--magic-prime", type=int, default=None)
+    p.add_argument("--sampling-mode", choices=["magic", "sequential"], default="magic")
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--phase", choices=["read_screening_only", "read_write"], default="read_screening_only")
+    add_architecture_args(p)
+    add_execution_args(p)
+    p.add_argument("--gradient-accumulation-steps", type=int, default=1)
+    p.add_argument("--print-every", type=int, default=10)
+    p.add_argument("--output-dir", default=None)
+    p.add_argument("--save-every", type=int, default=0)
+    p.add_argument("--keep-last-checkpoints", type=int, default=0)
+    p.add_argument("--checkpoint-backend", choices=["flax", "orbax", "single", "sharded"], default="flax")
+    p.add_argument("--resume", default=None)
+    p.add_argument("--prefetch-size", type=int, default=2)
+    p.add_argument("--carry-state", action="store_true")
+    p.add_argument("--eval-every", type=int, default=0)
+    p.add_argument("--eval-steps", type=int, default=1)
+    p.add_argument("--eval-data-file", default=None)
+    p.add_argument("--log-jsonl", default=None)
+    p.add_argument("--log-csv", default=None)
+    p.add_argument("--summary-json", default=None)
+    p.add_argument("--summary-every", type=int, default=10)
+    p.add_argument("--disable-python-gc", action="store_true",
+                   help="turn the cyclic garbage collector off during the step loop (it is restored afterwards)")
+    p.add_argument("--save-best-checkpoint", action="store_true")
+    p.add_argument("--best-metric", default="loss")
+    p.add_argument("--best-mode", choices=["min", "max"], default="min")
+    p.add_argument("--mesh-axis-names", nargs="+", default=["data"])
+    p.add_argument("--mesh-axis-sizes", type=int, nargs="+", default=None)
+    p.add_argument("--param-axis-name", default=None)
+    p.add_argument("--dp-mode", choices=["fused", "allreduce"], default="allreduce")
+    p.add_argument("--device", default="auto")
+    return parse_args_with_config(p, argv)
+
+
+def _now():
+    return datetime.now(timezone.utc).isoformat()
+
+
+def _jsonable(v):
+    if isinstance(v, Path):
+        return str(v)
+    if isinstance(v, dict):
+        return {str(k): _jsonable(x) for k, x in v.items()}
+    if isinstance(v, (list, tuple)):
+        return [_jsonable(x) for x in v]
+    return v
+
+
+def _log_paths(args):
+    if args.output_dir is None:
+        return args.log_jsonl, args.log_csv
+    out = Path(args.output_dir)
+    return (args.log_jsonl or out / "metrics.jsonl"), (args.log_csv or out / "metrics.csv")
+
+
+def _summary_path(args):
+    if args.summary_json is not None:
+        return Path(args.summary_json)
+    return None if args.output_dir is None else Path(args.output_dir) / "run_summary.json"
+
+
+def _write_json(path, payload):
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump(_jsonable(payload), f, indent=2, sort_keys=True)
+        f.write("\n")
+
+
+def _write_summary(args, info, summary):
+    path = _summary_path(args)
+    if path is None or info["process_index"] != 0:
+        return
+    summary["updated_at"] = _now()
+    _write_json(path, summary)
+
+
+def metric_record(args, split, step, metrics, *, elapsed=None) -> dict:
+    tokens = args.global_batch_size * args.ctx_len
+    rec = {"split": split, "step": int(step), "tokens": tokens, "tokens_per_sec": None}
+    for key in ("loss", "total_loss", "perplexity", "rel_read_mean", "active_slots_mean", "u_norm_mean",
+                "rel_write_mean", "rel_write_effective_mean"):
+        rec[key] = metrics.get(key)
+    if elapsed is not None and elapsed > 0:
+        rec["tokens_per_sec"] = tokens / elapsed
+    return rec
+
+
+def is_better_eval(value, best, mode) -> bool:
+    if value is None or not math.isfinite(float(value)):
+        return False
+    if best is None:
+        return True
+    return float(value) > float(best["value"]) if mode == "max" else float(value) < float(best["value"])
+
+
+def validate_args(args, world):
+    if args.carry_state and args.sampling_mode != "sequential":
+        raise ValueError("--carry-state requires --sampling-mode sequential")
+    if args.gradient_accumulation_steps <= 0:
+        raise ValueError("gradient_accumulation_steps must be positive")
+    if args.global_batch_size % world != 0:
+        raise ValueError("global_batch_size must be divisible by the number of processes")
+    if (args.global_batch_size // world) % args.gradient_accumulation_steps != 0:
+        raise ValueError("per-process batch must be divisible by gradient_accumulation_steps")
+
+
+@torch.no_grad()
+def run_validation(args, model, cfg, device, info, eval_state):
+    """Mean CE over ``--eval-steps`` batches; with carry-state the evaluation keeps its own carried state."""
+    data_file = args.eval_data_file or args.data_file
+    ds = create_host_binidx_dataset(
+        data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size, magic_prime=None,
+        epoch_steps=max(args.eval_steps, 1), process_index=info["process_index"],
+        process_count=info["process_count"], sampling_mode=args.sampling_mode,
+    )
+    B = ds.layout.process_batch_size
+    was_training = model.training
+    model.eval()
+    records = []
+    try:
+        for step in range(args.eval_steps):
+            batch = {k: v.to(device) for k, v in ds.get_batch(step).items()}
+            if args.carry_state and eval_state.get("rwkv") is not None and not ds.should_reset_state_before_step(step):
+                rs, ss = eval_state["rwkv"], eval_state["screen"]
+            else:
+                rs = init_rwkv_state(B, cfg, device=device)
+                ss = init_screen_state(B, cfg.screening if cfg.screening_active else _empty(cfg), device=device)
+            _, (metrics, nr, ns) = model_loss(model, batch, rs, ss, phase=args.phase, include_l2wrap=False)
+            if args.carry_state:
+                eval_state["rwkv"], eval_state["screen"] = tuple(s.detach() for s in nr), ns.detach()
+            records.append(metrics_to_host_dict(metrics))
+    finally:
+        ds.close()
+        model.train(was_training)
+    mean = mean_metric_dict(records)
+    if info["process_count"] > 1:
+        t = torch.tensor([mean.get("loss", 0.0)], device=device)
+        torch.distributed.all_reduce(t)
+        mean["loss"] = float(t) / info["process_count"]
+    mean["perplexity"] = math.exp(min(mean.get("loss", 0.0), 20.0))
+    return mean
+
+
+def _empty(cfg):
+    import copy
+
+    scr = copy.copy(cfg.screening)
+    scr.screened_layers = ()
+    return scr
+
+
+def run_distributed_training(args):
+    info = initialize_distributed()
+    rank, world = info["process_index"], info["process_count"]
+    mesh = make_mesh(tuple(args.mesh_axis_names), args.mesh_axis_sizes, world_size=world)
+    if mesh.model_size != 1:
+        raise ValueError("this trainer drives data parallelism; tensor-parallel runs use rwkv7m_b200.parallel.tp")
+    validate_args(args, world)
+    if torch.cuda.is_available() and args.device in ("auto", None):
+        device = torch.device("cuda", info["local_rank"])
+        torch.cuda.set_device(device)
+    else:
+        device = pick_device(args.device)
+    if args.resume:
+        meta = load_distributed_checkpoint_metadata(args.resume)
+        cfg, start_step = meta.config, meta.start_step
+        if args.model_config is not None or args.model_preset is not None:
+            if model_config_to_dict(build_config(args)) != model_config_to_dict(cfg):
+                raise ValueError("--model-config does not match the model config stored in --resume")
+    else:
+        cfg, start_step = build_config(args), 0
+    if args.ctx_len > cfg.max_seq_len:
+        raise ValueError(f"ctx_len={args.ctx_len} exceeds model max_seq_len={cfg.max_seq_len}")
+    if cfg.vocab_parallel:
+        raise ValueError("vocab_parallel requires a model-parallel mesh axis")
+
+    dataset = create_host_binidx_dataset(
+        args.data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size,
+        magic_prime=args.magic_prime, epoch_steps=max(args.steps, 1), process_index=rank, process_count=world,
+        sampling_mode=args.sampling_mode,
+    )
+    B = dataset.layout.process_batch_size
+    alloc = None
+    mode = "single" if world == 1 else args.dp_mode
+    if mode == "fused":
+        from ..parallel.fused_dp import SymmetricFlatBuffers
+
+        alloc = SymmetricFlatBuffers()
+    runtime, train_state = create_train_runtime(
+        args.seed, cfg, batch_size=B, total_steps=max(start_step + args.steps, 1), device=device,
+        shard_multiple=max(world, 1) * 8, buffer_allocator=alloc,
+    )
+    trainer = DataParallelTrainer(train_state, mode=mode)
+    if trainer.fused is not None:
+        train_state.extras["fused_optimizer"] = trainer.fused
+    if args.resume:
+        train_state, _ = restore_distributed_train_state(args.resume, train_state, info)
+        if args.carry_state:
+            st = restore_distributed_runtime_state(
+                args.resume, {"rwkv_state": runtime.rwkv_state, "screen_state": runtime.screen_state}, info)
+            if st is not None:
+                runtime.rwkv_state, runtime.screen_state = st["rwkv_state"], st["screen_state"]
+            elif rank == 0:
+                print("runtime state not found; carry-state resume starts from zero runtime state")
+
+    def say(msg):
+        if rank == 0:
+            print(msg, flush=True)
+
+    jsonl_path, csv_path = _log_paths(args)
+    summary = {
+        "status": "running", "started_at": _now(), "updated_at": _now(), "ended_at": None,
+        "start_step": int(start_step), "current_step": int(start_step), "completed_steps": 0,
+        "requested_steps": int(args.steps), "tokens_per_step": args.global_batch_size * args.ctx_len,
+        "tokens_seen": 0, "checkpoint_backend": args.checkpoint_backend, "sampling_mode": args.sampling_mode,
+        "carry_state": args.carry_state, "latest_checkpoint": None, "best_eval": None, "last_train": None,
+        "last_eval": None, "process_info": dict(info), "dp_mode": mode,
+    }
+    if args.output_dir is not None and rank == 0:
+        _write_json(Path(args.output_dir) / "run_config.json", {
+            "args": vars(args), "model_config": model_config_to_dict(cfg), "process_info": dict(info),
+            "environment": environment_manifest(), "mesh": {"data": mesh.data_size, "model": mesh.model_size},
+        })
+    _write_summary(args, info, summary)
+
+    def save(step, extra=None):
+        if args.output_dir is None:
+            return None
+        path = checkpoint_path(args.output_dir, step)
+        metadata = {
+            "data_file": args.data_file, "ctx_len": args.ctx_len, "global_batch_size": args.global_batch_size,
+            "phase": args.phase, "carry_state": args.carry_state, "sampling_mode": args.sampling_mode,
+            "total_requested_steps": args.steps, "world_size": world, **(extra or {}),
+        }
+        save_data_parallel_checkpoint(
+            path, train_state, cfg, info, backend=args.checkpoint_backend, rng_key=[0, args.seed],
+            dataset_position={"step": int(step)}, metadata=metadata,
+            runtime_state=({"rwkv_state": runtime.rwkv_state, "screen_state": runtime.screen_state}
+                           if args.carry_state else None),
+        )
+        summary["latest_checkpoint"] = str(path)
+        protected = [summary["best_eval"]["checkpoint"]] if summary.get("best_eval") and summary["best_eval"].get("checkpoint") else []
+        rotate_checkpoints(args.output_dir, args.keep_last_checkpoints, info, protected_paths=protected + [path])
+        say(f"saved checkpoint {path}")
+        return path
+
+    gc_was_enabled = gc.isenabled()
+    if args.disable_python_gc:
+        gc.disable()
+    eval_state = {}
+    use_cuda = device.type == "cuda"
+    try:
+        say(f"data_tokens={dataset.data_size} magic_prime={dataset.magic_prime} ctx_len={args.ctx_len} "
+            f"global_batch_size={args.global_batch_size} world={world} dp_mode={mode} start_step={start_step}")
+        last_ckpt = None
+        for step, batch in iter_prefetched_global_batches(dataset, device, start_step=start_step, steps=args.steps,
+                                                          prefetch_size=args.prefetch_size):
+            if args.carry_state and dataset.should_reset_state_before_step(step):
+                runtime.rwkv_state, runtime.screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
+            if use_cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            t0 = time.perf_counter()
+            train_state, metrics = train_batch(
+                train_state, batch, runtime, phase=args.phase, carry_state=args.carry_state,
+                gradient_accumulation_steps=args.gradient_accumulation_steps,
+            )
+            if use_cuda:
+                e1.record()
+                e1.synchronize()
+                elapsed = e0.elapsed_time(e1) / 1e3
+            else:
+                elapsed = time.perf_counter() - t0
+            done = int(train_state.step)
+            host = metrics_to_host_dict(metrics)
+            rec = metric_record(args, "train", done, host, elapsed=elapsed)
+            write_metric_record(jsonl_path, csv_path, rec, process_info=info)
+            summary.update(current_step=done, completed_steps=done - start_step,
+                           tokens_seen=(done - start_step) * summary["tokens_per_step"], last_train=rec)
+            local = done - start_step - 1
+            if args.print_every and (local % args.print_every == 0 or local == args.steps - 1):
+                say(f"step={done} loss={host.get('loss', float('nan')):.6f} tok/s={rec['tokens_per_sec']:.0f}")
+            if args.eval_every > 0 and done % args.eval_every == 0:
+                ev = run_validation(args, train_state.model, cfg, device, info, eval_state)
+                erec = metric_record(args, "eval", done, ev)
+                write_metric_record(jsonl_path, csv_path, erec, process_info=info)
+                summary["last_eval"] = erec
+                say(f"eval step={done} loss={ev['loss']:.6f} perplexity={ev['perplexity']:.6f}")
+                value = ev.get(args.best_metric)
+                if is_better_eval(value, summary["best_eval"], args.best_mode):
+                    best = {"metric": args.best_metric, "mode": args.best_mode, "value": float(value), "step": done,
+                            "checkpoint": None}
+                    if args.save_best_checkpoint and args.output_dir is not None:
+                        summary["best_eval"] = best
+                        last_ckpt = save(done, {"best_eval": True})
+                        best["checkpoint"] = str(last_ckpt)
+                    summary["best_eval"] = best
+                    if args.output_dir is not None and rank == 0:
+                        _write_json(Path(args.output_dir) / "best_eval.json", best)
+            if args.output_dir is not None and args.save_every > 0 and done % args.save_every == 0:
+                if last_ckpt is None or Path(last_ckpt).name != f"ckpt-{done:08d}":
+                    last_ckpt = save(done)
+            if args.summary_every > 0 and (done - start_step) % args.summary_every == 0:
+                _write_summary(args, info, summary)
+        final = int(train_state.step)
+        if args.output_dir is not None and (last_ckpt is None or Path(last_ckpt).name != f"ckpt-{final:08d}"):
+            last_ckpt = save(final)
+        if trainer.fused is not None and trainer.fused.error_code() != 0:
+            raise RuntimeError(f"a bounded wait on a peer GPU ran out (code {trainer.fused.error_code():#x})")
+        summary.update(status="completed", ended_at=_now())
+        _write_summary(args, info, summary)
+    except BaseException as exc:
+        summary.update(status="failed", ended_at=_now(), error_type=type(exc).__name__, error_message=str(exc))
+        _write_summary(args, info, summary)
+        raise
+    finally:
+        dataset.close()
+        if args.disable_python_gc and gc_was_enabled:
+            gc.enable()
+    return train_state, runtime, summary
+
+
+def main(argv=None):
+    return run_distributed_training(parse_args(argv))
+
+
+if __name__ == "__main__":
+    main()

@@ -15,7 +15,7 @@
 //                      the parameter all-gather is the epilogue of the optimizer kernel
 //   barrier            new parameters have landed everywhere
 //
-// No TMA and no cluster multicast is used here; peers are reached with ld/st/red and multimem.
+// Peers are reached with plain ld/st/red and multimem instructions only.
 // Every wait is bounded (about two seconds) and reports through an error word instead of hanging.
 // The reference has no counterpart: its data parallelism is an XLA-inserted all-reduce with
 // replicated optimizer state (src/rwkv7m/distributed/trainer.py:31-51).

@@ -1,0 +1,265 @@
+"""Checkpoints of distributed runs: ``ckpt-%08d`` directories, save / restore, rotation.
+
+Directory layout and ``checkpoint.json`` fields follow the reference
+(src/rwkv7m/distributed/checkpoint.py:34-126,208-302).  Its two backends map
+onto this framework as follows: ``single`` (alias ``flax``) lets rank 0 write
+the complete train state after gathering any sharded Adam moments; ``sharded``
+(alias ``orbax``) lets every rank write its own optimizer shard and runtime
+state next to rank 0's model files, and needs the same world size to restore.
+"""
+
+from __future__ import annotations
+
+import json
+import shutil
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+from safetensors.torch import load_file, save_file
+
+from ..config import model_config_from_dict, model_config_to_dict
+from ..io.checkpoint import (
+    CHECKPOINT_JSON,
+    MODEL_SAFETENSORS,
+    RUNTIME_STATE_FILE,
+    TRAIN_STATE_FILE,
+    load_train_checkpoint,
+    load_train_runtime_state,
+    save_runtime_state,
+    save_train_checkpoint,
+)
+from ..io.names import from_portable, to_portable
+from ..io.safetensors_io import save_model_safetensors
+
+BACKEND_ALIASES = {"flax": "single", "single": "single", "orbax": "sharded", "sharded": "sharded"}
+
+
+@dataclass(frozen=True)
+class DistributedCheckpointPayload:
+    config: object
+    metadata: dict
+    start_step: int
+    dataset_position: dict | None
+
+
+def normalize_backend(name: str) -> str:
+    if name not in BACKEND_ALIASES:
+        raise ValueError(f"checkpoint backend must be one of {sorted(BACKEND_ALIASES)}")
+    return BACKEND_ALIASES[name]
+
+
+def checkpoint_path(output_dir, step) -> Path:
+    return Path(output_dir) / f"ckpt-{int(step):08d}"
+
+
+def list_checkpoint_dirs(output_dir) -> list:
+    output_dir = Path(output_dir)
+    if not output_dir.exists():
+        return []
+    found = []
+    for path in output_dir.iterdir():
+        if path.is_dir() and path.name.startswith("ckpt-"):
+            tail = path.name[len("ckpt-"):]
+            if tail.isdigit():
+                found.append((int(tail), path))
+    return [p for _, p in sorted(found)]
+
+
+def load_distributed_checkpoint_raw_metadata(checkpoint_dir):
+    with open(Path(checkpoint_dir) / CHECKPOINT_JSON, "r", encoding="utf-8") as f:
+        payload = json.load(f)
+    return model_config_from_dict(payload["config"]), payload
+
+
+def load_distributed_checkpoint_metadata(checkpoint_dir) -> DistributedCheckpointPayload:
+    config, payload = load_distributed_checkpoint_raw_metadata(checkpoint_dir)
+    return DistributedCheckpointPayload(config, payload, int(payload.get("step", 0)), payload.get("dataset_position"))
+
+
+def _world(process_info):
+    return int(process_info["process_index"]), int(process_info["process_count"])
+
+
+def _barrier(process_info):
+    if process_info["process_count"] > 1 and dist.is_initialized():
+        dist.barrier()
+
+
+def _moment_shard(train_state):
+    """(exp_avg, exp_avg_sq, begin, end) of this rank, or None when moments are replicated."""
+    fused = train_state.extras.get("fused_optimizer")
+    if fused is None:
+        return None
+    return fused.exp_avg, fused.exp_avg_sq, fused.begin, fused.end
+
+
+def _gather_moments_into_optimizer(train_state, process_info):
+    """Materialise full Adam moments on the optimizer object (every rank) from the per-rank shards."""
+    shard = _moment_shard(train_state)
+    if shard is None:
+        return False
+    m, v, begin, end = shard
+    opt = train_state.optimizer
+    total = opt.flat.master.numel()
+    full_m = torch.empty(total, dtype=m.dtype, device=m.device)
+    full_v = torch.empty_like(full_m)
+    dist.all_gather_into_tensor(full_m, m)
+    dist.all_gather_into_tensor(full_v, v)
+    opt.exp_avg, opt.exp_avg_sq = full_m, full_v
+    return True
+
+
+def save_data_parallel_checkpoint(checkpoint_dir, train_state, config, process_info, *, backend="single",
+                                  rng_key=None, dataset_position=None, metadata=None, runtime_state=None):
+    backend = normalize_backend(backend)
+    rank, world = _world(process_info)
+    checkpoint_dir = Path(checkpoint_dir)
+    if backend == "single":
+        gathered = _gather_moments_into_optimizer(train_state, process_info) if world > 1 else False
+        if rank == 0:
+            save_train_checkpoint(checkpoint_dir, train_state, config, rng_key=rng_key,
+                                  dataset_position=dataset_position, metadata=metadata, runtime_state=runtime_state)
+            _patch_json(checkpoint_dir, {"backend": "single", "world_size": world})
+        if gathered:
+            train_state.optimizer.exp_avg = train_state.optimizer.exp_avg_sq = None
+        _barrier(process_info)
+        return checkpoint_dir
+    # sharded: every rank writes its part
+    if rank == 0:
+        checkpoint_dir.mkdir(parents=True, exist_ok=True)
+    _barrier(process_info)
+    shard = _moment_shard(train_state)
+    opt = train_state.optimizer
+    if shard is None:
+        total = opt.flat.master.numel()
+        per = total // world if total % world == 0 else total
+        begin, end = (rank * per, (rank + 1) * per) if per != total else (0, total if rank == 0 else 0)
+        m, v = opt.exp_avg[begin:end], opt.exp_avg_sq[begin:end]
+    else:
+        m, v, begin, end = shard
+    save_file(
+        {"exp_avg": m.detach().contiguous().cpu(), "exp_avg_sq": v.detach().contiguous().cpu(),
+         "range": torch.tensor([begin, end], dtype=torch.int64)},
+        str(checkpoint_dir / f"optimizer_shard.rank{rank:05d}.safetensors"),
+    )
+    if runtime_state is not None:
+        save_runtime_state(checkpoint_dir / f"runtime_state.rank{rank:05d}.safetensors", runtime_state)
+    if rank == 0:
+        tensors = {f"model/{k}": v for k, v in to_portable(train_state.model).items()}
+        tensors["optimizer/count"] = torch.tensor([opt.count], dtype=torch.int64)
+        save_file(tensors, str(checkpoint_dir / TRAIN_STATE_FILE))
+        save_model_safetensors(checkpoint_dir / MODEL_SAFETENSORS, train_state.model, config,
+                               metadata={"checkpoint_step": int(train_state.step), **(metadata or {})})
+        payload = {
+            "format": "rwkv7m_train_checkpoint", "format_version": 1, "backend": "sharded", "world_size": world,
+            "step": int(train_state.step), "config": model_config_to_dict(config),
+            "rng_key": None if rng_key is None else [int(x) for x in torch.as_tensor(rng_key).reshape(-1).tolist()],
+            "dataset_position": dataset_position, "metadata": metadata or {},
+        }
+        with open(checkpoint_dir / CHECKPOINT_JSON, "w", encoding="utf-8") as f:
+            json.dump(payload, f, indent=2, sort_keys=True)
+            f.write("\n")
+    _barrier(process_info)
+    return checkpoint_dir
+
+
+def _patch_json(checkpoint_dir, extra: dict):
+    path = Path(checkpoint_dir) / CHECKPOINT_JSON
+    with open(path, "r", encoding="utf-8") as f:
+        payload = json.load(f)
+    payload.update(extra)
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump(payload, f, indent=2, sort_keys=True)
+        f.write("\n")
+
+
+def restore_distributed_train_state(checkpoint_dir, train_state_template, process_info=None):
+    """Restore parameters on every rank and Adam moments into whichever layout the template uses."""
+    checkpoint_dir = Path(checkpoint_dir)
+    process_info = process_info or {"process_index": 0, "process_count": 1}
+    rank, world = _world(process_info)
+    config, payload = load_distributed_checkpoint_raw_metadata(checkpoint_dir)
+    opt = train_state_template.optimizer
+    shard = _moment_shard(train_state_template)
+    if payload.get("backend", "single") == "sharded":
+        if int(payload.get("world_size", 1)) != world:
+            raise ValueError(
+                f"sharded checkpoint was written by {payload.get('world_size')} ranks; restore with the same count "
+                "or convert it by saving with the 'single' backend"
+            )
+        tensors = load_file(str(checkpoint_dir / TRAIN_STATE_FILE))
+        from_portable(train_state_template.model,
+                      {k[len("model/"):]: v for k, v in tensors.items() if k.startswith("model/")}, strict=True)
+        opt.count = int(tensors["optimizer/count"].reshape(-1)[0])
+        part = load_file(str(checkpoint_dir / f"optimizer_shard.rank{rank:05d}.safetensors"))
+        begin, end = (int(x) for x in part["range"].tolist())
+        if shard is not None:
+            m, v, b2, e2 = shard
+            if (b2, e2) != (begin, end):
+                raise ValueError("optimizer shard bounds differ from the checkpoint")
+            m.copy_(part["exp_avg"])
+            v.copy_(part["exp_avg_sq"])
+        else:
+            pieces_m = torch.zeros_like(opt.exp_avg)
+            pieces_v = torch.zeros_like(opt.exp_avg_sq)
+            for r in range(world):
+                p = load_file(str(checkpoint_dir / f"optimizer_shard.rank{r:05d}.safetensors"))
+                b, e = (int(x) for x in p["range"].tolist())
+                pieces_m[b:e].copy_(p["exp_avg"])
+                pieces_v[b:e].copy_(p["exp_avg_sq"])
+            opt.exp_avg.copy_(pieces_m)
+            opt.exp_avg_sq.copy_(pieces_v)
+        opt.flat.sync_compute()
+    else:
+        if shard is not None:
+            # load the replicated moments into temporary full buffers, then keep only the owned slice
+            total = opt.flat.master.numel()
+            opt.exp_avg = torch.zeros(total, dtype=torch.float32, device=opt.flat.master.device)
+            opt.exp_avg_sq = torch.zeros_like(opt.exp_avg)
+        load_train_checkpoint(checkpoint_dir, train_state_template)
+        if shard is not None:
+            m, v, begin, end = shard
+            m.copy_(opt.exp_avg[begin:end])
+            v.copy_(opt.exp_avg_sq[begin:end])
+            opt.exp_avg = opt.exp_avg_sq = None
+    return train_state_template, DistributedCheckpointPayload(
+        config, payload, int(payload.get("step", 0)), payload.get("dataset_position")
+    )
+
+
+def restore_distributed_runtime_state(checkpoint_dir, runtime_state_template, process_info=None):
+    checkpoint_dir = Path(checkpoint_dir)
+    rank = int((process_info or {"process_index": 0})["process_index"])
+    per_rank = checkpoint_dir / f"runtime_state.rank{rank:05d}.safetensors"
+    if per_rank.exists():
+        tmp = checkpoint_dir / RUNTIME_STATE_FILE
+        tensors = load_file(str(per_rank))
+        from ..state import rwkv_state_from_dict, screen_state_from_dict
+
+        n_layers = len({k.split("/")[0] for k in tensors if k.startswith("layer_")})
+        n_scr = len({k.split("/")[0] for k in tensors if k.startswith("screen_")})
+        ref = runtime_state_template["rwkv_state"][0].wkv
+        return {
+            "rwkv_state": tuple(l.to(ref.device) for l in rwkv_state_from_dict(tensors, n_layers)),
+            "screen_state": screen_state_from_dict(tensors, n_scr).to(ref.device),
+        }
+    if (checkpoint_dir / RUNTIME_STATE_FILE).exists():
+        return load_train_runtime_state(checkpoint_dir, runtime_state_template)
+    return None
+
+
+def rotate_checkpoints(output_dir, keep_last, process_info, *, protected_paths=None) -> list:
+    """Delete all but the newest ``keep_last`` checkpoints (rank 0), never a protected one
+    (e.g. the best-eval checkpoint)."""
+    if output_dir is None or keep_last is None or keep_last <= 0:
+        return []
+    if process_info["process_index"] != 0:
+        return []
+    protected = {Path(p).resolve() for p in (protected_paths or []) if p is not None}
+    ckpts = list_checkpoint_dirs(output_dir)
+    doomed = [p for p in ckpts[: max(0, len(ckpts) - int(keep_last))] if p.resolve() not in protected]
+    for p in doomed:
+        shutil.rmtree(p)
+    return doomed

@@ -1,0 +1,107 @@
+"""Process-group bootstrap and the (data, model) rank grid.
+
+The reference initialises ``jax.distributed`` from environment variables and
+builds a named device mesh (src/rwkv7m/distributed/mesh.py:17-84).  Here one
+process drives one GPU; ``torchrun``'s ``RANK / LOCAL_RANK / WORLD_SIZE /
+MASTER_ADDR / MASTER_PORT`` replace the JAX coordinator variables, NCCL is the
+backend on GPUs and gloo on CPU, and a ``Mesh`` is a pure description of which
+ranks form each data-parallel and model-parallel group.
+"""
+
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def process_info() -> dict:
+    if dist.is_available() and dist.is_initialized():
+        return {"process_index": dist.get_rank(), "process_count": dist.get_world_size(),
+                "local_rank": int(os.environ.get("LOCAL_RANK", "0"))}
+    return {"process_index": int(os.environ.get("RANK", "0")), "process_count": int(os.environ.get("WORLD_SIZE", "1")),
+            "local_rank": int(os.environ.get("LOCAL_RANK", "0"))}
+
+
+def initialize_distributed(backend: str | None = None, timeout_s: float = 600.0) -> dict:
+    """Join the process group described by the torchrun environment (no-op for a single process)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1 or (dist.is_available() and dist.is_initialized()):
+        return process_info()
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    kwargs = {"timeout": datetime.timedelta(seconds=timeout_s)}
+    if backend == "nccl":
+        torch.cuda.set_device(local)
+        kwargs["device_id"] = torch.device("cuda", local)
+    dist.init_process_group(backend, **kwargs)
+    return process_info()
+
+
+@dataclass(frozen=True)
+class Mesh:
+    """``data x model`` grid; rank = data_index * model_size + model_index (model axis fastest,
+    so a model-parallel group sits on adjacent GPUs)."""
+
+    data_size: int
+    model_size: int
+    axis_names: tuple = ("data", "model")
+
+    @property
+    def size(self) -> int:
+        return self.data_size * self.model_size
+
+    def coords(self, rank: int) -> tuple:
+        if not 0 <= rank < self.size:
+            raise ValueError(f"rank {rank} outside mesh of {self.size}")
+        return rank // self.model_size, rank % self.model_size
+
+    def model_group_ranks(self, rank: int) -> list:
+        d, _ = self.coords(rank)
+        return [d * self.model_size + m for m in range(self.model_size)]
+
+    def data_group_ranks(self, rank: int) -> list:
+        _, m = self.coords(rank)
+        return [d * self.model_size + m for d in range(self.data_size)]
+
+
+def make_mesh(axis_names=("data", "model"), axis_sizes=None, world_size: int | None = None) -> Mesh:
+    """``axis_sizes`` may leave one axis as -1 to absorb the remaining ranks."""
+    world = world_size if world_size is not None else process_info()["process_count"]
+    names = tuple(axis_names)
+    if set(names) - {"data", "model"}:
+        raise ValueError("mesh axes must be named 'data' and/or 'model'")
+    sizes = dict(zip(names, axis_sizes if axis_sizes is not None else [world] + [1] * (len(names) - 1)))
+    data, model = sizes.get("data", 1), sizes.get("model", 1)
+    if data == -1 and model == -1:
+        raise ValueError("only one mesh axis may be -1")
+    if data == -1:
+        data = world // model
+    if model == -1:
+        model = world // data
+    if data <= 0 or model <= 0 or data * model != world:
+        raise ValueError(f"mesh {data}x{model} does not match world size {world}")
+    return Mesh(data_size=data, model_size=model)
+
+
+def new_subgroups(mesh: Mesh):
+    """Create the NCCL/gloo groups of this rank: (data_group, model_group).  Collective on all ranks."""
+    rank = dist.get_rank()
+    data_group = model_group = None
+    for m in range(mesh.model_size):
+        ranks = [d * mesh.model_size + m for d in range(mesh.data_size)]
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            data_group = g
+    for d in range(mesh.data_size):
+        ranks = [d * mesh.model_size + m for m in range(mesh.model_size)]
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            model_group = g
+    return data_group, model_group

@@ -1,0 +1,109 @@
+"""Command-line tools run in-process on tiny models (CPU)."""
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from rwkv7m_b200.cli import eval_binidx, generate, make_binidx, plan_scale, train_binidx, train_binidx_distributed
+from rwkv7m_b200.cli.common import default_bank_ids, parse_args_with_config
+
+TINY = ["--vocab-size", "300", "--d-model", "32", "--d-ffn", "64", "--n-layers", "2", "--n-heads", "2",
+        "--head-size", "16", "--d-slot", "16", "--d-k", "8", "--d-v", "8", "--device", "cpu"]
+
+
+def test_config_file_supplies_defaults_and_rejects_unknown_keys(tmp_path):
+    import argparse
+
+    p = argparse.ArgumentParser()
+    p.add_argument("--alpha", type=int, required=True)
+    p.add_argument("--beta", type=int, default=1)
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps({"alpha": 5}))
+    args = parse_args_with_config(p, ["--config", str(cfg), "--beta", "3"])
+    assert (args.alpha, args.beta) == (5, 3)
+    cfg.write_text(json.dumps({"gamma": 1}))
+    p2 = argparse.ArgumentParser()
+    p2.add_argument("--alpha", type=int, default=0)
+    with pytest.raises(ValueError):
+        parse_args_with_config(p2, ["--config", str(cfg)])
+
+
+def test_default_bank_ids():
+    assert default_bank_ids(1) == (0,)
+    assert default_bank_ids(2) == (0, 2)
+    assert default_bank_ids(4) == (0, 0, 1, 2)
+    assert default_bank_ids(16) == (0,) * 8 + (1,) * 4 + (2,) * 4
+
+
+def test_train_save_resume_and_eval(tiny_binidx, tmp_path):
+    out = tmp_path / "run"
+    base = ["--data-file", tiny_binidx, "--ctx-len", "4", "--batch-size", "2", "--print-every", "0",
+            "--output-dir", str(out)] + TINY
+    args = train_binidx.parse_args(base + ["--steps", "1"])
+    ts, rt, ckpt = train_binidx.run_training(args)
+    assert ckpt.name == "ckpt-00000001" and (ckpt / "model.safetensors").exists()
+    assert json.loads((ckpt / "checkpoint.json").read_text())["step"] == 1
+    args = train_binidx.parse_args(base + ["--steps", "1", "--resume", str(ckpt)])
+    ts2, _, ckpt2 = train_binidx.run_training(args)
+    assert int(ts2.step) == 2 and ckpt2.name == "ckpt-00000002"
+    m = eval_binidx.evaluate_binidx(eval_binidx.parse_args(
+        ["--data-file", tiny_binidx, "--checkpoint", str(ckpt2), "--ctx-len", "4", "--steps", "2",
+         "--print-every", "0", "--device", "cpu"]))
+    assert m["loss"] > 0 and m["perplexity"] == pytest.approx(np.exp(min(m["loss"], 20.0)))
+
+
+def test_carry_state_requires_sequential_and_writes_runtime_state(tiny_binidx, tmp_path):
+    base = ["--data-file", tiny_binidx, "--ctx-len", "4", "--batch-size", "2", "--steps", "2", "--print-every", "0",
+            "--output-dir", str(tmp_path / "r")] + TINY
+    with pytest.raises(ValueError):
+        train_binidx.run_training(train_binidx.parse_args(base + ["--carry-state"]))
+    _, rt, ckpt = train_binidx.run_training(
+        train_binidx.parse_args(base + ["--carry-state", "--sampling-mode", "sequential"]))
+    assert (ckpt / "runtime_state.safetensors").exists()
+    assert float(rt.rwkv_state[0].wkv.abs().sum()) > 0
+
+
+def test_make_binidx_and_generate(tmp_path, tiny_binidx):
+    src = tmp_path / "toy.jsonl"
+    src.write_text("\n".join(json.dumps({"text": t}) for t in ["hello world", "RWKV は速い", "abc"]) + "\n")
+    stats = make_binidx.build_binidx(str(src), str(tmp_path / "toy"), epochs=2, seed=1)
+    assert stats["items"] == 6 and stats["tokens"] > 6
+    out = tmp_path / "g"
+    args = train_binidx.parse_args(["--data-file", tiny_binidx, "--ctx-len", "4", "--steps", "1", "--print-every", "0",
+                                    "--output-dir", str(out), "--vocab-size", "65536", "--d-model", "32", "--d-ffn",
+                                    "64", "--n-layers", "1", "--n-heads", "2", "--head-size", "16", "--no-screening",
+                                    "--device", "cpu"])
+    _, _, ckpt = train_binidx.run_training(args)
+    text = generate.main(["--checkpoint", str(ckpt), "--prompt", "hi", "--max-new-tokens", "3", "--temperature", "0",
+                          "--device", "cpu"])
+    assert text.startswith("hi")
+
+
+def test_plan_scale_outputs_exact_counts(capsys):
+    est = plan_scale.main(["--model-preset", "0.185b", "--model-axis-size", "1", "--optimizer-shards", "8"])
+    assert est.parameter_summary.total == 184_985_222
+    assert est.optimizer_state_bytes == -(-184_985_222 * 2 * 4 // 8)
+    assert "limitations" in json.loads(capsys.readouterr().out)
+
+
+def test_distributed_trainer_single_process_artifacts(tiny_binidx, tmp_path):
+    out = tmp_path / "dp"
+    argv = ["--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2", "--steps", "4",
+            "--print-every", "0", "--output-dir", str(out), "--save-every", "1", "--keep-last-checkpoints", "2",
+            "--eval-every", "2", "--save-best-checkpoint", "--summary-every", "1", "--disable-python-gc"] + TINY
+    ts, rt, summary = train_binidx_distributed.run_distributed_training(train_binidx_distributed.parse_args(argv))
+    assert summary["status"] == "completed" and summary["completed_steps"] == 4
+    assert json.loads((out / "run_summary.json").read_text())["status"] == "completed"
+    assert (out / "run_config.json").exists() and (out / "best_eval.json").exists()
+    lines = [json.loads(l) for l in (out / "metrics.jsonl").read_text().splitlines()]
+    assert sum(l["split"] == "train" for l in lines) == 4 and sum(l["split"] == "eval" for l in lines) == 2
+    kept = sorted(p.name for p in out.iterdir() if p.name.startswith("ckpt-"))
+    best = Path(json.loads((out / "best_eval.json").read_text())["checkpoint"]).name
+    assert "ckpt-00000004" in kept and best in kept and len(kept) <= 3
+    # resume: two more updates
+    ts2, _, s2 = train_binidx_distributed.run_distributed_training(train_binidx_distributed.parse_args(
+        argv[:6] + ["--steps", "2"] + argv[8:] + ["--resume", str(out / "ckpt-00000004")]))
+    assert int(ts2.step) == 6 and s2["start_step"] == 4
