@@ -51,7 +51,8 @@ def reference_arm(args):
     ref = ROOT / "baseline" / "_ref"
     reason = None
     if not ref.exists():
-        reason = "baseline/_ref is absent: pip install of /root/reference failed offline (requires-python >=3.13, jax/flax/optax/orbax wheels not in the wheelhouse)"
+        reason = ("baseline/_ref is absent: the offline pip install of the reference fails (build backend hatchling is not "
+                  "in the wheelhouse; it also requires Python >= 3.13 and jax/flax/optax/orbax, none of which are installed)")
     else:
         sys.path.insert(0, str(ref))
         try:
