@@ -180,7 +180,13 @@ def main(argv=None):
             if world > 1 and args.dp == "fused":
                 from rwkv7m_b200.parallel.fused_dp import SymmetricFlatBuffers
 
-                alloc = SymmetricFlatBuffers()
+                try:
+                    alloc = SymmetricFlatBuffers()
+                except Exception as exc:  # symmetric memory unavailable on this box: library collectives instead
+                    if rank == 0:
+                        print(f"bench: symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL all-reduce",
+                              file=sys.stderr)
+                    args.dp = "nccl"
             runtime, train_state = R.create_train_runtime(
                 7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8,
                 buffer_allocator=alloc,

@@ -49,13 +49,14 @@ def main():
     m_ref, c_ref, l_ref, n_ref, _, _ = run("allreduce")
     m_fus, c_fus, l_fus, n_fus, err, mc = run("fused")
     diff = float((m_ref - m_fus).abs().max())
+    rel_l2 = float((m_ref - m_fus).norm() / m_ref.norm())
     cdiff = float((c_ref.float() - c_fus.float()).abs().max())
     # all ranks must hold identical parameters after the fused step
     gathered = [torch.zeros_like(m_fus) for _ in range(world)]
     dist.all_gather(gathered, m_fus)
     spread = max(float((g - m_fus).abs().max()) for g in gathered)
     if rank == 0:
-        print(json.dumps({"max_master_diff": diff, "max_compute_diff": cdiff, "rank_spread": spread,
+        print(json.dumps({"max_master_diff": diff, "rel_l2_diff": rel_l2, "max_compute_diff": cdiff, "rank_spread": spread,
                           "loss_ref": l_ref, "loss_fused": l_fus, "norm_ref": n_ref, "norm_fused": n_fus,
                           "error_code": err, "multicast": mc, "world": world}))
     dist.destroy_process_group()
