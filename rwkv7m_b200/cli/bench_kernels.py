@@ -92,9 +92,12 @@ def bench_gemm(shapes, iters=10):
         flops = 2.0 * M * N * Kd
         K.gemm_error_reset(a)
         for name, fn in (
-            ("tn", lambda: K.gemm(a, b, d, K.GEMM_TN, K.EPI_BF16)),
-            ("nn", lambda: K.gemm(a, bt, d, K.GEMM_NN, K.EPI_BF16)),
-            ("wgrad_f32acc", lambda: K.gemm(at, bt, d32, K.GEMM_WGRAD, K.EPI_ACC_F32)),
+            ("tn", lambda: K.gemm(a, b, d, K.GEMM_TN, K.EPI_BF16, 0)),
+            ("tn_pair", lambda: K.gemm(a, b, d, K.GEMM_TN, K.EPI_BF16, 1)),
+            ("nn", lambda: K.gemm(a, bt, d, K.GEMM_NN, K.EPI_BF16, 0)),
+            ("nn_pair", lambda: K.gemm(a, bt, d, K.GEMM_NN, K.EPI_BF16, 1)),
+            ("wgrad_f32acc", lambda: K.gemm(at, bt, d32, K.GEMM_WGRAD, K.EPI_ACC_F32, 0)),
+            ("wgrad_f32acc_pair", lambda: K.gemm(at, bt, d32, K.GEMM_WGRAD, K.EPI_ACC_F32, 1)),
             ("cublas_tn", lambda: torch.matmul(a, b.t(), out=d)),
         ):
             t = _time(fn, iters, flush=flush)

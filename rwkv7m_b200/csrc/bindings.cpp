@@ -135,7 +135,7 @@ Tensor& gemm_error_flag(const at::Device& dev) {
 }
 
 // D = op(A) op(B); see kernels.h for the three layouts.  D must be preallocated.
-void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue) {
+void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue, int64_t pair) {
   static const bool trace = [] { const char* e = getenv("RWKV7M_B200_TRACE"); return e != nullptr && e[0] == '1'; }();
   if (trace) { fprintf(stderr, "[gemm-bind] enter layout=%d epi=%d\n", (int)layout, (int)epilogue); fflush(stderr); }
   c10::cuda::CUDAGuard guard(A.device());
@@ -146,7 +146,7 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   rk::GemmArgs p{};
   p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = D.data_ptr();
   p.lda = (int)A.stride(0); p.ldb = (int)B.stride(0); p.ldd = (int)D.stride(0);
-  p.layout = (int)layout; p.epilogue = (int)epilogue;
+  p.layout = (int)layout; p.epilogue = (int)epilogue; p.pair = (int)pair;
   if (layout == rk::kGemmTN) {
     p.M = (int)A.size(0); p.K = (int)A.size(1); p.N = (int)B.size(0);
     TORCH_CHECK(B.size(1) == p.K, "gemm TN: K mismatch");

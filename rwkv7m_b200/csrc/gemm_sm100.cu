@@ -63,6 +63,67 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   return false;
 }
 
+// Write one 32-column chunk of an accumulator row (thread = row) with the selected epilogue.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __restrict__ Dptr, int row, int col0, int M,
+                                            int N, int ldd) {
+  if (row < M && col0 < N) {
+          if (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + (size_t)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1; }
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                pk[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float x0 = __uint_as_float(v[j]);
+                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; }
+                out[j] = f2bf(x0);
+              }
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(Dptr) + (size_t)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              float4* o4 = reinterpret_cast<float4*>(out);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 t = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                if (EPI == kEpiAccumF32) { float4 o = o4[j]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
+                o4[j] = t;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float t = __uint_as_float(v[j]);
+                if (EPI == kEpiAccumF32) t += out[j];
+                out[j] = t;
+              }
+            }
+          }
+        }
+}
+
+// Tile order: blocks of kRasterM consecutive m-tiles sweep all n-tiles before the next block starts, so the
+// CTAs that run at the same time share a few A row-panels and B column-panels and both stay in L2.
+constexpr int kRasterM = 16;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group_size = kRasterM * tiles_n;
+  const int group = tile / group_size;
+  const int first = group * kRasterM;
+  const int rows = min(kRasterM, tiles_m - first);
+  const int within = tile - group * group_size;
+  tm = first + within % rows;
+  tn = within / rows;
+}
+
 template <int BN>
 struct Tile {
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
@@ -116,8 +177,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM;
-        const int n0 = (tile / tiles_m) * BN;
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = tiles + stage * TL::kStageBytes;
@@ -180,8 +242,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -191,48 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, v);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
-          if (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + (size_t)row * ldd + col0;
-            if (col0 + 32 <= N) {
-              uint32_t pk[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1; }
-                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                pk[j] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              uint4* o4 = reinterpret_cast<uint4*>(out);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) o4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float x0 = __uint_as_float(v[j]);
-                if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; }
-                out[j] = f2bf(x0);
-              }
-            }
-          } else {
-            float* out = reinterpret_cast<float*>(Dptr) + (size_t)row * ldd + col0;
-            if (col0 + 32 <= N) {
-              float4* o4 = reinterpret_cast<float4*>(out);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 t = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                if (EPI == kEpiAccumF32) { float4 o = o4[j]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
-                o4[j] = t;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float t = __uint_as_float(v[j]);
-                if (EPI == kEpiAccumF32) t += out[j];
-                out[j] = t;
-              }
-            }
-          }
-        }
+        store_chunk<EPI>(v, Dptr, row, col0, M, N, ldd);
       }
       tc_fence_before();
       __syncwarp();
@@ -253,6 +275,177 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
   }
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TL::kTmemCols); }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2.
+// Each CTA loads only its own 128 rows of A and 128 columns of B per k-block (32 KB instead of the
+// 48 KB a lone 128 x 256 CTA needs for the same FLOPs) and keeps the 128 x 256 half of the accumulator
+// that belongs to its rows in its own tensor memory.  The even CTA of the pair ("leader") owns the
+// full-stage barriers and issues every MMA; completions are signalled to both CTAs.
+//   full[s]   leader only, count 1 (leader's expect_tx) + bytes of both CTAs' TMA loads
+//   empty[s]  one per CTA, count 1 (commit from the leader's MMA thread, delivered to both CTAs)
+//   tfull[a]  one per CTA, count 1 (same mechanism)
+//   tempty[a] leader only, count 8 (4 epilogue warps of each CTA; the peer's arrive remotely)
+// ---------------------------------------------------------------------------------------------
+struct PairTile {
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = BM * BK * 2;        // this CTA's 128 rows of A
+  static constexpr int kBBytes = 128 * BK * 2;       // this CTA's 128 columns of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 512;              // two 256-column accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int A_MN, int B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int* __restrict__ err) {
+  using TL = PairTile;
+  constexpr int kStages = TL::kStages;
+  constexpr int BN2 = 256;  // tile width of the pair
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * TL::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tfull_bar = bars + 2 * kStages;
+  uint64_t* tempty_bar = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const bool leader = cta == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (N + BN2 - 1) / BN2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull_bar[s], 1); mbar_init(&tempty_bar[s], 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, TL::kTmemCols); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 2 * BM + (int)cta * BM;   // this CTA's rows
+        const int n0 = tn * BN2 + (int)cta * 128;     // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * TL::kStageBytes;
+          uint8_t* sb = sa + TL::kABytes;
+          // completion of both CTAs' copies is counted on the leader's barrier
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * TL::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d_pair(sa, &tmA, bar, k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (BK * 128), &tmA, bar, m0 + 64 * c, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(sb, &tmB, bar, k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d_pair(sb + c * (BK * 128), &tmB, bar, n0 + 64 * c, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x30000 | 1); }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN2, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        if (!wait_bar(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * TL::kStageBytes);
+          const uint32_t sb = sa + TL::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN == 0 ? umma_smem_desc_sw128(sa + k * 32, 16, 1024)
+                                          : umma_smem_desc_sw128(sa + k * 2048, BK * 128, 1024);
+            const uint64_t db = B_MN == 0 ? umma_smem_desc_sw128(sb + k * 32, 16, 1024)
+                                          : umma_smem_desc_sw128(sb + k * 2048, BK * 128, 1024);
+            umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc], 3);
+        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x30000 | 2); }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows x 256 columns) ----------------
+    const int q = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN2;
+      if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN2 / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN2 + c * 32, v);
+        tmem_ld_wait();
+        store_chunk<EPI>(v, Dptr, row, n0 + c * 32, M, N, ldd);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x30000 | 3); }
+  }
+
+  // ---------------- teardown ----------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) { }
+    __syncthreads();
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still signal into its shared memory
+  if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, TL::kTmemCols); }
 }
 
 // ---- host side ------------------------------------------------------------------
@@ -394,6 +587,49 @@ int launch_layout(const GemmArgs& p, cudaStream_t st) {
   return 5;
 }
 
+template <int A_MN, int B_MN, int EPI>
+int launch_pair(const GemmArgs& p, cudaStream_t st) {
+  using TL = PairTile;
+  alignas(64) CUtensorMap ta;
+  alignas(64) CUtensorMap tb;
+  bool ok;
+  if (A_MN == 0) ok = make_map(&ta, p.A, p.M, p.K, p.lda, BM); else ok = make_map(&ta, p.A, p.K, p.M, p.lda, BK);
+  if (!ok) return 2;
+  if (B_MN == 0) ok = make_map(&tb, p.B, p.N, p.K, p.ldb, 128); else ok = make_map(&tb, p.B, p.K, p.N, p.ldb, BK);
+  if (!ok) return 2;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::kSmemBytes) != cudaSuccess) return 3;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, p.error_flag);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+template <int A_MN, int B_MN>
+int launch_pair_epi(const GemmArgs& p, cudaStream_t st) {
+  switch (p.epilogue) {
+    case kEpiStoreBf16: return launch_pair<A_MN, B_MN, kEpiStoreBf16>(p, st);
+    case kEpiReluSqBf16: return launch_pair<A_MN, B_MN, kEpiReluSqBf16>(p, st);
+    case kEpiStoreF32: return launch_pair<A_MN, B_MN, kEpiStoreF32>(p, st);
+    case kEpiAccumF32: return launch_pair<A_MN, B_MN, kEpiAccumF32>(p, st);
+  }
+  return 5;
+}
+
+int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
+  switch (p.layout) {
+    case kGemmTN: return launch_pair_epi<0, 0>(p, st);
+    case kGemmNN: return launch_pair_epi<0, 1>(p, st);
+    case kGemmNT_wgrad: return launch_pair_epi<1, 1>(p, st);
+  }
+  return 5;
+}
+
 }  // namespace
 
 int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
@@ -405,6 +641,8 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   const bool out_bf16 = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16;
   if (p.ldd & (out_bf16 ? 7 : 3)) return 6;
   if (p.error_flag == nullptr) return 7;
+  // the CTA-pair kernel needs at least one full 256-row tile and a wide N to pay off
+  if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair_layout(p, st);
   if (p.N > 128) return launch_layout<256>(p, st);
   return launch_layout<128>(p, st);
 }

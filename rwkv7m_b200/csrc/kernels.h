@@ -117,6 +117,7 @@ struct GemmArgs {
   int M, N, K;
   int lda, ldb, ldd;   // leading dimensions in elements of the stored matrices
   int layout, epilogue;
+  int pair;            // non-zero: use the CTA-pair (cta_group::2) kernel when the shape allows
   int* error_flag;     // device int, set non-zero if a bounded wait ran out
 };
 int gemm_bf16(const GemmArgs& p, cudaStream_t st);

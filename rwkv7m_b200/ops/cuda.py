@@ -80,9 +80,18 @@ def wkv7(r, w, k, v, a, b, state0):
 # ---------------------------------------------------------------------------
 
 
-def gemm(a, b, out, layout, epilogue):
+# CTA-pair (cta_group::2) GEMM for large shapes; RWKV7M_B200_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel.
+GEMM_PAIR = os.environ.get("RWKV7M_B200_GEMM_PAIR", "1") != "0"
+
+
+def set_gemm_pair(enabled: bool):
+    global GEMM_PAIR
+    GEMM_PAIR = bool(enabled)
+
+
+def gemm(a, b, out, layout, epilogue, pair=None):
     """Raw GEMM launcher: see csrc/kernels.h for layouts.  Returns ``out``."""
-    _C.gemm(a, b, out, layout, epilogue)
+    _C.gemm(a, b, out, layout, epilogue, int(GEMM_PAIR if pair is None else pair))
     _count()
     return out
 

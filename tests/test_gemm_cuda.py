@@ -18,7 +18,17 @@ def _rand(*shape, seed=0):
 
 
 SHAPES = [(128, 256, 64), (256, 512, 128), (384, 256, 512), (200, 136, 72), (64, 32, 2048), (1000, 768, 320),
-          (4096, 2048, 2048)]
+          (4096, 2048, 2048), (2304, 1000, 4096)]
+
+
+@pytest.fixture(params=[0, 1], ids=["single", "pair"], autouse=True)
+def _pair_mode(request):
+    """Every test runs on the single-CTA kernel and on the CTA-pair kernel (large shapes only switch)."""
+    kk = _K()
+    old = kk.GEMM_PAIR
+    kk.set_gemm_pair(bool(request.param))
+    yield
+    kk.set_gemm_pair(old)
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
