@@ -85,13 +85,19 @@ def create_runtime(rng_key, config, *, batch_size: int = 1, device=None) -> RWKV
 
 
 def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, device=None,
-                         shard_multiple: int = 1, buffer_allocator=None):
+                         shard_multiple: int = 1, buffer_allocator=None, tp=None):
     config = load_model_config(config)
     train_state = initialize_train_state(
         _seed(rng_key) + 1, config, total_steps=total_steps, device=_default_device(device),
-        shard_multiple=shard_multiple, buffer_allocator=buffer_allocator,
+        shard_multiple=shard_multiple, buffer_allocator=buffer_allocator, tp=tp,
     )
-    return _make_runtime(train_state.model, config, batch_size), train_state
+    runtime = _make_runtime(train_state.model, config, batch_size)
+    if tp is not None:
+        from .parallel.tp import TensorParallelTrainer
+
+        runtime.rwkv_state = runtime.initial_rwkv_state = tp.init_rwkv_state(batch_size, config, device=runtime.device)
+        TensorParallelTrainer(train_state, tp)
+    return runtime, train_state
 
 
 def load_runtime_params(runtime: RWKV7MRuntime, params):
@@ -180,7 +186,9 @@ def train_batch(train_state, batch, runtime: RWKV7MRuntime, *, phase="read_scree
         if bsz == runtime.batch_size:
             rwkv_state, screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
         else:
-            rwkv_state = init_rwkv_state(bsz, runtime.config, device=device)
+            tp = getattr(runtime.model, "tp", None)
+            rwkv_state = (tp.init_rwkv_state(bsz, runtime.config, device=device) if tp is not None
+                          else init_rwkv_state(bsz, runtime.config, device=device))
             screen_state = init_screen_state(
                 bsz, runtime.config.screening if runtime.config.use_screening else _no_screen(runtime.config),
                 device=device,

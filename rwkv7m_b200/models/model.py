@@ -75,6 +75,11 @@ class ScreenedRWKVModel(nn.Module):
     def compute_recurrent_hidden(self, input_ids, rwkv_state, screen_state, *, phase="read_screening_only"):
         cfg = self.config
         phase = normalize_phase(phase)
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            if cfg.screening_active:
+                raise NotImplementedError("screening memory is not sharded yet: run screened models data-parallel")
+            input_ids = tp.local_time_slice(input_ids)  # the residual stream is sharded over time
         x = ops.embedding(input_ids, self.emb.weight, self.compute_dtype)
         screened_idx = {layer: i for i, layer in enumerate(cfg.screening.screened_layers)} if cfg.use_screening else {}
         v_first = torch.zeros_like(x)
@@ -103,13 +108,48 @@ class ScreenedRWKVModel(nn.Module):
             raise ValueError(
                 f"hidden final dimension must equal config.d_model, got {hidden.shape[-1]} and {self.config.d_model}"
             )
-        return ops.linear(self.ln_out(hidden), self.head.weight)
+        tp = getattr(self, "tp", None)
+        h = self.ln_out(hidden)
+        if tp is not None:
+            h = tp.gather_seq(h)
+        logits = ops.linear(h, self.head.weight)
+        if tp is not None and tp.vocab_parallel:
+            parts = [torch.empty_like(logits) for _ in range(tp.world)]
+            torch.distributed.all_gather(parts, logits.contiguous(), group=tp.group)
+            logits = torch.cat(parts, dim=-1)
+        return logits
 
     def compute_training_loss(self, hidden, targets, mask=None, *, chunk=None):
         """CE / L2Wrap numerators and denominators without exposing the logits."""
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            return self._tp_training_loss(hidden, targets, mask, chunk, tp)
         ce_total, ce_count, l2_total, l2_count = ops.head_loss(
             hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, targets, mask, chunk, self.ln_out.eps
         )
+        return {"ce_total": ce_total, "ce_count": ce_count, "l2_total": l2_total, "l2_count": l2_count}
+
+    def _tp_training_loss(self, hidden, targets, mask, chunk, tp):
+        """Loss pieces under tensor parallelism; ``hidden`` is this rank's time slice."""
+        if tp.vocab_parallel:
+            from ..parallel.tp import vocab_parallel_cross_entropy
+
+            h = tp.gather_seq(self.ln_out(hidden))
+            T = h.shape[1]
+            step = chunk or T
+            totals = None
+            for s0 in range(0, T, step):
+                logits = ops.linear(h[:, s0 : s0 + step], self.head.weight)
+                part = vocab_parallel_cross_entropy(
+                    logits, targets[:, s0 : s0 + step], None if mask is None else mask[:, s0 : s0 + step], tp)
+                totals = part if totals is None else tuple(a + b for a, b in zip(totals, part))
+            ce_total, ce_count, l2_total, l2_count = totals
+        else:
+            t_loc = tp.local_time_slice(targets)
+            m_loc = None if mask is None else tp.local_time_slice(mask)
+            parts = ops.head_loss(hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, t_loc, m_loc,
+                                  chunk, self.ln_out.eps)
+            ce_total, ce_count, l2_total, l2_count = (tp.sum_scalar(p.float().reshape(())) for p in parts)
         return {"ce_total": ce_total, "ce_count": ce_count, "l2_total": l2_total, "l2_count": l2_count}
 
     def forward(self, input_ids, rwkv_state, screen_state, *, phase="read_screening_only"):

@@ -108,8 +108,10 @@ class RWKV7TimeMix(nn.Module):
     def forward(self, x, v_first, prev_x, wkv_state):
         """x: [B,T,C] (already LN1'd).  Returns (out, v_first, last_x fp32, final wkv state)."""
         cfg = self.config
-        B, T, C = x.shape
-        H, N = cfg.n_heads, cfg.head_size
+        B, T, _ = x.shape
+        # under tensor parallelism this rank holds H/w heads: sizes come from the (possibly sharded) parameters
+        H, N = self.r_k.shape[0], cfg.head_size
+        C = H * N
         x_r, x_w, x_k, x_v, x_a, x_g = ops.shift_mix(x, prev_x, self.x_mix)
         r = ops.linear(x_r, self.receptance.weight)
         k = ops.linear(x_k, self.key.weight)
@@ -170,10 +172,21 @@ class RWKV7Block(nn.Module):
         self.ffn = RWKV7ChannelMix(config, layer_idx)
 
     def forward(self, x, v_first, state: LayerRWKVState):
+        tp = getattr(self, "tp", None)
         if self.ln0 is not None:
             x = self.ln0(x)
-        att_out, v_first, tm_x, wkv = self.att(self.ln1(x), v_first, state.time_mix_x, state.wkv)
+        h = self.ln1(x)
+        if tp is not None:  # sequence-sharded residual: gather tokens for the column-parallel projections
+            h = tp.gather_seq(h)
+        att_out, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv)
+        if tp is not None:  # row-parallel output: sum the partial results, keep this rank's tokens
+            att_out = tp.reduce_scatter_seq(att_out)
         x = x + att_out
-        ffn_out, cm_x = self.ffn(self.ln2(x), state.channel_mix_x)
+        h = self.ln2(x)
+        if tp is not None:
+            h = tp.gather_seq(h)
+        ffn_out, cm_x = self.ffn(h, state.channel_mix_x)
+        if tp is not None:
+            ffn_out = tp.reduce_scatter_seq(ffn_out)
         x = x + ffn_out
         return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)

@@ -1,0 +1,293 @@
+"""Tensor (model) parallelism with a sequence-sharded residual stream.
+
+The reference shards hidden activations on the feature axis and lets XLA insert
+all-reduces (src/rwkv7m/model/nnx_model.py:203-212,438-442,464-590,759-789;
+13 all-reduce + 3 all-to-all per tiny forward, docs/tpu_research_cloud.md:137-141).
+This framework uses the column/row-parallel pairing instead, which needs exactly
+one all-gather and one reduce-scatter per sub-block:
+
+  residual x            [B, T/w, C]   sharded over time, LayerNorm is local
+  all-gather over time  [B, T,   C]   input of the column-parallel projections
+  r/k/v, LoRA-up, ffn.key             output channels (= heads) sharded: [.., C/w] or [.., F/w]
+  WKV7, key normalisation, GroupNorm  per head, therefore local
+  att.output, ffn.value               row-parallel: partial [B, T, C] -> reduce-scatter over time
+
+Parameters that every rank holds in full (LayerNorms, token-shift mixes, LoRA-down, embedding)
+see different tokens or different heads per rank, so their gradients are summed over the group
+after backward.  The LM head is either replicated over the sequence shards or vocabulary-parallel
+(max / sum-exp / target-logit reductions, src/rwkv7m/model/losses.py:26-69).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..state import LayerRWKVState
+
+# (suffix, dim) of parameters sharded across the model-parallel group; dim indexes the
+# framework's own [out, in] layout.
+_SHARD_RULES = (
+    ("att.receptance.weight", 0), ("att.key.weight", 0), ("att.value.weight", 0), ("att.output.weight", 1),
+    ("att.w2", 0), ("att.a2", 0), ("att.v2", 0), ("att.g2", 0),
+    ("att.w0", 0), ("att.a0", 0), ("att.v0", 0), ("att.k_k", 0), ("att.k_a", 0), ("att.r_k", 0),
+    ("att.ln_x.weight", 0), ("att.ln_x.bias", 0),
+    ("ffn.key.weight", 0), ("ffn.value.weight", 1),
+)
+
+
+def shard_dim(name: str, vocab_parallel: bool = False):
+    """Shard dimension of a parameter, or None when it is replicated."""
+    for suffix, dim in _SHARD_RULES:
+        if name.endswith(suffix):
+            return dim
+    if vocab_parallel and name == "head.weight":
+        return 0
+    return None
+
+
+def parameter_partition_summary(model, world: int, vocab_parallel: bool = False) -> dict:
+    """Counts for run_config.json (reference: src/rwkv7m/distributed/partitioning.py:55-96)."""
+    sharded = replicated = 0
+    rows = []
+    for name, p in model.named_parameters():
+        d = shard_dim(name, vocab_parallel)
+        if d is None:
+            replicated += p.numel()
+        else:
+            sharded += p.numel()
+        rows.append({"name": name, "shape": list(p.shape), "shard_dim": d})
+    return {"world": world, "sharded_elements_per_rank": sharded, "replicated_elements": replicated, "parameters": rows}
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """y = sum over ranks; every rank's input gets the incoming gradient unchanged."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def _all_gather_time(x, group, world):
+    """[B, T/w, ...] on every rank -> [B, T, ...]."""
+    flat = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x.contiguous(), group=group)
+    parts = flat.view((world,) + tuple(x.shape))
+    return parts.transpose(0, 1).reshape(x.shape[0], world * x.shape[1], *x.shape[2:])
+
+
+def _reduce_scatter_time(x, group, world, rank):
+    """Partial [B, T, ...] on every rank -> summed [B, T/w, ...] of this rank's time slice."""
+    B, T = x.shape[0], x.shape[1]
+    chunks = x.reshape(B, world, T // world, *x.shape[2:]).transpose(0, 1).contiguous()
+    if dist.get_backend(group) == "gloo":
+        dist.all_reduce(chunks, group=group)
+        return chunks[rank].clone()
+    out = torch.empty(chunks.shape[1:], dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, chunks.view((world * chunks.shape[1],) + tuple(chunks.shape[2:])), group=group)
+    return out
+
+
+class _GatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _all_gather_time(x, tp.group, tp.world)
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        return _reduce_scatter_time(g.contiguous(), tp.group, tp.world, tp.rank), None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _reduce_scatter_time(x.contiguous(), tp.group, tp.world, tp.rank)
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        return _all_gather_time(g, tp.group, tp.world), None
+
+
+@dataclass
+class TensorParallel:
+    """Model-parallel context attached to a sharded model (``model.tp``)."""
+
+    group: object
+    world: int
+    rank: int
+    vocab_parallel: bool = False
+
+    @classmethod
+    def from_group(cls, group=None, vocab_parallel=False):
+        group = group if group is not None else dist.group.WORLD
+        return cls(group, dist.get_world_size(group), dist.get_rank(group), vocab_parallel)
+
+    # ---- activation collectives ----------------------------------------------
+    def gather_seq(self, x):
+        return _GatherSeq.apply(x, self)
+
+    def reduce_scatter_seq(self, x):
+        return _ReduceScatterSeq.apply(x, self)
+
+    def sum_scalar(self, x):
+        return _AllReduceSum.apply(x, self.group)
+
+    def local_time_slice(self, t):
+        """This rank's contiguous chunk of the time axis of a [B, T, ...] tensor."""
+        T = t.shape[1]
+        if T % self.world != 0:
+            raise ValueError(f"sequence length {T} must be divisible by the model-parallel size {self.world}")
+        n = T // self.world
+        return t[:, self.rank * n : (self.rank + 1) * n]
+
+    # ---- parameters --------------------------------------------------------------
+    def shard_model(self, model):
+        """Replace every sharded parameter by this rank's slice (in place) and tag the rest as replicated."""
+        cfg = model.config
+        if cfg.n_heads % self.world != 0 or cfg.ffn_dim % self.world != 0:
+            raise ValueError("n_heads and d_ffn must be divisible by the model-parallel size")
+        if self.vocab_parallel and cfg.vocab_size % self.world != 0:
+            raise ValueError("vocab_size must be divisible by the model-parallel size")
+        for name, p in model.named_parameters():
+            d = shard_dim(name, self.vocab_parallel)
+            if d is None:
+                p._tp_replicated = True
+                continue
+            n = p.shape[d] // self.world
+            p.data = p.data.narrow(d, self.rank * n, n).clone()
+            p._tp_shard_dim = d
+        model.tp = self
+        for layer in model.layers:
+            layer.block.tp = self
+        return model
+
+    def sync_replicated(self, model, src: int = 0):
+        """Make the replicated parameters bit-identical on every rank."""
+        for _, p in model.named_parameters():
+            if getattr(p, "_tp_replicated", False):
+                dist.broadcast(p.data, src=dist.get_global_rank(self.group, src), group=self.group)
+
+    def reduce_replicated_grads(self, model):
+        """Sum the gradients of replicated parameters over the group (call after backward)."""
+        grads = [p.grad for _, p in model.named_parameters()
+                 if getattr(p, "_tp_replicated", False) and p.grad is not None]
+        for g in grads:
+            dist.all_reduce(g, group=self.group)
+
+    def grad_norm_sq_reduce(self, model):
+        """Callback for ``AdamWChain.step``: turns the local sum of squared gradients into the global one
+        (replicated parameters must be counted once, not once per rank)."""
+
+        def reduce(norm_sq):
+            rep = norm_sq.new_zeros(1)
+            for _, p in model.named_parameters():
+                if getattr(p, "_tp_replicated", False) and p.grad is not None:
+                    rep += p.grad.float().pow(2).sum()
+            local = norm_sq - rep * (self.world - 1) / self.world
+            dist.all_reduce(local, group=self.group)
+            norm_sq.copy_(local)
+
+        return reduce
+
+    def gather_full_parameters(self, model) -> dict:
+        """Un-sharded ``name -> tensor`` mapping (every rank gets the full tensors)."""
+        out = {}
+        for name, p in model.named_parameters():
+            d = getattr(p, "_tp_shard_dim", None)
+            if d is None:
+                out[name] = p.detach()
+                continue
+            parts = [torch.empty_like(p.data) for _ in range(self.world)]
+            dist.all_gather(parts, p.data.contiguous(), group=self.group)
+            out[name] = torch.cat(parts, dim=d)
+        return out
+
+    # ---- state -------------------------------------------------------------------------
+    def init_rwkv_state(self, batch_size, config, device=None) -> tuple:
+        H = config.n_heads // self.world
+        N = config.head_size
+        return tuple(
+            LayerRWKVState(
+                torch.zeros(batch_size, config.d_model, device=device),
+                torch.zeros(batch_size, config.d_model, device=device),
+                torch.zeros(batch_size, H, N, N, device=device),
+            )
+            for _ in range(config.n_layers)
+        )
+
+
+def vocab_parallel_cross_entropy(logits_local, targets, mask, tp: TensorParallel):
+    """CE / L2Wrap pieces from vocabulary-sharded logits [.., V/w] (fp32 math).
+
+    Three reductions over the group: the running max, the sum of exponentials and the target
+    logit (only the owner of the target column contributes it).
+    """
+    lf = logits_local.float()
+    Vl = lf.shape[-1]
+    lo = tp.rank * Vl
+    local_max = lf.max(dim=-1).values
+    gmax = local_max.detach().clone()
+    dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=tp.group)
+    sumexp = tp.sum_scalar(torch.exp(lf - gmax.unsqueeze(-1)).sum(-1))
+    t = targets.long() - lo
+    owned = (t >= 0) & (t < Vl)
+    picked = lf.gather(-1, t.clamp(0, Vl - 1).unsqueeze(-1)).squeeze(-1)
+    tgt = tp.sum_scalar(torch.where(owned, picked, torch.zeros_like(picked)))
+    nll = torch.log(sumexp) + gmax - tgt
+    mask = torch.ones_like(nll) if mask is None else mask.float()
+    ce_total = (nll * mask).sum()
+    ce_count = mask.sum()
+    # L2Wrap acts on the global max logit: only the rank that owns it carries the gradient
+    is_owner = (local_max.detach() >= gmax).float()
+    max_logit = tp.sum_scalar(local_max * is_owner) / torch.clamp(_count_owners(is_owner, tp), min=1.0)
+    l2_total = 0.5e-4 * (max_logit * max_logit).sum()
+    l2_count = torch.tensor(float(max_logit.numel()), device=lf.device)
+    return ce_total, ce_count, l2_total, l2_count
+
+
+def _count_owners(is_owner, tp):
+    c = is_owner.clone()
+    dist.all_reduce(c, group=tp.group)
+    return c
+
+
+class TensorParallelTrainer:
+    """Installs the tensor-parallel optimizer step on a train state whose model was sharded with
+    :meth:`TensorParallel.shard_model`.  Every rank of the group consumes the same batch."""
+
+    def __init__(self, train_state, tp: TensorParallel):
+        self.tp = tp
+        self.train_state = train_state
+        train_state.extras["train_step"] = self.train_step
+
+    def train_step(self, train_state, batch, rwkv_state, screen_state, *, phase="read_screening_only",
+                   gradient_accumulation_steps=1):
+        from ..config import normalize_phase
+        from ..train.train_step import accumulate_gradients
+
+        phase = normalize_phase(phase)
+        model, opt = train_state.model, train_state.optimizer
+        model.train()
+        opt.zero_grad()
+        new_rwkv, new_screen, metrics = accumulate_gradients(
+            model, batch, rwkv_state, screen_state, phase=phase,
+            gradient_accumulation_steps=gradient_accumulation_steps,
+        )
+        opt.flat.collect_grads()
+        self.tp.reduce_replicated_grads(model)
+        opt.step(grad_norm_sq_reduce=self.tp.grad_norm_sq_reduce(model))
+        metrics["grad_norm"] = opt.grad_norm
+        return train_state, new_rwkv, new_screen, metrics

@@ -49,8 +49,11 @@ class TrainState:
 
 
 def initialize_train_state(seed, config: ModelConfig, *, total_steps: int = 10000, device=None,
-                           shard_multiple: int = 1, buffer_allocator=None) -> TrainState:
+                           shard_multiple: int = 1, buffer_allocator=None, tp=None) -> TrainState:
     model = initialize_model(seed, config, device=device)
+    if tp is not None:  # shard before the optimizer takes ownership of the parameter storage
+        tp.shard_model(model)
+        tp.sync_replicated(model)
     optimizer = create_optimizer(model, config, total_steps, shard_multiple, buffer_allocator)
     return TrainState(model=model, optimizer=optimizer, config=config)
 
