@@ -1,0 +1,130 @@
+"""Run auditor (clean and damaged runs), lifecycle probe across processes, toy loop, collective counters."""
+
+import json
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from rwkv7m_b200.cli import audit_distributed_run as audit_cli
+from rwkv7m_b200.cli import train_binidx_distributed
+from rwkv7m_b200.parallel.audit import audit_distributed_run, audit_report_to_dict
+from rwkv7m_b200.parallel.collectives import audit_collectives, count_collectives, ownership_table
+
+TINY = ["--d-model", "32", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64",
+        "--vocab-size", "300", "--n-slots", "4", "--d-slot", "16", "--d-k", "8", "--d-v", "8"]
+
+
+@pytest.fixture()
+def finished_run(tiny_binidx, tmp_path):
+    out = tmp_path / "run"
+    argv = ["--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2", "--steps", "4",
+            "--print-every", "0", "--output-dir", str(out), "--save-every", "2", "--keep-last-checkpoints", "2",
+            "--eval-every", "2", "--save-best-checkpoint", "--summary-every", "1"] + TINY
+    train_binidx_distributed.run_distributed_training(train_binidx_distributed.parse_args(argv))
+    return out
+
+
+def codes(report):
+    return {i.code for i in report.issues if i.severity == "error"}
+
+
+def test_clean_run_passes_strict_audit(finished_run):
+    report = audit_distributed_run(finished_run, require_complete=True, require_best_checkpoint=True, min_train_records=4)
+    assert report.ok, [i for i in report.issues]
+    data = audit_report_to_dict(report)
+    assert data["run_status"] == "completed" and data["current_step"] == 4 and data["error_count"] == 0
+    assert audit_cli.main([str(finished_run), "--require-complete", "--json"]) == 0
+
+
+def test_damaged_runs_are_flagged(finished_run, tmp_path):
+    # 1. non-finite loss and a step going backwards in metrics.jsonl
+    bad = tmp_path / "bad_metrics"
+    shutil.copytree(finished_run, bad)
+    lines = (bad / "metrics.jsonl").read_text().splitlines()
+    recs = [json.loads(l) for l in lines]
+    train_idx = [i for i, r in enumerate(recs) if r["split"] == "train"]
+    recs[train_idx[1]]["loss"] = float("nan")
+    recs[train_idx[2]]["step"] = 0
+    (bad / "metrics.jsonl").write_text("\n".join(json.dumps(r) for r in recs) + "\n")
+    c = codes(audit_distributed_run(bad))
+    assert "metrics_loss_invalid" in c and "metrics_train_steps_not_monotonic" in c
+
+    # 2. checkpoint with a missing tensor file; best_eval pointing at a deleted checkpoint
+    bad2 = tmp_path / "bad_ckpt"
+    shutil.copytree(finished_run, bad2)
+    ckpts = sorted(p for p in bad2.iterdir() if p.name.startswith("ckpt-"))
+    (ckpts[-1] / "train_state.safetensors").unlink()
+    best = json.loads((bad2 / "best_eval.json").read_text())
+    best["checkpoint"] = str(bad2 / "ckpt-99999999")
+    (bad2 / "best_eval.json").write_text(json.dumps(best))
+    c = codes(audit_distributed_run(bad2, require_best_checkpoint=True))
+    assert "checkpoint_train_state_missing" in c and "best_eval_checkpoint_missing" in c
+
+    # 3. summary claims more steps than were logged; truncated json
+    bad3 = tmp_path / "bad_summary"
+    shutil.copytree(finished_run, bad3)
+    s = json.loads((bad3 / "run_summary.json").read_text())
+    s["completed_steps"] = 40
+    s["status"] = "running"
+    (bad3 / "run_summary.json").write_text(json.dumps(s))
+    (bad3 / "run_config.json").write_text("{ truncated")
+    rep = audit_distributed_run(bad3, require_complete=True)
+    c = codes(rep)
+    assert "summary_not_completed" in c and "run_config_invalid" in c and not rep.ok
+    assert audit_cli.main([str(bad3), "--require-complete"]) == 1
+
+    # 4. empty directory
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    assert "run_summary_missing" in codes(audit_distributed_run(empty))
+
+
+def test_lifecycle_probe_restores_in_another_process(tmp_path):
+    d = str(tmp_path / "life")
+    for mode in ("create", "restore"):
+        r = subprocess.run([sys.executable, "-m", "rwkv7m_b200.cli.verify_lifecycle", mode, "--directory", d],
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout)["ok"] is True
+    # a tampered expectation must fail the probe
+    probe = Path(d) / "lifecycle_probe.json"
+    data = json.loads(probe.read_text())
+    data["expected_next_loss"] += 0.5
+    probe.write_text(json.dumps(data))
+    from rwkv7m_b200.parallel.lifecycle import restore_lifecycle_checkpoint
+    assert restore_lifecycle_checkpoint(d)["ok"] is False
+
+
+def test_toy_training_loop_reduces_loss():
+    from rwkv7m_b200.config import tiny_config
+    from rwkv7m_b200.train.train_loop import run_toy_training
+
+    cfg = tiny_config(vocab_size=32, d_model=32, n_layers=2, n_heads=2)
+    cfg.learning_rate = 3e-3
+    cfg.warmup_steps = 2
+    out = run_toy_training(cfg, num_steps=30, batch_size=2, seq_len=8, seed=0)
+    # seed*100003+step gives a new batch each step; on random data the loss moves toward log(V)
+    assert len(out["losses"]) == 30 and all(l == l for l in out["losses"])
+    assert sum(out["losses"][-5:]) / 5 < sum(out["losses"][:5]) / 5 + 0.05
+
+
+def test_collective_ownership_and_counter():
+    assert {r["parallelism"] for r in ownership_table()} == {"dp", "tp", "any"}
+    assert all(r["parallelism"] in ("tp", "any") for r in ownership_table("tp"))
+    assert audit_collectives("a = all-reduce-start(b)\nc = reduce-scatter(d)")["reduce-scatter"] == 1
+    import torch.distributed as dist
+    import tempfile, os
+    store = dist.FileStore(os.path.join(tempfile.mkdtemp(), "s"), 1)
+    dist.init_process_group("gloo", store=store, rank=0, world_size=1)
+    try:
+        with count_collectives() as c:
+            t = torch.ones(8)
+            dist.all_reduce(t)
+            dist.all_reduce(t)
+        assert c["calls"]["all_reduce"] == 2 and c["bytes"]["all_reduce"] == 64
+    finally:
+        dist.destroy_process_group()

@@ -35,3 +35,17 @@ def test_fused_step_matches_allreduce(multicast):
     assert abs(res["norm_ref"] - res["norm_fused"]) < 1e-3 * max(res["norm_ref"], 1e-6)
     for a, b in zip(res["loss_ref"], res["loss_fused"]):
         assert abs(a - b) < 5e-3 * abs(a)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_matches_single_gpu():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29533", str(Path(__file__).with_name("tp_worker.py"))]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    for key in ("vp0", "vp1"):
+        r = res[key]
+        assert r["rel_l2"] < 3e-3, res
+        for a, b in zip(r["loss_ref"], r["loss_tp"]):
+            assert abs(a - b) < 1e-2 * abs(a), res

@@ -1,0 +1,53 @@
+"""Worker for the multi-GPU tensor-parallel test (launched with torch.distributed.run)."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    local = int(os.environ["LOCAL_RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+
+    import rwkv7m_b200 as R
+    from rwkv7m_b200.parallel.tp import TensorParallel
+
+    cfg = R.ModelConfig(d_model=256, d_ffn=512, n_layers=2, n_heads=4, head_size=64, vocab_size=512,
+                        max_seq_len=64, dtype="bfloat16", use_screening=False, warmup_steps=0, lr_init=1e-3)
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, 512, (2, 65), generator=g).to(torch.int32)
+    batch = {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(), "mask": torch.ones(2, 64)}
+
+    def run(tp):
+        rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=50, device=dev, tp=tp)
+        losses = []
+        for _ in range(3):
+            ts, m = R.train_batch(ts, batch, rt)
+            losses.append(float(m["loss"]))
+        params = tp.gather_full_parameters(ts.model) if tp is not None else dict(ts.model.named_parameters())
+        return {n: p.detach().float().clone() for n, p in params.items()}, losses, float(ts.optimizer.grad_norm)
+
+    ref, l_ref, n_ref = run(None)
+    out = {}
+    for vp in (False, True):
+        got, l_tp, n_tp = run(TensorParallel.from_group(vocab_parallel=vp))
+        num = sum(float((ref[n] - got[n]).pow(2).sum()) for n in ref) ** 0.5
+        den = sum(float(ref[n].pow(2).sum()) for n in ref) ** 0.5
+        out[f"vp{int(vp)}"] = {"rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "norm_ref": n_ref, "norm_tp": n_tp}
+    if rank == 0:
+        print(json.dumps(out))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
