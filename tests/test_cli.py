@@ -107,3 +107,30 @@ def test_distributed_trainer_single_process_artifacts(tiny_binidx, tmp_path):
     ts2, _, s2 = train_binidx_distributed.run_distributed_training(train_binidx_distributed.parse_args(
         argv[:6] + ["--steps", "2"] + argv[8:] + ["--resume", str(out / "ckpt-00000004")]))
     assert int(ts2.step) == 6 and s2["start_step"] == 4
+
+
+def test_compare_variants_plan_run_summarize(tiny_binidx, tmp_path):
+    from rwkv7m_b200.cli import compare_variants
+
+    model = ["--d-model", "32", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64",
+             "--vocab-size", "300", "--n-slots", "4", "--d-slot", "16", "--d-k", "8", "--d-v", "8", "--screened-layers", "1"]
+    plan = compare_variants.plan_variants(model)
+    v = plan["variants"]
+    C, dk, dv, ds, M = 32, 8, 8, 16, 4
+    read_extra = 2 * C + C * dk + ds * dk + ds * dv + dv * C + C * C + C + (2 * C + ds) * ds + ds + 2 + M * ds + 3
+    assert v["local_read_screening"]["trainable_params"] - v["local_core_baseline"]["trainable_params"] == read_extra
+    assert v["local_mechanism"]["trainable_params"] - v["local_read_screening"]["trainable_params"] == 2 * C * dk + ds * dk + 1
+    assert v["local_param_control"]["trainable_params"] >= plan["param_target"] > v["local_core_baseline"]["trainable_params"]
+    assert v["local_param_control"]["d_ffn"] % 32 == 0 and v["local_param_control"]["use_screening"] == 0
+
+    root = tmp_path / "cmp"
+    train = ["--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2", "--steps", "4", "--print-every", "0",
+             "--eval-every", "2", "--summary-every", "0"]
+    out = compare_variants.run_variants(root, model + train)
+    assert all(s["status"] == "completed" for s in out["summaries"].values()) and len(out["summaries"]) == 4
+    summary = compare_variants.summarize(root, tokens_per_step=8, loss_targets=[100.0])
+    assert set(summary) == set(compare_variants.VARIANT_ORDER)
+    for row in summary.values():
+        assert row["train_steps"] == 4 and row["final_eval_loss"] is not None and row["eval_loss_auc_mean"] is not None
+        assert row["targets"]["100"]["step"] == 2 and "local_core_baseline_final" in row["targets"]
+    assert (root / "summary.csv").exists() and (root / "parameter_counts.csv").exists()
