@@ -41,7 +41,7 @@ rk::WkvArgs wkv_args(const Tensor& r, const Tensor& w, const Tensor& k, const Te
 }
 
 std::vector<Tensor> wkv7_fwd(const Tensor& r, const Tensor& w, const Tensor& k, const Tensor& v, const Tensor& a,
-                             const Tensor& b, const Tensor& s0, bool save, int64_t interval) {
+                             const Tensor& b, const Tensor& s0, bool save, int64_t interval, bool chunked) {
   c10::cuda::CUDAGuard guard(r.device());
   TORCH_CHECK(interval >= 1, "checkpoint interval must be positive");
   rk::WkvArgs p = wkv_args(r, w, k, v, a, b, s0, interval);
@@ -59,13 +59,17 @@ std::vector<Tensor> wkv7_fwd(const Tensor& r, const Tensor& w, const Tensor& k, 
     sa = torch::empty({0}, r.options().dtype(at::kFloat));
     ckpt = sa;
   }
-  TORCH_CHECK(rk::wkv7_forward(p, stream()) == 0, "wkv7_forward: unsupported shape");
+  if (chunked && rk::wkv7_chunk_supported(p)) {
+    TORCH_CHECK(rk::wkv7_chunk_forward(p, stream()) == 0, "wkv7_chunk_forward: launch failed");
+  } else {
+    TORCH_CHECK(rk::wkv7_forward(p, stream()) == 0, "wkv7_forward: unsupported shape");
+  }
   return {y, sT, sa, ckpt};
 }
 
 std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, const Tensor& v, const Tensor& a,
                              const Tensor& b, const Tensor& s0, const Tensor& sa, const Tensor& ckpt,
-                             const Tensor& dy, const c10::optional<Tensor>& dsT, int64_t interval) {
+                             const Tensor& dy, const c10::optional<Tensor>& dsT, int64_t interval, bool chunked) {
   c10::cuda::CUDAGuard guard(r.device());
   rk::WkvArgs p = wkv_args(r, w, k, v, a, b, s0, interval);
   check_vec(dy, r, "dy");
@@ -86,7 +90,11 @@ std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, 
   }
   p.dr = dr.data_ptr(); p.dw = dw.data_ptr(); p.dk = dk.data_ptr(); p.dv = dv.data_ptr();
   p.da = da.data_ptr(); p.db = db.data_ptr(); p.ds0 = ds0.data_ptr<float>();
-  TORCH_CHECK(rk::wkv7_backward(p, stream()) == 0, "wkv7_backward: unsupported shape");
+  if (chunked && rk::wkv7_chunk_bwd_supported(p)) {
+    TORCH_CHECK(rk::wkv7_chunk_backward(p, stream()) == 0, "wkv7_chunk_backward: launch failed");
+  } else {
+    TORCH_CHECK(rk::wkv7_backward(p, stream()) == 0, "wkv7_backward: unsupported shape");
+  }
   return {dr, dw, dk, dv, da, db, ds0};
 }
 
@@ -449,6 +457,23 @@ int64_t dp_aux_words() { return rk::dp_aux_words(); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wkv7_fwd", &wkv7_fwd);
   m.def("wkv7_bwd", &wkv7_bwd);
+  m.def("wkv7_chunk_error", [](bool reset) { return rk::wkv7_chunk_error(reset) | rk::wkv7_chunk_bwd_error(reset); });
+#ifdef RK_WKV_PROF
+  m.def("wkv7_chunk_bwd_prof", [](bool reset) {
+    std::vector<int64_t> v(16);
+    long long raw[16];
+    rk::wkv7_chunk_bwd_prof(raw, reset);
+    for (int i = 0; i < 16; ++i) v[i] = raw[i];
+    return v;
+  });
+  m.def("wkv7_chunk_prof", [](bool reset) {
+    std::vector<int64_t> v(16);
+    long long raw[16];
+    rk::wkv7_chunk_prof(raw, reset);
+    for (int i = 0; i < 16; ++i) v[i] = raw[i];
+    return v;
+  });
+#endif
   m.def("grad_norm_sq", &grad_norm_sq);
   m.def("adamw_flat", &adamw_flat);
   m.def("gemm", &gemm);

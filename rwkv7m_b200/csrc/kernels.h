@@ -27,6 +27,18 @@ struct WkvArgs {
 };
 int wkv7_forward(const WkvArgs& p, cudaStream_t st);
 int wkv7_backward(const WkvArgs& p, cudaStream_t st);
+// Chunked tensor-core forward (head size 64, bf16, checkpoint interval 16 when aux is saved).
+bool wkv7_chunk_supported(const WkvArgs& p);
+int wkv7_chunk_forward(const WkvArgs& p, cudaStream_t st);
+int wkv7_chunk_error(bool reset);   // non-zero after a bounded wait ran out inside the chunked forward kernel
+// Chunked tensor-core backward: consumes sa (= U) and the 16-step state checkpoints written by either forward.
+bool wkv7_chunk_bwd_supported(const WkvArgs& p);
+int wkv7_chunk_backward(const WkvArgs& p, cudaStream_t st);
+int wkv7_chunk_bwd_error(bool reset);
+#ifdef RK_WKV_PROF
+void wkv7_chunk_bwd_prof(long long* out, bool reset);
+void wkv7_chunk_prof(long long* out, bool reset);   // per-phase clock counts of CTA 0 (profiling builds only)
+#endif
 
 // ---- optimizer ------------------------------------------------------------------
 // out[0] += sum(g^2) over n elements (out must be zeroed by the caller).

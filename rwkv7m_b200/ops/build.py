@@ -18,13 +18,18 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parents[1]
 CSRC = PKG / "csrc"
 EXT_NAME = "_C"
-SOURCES = ["bindings.cpp", "wkv7.cu", "optim.cu", "gemm_sm100.cu", "elementwise.cu", "loss.cu", "dp_fused.cu", "noalloc.cu"]
+SOURCES = ["bindings.cpp", "wkv7.cu", "wkv7_chunk.cu", "wkv7_chunk_bwd.cu", "optim.cu", "gemm_sm100.cu", "elementwise.cu", "loss.cu", "dp_fused.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--use_fast_math",
     "-std=c++17", "--expt-relaxed-constexpr", "-Xptxas", "-v",
 ]
 
 _module = None
+
+
+def _extra_defines():
+    """Extra -D flags for instrumented builds, e.g. RWKV7M_B200_DEFINES=RK_WKV_PROF."""
+    return [f"-D{d}" for d in os.environ.get("RWKV7M_B200_DEFINES", "").split(",") if d]
 
 
 def _so_path():
@@ -54,8 +59,8 @@ def build_extension(verbose: bool = False, force: bool = False):
     cpp_extension.load(
         name=EXT_NAME,
         sources=[str(CSRC / s) for s in SOURCES],
-        extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=NVCC_FLAGS,
+        extra_cflags=["-O3", "-std=c++17"] + _extra_defines(),
+        extra_cuda_cflags=NVCC_FLAGS + _extra_defines(),
         extra_include_paths=[str(CSRC)],
         build_directory=str(build_dir),
         verbose=verbose,

@@ -48,14 +48,33 @@ def set_gemm_backend(name: str):
 # ---------------------------------------------------------------------------
 
 
+# "chunked": tcgen05 chunk kernels for bf16 / head size 64 / T >= 64; "sequential": register-state scan kernels.
+WKV_IMPL = os.environ.get("RWKV7M_B200_WKV", "chunked")
+WKV_CHUNK_MIN_T = 64
+
+
+def set_wkv_impl(name: str):
+    global WKV_IMPL
+    if name not in ("chunked", "sequential"):
+        raise ValueError("wkv impl must be 'chunked' or 'sequential'")
+    WKV_IMPL = name
+
+
+def wkv_chunk_error_code(reset: bool = True) -> int:
+    """Non-zero if a chunked WKV CTA gave up on a bounded wait (host sync)."""
+    return int(_C.wkv7_chunk_error(reset))
+
+
 class Wkv7Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r, w, k, v, a, b, s0):
         r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
         s0 = s0.contiguous().float()
         need_grad = any(ctx.needs_input_grad)
-        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHECKPOINT_INTERVAL)
+        chunked = WKV_IMPL == "chunked" and r.shape[1] >= WKV_CHUNK_MIN_T
+        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHECKPOINT_INTERVAL, chunked)
         _count()
+        ctx.chunked = chunked
         if need_grad:
             ctx.save_for_backward(r, w, k, v, a, b, s0, sa, ckpt)
         return y, sT
@@ -65,7 +84,7 @@ class Wkv7Fn(torch.autograd.Function):
         r, w, k, v, a, b, s0, sa, ckpt = ctx.saved_tensors
         dy = dy.contiguous()
         dr, dw, dk, dv, da, db, ds0 = _C.wkv7_bwd(
-            r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, WKV_CHECKPOINT_INTERVAL
+            r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, WKV_CHECKPOINT_INTERVAL, ctx.chunked
         )
         _count()
         return dr, dw, dk, dv, da, db, ds0

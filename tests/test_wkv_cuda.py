@@ -93,4 +93,53 @@ def test_rejects_bad_state_dtype():
     from rwkv7m_b200.ops.build import load_extension
 
     with pytest.raises(RuntimeError):
-        load_extension().wkv7_fwd(*vecs, s0.double(), False, 16)
+        load_extension().wkv7_fwd(*vecs, s0.double(), False, 16, False)
+
+
+@pytest.mark.parametrize("T", [64, 128, 200])
+@pytest.mark.parametrize("save", [False, True])
+def test_chunked_tensor_core_forward_matches_sequential_kernel(T, save):
+    """The tcgen05 chunk kernel must reproduce the scan kernel: outputs, final state and, in training mode,
+    the saved U vectors and 16-step state checkpoints the backward kernel consumes."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    vecs, s0 = _inputs(2, T, 3, 64, torch.bfloat16, seed=T)
+    seq = C.wkv7_fwd(*vecs, s0, save, 16, False)
+    for _ in range(2):  # twice in a row: the kernel reuses its shared-memory tiles and TMEM columns per chunk
+        chk = C.wkv7_fwd(*vecs, s0, save, 16, True)
+        torch.cuda.synchronize()
+        assert C.wkv7_chunk_error(True) == 0
+        y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
+        scale = float(y_ref.abs().max())
+        assert float((chk[0].float() - y_ref).abs().max()) / scale < 2e-2
+        assert float((chk[0].float() - seq[0].float()).abs().max()) / scale < 2e-2
+        assert float((chk[1] - sT_ref).norm() / sT_ref.norm()) < 1e-2
+        if save:
+            assert float((chk[2] - seq[2]).norm() / seq[2].norm()) < 1e-2       # sa
+            assert chk[3].shape == seq[3].shape
+            assert float((chk[3] - seq[3]).norm() / seq[3].norm()) < 1e-2       # checkpoints
+
+
+def test_chunked_forward_feeds_backward():
+    from rwkv7m_b200.ops import cuda as K
+
+    vecs, s0 = _inputs(1, 128, 2, 64, torch.bfloat16, seed=21)
+    wy = torch.randn(1, 128, 2, 64, device="cuda")
+
+    def run(fn, cast):
+        leaves = [cast(t).clone().requires_grad_(True) for t in vecs]
+        y, _ = fn(*leaves, s0)
+        (y.float() * wy).sum().backward()
+        return [l.grad.float() for l in leaves]
+
+    old = K.WKV_IMPL
+    try:
+        K.set_wkv_impl("chunked")
+        got = run(ops.wkv7, lambda t: t)
+    finally:
+        K.set_wkv_impl(old)
+    want = run(R.wkv7, lambda t: t.float())
+    for name, a, b in zip("r w k v a b".split(), got, want):
+        rel = float((a - b).norm() / (b.norm() + 1e-9))
+        assert rel < 4e-2, (name, rel)
