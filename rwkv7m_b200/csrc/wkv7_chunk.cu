@@ -9,15 +9,16 @@
 //   U    = (I - A_ab)^-1 Z          forward substitution in fp32 on the CUDA cores; U_t = S_{t-1} a_t
 //   Y    = R~ S0^T + A_rk V + A_rb U                                                                   (MMA)
 //   S1^T = diag(P_L) S0^T + B^^T U + K^^T V                                                            (MMA)
-// One CTA per (batch, head) walks the chunks in order.  Every product is a tcgen05.mma with M = 128 (two
-// 64-row operands stacked, or 64 useful rows plus 64 ignored ones), bf16 operands written into shared memory in
-// the 128-byte-swizzled canonical layout, fp32 accumulators in tensor memory.  The fp32 master copy of the
-// state lives in the registers of 64 threads (thread k holds row k of S^T); its bf16 image is the B operand
-// of the next chunk.  Decay is bounded below by exp(-exp(-0.5)) = 0.545 per step, so every scale factor stays
-// inside the fp32 / bf16 exponent range over 64 steps.
+// One CTA of 8 warps per (batch, head) walks the chunks in order; two CTAs share an SM.  Every product is a
+// tcgen05.mma with M = 128 (two 64-row operands stacked, or 64 useful rows plus 64 ignored ones), bf16
+// operands written into shared memory in the 128-byte-swizzled canonical layout, fp32 accumulators in tensor
+// memory.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
+// S^T); its bf16 image is the B operand of the next chunk.  The substitution runs on two threads per value
+// column (rows split by parity, one shuffle per step).  Decay is bounded below by exp(-exp(-0.5)) = 0.545
+// per step, so every scale factor stays inside the fp32 / bf16 exponent range over 64 steps.
 //
-// In training mode the kernel also writes what the time-sequential backward kernel consumes: U (as `sa`) and
-// the state after every 16th step.  Reference semantics: src/rwkv7m/model/rwkv_core.py:54-86,
+// In training mode the kernel also writes U (the `sa` vectors) and the state after every chunk, which is what
+// the chunked backward kernel consumes.  Reference semantics: src/rwkv7m/model/rwkv_core.py:54-86,
 // src/rwkv7m/kernels/wkv_pallas_gpu.py:66-164.
 #include "common.cuh"
 #include "kernels.h"
@@ -31,7 +32,7 @@ namespace {
 
 constexpr int L = 64;        // chunk length
 constexpr int NH = 64;       // head size
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
 constexpr int kFStride = 68; // row stride (floats) of the fp32 scratch matrices: 16-byte aligned, conflict-light
 
 // shared memory map (byte offsets from a 1024-byte aligned base)
@@ -41,13 +42,13 @@ constexpr uint32_t kOffBKe = kOffBK + 18432;      // [128][64] bf16: rows 0-63 B
 constexpr uint32_t kOffUV = kOffBKe + 16384;      // [128][64] bf16: rows 0-63 U, 64-127 V
 constexpr uint32_t kOffX2 = kOffUV + 16384;       // [64][64] bf16: A_rb (rows 64-127 of an operand that starts 8 KB earlier)
 constexpr uint32_t kOffS = kOffX2 + 8192;         // [64][64] bf16: S^T
-constexpr uint32_t kOffF = kOffS + 8192;          // fp32 [64][68]: cumulative log decay, later A_ab
-constexpr uint32_t kOffPL = kOffF + L * kFStride * 4;   // fp32 [4][64]: P at steps 15, 31, 47, 63
-constexpr uint32_t kOffBar = kOffPL + 4 * NH * 4; // 4 mbarriers, tmem slot, failure flag
+constexpr uint32_t kOffF = kOffS + 8192;          // fp32 [64][68]: A_ab^T with the row index split by parity
+constexpr uint32_t kOffPL = kOffF + L * kFStride * 4;   // fp32 [64]: P_L
+constexpr uint32_t kOffBar = kOffPL + NH * 4;     // 3 mbarriers, tmem slot, failure flag
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;    // + alignment slack
 
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColD1 = 0;    // 128 columns: A matrices; later the state products
+constexpr uint32_t kColD1 = 0;    // 128 columns: A matrices; later the state products (first 64)
 constexpr uint32_t kColD2 = 128;  // 64 columns: Z (lanes 0-63) and Y (lanes 64-127)
 
 __device__ int g_wkv_chunk_error = 0;
@@ -73,10 +74,6 @@ struct ChunkPtrs {
   float *sT, *sa, *ckpt;
 };
 
-}  // namespace
-
-namespace {
-
 template <bool SAVE>
 __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g, int T, int H, int BH) {
   extern __shared__ uint8_t smem_raw[];
@@ -89,14 +86,14 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   float* F = reinterpret_cast<float*>(sm + kOffF);
   float* Zs = reinterpret_cast<float*>(sm + kOffBK);
   float* PL = reinterpret_cast<float*>(sm + kOffPL);
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, bi = bh / H, hi = bh - bi * H;
   const size_t stride_t = (size_t)H * NH;
   const size_t base = (size_t)bi * T * stride_t + (size_t)hi * NH;
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 1);
     *failed = 0;
     mbar_fence_init();
   }
@@ -105,26 +102,28 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  const int trow = tid & 63;
+  // tensor-memory view of this thread: row m of the 128-row accumulators, column half ch
+  const int wq = warp & 3, ch = warp >> 2;
+  const int m = wq * 32 + lane;
+  const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+  const bool lower = wq < 2;            // rows 0-63 (A~ rows, Z, state) vs rows 64-127 (R~ rows, Y)
+  const int trow = m & 63;
 
-  // fp32 master copy of the state: thread k (< 64) holds row k of S^T, i.e. S[v][k] for all v
-  float st[NH];
-  if (tid < 64) {
+  // fp32 master copy of the state: thread (k = trow, ch) of the lower warps holds S[v][k] for v in [32 ch, 32 ch + 32)
+  float st[32];
+  if (lower) {
 #pragma unroll
-    for (int v = 0; v < NH; ++v) st[v] = g.s0 != nullptr ? g.s0[((size_t)bh * NH + v) * NH + tid] : 0.f;
+    for (int j = 0; j < 32; ++j) st[j] = g.s0 != nullptr ? g.s0[((size_t)bh * NH + 32 * ch + j) * NH + trow] : 0.f;
 #pragma unroll
-    for (int p = 0; p < 8; ++p) {
+    for (int p = 0; p < 4; ++p) {
       float x[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[j] = st[8 * p + j];
-      *reinterpret_cast<uint4*>(sm + kOffS + sw128(tid, p)) = pack8(x);
+      *reinterpret_cast<uint4*>(sm + kOffS + sw128(trow, 4 * ch + p)) = pack8(x);
     }
   }
 
   const int nchunks = (T + L - 1) / L;
-  const int nck = (T + 15) / 16;
-  const int piece = 2 * warp + ((tid >> 4) & 1), lq = tid & 15;  // operand preparation: column piece, row quad
   bool ok = true;
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
@@ -132,78 +131,102 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * L;
     const uint32_t par = (uint32_t)(c & 1);
-    // ---- operands: every warp owns two 16-byte column pieces, lane l' of a 16-lane group owns rows 4l'..4l'+3 --
+    // ---- raw tiles: coalesced asynchronous copies straight into the operand tile slots (8 lanes per 128-byte row) ----
     {
-      const size_t go0 = base + (size_t)(t0 + 4 * lq) * stride_t + piece * 8;
+      const int p8 = tid & 7;
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-      uint4 rw[4], ra[4], rr[4], rb[4], rk[4], rv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const bool valid = t0 + 4 * lq + i < T;
-        const size_t go = go0 + (size_t)i * stride_t;
-        rw[i] = valid ? *reinterpret_cast<const uint4*>(g.w + go) : zero;
-        ra[i] = valid ? *reinterpret_cast<const uint4*>(g.a + go) : zero;
-        rr[i] = valid ? *reinterpret_cast<const uint4*>(g.r + go) : zero;
-        rb[i] = valid ? *reinterpret_cast<const uint4*>(g.b + go) : zero;
-        rk[i] = valid ? *reinterpret_cast<const uint4*>(g.k + go) : zero;
-        rv[i] = valid ? *reinterpret_cast<const uint4*>(g.v + go) : zero;
+      for (int i = 0; i < 2; ++i) {
+        const int row = (tid >> 3) + 32 * i;
+        const uint32_t off = sw128(row, p8);
+        const size_t go = base + (size_t)(t0 + row) * stride_t + p8 * 8;
+        if (t0 + row < T) {
+          cp_async16(sm + kOffAR + off, g.a + go);
+          cp_async16(sm + kOffAR + 8192 + off, g.r + go);
+          cp_async16(sm + kOffBK + off, g.b + go);
+          cp_async16(sm + kOffBK + 8192 + off, g.k + go);
+          cp_async16(sm + kOffBKe + off, g.w + go);
+          cp_async16(sm + kOffUV + 8192 + off, g.v + go);
+        } else {
+          *reinterpret_cast<uint4*>(sm + kOffAR + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffAR + 8192 + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffBK + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffBK + 8192 + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffBKe + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = zero;
+        }
       }
-      if (c + 1 < nchunks) {  // pull the next chunk's rows into L2 while this chunk is being processed
+      if (c + 1 < nchunks) {  // pull the next chunk's rows (one 128-byte line each) into L2
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int t = t0 + L + 4 * lq + i;
-          if (t < T && (piece & 1) == 0) {  // one prefetch per 32-byte sector pair is enough: pieces 2w and 2w+1 share it
-            const size_t go = go0 + (size_t)(L + i) * stride_t;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.w + go));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.a + go));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.r + go));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.b + go));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.k + go));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(g.v + go));
+        for (int j = 0; j < 2; ++j) {
+          const int e = tid + 256 * j;
+          const int which = e >> 6, row = e & 63;
+          if (e < 384 && t0 + L + row < T) {
+            const __nv_bfloat16* src = which == 0 ? g.a : which == 1 ? g.r : which == 2 ? g.b : which == 3 ? g.k : which == 4 ? g.w : g.v;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(src + base + (size_t)(t0 + L + row) * stride_t));
           }
         }
       }
-      // inclusive cumulative log decay of the lane's four rows, then a 16-lane scan of the lane totals
-      float lp[4][8], ex[8], ptot[8];
+      cp_async_wait_all();
+      __syncthreads();
+    }
+    PROF_MARK(8);
+    // ---- rescale in place: warp w owns the 16-byte column piece w, lane l owns rows l and l + 32 ----------------------
+    {
+      const int piece = warp;
+      uint4 rw[2], ra[2], rr[2], rb[2], rk[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t off = sw128(lane + 32 * i, piece);
+        rw[i] = *reinterpret_cast<const uint4*>(sm + kOffBKe + off);
+        ra[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + off);
+        rr[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + 8192 + off);
+        rb[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + off);
+        rk[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + 8192 + off);
+      }
+      // cumulative log decay: one warp scan per half (rows 0-31, rows 32-63), the second offset by the first total
+      float ld[2][8], lp[2][8], ptot[8];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
         float x[8];
         unpack8(rw[i], x);
-        const bool valid = t0 + 4 * lq + i < T;
+        const bool valid = t0 + lane + 32 * i < T;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float ld = valid ? -__expf(x[j]) : 0.f;
-          lp[i][j] = i == 0 ? ld : lp[i - 1][j] + ld;
-        }
+        for (int j = 0; j < 8; ++j) ld[i][j] = valid ? -__expf(x[j]) : 0.f;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float tot = lp[3][j];
+        float s0_ = ld[0][j], s1_ = ld[1][j];
 #pragma unroll
-        for (int off = 1; off < 16; off <<= 1) {
-          const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
-          if (lq >= off) tot += o;
+        for (int off = 1; off < 32; off <<= 1) {
+          const float o0 = __shfl_up_sync(0xffffffffu, s0_, off);
+          const float o1 = __shfl_up_sync(0xffffffffu, s1_, off);
+          if (lane >= off) { s0_ += o0; s1_ += o1; }
         }
-        ex[j] = tot - lp[3][j];                                   // cumulative log decay before this lane's rows
-        ptot[j] = __expf(__shfl_sync(0xffffffffu, tot, 15, 16));  // P_L of the column
+        const float tot0 = __shfl_sync(0xffffffffu, s0_, 31);
+        lp[0][j] = s0_;
+        lp[1][j] = tot0 + s1_;
+        ptot[j] = __expf(tot0 + __shfl_sync(0xffffffffu, s1_, 31));  // P_L of the column
       }
-      PROF_MARK(8);
-      float eprev[8];
+      if (lane == 31) {
+        float* dst = PL + piece * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(ptot[0], ptot[1], ptot[2], ptot[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(ptot[4], ptot[5], ptot[6], ptot[7]);
+      }
+      PROF_MARK(9);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) eprev[j] = __expf(ex[j]);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = 4 * lq + i;
-        const uint32_t off = sw128(row, piece);
-        float e1[8], inv[8], x[8], y[8];
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t off = sw128(lane + 32 * i, piece);
+        float e1[8], e0[8], inv[8], x[8], y[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          e1[j] = __expf(ex[j] + lp[i][j]);
+          e1[j] = __expf(lp[i][j]);                 // P_t
+          e0[j] = __expf(lp[i][j] - ld[i][j]);      // P_{t-1}
           inv[j] = __frcp_rn(e1[j]);
         }
         unpack8(ra[i], x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * eprev[j];
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * e0[j];
         *reinterpret_cast<uint4*>(sm + kOffAR + off) = pack8(y);
         unpack8(rr[i], x);
 #pragma unroll
@@ -223,20 +246,12 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] *= ptot[j];
         *reinterpret_cast<uint4*>(sm + kOffBKe + 8192 + off) = pack8(y);
-        *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = rv[i];
-        if (i == 3 && (lq & 3) == 3) {  // P at steps 15, 31, 47, 63
-          float* dst = PL + (lq >> 2) * NH + piece * 8;
-          *reinterpret_cast<float4*>(dst) = make_float4(e1[0], e1[1], e1[2], e1[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(e1[4], e1[5], e1[6], e1[7]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) eprev[j] = e1[j];
       }
     }
-    PROF_MARK(9);
+    PROF_MARK(10);
     fence_proxy_async_smem();
     __syncthreads();
-    PROF_MARK(1);
+    PROF_MARK(0);
     // ---- MMA 1: the four triangular score matrices ------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -248,30 +263,33 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     }
     if (!mbar_wait(&bars[0], par, failed)) { *failed = 1; }
     tc_fence_after();
-    PROF_MARK(2);
+    PROF_MARK(1);
+    // thread (row m, half ch) reads 64 columns: ch = 0 -> products with B~ (A_ab | A_rb), ch = 1 -> with K~ (A_ak | A_rk)
 #pragma unroll
-    for (int hq = 0; hq < 4; ++hq) {  // hq>>1: which matrix of the row, hq&1: which half of its columns
+    for (int q = 0; q < 2; ++q) {
       uint32_t v[32];
-      tmem_ld_32x32(tmem + lane_base + kColD1 + hq * 32, v);
+      tmem_ld_32x32(tmem + lane_base + kColD1 + ch * 64 + q * 32, v);
       tmem_ld_wait();
-      const int s0 = (hq & 1) * 32;
-      if (tid < 64) {
-        if (hq < 2) {  // A_ab, strictly lower, fp32, stored transposed (column s contiguous over t) for the substitution
+      const int s0 = q * 32;
+      if (lower) {
+        if (ch == 0) {  // A_ab, strictly lower, fp32, stored transposed with the row index split by parity:
+                        // F[s][(t & 1) * 32 + (t >> 1)] = A_ab[t][s]
+          float* dst = F + s0 * kFStride + (trow & 1) * 32 + (trow >> 1);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) F[(s0 + j) * kFStride + trow] = s0 + j < trow ? __uint_as_float(v[j]) : 0.f;
-        } else {       // A_ak, strictly lower
-          store_masked_bf16(sm + kOffBK, trow, (hq & 1) * 4, v, s0, [&](int s) { return s < trow; });
+          for (int j = 0; j < 32; ++j) dst[j * kFStride] = s0 + j < trow ? __uint_as_float(v[j]) : 0.f;
+        } else {        // A_ak, strictly lower
+          store_masked_bf16(sm + kOffBK, trow, q * 4, v, s0, [&](int s) { return s < trow; });
         }
       } else {
-        if (hq < 2) store_masked_bf16(sm + kOffX2, trow, (hq & 1) * 4, v, s0, [&](int s) { return s <= trow; });          // A_rb
-        else store_masked_bf16(sm + kOffBK + 8192, trow, (hq & 1) * 4, v, s0, [&](int s) { return s <= trow; });          // A_rk
+        if (ch == 0) store_masked_bf16(sm + kOffX2, trow, q * 4, v, s0, [&](int s) { return s <= trow; });           // A_rb
+        else store_masked_bf16(sm + kOffBK + 8192, trow, q * 4, v, s0, [&](int s) { return s <= trow; });           // A_rk
       }
     }
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
-    PROF_MARK(3);
+    PROF_MARK(2);
     // ---- MMA 2: Z = A~ S0^T + A_ak V (lanes 0-63),  Y = R~ S0^T + A_rk V (lanes 64-127) -------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -286,47 +304,53 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     }
     if (!mbar_wait(&bars[1], par, failed)) { *failed = 1; }
     tc_fence_after();
+    PROF_MARK(3);
+    if (lower) {  // Z rows -> shared memory, 32 columns per thread
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + kColD2 + ch * 32, v);
+      tmem_ld_wait();
+      float* dst = Zs + trow * kFStride + ch * 32;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    }
+    tc_fence_before();
+    __syncthreads();
     PROF_MARK(4);
-    if (tid < 64) {
+    if (tid < 128) {
+      // Forward substitution on two threads per value column: thread (vcol, h) owns the rows of parity h.  Once u_s
+      // is final its owner broadcasts it with one shuffle and both threads push it into their later rows, so all
+      // updates of a step are independent.  Rows at or above the diagonal meet a stored zero.
+      const int vcol = tid >> 1, h = tid & 1;
+      float u[32];
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + kColD2 + q * 32, v);
-        tmem_ld_wait();
-        float* dst = Zs + trow * kFStride + q * 32;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-      }
-      asm volatile("bar.sync 1, 64;" ::: "memory");
-      PROF_MARK(10);
-      // forward substitution, thread = value column, right-looking: once u_s is final it is pushed into
-      // every later row, so all updates of one step are independent of each other
-      float u[L];
-#pragma unroll
-      for (int t = 0; t < L; ++t) u[t] = Zs[t * kFStride + tid];
+      for (int i = 0; i < 32; ++i) u[i] = Zs[(2 * i + h) * kFStride + vcol];
+      const float* Fh = F + 32 * h;
 #pragma unroll
       for (int s_ = 0; s_ < L - 1; ++s_) {
+        const float us = __shfl_sync(0xffffffffu, u[s_ >> 1], (lane & ~1) | (s_ & 1));
+        constexpr int kDummy = 0;
+        (void)kDummy;
 #pragma unroll
-        for (int t4 = 0; t4 < L / 4; ++t4) {
-          if (4 * t4 + 3 > s_) {
-            const float4 A = *reinterpret_cast<const float4*>(F + s_ * kFStride + 4 * t4);
-            if (4 * t4 + 0 > s_) u[4 * t4 + 0] = fmaf(A.x, u[s_], u[4 * t4 + 0]);
-            if (4 * t4 + 1 > s_) u[4 * t4 + 1] = fmaf(A.y, u[s_], u[4 * t4 + 1]);
-            if (4 * t4 + 2 > s_) u[4 * t4 + 2] = fmaf(A.z, u[s_], u[4 * t4 + 2]);
-            if (4 * t4 + 3 > s_) u[4 * t4 + 3] = fmaf(A.w, u[s_], u[4 * t4 + 3]);
+        for (int i4 = 0; i4 < 8; ++i4) {
+          if (4 * i4 + 3 >= ((s_ + 1) >> 1)) {   // this group of four rows holds a row index 2i+h that can exceed s
+            const float4 A = *reinterpret_cast<const float4*>(Fh + s_ * kFStride + 4 * i4);
+            if (4 * i4 + 0 >= (s_ >> 1)) u[4 * i4 + 0] = fmaf(A.x, us, u[4 * i4 + 0]);
+            if (4 * i4 + 1 >= (s_ >> 1)) u[4 * i4 + 1] = fmaf(A.y, us, u[4 * i4 + 1]);
+            if (4 * i4 + 2 >= (s_ >> 1)) u[4 * i4 + 2] = fmaf(A.z, us, u[4 * i4 + 2]);
+            if (4 * i4 + 3 >= (s_ >> 1)) u[4 * i4 + 3] = fmaf(A.w, us, u[4 * i4 + 3]);
           }
         }
       }
-#pragma unroll
-      for (int t = 0; t < L; ++t) {
-        *reinterpret_cast<__nv_bfloat16*>(sm + kOffUV + sw128(t, tid >> 3) + (tid & 7) * 2) = f2bf(u[t]);
-        if (SAVE && t0 + t < T) g.sa[base + (size_t)(t0 + t) * stride_t + tid] = u[t];
-      }
       PROF_MARK(11);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int t = 2 * i + h;
+        *reinterpret_cast<__nv_bfloat16*>(sm + kOffUV + sw128(t, vcol >> 3) + (vcol & 7) * 2) = f2bf(u[i]);
+        if (SAVE && t0 + t < T) g.sa[base + (size_t)(t0 + t) * stride_t + vcol] = u[i];
+      }
     }
-    tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
@@ -339,114 +363,48 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         umma_bf16(tmem + kColD2, desc_k(sbase + kOffX2 - 8192 + k * 32), desc_mn(sbase + kOffUV + k * 2048, 8192), idesc3, 1);
-      if (!SAVE) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_bf16(tmem + kColD1, desc_mn(sbase + kOffBKe + k * 2048, 16384), desc_mn(sbase + kOffUV + k * 2048, 8192),
-                    idesc4, k > 0);
-      } else {  // one accumulator per 16-step block so the intermediate states can be written out
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          umma_bf16(tmem + kColD1 + 64 * q, desc_mn(sbase + kOffBKe + q * 2048, 16384),
-                    desc_mn(sbase + kOffUV + q * 2048, 8192), idesc4, 0);
-          umma_bf16(tmem + kColD1 + 64 * q, desc_mn(sbase + kOffBKe + (4 + q) * 2048, 16384),
-                    desc_mn(sbase + kOffUV + (4 + q) * 2048, 8192), idesc4, 1);
-        }
-      }
+      for (int k = 0; k < 8; ++k)
+        umma_bf16(tmem + kColD1, desc_mn(sbase + kOffBKe + k * 2048, 16384), desc_mn(sbase + kOffUV + k * 2048, 8192),
+                  idesc4, k > 0);
       umma_commit(&bars[2]);
     }
     if (!mbar_wait(&bars[2], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(6);
-    if (tid >= 64) {  // output rows
-      const int t = t0 + trow;
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + kColD2 + q * 32, v);
+    {
+      uint32_t v[32];
+      if (!lower) {  // output row t, columns [32 ch, 32 ch + 32)
+        tmem_ld_32x32(tmem + lane_base + kColD2 + ch * 32, v);
         tmem_ld_wait();
+        const int t = t0 + trow;
         if (t < T) {
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
             float x[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[8 * p + j]);
-            *reinterpret_cast<uint4*>(g.y + base + (size_t)t * stride_t + q * 32 + p * 8) = pack8(x);
+            *reinterpret_cast<uint4*>(g.y + base + (size_t)t * stride_t + ch * 32 + p * 8) = pack8(x);
           }
         }
-      }
-    }
-    if (!SAVE) {
-      if (tid < 64) {
-        const float pl = PL[3 * NH + tid];
+      } else {       // state row k = trow, value columns [32 ch, 32 ch + 32)
+        tmem_ld_32x32(tmem + lane_base + kColD1 + ch * 32, v);
+        tmem_ld_wait();
+        const float pl = PL[trow];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem + lane_base + kColD1 + q * 32, v);
-          tmem_ld_wait();
+        for (int j = 0; j < 32; ++j) st[j] = fmaf(pl, st[j], __uint_as_float(v[j]));
 #pragma unroll
-          for (int j = 0; j < 32; ++j) st[q * 32 + j] = fmaf(pl, st[q * 32 + j], __uint_as_float(v[j]));
+        for (int p = 0; p < 4; ++p) {
+          float x[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = st[8 * p + j];
+          *reinterpret_cast<uint4*>(sm + kOffS + sw128(trow, 4 * ch + p)) = pack8(x);
         }
-      }
-    } else {
-      float acc[NH];
-      const float p63 = PL[3 * NH + (tid & 63)];
-      const float ip63 = 1.0f / p63;
+        if (SAVE) {  // state after this chunk, [v][k] layout
+          float* dst = g.ckpt + ((size_t)c * BH + bh) * NH * NH + (size_t)(32 * ch) * NH + trow;
 #pragma unroll
-      for (int round = 0; round < 2; ++round) {
-        if (round == 1) {
-          tc_fence_before();
-          __syncthreads();
-          if (tid == 0) {
-            tc_fence_after();
-            constexpr uint32_t idesc4 = umma_idesc_bf16(128, 64, 1, 1);
-#pragma unroll
-            for (int q = 2; q < 4; ++q) {
-              umma_bf16(tmem + kColD1 + 64 * (q - 2), desc_mn(sbase + kOffBKe + q * 2048, 16384),
-                        desc_mn(sbase + kOffUV + q * 2048, 8192), idesc4, 0);
-              umma_bf16(tmem + kColD1 + 64 * (q - 2), desc_mn(sbase + kOffBKe + (4 + q) * 2048, 16384),
-                        desc_mn(sbase + kOffUV + (4 + q) * 2048, 8192), idesc4, 1);
-            }
-            umma_commit(&bars[3]);
-          }
-          if (!mbar_wait(&bars[3], par, failed)) { *failed = 1; }
-          tc_fence_after();
+          for (int j = 0; j < 32; ++j) dst[(size_t)j * NH] = st[j];
         }
-        if (tid < 64) {
-#pragma unroll
-          for (int qq = 0; qq < 2; ++qq) {
-            const int q = round * 2 + qq;  // 16-step block inside the chunk
-            const float pq = PL[q * NH + tid];
-            const float ratio = pq * ip63;
-            const int ck = c * 4 + q;
-            float* dst = g.ckpt + ((size_t)ck * BH + bh) * NH * NH + tid;
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-              uint32_t v[32];
-              tmem_ld_32x32(tmem + lane_base + kColD1 + 64 * qq + hlf * 32, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int vi = hlf * 32 + j;
-                acc[vi] = (q == 0 ? 0.f : acc[vi]) + __uint_as_float(v[j]);
-                if (ck < nck) dst[(size_t)vi * NH] = fmaf(pq, st[vi], ratio * acc[vi]);
-              }
-            }
-          }
-        }
-      }
-      if (tid < 64) {
-#pragma unroll
-        for (int vi = 0; vi < NH; ++vi) st[vi] = fmaf(p63, st[vi], acc[vi]);
-      }
-    }
-    if (tid < 64) {  // bf16 image of the new state for the next chunk
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        float x[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = st[8 * p + j];
-        *reinterpret_cast<uint4*>(sm + kOffS + sw128(tid, p)) = pack8(x);
       }
     }
     tc_fence_before();
@@ -455,9 +413,9 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     if (*failed) { ok = false; break; }
     PROF_MARK(7);
   }
-  if (tid < 64 && g.sT != nullptr) {
+  if (lower && g.sT != nullptr) {
 #pragma unroll
-    for (int v = 0; v < NH; ++v) g.sT[((size_t)bh * NH + v) * NH + tid] = st[v];
+    for (int j = 0; j < 32; ++j) g.sT[((size_t)bh * NH + 32 * ch + j) * NH + trow] = st[j];
   }
   if (!ok && tid == 0) atomicExch(&g_wkv_chunk_error, 0x30000 | (bh & 0xffff));
   tc_fence_before();
@@ -467,9 +425,7 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
 
 }  // namespace
 
-bool wkv7_chunk_supported(const WkvArgs& p) {
-  return p.is_bf16 && p.N == NH && (p.sa == nullptr || p.interval == 16);
-}
+bool wkv7_chunk_supported(const WkvArgs& p) { return p.is_bf16 && p.N == NH && (p.sa == nullptr || p.interval == L); }
 
 int wkv7_chunk_forward(const WkvArgs& p, cudaStream_t st) {
   if (!wkv7_chunk_supported(p)) return 1;

@@ -12,8 +12,8 @@
 //   dr = dR~ P_t,  da = dA~ P_{t-1},  db = DB / P_t,  dk = DK / P_t
 //   dlogP_t = r~ dR~ - b~ DB - k~ DK + (a~ dA~)_{t+1}  (+ <dS1, S1> per key channel at the last step)
 //   dw_t = logd_t * sum_{t' >= t} dlogP_t'
-// One CTA per (batch, head) walks the chunks from last to first; the fp32 master copy of dS lives in the
-// registers of 64 threads.  Every product is a tcgen05.mma with M = 128 over 128-byte-swizzled bf16 tiles in
+// One CTA of 8 warps per (batch, head) walks the chunks from last to first; the fp32 master copy of dS lives in
+// registers (32 values per thread).  Every product is a tcgen05.mma with M = 128 over 128-byte-swizzled bf16 tiles in
 // shared memory, accumulators in tensor memory.  All waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
@@ -27,7 +27,7 @@ namespace {
 
 constexpr int L = 64;
 constexpr int NH = 64;
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
 constexpr int kFStride = 68;
 
 constexpr uint32_t kOffAR = 0;                       // [128][64] bf16: A~ | R~
@@ -37,11 +37,13 @@ constexpr uint32_t kOffZY = kOffUV + 16384;          // [128][64] bf16: dZ | dY
 constexpr uint32_t kOffS0 = kOffZY + 16384;          // [64][64] bf16: S0^T  (row = key channel)
 constexpr uint32_t kOffG = kOffS0 + 8192;            // [64][64] bf16: G = diag(P_L) dS1^T
 constexpr uint32_t kOffX = kOffG + 8192;             // [128][128] bf16 as two [128][64] column blocks: A then dA matrices
-constexpr uint32_t kOffF = kOffX + 32768;            // fp32 [64][68]: A_ab; later (a~ dA~)
+constexpr uint32_t kOffF = kOffX + 32768;            // fp32 [64][68]: A_ab (columns split by parity); later (a~ dA~)
 constexpr uint32_t kOffZ = kOffF + L * kFStride * 4; // fp32 [64][68]: dUdir; later the dlogP terms
 constexpr uint32_t kOffLP = kOffZ + L * kFStride * 4;// fp32 [64][68]: inclusive cumulative log decay
 constexpr uint32_t kOffPL = kOffLP + L * kFStride * 4; // fp32 [64]: P_L
-constexpr uint32_t kOffBar = kOffPL + NH * 4;
+constexpr uint32_t kOffLT = kOffPL + NH * 4;         // fp32 [2][64]: halves of <dS1, S1>
+constexpr uint32_t kOffBS = kOffLT + 2 * NH * 4;     // fp32 [4][64]: block sums of the decay-gradient scan
+constexpr uint32_t kOffBar = kOffBS + 4 * NH * 4;
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;
 
 constexpr uint32_t kTmemCols = 512;
@@ -76,6 +78,7 @@ __device__ long long g_wkv_chunk_bwd_prof[16];
 
 }  // namespace
 
+
 namespace {
 
 __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, int T, int H, int BH) {
@@ -89,7 +92,9 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   float* Zs = reinterpret_cast<float*>(sm + kOffZ);
   float* LP = reinterpret_cast<float*>(sm + kOffLP);
   float* PL = reinterpret_cast<float*>(sm + kOffPL);
-  const int tid = threadIdx.x, warp = tid >> 5;
+  float* LT = reinterpret_cast<float*>(sm + kOffLT);
+  float* BS = reinterpret_cast<float*>(sm + kOffBS);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, bi = bh / H, hi = bh - bi * H;
   const size_t stride_t = (size_t)H * NH;
   const size_t base = (size_t)bi * T * stride_t + (size_t)hi * NH;
@@ -105,19 +110,21 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  const int trow = tid & 63;
-  const int piece = 2 * warp + ((tid >> 4) & 1), lq = tid & 15;
+  // tensor-memory view of this thread: row m of the 128-row accumulators, column half ch
+  const int wq = warp & 3, ch = warp >> 2;
+  const int m = wq * 32 + lane;
+  const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+  const bool lower = wq < 2;
+  const int trow = m & 63;
 
-  // fp32 master copy of dS: thread k (< 64) holds row k of dS^T, i.e. dS[v][k] for all v
-  float ds[NH];
-  if (tid < 64) {
+  // fp32 master copy of dS: thread (k = trow, ch) of the lower warps holds dS[v][k] for v in [32 ch, 32 ch + 32)
+  float ds[32];
+  if (lower) {
 #pragma unroll
-    for (int v = 0; v < NH; ++v) ds[v] = g.dsT != nullptr ? g.dsT[((size_t)bh * NH + v) * NH + tid] : 0.f;
+    for (int j = 0; j < 32; ++j) ds[j] = g.dsT != nullptr ? g.dsT[((size_t)bh * NH + 32 * ch + j) * NH + trow] : 0.f;
   }
 
   const int nchunks = (T + L - 1) / L;
-  const int nck = (T + 15) / 16;
   bool ok = true;
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
@@ -125,83 +132,134 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   uint32_t par = 0;
   for (int c = nchunks - 1; c >= 0; --c, par ^= 1u) {
     const int t0 = c * L;
-    const float* S0g = c == 0 ? g.s0 + (size_t)bh * NH * NH : g.ckpt + ((size_t)(c * 4 - 1) * BH + bh) * NH * NH;
-    const float* S1g = g.ckpt + ((size_t)min(c * 4 + 3, nck - 1) * BH + bh) * NH * NH;
-    // ---- P0: operand tiles ------------------------------------------------------------------------------------
+    const float* S0g = c == 0 ? g.s0 + (size_t)bh * NH * NH : g.ckpt + ((size_t)(c - 1) * BH + bh) * NH * NH;
+    const float* S1g = g.ckpt + ((size_t)c * BH + bh) * NH * NH;
+    // ---- raw tiles: coalesced asynchronous copies straight into tile slots (8 lanes per 128-byte row); w and the
+    //      fp32 U rows are parked in the score-matrix region, which is free until the first readout ----------------
     {
-      const size_t go0 = base + (size_t)(t0 + 4 * lq) * stride_t + piece * 8;
+      const int p8 = tid & 7;
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-      // v and dy are copied unchanged: asynchronous 16-byte copies straight into the swizzled tiles
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = 4 * lq + i;
-        const uint32_t off = sw128(row, piece);
+      for (int i = 0; i < 2; ++i) {
+        const int row = (tid >> 3) + 32 * i;
+        const uint32_t off = sw128(row, p8);
+        const size_t go = base + (size_t)(t0 + row) * stride_t + p8 * 8;
+        uint8_t* urow = sm + kOffX + 8192 + row * 256 + p8 * 32;   // fp32 U, plain row-major
         if (t0 + row < T) {
-          cp_async16(sm + kOffUV + 8192 + off, g.v + go0 + (size_t)i * stride_t);
-          cp_async16(sm + kOffZY + 8192 + off, g.dy + go0 + (size_t)i * stride_t);
+          cp_async16(sm + kOffAR + off, g.a + go);
+          cp_async16(sm + kOffAR + 8192 + off, g.r + go);
+          cp_async16(sm + kOffBK + off, g.b + go);
+          cp_async16(sm + kOffBK + 8192 + off, g.k + go);
+          cp_async16(sm + kOffX + off, g.w + go);
+          cp_async16(sm + kOffUV + 8192 + off, g.v + go);
+          cp_async16(sm + kOffZY + 8192 + off, g.dy + go);
+          cp_async16(urow, g.sa + go);
+          cp_async16(urow + 16, g.sa + go + 4);
         } else {
+          *reinterpret_cast<uint4*>(sm + kOffAR + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffAR + 8192 + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffBK + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffBK + 8192 + off) = zero;
+          *reinterpret_cast<uint4*>(sm + kOffX + off) = zero;
           *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = zero;
           *reinterpret_cast<uint4*>(sm + kOffZY + 8192 + off) = zero;
+          *reinterpret_cast<uint4*>(urow) = zero;
+          *reinterpret_cast<uint4*>(urow + 16) = zero;
         }
       }
-      uint4 rw[4], ra[4], rr[4], rb[4], rk[4];
-      float4 u0[4], u1[4];
+      if (c > 0) {  // pull the previous chunk's rows (processed next) into L2, one 128-byte line per request
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const bool valid = t0 + 4 * lq + i < T;
-        const size_t go = go0 + (size_t)i * stride_t;
-        rw[i] = valid ? *reinterpret_cast<const uint4*>(g.w + go) : zero;
-        ra[i] = valid ? *reinterpret_cast<const uint4*>(g.a + go) : zero;
-        rr[i] = valid ? *reinterpret_cast<const uint4*>(g.r + go) : zero;
-        rb[i] = valid ? *reinterpret_cast<const uint4*>(g.b + go) : zero;
-        rk[i] = valid ? *reinterpret_cast<const uint4*>(g.k + go) : zero;
-        u0[i] = valid ? *reinterpret_cast<const float4*>(g.sa + go) : make_float4(0.f, 0.f, 0.f, 0.f);
-        u1[i] = valid ? *reinterpret_cast<const float4*>(g.sa + go + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < 2; ++j) {
+          const int e = tid + 256 * j;
+          const int which = e >> 6, row = e & 63;
+          if (e < 448) {
+            const __nv_bfloat16* src = which == 0 ? g.a : which == 1 ? g.r : which == 2 ? g.b : which == 3 ? g.k
+                                       : which == 4 ? g.w : which == 5 ? g.v : g.dy;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(src + base + (size_t)(t0 - L + row) * stride_t));
+          }
+        }
+        if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(g.sa + base + (size_t)(t0 - L + (tid >> 1)) * stride_t + (tid & 1) * 32));
       }
-      float lp[4][8], ex[8];
+      // S0^T tile: thread (k, vq) converts S0[16 vq .. 16 vq + 15][k]
+      {
+        const int k = tid & 63, vq = tid >> 6;
+        float x[16];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+        for (int j = 0; j < 16; ++j) x[j] = S0g[(size_t)(16 * vq + j) * NH + k];
+        float y0[8], y1[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { y0[j] = x[j]; y1[j] = x[8 + j]; }
+        *reinterpret_cast<uint4*>(sm + kOffS0 + sw128(k, 2 * vq)) = pack8(y0);
+        *reinterpret_cast<uint4*>(sm + kOffS0 + sw128(k, 2 * vq + 1)) = pack8(y1);
+      }
+      if (lower) {   // <dS1, S1> per key channel, one half of the value columns per thread
+        float lt = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) lt = fmaf(ds[j], S1g[(size_t)(32 * ch + j) * NH + trow], lt);
+        LT[ch * NH + trow] = lt;
+      }
+      cp_async_wait_all();
+      __syncthreads();
+    }
+    PROF_MARK(12);
+    // ---- rescale in place: warp w owns the 16-byte column piece w, lane l owns rows l and l + 32 ----------------------
+    {
+      const int piece = warp;
+      uint4 rw[2], ra[2], rr[2], rb[2], rk[2];
+      float4 u0[2], u1[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int row = lane + 32 * i;
+        const uint32_t off = sw128(row, piece);
+        rw[i] = *reinterpret_cast<const uint4*>(sm + kOffX + off);
+        ra[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + off);
+        rr[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + 8192 + off);
+        rb[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + off);
+        rk[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + 8192 + off);
+        const float* urow = reinterpret_cast<const float*>(sm + kOffX + 8192 + row * 256 + piece * 32);
+        u0[i] = *reinterpret_cast<const float4*>(urow);
+        u1[i] = *reinterpret_cast<const float4*>(urow + 4);
+      }
+      float ld[2][8], lp[2][8];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
         float x[8];
         unpack8(rw[i], x);
-        const bool valid = t0 + 4 * lq + i < T;
+        const bool valid = t0 + lane + 32 * i < T;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float ld = valid ? -__expf(x[j]) : 0.f;
-          lp[i][j] = i == 0 ? ld : lp[i - 1][j] + ld;
-        }
+        for (int j = 0; j < 8; ++j) ld[i][j] = valid ? -__expf(x[j]) : 0.f;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float tot = lp[3][j];
+        float s0_ = ld[0][j], s1_ = ld[1][j];
 #pragma unroll
-        for (int off = 1; off < 16; off <<= 1) {
-          const float o = __shfl_up_sync(0xffffffffu, tot, off, 16);
-          if (lq >= off) tot += o;
+        for (int off = 1; off < 32; off <<= 1) {
+          const float o0 = __shfl_up_sync(0xffffffffu, s0_, off);
+          const float o1 = __shfl_up_sync(0xffffffffu, s1_, off);
+          if (lane >= off) { s0_ += o0; s1_ += o1; }
         }
-        ex[j] = tot - lp[3][j];
-        if (lq == 15) PL[piece * 8 + j] = __expf(tot);
+        const float tot0 = __shfl_sync(0xffffffffu, s0_, 31);
+        lp[0][j] = s0_;
+        lp[1][j] = tot0 + s1_;
+        if (lane == 31) PL[piece * 8 + j] = __expf(lp[1][j]);
       }
-      float eprev[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) eprev[j] = __expf(ex[j]);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = 4 * lq + i;
+      for (int i = 0; i < 2; ++i) {
+        const int row = lane + 32 * i;
         const uint32_t off = sw128(row, piece);
-        float e1[8], inv[8], x[8], y[8];
+        float e1[8], e0[8], inv[8], x[8], y[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float c_ = ex[j] + lp[i][j];
-          e1[j] = __expf(c_);
+          e1[j] = __expf(lp[i][j]);
+          e0[j] = __expf(lp[i][j] - ld[i][j]);
           inv[j] = __frcp_rn(e1[j]);
-          y[j] = c_;
         }
         float* lpd = LP + row * kFStride + piece * 8;
-        *reinterpret_cast<float4*>(lpd) = make_float4(y[0], y[1], y[2], y[3]);
-        *reinterpret_cast<float4*>(lpd + 4) = make_float4(y[4], y[5], y[6], y[7]);
+        *reinterpret_cast<float4*>(lpd) = make_float4(lp[i][0], lp[i][1], lp[i][2], lp[i][3]);
+        *reinterpret_cast<float4*>(lpd + 4) = make_float4(lp[i][4], lp[i][5], lp[i][6], lp[i][7]);
         unpack8(ra[i], x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * eprev[j];
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * e0[j];
         *reinterpret_cast<uint4*>(sm + kOffAR + off) = pack8(y);
         unpack8(rr[i], x);
 #pragma unroll
@@ -218,31 +276,11 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         y[0] = u0[i].x; y[1] = u0[i].y; y[2] = u0[i].z; y[3] = u0[i].w;
         y[4] = u1[i].x; y[5] = u1[i].y; y[6] = u1[i].z; y[7] = u1[i].w;
         *reinterpret_cast<uint4*>(sm + kOffUV + off) = pack8(y);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) eprev[j] = e1[j];
       }
     }
-    PROF_MARK(0);
-    // S0^T tile and the <dS1, S1> term of the decay gradient (thread = key channel)
-    float lterm = 0.f;
-    if (tid < 64) {
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        float x[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int v = 8 * p + j;
-          x[j] = S0g[(size_t)v * NH + tid];
-          lterm = fmaf(ds[v], S1g[(size_t)v * NH + tid], lterm);
-        }
-        *reinterpret_cast<uint4*>(sm + kOffS0 + sw128(tid, p)) = pack8(x);
-      }
-    }
-    PROF_MARK(1);
-    cp_async_wait_all();
     fence_proxy_async_smem();
     __syncthreads();
-    PROF_MARK(2);
+    PROF_MARK(0);
     // ---- MMA 1: forward score matrices ------------------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -252,45 +290,51 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         umma_bf16(tmem + kC1, desc_k(sbase + kOffAR + k * 32), desc_k(sbase + kOffBK + k * 32), idesc, k > 0);
       umma_commit(&bars[0]);
     }
-    if (tid < 64) {  // G = diag(P_L) dS1^T while the MMA runs
-      const float pl = PL[tid];
+    if (lower) {  // G = diag(P_L) dS1^T while the MMA runs
+      const float pl = PL[trow];
 #pragma unroll
-      for (int p = 0; p < 8; ++p) {
+      for (int p = 0; p < 4; ++p) {
         float x[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = pl * ds[8 * p + j];
-        *reinterpret_cast<uint4*>(sm + kOffG + sw128(tid, p)) = pack8(x);
+        *reinterpret_cast<uint4*>(sm + kOffG + sw128(trow, 4 * ch + p)) = pack8(x);
       }
     }
     if (!mbar_wait(&bars[0], par, failed)) { *failed = 1; }
     tc_fence_after();
-    PROF_MARK(3);
+    PROF_MARK(1);
+    // thread (row m, half ch) reads 64 columns: ch = 0 -> products with B~ (A_ab | A_rb), ch = 1 -> with K~ (A_ak | A_rk)
 #pragma unroll
-    for (int hq = 0; hq < 4; ++hq) {
+    for (int q = 0; q < 2; ++q) {
       uint32_t v[32];
-      tmem_ld_32x32(tmem + lane_base + kC1 + hq * 32, v);
+      tmem_ld_32x32(tmem + lane_base + kC1 + ch * 64 + q * 32, v);
       tmem_ld_wait();
-      const int s0 = (hq & 1) * 32;
-      uint8_t* blk = sm + kOffX + (hq >> 1) * 16384;
-      if (tid < 64) {
-        if (hq < 2) {  // A_ab also in fp32 (row t contiguous over s) for the substitution
-          float* dst = F + trow * kFStride + s0;
+      const int s0 = q * 32;
+      uint8_t* blk = sm + kOffX + ch * 16384;
+      if (lower) {
+        if (ch == 0) {  // A_ab also in fp32 for the substitution, columns split by parity: F[t][(s & 1) * 32 + (s >> 1)]
+          float* de = F + trow * kFStride + (s0 >> 1);
+          float* dd = de + 32;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(dst + j) =
-                make_float4(s0 + j < trow ? __uint_as_float(v[j]) : 0.f, s0 + j + 1 < trow ? __uint_as_float(v[j + 1]) : 0.f,
-                            s0 + j + 2 < trow ? __uint_as_float(v[j + 2]) : 0.f, s0 + j + 3 < trow ? __uint_as_float(v[j + 3]) : 0.f);
+          for (int j = 0; j < 32; j += 8) {
+            *reinterpret_cast<float4*>(de + (j >> 1)) =
+                make_float4(s0 + j < trow ? __uint_as_float(v[j]) : 0.f, s0 + j + 2 < trow ? __uint_as_float(v[j + 2]) : 0.f,
+                            s0 + j + 4 < trow ? __uint_as_float(v[j + 4]) : 0.f, s0 + j + 6 < trow ? __uint_as_float(v[j + 6]) : 0.f);
+            *reinterpret_cast<float4*>(dd + (j >> 1)) =
+                make_float4(s0 + j + 1 < trow ? __uint_as_float(v[j + 1]) : 0.f, s0 + j + 3 < trow ? __uint_as_float(v[j + 3]) : 0.f,
+                            s0 + j + 5 < trow ? __uint_as_float(v[j + 5]) : 0.f, s0 + j + 7 < trow ? __uint_as_float(v[j + 7]) : 0.f);
+          }
         }
-        store_masked_bf16(blk, trow, (hq & 1) * 4, v, s0, [&](int s) { return s < trow; });
+        store_masked_bf16(blk, trow, q * 4, v, s0, [&](int s) { return s < trow; });
       } else {
-        store_masked_bf16(blk, 64 + trow, (hq & 1) * 4, v, s0, [&](int s) { return s <= trow; });
+        store_masked_bf16(blk, 64 + trow, q * 4, v, s0, [&](int s) { return s <= trow; });
       }
     }
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
-    PROF_MARK(4);
+    PROF_MARK(2);
     // ---- MMA 2: dUdir = A_rb^T dY + B~ G (lanes 0-63),  dVp = A_rk^T dY + K~ G (lanes 64-127) ---------------------
     if (tid == 0) {
       tc_fence_after();
@@ -307,47 +351,50 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
     }
     if (!mbar_wait(&bars[1], par, failed)) { *failed = 1; }
     tc_fence_after();
-    PROF_MARK(5);
-    if (tid < 64) {
+    PROF_MARK(3);
+    if (lower) {
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + kC2 + ch * 32, v);
+      tmem_ld_wait();
+      float* dst = Zs + trow * kFStride + ch * 32;
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + kC2 + q * 32, v);
-        tmem_ld_wait();
-        float* dst = Zs + trow * kFStride + q * 32;
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    }
+    tc_fence_before();
+    __syncthreads();
+    PROF_MARK(4);
+    if (tid < 128) {
+      // Backward substitution on two threads per value column: thread (vcol, h) owns the rows of parity h.  Once dZ_t
+      // is final its owner broadcasts it with one shuffle and both threads push it into their earlier rows.
+      const int vcol = tid >> 1, h = tid & 1;
+      float z[32];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                            __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-      }
-      asm volatile("bar.sync 1, 64;" ::: "memory");
-      PROF_MARK(6);
-      // backward substitution, thread = value column: once dZ_t is final it is pushed into every earlier row
-      float z[L];
-#pragma unroll
-      for (int t = 0; t < L; ++t) z[t] = Zs[t * kFStride + tid];
+      for (int i = 0; i < 32; ++i) z[i] = Zs[(2 * i + h) * kFStride + vcol];
+      const float* Fh = F + 32 * h;
 #pragma unroll
       for (int t = L - 1; t > 0; --t) {
+        const float zt = __shfl_sync(0xffffffffu, z[t >> 1], (lane & ~1) | (t & 1));
 #pragma unroll
-        for (int s4 = 0; s4 < L / 4; ++s4) {
-          if (4 * s4 < t) {
-            const float4 A = *reinterpret_cast<const float4*>(F + t * kFStride + 4 * s4);
-            if (4 * s4 + 0 < t) z[4 * s4 + 0] = fmaf(A.x, z[t], z[4 * s4 + 0]);
-            if (4 * s4 + 1 < t) z[4 * s4 + 1] = fmaf(A.y, z[t], z[4 * s4 + 1]);
-            if (4 * s4 + 2 < t) z[4 * s4 + 2] = fmaf(A.z, z[t], z[4 * s4 + 2]);
-            if (4 * s4 + 3 < t) z[4 * s4 + 3] = fmaf(A.w, z[t], z[4 * s4 + 3]);
+        for (int i4 = 0; i4 < 8; ++i4) {
+          if (4 * i4 <= ((t - 1) >> 1)) {   // rows 2i+h < t; an entry at or above the diagonal is a stored zero
+            const float4 A = *reinterpret_cast<const float4*>(Fh + t * kFStride + 4 * i4);
+            if (4 * i4 + 0 <= ((t - 1) >> 1)) z[4 * i4 + 0] = fmaf(A.x, zt, z[4 * i4 + 0]);
+            if (4 * i4 + 1 <= ((t - 1) >> 1)) z[4 * i4 + 1] = fmaf(A.y, zt, z[4 * i4 + 1]);
+            if (4 * i4 + 2 <= ((t - 1) >> 1)) z[4 * i4 + 2] = fmaf(A.z, zt, z[4 * i4 + 2]);
+            if (4 * i4 + 3 <= ((t - 1) >> 1)) z[4 * i4 + 3] = fmaf(A.w, zt, z[4 * i4 + 3]);
           }
         }
       }
 #pragma unroll
-      for (int t = 0; t < L; ++t)
-        *reinterpret_cast<__nv_bfloat16*>(sm + kOffZY + sw128(t, tid >> 3) + (tid & 7) * 2) = f2bf(z[t]);
+      for (int i = 0; i < 32; ++i)
+        *reinterpret_cast<__nv_bfloat16*>(sm + kOffZY + sw128(2 * i + h, vcol >> 3) + (vcol & 7) * 2) = f2bf(z[i]);
     }
-    tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
-    PROF_MARK(7);
+    PROF_MARK(5);
     // ---- MMA 3-7: everything that needs dZ but not the dA matrices ------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -373,50 +420,44 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
     }
     if (!mbar_wait(&bars[2], par, failed)) { *failed = 1; }
     tc_fence_after();
-    PROF_MARK(8);
+    PROF_MARK(6);
 #pragma unroll
-    for (int hq = 0; hq < 4; ++hq) {   // dA matrices, masked, into the two column blocks of X
+    for (int q = 0; q < 2; ++q) {   // dA matrices, masked, into column block ch of X
       uint32_t v[32];
-      tmem_ld_32x32(tmem + lane_base + kC1 + hq * 32, v);
+      tmem_ld_32x32(tmem + lane_base + kC1 + ch * 64 + q * 32, v);
       tmem_ld_wait();
-      const int s0 = (hq & 1) * 32;
-      uint8_t* blk = sm + kOffX + (hq >> 1) * 16384;
-      if (tid < 64) store_masked_bf16(blk, trow, (hq & 1) * 4, v, s0, [&](int s) { return s < trow; });
-      else store_masked_bf16(blk, 64 + trow, (hq & 1) * 4, v, s0, [&](int s) { return s <= trow; });
+      uint8_t* blk = sm + kOffX + ch * 16384;
+      if (lower) store_masked_bf16(blk, trow, q * 4, v, q * 32, [&](int s) { return s < trow; });
+      else store_masked_bf16(blk, 64 + trow, q * 4, v, q * 32, [&](int s) { return s <= trow; });
     }
-    if (tid >= 64) {   // dV rows
-      const int t = t0 + trow;
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + kC2 + q * 32, v);
+    {
+      uint32_t v[32];
+      if (!lower) {   // dV row t, columns [32 ch, 32 ch + 32)
+        tmem_ld_32x32(tmem + lane_base + kC2 + ch * 32, v);
         tmem_ld_wait();
+        const int t = t0 + trow;
         if (t < T) {
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
             float x[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[8 * p + j]);
-            *reinterpret_cast<uint4*>(g.dv + base + (size_t)t * stride_t + q * 32 + p * 8) = pack8(x);
+            *reinterpret_cast<uint4*>(g.dv + base + (size_t)t * stride_t + ch * 32 + p * 8) = pack8(x);
           }
         }
-      }
-    } else {           // dS0^T = G + R~^T dY + A~^T dZ
-      const float pl = PL[tid];
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + kC6 + q * 32, v);
+      } else {        // dS0^T = G + R~^T dY + A~^T dZ
+        tmem_ld_32x32(tmem + lane_base + kC6 + ch * 32, v);
         tmem_ld_wait();
+        const float pl = PL[trow];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) ds[q * 32 + j] = fmaf(pl, ds[q * 32 + j], __uint_as_float(v[j]));
+        for (int j = 0; j < 32; ++j) ds[j] = fmaf(pl, ds[j], __uint_as_float(v[j]));
       }
     }
     tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
-    PROF_MARK(9);
+    PROF_MARK(7);
     // ---- MMA 8-9: the products with the dA matrices ----------------------------------------------------------------
     if (tid == 0) {
       tc_fence_after();
@@ -435,85 +476,93 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
     }
     if (!mbar_wait(&bars[3], par, failed)) { *failed = 1; }
     tc_fence_after();
-    PROF_MARK(10);
+    PROF_MARK(8);
     // ---- epilogue: undo the rescaling, write dr/dk/da/db, assemble the decay gradient --------------------------------
     {
       const int t = t0 + trow;
-      const bool lower = tid < 64;          // lanes 0-63: (dA~, DB) of row t;  lanes 64-127: (dR~, DK) of row t
-      float e1r[NH];                        // upper lanes keep r~ dR~ - k~ DK until the lower lanes have stored their term
+      float e1r[32];   // upper lanes keep r~ dR~ - k~ DK until the lower lanes have stored their term
       const uint8_t* arow = sm + kOffAR + (lower ? 0 : 8192);
       const uint8_t* brow = sm + kOffBK + (lower ? 0 : 8192);
       __nv_bfloat16* g3 = (lower ? g.da : g.dr) + base + (size_t)t * stride_t;
       __nv_bfloat16* g4 = (lower ? g.db : g.dk) + base + (size_t)t * stride_t;
+      float d3[32], d4[32];
+      tmem_ld_f32(tmem + lane_base + kC3 + ch * 32, d3);
+      tmem_ld_f32(tmem + lane_base + kC4 + ch * 32, d4);
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        float d3[32], d4[32];
-        tmem_ld_f32(tmem + lane_base + kC3 + q * 32, d3);
-        tmem_ld_f32(tmem + lane_base + kC4 + q * 32, d4);
+      for (int p = 0; p < 4; ++p) {
+        const int k0 = ch * 32 + p * 8;
+        float av[8], bv[8], o3[8], o4[8];
+        unpack8(*reinterpret_cast<const uint4*>(arow + sw128(trow, ch * 4 + p)), av);
+        unpack8(*reinterpret_cast<const uint4*>(brow + sw128(trow, ch * 4 + p)), bv);
+        const float* lp = LP + trow * kFStride + k0;
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const int k0 = q * 32 + p * 8;
-          float av[8], bv[8], s3[8], s4[8], o3[8], o4[8];
-          unpack8(*reinterpret_cast<const uint4*>(arow + sw128(trow, q * 4 + p)), av);
-          unpack8(*reinterpret_cast<const uint4*>(brow + sw128(trow, q * 4 + p)), bv);
-          const float* lp = LP + trow * kFStride + k0;
+        for (int j = 0; j < 8; ++j) {
+          const float x = lp[j];
+          const float s4 = __expf(-x);                                                           // 1 / P_t
+          const float s3 = lower ? (trow > 0 ? __expf(lp[j - kFStride]) : 1.f) : __expf(x);      // P_{t-1} or P_t
+          o3[j] = d3[p * 8 + j] * s3;
+          o4[j] = d4[p * 8 + j] * s4;
+        }
+        if (t < T) {
+          *reinterpret_cast<uint4*>(g3 + k0) = pack8(o3);
+          *reinterpret_cast<uint4*>(g4 + k0) = pack8(o4);
+        }
+        if (lower) {
+          float* zq = Zs + trow * kFStride + k0;
+          float* fq = F + trow * kFStride + k0;
+          *reinterpret_cast<float4*>(zq) = make_float4(-bv[0] * d4[p * 8 + 0], -bv[1] * d4[p * 8 + 1], -bv[2] * d4[p * 8 + 2], -bv[3] * d4[p * 8 + 3]);
+          *reinterpret_cast<float4*>(zq + 4) = make_float4(-bv[4] * d4[p * 8 + 4], -bv[5] * d4[p * 8 + 5], -bv[6] * d4[p * 8 + 6], -bv[7] * d4[p * 8 + 7]);
+          *reinterpret_cast<float4*>(fq) = make_float4(av[0] * d3[p * 8 + 0], av[1] * d3[p * 8 + 1], av[2] * d3[p * 8 + 2], av[3] * d3[p * 8 + 3]);
+          *reinterpret_cast<float4*>(fq + 4) = make_float4(av[4] * d3[p * 8 + 4], av[5] * d3[p * 8 + 5], av[6] * d3[p * 8 + 6], av[7] * d3[p * 8 + 7]);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float x = lp[j];
-            s4[j] = __expf(-x);                                                   // 1 / P_t
-            s3[j] = lower ? (trow > 0 ? __expf(lp[j - kFStride]) : 1.f) : __expf(x);  // P_{t-1} or P_t
-            o3[j] = d3[p * 8 + j] * s3[j];
-            o4[j] = d4[p * 8 + j] * s4[j];
-          }
-          if (t < T) {
-            *reinterpret_cast<uint4*>(g3 + k0) = pack8(o3);
-            *reinterpret_cast<uint4*>(g4 + k0) = pack8(o4);
-          }
-          if (lower) {
-            float* zq = Zs + trow * kFStride + k0;
-            float* fq = F + trow * kFStride + k0;
-            *reinterpret_cast<float4*>(zq) = make_float4(-bv[0] * d4[p * 8 + 0], -bv[1] * d4[p * 8 + 1], -bv[2] * d4[p * 8 + 2], -bv[3] * d4[p * 8 + 3]);
-            *reinterpret_cast<float4*>(zq + 4) = make_float4(-bv[4] * d4[p * 8 + 4], -bv[5] * d4[p * 8 + 5], -bv[6] * d4[p * 8 + 6], -bv[7] * d4[p * 8 + 7]);
-            *reinterpret_cast<float4*>(fq) = make_float4(av[0] * d3[p * 8 + 0], av[1] * d3[p * 8 + 1], av[2] * d3[p * 8 + 2], av[3] * d3[p * 8 + 3]);
-            *reinterpret_cast<float4*>(fq + 4) = make_float4(av[4] * d3[p * 8 + 4], av[5] * d3[p * 8 + 5], av[6] * d3[p * 8 + 6], av[7] * d3[p * 8 + 7]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) e1r[k0 + j] = av[j] * d3[p * 8 + j] - bv[j] * d4[p * 8 + j];
-          }
+          for (int j = 0; j < 8; ++j) e1r[p * 8 + j] = av[j] * d3[p * 8 + j] - bv[j] * d4[p * 8 + j];
         }
       }
-      PROF_MARK(11);
+      PROF_MARK(9);
       __syncthreads();
       if (!lower) {
 #pragma unroll
-        for (int k4 = 0; k4 < NH; k4 += 4) {
-          float4* zq = reinterpret_cast<float4*>(Zs + trow * kFStride + k4);
+        for (int k4 = 0; k4 < 32; k4 += 4) {
+          float4* zq = reinterpret_cast<float4*>(Zs + trow * kFStride + ch * 32 + k4);
           float4 o = *zq;
           o.x += e1r[k4]; o.y += e1r[k4 + 1]; o.z += e1r[k4 + 2]; o.w += e1r[k4 + 3];
           *zq = o;
         }
       }
       __syncthreads();
-      PROF_MARK(12);
-      if (lower) {   // thread = key channel: reverse cumulative sum over the steps of the chunk
-        float run = lterm;
-#pragma unroll 8
-        for (int tt = L - 1; tt >= 0; --tt) {
-          run += Zs[tt * kFStride + tid] + (tt < L - 1 ? F[(tt + 1) * kFStride + tid] : 0.f);
-          const float logd = LP[tt * kFStride + tid] - (tt > 0 ? LP[(tt - 1) * kFStride + tid] : 0.f);
-          if (t0 + tt < T) g.dw[base + (size_t)(t0 + tt) * stride_t + tid] = f2bf(run * logd);
+      PROF_MARK(10);
+      {   // decay gradient: thread (k, blk) scans rows 16 blk .. 16 blk + 15 from the end, then adds the later blocks
+        const int k = tid & 63, blk = tid >> 6;
+        float part[16];
+        float run = 0.f;
+#pragma unroll
+        for (int j = 15; j >= 0; --j) {
+          const int tt = 16 * blk + j;
+          run += Zs[tt * kFStride + k] + (tt < L - 1 ? F[(tt + 1) * kFStride + k] : 0.f);
+          part[j] = run;
+        }
+        BS[blk * NH + k] = run;
+        __syncthreads();
+        float offs = LT[k] + LT[NH + k];
+#pragma unroll
+        for (int b2 = 1; b2 < 4; ++b2) offs += b2 > blk ? BS[b2 * NH + k] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tt = 16 * blk + j;
+          const float logd = LP[tt * kFStride + k] - (tt > 0 ? LP[(tt - 1) * kFStride + k] : 0.f);
+          if (t0 + tt < T) g.dw[base + (size_t)(t0 + tt) * stride_t + k] = f2bf((part[j] + offs) * logd);
         }
       }
     }
-    PROF_MARK(13);
     tc_fence_before();
     __syncthreads();
     if (*failed) { ok = false; break; }
-    PROF_MARK(14);
+    PROF_MARK(11);
   }
-  if (tid < 64 && g.ds0 != nullptr) {
+  if (lower && g.ds0 != nullptr) {
 #pragma unroll
-    for (int v = 0; v < NH; ++v) g.ds0[((size_t)bh * NH + v) * NH + tid] = ds[v];
+    for (int j = 0; j < 32; ++j) g.ds0[((size_t)bh * NH + 32 * ch + j) * NH + trow] = ds[j];
   }
   if (!ok && tid == 0) atomicExch(&g_wkv_chunk_bwd_error, 0x40000 | (bh & 0xffff));
   tc_fence_before();
@@ -523,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
 
 }  // namespace
 
-bool wkv7_chunk_bwd_supported(const WkvArgs& p) { return p.is_bf16 && p.N == NH && p.interval == 16; }
+bool wkv7_chunk_bwd_supported(const WkvArgs& p) { return p.is_bf16 && p.N == NH && p.interval == L; }
 
 int wkv7_chunk_backward(const WkvArgs& p, cudaStream_t st) {
   if (!wkv7_chunk_bwd_supported(p)) return 1;

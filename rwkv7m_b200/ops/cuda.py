@@ -51,6 +51,7 @@ def set_gemm_backend(name: str):
 # "chunked": tcgen05 chunk kernels for bf16 / head size 64 / T >= 64; "sequential": register-state scan kernels.
 WKV_IMPL = os.environ.get("RWKV7M_B200_WKV", "chunked")
 WKV_CHUNK_MIN_T = 64
+WKV_CHUNK_LEN = 64
 
 
 def set_wkv_impl(name: str):
@@ -71,8 +72,11 @@ class Wkv7Fn(torch.autograd.Function):
         r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
         s0 = s0.contiguous().float()
         need_grad = any(ctx.needs_input_grad)
-        chunked = WKV_IMPL == "chunked" and r.shape[1] >= WKV_CHUNK_MIN_T
-        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHECKPOINT_INTERVAL, chunked)
+        chunked = (WKV_IMPL == "chunked" and r.shape[1] >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16
+                   and r.shape[-1] == 64)
+        # the chunk kernels keep one state per 64-step chunk, the scan kernels one per 16 steps
+        ctx.interval = WKV_CHUNK_LEN if chunked else WKV_CHECKPOINT_INTERVAL
+        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, ctx.interval, chunked)
         _count()
         ctx.chunked = chunked
         if need_grad:
@@ -84,7 +88,7 @@ class Wkv7Fn(torch.autograd.Function):
         r, w, k, v, a, b, s0, sa, ckpt = ctx.saved_tensors
         dy = dy.contiguous()
         dr, dw, dk, dv, da, db, ds0 = _C.wkv7_bwd(
-            r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, WKV_CHECKPOINT_INTERVAL, ctx.chunked
+            r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, ctx.interval, ctx.chunked
         )
         _count()
         return dr, dw, dk, dv, da, db, ds0

@@ -37,8 +37,9 @@ def test_forward_bf16():
     vecs, s0 = _inputs(2, 64, 2, 64, torch.bfloat16)
     y, sT = ops.wkv7(*vecs, s0)
     y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
-    assert torch.allclose(y.float(), y_ref, atol=2e-2, rtol=2e-2)
-    assert torch.allclose(sT, sT_ref, atol=1e-4, rtol=1e-3)
+    # bf16 outputs; T = 64 takes the chunked tensor-core path, whose operands are rounded to bf16 as well
+    assert float((y.float() - y_ref).norm() / y_ref.norm()) < 8e-3
+    assert float((sT - sT_ref).norm() / sT_ref.norm()) < 5e-3
 
 
 @pytest.mark.parametrize("N,T", [(16, 7), (64, 16), (64, 45), (32, 33)])
@@ -100,28 +101,52 @@ def test_rejects_bad_state_dtype():
 @pytest.mark.parametrize("save", [False, True])
 def test_chunked_tensor_core_forward_matches_sequential_kernel(T, save):
     """The tcgen05 chunk kernel must reproduce the scan kernel: outputs, final state and, in training mode,
-    the saved U vectors and 16-step state checkpoints the backward kernel consumes."""
+    the saved U vectors and the state after every 64-step chunk."""
     from rwkv7m_b200.ops.build import load_extension
 
     C = load_extension()
     vecs, s0 = _inputs(2, T, 3, 64, torch.bfloat16, seed=T)
     seq = C.wkv7_fwd(*vecs, s0, save, 16, False)
+    y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
     for _ in range(2):  # twice in a row: the kernel reuses its shared-memory tiles and TMEM columns per chunk
-        chk = C.wkv7_fwd(*vecs, s0, save, 16, True)
+        chk = C.wkv7_fwd(*vecs, s0, save, 64, True)
         torch.cuda.synchronize()
         assert C.wkv7_chunk_error(True) == 0
-        y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
-        scale = float(y_ref.abs().max())
-        assert float((chk[0].float() - y_ref).abs().max()) / scale < 2e-2
-        assert float((chk[0].float() - seq[0].float()).abs().max()) / scale < 2e-2
-        assert float((chk[1] - sT_ref).norm() / sT_ref.norm()) < 1e-2
+        assert float((chk[0].float() - y_ref).norm() / y_ref.norm()) < 8e-3
+        assert float((chk[0].float() - seq[0].float()).norm() / y_ref.norm()) < 8e-3
+        assert float((chk[1] - sT_ref).norm() / sT_ref.norm()) < 5e-3
         if save:
-            assert float((chk[2] - seq[2]).norm() / seq[2].norm()) < 1e-2       # sa
-            assert chk[3].shape == seq[3].shape
-            assert float((chk[3] - seq[3]).norm() / seq[3].norm()) < 1e-2       # checkpoints
+            assert float((chk[2] - seq[2]).norm() / seq[2].norm()) < 8e-3       # U
+            assert chk[3].shape[0] == (T + 63) // 64
+            for c in range(chk[3].shape[0]):
+                want = seq[3][min(4 * c + 3, seq[3].shape[0] - 1)]
+                assert float((chk[3][c] - want).norm() / want.norm()) < 5e-3
 
 
-def test_chunked_forward_feeds_backward():
+@pytest.mark.parametrize("T", [64, 136, 256])
+def test_chunked_tensor_core_backward_matches_fp32_autograd(T):
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    B, H = 2, 2
+    vecs, s0 = _inputs(B, T, H, 64, torch.bfloat16, seed=100 + T)
+    g = torch.Generator().manual_seed(1)
+    dy = (torch.randn(B, T, H, 64, generator=g) * 0.5).cuda().bfloat16()
+    dsT = (torch.randn(B, H, 64, 64, generator=g) * 0.1).cuda()
+    leaves = [t.float().clone().requires_grad_(True) for t in vecs] + [s0.clone().requires_grad_(True)]
+    y, sT = R.wkv7(*leaves)
+    ((y * dy.float()).sum() + (sT * dsT).sum()).backward()
+    _, _, sa, ckpt = C.wkv7_fwd(*vecs, s0, True, 64, True)
+    for _ in range(2):
+        got = C.wkv7_bwd(*vecs, s0, sa, ckpt, dy, dsT, 64, True)
+        torch.cuda.synchronize()
+        assert C.wkv7_chunk_error(True) == 0
+        for name, a, leaf in zip("r w k v a b s0".split(), got, leaves):
+            rel = float((a.float() - leaf.grad).norm() / (leaf.grad.norm() + 1e-9))
+            assert rel < 1.5e-2, (name, rel)
+
+
+def test_chunked_path_through_autograd_function():
     from rwkv7m_b200.ops import cuda as K
 
     vecs, s0 = _inputs(1, 128, 2, 64, torch.bfloat16, seed=21)
@@ -137,9 +162,11 @@ def test_chunked_forward_feeds_backward():
     try:
         K.set_wkv_impl("chunked")
         got = run(ops.wkv7, lambda t: t)
+        K.set_wkv_impl("sequential")
+        seq = run(ops.wkv7, lambda t: t)
     finally:
         K.set_wkv_impl(old)
     want = run(R.wkv7, lambda t: t.float())
-    for name, a, b in zip("r w k v a b".split(), got, want):
-        rel = float((a - b).norm() / (b.norm() + 1e-9))
-        assert rel < 4e-2, (name, rel)
+    for name, a, s_, b in zip("r w k v a b".split(), got, seq, want):
+        assert float((a - b).norm() / (b.norm() + 1e-9)) < 1.5e-2, name
+        assert float((s_ - b).norm() / (b.norm() + 1e-9)) < 1.5e-2, name
