@@ -108,23 +108,98 @@ def bench_gemm(shapes, iters=10):
     return out
 
 
+def bench_fused(M, C, H, iters=10):
+    """Forward and backward of the fused memory-bound kernels on an [M, C] activation (M = B*T tokens), with the
+    algorithmic bytes each pass must move, so achieved GB/s can be read against the measured copy bandwidth."""
+    from rwkv7m_b200 import ops
+
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    B, T = 8, M // 8
+    bf = lambda *shape: (torch.randn(*shape, device="cuda") * 0.5).bfloat16()
+    par = lambda *shape: torch.randn(*shape, device="cuda", requires_grad=True)
+    x = bf(B, T, C).requires_grad_(True)
+    act = M * C * 2  # bytes of one bf16 activation
+    cases = []
+    ln_w, ln_b = par(C), par(C)
+    cases.append(("layer_norm", lambda: ops.layer_norm(x, ln_w, ln_b), 2 * act, 3 * act))
+    prev, mix = torch.zeros(B, C, device="cuda"), par(6, C)
+    cases.append(("shift_mix6", lambda: torch.stack(ops.shift_mix(x, prev, mix)).sum(0), 7 * act, 7 * act))
+    k, v, wl, al, vl, vf = (bf(B, T, C).requires_grad_(True) for _ in range(6))
+    w0, a0, v0, kk_, ka = (par(C) for _ in range(5))
+    cases.append(("tmix_pre", lambda: sum(ops.tmix_pre(k, v, wl, al, vl, vf, w0, a0, v0, kk_, ka, H)), 11 * act, 17 * act))
+    y, r, g = (bf(B, T, C).requires_grad_(True) for _ in range(3))
+    gw, gb, rk = par(C), par(C), par(H, C // H)
+    cases.append(("gn_bonus_gate", lambda: ops.gn_bonus_gate(y, r, k, v, g, gw, gb, rk, H), 6 * act, 11 * act))
+    out = []
+    for name, fn, fwd_bytes, bwd_bytes in cases:
+        with torch.no_grad():
+            tf = _time(fn, iters, flush=flush)
+        o = fn()
+        dy = torch.randn_like(o)
+
+        def fb():
+            fn().backward(dy)
+
+        tb = _time(fb, iters, flush=flush)
+        bwd_ms = max(tb["median_ms"] - tf["median_ms"], 1e-6)
+        out.append({"kernel": name, "M": M, "C": C, "fwd_ms": tf["median_ms"], "fwd_gbs": fwd_bytes / tf["median_ms"] / 1e6,
+                    "fwd_bwd_ms": tb["median_ms"], "bwd_gbs_est": bwd_bytes / bwd_ms / 1e6})
+    return out
+
+
+def bench_optimizer(n, iters=10):
+    """Flat AdamW (fp32 master + moments, bf16 shadow) and the gradient-norm reduction over n elements."""
+    from rwkv7m_b200.ops import cuda as K
+
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    shadow = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    norm = torch.zeros(1, device="cuda")
+
+    def norm_fn():
+        norm.zero_()
+        K.grad_norm_sq(g, norm)
+
+    def adam_fn():
+        K.adamw_flat(p, g, m, v, shadow, norm, (n // 2, n), lr=1e-4, beta1=0.9, beta2=0.99, eps=1e-8,
+                     weight_decay=0.01, bc1=0.1, bc2=0.01, max_norm=1.0, begin=0, end=n, grad_scale=1.0, zero_grad=True)
+
+    tn, ta = _time(norm_fn, iters), _time(adam_fn, iters)
+    return [{"kernel": "grad_norm_sq", "n": n, "ms": tn["median_ms"], "gbs": 4.0 * n / tn["median_ms"] / 1e6},
+            {"kernel": "adamw_flat", "n": n, "ms": ta["median_ms"], "gbs": (4 * 4 * 2 + 2) * n / ta["median_ms"] / 1e6}]
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="wkv,gemm")
+    ap.add_argument("--what", default="wkv,gemm", help="comma list of wkv, gemm, fused, optim")
+    ap.add_argument("--gemm-shape", default=None, help="M,N,K of a single GEMM case")
+    ap.add_argument("--wkv-shape", default=None, help="T,B,H,N of a single WKV case")
+    ap.add_argument("--wkv-impl", choices=["chunked", "sequential"], default=None)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json-out", default=None)
     ap.add_argument("--small", action="store_true", help="small shapes only (profiling captures)")
     args = ap.parse_args(argv)
     results = []
+    if args.wkv_impl:
+        from rwkv7m_b200.ops import cuda as K
+        K.set_wkv_impl(args.wkv_impl)
     if "wkv" in args.what:
         shapes = [(128, 1, 12, 64), (512, 4, 12, 64)] if args.small else [
             (128, 1, 12, 64), (128, 4, 12, 64), (512, 1, 12, 64), (512, 4, 12, 64), (4096, 8, 12, 64), (4096, 8, 32, 64)]
+        if args.wkv_shape:
+            shapes = [tuple(int(x) for x in args.wkv_shape.split(","))]
         results += bench_wkv(shapes, iters=args.iters)
     if "gemm" in args.what:
         shapes = [(4096, 2048, 2048)] if args.small else [
             (32768, 2048, 2048), (32768, 8192, 2048), (32768, 2048, 8192), (8192, 65536, 2048), (32768, 128, 2048),
             (32768, 768, 768), (8192, 8192, 8192)]
+        if args.gemm_shape:
+            shapes = [tuple(int(x) for x in args.gemm_shape.split(","))]
         results += bench_gemm(shapes, iters=args.iters)
+    if "fused" in args.what:
+        results += bench_fused(8192 if args.small else 32768, 2048, 32, iters=args.iters)
+    if "optim" in args.what:
+        results += bench_optimizer((64 if args.small else 512) * 1024 * 1024, iters=args.iters)
     for r in results:
         print(json.dumps(r))
     if args.json_out:
