@@ -449,6 +449,45 @@ int64_t dp_step(const std::vector<int64_t>& grad, const std::vector<int64_t>& ma
   return (int64_t)b;
 }
 
+rk::TpPeers make_tp_peers(const std::vector<int64_t>& buf, int64_t buf_mc, const std::vector<int64_t>& aux, int64_t rank) {
+  rk::TpPeers p{};
+  TORCH_CHECK(buf.size() == aux.size() && buf.size() >= 1 && buf.size() <= (size_t)rk::kMaxRanks, "bad peer lists");
+  for (size_t i = 0; i < buf.size(); ++i) {
+    p.buf[i] = reinterpret_cast<const void*>(buf[i]);
+    p.aux[i] = reinterpret_cast<void*>(aux[i]);
+  }
+  p.buf_mc = reinterpret_cast<const void*>(buf_mc);
+  p.rank = (int)rank; p.world = (int)buf.size();
+  return p;
+}
+
+// barrier (target = barriers issued so far on this aux buffer + 1), then all-gather over time into `out`
+void tp_gather_seq(const std::vector<int64_t>& buf, const std::vector<int64_t>& aux, int64_t rank, int64_t target, Tensor out,
+                   int64_t B, int64_t Tl, int64_t C) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 && C % 8 == 0);
+  TORCH_CHECK(out.numel() == B * Tl * C * (int64_t)buf.size(), "gather output must be [B, world*Tl, C]");
+  rk::TpPeers p = make_tp_peers(buf, 0, aux, rank);
+  rk::tp_barrier(p, (uint32_t)target, stream());
+  rk::tp_gather_seq(p, out.data_ptr(), (int)B, (int)Tl, (int)C, stream());
+}
+
+// barrier, then out = residual + sum over ranks of this rank's time slice of the partial buffers
+void tp_reduce_scatter_add(const std::vector<int64_t>& buf, int64_t buf_mc, const std::vector<int64_t>& aux, int64_t rank,
+                           int64_t target, const c10::optional<Tensor>& residual, Tensor out, int64_t B, int64_t Tl, int64_t C) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 && C % 8 == 0);
+  TORCH_CHECK(out.numel() == B * Tl * C, "reduce-scatter output must be [B, Tl, C]");
+  const void* res = nullptr;
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16 && residual->numel() == out.numel());
+    res = residual->data_ptr();
+  }
+  rk::TpPeers p = make_tp_peers(buf, buf_mc, aux, rank);
+  rk::tp_barrier(p, (uint32_t)target, stream());
+  rk::tp_reduce_scatter_add(p, res, out.data_ptr(), (int)B, (int)Tl, (int)C, stream());
+}
+
 int64_t dp_aux_error_word() { return rk::dp_aux_error_word(); }
 int64_t dp_aux_words() { return rk::dp_aux_words(); }
 
@@ -491,6 +530,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("dp_step", &dp_step);
+  m.def("tp_gather_seq", &tp_gather_seq);
+  m.def("tp_reduce_scatter_add", &tp_reduce_scatter_add);
+  m.def("tp_aux_error_word", []() { return (int64_t)rk::tp_aux_error_word(); });
+  m.def("tp_aux_words", []() { return (int64_t)rk::tp_aux_words(); });
   m.def("dp_aux_error_word", &dp_aux_error_word);
   m.def("dp_aux_words", &dp_aux_words);
 }

@@ -117,6 +117,21 @@ void dp_adamw_allgather(const DpPeers& peers, const DpAdamW& a, cudaStream_t st)
 int dp_aux_error_word();
 int dp_aux_words();
 
+// ---- tensor-parallel sequence collectives over symmetric memory ---------------------------
+struct TpPeers {
+  const void* buf[kMaxRanks];  // the same symmetric buffer on every rank (peer-mapped)
+  const void* buf_mc;          // its multicast address, or null without NVSwitch multicast
+  void* aux[kMaxRanks];        // scratch words: barrier counters and the error word
+  int rank, world;
+};
+void tp_barrier(const TpPeers& peers, uint32_t target, cudaStream_t st);
+// out[B, world*Tl, C] (local) <- buf_r[B, Tl, C] of every rank r
+void tp_gather_seq(const TpPeers& peers, void* out, int B, int Tl, int C, cudaStream_t st);
+// out[B, Tl, C] (local) <- residual + sum_r buf_r[B, world*Tl, C] restricted to this rank's time slice; residual may be null
+void tp_reduce_scatter_add(const TpPeers& peers, const void* residual, void* out, int B, int Tl, int C, cudaStream_t st);
+int tp_aux_error_word();
+int tp_aux_words();
+
 // ---- GEMM (tcgen05) -------------------------------------------------------------
 enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
 enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3 };

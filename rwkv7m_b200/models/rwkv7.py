@@ -10,6 +10,7 @@ checkpoint layout (``[in, out]`` kernels, ``[1,1,C]`` vectors) is produced by
 
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -58,6 +59,11 @@ class Linear(nn.Module):
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
         return y
+
+
+def _partial_output(module):
+    tp = getattr(module, "tp", None)
+    return contextlib.nullcontext() if tp is None else tp.partial_output()
 
 
 class RWKV7TimeMix(nn.Module):
@@ -140,7 +146,8 @@ class RWKV7TimeMix(nn.Module):
         y = ops.gn_bonus_gate(
             y.reshape(B, T, C), r, k_mod, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps
         )
-        out = ops.linear(y, self.output.weight)
+        with _partial_output(self):  # tensor parallel: the partial result goes straight into the reduce-scatter buffer
+            out = ops.linear(y, self.output.weight)
         return out, v_first, x[:, -1].float(), final_state
 
 
@@ -157,7 +164,9 @@ class RWKV7ChannelMix(nn.Module):
     def forward(self, x, prev_x):
         (xk,) = ops.shift_mix(x, prev_x, self.x_k.unsqueeze(0))
         h = ops.linear_relu_sq(xk, self.key.weight)
-        return ops.linear(h, self.value.weight), x[:, -1].float()
+        with _partial_output(self):
+            out = ops.linear(h, self.value.weight)
+        return out, x[:, -1].float()
 
 
 class RWKV7Block(nn.Module):
@@ -179,14 +188,11 @@ class RWKV7Block(nn.Module):
         if tp is not None:  # sequence-sharded residual: gather tokens for the column-parallel projections
             h = tp.gather_seq(h)
         att_out, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv)
-        if tp is not None:  # row-parallel output: sum the partial results, keep this rank's tokens
-            att_out = tp.reduce_scatter_seq(att_out)
-        x = x + att_out
+        # row-parallel output: sum the partial results over ranks, keep this rank's tokens, add the residual
+        x = x + att_out if tp is None else tp.reduce_scatter_add(att_out, x)
         h = self.ln2(x)
         if tp is not None:
             h = tp.gather_seq(h)
         ffn_out, cm_x = self.ffn(h, state.channel_mix_x)
-        if tp is not None:
-            ffn_out = tp.reduce_scatter_seq(ffn_out)
-        x = x + ffn_out
+        x = x + ffn_out if tp is None else tp.reduce_scatter_add(ffn_out, x)
         return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)

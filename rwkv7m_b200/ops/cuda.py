@@ -144,6 +144,35 @@ def _gemm_ok(x2, wc):
     )
 
 
+_NEXT_LINEAR_OUT = None
+
+
+class linear_output:
+    """``with linear_output(buf): y = linear(x, w)`` makes the next forward GEMM write its [M, N] bf16 result into
+    ``buf`` (for instance a symmetric-memory buffer that peers read) instead of a fresh allocation."""
+
+    def __init__(self, buf):
+        self.buf = buf
+
+    def __enter__(self):
+        global _NEXT_LINEAR_OUT
+        _NEXT_LINEAR_OUT = self.buf
+        return self
+
+    def __exit__(self, *exc):
+        global _NEXT_LINEAR_OUT
+        _NEXT_LINEAR_OUT = None
+        return False
+
+
+def _take_linear_out(M, N, device):
+    global _NEXT_LINEAR_OUT
+    buf, _NEXT_LINEAR_OUT = _NEXT_LINEAR_OUT, None
+    if buf is not None and buf.numel() >= M * N and buf.dtype == torch.bfloat16 and buf.device == device:
+        return buf.view(-1)[: M * N].view(M, N)
+    return torch.empty(M, N, dtype=torch.bfloat16, device=device)
+
+
 class LinearFn(torch.autograd.Function):
     """y = x @ W^T (optionally relu(.)^2), W stored [out, in].
 
@@ -161,7 +190,7 @@ class LinearFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         M, N = x2.shape[0], wc.shape[0]
-        y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        y = _take_linear_out(M, N, x.device)
         gemm(x2, wc, y, GEMM_TN, EPI_RELUSQ if relu_sq else EPI_BF16)
         ctx.relu_sq = relu_sq
         ctx.weight = w

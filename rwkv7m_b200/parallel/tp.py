@@ -129,6 +129,7 @@ class TensorParallel:
     world: int
     rank: int
     vocab_parallel: bool = False
+    fused: object = None   # FusedSeqCollectives: the framework's own NVLink kernels instead of NCCL
 
     @classmethod
     def from_group(cls, group=None, vocab_parallel=False):
@@ -136,11 +137,43 @@ class TensorParallel:
         return cls(group, dist.get_world_size(group), dist.get_rank(group), vocab_parallel)
 
     # ---- activation collectives ----------------------------------------------
+    def enable_fused(self, max_full_elements: int, device, use_multicast: bool = True):
+        """Route the sequence collectives through the in-kernel NVLink path (bf16 CUDA tensors only)."""
+        from .tp_fused import FusedSeqCollectives
+
+        self.fused = FusedSeqCollectives(self.group, max_full_elements, device, use_multicast)
+        return self.fused
+
+    def _use_fused(self, x):
+        return self.fused is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3
+
     def gather_seq(self, x):
+        if self._use_fused(x):
+            from .tp_fused import _FusedGather
+
+            return _FusedGather.apply(x, self.fused)
         return _GatherSeq.apply(x, self)
 
     def reduce_scatter_seq(self, x):
         return _ReduceScatterSeq.apply(x, self)
+
+    def partial_output(self):
+        """Context manager: the next ``ops.linear`` writes into the symmetric buffer of the coming reduce-scatter."""
+        import contextlib
+
+        if self.fused is None:
+            return contextlib.nullcontext()
+        from ..ops import cuda as K
+
+        return K.linear_output(self.fused.partial_buffer())
+
+    def reduce_scatter_add(self, partial, residual):
+        """residual + reduce-scatter over time of the row-parallel partial result."""
+        if self._use_fused(partial) and residual.dtype == torch.bfloat16:
+            from .tp_fused import _FusedReduceScatterAdd
+
+            return _FusedReduceScatterAdd.apply(partial, residual, self.fused)
+        return residual + _ReduceScatterSeq.apply(partial, self)
 
     def sum_scalar(self, x):
         return _AllReduceSum.apply(x, self.group)
@@ -172,6 +205,8 @@ class TensorParallel:
         model.tp = self
         for layer in model.layers:
             layer.block.tp = self
+            layer.block.att.tp = self
+            layer.block.ffn.tp = self
         return model
 
     def sync_replicated(self, model, src: int = 0):

@@ -44,8 +44,11 @@ def test_tensor_parallel_matches_single_gpu():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
-    for key in ("vp0", "vp1"):
+    for key in ("vp0", "vp1", "fused_mc1", "fused_mc0"):
         r = res[key]
         assert r["rel_l2"] < 3e-3, res
         for a, b in zip(r["loss_ref"], r["loss_tp"]):
             assert abs(a - b) < 1e-2 * abs(a), res
+    for key in ("fused_mc1", "fused_mc0"):   # in-kernel NVLink collectives: multimem.ld_reduce and plain peer loads
+        r = res[key]
+        assert r["gather_exact"] and r["rs_max_err"] < 0.05 and r["error_code"] == 0, res

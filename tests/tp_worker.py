@@ -11,6 +11,12 @@ import torch
 import torch.distributed as dist
 
 
+def _all_gather(x, world):
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x.contiguous())
+    return parts
+
+
 def main():
     rank = int(os.environ["RANK"])
     local = int(os.environ["LOCAL_RANK"])
@@ -44,6 +50,29 @@ def main():
         num = sum(float((ref[n] - got[n]).pow(2).sum()) for n in ref) ** 0.5
         den = sum(float(ref[n].pow(2).sum()) for n in ref) ** 0.5
         out[f"vp{int(vp)}"] = {"rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "norm_ref": n_ref, "norm_tp": n_tp}
+    # the same step with the sequence collectives on this framework's own NVLink kernels
+    for mc in (True, False):
+        tpf = TensorParallel.from_group(vocab_parallel=False)
+        comm = tpf.enable_fused(2 * 64 * 256, dev, use_multicast=mc)
+        # collectives against NCCL first
+        g = torch.Generator().manual_seed(5 + rank)
+        xl = torch.randn(2, 64 // world, 256, generator=g).to(dev).bfloat16()
+        full = comm.gather(xl)
+        ref_full = torch.cat([t for t in _all_gather(xl, world)], dim=1)
+        part = torch.randn(2, 64, 256, generator=g).to(dev).bfloat16()
+        res = torch.randn(2, 64 // world, 256, generator=g).to(dev).bfloat16()
+        got_rs = comm.reduce_scatter_add(part, res)
+        tot = part.float().clone()
+        dist.all_reduce(tot)
+        n = 64 // world
+        want_rs = tot[:, rank * n:(rank + 1) * n] + res.float()
+        got, l_tp, n_tp = run(tpf)
+        num = sum(float((ref[k] - got[k]).pow(2).sum()) for k in ref) ** 0.5
+        den = sum(float(ref[k].pow(2).sum()) for k in ref) ** 0.5
+        out[f"fused_mc{int(mc)}"] = {
+            "rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "multicast_used": bool(comm.use_multicast),
+            "gather_exact": bool(torch.equal(full, ref_full)),
+            "rs_max_err": float((got_rs.float() - want_rs).abs().max()), "error_code": comm.error_code()}
     if rank == 0:
         print(json.dumps(out))
     dist.destroy_process_group()
