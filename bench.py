@@ -40,6 +40,10 @@ def parse_args(argv=None):
     ap.add_argument("--remat", default="auto", choices=["auto", "on", "off"])
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
+                    help="dp: weak scaling, --batch sequences per GPU; tp: tensor parallel over all GPUs, --batch = global batch")
+    ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--vocab-parallel", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
     return ap.parse_args(argv)
@@ -158,7 +162,8 @@ def main(argv=None):
     remat_modes = {"on": [L], "off": [0], "auto": [0, L // 3, (2 * L) // 3, L]}[args.remat]
 
     B, T, V = args.batch, args.seq, cfg.vocab_size
-    gen = torch.Generator().manual_seed(1234 + rank)
+    use_tp = args.parallel == "tp" and world > 1
+    gen = torch.Generator().manual_seed(1234 + (0 if use_tp else rank))  # tensor-parallel ranks share the batch
 
     def make_batch(pinned):
         ids = torch.randint(0, V, (B, T + 1), generator=gen, dtype=torch.int64).to(torch.int32)
@@ -187,13 +192,24 @@ def main(argv=None):
                         print(f"bench: symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL all-reduce",
                               file=sys.stderr)
                     args.dp = "nccl"
+            tp = None
+            if use_tp:
+                from rwkv7m_b200.parallel.tp import TensorParallel
+
+                alloc = None
+                tp = TensorParallel.from_group(vocab_parallel=args.vocab_parallel)
+                if args.tp_comm == "fused":
+                    tp.enable_fused(B * T * cfg.d_model, device)
             runtime, train_state = R.create_train_runtime(
                 7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8,
-                buffer_allocator=alloc,
+                buffer_allocator=alloc, tp=tp,
             )
             train_state.model.remat_layer_count = remat
-            mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
-            trainer = DataParallelTrainer(train_state, mode=mode)
+            if use_tp:
+                trainer = tp   # create_train_runtime installed the tensor-parallel step
+            else:
+                mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
+                trainer = DataParallelTrainer(train_state, mode=mode)
             dev_batches = [make_batch(False) for _ in range(2)]
             for i in range(args.warmup):
                 train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime)
@@ -254,11 +270,11 @@ def main(argv=None):
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_max, e2e_ms_max = float(times[0]), float(times[1])
-    tokens = B * T * world * args.steps
+    tokens = B * T * (1 if use_tp else world) * args.steps
     value = tokens / (ms_max / 1e3)
     if rank == 0:
         line = {
-            "metric": METRIC,
+            "metric": METRIC if (args.model == "1.5b" and T == 4096) else f"train tokens/s/box at {args.model} ctx{T}",
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
@@ -266,16 +282,17 @@ def main(argv=None):
             "warmup": args.warmup,
             "ms_per_step": ms_max / args.steps,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong" if use_tp else "weak",
             "vs_baseline": None,
             "dtype": "bf16",
             "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": {
                 "model": ("REDUCED-LAYERS " if args.layers > 0 else "") + f"rwkv7-{args.model} (d_model {cfg.d_model}, layers {cfg.n_layers}, d_ffn {cfg.ffn_dim}, vocab {V})",
-                "global_batch": B * world,
+                "global_batch": B * (1 if use_tp else world),
                 "seq_len": T,
-                "parallelism": f"dp{world}" + ("" if world == 1 else f"-{args.dp}"),
+                "parallelism": (f"tp{world}-{args.tp_comm}" + ("-vocab" if args.vocab_parallel else "")) if use_tp
+                               else f"dp{world}" + ("" if world == 1 else f"-{args.dp}"),
                 "remat_layers": int(used_remat),
                 "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                 "gemm": args.gemm,
