@@ -123,10 +123,10 @@ def bench_fused(M, C, H, iters=10):
     ln_w, ln_b = par(C), par(C)
     cases.append(("layer_norm", lambda: ops.layer_norm(x, ln_w, ln_b), 2 * act, 3 * act))
     prev, mix = torch.zeros(B, C, device="cuda"), par(6, C)
-    cases.append(("shift_mix6", lambda: torch.stack(ops.shift_mix(x, prev, mix)).sum(0), 7 * act, 7 * act))
+    cases.append(("shift_mix6", lambda: ops.shift_mix(x, prev, mix), 7 * act, 7 * act))
     k, v, wl, al, vl, vf = (bf(B, T, C).requires_grad_(True) for _ in range(6))
     w0, a0, v0, kk_, ka = (par(C) for _ in range(5))
-    cases.append(("tmix_pre", lambda: sum(ops.tmix_pre(k, v, wl, al, vl, vf, w0, a0, v0, kk_, ka, H)), 11 * act, 17 * act))
+    cases.append(("tmix_pre", lambda: ops.tmix_pre(k, v, wl, al, vl, vf, w0, a0, v0, kk_, ka, H), 11 * act, 17 * act))
     y, r, g = (bf(B, T, C).requires_grad_(True) for _ in range(3))
     gw, gb, rk = par(C), par(C), par(H, C // H)
     cases.append(("gn_bonus_gate", lambda: ops.gn_bonus_gate(y, r, k, v, g, gw, gb, rk, H), 6 * act, 11 * act))
@@ -135,10 +135,12 @@ def bench_fused(M, C, H, iters=10):
         with torch.no_grad():
             tf = _time(fn, iters, flush=flush)
         o = fn()
-        dy = torch.randn_like(o)
+        outs = list(o) if isinstance(o, (tuple, list)) else [o]
+        dys = [torch.randn_like(t) for t in outs]
 
         def fb():
-            fn().backward(dy)
+            r = fn()
+            torch.autograd.backward(list(r) if isinstance(r, (tuple, list)) else [r], dys)
 
         tb = _time(fb, iters, flush=flush)
         bwd_ms = max(tb["median_ms"] - tf["median_ms"], 1e-6)

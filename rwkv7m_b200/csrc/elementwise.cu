@@ -20,7 +20,11 @@ using bf162 = __nv_bfloat162;
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
-__device__ __forceinline__ float2 ld2(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const bf162*>(p)); }
+// read-only path: lets the compiler hoist the loads of the next unrolled rows above this row's stores
+__device__ __forceinline__ float2 ld2(const bf16* p) {
+  const unsigned int raw = __ldg(reinterpret_cast<const unsigned int*>(p));
+  return __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw));
+}
 __device__ __forceinline__ void st2(bf16* p, float a, float b) { *reinterpret_cast<bf162*>(p) = __floats2bfloat162_rn(a, b); }
 
 // ---------------------------------------------------------------------------------
@@ -261,6 +265,7 @@ __global__ void tmix_pre_fwd_kernel(TmixPreParams p) {
   float v0a = 0.f, v0b = 0.f;
   if (has_v) { v0a = p.v0[c]; v0b = p.v0[c + 1]; }
   const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+#pragma unroll 1
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
     const float2 k = ld2(p.k_raw + o), v = ld2(p.v_raw + o), wl = ld2(p.w_lora + o), al = ld2(p.a_lora + o);
@@ -297,6 +302,7 @@ __global__ void tmix_pre_bwd_kernel(TmixPreParams p) {
   float gw0a = 0.f, gw0b = 0.f, ga0a = 0.f, ga0b = 0.f, gv0a = 0.f, gv0b = 0.f, gkka = 0.f, gkkb = 0.f, gkaa = 0.f,
         gkab = 0.f;
   const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+#pragma unroll 1
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
     const float2 k = ld2(p.k_raw + o), v = ld2(p.v_raw + o), wl = ld2(p.w_lora + o), al = ld2(p.a_lora + o);
@@ -396,6 +402,7 @@ __global__ void gn_bonus_gate_fwd_kernel(GnParams p) {
   const float lw0 = p.ln_w[c], lw1 = p.ln_w[c + 1], lb0 = p.ln_b[c], lb1 = p.ln_b[c + 1];
   const float rk0 = p.r_k[c], rk1 = p.r_k[c + 1];
   const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+#pragma unroll 4
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
     const float2 y = ld2(p.y + o), r = ld2(p.r + o), k = ld2(p.k + o), v = ld2(p.v + o), g = ld2(p.g + o);
@@ -417,6 +424,7 @@ __global__ void gn_bonus_gate_bwd_kernel(GnParams p) {
   const float rk0 = p.r_k[c], rk1 = p.r_k[c + 1];
   float aw0 = 0.f, aw1 = 0.f, ab0 = 0.f, ab1 = 0.f, ar0 = 0.f, ar1 = 0.f;
   const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+#pragma unroll 1
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
     const float2 y = ld2(p.y + o), r = ld2(p.r + o), k = ld2(p.k + o), v = ld2(p.v + o), g = ld2(p.g + o),
