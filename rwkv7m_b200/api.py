@@ -81,7 +81,20 @@ def create_runtime(rng_key, config, *, batch_size: int = 1, device=None) -> RWKV
     config = load_model_config(config)
     model = initialize_model(_seed(rng_key), config, device=_default_device(device))
     model.eval()
+    _attach_inference_weights(model)
     return _make_runtime(model, config, batch_size)
+
+
+def _attach_inference_weights(model):
+    """Inference on a GPU in bf16: keep one bf16 copy of every matrix next to the fp32 parameter so the GEMMs never
+    re-cast weights per call (training keeps the same copies inside the flat optimizer buffers)."""
+    from .models.model import torch_dtype
+
+    if torch_dtype(model.config.dtype) != torch.bfloat16:
+        return
+    for p in model.parameters():
+        if p.is_cuda and p.dim() == 2 and p.dtype != torch.bfloat16 and getattr(p, "_main_grad", None) is None:
+            p._compute = p.detach().to(torch.bfloat16)
 
 
 def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, device=None,
@@ -103,6 +116,8 @@ def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int =
 def load_runtime_params(runtime: RWKV7MRuntime, params):
     """Load a portable parameter tree (nested or ``/``-joined flat) into the runtime's model."""
     load_params_into_model(runtime.model, params)
+    if not runtime.model.training:
+        _attach_inference_weights(runtime.model)
     runtime.variables = {"params": dict(runtime.model.named_parameters())}
     return runtime
 

@@ -251,7 +251,11 @@ struct TmixPreParams {
   bf16 *dk_raw, *dv_raw, *dw_lora, *da_lora, *dvg_lora, *dv_first;
   float *dw0_part, *da0_part, *dv0_part, *dkk_part, *dka_part;  // [parts, C]
   int M, C;
+  int rows_per_part;  // forward only: rows walked by one block (small for decode-sized M so the grid stays wide)
 };
+
+// Rows per block of the forward head-wise kernels: 128 at training sizes, fewer when there are few rows.
+static int fwd_rows_per_part(int M) { return M >= 16384 ? kRowsPerPart : (M >= 1024 ? 16 : 1); }
 
 __global__ void tmix_pre_fwd_kernel(TmixPreParams p) {
   const int H = p.C / 64;
@@ -264,7 +268,7 @@ __global__ void tmix_pre_fwd_kernel(TmixPreParams p) {
   const bool has_v = p.vg_lora != nullptr;
   float v0a = 0.f, v0b = 0.f;
   if (has_v) { v0a = p.v0[c]; v0b = p.v0[c + 1]; }
-  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  const int r0 = blockIdx.y * p.rows_per_part, r1 = min(p.M, r0 + p.rows_per_part);
 #pragma unroll 1
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
@@ -358,7 +362,8 @@ void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* o
   p.w0 = par[0]; p.a0 = par[1]; p.v0 = par[2]; p.k_k = par[3]; p.k_a = par[4];
   p.w = (bf16*)out[0]; p.k_mod = (bf16*)out[1]; p.v = (bf16*)out[2]; p.neg_kk = (bf16*)out[3]; p.kka = (bf16*)out[4];
   p.M = M; p.C = C;
-  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  p.rows_per_part = fwd_rows_per_part(M);
+  dim3 grid((C / 64 + 7) / 8, (M + p.rows_per_part - 1) / p.rows_per_part);
   tmix_pre_fwd_kernel<<<grid, 256, 0, st>>>(p);
 }
 
@@ -391,6 +396,7 @@ struct GnParams {
   float *dlnw_part, *dlnb_part, *drk_part;
   int M, C;
   float eps;
+  int rows_per_part;  // forward only
 };
 
 __global__ void gn_bonus_gate_fwd_kernel(GnParams p) {
@@ -401,7 +407,7 @@ __global__ void gn_bonus_gate_fwd_kernel(GnParams p) {
   const int c = head * 64 + lane * 2;
   const float lw0 = p.ln_w[c], lw1 = p.ln_w[c + 1], lb0 = p.ln_b[c], lb1 = p.ln_b[c + 1];
   const float rk0 = p.r_k[c], rk1 = p.r_k[c + 1];
-  const int r0 = blockIdx.y * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  const int r0 = blockIdx.y * p.rows_per_part, r1 = min(p.M, r0 + p.rows_per_part);
 #pragma unroll 4
   for (int row = r0; row < r1; ++row) {
     const size_t o = (size_t)row * p.C + c;
@@ -462,7 +468,8 @@ void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out
   p.g = (const bf16*)in[4];
   p.ln_w = par[0]; p.ln_b = par[1]; p.r_k = par[2];
   p.out = (bf16*)out; p.M = M; p.C = C; p.eps = eps;
-  dim3 grid((C / 64 + 7) / 8, row_parts(M));
+  p.rows_per_part = fwd_rows_per_part(M);
+  dim3 grid((C / 64 + 7) / 8, (M + p.rows_per_part - 1) / p.rows_per_part);
   gn_bonus_gate_fwd_kernel<<<grid, 256, 0, st>>>(p);
 }
 

@@ -500,10 +500,13 @@ bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int
   if (fn == nullptr) return false;
   // The driver entry point needs the primary context bound to the calling thread.  A worker
   // thread (e.g. an autograd thread) whose first CUDA action is this call has none yet.
-  {
+  // Done once per thread, so later calls are legal while a stream of this thread is being captured into a graph.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess)
       return false;
+    context_bound = true;
   }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -643,6 +646,8 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   if (p.error_flag == nullptr) return 7;
   // the CTA-pair kernel needs at least one full 256-row tile and a wide N to pay off
   if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair_layout(p, st);
+  // decode-sized problems (one m-tile): narrow n-tiles so that the weight matrix is streamed by many SMs at once
+  if (p.layout == kGemmTN && p.M <= BM && p.N >= 1024) return launch_epi<32, 0, 0>(p, st);
   if (p.N > 128) return launch_layout<256>(p, st);
   return launch_layout<128>(p, st);
 }

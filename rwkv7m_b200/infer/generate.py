@@ -47,8 +47,73 @@ def sample_next(last_logits, temperature, top_p, generator=None):
 
 
 @torch.no_grad()
+def prefill_last(model, prompt_ids, rwkv_state, screen_state, *, phase="read_screening_only"):
+    """Prefill that projects only the last position onto the vocabulary (the [B, T, V] logits of a long
+    prompt are never materialised).  Returns (last logits [B, V], rwkv_state, screen_state)."""
+    model.eval()
+    hidden, rwkv_state, screen_state, _ = model.compute_recurrent_hidden(prompt_ids, rwkv_state, screen_state, phase=phase)
+    return model.compute_logits(hidden[:, -1:])[:, -1, :], rwkv_state, screen_state
+
+
+class GraphDecoder:
+    """One decode step captured in a CUDA graph.
+
+    A T=1 forward of a multi-billion-parameter model is a few thousand short kernels; replaying them from a
+    graph removes the launch gaps.  The token ids, the recurrent state and the logits live in static buffers:
+    ``step(ids)`` copies the ids in, replays, and returns the logits buffer; the new state is copied back into
+    the static state inside the graph.  Models with screening memory fall back to eager decoding.
+    """
+
+    def __init__(self, model, rwkv_state, *, phase="read_screening_only"):
+        from ..state import LayerRWKVState, init_screen_state
+
+        self.model = model
+        self.phase = phase
+        dev = rwkv_state[0].wkv.device
+        B = rwkv_state[0].wkv.shape[0]
+        self.ids = torch.zeros(B, 1, dtype=torch.int32, device=dev)
+        self.state = tuple(LayerRWKVState(s.time_mix_x.clone(), s.channel_mix_x.clone(), s.wkv.clone()) for s in rwkv_state)
+        self.screen = init_screen_state(B, model.config.screening, device=dev)
+        model.eval()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(2):  # warm-up outside capture: builds tensor maps, allocator pools, lazy init
+                self._body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        # warm-up advanced the state: restore it
+        for dst, src in zip(self.state, rwkv_state):
+            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x); dst.wkv.copy_(src.wkv)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.logits = self._body()
+
+    def _body(self):
+        logits, new_state, _, _ = self.model(self.ids, self.state, self.screen, phase=self.phase)
+        for dst, src in zip(self.state, new_state):
+            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x); dst.wkv.copy_(src.wkv)
+        return logits[:, -1, :]
+
+    def load_state(self, rwkv_state):
+        for dst, src in zip(self.state, rwkv_state):
+            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x); dst.wkv.copy_(src.wkv)
+
+    def step(self, ids):
+        self.ids.copy_(ids.view_as(self.ids))
+        self.graph.replay()
+        return self.logits
+
+
+def _graph_ok(model, prompt_ids):
+    cfg = model.config
+    screened = bool(cfg.use_screening and cfg.screening.screened_layers)
+    return (prompt_ids.is_cuda and not screened and getattr(model, "tp", None) is None
+            and next(model.parameters()).dtype is not None)
+
+
+@torch.no_grad()
 def generate(model, prompt_ids, rwkv_state, screen_state, *, max_new_tokens=50, temperature=1.0,
-             top_p=0.9, rng_key=None, phase="read_screening_only"):
+             top_p=0.9, rng_key=None, phase="read_screening_only", use_cuda_graph=None):
     """Returns (new ids [B, max_new_tokens], rwkv_state, screen_state)."""
     if rng_key is None:
         rng_key = 0
@@ -56,9 +121,18 @@ def generate(model, prompt_ids, rwkv_state, screen_state, *, max_new_tokens=50, 
         generator = rng_key
     else:
         generator = torch.Generator().manual_seed(int(torch.as_tensor(rng_key).flatten()[-1].item()))
-    logits, rwkv_state, screen_state, _ = prefill(model, prompt_ids, rwkv_state, screen_state, phase=phase)
-    last = logits[:, -1, :]
+    last, rwkv_state, screen_state = prefill_last(model, prompt_ids, rwkv_state, screen_state, phase=phase)
+    if use_cuda_graph is None:
+        use_cuda_graph = max_new_tokens >= 8 and _graph_ok(model, prompt_ids)
     out = []
+    if use_cuda_graph:
+        dec = GraphDecoder(model, rwkv_state, phase=phase)
+        for _ in range(max_new_tokens):
+            nxt = sample_next(last, temperature, top_p, generator)
+            out.append(nxt)
+            last = dec.step(nxt)
+        rwkv_state = tuple(s.detach() for s in dec.state)
+        return torch.cat(out, dim=1).to(torch.int32), rwkv_state, screen_state
     for _ in range(max_new_tokens):
         nxt = sample_next(last, temperature, top_p, generator)
         out.append(nxt)
