@@ -117,6 +117,40 @@ void dp_adamw_allgather(const DpPeers& peers, const DpAdamW& a, cudaStream_t st)
 int dp_aux_error_word();
 int dp_aux_words();
 
+// ---- screening-memory slot scan -----------------------------------------------------------------------
+struct ScreenScanArgs {
+  int B, T, M, ds, dk, dv;
+  // inputs (fp32)
+  const float *q_r, *q_w;       // [B,T,dk]; q_w unused without write screening
+  const float* delta_xh;        // [B,T,ds]
+  const float* delta_slot;      // [M,ds]
+  const float* slot_embed;      // [M,ds]
+  const float* WT;              // [ds][J]  transposed concatenation of k_proj_r | v_proj | k_proj_w, J = dk + dv + dk
+  const float* W;               // [J][ds]  the same weights, untransposed (backward)
+  const float* mu;              // [M] per-slot write rate
+  const float *slots0, *ages0, *usage0;   // [B,M,ds], [B,M], [B,M]
+  float tau_r, tau_w, eps, cap, write_rel_floor, usage_decay, age_ref, age_sigma;
+  bool write_enabled, value_unit_norm, age_mask;
+  // forward outputs
+  float* u_out;                 // [B,T,dv]
+  float *slots_out, *ages_out, *usage_out;
+  float* stats;                 // [9] running sums over batch rows and steps
+  float* saved_slots;           // [B,T,ds,16] bank before each step (nullptr = inference)
+  float* saved_ages;            // [B,T,16]
+  // backward
+  const float* du;              // [B,T,dv]
+  const float* dslots_out;      // [B,M,ds] or nullptr
+  float *d_q_r, *d_q_w, *d_delta_xh;      // [B,T,dk], [B,T,dk], [B,T,ds]
+  float* d_proj;                // [B,T,16,J] cotangent of the raw projections
+  float* d_delta_slot;          // [M,ds]  accumulated with atomics (zeroed by the caller)
+  float* d_slots0;              // [B,M,ds]
+  float* d_mu;                  // [M]     atomics
+  float* d_scalars;             // [2]     d tau_r, d tau_w (atomics)
+};
+bool screen_scan_supported(const ScreenScanArgs& a);
+int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st);
+int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st);
+
 // ---- tensor-parallel sequence collectives over symmetric memory ---------------------------
 struct TpPeers {
   const void* buf[kMaxRanks];  // the same symmetric buffer on every rank (peer-mapped)

@@ -18,7 +18,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parents[1]
 CSRC = PKG / "csrc"
 EXT_NAME = "_C"
-SOURCES = ["bindings.cpp", "wkv7.cu", "wkv7_chunk.cu", "wkv7_chunk_bwd.cu", "optim.cu", "gemm_sm100.cu", "elementwise.cu", "loss.cu", "dp_fused.cu", "tp_fused.cu", "noalloc.cu"]
+SOURCES = ["bindings.cpp", "wkv7.cu", "wkv7_chunk.cu", "wkv7_chunk_bwd.cu", "optim.cu", "gemm_sm100.cu", "elementwise.cu", "loss.cu", "screening.cu", "dp_fused.cu", "tp_fused.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--use_fast_math",
     "-std=c++17", "--expt-relaxed-constexpr", "-Xptxas", "-v",

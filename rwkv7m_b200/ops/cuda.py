@@ -512,10 +512,95 @@ def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
     return totals
 
 
+class ScreenScanFn(torch.autograd.Function):
+    """Slot scan of the screening memory (csrc/screening.cu).  Differentiable inputs: q_r, q_w, delta_xh,
+    delta_slot, slot_embed, the three projection weights, mu, tau_r, tau_w and the initial slots."""
+
+    @staticmethod
+    def forward(ctx, q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, tau_r, tau_w, slots0, ages0,
+                usage0, settings):
+        f32 = lambda t: t.detach().float().contiguous()
+        W = torch.cat([f32(w_kr), f32(w_v), f32(w_kw)], dim=0).contiguous()
+        WT = W.t().contiguous()
+        floats = [float(tau_r), float(tau_w), settings["eps"], settings["cap"], settings["floor"],
+                  settings["usage_decay"], settings["age_ref"], settings["age_sigma"]]
+        flags = (bool(settings["write_enabled"]), bool(settings["value_unit_norm"]), bool(settings["age_mask"]))
+        tensors = [f32(q_r), f32(q_w), f32(delta_xh), f32(delta_slot), f32(slot_embed), WT, W, f32(mu),
+                   f32(slots0), f32(ages0), f32(usage0)]
+        need_grad = any(ctx.needs_input_grad)
+        u, so, ao, uo, stats, saved, saved_ages = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad)
+        _count()
+        ctx.floats, ctx.flags = floats, flags
+        ctx.dk, ctx.dv, ctx.M = w_kr.shape[0], w_v.shape[0], slots0.shape[1]
+        ctx.dtypes = [t.dtype for t in (q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, slots0)]
+        if need_grad:
+            ctx.save_for_backward(*tensors, saved, saved_ages)
+        ctx.mark_non_differentiable(ao, uo, stats)
+        return u, so, ao, uo, stats
+
+    @staticmethod
+    def backward(ctx, du, dso, *_):
+        *tensors, saved, saved_ages = ctx.saved_tensors
+        dqr, dqw, dxh, dds, ds0, dmu, dsc, dproj = _C.screen_scan_bwd(
+            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, du.float().contiguous(), dso)
+        _count()
+        slot_embed, W = tensors[4], tensors[6]
+        dk, dv, M = ctx.dk, ctx.dv, ctx.M
+        B, T, ds, _ = saved.shape
+        J = W.shape[0]
+        # weight gradients: one GEMM over all (batch, step, slot) rows of the projection cotangents
+        P2 = dproj.reshape(B * T * 16, J)
+        S2 = saved.permute(0, 1, 3, 2).reshape(B * T * 16, ds)
+        dW = P2.t() @ S2
+        psum = dproj.sum(dim=(0, 1))[:M]                      # [M, J]
+        kw = slice(dk + dv, J)
+        dW[kw] += psum[:, kw].t() @ slot_embed                 # the write keys see S + E
+        dE = psum[:, kw] @ W[kw]
+        dt = ctx.dtypes
+        grads = [dqr.to(dt[0]), dqw.to(dt[1]) if ctx.flags[0] else None, dxh.to(dt[2]), dds.to(dt[3]), dE.to(dt[4]),
+                 dW[:dk].to(dt[5]), dW[dk:dk + dv].to(dt[6]), dW[kw].to(dt[7]) if ctx.flags[0] else None, dmu.to(dt[8]),
+                 dsc[0], dsc[1] if ctx.flags[0] else None, ds0.to(dt[9]), None, None, None]
+        return tuple(grads)
+
+
+def _screen_kernel_ok(mod, q_r, h_base, write_enabled):
+    cfg = mod.config
+    ds, dk, dv, M = cfg.d_slot, cfg.d_k, cfg.d_v, cfg.n_slots
+    return (not cfg.use_leaky_warmup and M <= 16 and ds in (16, 32, 64, 128, 256) and 2 * dk + dv <= 256
+            and dk <= 256 and dv <= 256 and q_r.is_cuda)
+
+
 def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars):
     from ..models.screening import screening_scan_reference
 
-    return screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars)
+    write_enabled = bool(scalars["write_enabled"])
+    if not _screen_kernel_ok(mod, q_r, h_base, write_enabled):
+        return screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars)
+    from ..state import LayerScreenState
+
+    cfg = mod.config
+    tau_r, tau_w, lam, mu = scalars["tau_r"], scalars["tau_w"], scalars["lam"], scalars["mu"]
+    compute = h_base.dtype
+    if write_enabled:
+        w_kw, qw = mod.k_proj_w.weight, q_w
+    else:
+        w_kw, qw = torch.zeros_like(mod.k_proj_r.weight), torch.zeros_like(q_r)
+    settings = {"eps": cfg.eps, "cap": cfg.tanh_norm_cap, "floor": cfg.write_rel_floor, "usage_decay": cfg.usage_ema_decay,
+                "age_ref": cfg.age_ref, "age_sigma": cfg.age_sigma, "write_enabled": write_enabled,
+                "value_unit_norm": cfg.use_value_unit_norm, "age_mask": cfg.use_age_mask}
+    u, slots, ages, usage, st = ScreenScanFn.apply(
+        q_r, qw, delta_xh, delta_slot, mod.slot_embed, mod.k_proj_r.weight, mod.v_proj.weight, w_kw, mu,
+        tau_r, tau_w if write_enabled else torch.zeros((), device=q_r.device), state.slots, state.ages, state.usage_ema,
+        settings)
+    read_out = linear(u.to(compute), mod.out_proj.weight)
+    h_seq = (h_base + (lam * gate * read_out.float()).to(compute)).to(compute)
+    n = float(q_r.shape[0] * q_r.shape[1])
+    sv = (st / n).detach()
+    stats = {"rel_read_mean": sv[0], "rel_read_max": sv[1], "active_slots_mean": sv[2], "z_norm_mean": sv[3],
+             "u_norm_mean": sv[4], "rel_write_mean": sv[5], "rel_write_effective_mean": sv[6],
+             "slot_update_norm_mean": sv[7], "slot_usage_ema_mean": sv[8],
+             "tau_r": tau_r.detach(), "lambda_screen": lam.detach(), "tau_w": tau_w.detach()}
+    return h_seq, LayerScreenState(slots=slots, ages=ages, usage_ema=usage), stats
 
 
 # ---------------------------------------------------------------------------
