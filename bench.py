@@ -44,6 +44,8 @@ def parse_args(argv=None):
                     help="dp: weak scaling, --batch sequences per GPU; tp: tensor parallel over all GPUs, --batch = global batch")
     ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--vocab-parallel", action="store_true")
+    ap.add_argument("--screening", action="store_true",
+                    help="enable the screening memory of the 0.185b preset (read/write phase, carry-state streaming)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
     return ap.parse_args(argv)
@@ -157,6 +159,17 @@ def main(argv=None):
         cfg = bench_config(args.model)
     if args.layers > 0:
         cfg.n_layers = args.layers
+    phase, carry = "read_screening_only", False
+    if args.screening:
+        import copy
+
+        from rwkv7m_b200.config import model_preset
+
+        scr = copy.deepcopy(model_preset("0.185b").screening)
+        scr.d_model = cfg.d_model
+        scr.screened_layers = tuple(l for l in scr.screened_layers if l < cfg.n_layers) or (cfg.n_layers // 2,)
+        cfg.use_screening, cfg.screening = True, scr
+        phase, carry = "read_write", True
     cfg.head_chunk_size = max(1, 8192 // args.batch)
     L = cfg.n_layers
     remat_modes = {"on": [L], "off": [0], "auto": [0, L // 3, (2 * L) // 3, L]}[args.remat]
@@ -212,7 +225,7 @@ def main(argv=None):
                 trainer = DataParallelTrainer(train_state, mode=mode)
             dev_batches = [make_batch(False) for _ in range(2)]
             for i in range(args.warmup):
-                train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime)
+                train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime, phase=phase, carry_state=carry)
             torch.cuda.synchronize()
             used_remat = remat
             break
@@ -242,7 +255,7 @@ def main(argv=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime)
+        train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime, phase=phase, carry_state=carry)
     e1.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
@@ -259,7 +272,8 @@ def main(argv=None):
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for i in range(args.steps):
-            train_state, metrics = R.train_batch(train_state, host_batches[i % len(host_batches)], runtime)
+            train_state, metrics = R.train_batch(train_state, host_batches[i % len(host_batches)], runtime,
+                                                 phase=phase, carry_state=carry)
             loss_host = float(metrics["loss"])  # device -> host read of the step result
         f1.record()
         sync_all()
@@ -294,6 +308,7 @@ def main(argv=None):
                 "parallelism": (f"tp{world}-{args.tp_comm}" + ("-vocab" if args.vocab_parallel else "")) if use_tp
                                else f"dp{world}" + ("" if world == 1 else f"-{args.dp}"),
                 "remat_layers": int(used_remat),
+                "screening": ("read_write, carry-state, slots %d x %d" % (cfg.screening.n_slots, cfg.screening.d_slot)) if args.screening else "off",
                 "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                 "gemm": args.gemm,
                 "master_weights": "fp32", "adam_moments": "fp32",
