@@ -51,6 +51,8 @@ from .ops import wkv7
 from .ops.reference import wkv7 as wkv7_reference
 from .state import LayerRWKVState, LayerScreenState, ModelScreenState, init_rwkv_state, init_screen_state
 from .tokenizer import RWKVTokenizer, tokenizer_metadata
+from .train.train_loop import run_toy_training
+from .train.train_step import generate_toy_batch, initialize_train_state, train_step
 
 __version__ = "0.1.0"
 
