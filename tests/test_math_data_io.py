@@ -159,4 +159,5 @@ def test_scaling_planner_divides_by_model_axis():
     assert summ.total == sum(p.numel() for p in R.create_runtime(0, cfg).model.parameters())
     one = estimate_training_memory(cfg, DTypePolicy.stability(), model_axis_size=1)
     four = estimate_training_memory(cfg, DTypePolicy.stability(), model_axis_size=4)
-    assert four.optimizer_state_bytes == math.ceil(one.optimizer_state_bytes / 4)
+    assert four.global_estimated_bytes == one.global_estimated_bytes
+    assert four.per_device_estimated_bytes == math.ceil(one.per_device_estimated_bytes / 4)
