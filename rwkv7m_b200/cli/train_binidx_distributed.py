@@ -89,6 +89,11 @@ def parse_args(argv=None):
     p.add_argument("--param-axis-name", default=None)
     p.add_argument("--dp-mode", choices=["fused", "allreduce"], default="allreduce")
     p.add_argument("--device", default="auto")
+    p.add_argument("--collective-timeout-s", type=float, default=600.0,
+                   help="process-group timeout: a rank that stops answering ends the others' next collective with an error")
+    p.add_argument("--inject-failure-step", type=int, default=None,
+                   help="failure drill (host side): raise on --inject-failure-rank before this optimizer step")
+    p.add_argument("--inject-failure-rank", type=int, default=0)
     return parse_args_with_config(p, argv)
 
 
@@ -211,7 +216,7 @@ def _empty(cfg):
 
 
 def run_distributed_training(args):
-    info = initialize_distributed()
+    info = initialize_distributed(timeout_s=args.collective_timeout_s)
     rank, world = info["process_index"], info["process_count"]
     mesh = make_mesh(tuple(args.mesh_axis_names), args.mesh_axis_sizes, world_size=world)
     if mesh.model_size != 1:
@@ -318,6 +323,9 @@ def run_distributed_training(args):
                                                           prefetch_size=args.prefetch_size):
             if args.carry_state and dataset.should_reset_state_before_step(step):
                 runtime.rwkv_state, runtime.screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
+            if args.inject_failure_step is not None and step == args.inject_failure_step and rank == args.inject_failure_rank:
+                # between steps, nothing in flight: the other ranks learn of it through the collective timeout
+                raise RuntimeError(f"injected failure on rank {rank} before step {step}")
             if use_cuda:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()

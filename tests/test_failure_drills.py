@@ -1,0 +1,84 @@
+"""Failure drills made on the host: a rank that raises between steps, a truncated checkpoint, and a peer that never
+signals a device-side barrier (bounded wait -> error word)."""
+
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from rwkv7m_b200.cli import train_binidx_distributed as trainer
+from rwkv7m_b200.parallel.audit import audit_distributed_run
+
+TINY = ["--d-model", "32", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64",
+        "--vocab-size", "300", "--no-screening"]
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_rank_failure_marks_run_failed_and_resume_recovers(tiny_binidx, tmp_path):
+    out = tmp_path / "drill"
+    common = ["--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2", "--print-every", "0",
+              "--output-dir", str(out), "--save-every", "1", "--summary-every", "1", "--device", "cpu"] + TINY
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), "-m", "rwkv7m_b200.cli.train_binidx_distributed", "--steps", "6",
+           "--collective-timeout-s", "8", "--inject-failure-step", "3", "--inject-failure-rank", "1"] + common
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=str(ROOT))
+    assert res.returncode != 0
+    summary = json.loads((out / "run_summary.json").read_text())
+    assert summary["status"] == "failed" and summary["error_type"] and summary["completed_steps"] == 3
+    rep = audit_distributed_run(out, require_complete=True)
+    assert not rep.ok and "summary_not_completed" in {i.code for i in rep.issues}
+    # recovery = resume from the last good checkpoint in a fresh single-process run
+    last = sorted(p for p in out.iterdir() if p.name.startswith("ckpt-"))[-1]
+    assert last.name == "ckpt-00000003"
+    ts, _, s2 = trainer.run_distributed_training(trainer.parse_args(["--steps", "2", "--resume", str(last)] + common))
+    assert s2["status"] == "completed" and int(ts.step) == 5
+    assert audit_distributed_run(out, require_complete=True).ok
+
+
+def test_truncated_checkpoint_is_flagged_and_refused(tiny_binidx, tmp_path):
+    out = tmp_path / "trunc"
+    argv = ["--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2", "--steps", "2", "--print-every", "0",
+            "--output-dir", str(out), "--save-every", "1", "--device", "cpu"] + TINY
+    trainer.run_distributed_training(trainer.parse_args(argv))
+    ckpt = out / "ckpt-00000002"
+    blob = (ckpt / "train_state.safetensors").read_bytes()
+    (ckpt / "train_state.safetensors").write_bytes(blob[: len(blob) // 3])
+    with pytest.raises(Exception):
+        trainer.run_distributed_training(trainer.parse_args(argv[:6] + ["--steps", "1"] + argv[8:] + ["--resume", str(ckpt)]))
+    (ckpt / "model.safetensors").write_bytes(b"")
+    codes = {i.code for i in audit_distributed_run(out).issues}
+    assert "checkpoint_file_empty" in codes
+
+
+@pytest.mark.gpu
+def test_device_barrier_wait_is_bounded_and_reports():
+    """A peer that never arrives: the barrier kernel gives up after its time limit, writes the error word and the
+    context stays usable (the wait is on a flag nothing sets; no fault, no trap)."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    dev = torch.device("cuda", 0)
+    aux0 = torch.zeros(C.tp_aux_words(), dtype=torch.int32, device=dev)
+    aux1 = torch.zeros(C.tp_aux_words(), dtype=torch.int32, device=dev)      # stands in for the silent peer's scratch
+    x = torch.randn(1, 4, 64, device=dev).bfloat16()
+    out = torch.empty(1, 8, 64, device=dev, dtype=torch.bfloat16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    C.tp_gather_seq([x.data_ptr(), x.data_ptr()], [aux0.data_ptr(), aux1.data_ptr()], 0, 1, out, 1, 4, 64)
+    e1.record()
+    torch.cuda.synchronize()
+    assert 1000.0 < e0.elapsed_time(e1) < 10000.0                           # waited about two seconds, then returned
+    assert int(aux0[C.tp_aux_error_word()].item()) == (0x50000 | 1)          # "peer 1 never arrived"
+    assert torch.equal(out[:, :4], x) and float(torch.ones(4, device=dev).sum()) == 4.0   # context still healthy
