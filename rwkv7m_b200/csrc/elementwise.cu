@@ -240,7 +240,7 @@ void shift_mix_bwd(const void* const* dout, const void* x, const float* prev, co
 // 8 warps covers 8 heads; blocks walk kRowsPerBlock rows so per-channel parameter
 // gradients accumulate in registers before the partial write.
 // ---------------------------------------------------------------------------------
-constexpr int kRowsPerPart = 128;
+constexpr int kRowsPerPart = 64;
 
 struct TmixPreParams {
   const bf16 *k_raw, *v_raw, *w_lora, *a_lora, *vg_lora, *v_first;  // vg_lora / v_first null on layer 0
@@ -353,6 +353,127 @@ __global__ void tmix_pre_bwd_kernel(TmixPreParams p) {
   if (has_v) { p.dv0_part[po] = gv0a; p.dv0_part[po + 1] = gv0b; }
 }
 
+// ---- wide variants: one block walks whole rows, thread = 8 consecutive channels (16-byte accesses), the 8 lanes of a
+//      head reduce with three shuffles; per-channel parameter gradients stay in registers over the block's rows ----------
+__device__ __forceinline__ void ld8(const bf16* p, float (&x)[8]) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&w[i]));
+    x[2 * i] = f.x; x[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void st8(bf16* p, const float (&x)[8]) {
+  uint4 o;
+  bf162 h;
+  h = __floats2bfloat162_rn(x[0], x[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(x[2], x[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(x[4], x[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2bfloat162_rn(x[6], x[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+__device__ __forceinline__ float head_sum8(float v) {   // sum over the 8 lanes that hold one 64-channel head
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+__global__ void __launch_bounds__(256, 1) tmix_pre_bwd_wide_kernel(TmixPreParams p) {
+  const int c = threadIdx.x * 8;
+  float w0[8], a0[8], kk_[8], ka[8], v0[8];
+  float gw0[8], ga0[8], gkk[8], gka[8], gv0[8];
+  const bool has_v = p.vg_lora != nullptr;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    w0[j] = p.w0[c + j]; a0[j] = p.a0[c + j]; kk_[j] = p.k_k[c + j]; ka[j] = p.k_a[c + j];
+    v0[j] = has_v ? p.v0[c + j] : 0.f;
+    gw0[j] = ga0[j] = gkk[j] = gka[j] = gv0[j] = 0.f;
+  }
+  const int r0 = blockIdx.x * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  // software pipeline: the raw 16-byte pieces of the next row are in flight while this row is processed
+  uint4 nx[11];
+  auto fetch = [&](int row) {
+    const size_t o = (size_t)row * p.C + c;
+    nx[0] = __ldg(reinterpret_cast<const uint4*>(p.k_raw + o)); nx[1] = __ldg(reinterpret_cast<const uint4*>(p.v_raw + o));
+    nx[2] = __ldg(reinterpret_cast<const uint4*>(p.w_lora + o)); nx[3] = __ldg(reinterpret_cast<const uint4*>(p.a_lora + o));
+    nx[4] = __ldg(reinterpret_cast<const uint4*>(p.dw + o)); nx[5] = __ldg(reinterpret_cast<const uint4*>(p.dk_mod + o));
+    nx[6] = __ldg(reinterpret_cast<const uint4*>(p.dv + o)); nx[7] = __ldg(reinterpret_cast<const uint4*>(p.dneg_kk + o));
+    nx[8] = __ldg(reinterpret_cast<const uint4*>(p.dkka + o));
+    if (has_v) {
+      nx[9] = __ldg(reinterpret_cast<const uint4*>(p.vg_lora + o)); nx[10] = __ldg(reinterpret_cast<const uint4*>(p.v_first + o));
+    }
+  };
+  auto cvt = [](const uint4& raw, float (&x)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&w[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    }
+  };
+  if (r0 < r1) fetch(r0);
+#pragma unroll 1
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    float k[8], v[8], wl[8], al[8], gw[8], gk[8], gv[8], gn[8], gb[8];
+    cvt(nx[0], k); cvt(nx[1], v); cvt(nx[2], wl); cvt(nx[3], al); cvt(nx[4], gw); cvt(nx[5], gk); cvt(nx[6], gv);
+    cvt(nx[7], gn); cvt(nx[8], gb);
+    float vg[8], vf[8];
+    if (has_v) { cvt(nx[9], vg); cvt(nx[10], vf); }
+    if (row + 1 < r1) fetch(row + 1);
+    float out[8], aa[8], x[8], dkk[8];
+    // decay
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { out[j] = gw[j] * sigmoidf_(-(w0[j] + wl[j])); gw0[j] += out[j]; }
+    st8(p.dw_lora + o, out);
+    // key normalisation
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { aa[j] = sigmoidf_(a0[j] + al[j]); x[j] = k[j] * kk_[j]; ss = fmaf(x[j], x[j], ss); }
+    const float inv = rsqrtf(head_sum8(ss) + 1e-24f);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { x[j] *= inv; dkk[j] = -gn[j] + gb[j] * aa[j]; dot = fmaf(dkk[j], x[j], dot); }
+    dot = head_sum8(dot);
+    float dal[8], dkr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float dx = (dkk[j] - x[j] * dot) * inv;
+      gkk[j] += dx * k[j];
+      const float da = gk[j] * k[j] * ka[j] + gb[j] * x[j];
+      dal[j] = da * aa[j] * (1.f - aa[j]);
+      ga0[j] += dal[j];
+      gka[j] += gk[j] * k[j] * (aa[j] - 1.f);
+      dkr[j] = dx * kk_[j] + gk[j] * (1.f + (aa[j] - 1.f) * ka[j]);
+    }
+    st8(p.da_lora + o, dal);
+    st8(p.dk_raw + o, dkr);
+    // value residual
+    if (has_v) {
+      float dvr[8], dvf[8], dvg[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = sigmoidf_(v0[j] + vg[j]);
+        dvr[j] = gv[j] * (1.f - g);
+        dvf[j] = gv[j] * g;
+        dvg[j] = gv[j] * (vf[j] - v[j]) * g * (1.f - g);
+        gv0[j] += dvg[j];
+      }
+      st8(p.dv_raw + o, dvr); st8(p.dv_first + o, dvf); st8(p.dvg_lora + o, dvg);
+    } else {
+      st8(p.dv_raw + o, gv);
+    }
+  }
+  const size_t po = (size_t)blockIdx.x * p.C + c;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    p.dw0_part[po + j] = gw0[j]; p.da0_part[po + j] = ga0[j]; p.dkk_part[po + j] = gkk[j]; p.dka_part[po + j] = gka[j];
+    if (has_v) p.dv0_part[po + j] = gv0[j];
+  }
+}
+
 int row_parts(int M) { return (M + kRowsPerPart - 1) / kRowsPerPart; }
 
 void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* out, int M, int C, cudaStream_t st) {
@@ -380,6 +501,10 @@ void tmix_pre_bwd(const void* const* in, const float* const* par, const void* co
   p.dw0_part = gpar_part[0]; p.da0_part = gpar_part[1]; p.dv0_part = gpar_part[2]; p.dkk_part = gpar_part[3];
   p.dka_part = gpar_part[4];
   p.M = M; p.C = C;
+  if (C % 64 == 0 && C / 8 <= 256 && (C / 8) % 32 == 0) {
+    tmix_pre_bwd_wide_kernel<<<row_parts(M), C / 8, 0, st>>>(p);
+    return;
+  }
   dim3 grid((C / 64 + 7) / 8, row_parts(M));
   tmix_pre_bwd_kernel<<<grid, 256, 0, st>>>(p);
 }
