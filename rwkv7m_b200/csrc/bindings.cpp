@@ -563,6 +563,29 @@ void tp_reduce_scatter_add(const std::vector<int64_t>& buf, int64_t buf_mc, cons
   rk::tp_reduce_scatter_add(p, res, out.data_ptr(), (int)B, (int)Tl, (int)C, stream());
 }
 
+// Row-parallel GEMM fused with the reduce-scatter over time: barrier (every owner initialised its output buffer),
+// y = x W^T with the scatter-add epilogue pushing each tile into its owner's buffer over NVLink, barrier (all pushes
+// landed).  `scatter` is a device-resident rk::GemmScatter (int64 words: 8 pointers, world | T << 32, Tl).
+void tp_gemm_reduce_scatter(const Tensor& x2, const Tensor& w, const Tensor& scatter, int64_t ldd,
+                            const std::vector<int64_t>& buf, const std::vector<int64_t>& aux, int64_t rank,
+                            int64_t target_before, int64_t pair) {
+  c10::cuda::CUDAGuard guard(x2.device());
+  TORCH_CHECK(x2.is_cuda() && x2.is_contiguous() && x2.scalar_type() == at::kBFloat16 && x2.dim() == 2);
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1 && w.size(1) == x2.size(1));
+  TORCH_CHECK(scatter.is_cuda() && scatter.scalar_type() == at::kLong && scatter.numel() >= 10);
+  rk::TpPeers peers = make_tp_peers(buf, 0, aux, rank);
+  rk::tp_barrier(peers, (uint32_t)target_before, stream());
+  rk::GemmArgs p{};
+  p.A = x2.data_ptr(); p.B = w.data_ptr(); p.D = scatter.data_ptr();
+  p.M = (int)x2.size(0); p.K = (int)x2.size(1); p.N = (int)w.size(0);
+  p.lda = (int)x2.stride(0); p.ldb = (int)w.stride(0); p.ldd = (int)ldd;
+  p.layout = rk::kGemmTN; p.epilogue = rk::kEpiScatterAddBf16; p.pair = (int)pair;
+  p.error_flag = gemm_error_flag(x2.device()).data_ptr<int>();
+  const int rc = rk::gemm_bf16(p, stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 (scatter epilogue) launch failed with code ", rc);
+  rk::tp_barrier(peers, (uint32_t)target_before + 1, stream());
+}
+
 int64_t dp_aux_error_word() { return rk::dp_aux_error_word(); }
 int64_t dp_aux_words() { return rk::dp_aux_words(); }
 
@@ -608,6 +631,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("screen_scan_fwd", &screen_scan_fwd);
   m.def("screen_scan_bwd", &screen_scan_bwd);
   m.def("tp_gather_seq", &tp_gather_seq);
+  m.def("tp_gemm_reduce_scatter", &tp_gemm_reduce_scatter);
   m.def("tp_reduce_scatter_add", &tp_reduce_scatter_add);
   m.def("tp_aux_error_word", []() { return (int64_t)rk::tp_aux_error_word(); });
   m.def("tp_aux_words", []() { return (int64_t)rk::tp_aux_words(); });

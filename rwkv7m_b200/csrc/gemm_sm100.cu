@@ -67,6 +67,29 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __restrict__ Dptr, int row, int col0, int M,
                                             int N, int ldd) {
+  if (EPI == kEpiScatterAddBf16) {
+    // Reduce-scatter over time fused into the epilogue: the row belongs to the rank that owns its time slice; the
+    // partial result is added straight into that rank's output buffer (peer memory over NVLink, bf16x2 atomics).
+    if (row < M && col0 + 32 <= N) {
+      const GemmScatter* sc = reinterpret_cast<const GemmScatter*>(Dptr);
+      const int T = sc->T, Tl = sc->Tl;
+      const int bi = row / T, t = row - bi * T;
+      const int owner = t / Tl;
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(sc->out[owner]) + ((size_t)bi * Tl + (t - owner * Tl)) * ldd + col0;
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(out + 8 * j), "r"(pk[4 * j]),
+                     "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]), "r"(pk[4 * j + 3])
+                     : "memory");
+    }
+    return;
+  }
   if (row < M && col0 < N) {
           if (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + (size_t)row * ldd + col0;
@@ -641,6 +664,13 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(p.A) & 15) || (reinterpret_cast<uintptr_t>(p.B) & 15) ||
       (reinterpret_cast<uintptr_t>(p.D) & 15) || (p.lda & 7) || (p.ldb & 7))
     return 6;
+  if (p.epilogue == kEpiScatterAddBf16) {
+    // D is a device-resident GemmScatter; ldd is the row pitch of the per-rank output buffers
+    if (p.layout != kGemmTN || (p.N & 31) || (p.ldd & 7)) return 6;
+    if (p.error_flag == nullptr) return 7;
+    if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair<0, 0, kEpiScatterAddBf16>(p, st);
+    return launch<256, 0, 0, kEpiScatterAddBf16>(p, st);
+  }
   const bool out_bf16 = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16;
   if (p.ldd & (out_bf16 ? 7 : 3)) return 6;
   if (p.error_flag == nullptr) return 7;

@@ -168,7 +168,13 @@ int tp_aux_words();
 
 // ---- GEMM (tcgen05) -------------------------------------------------------------
 enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
-enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3 };
+enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3, kEpiScatterAddBf16 = 4 };
+// Target of the kEpiScatterAddBf16 epilogue (GEMM -> reduce-scatter over time in one kernel): rows are [B, T] tokens,
+// rank r owns tokens [r*Tl, (r+1)*Tl) of every batch row and receives them in out[r] laid out [B, Tl, N].
+struct GemmScatter {
+  void* out[kMaxRanks];
+  int world, T, Tl, pad;
+};
 struct GemmArgs {
   // D[M,N] = A (M x K) * B (K x N) with fp32 accumulation.
   //  layout kGemmTN      : A stored [M,K] row-major, B stored [N,K] row-major      (y = x W^T)

@@ -61,9 +61,11 @@ class Linear(nn.Module):
         return y
 
 
-def _partial_output(module):
+def _row_parallel_linear(module, x, weight):
+    """Output projection of a sub-block.  Under tensor parallelism the result is a partial sum over ranks: it is
+    either written straight into the reduce-scatter buffer or deferred so that the GEMM itself can scatter it."""
     tp = getattr(module, "tp", None)
-    return contextlib.nullcontext() if tp is None else tp.partial_output()
+    return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight)
 
 
 class RWKV7TimeMix(nn.Module):
@@ -146,8 +148,7 @@ class RWKV7TimeMix(nn.Module):
         y = ops.gn_bonus_gate(
             y.reshape(B, T, C), r, k_mod, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps
         )
-        with _partial_output(self):  # tensor parallel: the partial result goes straight into the reduce-scatter buffer
-            out = ops.linear(y, self.output.weight)
+        out = _row_parallel_linear(self, y, self.output.weight)
         return out, v_first, x[:, -1].float(), final_state
 
 
@@ -164,8 +165,7 @@ class RWKV7ChannelMix(nn.Module):
     def forward(self, x, prev_x):
         (xk,) = ops.shift_mix(x, prev_x, self.x_k.unsqueeze(0))
         h = ops.linear_relu_sq(xk, self.key.weight)
-        with _partial_output(self):
-            out = ops.linear(h, self.value.weight)
+        out = _row_parallel_linear(self, h, self.value.weight)
         return out, x[:, -1].float()
 
 

@@ -121,6 +121,13 @@ class _ReduceScatterSeq(torch.autograd.Function):
         return _all_gather_time(g, tp.group, tp.world), None
 
 
+class _DeferredLinear:
+    """A row-parallel projection whose GEMM is launched by the reduce-scatter that consumes it."""
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+
+
 @dataclass
 class TensorParallel:
     """Model-parallel context attached to a sharded model (``model.tp``)."""
@@ -137,11 +144,13 @@ class TensorParallel:
         return cls(group, dist.get_world_size(group), dist.get_rank(group), vocab_parallel)
 
     # ---- activation collectives ----------------------------------------------
-    def enable_fused(self, max_full_elements: int, device, use_multicast: bool = True):
-        """Route the sequence collectives through the in-kernel NVLink path (bf16 CUDA tensors only)."""
+    def enable_fused(self, max_full_elements: int, device, use_multicast: bool = True, gemm_epilogue_scatter: bool = True):
+        """Route the sequence collectives through the in-kernel NVLink path (bf16 CUDA tensors only).  With
+        ``gemm_epilogue_scatter`` the row-parallel GEMMs push their tiles to the owning rank from the epilogue."""
         from .tp_fused import FusedSeqCollectives
 
         self.fused = FusedSeqCollectives(self.group, max_full_elements, device, use_multicast)
+        self.gemm_epilogue_scatter = bool(gemm_epilogue_scatter)
         return self.fused
 
     def _use_fused(self, x):
@@ -157,18 +166,29 @@ class TensorParallel:
     def reduce_scatter_seq(self, x):
         return _ReduceScatterSeq.apply(x, self)
 
-    def partial_output(self):
-        """Context manager: the next ``ops.linear`` writes into the symmetric buffer of the coming reduce-scatter."""
-        import contextlib
+    def row_parallel_linear(self, x, weight):
+        """x @ weight^T where ``weight`` is this rank's input-channel shard: a partial sum over the group."""
+        from .. import ops
 
-        if self.fused is None:
-            return contextlib.nullcontext()
-        from ..ops import cuda as K
+        if self._use_fused(x) and weight.shape[0] % 32 == 0:
+            from ..ops import cuda as K
 
-        return K.linear_output(self.fused.partial_buffer())
+            if getattr(self, "gemm_epilogue_scatter", False):
+                return _DeferredLinear(x, weight)           # executed by reduce_scatter_add, collective in the epilogue
+            with K.linear_output(self.fused.partial_buffer()):
+                return ops.linear(x, weight)
+        return ops.linear(x, weight)
 
     def reduce_scatter_add(self, partial, residual):
         """residual + reduce-scatter over time of the row-parallel partial result."""
+        if isinstance(partial, _DeferredLinear):
+            from .tp_fused import _FusedLinearReduceScatterAdd
+
+            if residual.dtype == torch.bfloat16:
+                return _FusedLinearReduceScatterAdd.apply(partial.x, partial.weight, residual, self.fused)
+            from .. import ops
+
+            partial = ops.linear(partial.x, partial.weight)
         if self._use_fused(partial) and residual.dtype == torch.bfloat16:
             from .tp_fused import _FusedReduceScatterAdd
 

@@ -43,14 +43,18 @@ class FusedSeqCollectives:
         mk = lambda n, dt: symm.empty(n, dtype=dt, device=device)
         self.xbuf = [mk(self.capacity // self.world, torch.bfloat16) for _ in range(2)]
         self.pbuf = [mk(self.capacity, torch.bfloat16) for _ in range(2)]
+        self.obuf = [mk(self.capacity // self.world, torch.bfloat16) for _ in range(2)]   # owners' reduce-scatter outputs
         self.aux = mk(self._C.tp_aux_words(), torch.int32)
         self.aux.zero_()
-        for t in self.xbuf + self.pbuf:
+        for t in self.xbuf + self.pbuf + self.obuf:
             t.zero_()
         torch.cuda.synchronize()
         self.hx = [symm.rendezvous(t, self.group) for t in self.xbuf]
         self.hp = [symm.rendezvous(t, self.group) for t in self.pbuf]
+        self.ho = [symm.rendezvous(t, self.group) for t in self.obuf]
         self.haux = symm.rendezvous(self.aux, self.group)
+        self.oi = 0
+        self._scatter_desc = {}
         self.use_multicast = bool(use_multicast) and all(int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in self.hp)
         self.barriers = 0
         self.gi = 0
@@ -102,6 +106,71 @@ class FusedSeqCollectives:
         self._C.tp_reduce_scatter_add(self._ptrs(self.hp[i]), int(self.hp[i].multicast_ptr) if self.use_multicast else 0,
                                       self._ptrs(self.haux), self.rank, self.barriers, res, out, B, Tl, C)
         return out
+
+
+    # ---- row-parallel GEMM with the reduce-scatter in its epilogue --------------------------------------------------
+    def gemm_reduce_scatter(self, x2, wc, residual, B, T):
+        """x2 [B*T, K] bf16, wc [C, K] bf16 (this rank's input-channel shard), residual [B, T/w, C] -> residual + the
+        reduce-scatter over time of x2 wc^T.  Every output tile leaves the GEMM epilogue as bf16x2 atomic adds into
+        the owner rank's buffer over NVLink, so the transfer overlaps the remaining tiles."""
+        from ..ops import cuda as K
+
+        C = wc.shape[0]
+        Tl = T // self.world
+        n = B * Tl * C
+        if n * self.world > self.capacity or T % self.world != 0 or C % 32 != 0:
+            raise ValueError("shape does not fit the symmetric buffers")
+        i = self.oi
+        self.oi ^= 1
+        ob = self.obuf[i][:n].view(B, Tl, C)
+        ob.copy_(residual)                                   # owners start from the residual; peers add into it
+        key = (i, T, Tl)
+        if key not in self._scatter_desc:
+            words = self._ptrs(self.ho[i]) + [0] * (8 - self.world) + [self.world | (T << 32), Tl]
+            self._scatter_desc[key] = torch.tensor(words, dtype=torch.int64, device=x2.device)
+        self._C.tp_gemm_reduce_scatter(x2, wc, self._scatter_desc[key], C, self._ptrs(self.ho[i]), self._ptrs(self.haux),
+                                       self.rank, self.barriers + 1, int(K.GEMM_PAIR))
+        self.barriers += 2
+        K._count(3)
+        return ob.clone()                                    # the symmetric buffer is reused two collectives later
+
+
+class _FusedLinearReduceScatterAdd(torch.autograd.Function):
+    """residual + reduce_scatter_time(x @ W^T) with the collective inside the GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual, comm):
+        from ..ops import cuda as K
+
+        wc = K._compute_weight(w)
+        B, T, Kd = x.shape
+        x2 = x.reshape(B * T, Kd)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        out = comm.gemm_reduce_scatter(x2, wc, residual.contiguous(), B, T)
+        ctx.comm, ctx.weight, ctx.x_shape = comm, w, x.shape
+        ctx.save_for_backward(x2, wc)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops import cuda as K
+
+        x2, wc = ctx.saved_tensors
+        w = ctx.weight
+        g = g.contiguous()
+        dy2 = ctx.comm.gather(g).reshape(-1, wc.shape[0])     # all-gather over time of the output cotangent
+        dx = torch.empty(x2.shape, dtype=torch.bfloat16, device=g.device)
+        K.gemm(dy2, wc, dx, K.GEMM_NN, K.EPI_BF16)
+        dw = None
+        main = getattr(w, "_main_grad", None)
+        if main is not None and main.dtype == torch.float32:
+            K.gemm(dy2, x2, main, K.GEMM_WGRAD, K.EPI_ACC_F32)
+        else:
+            dw32 = torch.empty(wc.shape, dtype=torch.float32, device=g.device)
+            K.gemm(dy2, x2, dw32, K.GEMM_WGRAD, K.EPI_F32)
+            dw = dw32.to(w.dtype)
+        return dx.view(ctx.x_shape), dw, g, None
 
 
 class _FusedGather(torch.autograd.Function):

@@ -52,3 +52,4 @@ def test_tensor_parallel_matches_single_gpu():
     for key in ("fused_mc1", "fused_mc0"):   # in-kernel NVLink collectives: multimem.ld_reduce and plain peer loads
         r = res[key]
         assert r["gather_exact"] and r["rs_max_err"] < 0.05 and r["error_code"] == 0, res
+        assert r["gemm_rs_max_err"] < 0.02 * r["gemm_rs_scale"] + 0.05, res

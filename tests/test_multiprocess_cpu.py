@@ -59,6 +59,7 @@ def _dp_worker(rank, world, port, out):
         losses.append(float(m["loss"]))
     if rank == 0:
         torch.save({"params": {n: p.detach().clone() for n, p in ts.model.named_parameters()}, "losses": losses}, out)
+    dist.barrier()   # leave together: a rank that tears gloo down while its peer is still in a collective aborts
     dist.destroy_process_group()
 
 
@@ -77,6 +78,7 @@ def _tp_worker(rank, world, port, out, vocab_parallel):
     logits, _ = R.infer_prefill(rt, batch["input_ids"])
     if rank == 0:
         torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "logits": logits}, out)
+    dist.barrier()   # leave together: a rank that tears gloo down while its peer is still in a collective aborts
     dist.destroy_process_group()
 
 

@@ -51,9 +51,9 @@ def main():
         den = sum(float(ref[n].pow(2).sum()) for n in ref) ** 0.5
         out[f"vp{int(vp)}"] = {"rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "norm_ref": n_ref, "norm_tp": n_tp}
     # the same step with the sequence collectives on this framework's own NVLink kernels
-    for mc in (True, False):
+    for mc, push in ((True, True), (False, False)):
         tpf = TensorParallel.from_group(vocab_parallel=False)
-        comm = tpf.enable_fused(2 * 64 * 256, dev, use_multicast=mc)
+        comm = tpf.enable_fused(2 * 64 * 256, dev, use_multicast=mc, gemm_epilogue_scatter=push)
         # collectives against NCCL first
         g = torch.Generator().manual_seed(5 + rank)
         xl = torch.randn(2, 64 // world, 256, generator=g).to(dev).bfloat16()
@@ -69,7 +69,15 @@ def main():
         got, l_tp, n_tp = run(tpf)
         num = sum(float((ref[k] - got[k]).pow(2).sum()) for k in ref) ** 0.5
         den = sum(float(ref[k].pow(2).sum()) for k in ref) ** 0.5
+        # GEMM with the reduce-scatter in its epilogue against all-reduce + slice
+        xg = torch.randn(2, 64, 128, generator=g).to(dev).bfloat16()
+        wg = torch.randn(256, 128, generator=g).to(dev).bfloat16() * 0.1
+        got_g = comm.gemm_reduce_scatter(xg.reshape(128, 128), wg, res, 2, 64)
+        tot_g = (xg.float() @ wg.float().t())
+        dist.all_reduce(tot_g)
+        want_g = tot_g[:, rank * n:(rank + 1) * n] + res.float()
         out[f"fused_mc{int(mc)}"] = {
+            "gemm_rs_max_err": float((got_g.float() - want_g).abs().max()), "gemm_rs_scale": float(want_g.abs().max()),
             "rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "multicast_used": bool(comm.use_multicast),
             "gather_exact": bool(torch.equal(full, ref_full)),
             "rs_max_err": float((got_rs.float() - want_rs).abs().max()), "error_code": comm.error_code()}
