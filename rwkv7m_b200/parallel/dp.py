@@ -38,7 +38,25 @@ class DataParallelTrainer:
         if mode == "fused":
             from .fused_dp import FusedShardedAdamW
 
-            self.fused = FusedShardedAdamW(train_state.optimizer, group=group)
+            # every rank must take the same path: agree on whether the symmetric-memory setup worked everywhere
+            failure = None
+            try:
+                self.fused = FusedShardedAdamW(train_state.optimizer, group=group)
+            except Exception as exc:  # no peer access / multicast / symmetric allocator on this box
+                failure = exc
+            flag = torch.tensor([0 if failure is None else 1], dtype=torch.int32,
+                                device=train_state.optimizer.flat.master.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+            if int(flag.item()) != 0:
+                if self.fused is not None or train_state.optimizer.exp_avg is None:
+                    raise RuntimeError("fused data parallelism failed on some ranks after the optimizer state was "
+                                       "re-sharded; cannot fall back") from failure
+                if self.rank == 0:
+                    import sys
+
+                    print(f"fused data parallelism unavailable ({failure!r}); using the NCCL all-reduce path", file=sys.stderr)
+                self.fused = None
+                self.mode = "allreduce"
         if self.world > 1:
             self.broadcast_parameters()
         train_state.extras["train_step"] = self.train_step
