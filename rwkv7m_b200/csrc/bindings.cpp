@@ -214,7 +214,7 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   check_par(w, C, "weight"); check_par(mean, M, "mean"); check_par(rstd, M, "rstd");
   TORCH_CHECK(dy.numel() == x.numel());
   Tensor dx = torch::empty_like(x);
-  int parts = (int)std::min<int64_t>(64, std::max<int64_t>(1, M / 256));
+  int parts = (int)std::min<int64_t>(148 * 2, std::max<int64_t>(1, M / 64));   // blocks of the backward grid
   auto f32 = x.options().dtype(at::kFloat);
   Tensor dwp = torch::empty({parts, C}, f32), dbp = torch::empty({parts, C}, f32);
   rk::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),

@@ -113,6 +113,116 @@ __global__ void layernorm_bwd_wb_kernel(const bf16* __restrict__ dy, const bf16*
   }
 }
 
+// dx in one pass: one warp per row with 16-byte accesses keeps the row of dy and x in registers, so nothing is read twice.
+template <int NCH>   // C = NCH * 256
+__global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                     const float* __restrict__ w, const float* __restrict__ mean,
+                                                                     const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                                                     float* __restrict__ dw_part, float* __restrict__ db_part,
+                                                                     int M) {
+  constexpr int C = NCH * 256;
+  __shared__ float s_w[C];
+  for (int c = threadIdx.x; c < C; c += 256) s_w[c] = w[c];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_per = (M + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per, r1 = min(M, r0 + rows_per);
+  for (int row = r0 + warp; row < r1; row += 8) {
+    const bf16* gr = dy + (size_t)row * C + lane * 8;
+    const bf16* xr = x + (size_t)row * C + lane * 8;
+    uint4 graw[NCH], xraw[NCH];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      graw[i] = __ldg(reinterpret_cast<const uint4*>(gr + i * 256));
+      xraw[i] = __ldg(reinterpret_cast<const uint4*>(xr + i * 256));
+    }
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
+      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
+      const float* wp = s_w + i * 256 + lane * 8;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+        const float g0 = g.x * wp[2 * j], g1 = g.y * wp[2 * j + 1];
+        s1 += g0 + g1;
+        s2 = fmaf(g0, (v.x - mu) * rs, s2);
+        s2 = fmaf(g1, (v.y - mu) * rs, s2);
+      }
+    }
+    s1 = warp_sum(s1) * (1.f / C);
+    s2 = warp_sum(s2) * (1.f / C);
+    bf16* dr = dx + (size_t)row * C + lane * 8;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
+      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
+      const int cb = i * 256 + lane * 8;
+      uint4 o;
+      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+        const float xh0 = (v.x - mu) * rs, xh1 = (v.y - mu) * rs;
+        bf162 h = __floats2bfloat162_rn(rs * (g.x * s_w[cb + 2 * j] - s1 - xh0 * s2), rs * (g.y * s_w[cb + 2 * j + 1] - s1 - xh1 * s2));
+        op[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dr + i * 256) = o;
+    }
+  }
+}
+
+// dw / db partial sums with 16-byte accesses: thread = 8 consecutive channels, block row p sums the rows of part p.
+__global__ void __launch_bounds__(256) layernorm_bwd_wb_wide_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                    float* __restrict__ dw_part, float* __restrict__ db_part,
+                                                                    int M, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int rows_per = (M + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rows_per, r1 = min(M, r0 + rows_per);
+  float aw[8], ab[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { aw[j] = 0.f; ab[j] = 0.f; }
+#pragma unroll 4
+  for (int r = r0; r < r1; ++r) {
+    const uint4 graw = __ldg(reinterpret_cast<const uint4*>(dy + (size_t)r * C + c));
+    const uint4 xraw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * C + c));
+    const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
+    const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw);
+    const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+      aw[2 * j] = fmaf(g.x, (v.x - mu) * rs, aw[2 * j]); aw[2 * j + 1] = fmaf(g.y, (v.y - mu) * rs, aw[2 * j + 1]);
+      ab[2 * j] += g.x; ab[2 * j + 1] += g.y;
+    }
+  }
+  float* dwp = dw_part + (size_t)blockIdx.y * C + c;
+  float* dbp = db_part + (size_t)blockIdx.y * C + c;
+  *reinterpret_cast<float4*>(dwp) = make_float4(aw[0], aw[1], aw[2], aw[3]);
+  *reinterpret_cast<float4*>(dwp + 4) = make_float4(aw[4], aw[5], aw[6], aw[7]);
+  *reinterpret_cast<float4*>(dbp) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+  *reinterpret_cast<float4*>(dbp + 4) = make_float4(ab[4], ab[5], ab[6], ab[7]);
+}
+
+template <int NCH>
+static void launch_ln_bwd_fused(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                                float* dw_part, float* db_part, int parts, int M, cudaStream_t st) {
+  int blocks = (M + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  layernorm_bwd_fused_kernel<NCH><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, dw_part,
+                                                          db_part, M);
+  constexpr int C = NCH * 256;
+  dim3 grid((C / 8 + 255) / 256, parts);
+  layernorm_bwd_wb_wide_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
+}
+
 void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int M, int C,
                    float eps, cudaStream_t st) {
   int blocks = (M + 7) / 8;
@@ -122,6 +232,14 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
 
 void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
                    float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st) {
+  switch (C) {   // single-pass kernel for the common widths
+    case 256: return launch_ln_bwd_fused<1>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    case 512: return launch_ln_bwd_fused<2>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    case 768: return launch_ln_bwd_fused<3>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    case 1024: return launch_ln_bwd_fused<4>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    case 2048: return launch_ln_bwd_fused<8>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    default: break;
+  }
   int blocks = (M + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
   layernorm_bwd_dx_kernel<<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, M, C);
@@ -212,6 +330,107 @@ __global__ void shift_mix_bwd_kernel(ShiftGrads<K> dout, const bf16* __restrict_
   }
 }
 
+// Wide variant of the backward: thread = 4 consecutive channels (8-byte accesses), the loads of the next (earlier)
+// token are issued before the current one is processed.
+__device__ __forceinline__ void ld4(const bf16* p, float (&x)[4]) {
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.y));
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+
+template <int K>
+__global__ void __launch_bounds__(128) shift_mix_bwd_wide_kernel(ShiftGrads<K> dout, const bf16* __restrict__ x,
+                                                                 const float* __restrict__ prev, const float* __restrict__ mix,
+                                                                 bf16* __restrict__ dx, float* __restrict__ dprev,
+                                                                 float* __restrict__ dmix_part, int B, int T, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * kShiftSeg;
+  const int t1 = min(T, t0 + kShiftSeg);
+  float m[K][4], acc[K][4];
+#pragma unroll
+  for (int z = 0; z < K; ++z)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { m[z][j] = mix[z * C + c + j]; acc[z][j] = 0.f; }
+  float carry[4] = {0.f, 0.f, 0.f, 0.f};   // sum_z dout_z[t+1] * mix_z
+  if (t1 < T) {
+    const size_t o = ((size_t)b * T + t1) * C + c;
+#pragma unroll
+    for (int z = 0; z < K; ++z) {
+      float g[4];
+      ld4(dout.p[z] + o, g);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) carry[j] = fmaf(g[j], m[z][j], carry[j]);
+    }
+  }
+  float cur[4], g[K][4], pv[4];
+  ld4(x + ((size_t)b * T + t1 - 1) * C + c, cur);
+  {
+    const size_t o = ((size_t)b * T + t1 - 1) * C + c;
+#pragma unroll
+    for (int z = 0; z < K; ++z) ld4(dout.p[z] + o, g[z]);
+    if (t1 - 1 == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pv[j] = prev[(size_t)b * C + c + j];
+    } else {
+      ld4(x + o - C, pv);
+    }
+  }
+  for (int t = t1 - 1; t >= t0; --t) {
+    const size_t o = ((size_t)b * T + t) * C + c;
+    float gn[K][4], pn[4];
+    const bool more = t - 1 >= t0;
+    if (more) {   // next iteration's token (t - 1): gradients and its predecessor
+#pragma unroll
+      for (int z = 0; z < K; ++z) ld4(dout.p[z] + o - C, gn[z]);
+      if (t - 1 == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pn[j] = prev[(size_t)b * C + c + j];
+      } else {
+        ld4(x + o - 2 * (size_t)C, pn);
+      }
+    }
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, n[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int z = 0; z < K; ++z)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gv = g[z][j];
+        s[j] = fmaf(gv, 1.f - m[z][j], s[j]);
+        n[j] = fmaf(gv, m[z][j], n[j]);
+        acc[z][j] = fmaf(gv, pv[j] - cur[j], acc[z][j]);
+      }
+    {
+      bf162 h0 = __floats2bfloat162_rn(s[0] + carry[0], s[1] + carry[1]);
+      bf162 h1 = __floats2bfloat162_rn(s[2] + carry[2], s[3] + carry[3]);
+      uint2 o2;
+      o2.x = *reinterpret_cast<uint32_t*>(&h0); o2.y = *reinterpret_cast<uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(dx + o) = o2;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { carry[j] = n[j]; cur[j] = pv[j]; }
+    if (more) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pv[j] = pn[j];
+#pragma unroll
+      for (int z = 0; z < K; ++z)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) g[z][j] = gn[z][j];
+    }
+  }
+  if (t0 == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dprev[(size_t)b * C + c + j] = carry[j];
+  }
+  const int part = blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+  for (int z = 0; z < K; ++z)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dmix_part[((size_t)part * K + z) * C + c + j] = acc[z][j];
+}
+
 int shift_mix_parts(int B, int T) { return B * ((T + kShiftSeg - 1) / kShiftSeg); }
 
 void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out, int K, int B, int T, int C,
@@ -224,6 +443,19 @@ void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out
 void shift_mix_bwd(const void* const* dout, const void* x, const float* prev, const float* mix, void* dx,
                    float* dprev, float* dmix_part, int K, int B, int T, int C, cudaStream_t st) {
   dim3 block(128), grid((C / 2 + 127) / 128, (T + kShiftSeg - 1) / kShiftSeg, B);
+  if (C % 4 == 0) {   // 8-byte accesses
+    dim3 gridw((C / 4 + 127) / 128, (T + kShiftSeg - 1) / kShiftSeg, B);
+    if (K == 6) {
+      ShiftGrads<6> g;
+      for (int z = 0; z < 6; ++z) g.p[z] = (const bf16*)dout[z];
+      shift_mix_bwd_wide_kernel<6><<<gridw, block, 0, st>>>(g, (const bf16*)x, prev, mix, (bf16*)dx, dprev, dmix_part, B, T, C);
+    } else {
+      ShiftGrads<1> g;
+      g.p[0] = (const bf16*)dout[0];
+      shift_mix_bwd_wide_kernel<1><<<gridw, block, 0, st>>>(g, (const bf16*)x, prev, mix, (bf16*)dx, dprev, dmix_part, B, T, C);
+    }
+    return;
+  }
   if (K == 6) {
     ShiftGrads<6> g;
     for (int z = 0; z < 6; ++z) g.p[z] = (const bf16*)dout[z];
