@@ -131,6 +131,7 @@ def bench_fused(M, C, H, iters=10):
     gw, gb, rk = par(C), par(C), par(H, C // H)
     cases.append(("gn_bonus_gate", lambda: ops.gn_bonus_gate(y, r, k, v, g, gw, gb, rk, H), 6 * act, 11 * act))
     out = []
+    leaves = [x, ln_w, ln_b, mix, k, v, wl, al, vl, vf, w0, a0, v0, kk_, ka, y, r, g, gw, gb, rk]
     for name, fn, fwd_bytes, bwd_bytes in cases:
         with torch.no_grad():
             tf = _time(fn, iters, flush=flush)
@@ -139,6 +140,8 @@ def bench_fused(M, C, H, iters=10):
         dys = [torch.randn_like(t) for t in outs]
 
         def fb():
+            for t in leaves:          # no gradient-accumulation kernels in the timed region
+                t.grad = None
             r = fn()
             torch.autograd.backward(list(r) if isinstance(r, (tuple, list)) else [r], dys)
 

@@ -818,6 +818,79 @@ __global__ void gn_bonus_gate_bwd_kernel(GnParams p) {
   p.drk_part[po] = ar0; p.drk_part[po + 1] = ar1;
 }
 
+// Wide variants (thread = 8 consecutive channels, 8 lanes per head, next row's pieces in flight while this row is processed).
+__global__ void __launch_bounds__(256, 2) gn_bonus_gate_bwd_wide_kernel(GnParams p) {
+  const int c = threadIdx.x * 8;
+  float lw[8], lb[8], rk[8], aw[8], ab[8], ar[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { lw[j] = p.ln_w[c + j]; lb[j] = p.ln_b[c + j]; rk[j] = p.r_k[c + j]; aw[j] = ab[j] = ar[j] = 0.f; }
+  const int r0 = blockIdx.x * kRowsPerPart, r1 = min(p.M, r0 + kRowsPerPart);
+  uint4 nx[6];
+  auto fetch = [&](int row) {
+    const size_t o = (size_t)row * p.C + c;
+    nx[0] = __ldg(reinterpret_cast<const uint4*>(p.y + o)); nx[1] = __ldg(reinterpret_cast<const uint4*>(p.r + o));
+    nx[2] = __ldg(reinterpret_cast<const uint4*>(p.k + o)); nx[3] = __ldg(reinterpret_cast<const uint4*>(p.v + o));
+    nx[4] = __ldg(reinterpret_cast<const uint4*>(p.g + o)); nx[5] = __ldg(reinterpret_cast<const uint4*>(p.dout + o));
+  };
+  auto cvt = [](const uint4& raw, float (&x)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&w[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    }
+  };
+  if (r0 < r1) fetch(r0);
+#pragma unroll 1
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    float y[8], r[8], k[8], v[8], g[8], go[8];
+    cvt(nx[0], y); cvt(nx[1], r); cvt(nx[2], k); cvt(nx[3], v); cvt(nx[4], g); cvt(nx[5], go);
+    if (row + 1 < r1) fetch(row + 1);
+    float sy = 0.f, srk = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sy += y[j]; srk = fmaf(r[j] * k[j], rk[j], srk); }
+    const float mu = head_sum8(sy) * (1.f / 64.f);
+    const float s = head_sum8(srk);
+    float sv = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { y[j] -= mu; sv = fmaf(y[j], y[j], sv); }
+    const float rs = rsqrtf(head_sum8(sv) * (1.f / 64.f) + p.eps);
+    float dp[8], xh[8], out[8];
+    float dsum = 0.f, m1 = 0.f, m2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      xh[j] = y[j] * rs;
+      const float pre = xh[j] * lw[j] + lb[j] + s * v[j];
+      out[j] = go[j] * pre;                       // d gate
+      dp[j] = go[j] * g[j];
+      dsum = fmaf(dp[j], v[j], dsum);
+      const float dxn = dp[j] * lw[j];
+      m1 += dxn; m2 = fmaf(dxn, xh[j], m2);
+      aw[j] = fmaf(dp[j], xh[j], aw[j]); ab[j] += dp[j];
+    }
+    st8(p.dg + o, out);
+    const float ds = head_sum8(dsum);
+    m1 = head_sum8(m1) * (1.f / 64.f);
+    m2 = head_sum8(m2) * (1.f / 64.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = dp[j] * s;
+    st8(p.dv + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { out[j] = ds * k[j] * rk[j]; ar[j] = fmaf(ds * r[j], k[j], ar[j]); }
+    st8(p.dr + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = ds * r[j] * rk[j];
+    st8(p.dk + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = rs * (dp[j] * lw[j] - m1 - xh[j] * m2);
+    st8(p.dy + o, out);
+  }
+  const size_t po = (size_t)blockIdx.x * p.C + c;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { p.dlnw_part[po + j] = aw[j]; p.dlnb_part[po + j] = ab[j]; p.drk_part[po + j] = ar[j]; }
+}
+
 void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out, int M, int C, float eps,
                        cudaStream_t st) {
   GnParams p{};
@@ -840,6 +913,10 @@ void gn_bonus_gate_bwd(const void* const* in, const float* const* par, const voi
   p.dy = (bf16*)gin[0]; p.dr = (bf16*)gin[1]; p.dk = (bf16*)gin[2]; p.dv = (bf16*)gin[3]; p.dg = (bf16*)gin[4];
   p.dlnw_part = gpar_part[0]; p.dlnb_part = gpar_part[1]; p.drk_part = gpar_part[2];
   p.M = M; p.C = C; p.eps = eps;
+  if (C % 64 == 0 && C / 8 <= 256 && (C / 8) % 32 == 0) {
+    gn_bonus_gate_bwd_wide_kernel<<<row_parts(M), C / 8, 0, st>>>(p);
+    return;
+  }
   dim3 grid((C / 64 + 7) / 8, row_parts(M));
   gn_bonus_gate_bwd_kernel<<<grid, 256, 0, st>>>(p);
 }
