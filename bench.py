@@ -42,7 +42,8 @@ def parse_args(argv=None):
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
                     help="dp: weak scaling, --batch sequences per GPU; tp: tensor parallel over all GPUs, --batch = global batch")
-    ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--tp-comm", default="fused", choices=["fused", "fused-separate", "nccl"],
+                    help="fused: reduce-scatter inside the GEMM epilogue; fused-separate: GEMM then one NVLink reduce kernel")
     ap.add_argument("--vocab-parallel", action="store_true")
     ap.add_argument("--screening", action="store_true",
                     help="enable the screening memory of the 0.185b preset (read/write phase, carry-state streaming)")
@@ -211,8 +212,8 @@ def main(argv=None):
 
                 alloc = None
                 tp = TensorParallel.from_group(vocab_parallel=args.vocab_parallel)
-                if args.tp_comm == "fused":
-                    tp.enable_fused(B * T * cfg.d_model, device)
+                if args.tp_comm != "nccl":
+                    tp.enable_fused(B * T * cfg.d_model, device, gemm_epilogue_scatter=args.tp_comm == "fused")
             runtime, train_state = R.create_train_runtime(
                 7, cfg, batch_size=B, total_steps=10_000, device=device, shard_multiple=max(world, 1) * 8,
                 buffer_allocator=alloc, tp=tp,
