@@ -174,9 +174,60 @@ def bench_optimizer(n, iters=10):
             {"kernel": "adamw_flat", "n": n, "ms": ta["median_ms"], "gbs": (4 * 4 * 2 + 2) * n / ta["median_ms"] / 1e6}]
 
 
+def bench_loss(M, C, V, iters=5):
+    """Chunked LM head + cross-entropy + L2Wrap (final LayerNorm, head GEMM, ce_fwd / ce_bwd kernels), forward+backward."""
+    from rwkv7m_b200 import ops
+
+    hidden = (torch.randn(8, M // 8, C, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    ln_w, ln_b = torch.ones(C, device="cuda", requires_grad=True), torch.zeros(C, device="cuda", requires_grad=True)
+    head = (torch.randn(V, C, device="cuda") * 0.02).requires_grad_(True)
+    head._compute = head.detach().bfloat16()
+    targets = torch.randint(0, V, (8, M // 8), device="cuda", dtype=torch.int32)
+
+    def fb():
+        for t in (hidden, ln_w, ln_b, head):
+            t.grad = None
+        ce, cnt, l2, l2c = ops.head_loss(hidden, ln_w, ln_b, head, targets, None, chunk=max(1, 8192 // 8))
+        (ce / cnt + l2 / l2c).backward()
+
+    t = _time(fb, iters)
+    flops = 3 * 2.0 * M * C * V
+    return [{"kernel": "head_loss fwd+bwd", "M": M, "C": C, "V": V, "ms": t["median_ms"], "tflops": flops / t["median_ms"] / 1e9}]
+
+
+def bench_screening(B, T, iters=3):
+    """Screening slot scan (0.185b preset sizes: 16 slots x 128, d_k = d_v = 64), read/write phase, forward and backward."""
+    from rwkv7m_b200.config import model_preset
+    from rwkv7m_b200.models.screening import StateLevelScreening
+    from rwkv7m_b200.state import LayerScreenState
+
+    cfg = model_preset("0.185b").screening
+    mod = StateLevelScreening(cfg).cuda()
+    C = cfg.d_model
+    x = torch.randn(B, T, C, device="cuda").requires_grad_(True)
+    h = torch.randn(B, T, C, device="cuda")
+    st = LayerScreenState(torch.zeros(B, cfg.n_slots, cfg.d_slot, device="cuda"), torch.zeros(B, cfg.n_slots, device="cuda"),
+                          torch.zeros(B, cfg.n_slots, device="cuda"))
+
+    def fwd():
+        with torch.no_grad():
+            mod(x, h, st, phase="read_write")
+
+    def fb():
+        x.grad = None
+        for p in mod.parameters():
+            p.grad = None
+        out, _, _ = mod(x, h, st, phase="read_write")
+        out.sum().backward()
+
+    tf, tb = _time(fwd, iters), _time(fb, iters)
+    return [{"kernel": "screening layer (fp32 module, slot scan kernels)", "B": B, "T": T, "slots": cfg.n_slots, "d_slot": cfg.d_slot,
+             "fwd_ms": tf["median_ms"], "fwd_bwd_ms": tb["median_ms"], "us_per_step_fwd": 1e3 * tf["median_ms"] / T}]
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="wkv,gemm", help="comma list of wkv, gemm, fused, optim")
+    ap.add_argument("--what", default="wkv,gemm", help="comma list of wkv, gemm, fused, optim, loss, screening")
     ap.add_argument("--gemm-shape", default=None, help="M,N,K of a single GEMM case")
     ap.add_argument("--wkv-shape", default=None, help="T,B,H,N of a single WKV case")
     ap.add_argument("--wkv-impl", choices=["chunked", "sequential"], default=None)
@@ -203,6 +254,10 @@ def main(argv=None):
         results += bench_gemm(shapes, iters=args.iters)
     if "fused" in args.what:
         results += bench_fused(8192 if args.small else 32768, 2048, 32, iters=args.iters)
+    if "loss" in args.what:
+        results += bench_loss(4096 if args.small else 32768, 2048, 65536, iters=min(args.iters, 5))
+    if "screening" in args.what:
+        results += bench_screening(8, 256 if args.small else 4096, iters=min(args.iters, 3))
     if "optim" in args.what:
         results += bench_optimizer((64 if args.small else 512) * 1024 * 1024, iters=args.iters)
     for r in results:

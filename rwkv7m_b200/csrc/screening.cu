@@ -66,15 +66,16 @@ __host__ __device__ inline int scan_smem_floats(int ds, int dk, int dv) {
 }
 
 // raw projections of all slots: P[m][j] = sum_d St[d][m] * WT[d][j]  (+ EW for the write keys)
-__device__ __forceinline__ void project(const ScanSmem& s, const float* __restrict__ WT, int ds, int J, int dk, int dv,
-                                        int tid, bool add_ew) {
+template <bool SMEM_W>
+__device__ __forceinline__ void project(const ScanSmem& s, const float* __restrict__ WT, int wstride, int ds, int J, int dk,
+                                        int dv, int tid, bool add_ew) {
   if (tid < J) {
     float acc[kMp];
 #pragma unroll
     for (int m = 0; m < kMp; ++m) acc[m] = 0.f;
 #pragma unroll 4
     for (int d = 0; d < ds; ++d) {
-      const float w = __ldg(WT + (size_t)d * J + tid);
+      const float w = SMEM_W ? WT[d * wstride + tid] : __ldg(WT + (size_t)d * wstride + tid);
       const float4* sp = reinterpret_cast<const float4*>(s.St + d * kMp);
       const float4 a = sp[0], b = sp[1], c = sp[2], e = sp[3];
       acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
@@ -119,6 +120,7 @@ __device__ __forceinline__ void slot_scalars(const ScanSmem& s, const ScreenScan
   }
 }
 
+template <bool SMEM_W>
 __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
   const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
@@ -126,6 +128,13 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
   const int b = blockIdx.x;
   const int J = 2 * a.dk + a.dv;
   const int nel = a.ds * kMp;
+  // the projection weights live in shared memory (row stride J + 1) when they fit, else they stream through L1 / L2
+  float* Wsm = smem_f + scan_smem_floats(a.ds, a.dk, a.dv);
+  const float* WTp = SMEM_W ? Wsm : a.WT;
+  const int wstride = SMEM_W ? J + 1 : J;
+  if (SMEM_W) {
+    for (int e = tid; e < a.ds * J; e += kThreads) Wsm[(e / J) * wstride + e % J] = a.WT[e];
+  }
 
   // ---- load the bank, delta_slot and the slot embedding (all transposed to [d][16]) ----------------------------------
   for (int e = tid; e < nel; e += kThreads) {
@@ -140,7 +149,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     s.upd[tid] = 0.f;
   }
   __syncthreads();
-  project(s, a.WT, a.ds, J, a.dk, a.dv, tid, false);   // E Wkw^T (only the write-key columns are kept)
+  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, false);   // E Wkw^T (only the write-key columns are kept)
   __syncthreads();
   for (int e = tid; e < kMp * a.dk; e += kThreads) s.EW[e] = s.P[(e / a.dk) * kJp + a.dk + a.dv + e % a.dk];
   __syncthreads();
@@ -153,14 +162,20 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
   for (int i = 0; i < 9; ++i) st_acc[i] = 0.f;
   __syncthreads();
 
+  // the step's vectors are fetched one step ahead into registers (thread tid: q_r / q_w element tid, delta_xh element tid)
+  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f;
+  auto fetch = [&](int t) {
+    const size_t bt = (size_t)b * a.T + t;
+    if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
+    if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
+  };
+  fetch(0);
   for (int t = 0; t < a.T; ++t) {
     const size_t bt = (size_t)b * a.T + t;
     // ---- stage the step's vectors; save the bank for the backward pass ------------------------------------------------
-    if (tid < a.dk) {
-      s.qr[tid] = a.q_r[bt * a.dk + tid];
-      s.qw[tid] = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f;
-    }
-    for (int d = tid; d < a.ds; d += kThreads) s.dxh[d] = a.delta_xh[bt * a.ds + d];
+    if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
+    if (tid < a.ds) s.dxh[tid] = n_dx;
+    if (t + 1 < a.T) fetch(t + 1);
     if (a.saved_slots != nullptr) {
       float* dst = a.saved_slots + bt * nel;
       for (int e = tid; e < nel; e += kThreads) dst[e] = s.St[e];
@@ -168,7 +183,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     }
     if (tid < kMp) s.upd[tid] = 0.f;
     __syncthreads();
-    project(s, a.WT, a.ds, J, a.dk, a.dv, tid, true);
+    project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
     __syncthreads();
     slot_scalars(s, a, warp, lane);
     __syncthreads();
@@ -246,6 +261,7 @@ __host__ __device__ inline int scan_bwd_smem_floats(int ds, int dk, int dv) {
   return scan_smem_floats(ds, dk, dv) + ds * kMp /*dSt*/ + kJp * kMp /*dPt*/ + 2 * dv /*du, dz*/ + kMp * 4 /*dstr, dsimr, dsimw, pad*/;
 }
 
+template <bool SMEM_W>
 __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
   const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
@@ -262,6 +278,12 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
   const int J = 2 * a.dk + a.dv;
   const int nel = a.ds * kMp;
   const float e2 = a.eps * a.eps;
+  float* Wsm = extra + kMp;   // after the scratch arrays; one padded copy of W^T serves both the projections and their backward
+  const float* WTp = SMEM_W ? Wsm : a.WT;
+  const int wstride = SMEM_W ? J + 1 : J;
+  if (SMEM_W) {
+    for (int e = tid; e < a.ds * J; e += kThreads) Wsm[(e / J) * wstride + e % J] = a.WT[e];
+  }
 
   for (int e = tid; e < nel; e += kThreads) {
     const int d = e / kMp, m = e % kMp;
@@ -271,7 +293,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
     dSt[e] = (live && a.dslots_out != nullptr) ? a.dslots_out[((size_t)b * a.M + m) * a.ds + d] : 0.f;
   }
   __syncthreads();
-  project(s, a.WT, a.ds, J, a.dk, a.dv, tid, false);
+  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, false);
   __syncthreads();
   for (int e = tid; e < kMp * a.dk; e += kThreads) s.EW[e] = s.P[(e / a.dk) * kJp + a.dk + a.dv + e % a.dk];
   float dslot_acc[16];          // this thread's elements of d(delta_slot): e = tid + 256 i
@@ -281,6 +303,14 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
   float dmu_acc2 = 0.f;
   __syncthreads();
 
+  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f, n_du = 0.f;
+  auto fetch = [&](int t) {
+    const size_t bt = (size_t)b * a.T + t;
+    if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
+    if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
+    if (tid < a.dv) n_du = a.du[bt * a.dv + tid];
+  };
+  fetch(a.T - 1);
   for (int t = a.T - 1; t >= 0; --t) {
     const size_t bt = (size_t)b * a.T + t;
     {
@@ -288,14 +318,12 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       for (int e = tid; e < nel; e += kThreads) s.St[e] = src[e];
     }
     if (tid < kMp) { s.ages[tid] = a.saved_ages[bt * kMp + tid]; dstr[tid] = 0.f; }
-    if (tid < a.dk) {
-      s.qr[tid] = a.q_r[bt * a.dk + tid];
-      s.qw[tid] = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f;
-    }
-    for (int d = tid; d < a.ds; d += kThreads) s.dxh[d] = a.delta_xh[bt * a.ds + d];
-    if (tid < a.dv) du[tid] = a.du[bt * a.dv + tid];
+    if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
+    if (tid < a.ds) s.dxh[tid] = n_dx;
+    if (tid < a.dv) du[tid] = n_du;
+    if (t > 0) fetch(t - 1);
     __syncthreads();
-    project(s, a.WT, a.ds, J, a.dk, a.dv, tid, true);
+    project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
     __syncthreads();
     slot_scalars(s, a, warp, lane);
     __syncthreads();
@@ -409,7 +437,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
 #pragma unroll
         for (int m = 0; m < kMp; ++m) acc[m] = 0.f;
         for (int j = j0; j < j1; ++j) {
-          const float w = __ldg(a.W + (size_t)j * a.ds + d);
+          const float w = SMEM_W ? Wsm[d * wstride + j] : __ldg(a.W + (size_t)j * a.ds + d);
           const float4* gp = reinterpret_cast<const float4*>(dPt + j * kMp);
           const float4 x = gp[0], y = gp[1], z4 = gp[2], u4 = gp[3];
           acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]); acc[2] = fmaf(w, x.z, acc[2]); acc[3] = fmaf(w, x.w, acc[3]);
@@ -451,17 +479,29 @@ bool screen_scan_supported(const ScreenScanArgs& a) {
 
 int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st) {
   if (!screen_scan_supported(a)) return 1;
-  const size_t smem = (size_t)scan_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
-  cudaFuncSetAttribute(screen_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  screen_scan_fwd_kernel<<<a.B, kThreads, smem, st>>>(a);
+  const size_t base = (size_t)scan_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
+  const size_t wbytes = (size_t)a.ds * (2 * a.dk + a.dv + 1) * sizeof(float);
+  if (base + wbytes <= 200 * 1024) {
+    cudaFuncSetAttribute(screen_scan_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(base + wbytes));
+    screen_scan_fwd_kernel<true><<<a.B, kThreads, base + wbytes, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(screen_scan_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)base);
+    screen_scan_fwd_kernel<false><<<a.B, kThreads, base, st>>>(a);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st) {
   if (!screen_scan_supported(a)) return 1;
-  const size_t smem = (size_t)scan_bwd_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
-  cudaFuncSetAttribute(screen_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  screen_scan_bwd_kernel<<<a.B, kThreads, smem, st>>>(a);
+  const size_t base = (size_t)(scan_bwd_smem_floats(a.ds, a.dk, a.dv) + kMp) * sizeof(float);
+  const size_t wbytes = (size_t)a.ds * (2 * a.dk + a.dv + 1) * sizeof(float);
+  if (base + wbytes <= 200 * 1024) {
+    cudaFuncSetAttribute(screen_scan_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(base + wbytes));
+    screen_scan_bwd_kernel<true><<<a.B, kThreads, base + wbytes, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(screen_scan_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)base);
+    screen_scan_bwd_kernel<false><<<a.B, kThreads, base, st>>>(a);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
