@@ -48,6 +48,8 @@ def parse_args(argv=None):
     ap.add_argument("--screening", action="store_true",
                     help="enable the screening memory of the 0.185b preset (read/write phase, carry-state streaming)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--phases", action="store_true",
+                    help="also report the mean device time of forward+backward and of gradient exchange + optimizer")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
     return ap.parse_args(argv)
 
@@ -224,6 +226,8 @@ def main(argv=None):
             else:
                 mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
                 trainer = DataParallelTrainer(train_state, mode=mode)
+            if args.phases and hasattr(trainer, "record_phases"):
+                trainer.record_phases = True
             dev_batches = [make_batch(False) for _ in range(2)]
             for i in range(args.warmup):
                 train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime, phase=phase, carry_state=carry)
@@ -263,6 +267,7 @@ def main(argv=None):
     ms = e0.elapsed_time(e1)
     launches = K.LAUNCH_COUNT - launches0
     last_loss = float(metrics["loss"])
+    phases = trainer.phase_times_ms(args.steps) if (args.phases and hasattr(trainer, "phase_times_ms")) else None
 
     # ---- end-to-end through the public API -------------------------------------
     e2e = None
@@ -320,6 +325,8 @@ def main(argv=None):
             "gpu_launches": launches,
             "last_loss": last_loss,
         }
+        if phases is not None:
+            line["phases"] = phases
         if e2e is not None:
             line["e2e"] = {
                 "value": tokens / (e2e_ms_max / 1e3),

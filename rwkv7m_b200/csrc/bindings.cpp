@@ -419,10 +419,35 @@ rk::DpPeers make_peers(const std::vector<int64_t>& grad, const std::vector<int64
 
 // One optimizer step.  Pointer lists are raw device addresses of the symmetric buffers of every rank.
 // Returns the number of barriers issued so far.
+// Optional per-kernel timing of the fused data-parallel step (RWKV7M_B200_DP_TIMING=1): CUDA events around the five
+// launches of the most recent step, read back with dp_step_timings().
+struct DpTiming {
+  bool on = false, init = false, valid = false;
+  cudaEvent_t ev[6];
+};
+static DpTiming& dp_timing() {
+  static DpTiming t;
+  if (!t.init) {
+    t.init = true;
+    const char* e = getenv("RWKV7M_B200_DP_TIMING");
+    t.on = e != nullptr && e[0] == '1';
+    if (t.on) for (auto& ev : t.ev) cudaEventCreate(&ev);
+  }
+  return t;
+}
+std::vector<double> dp_step_timings() {
+  DpTiming& t = dp_timing();
+  std::vector<double> out;
+  if (!t.on || !t.valid) return out;
+  cudaEventSynchronize(t.ev[5]);
+  for (int i = 0; i < 5; ++i) { float ms = 0.f; cudaEventElapsedTime(&ms, t.ev[i], t.ev[i + 1]); out.push_back(ms); }
+  return out;
+}
+
 int64_t dp_step(const std::vector<int64_t>& grad, const std::vector<int64_t>& master, const std::vector<int64_t>& shadow,
                 const std::vector<int64_t>& aux, int64_t grad_mc, int64_t master_mc, int64_t shadow_mc, Tensor m,
                 Tensor v, Tensor norm_out, int64_t rank, int64_t begin, int64_t end, int64_t n_decay,
-                int64_t n_nodecay_end, int64_t barriers_done, int64_t step_index, double lr, double beta1, double beta2,
+                int64_t n_nodecay_end, int64_t master_bcast_from, int64_t barriers_done, int64_t step_index, double lr, double beta1, double beta2,
                 double eps, double weight_decay, double bc1, double bc2, double max_norm) {
   c10::cuda::CUDAGuard guard(m.device());
   const int world = (int)grad.size();
@@ -435,17 +460,29 @@ int64_t dp_step(const std::vector<int64_t>& grad, const std::vector<int64_t>& ma
   cudaStream_t st = stream();
   uint32_t b = (uint32_t)barriers_done;
   const int parity = (int)(step_index & 1);
+  DpTiming& tm = dp_timing();
+  auto mark = [&](int i) { if (tm.on) cudaEventRecord(tm.ev[i], st); };
+  mark(0);
   rk::dp_barrier(peers, (int)rank, world, ++b, -1, st);
+  mark(1);
   rk::dp_reduce_shard(peers, (int)rank, world, begin, end, st);
+  mark(2);
   rk::dp_barrier(peers, (int)rank, world, ++b, parity, st);
+  mark(3);
   rk::DpAdamW a{};
   a.rank = (int)rank; a.world = world; a.parity = parity; a.begin = begin; a.end = end;
   a.n_decay = n_decay; a.n_nodecay_end = n_nodecay_end;
+  // without a bf16 compute copy the forward reads the master values, so every rank needs all of them
+  a.master_bcast_from = shadow.empty() ? 0 : master_bcast_from;
+  TORCH_CHECK(a.master_bcast_from % 4 == 0, "master_bcast_from must be a multiple of 4 elements");
   a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>(); a.norm_out = norm_out.data_ptr<float>();
   a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2; a.eps = (float)eps;
   a.weight_decay = (float)weight_decay; a.bc1 = (float)bc1; a.bc2 = (float)bc2; a.max_norm = (float)max_norm;
   rk::dp_adamw_allgather(peers, a, st);
+  mark(4);
   rk::dp_barrier(peers, (int)rank, world, ++b, -1, st);
+  mark(5);
+  tm.valid = tm.on;
   return (int64_t)b;
 }
 
@@ -628,6 +665,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("dp_step", &dp_step);
+  m.def("dp_step_timings", &dp_step_timings);
   m.def("screen_scan_fwd", &screen_scan_fwd);
   m.def("screen_scan_bwd", &screen_scan_bwd);
   m.def("tp_gather_seq", &tp_gather_seq);

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) dp_reduce_shard_kernel(DpPeers peers, int
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(256) dp_adamw_allgather_kernel(DpPeers peers, DpAdamW a) {
   const float* my_grad = reinterpret_cast<const float*>(peers.grad[a.rank]);
-  const float* my_master = reinterpret_cast<const float*>(peers.master[a.rank]);
+  float* my_master = reinterpret_cast<float*>(peers.master[a.rank]);
   const float* slots = reinterpret_cast<const float*>(peers.aux[a.rank]) + kAuxNorm + a.parity * kMaxRanks;
   float nsq = 0.f;
   for (int p = 0; p < a.world; ++p) nsq += slots[p];
@@ -159,13 +159,15 @@ __global__ void __launch_bounds__(256) dp_adamw_allgather_kernel(DpPeers peers, 
     const __nv_bfloat162 h0 = __floats2bfloat162_rn(w[0], w[1]);
     const __nv_bfloat162 h1 = __floats2bfloat162_rn(w[2], w[3]);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&h0), b1 = *reinterpret_cast<const uint32_t*>(&h1);
+    const bool bcast_master = i >= a.master_bcast_from;
+    if (!bcast_master) *reinterpret_cast<float4*>(my_master + i) = wn;
     if (MULTIMEM) {
-      multimem_st_f32x4(reinterpret_cast<float*>(peers.master_mc) + i, wn);
+      if (bcast_master) multimem_st_f32x4(reinterpret_cast<float*>(peers.master_mc) + i, wn);
       if (peers.shadow_mc != nullptr)
         multimem_st_b32x2(reinterpret_cast<__nv_bfloat16*>(peers.shadow_mc) + i, b0, b1);
     } else {
       for (int p = 0; p < a.world; ++p) {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.master[p]) + i) = wn;
+        if (bcast_master) *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.master[p]) + i) = wn;
         if (peers.shadow[p] != nullptr)
           *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(peers.shadow[p]) + i) = make_uint2(b0, b1);
       }

@@ -136,12 +136,11 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
 
 // Tile order: blocks of kRasterM consecutive m-tiles sweep all n-tiles before the next block starts, so the
 // CTAs that run at the same time share a few A row-panels and B column-panels and both stay in L2.
-constexpr int kRasterM = 16;
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int group_size = kRasterM * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int raster_m, int& tm, int& tn) {
+  const int group_size = raster_m * tiles_n;
   const int group = tile / group_size;
-  const int first = group * kRasterM;
-  const int rows = min(kRasterM, tiles_m - first);
+  const int first = group * raster_m;
+  const int rows = min(raster_m, tiles_m - first);
   const int within = tile - group * group_size;
   tm = first + within % rows;
   tn = within / rows;
@@ -160,7 +159,7 @@ struct Tile {
 template <int BN, int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Dptr, int M, int N, int K, int ldd, int* __restrict__ err) {
+                 void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int* __restrict__ err) {
   using TL = Tile<BN>;
   constexpr int kStages = TL::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -201,7 +200,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -266,7 +265,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -323,7 +322,7 @@ struct PairTile {
 template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int* __restrict__ err) {
+                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int* __restrict__ err) {
   using TL = PairTile;
   constexpr int kStages = TL::kStages;
   constexpr int BN2 = 256;  // tile width of the pair
@@ -370,7 +369,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
         const int m0 = tm * 2 * BM + (int)cta * BM;   // this CTA's rows
         const int n0 = tn * BN2 + (int)cta * 128;     // this CTA's columns of B
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -438,7 +437,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
       const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN2;
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -558,6 +557,15 @@ int sm_count() {
   return n;
 }
 
+// Height (in m-tiles) of the raster groups; RWKV7M_B200_GEMM_RASTER overrides the default for experiments.
+int raster_rows(const GemmArgs& p) {
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("RWKV7M_B200_GEMM_RASTER"); forced = e != nullptr ? atoi(e) : 0; }
+  if (forced > 0) return forced;
+  (void)p;
+  return 16;
+}
+
 #define RK_TRACE(...) do { if (trace_on()) { fprintf(stderr, "[gemm] " __VA_ARGS__); fflush(stderr); } } while (0)
 bool trace_on() {
   static int on = -1;
@@ -587,7 +595,7 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   RK_TRACE("attr ok grid=%d smem=%d\n", grid, TL::kSmemBytes);
-  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, p.error_flag);
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.error_flag);
   RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -632,7 +640,7 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, p.error_flag);
+  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.error_flag);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

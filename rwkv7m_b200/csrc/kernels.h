@@ -105,6 +105,8 @@ struct DpAdamW {
   int rank, world, parity;
   int64_t begin, end;              // owned element range in the flat buffers
   int64_t n_decay, n_nodecay_end;  // group boundaries
+  int64_t master_bcast_from;       // new fp32 master values go to every rank from this index on; below it only the owner
+                                   // keeps them (peers receive just the bf16 compute copy)
   float* m; float* v;              // Adam moments of the owned shard (local index = i - begin)
   float* norm_out;                 // receives the global gradient norm
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2, max_norm;

@@ -51,40 +51,112 @@ void grad_norm_sq(const void* g, bool g_is_bf16, int64_t n, float* out, cudaStre
     grad_norm_sq_kernel<float><<<blocks, 256, 0, st>>>((const float*)g, n, out);
 }
 
-template <typename P, typename G, typename S>
-__global__ void adamw_kernel(AdamWArgs p) {
+// Four consecutive elements as one 16-byte (fp32) or 8-byte (bf16) access.
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&o)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&o)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  } else {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(o[0], o[1]);
+    h[1] = __floats2bfloat162_rn(o[2], o[3]);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+}
+
+struct AdamWScalars {
+  float clip, inv_bc1, inv_bc2;
+};
+
+// One element of the update; returns the new master value.
+__device__ __forceinline__ float adamw_one(const AdamWArgs& p, const AdamWScalars& c, int64_t i, float g, float w,
+                                           float& mi, float& vi) {
+  g *= c.clip;
+  mi = p.beta1 * mi + (1.0f - p.beta1) * g;
+  vi = p.beta2 * vi + (1.0f - p.beta2) * g * g;
+  float upd = (mi * c.inv_bc1) / (sqrtf(vi * c.inv_bc2) + p.eps);
+  if (i < p.n_decay) upd += p.weight_decay * w;
+  if (i >= p.n_nodecay_end) upd *= 2.0f;
+  return w - p.lr * upd;
+}
+
+// VEC: every thread owns groups of four consecutive elements (the launcher checks that all base pointers are
+// 16-byte aligned); the ragged head and tail of [begin, end) are done one element at a time by block 0.
+template <typename P, typename G, typename S, bool VEC>
+__global__ void __launch_bounds__(256) adamw_kernel(AdamWArgs p) {
   P* param = (P*)p.param;
   G* grad = (G*)p.grad;
   S* m = (S*)p.m;
   S* v = (S*)p.v;
   __nv_bfloat16* shadow = (__nv_bfloat16*)p.shadow;
   const float norm = sqrtf(*p.norm_sq) * p.grad_scale;
-  const float clip = (norm < p.max_norm ? 1.0f : p.max_norm / norm) * p.grad_scale;
-  const float inv_bc1 = 1.0f / p.bc1, inv_bc2 = 1.0f / p.bc2;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = p.begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.end; i += stride) {
-    const float g = to_float(grad[i]) * clip;
-    const float mi = p.beta1 * to_float(m[i]) + (1.0f - p.beta1) * g;
-    const float vi = p.beta2 * to_float(v[i]) + (1.0f - p.beta2) * g * g;
+  AdamWScalars c;
+  c.clip = (norm < p.max_norm ? 1.0f : p.max_norm / norm) * p.grad_scale;
+  c.inv_bc1 = 1.0f / p.bc1;
+  c.inv_bc2 = 1.0f / p.bc2;
+  auto scalar = [&](int64_t i) {
+    float mi = to_float(m[i]), vi = to_float(v[i]);
+    const float w = adamw_one(p, c, i, to_float(grad[i]), to_float(param[i]), mi, vi);
     m[i] = from_float<S>(mi);
     v[i] = from_float<S>(vi);
-    float w = to_float(param[i]);
-    float upd = (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + p.eps);
-    if (i < p.n_decay) upd += p.weight_decay * w;
-    if (i >= p.n_nodecay_end) upd *= 2.0f;
-    w -= p.lr * upd;
     param[i] = from_float<P>(w);
     if (shadow != nullptr) shadow[i] = f2bf(w);
     if (p.zero_grad) grad[i] = from_float<G>(0.f);
+  };
+  if constexpr (!VEC) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = p.begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.end; i += stride) scalar(i);
+  } else {
+    const int64_t v0 = (p.begin + 3) & ~(int64_t)3, v1 = p.end & ~(int64_t)3;
+    if (blockIdx.x == 0) {
+      const int64_t head_end = v0 < p.end ? v0 : p.end;
+      for (int64_t i = p.begin + threadIdx.x; i < head_end; i += blockDim.x) scalar(i);
+      for (int64_t i = (v1 > v0 ? v1 : head_end) + threadIdx.x; i < p.end; i += blockDim.x) scalar(i);
+    }
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t i = v0 + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < v1; i += stride) {
+      float g[4], mi[4], vi[4], w[4];
+      load4(grad + i, g);
+      load4(m + i, mi);
+      load4(v + i, vi);
+      load4(param + i, w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = adamw_one(p, c, i + j, g[j], w[j], mi[j], vi[j]);
+      store4(m + i, mi);
+      store4(v + i, vi);
+      store4(param + i, w);
+      if (shadow != nullptr) store4(shadow + i, w);
+      if (p.zero_grad) store4(grad + i, zero);
+    }
   }
 }
 
 void adamw_flat(const AdamWArgs& p, cudaStream_t st) {
   const int64_t n = p.end - p.begin;
   if (n <= 0) return;
-  int64_t want = (n + 255) / 256;
-  int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-#define RK_GO(P, G, S) adamw_kernel<P, G, S><<<blocks, 256, 0, st>>>(p)
+  const uintptr_t bits = (uintptr_t)p.param | (uintptr_t)p.grad | (uintptr_t)p.m | (uintptr_t)p.v | (uintptr_t)p.shadow;
+  const bool vec = (bits & 15) == 0;
+  int64_t want = ((vec ? n / 4 : n) + 255) / 256 + 1;
+  int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
+#define RK_GO(P, G, S)                                      \
+  do {                                                      \
+    if (vec) adamw_kernel<P, G, S, true><<<blocks, 256, 0, st>>>(p);  \
+    else adamw_kernel<P, G, S, false><<<blocks, 256, 0, st>>>(p);     \
+  } while (0)
   using bf = __nv_bfloat16;
   const int key = (p.param_bf16 ? 4 : 0) | (p.grad_bf16 ? 2 : 0) | (p.state_bf16 ? 1 : 0);
   switch (key) {

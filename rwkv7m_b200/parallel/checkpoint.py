@@ -95,6 +95,14 @@ def _moment_shard(train_state):
     return fused.exp_avg, fused.exp_avg_sq, fused.begin, fused.end
 
 
+def _sync_masters(train_state):
+    """The fused data-parallel step keeps the fp32 master value of a bulk weight only on its owner: refresh every
+    rank's copy before the parameters are read for a checkpoint (collective, no-op otherwise)."""
+    fused = train_state.extras.get("fused_optimizer")
+    if fused is not None and hasattr(fused, "gather_master"):
+        fused.gather_master()
+
+
 def _gather_moments_into_optimizer(train_state, process_info):
     """Materialise full Adam moments on the optimizer object (every rank) from the per-rank shards."""
     shard = _moment_shard(train_state)
@@ -116,6 +124,8 @@ def save_data_parallel_checkpoint(checkpoint_dir, train_state, config, process_i
     backend = normalize_backend(backend)
     rank, world = _world(process_info)
     checkpoint_dir = Path(checkpoint_dir)
+    if world > 1:
+        _sync_masters(train_state)
     if backend == "single":
         gathered = _gather_moments_into_optimizer(train_state, process_info) if world > 1 else False
         if rank == 0:

@@ -35,6 +35,9 @@ class DataParallelTrainer:
             mode = "single"
         self.mode = mode
         self.fused = None
+        # set record_phases = True to keep CUDA events around the forward/backward and the optimizer part of every step
+        self.record_phases = False
+        self._phase_events = []
         if mode == "fused":
             from .fused_dp import FusedShardedAdamW
 
@@ -61,6 +64,23 @@ class DataParallelTrainer:
             self.broadcast_parameters()
         train_state.extras["train_step"] = self.train_step
 
+    def phase_times_ms(self, last: int = 0):
+        """Mean device time of (forward + backward, gradient exchange + optimizer) over the recorded steps
+        (the ``last`` most recent ones when positive).  Synchronises the device."""
+        if not self._phase_events:
+            return None
+        torch.cuda.synchronize()
+        ev = self._phase_events[-last:] if last > 0 else self._phase_events
+        n = float(len(ev))
+        out = {"forward_backward_ms": sum(a.elapsed_time(b) for a, b, _ in ev) / n,
+               "exchange_optimizer_ms": sum(b.elapsed_time(c) for _, b, c in ev) / n}
+        if self.fused is not None:
+            kernels = self.fused._C.dp_step_timings()   # filled only with RWKV7M_B200_DP_TIMING=1
+            if kernels:
+                out["last_step_kernels_ms"] = dict(zip(
+                    ("barrier_in", "reduce_shard", "barrier_norm", "adamw_allgather", "barrier_out"), kernels))
+        return out
+
     def broadcast_parameters(self, src: int = 0):
         """Make every rank start from rank ``src``'s parameters."""
         flat = self.train_state.optimizer.flat
@@ -85,10 +105,16 @@ class DataParallelTrainer:
         if self.mode != "fused":
             opt.zero_grad()
         scale = 1.0 if self.world == 1 else self._loss_scale(batch)
+        events = None
+        if self.record_phases and opt.flat.master.is_cuda:
+            events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            events[0].record()
         new_rwkv, new_screen, metrics = accumulate_gradients(
             model, batch, rwkv_state, screen_state, phase=phase,
             gradient_accumulation_steps=gradient_accumulation_steps, loss_scale=scale,
         )
+        if events is not None:
+            events[1].record()
         if self.mode == "single":
             opt.step()
         elif self.mode == "allreduce":
@@ -97,6 +123,9 @@ class DataParallelTrainer:
             opt.step()
         else:
             self.fused.step()
+        if events is not None:
+            events[2].record()
+            self._phase_events.append(events)
         metrics["grad_norm"] = opt.grad_norm
         if self.world > 1:
             for key in ("loss", "total_loss"):

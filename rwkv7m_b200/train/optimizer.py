@@ -75,6 +75,11 @@ def decay_mask(name: str, param: torch.Tensor) -> bool:
     return param.ndim >= 2 and name.endswith(_DECAY_LEAVES) and ".ln" not in name
 
 
+def is_bulk(name: str) -> bool:
+    """Decayed leaves that the CUDA forward reads only through their bf16 compute copy."""
+    return ".screening." not in name
+
+
 def is_w0(name: str) -> bool:
     return name.endswith(".w0")
 
@@ -97,13 +102,19 @@ class FlatParams:
         groups = ([], [], [])
         for n, p in named:
             groups[2 if is_w0(n) else (0 if decay_mask(n, p) else 1)].append((n, p))
+        # inside the decayed group the "bulk" leaves come first: block projections, embedding and LM head, which
+        # the forward pass reads only through the bf16 compute copy (never through the master value)
+        groups[0].sort(key=lambda np_: 0 if is_bulk(np_[0]) else 1)
         self.entries = []  # (name, param, offset, numel)
         offset = 0
         ends = []
-        for group in groups:
+        self.n_bulk = 0
+        for gi, group in enumerate(groups):
             for n, p in group:
                 self.entries.append((n, p, offset, p.numel()))
                 offset = _round_up(offset + p.numel(), _ALIGN)
+                if gi == 0 and is_bulk(n):
+                    self.n_bulk = offset
             ends.append(offset)
         total = _round_up(max(offset, _ALIGN), _ALIGN * max(shard_multiple, 1))
         self.bounds = (ends[0], ends[1], total)

@@ -27,6 +27,8 @@ def main():
                         max_seq_len=64, dtype="bfloat16", use_screening=False, warmup_steps=0, lr_init=1e-3)
     use_mc = os.environ.get("RWKV7M_B200_DP_MULTICAST", "1") == "1"
 
+    stale_flags = []
+
     def run(mode):
         alloc = SymmetricFlatBuffers() if mode == "fused" else None
         rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=50, device=dev,
@@ -44,6 +46,10 @@ def main():
             losses.append(float(m["loss"]))
         err = trainer.fused.error_code() if mode == "fused" else 0
         mc = bool(trainer.fused.use_multicast) if mode == "fused" else False
+        if mode == "fused":
+            # the owner-only fp32 masters of the bulk weights are refreshed on request
+            stale_flags.append(bool(trainer.fused.master_stale))
+            trainer.fused.gather_master()
         return ts.optimizer.flat.master.clone(), ts.optimizer.flat.compute.clone(), losses, float(ts.optimizer.grad_norm), err, mc
 
     m_ref, c_ref, l_ref, n_ref, _, _ = run("allreduce")
@@ -58,7 +64,8 @@ def main():
     if rank == 0:
         print(json.dumps({"max_master_diff": diff, "rel_l2_diff": rel_l2, "max_compute_diff": cdiff, "rank_spread": spread,
                           "loss_ref": l_ref, "loss_fused": l_fus, "norm_ref": n_ref, "norm_fused": n_fus,
-                          "error_code": err, "multicast": mc, "world": world}))
+                          "error_code": err, "multicast": mc, "world": world,
+                          "master_stale_before_gather": stale_flags[-1]}))
     dist.destroy_process_group()
 
 

@@ -28,6 +28,7 @@ def test_fused_step_matches_allreduce(multicast):
     res = _run(2, multicast)
     assert res["error_code"] == 0
     assert res["rank_spread"] == 0.0
+    assert res["master_stale_before_gather"] is True   # bulk fp32 masters stay with their owner between gathers
     # Adam's first steps move every weight by about lr regardless of gradient size, so run-to-run
     # rounding differences show up as a few lr on isolated weights; the bulk must agree closely.
     assert res["max_master_diff"] < 5e-3, res
