@@ -44,16 +44,20 @@ class ScreenedRWKVLayer(nn.Module):
 
 
 class ScreenedRWKVModel(nn.Module):
-    def __init__(self, config: ModelConfig):
+    def __init__(self, config: ModelConfig, device=None):
+        """``device``: move every sub-module there as soon as it is built (values still come from the CPU generator,
+        so a seed gives the same weights everywhere), which keeps the host footprint at one layer."""
         super().__init__()
         self.config = config
+        place = (lambda m: m) if device is None else (lambda m: m.to(device))
         # execution control: recompute the first k layers in backward even when remat_blocks is off
         self.remat_layer_count = 0
         C, V = config.d_model, config.vocab_size
         self.emb = nn.Embedding(V, C)
         with torch.no_grad():
             self.emb.weight.copy_(_uniform((V, C), 1e-4))
-        self.layers = nn.ModuleList(ScreenedRWKVLayer(config, i) for i in range(config.n_layers))
+        place(self.emb)
+        self.layers = nn.ModuleList(place(ScreenedRWKVLayer(config, i)) for i in range(config.n_layers))
         self.ln_out = LayerNorm(C)
         gain = 0.5 * math.sqrt(V / C) if V > C else 0.5
         if config.lm_head_init == "orthogonal":
@@ -62,7 +66,7 @@ class ScreenedRWKVModel(nn.Module):
             std = gain / math.sqrt(C) / 0.87962566
             head = torch.empty(V, C)
             nn.init.trunc_normal_(head, std=std, a=-2 * std, b=2 * std)
-        self.head = Linear(C, V, init=head)
+        self.head = place(Linear(C, V, init=head))
         param_dtype = torch_dtype(config.param_dtype)
         if param_dtype != torch.float32:
             self.to(param_dtype)
@@ -200,7 +204,7 @@ def initialize_model(seed_or_generator, config: ModelConfig, device=None) -> Scr
         seed = int(torch.as_tensor(seed_or_generator).flatten()[-1].item())
     with torch.random.fork_rng(devices=[]):
         torch.manual_seed(seed)
-        model = ScreenedRWKVModel(config)
+        model = ScreenedRWKVModel(config, device=device)
     if device is not None:
         model = model.to(device)
     return model
