@@ -66,7 +66,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 // Write one 32-column chunk of an accumulator row (thread = row) with the selected epilogue.
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __restrict__ Dptr, int row, int col0, int M,
-                                            int N, int ldd) {
+                                            int N, int ldd, bool atomic = false) {
   if (EPI == kEpiScatterAddBf16) {
     // Reduce-scatter over time fused into the epilogue: the row belongs to the rank that owns its time slice; the
     // partial result is added straight into that rank's output buffer (peer memory over NVLink, bf16x2 atomics).
@@ -106,15 +106,31 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
 #pragma unroll
               for (int j = 0; j < 4; ++j) o4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+              // ragged right edge: fully unrolled with a per-element guard so that v stays in registers
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
                 float x0 = __uint_as_float(v[j]);
                 if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; }
-                out[j] = f2bf(x0);
+                if (col0 + j < N) out[j] = f2bf(x0);
               }
             }
           } else {
             float* out = reinterpret_cast<float*>(Dptr) + (size_t)row * ldd + col0;
-            if (col0 + 32 <= N) {
+            if (EPI == kEpiAccumF32 && atomic) {
+              // split-K: several CTAs hold partial sums of this tile
+              if (col0 + 32 <= N) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + 4 * j),
+                               "f"(__uint_as_float(v[4 * j])), "f"(__uint_as_float(v[4 * j + 1])),
+                               "f"(__uint_as_float(v[4 * j + 2])), "f"(__uint_as_float(v[4 * j + 3]))
+                               : "memory");
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < N) atomicAdd(out + j, __uint_as_float(v[j]));
+              }
+            } else if (col0 + 32 <= N) {
               float4* o4 = reinterpret_cast<float4*>(out);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -124,10 +140,13 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
                 o4[j] = t;
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float t = __uint_as_float(v[j]);
-                if (EPI == kEpiAccumF32) t += out[j];
-                out[j] = t;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < N) {
+                  float t = __uint_as_float(v[j]);
+                  if (EPI == kEpiAccumF32) t += out[j];
+                  out[j] = t;
+                }
               }
             }
           }
@@ -159,7 +178,8 @@ struct Tile {
 template <int BN, int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int* __restrict__ err) {
+                 void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int splits,
+                 int* __restrict__ err) {
   using TL = Tile<BN>;
   constexpr int kStages = TL::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -179,6 +199,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K (accumulating epilogue only): work item w covers k-blocks [kb0, kb1) of tile w % num_tiles
+  const int num_work = num_tiles * splits;
+  const int kb_per = (num_kb + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -198,11 +221,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        const int tile = work % num_tiles, split = work / num_tiles;
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = tiles + stage * TL::kStageBytes;
           uint8_t* sb = sa + TL::kABytes;
@@ -232,11 +257,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
         if (!wait_bar(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (work / num_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * TL::kStageBytes);
@@ -247,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                           : umma_smem_desc_sw128(sa + k * 2048, BK * 128, 1024);
             const uint64_t db = B_MN == 0 ? umma_smem_desc_sw128(sb + k * 32, 16, 1024)
                                           : umma_smem_desc_sw128(sb + k * 2048, BK * 128, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -263,20 +289,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    const bool atomic = splits > 1;
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
+      tile_coords(work % num_tiles, tiles_m, tiles_n, raster_m, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      if constexpr (BN >= 64) {
+        // two 32-column chunks per round: the second load is in flight while the first chunk is converted and stored
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < BN / 32; c += 2) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(t0 + c * 32, v0);
+          tmem_ld_32x32(t0 + c * 32 + 32, v1);
+          tmem_ld_wait();
+          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic);
+          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic);
+        }
+      } else {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, v);
+        tmem_ld_32x32(t0, v);
         tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        store_chunk<EPI>(v, Dptr, row, col0, M, N, ldd);
+        store_chunk<EPI>(v, Dptr, row, n0, M, N, ldd, atomic);
       }
       tc_fence_before();
       __syncwarp();
@@ -442,12 +479,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * BN2;
 #pragma unroll 1
-      for (int c = 0; c < BN2 / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN2 + c * 32, v);
+      for (int c = 0; c < BN2 / 32; c += 2) {   // two chunks per round: the second load overlaps the first chunk's stores
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(t0 + c * 32, v0);
+        tmem_ld_32x32(t0 + c * 32 + 32, v1);
         tmem_ld_wait();
-        store_chunk<EPI>(v, Dptr, row, n0 + c * 32, M, N, ldd);
+        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd);
+        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd);
       }
       tc_fence_before();
       __syncwarp();
@@ -593,9 +633,21 @@ int launch(const GemmArgs& p, cudaStream_t st) {
     attr_set = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  RK_TRACE("attr ok grid=%d smem=%d\n", grid, TL::kSmemBytes);
-  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.error_flag);
+  // split-K: a weight gradient with few output tiles and a long reduction (LoRA factors, K = tokens) would leave most
+  // SMs idle; the accumulating epilogue lets several CTAs add their partial sums to the same tile
+  int splits = 1;
+  if (EPI == kEpiAccumF32 && tiles * 2 <= sm_count()) {
+    const int num_kb = (p.K + BK - 1) / BK;
+    splits = sm_count() / tiles;
+    if (splits > num_kb / 8) splits = num_kb / 8;
+    if (splits < 1) splits = 1;
+    const int per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + per - 1) / per;   // no empty split
+  }
+  const int work = tiles * splits;
+  const int grid = work < sm_count() ? work : sm_count();
+  RK_TRACE("attr ok grid=%d smem=%d splits=%d\n", grid, TL::kSmemBytes, splits);
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.error_flag);
   RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -683,7 +735,9 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   if (p.ldd & (out_bf16 ? 7 : 3)) return 6;
   if (p.error_flag == nullptr) return 7;
   // the CTA-pair kernel needs at least one full 256-row tile and a wide N to pay off
-  if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair_layout(p, st);
+  // (with a short reduction the epilogue dominates and two independent CTAs drain their tiles faster: measured 59 vs
+  // 72 us at 32768 x 2048 x 128)
+  if (p.pair != 0 && p.M >= 256 && p.N >= 256 && p.K >= 512) return launch_pair_layout(p, st);
   // decode-sized problems (one m-tile): narrow n-tiles so that the weight matrix is streamed by many SMs at once
   if (p.layout == kGemmTN && p.M <= BM && p.N >= 1024) return launch_epi<32, 0, 0>(p, st);
   if (p.N > 128) return launch_layout<256>(p, st);
