@@ -22,6 +22,7 @@ def main(argv=None):
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--streams", type=int, default=3, help="side streams for the independent time-mix projections (0 = one stream)")
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args(argv)
 
@@ -53,7 +54,7 @@ def main(argv=None):
                 ids.append(nxt)
                 last, rs, ss, _ = decode_one(rt.model, nxt, rs, ss)
         else:
-            dec = GraphDecoder(rt.model, rs)
+            dec = GraphDecoder(rt.model, rs, parallel_streams=args.streams)
             e1.record()   # graph construction is a one-off per (model, batch) and excluded from the decode time
             ids = []
             for _ in range(args.new_tokens):
@@ -69,7 +70,7 @@ def main(argv=None):
     best = min(results, key=lambda r: r["decode_ms"])
     print(json.dumps({
         "metric": f"batched recurrent decode at {args.model}", "batch": args.batch, "prompt_tokens": args.prompt,
-        "new_tokens": args.new_tokens, "cuda_graph": not args.no_graph,
+        "new_tokens": args.new_tokens, "cuda_graph": not args.no_graph, "side_streams": args.streams,
         "decode_tokens_per_s": args.batch * args.new_tokens / (best["decode_ms"] / 1e3),
         "decode_ms_per_step": best["decode_ms"] / args.new_tokens,
         "prefill_plus_setup_ms": best["prefill_ms"], "runs": results,

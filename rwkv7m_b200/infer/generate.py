@@ -64,7 +64,8 @@ class GraphDecoder:
     the static state inside the graph.  Models with screening memory fall back to eager decoding.
     """
 
-    def __init__(self, model, rwkv_state, *, phase="read_screening_only"):
+    def __init__(self, model, rwkv_state, *, phase="read_screening_only", parallel_streams: int = 3):
+        from ..models.rwkv7 import StreamFork
         from ..state import LayerRWKVState, init_screen_state
 
         self.model = model
@@ -75,6 +76,18 @@ class GraphDecoder:
         self.state = tuple(LayerRWKVState(s.time_mix_x.clone(), s.channel_mix_x.clone(), s.wkv.clone()) for s in rwkv_state)
         self.screen = init_screen_state(B, model.config.screening, device=dev)
         model.eval()
+        # the independent projections of every time mix become parallel branches of the graph
+        fork = StreamFork(dev, parallel_streams) if parallel_streams > 0 else None
+        mixes = [m for m in model.modules() if hasattr(m, "fork") and hasattr(m, "receptance")]
+        for m in mixes:
+            m.fork = fork
+        try:
+            self._build(model, rwkv_state, dev)
+        finally:
+            for m in mixes:
+                m.fork = None
+
+    def _build(self, model, rwkv_state, dev):
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side), torch.no_grad():

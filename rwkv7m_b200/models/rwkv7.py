@@ -68,10 +68,49 @@ def _row_parallel_linear(module, x, weight):
     return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight)
 
 
+class StreamFork:
+    """Runs independent branches of a decode step on side streams and joins them on the current stream.
+
+    A T=1 step is a chain of short latency-bound kernels; the seven projections of the time mix (r, k, v and the four
+    LoRA pairs) do not depend on each other, so issuing them on different streams lets the GPU overlap them, also
+    when the step is captured into a CUDA graph (the branches become parallel graph nodes).  A tensor made on a side
+    stream is only read on the current stream after the join, and every fork first makes the side streams wait for
+    the current stream, so the caching allocator's per-stream reuse stays ordered.
+    """
+
+    def __init__(self, device, n_streams: int = 3):
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(n_streams)]
+
+    def run(self, branches):
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        n = len(self.streams) + 1
+        results = [None] * len(branches)
+        used = set()
+        for i, fn in enumerate(branches):
+            slot = i % n
+            if slot == 0:
+                results[i] = fn()
+                continue
+            side = self.streams[slot - 1]
+            if slot not in used:
+                side.wait_event(start)
+                used.add(slot)
+            with torch.cuda.stream(side):
+                results[i] = fn()
+        for slot in used:
+            done = torch.cuda.Event()
+            done.record(self.streams[slot - 1])
+            main.wait_event(done)
+        return results
+
+
 class RWKV7TimeMix(nn.Module):
     def __init__(self, config: ModelConfig, layer_idx: int):
         super().__init__()
         self.config = config
+        self.fork = None  # a StreamFork while a decoder wants the T=1 projections issued on parallel streams
         self.layer_idx = layer_idx
         C, H, N, L = config.d_model, config.n_heads, config.head_size, config.n_layers
         ranks = config.lora_ranks()
@@ -121,16 +160,25 @@ class RWKV7TimeMix(nn.Module):
         H, N = self.r_k.shape[0], cfg.head_size
         C = H * N
         x_r, x_w, x_k, x_v, x_a, x_g = ops.shift_mix(x, prev_x, self.x_mix)
-        r = ops.linear(x_r, self.receptance.weight)
-        k = ops.linear(x_k, self.key.weight)
-        v = ops.linear(x_v, self.value.weight)
-        w_lora = ops.lora(x_w, self.w1, self.w2, "tanh")
-        a_lora = ops.lora(x_a, self.a1, self.a2, "none")
-        g = ops.lora(x_g, self.g1, self.g2, "sigmoid")
+        branches = [
+            lambda: ops.linear(x_r, self.receptance.weight),
+            lambda: ops.linear(x_k, self.key.weight),
+            lambda: ops.linear(x_v, self.value.weight),
+            lambda: ops.lora(x_w, self.w1, self.w2, "tanh"),
+            lambda: ops.lora(x_a, self.a1, self.a2, "none"),
+            lambda: ops.lora(x_g, self.g1, self.g2, "sigmoid"),
+        ]
+        if self.layer_idx > 0:
+            branches.append(lambda: ops.lora(x_v, self.v1, self.v2, "none"))
+        if self.fork is not None and T == 1 and x.is_cuda and not torch.is_grad_enabled():
+            outs = self.fork.run(branches)
+        else:
+            outs = [fn() for fn in branches]
+        r, k, v, w_lora, a_lora, g = outs[:6]
         if self.layer_idx == 0:
             vg_lora, v_src, v0 = None, None, None
         else:
-            vg_lora, v_src, v0 = ops.lora(x_v, self.v1, self.v2, "none"), v_first, self.v0
+            vg_lora, v_src, v0 = outs[6], v_first, self.v0
         w, k_mod, v, neg_kk, kka = ops.tmix_pre(
             k, v, w_lora, a_lora, vg_lora, v_src, self.w0, self.a0, v0, self.k_k, self.k_a, H
         )
