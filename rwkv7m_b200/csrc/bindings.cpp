@@ -492,17 +492,20 @@ static const float* fptr(const Tensor& t) {
 }
 
 rk::ScreenScanArgs screen_args(const Tensor& q_r, const Tensor& q_w, const Tensor& delta_xh, const Tensor& delta_slot,
-                               const Tensor& slot_embed, const Tensor& WT, const Tensor& W, const Tensor& mu,
+                               const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask) {
   rk::ScreenScanArgs a{};
   a.B = (int)q_r.size(0); a.T = (int)q_r.size(1); a.dk = (int)q_r.size(2);
   a.M = (int)slots0.size(1); a.ds = (int)slots0.size(2);
-  a.dv = (int)W.size(0) - 2 * a.dk;
+  a.dv = (int)WT.size(1) - 2 * a.dk;
+  const int J = (int)WT.size(1);
   TORCH_CHECK(f.size() == 8, "expected 8 scalar settings");
-  TORCH_CHECK(W.size(1) == a.ds && WT.size(0) == a.ds && WT.size(1) == W.size(0), "weight shapes");
+  TORCH_CHECK(WT.size(0) == a.ds && a.dv >= 1, "weight shapes");
+  TORCH_CHECK(PD.dim() == 4 && PD.size(0) == a.B && PD.size(1) == a.T && PD.size(2) == 16 && PD.size(3) == J,
+              "PD must be [B, T, 16, J]");
   a.q_r = fptr(q_r); a.q_w = fptr(q_w); a.delta_xh = fptr(delta_xh); a.delta_slot = fptr(delta_slot);
-  a.slot_embed = fptr(slot_embed); a.WT = fptr(WT); a.W = fptr(W); a.mu = fptr(mu);
+  a.slot_embed = fptr(slot_embed); a.WT = fptr(WT); a.PD = fptr(PD); a.mu = fptr(mu);
   a.slots0 = fptr(slots0); a.ages0 = fptr(ages0); a.usage0 = fptr(usage0);
   a.tau_r = (float)f[0]; a.tau_w = (float)f[1]; a.eps = (float)f[2]; a.cap = (float)f[3]; a.write_rel_floor = (float)f[4];
   a.usage_decay = (float)f[5]; a.age_ref = (float)f[6]; a.age_sigma = (float)f[7];
@@ -511,54 +514,63 @@ rk::ScreenScanArgs screen_args(const Tensor& q_r, const Tensor& q_w, const Tenso
   return a;
 }
 
-// returns u, slots_out, ages_out, usage_out, stats[9], saved_slots, saved_ages
+// returns u, slots_out, ages_out, usage_out, stats[9], saved_slots, saved_ages, saved_P
 std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const Tensor& delta_xh, const Tensor& delta_slot,
-                                    const Tensor& slot_embed, const Tensor& WT, const Tensor& W, const Tensor& mu,
+                                    const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
                                     bool save) {
   c10::cuda::CUDAGuard guard(q_r.device());
-  rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, W, mu, slots0, ages0, usage0, f,
+  rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
                                      write_enabled, value_unit_norm, age_mask);
   auto o = q_r.options();
+  const int J = 2 * a.dk + a.dv;
   Tensor u = torch::empty({a.B, a.T, a.dv}, o);
   Tensor so = torch::empty_like(slots0), ao = torch::empty_like(ages0), uo = torch::empty_like(usage0);
   Tensor stats = torch::zeros({9}, o);
   Tensor saved = save ? torch::empty({a.B, a.T, a.ds, 16}, o) : torch::empty({0}, o);
   Tensor saved_ages = save ? torch::empty({a.B, a.T, 16}, o) : torch::empty({0}, o);
+  Tensor saved_P = save ? torch::empty({a.B, a.T, 16, J}, o) : torch::empty({0}, o);
   a.u_out = u.data_ptr<float>(); a.slots_out = so.data_ptr<float>(); a.ages_out = ao.data_ptr<float>();
   a.usage_out = uo.data_ptr<float>(); a.stats = stats.data_ptr<float>();
   a.saved_slots = save ? saved.data_ptr<float>() : nullptr;
   a.saved_ages = save ? saved_ages.data_ptr<float>() : nullptr;
+  a.saved_P = save ? saved_P.data_ptr<float>() : nullptr;
   TORCH_CHECK(rk::screen_scan_forward(a, stream()) == 0, "screen_scan_forward failed");
-  return {u, so, ao, uo, stats, saved, saved_ages};
+  return {u, so, ao, uo, stats, saved, saved_ages, saved_P};
 }
 
-// returns d_q_r, d_q_w, d_delta_xh, d_delta_slot, d_slots0, d_mu, d_scalars[2], d_proj[B,T,16,J]
+// returns d q_r, d q_w, d delta_xh (direct part), d delta_slot (direct part), d slots0 (direct part), d mu,
+// d (tau_r, tau_w), d PD [B,T,16,J], d P0 [B,16,J]
 std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const Tensor& delta_xh, const Tensor& delta_slot,
-                                    const Tensor& slot_embed, const Tensor& WT, const Tensor& W, const Tensor& mu,
+                                    const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
-                                    const Tensor& saved, const Tensor& saved_ages, const Tensor& du,
+                                    const Tensor& saved, const Tensor& saved_ages, const Tensor& saved_P, const Tensor& du,
                                     const c10::optional<Tensor>& dslots_out) {
   c10::cuda::CUDAGuard guard(q_r.device());
-  rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, W, mu, slots0, ages0, usage0, f,
+  rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
                                      write_enabled, value_unit_norm, age_mask);
   auto o = q_r.options();
   const int J = 2 * a.dk + a.dv;
+  TORCH_CHECK(saved_P.numel() == (int64_t)a.B * a.T * 16 * J && saved.numel() == (int64_t)a.B * a.T * a.ds * 16,
+              "saved tensors do not match the problem size");
   Tensor dqr = torch::empty_like(q_r), dqw = torch::zeros_like(q_r), dxh = torch::empty_like(delta_xh);
   Tensor dds = torch::zeros_like(delta_slot), ds0 = torch::empty_like(slots0), dmu = torch::zeros_like(mu);
   Tensor dsc = torch::zeros({2}, o);
-  Tensor dproj = torch::empty({a.B, a.T, 16, J}, o);
+  Tensor dPD = torch::empty({a.B, a.T, 16, J}, o);
+  Tensor dP0 = torch::empty({a.B, 16, J}, o);
   a.saved_slots = const_cast<float*>(fptr(saved)); a.saved_ages = const_cast<float*>(fptr(saved_ages));
+  a.saved_P = const_cast<float*>(fptr(saved_P));
   a.du = fptr(du);
   Tensor dso;
   if (dslots_out.has_value() && dslots_out->defined()) { dso = dslots_out->contiguous().to(at::kFloat); a.dslots_out = dso.data_ptr<float>(); }
   a.d_q_r = dqr.data_ptr<float>(); a.d_q_w = dqw.data_ptr<float>(); a.d_delta_xh = dxh.data_ptr<float>();
-  a.d_proj = dproj.data_ptr<float>(); a.d_delta_slot = dds.data_ptr<float>(); a.d_slots0 = ds0.data_ptr<float>();
+  a.d_PD = dPD.data_ptr<float>(); a.d_P0 = dP0.data_ptr<float>();
+  a.d_delta_slot = dds.data_ptr<float>(); a.d_slots0 = ds0.data_ptr<float>();
   a.d_mu = dmu.data_ptr<float>(); a.d_scalars = dsc.data_ptr<float>();
   TORCH_CHECK(rk::screen_scan_backward(a, stream()) == 0, "screen_scan_backward failed");
-  return {dqr, dqw, dxh, dds, ds0, dmu, dsc, dproj};
+  return {dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0};
 }
 
 rk::TpPeers make_tp_peers(const std::vector<int64_t>& buf, int64_t buf_mc, const std::vector<int64_t>& aux, int64_t rank) {

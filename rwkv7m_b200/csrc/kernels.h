@@ -128,7 +128,8 @@ struct ScreenScanArgs {
   const float* delta_slot;      // [M,ds]
   const float* slot_embed;      // [M,ds]
   const float* WT;              // [ds][J]  transposed concatenation of k_proj_r | v_proj | k_proj_w, J = dk + dv + dk
-  const float* W;               // [J][ds]  the same weights, untransposed (backward)
+  const float* PD;              // [B,T,16,J] projections of every step's write target tanh(delta_xh + delta_slot)
+                                //            (+ slot_embed Wkw^T on the write-key columns); rows >= M are zero
   const float* mu;              // [M] per-slot write rate
   const float *slots0, *ages0, *usage0;   // [B,M,ds], [B,M], [B,M]
   float tau_r, tau_w, eps, cap, write_rel_floor, usage_decay, age_ref, age_sigma;
@@ -139,11 +140,13 @@ struct ScreenScanArgs {
   float* stats;                 // [9] running sums over batch rows and steps
   float* saved_slots;           // [B,T,ds,16] bank before each step (nullptr = inference)
   float* saved_ages;            // [B,T,16]
+  float* saved_P;               // [B,T,16,J] raw projections before each step
   // backward
   const float* du;              // [B,T,dv]
   const float* dslots_out;      // [B,M,ds] or nullptr
   float *d_q_r, *d_q_w, *d_delta_xh;      // [B,T,dk], [B,T,dk], [B,T,ds]
-  float* d_proj;                // [B,T,16,J] cotangent of the raw projections
+  float* d_PD;                  // [B,T,16,J] cotangent of PD
+  float* d_P0;                  // [B,16,J]   cotangent of the projections of the initial bank
   float* d_delta_slot;          // [M,ds]  accumulated with atomics (zeroed by the caller)
   float* d_slots0;              // [B,M,ds]
   float* d_mu;                  // [M]     atomics

@@ -7,11 +7,15 @@
 //   rel_r[m] = trim_square(q_r[t] . k_r[m], tau_r) (* age mask)      rel_w[m] = trim_square(q_w[t] . k_w[m], tau_w)
 //   u[t]    = tanh_norm(sum_m rel_r[m] val[m])                       (output; the out-projection is a GEMM outside)
 //   S[m]   += mu[m] * max(rel_w[m], floor) * (tanh(dxh[t] + dslot[m]) - S[m])     (rate mu[m] alone without write screening)
-// The three projections are one pass over the concatenated, transposed weight W^T [ds][J] (J = dk + dv + dk):
-// thread j streams column j (coalesced, L1-resident) against all 16 slots.
-// The backward kernel walks the steps in reverse from the saved per-step banks, recomputes the step, and returns
-// the gradients of q_r, q_w, dxh and dslot, the cotangent of the raw projections (from which the caller forms the
-// weight gradients with one GEMM) and the scalar gradients.
+// The raw projections P[m] = S[m] W^T (+ E[m] Wkw^T for the write keys; W^T [ds][J], J = dk + dv + dk) are never
+// recomputed inside the loop.  The slot update is an interpolation towards a vector that does not depend on the state,
+//   S_{t+1}[m] = S_t[m] + s_m (D_t[m] - S_t[m]),   D_t[m] = tanh(dxh[t] + dslot[m]),
+// and the projections are linear, so they obey the same recurrence:
+//   P_{t+1}[m] = P_t[m] + s_m (PD_t[m] - P_t[m]),  PD_t[m] = D_t[m] W^T (+ E[m] Wkw^T),
+// where PD for all steps is one GEMM done by the caller before the scan.  A step therefore costs O(M (ds + J)) instead
+// of O(M ds J).  The backward kernel walks the steps in reverse from the saved per-step S and P, carries the cotangents
+// of both, and returns the gradients of q_r, q_w, dxh, dslot (direct part), PD, the initial S and P, and the scalars;
+// the caller turns d PD into weight / dxh / dslot gradients with GEMMs over all steps at once.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -33,6 +37,7 @@ struct ScanSmem {
   float* St;     // [ds][16]   slots, transposed
   float* DSt;    // [ds][16]   delta_slot, transposed
   float* P;      // [16][256]  raw projections of the current step
+  float* PD;     // [16][256]  projections of the step's write target
   float* EW;     // [16][dk]   slot_embed Wkw^T
   float* qr;     // [dk]
   float* qw;     // [dk]
@@ -49,6 +54,7 @@ __device__ __forceinline__ ScanSmem carve(float* base, int ds, int dk, int dv) {
   s.St = base; base += ds * kMp;
   s.DSt = base; base += ds * kMp;
   s.P = base; base += kMp * kJp;
+  s.PD = base; base += kMp * kJp;
   s.EW = base; base += kMp * dk;
   s.qr = base; base += dk;
   s.qw = base; base += dk;
@@ -62,7 +68,7 @@ __device__ __forceinline__ ScanSmem carve(float* base, int ds, int dk, int dv) {
 }
 
 __host__ __device__ inline int scan_smem_floats(int ds, int dk, int dv) {
-  return 2 * ds * kMp + kMp * kJp + kMp * dk + 2 * dk + ds + dv + kMp * 8 + 3 * kMp;
+  return 2 * ds * kMp + 2 * kMp * kJp + kMp * dk + 2 * dk + ds + dv + kMp * 8 + 3 * kMp;
 }
 
 // raw projections of all slots: P[m][j] = sum_d St[d][m] * WT[d][j]  (+ EW for the write keys)
@@ -128,13 +134,9 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
   const int b = blockIdx.x;
   const int J = 2 * a.dk + a.dv;
   const int nel = a.ds * kMp;
-  // the projection weights live in shared memory (row stride J + 1) when they fit, else they stream through L1 / L2
-  float* Wsm = smem_f + scan_smem_floats(a.ds, a.dk, a.dv);
-  const float* WTp = SMEM_W ? Wsm : a.WT;
-  const int wstride = SMEM_W ? J + 1 : J;
-  if (SMEM_W) {
-    for (int e = tid; e < a.ds * J; e += kThreads) Wsm[(e / J) * wstride + e % J] = a.WT[e];
-  }
+  // the projection weights are only needed for the initial bank: they stream through L1 / L2 once
+  const float* WTp = a.WT;
+  const int wstride = J;
 
   // ---- load the bank, delta_slot and the slot embedding (all transposed to [d][16]) ----------------------------------
   for (int e = tid; e < nel; e += kThreads) {
@@ -162,29 +164,47 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
   for (int i = 0; i < 9; ++i) st_acc[i] = 0.f;
   __syncthreads();
 
-  // the step's vectors are fetched one step ahead into registers (thread tid: q_r / q_w element tid, delta_xh element tid)
+  // projections of the initial bank (the only pass over the weights); afterwards they follow the slot recurrence
+  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
+
+  // the step's vectors are fetched one step ahead into registers (thread tid: q_r / q_w element tid, delta_xh element tid,
+  // column tid of the write target's projections for all 16 slots)
   float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f;
+  float n_pd[kMp];
+#pragma unroll
+  for (int m = 0; m < kMp; ++m) n_pd[m] = 0.f;
   auto fetch = [&](int t) {
     const size_t bt = (size_t)b * a.T + t;
     if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
     if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
+    if (tid < J) {
+      const float* src = a.PD + bt * kMp * J + tid;
+#pragma unroll
+      for (int m = 0; m < kMp; ++m) n_pd[m] = src[m * J];
+    }
   };
   fetch(0);
   for (int t = 0; t < a.T; ++t) {
     const size_t bt = (size_t)b * a.T + t;
-    // ---- stage the step's vectors; save the bank for the backward pass ------------------------------------------------
+    // ---- stage the step's vectors; save the bank and its projections for the backward pass -------------------------------
     if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
     if (tid < a.ds) s.dxh[tid] = n_dx;
+    float pd[kMp];
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) pd[m] = n_pd[m];
     if (t + 1 < a.T) fetch(t + 1);
+    if (tid < kMp) s.upd[tid] = 0.f;
+    __syncthreads();   // s.P and s.St of this step are complete (written at the end of the previous iteration)
     if (a.saved_slots != nullptr) {
       float* dst = a.saved_slots + bt * nel;
       for (int e = tid; e < nel; e += kThreads) dst[e] = s.St[e];
       if (tid < kMp) a.saved_ages[bt * kMp + tid] = s.ages[tid];
+      if (tid < J) {
+        float* dp = a.saved_P + bt * kMp * J + tid;
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) dp[m * J] = s.P[m * kJp + tid];
+      }
     }
-    if (tid < kMp) s.upd[tid] = 0.f;
-    __syncthreads();
-    project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
-    __syncthreads();
     slot_scalars(s, a, warp, lane);
     __syncthreads();
     // ---- read-out ----------------------------------------------------------------------------------------------------------
@@ -215,6 +235,13 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
         un = fmaf(nw - old, nw - old, un);
       }
       atomicAdd(&s.upd[m], un);
+    }
+    if (tid < J) {   // the projections follow the same interpolation
+#pragma unroll
+      for (int mm = 0; mm < kMp; ++mm) {
+        const float old = s.P[mm * kJp + tid];
+        s.P[mm * kJp + tid] = fmaf(s.sc[mm * 8 + 7], pd[mm] - old, old);
+      }
     }
     __syncthreads();
     if (tid < kMp && tid < a.M) {
@@ -258,7 +285,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
 namespace {
 
 __host__ __device__ inline int scan_bwd_smem_floats(int ds, int dk, int dv) {
-  return scan_smem_floats(ds, dk, dv) + ds * kMp /*dSt*/ + kJp * kMp /*dPt*/ + 2 * dv /*du, dz*/ + kMp * 4 /*dstr, dsimr, dsimw, pad*/;
+  return scan_smem_floats(ds, dk, dv) + ds * kMp /*dSt*/ + kJp * kMp /*dPc*/ + 2 * dv /*du, dz*/ + kMp * 4 /*dstr, dsimr, dsimw, pad*/;
 }
 
 template <bool SMEM_W>
@@ -267,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
   const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
   float* extra = smem_f + scan_smem_floats(a.ds, a.dk, a.dv);
   float* dSt = extra; extra += a.ds * kMp;      // [ds][16] cotangent of the bank after the current step
-  float* dPt = extra; extra += kJp * kMp;       // [J][16]  cotangent of the raw projections, transposed
+  float* dPc = extra; extra += kJp * kMp;       // [16][256] cotangent of the carried raw projections
   float* du = extra; extra += a.dv;
   float* dz = extra; extra += a.dv;
   float* dstr = extra; extra += kMp;            // cotangent of the write strength
@@ -278,24 +305,14 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
   const int J = 2 * a.dk + a.dv;
   const int nel = a.ds * kMp;
   const float e2 = a.eps * a.eps;
-  float* Wsm = extra + kMp;   // after the scratch arrays; one padded copy of W^T serves both the projections and their backward
-  const float* WTp = SMEM_W ? Wsm : a.WT;
-  const int wstride = SMEM_W ? J + 1 : J;
-  if (SMEM_W) {
-    for (int e = tid; e < a.ds * J; e += kThreads) Wsm[(e / J) * wstride + e % J] = a.WT[e];
-  }
 
   for (int e = tid; e < nel; e += kThreads) {
     const int d = e / kMp, m = e % kMp;
     const bool live = m < a.M;
-    s.St[e] = live ? a.slot_embed[m * a.ds + d] : 0.f;
     s.DSt[e] = live ? a.delta_slot[m * a.ds + d] : 0.f;
     dSt[e] = (live && a.dslots_out != nullptr) ? a.dslots_out[((size_t)b * a.M + m) * a.ds + d] : 0.f;
   }
-  __syncthreads();
-  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, false);
-  __syncthreads();
-  for (int e = tid; e < kMp * a.dk; e += kThreads) s.EW[e] = s.P[(e / a.dk) * kJp + a.dk + a.dv + e % a.dk];
+  for (int e = tid; e < kMp * kJp; e += kThreads) dPc[e] = 0.f;   // the projections after the last step feed nothing
   float dslot_acc[16];          // this thread's elements of d(delta_slot): e = tid + 256 i
 #pragma unroll
   for (int i = 0; i < 16; ++i) dslot_acc[i] = 0.f;
@@ -317,13 +334,17 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       const float* src = a.saved_slots + bt * nel;
       for (int e = tid; e < nel; e += kThreads) s.St[e] = src[e];
     }
+    if (tid < J) {   // the step's projections (saved by the forward pass) and those of its write target
+      const float* sp = a.saved_P + bt * kMp * J + tid;
+      const float* pp = a.PD + bt * kMp * J + tid;
+#pragma unroll
+      for (int m = 0; m < kMp; ++m) { s.P[m * kJp + tid] = sp[m * J]; s.PD[m * kJp + tid] = pp[m * J]; }
+    }
     if (tid < kMp) { s.ages[tid] = a.saved_ages[bt * kMp + tid]; dstr[tid] = 0.f; }
     if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
     if (tid < a.ds) s.dxh[tid] = n_dx;
     if (tid < a.dv) du[tid] = n_du;
     if (t > 0) fetch(t - 1);
-    __syncthreads();
-    project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
     __syncthreads();
     slot_scalars(s, a, warp, lane);
     __syncthreads();
@@ -338,8 +359,10 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       const int m = tid % kMp;
       const float strength = s.sc[m * 8 + 7];
       float dsp = 0.f;
-      int i = 0;
-      for (int e = tid; e < nel; e += kThreads, ++i) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {   // constant trip count keeps dslot_acc in registers; nel is a multiple of 256
+        const int e = tid + i * kThreads;
+        if (e >= nel) break;
         const int d = e / kMp;
         const float old = s.St[e];
         const float delta = tanhf(s.dxh[d] + s.DSt[e]);
@@ -355,6 +378,22 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
         if (m == 0) a.d_delta_xh[bt * a.ds + d] = r;
       }
       atomicAdd(&dstr[m], dsp);
+    }
+    // ---- backward of the projection update P' = P + s (PD - P): warp w owns slots 2w and 2w+1 -------------------------------
+    for (int mm = 0; mm < 2; ++mm) {
+      const int m = warp * 2 + mm;
+      const float strength = s.sc[m * 8 + 7];
+      float* gp = dPc + m * kJp;
+      float* out = a.d_PD + (bt * kMp + m) * J;
+      float dsp = 0.f;
+      for (int j = lane; j < J; j += 32) {
+        const float g = gp[j];
+        dsp = fmaf(g, s.PD[m * kJp + j] - s.P[m * kJp + j], dsp);
+        out[j] = strength * g;
+        gp[j] = (1.f - strength) * g;
+      }
+      dsp = warp_sum(dsp);
+      if (lane == 0) atomicAdd(&dstr[m], dsp);
     }
     __syncthreads();
     // ---- cotangent of z from the cotangent of u = f(n) z ---------------------------------------------------------------------
@@ -400,19 +439,16 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       } else if (lane == 0) {
         dsimr[m] = 0.f; dsimw[m] = 0.f;
       }
-      float* out = a.d_proj + (bt * kMp + m) * J;
+      float* gp = dPc + m * kJp;   // same warp and lanes as the scaling above: no barrier needed in between
       for (int j = lane; j < a.dk; j += 32) {   // read keys: k = x / nk, sim = q . k
-        const float g = live ? dsr * (s.qr[j] - Pm[j] / nk * simr) / nk : 0.f;
-        dPt[j * kMp + m] = g; out[j] = g;
+        if (live) gp[j] += dsr * (s.qr[j] - Pm[j] / nk * simr) / nk;
       }
       for (int v = lane; v < a.dv; v += 32) {   // values
         const float val = Pm[a.dk + v] / nv;
-        const float g = live ? (a.value_unit_norm ? relr * (dz[v] - val * drelr) / nv : relr * dz[v]) : 0.f;
-        dPt[(a.dk + v) * kMp + m] = g; out[a.dk + v] = g;
+        if (live) gp[a.dk + v] += a.value_unit_norm ? relr * (dz[v] - val * drelr) / nv : relr * dz[v];
       }
       for (int j = lane; j < a.dk; j += 32) {   // write keys
-        const float g = (live && a.write_enabled) ? dsw * (s.qw[j] - Pm[a.dk + a.dv + j] / nw * simw) / nw : 0.f;
-        dPt[(a.dk + a.dv + j) * kMp + m] = g; out[a.dk + a.dv + j] = g;
+        if (live && a.write_enabled) gp[a.dk + a.dv + j] += dsw * (s.qw[j] - Pm[a.dk + a.dv + j] / nw * simw) / nw;
       }
     }
     __syncthreads();
@@ -427,37 +463,21 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       a.d_q_r[bt * a.dk + tid] = gr;
       if (a.write_enabled) a.d_q_w[bt * a.dk + tid] = gw;
     }
-    // ---- projections backward into the bank: dS[m][d] += sum_j dP[m][j] W[j][d]; the j range is split over 256/ds groups ------
-    {
-      const int groups = kThreads / a.ds > 0 ? kThreads / a.ds : 1;
-      const int grp = tid / a.ds, d = tid % a.ds;
-      if (grp < groups) {
-        const int j0 = (J * grp) / groups, j1 = (J * (grp + 1)) / groups;
-        float acc[kMp];
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) acc[m] = 0.f;
-        for (int j = j0; j < j1; ++j) {
-          const float w = SMEM_W ? Wsm[d * wstride + j] : __ldg(a.W + (size_t)j * a.ds + d);
-          const float4* gp = reinterpret_cast<const float4*>(dPt + j * kMp);
-          const float4 x = gp[0], y = gp[1], z4 = gp[2], u4 = gp[3];
-          acc[0] = fmaf(w, x.x, acc[0]); acc[1] = fmaf(w, x.y, acc[1]); acc[2] = fmaf(w, x.z, acc[2]); acc[3] = fmaf(w, x.w, acc[3]);
-          acc[4] = fmaf(w, y.x, acc[4]); acc[5] = fmaf(w, y.y, acc[5]); acc[6] = fmaf(w, y.z, acc[6]); acc[7] = fmaf(w, y.w, acc[7]);
-          acc[8] = fmaf(w, z4.x, acc[8]); acc[9] = fmaf(w, z4.y, acc[9]); acc[10] = fmaf(w, z4.z, acc[10]); acc[11] = fmaf(w, z4.w, acc[11]);
-          acc[12] = fmaf(w, u4.x, acc[12]); acc[13] = fmaf(w, u4.y, acc[13]); acc[14] = fmaf(w, u4.z, acc[14]); acc[15] = fmaf(w, u4.w, acc[15]);
-        }
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) atomicAdd(&dSt[d * kMp + m], acc[m]);
-      }
-    }
     __syncthreads();
+  }
+  // cotangent of the initial projections: the caller folds it into d slots0, d W and d slot_embed
+  if (tid < J) {
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) a.d_P0[((size_t)b * kMp + m) * J + tid] = dPc[m * kJp + tid];
   }
   for (int e = tid; e < nel; e += kThreads) {
     const int d = e / kMp, m = e % kMp;
     if (m < a.M) a.d_slots0[((size_t)b * a.M + m) * a.ds + d] = dSt[e];
   }
-  {
-    int i = 0;
-    for (int e = tid; e < nel; e += kThreads, ++i) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int e = tid + i * kThreads;
+    if (e < nel) {
       const int d = e / kMp, m = e % kMp;
       if (m < a.M) atomicAdd(a.d_delta_slot + m * a.ds + d, dslot_acc[i]);
     }
@@ -478,30 +498,18 @@ bool screen_scan_supported(const ScreenScanArgs& a) {
 }
 
 int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a)) return 1;
-  const size_t base = (size_t)scan_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
-  const size_t wbytes = (size_t)a.ds * (2 * a.dk + a.dv + 1) * sizeof(float);
-  if (base + wbytes <= 200 * 1024) {
-    cudaFuncSetAttribute(screen_scan_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(base + wbytes));
-    screen_scan_fwd_kernel<true><<<a.B, kThreads, base + wbytes, st>>>(a);
-  } else {
-    cudaFuncSetAttribute(screen_scan_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)base);
-    screen_scan_fwd_kernel<false><<<a.B, kThreads, base, st>>>(a);
-  }
+  if (!screen_scan_supported(a) || a.PD == nullptr) return 1;
+  const size_t bytes = (size_t)scan_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
+  cudaFuncSetAttribute(screen_scan_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  screen_scan_fwd_kernel<false><<<a.B, kThreads, bytes, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a)) return 1;
-  const size_t base = (size_t)(scan_bwd_smem_floats(a.ds, a.dk, a.dv) + kMp) * sizeof(float);
-  const size_t wbytes = (size_t)a.ds * (2 * a.dk + a.dv + 1) * sizeof(float);
-  if (base + wbytes <= 200 * 1024) {
-    cudaFuncSetAttribute(screen_scan_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(base + wbytes));
-    screen_scan_bwd_kernel<true><<<a.B, kThreads, base + wbytes, st>>>(a);
-  } else {
-    cudaFuncSetAttribute(screen_scan_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)base);
-    screen_scan_bwd_kernel<false><<<a.B, kThreads, base, st>>>(a);
-  }
+  if (!screen_scan_supported(a) || a.PD == nullptr || a.saved_P == nullptr) return 1;
+  const size_t bytes = (size_t)(scan_bwd_smem_floats(a.ds, a.dk, a.dv) + kMp) * sizeof(float);
+  cudaFuncSetAttribute(screen_scan_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  screen_scan_bwd_kernel<false><<<a.B, kThreads, bytes, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -512,9 +512,31 @@ def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
     return totals
 
 
+def _screen_write_targets(delta_xh, delta_slot, slot_embed, W, dk, dv):
+    """D[b,t,m] = tanh(delta_xh[b,t] + delta_slot[m]) and its raw projections PD = D W^T, with slot_embed Wkw^T added
+    on the write-key columns and the slot axis zero-padded to 16 (the layout the scan kernels read)."""
+    B, T, ds = delta_xh.shape
+    M, J = delta_slot.shape[0], W.shape[0]
+    D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])          # [B,T,M,ds]
+    PD = torch.empty(B, T, 16, J, dtype=torch.float32, device=delta_xh.device)
+    if M == 16:
+        torch.matmul(D.view(B * T * 16, ds), W.t(), out=PD.view(B * T * 16, J))
+    else:
+        PD[:, :, :M] = D @ W.t()
+        PD[:, :, M:] = 0
+    PD[:, :, :M, dk + dv:] += slot_embed @ W[dk + dv:].t()
+    return D, PD
+
+
 class ScreenScanFn(torch.autograd.Function):
     """Slot scan of the screening memory (csrc/screening.cu).  Differentiable inputs: q_r, q_w, delta_xh,
-    delta_slot, slot_embed, the three projection weights, mu, tau_r, tau_w and the initial slots."""
+    delta_slot, slot_embed, the three projection weights, mu, tau_r, tau_w and the initial slots.
+
+    The slot update interpolates every slot towards a target that does not depend on the state, so the raw
+    projections of the bank follow the same recurrence as the bank itself; the projections of all targets are one
+    fp32 GEMM over every (batch, step, slot) row here, and the kernels never multiply by the weights inside the loop.
+    The backward kernel returns the cotangent of those target projections, which two more GEMMs turn into the weight,
+    delta_xh and delta_slot gradients."""
 
     @staticmethod
     def forward(ctx, q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, tau_r, tau_w, slots0, ages0,
@@ -522,40 +544,49 @@ class ScreenScanFn(torch.autograd.Function):
         f32 = lambda t: t.detach().float().contiguous()
         W = torch.cat([f32(w_kr), f32(w_v), f32(w_kw)], dim=0).contiguous()
         WT = W.t().contiguous()
+        dk, dv = w_kr.shape[0], w_v.shape[0]
         floats = [float(tau_r), float(tau_w), settings["eps"], settings["cap"], settings["floor"],
                   settings["usage_decay"], settings["age_ref"], settings["age_sigma"]]
         flags = (bool(settings["write_enabled"]), bool(settings["value_unit_norm"]), bool(settings["age_mask"]))
-        tensors = [f32(q_r), f32(q_w), f32(delta_xh), f32(delta_slot), f32(slot_embed), WT, W, f32(mu),
-                   f32(slots0), f32(ages0), f32(usage0)]
+        dxh32, dds32, E32 = f32(delta_xh), f32(delta_slot), f32(slot_embed)
+        _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv)
+        tensors = [f32(q_r), f32(q_w), dxh32, dds32, E32, WT, PD, f32(mu), f32(slots0), f32(ages0), f32(usage0)]
         need_grad = any(ctx.needs_input_grad)
-        u, so, ao, uo, stats, saved, saved_ages = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad)
+        u, so, ao, uo, stats, saved, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad)
         _count()
         ctx.floats, ctx.flags = floats, flags
-        ctx.dk, ctx.dv, ctx.M = w_kr.shape[0], w_v.shape[0], slots0.shape[1]
+        ctx.dk, ctx.dv, ctx.M = dk, dv, slots0.shape[1]
         ctx.dtypes = [t.dtype for t in (q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, slots0)]
         if need_grad:
-            ctx.save_for_backward(*tensors, saved, saved_ages)
+            ctx.save_for_backward(*tensors, W, saved, saved_ages, saved_P)
         ctx.mark_non_differentiable(ao, uo, stats)
         return u, so, ao, uo, stats
 
     @staticmethod
     def backward(ctx, du, dso, *_):
-        *tensors, saved, saved_ages = ctx.saved_tensors
-        dqr, dqw, dxh, dds, ds0, dmu, dsc, dproj = _C.screen_scan_bwd(
-            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, du.float().contiguous(), dso)
+        *tensors, W, saved, saved_ages, saved_P = ctx.saved_tensors
+        dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0 = _C.screen_scan_bwd(
+            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, saved_P, du.float().contiguous(), dso)
         _count()
-        slot_embed, W = tensors[4], tensors[6]
+        delta_xh, delta_slot, slot_embed, slots0 = tensors[2], tensors[3], tensors[4], tensors[8]
         dk, dv, M = ctx.dk, ctx.dv, ctx.M
-        B, T, ds, _ = saved.shape
+        B, T, ds = delta_xh.shape
         J = W.shape[0]
-        # weight gradients: one GEMM over all (batch, step, slot) rows of the projection cotangents
-        P2 = dproj.reshape(B * T * 16, J)
-        S2 = saved.permute(0, 1, 3, 2).reshape(B * T * 16, ds)
-        dW = P2.t() @ S2
-        psum = dproj.sum(dim=(0, 1))[:M]                      # [M, J]
         kw = slice(dk + dv, J)
-        dW[kw] += psum[:, kw].t() @ slot_embed                 # the write keys see S + E
-        dE = psum[:, kw] @ W[kw]
+        D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])       # recomputed, [B,T,M,ds]
+        g = dPD[:, :, :M]                                                              # [B,T,M,J]
+        g2, D2 = g.reshape(-1, J), D.reshape(-1, ds)
+        # targets: PD = D W^T (+ E Wkw^T); initial bank: P0 = S0 W^T (+ E Wkw^T)
+        g0 = dP0[:, :M]                                                                # [B,M,J]
+        dW = g2.t() @ D2 + g0.reshape(-1, J).t() @ slots0.reshape(-1, ds)
+        dD = (g2 @ W).view(B, T, M, ds)
+        dpre = dD * (1.0 - D * D)
+        dxh = dxh + dpre.sum(dim=2)
+        dds = dds + dpre.sum(dim=(0, 1))
+        ds0 = ds0 + g0 @ W
+        dEW = g[..., kw].sum(dim=(0, 1)) + g0[..., kw].sum(dim=0)                     # [M, dk]
+        dW[kw] += dEW.t() @ slot_embed
+        dE = dEW @ W[kw]
         dt = ctx.dtypes
         grads = [dqr.to(dt[0]), dqw.to(dt[1]) if ctx.flags[0] else None, dxh.to(dt[2]), dds.to(dt[3]), dE.to(dt[4]),
                  dW[:dk].to(dt[5]), dW[dk:dk + dv].to(dt[6]), dW[kw].to(dt[7]) if ctx.flags[0] else None, dmu.to(dt[8]),
