@@ -486,6 +486,45 @@ int64_t dp_step(const std::vector<int64_t>& grad, const std::vector<int64_t>& ma
   return (int64_t)b;
 }
 
+// ---- ZeRO-3 building blocks: the same kernels as the fused data-parallel step, launched unit by unit ----------------------
+static rk::DpPeers aux_only_peers(const std::vector<int64_t>& aux) {
+  TORCH_CHECK(aux.size() >= 1 && aux.size() <= (size_t)rk::kMaxRanks, "bad peer list");
+  rk::DpPeers p{};
+  for (size_t i = 0; i < aux.size(); ++i) p.aux[i] = reinterpret_cast<void*>(aux[i]);
+  return p;
+}
+
+// Device barrier over the symmetric scratch words; target = number of barriers issued so far + 1 (same on every rank).
+void dp_barrier_only(const std::vector<int64_t>& aux, int64_t rank, int64_t target, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  rk::DpPeers p = aux_only_peers(aux);
+  rk::dp_barrier(p, (int)rank, (int)aux.size(), (uint32_t)target, -1, stream());
+}
+
+// out[r * n + i] = src[r][i] for every rank r (bf16, n a multiple of 8): all-gather of parameter pieces by peer loads.
+void zero_gather(const std::vector<int64_t>& src, Tensor out, int64_t n) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 && n % 8 == 0 && n > 0);
+  TORCH_CHECK(out.numel() >= n * (int64_t)src.size() && n < (int64_t)1 << 31, "gather output too small");
+  TORCH_CHECK(src.size() >= 1 && src.size() <= (size_t)rk::kMaxRanks, "bad peer list");
+  rk::TpPeers p{};
+  for (size_t i = 0; i < src.size(); ++i) p.buf[i] = reinterpret_cast<const void*>(src[i]);
+  p.world = (int)src.size();
+  rk::tp_gather_seq(p, out.data_ptr(), 1, 1, (int)n, stream());
+}
+
+// Sum elements [begin, end) of every rank's fp32 gradient buffer into this rank's own buffer (multimem.ld_reduce when a
+// multicast address is given, else peer loads).  The caller frames it with barriers.
+void zero_reduce(const std::vector<int64_t>& grad, const std::vector<int64_t>& aux, int64_t grad_mc, int64_t rank,
+                 int64_t begin, int64_t end, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  TORCH_CHECK(grad.size() == aux.size() && begin % 4 == 0 && end % 4 == 0 && begin <= end);
+  rk::DpPeers p = aux_only_peers(aux);
+  for (size_t i = 0; i < grad.size(); ++i) p.grad[i] = reinterpret_cast<void*>(grad[i]);
+  p.grad_mc = reinterpret_cast<void*>(grad_mc);
+  rk::dp_reduce_shard(p, (int)rank, (int)grad.size(), begin, end, stream());
+}
+
 static const float* fptr(const Tensor& t) {
   TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kFloat, "screening scan tensors must be contiguous fp32 CUDA tensors");
   return t.data_ptr<float>();
@@ -678,6 +717,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_bwd", &ce_bwd);
   m.def("dp_step", &dp_step);
   m.def("dp_step_timings", &dp_step_timings);
+  m.def("dp_barrier_only", &dp_barrier_only);
+  m.def("zero_gather", &zero_gather);
+  m.def("zero_reduce", &zero_reduce);
   m.def("screen_scan_fwd", &screen_scan_fwd);
   m.def("screen_scan_bwd", &screen_scan_bwd);
   m.def("tp_gather_seq", &tp_gather_seq);

@@ -84,7 +84,14 @@ class ScreenedRWKVModel(nn.Module):
             if cfg.screening_active:
                 raise NotImplementedError("screening memory is not sharded yet: run screened models data-parallel")
             input_ids = tp.local_time_slice(input_ids)  # the residual stream is sharded over time
+        # parameter-sharding engine (ZeRO-3): told before a unit's weights are used; marks on the residual stream tell it
+        # when a unit's backward starts and ends
+        hook = getattr(self, "unit_hook", None)
+        if hook is not None:
+            hook.pre_forward(hook.unit_of("emb"))
         x = ops.embedding(input_ids, self.emb.weight, self.compute_dtype)
+        if hook is not None:
+            x = hook.mark_leave(x, hook.unit_of("emb"))
         screened_idx = {layer: i for i, layer in enumerate(cfg.screening.screened_layers)} if cfg.use_screening else {}
         v_first = torch.zeros_like(x)
         new_rwkv = list(rwkv_state)
@@ -92,10 +99,15 @@ class ScreenedRWKVModel(nn.Module):
         all_stats = []
         for idx, layer in enumerate(self.layers):
             scr = screen_state.layers[screened_idx[idx]] if idx in screened_idx else None
+            if hook is not None:
+                hook.pre_forward(hook.unit_of_layer(idx))
+                x = hook.mark_enter(x, hook.unit_of_layer(idx))
             if (cfg.remat_blocks or idx < self.remat_layer_count) and torch.is_grad_enabled():
                 x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
             else:
                 x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)
+            if hook is not None:
+                x = hook.mark_leave(x, hook.unit_of_layer(idx))
             new_rwkv[idx] = rwkv_l
             if idx in screened_idx:
                 new_screen[screened_idx[idx]] = scr_l
@@ -113,6 +125,10 @@ class ScreenedRWKVModel(nn.Module):
                 f"hidden final dimension must equal config.d_model, got {hidden.shape[-1]} and {self.config.d_model}"
             )
         tp = getattr(self, "tp", None)
+        hook = getattr(self, "unit_hook", None)
+        if hook is not None:
+            hook.pre_forward(hook.unit_of("head"))
+            hidden = hook.mark_enter(hidden, hook.unit_of("head"))
         h = self.ln_out(hidden)
         if tp is not None:
             h = tp.gather_seq(h)
@@ -128,9 +144,15 @@ class ScreenedRWKVModel(nn.Module):
         tp = getattr(self, "tp", None)
         if tp is not None:
             return self._tp_training_loss(hidden, targets, mask, chunk, tp)
+        hook = getattr(self, "unit_hook", None)
+        if hook is not None:
+            hook.pre_forward(hook.unit_of("head"))
+            hidden = hook.mark_enter(hidden, hook.unit_of("head"))
         ce_total, ce_count, l2_total, l2_count = ops.head_loss(
             hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, targets, mask, chunk, self.ln_out.eps
         )
+        if hook is not None:
+            ce_total = hook.mark_leave(ce_total, hook.unit_of("head"))
         return {"ce_total": ce_total, "ce_count": ce_count, "l2_total": l2_total, "l2_count": l2_count}
 
     def _tp_training_loss(self, hidden, targets, mask, chunk, tp):

@@ -54,3 +54,26 @@ def test_tensor_parallel_matches_single_gpu():
         r = res[key]
         assert r["gather_exact"] and r["rs_max_err"] < 0.05 and r["error_code"] == 0, res
         assert r["gemm_rs_max_err"] < 0.02 * r["gemm_rs_scale"] + 0.05, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("accum", [1, 2])
+def test_zero3_matches_allreduce(accum):
+    import os
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29535", str(Path(__file__).with_name("zero3_worker.py"))]
+    env = dict(os.environ, ZERO3_ACCUM=str(accum), NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert res["error_code"] == 0
+    assert res["rank_spread"] == 0.0
+    assert res["max_param_diff"] < 5e-3, res
+    assert res["rel_l2_diff"] < 2e-3, res
+    assert res["moment_rel_l2_diff"] < 2e-2, res
+    assert abs(res["norm_ref"] - res["norm_zero3"]) < 2e-3 * max(res["norm_ref"], 1e-6), res
+    for a, b in zip(res["loss_ref"], res["loss_zero3"]):
+        assert abs(a - b) < 5e-3 * abs(a)
+    # every rank holds its pieces of the bulk weights plus the replicated small leaves, not the whole model
+    assert res["master_elements_held"] < 0.75 * res["master_elements_replicated"]
