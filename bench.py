@@ -39,7 +39,9 @@ def parse_args(argv=None):
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--remat", default="auto", choices=["auto", "on", "off"])
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
-    ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--dp", default="fused", choices=["fused", "nccl", "zero3"],
+                    help="fused: replicated weights, sharded optimizer step over NVLink; nccl: all-reduce baseline; "
+                         "zero3: parameters, gradients and optimizer state sharded, per-layer gather / reduce-scatter")
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
                     help="dp: weak scaling, --batch sequences per GPU; tp: tensor parallel over all GPUs, --batch = global batch")
     ap.add_argument("--tp-comm", default="fused", choices=["fused", "fused-separate", "nccl"],
@@ -224,8 +226,14 @@ def main(argv=None):
             if use_tp:
                 trainer = tp   # create_train_runtime installed the tensor-parallel step
             else:
-                mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
-                trainer = DataParallelTrainer(train_state, mode=mode)
+                if world > 1 and args.dp == "zero3":
+                    from rwkv7m_b200.parallel.zero3 import Zero3Engine
+
+                    DataParallelTrainer(train_state, mode="allreduce").broadcast_parameters()
+                    trainer = Zero3Engine(train_state)
+                else:
+                    mode = "single" if world == 1 else ("fused" if args.dp == "fused" else "allreduce")
+                    trainer = DataParallelTrainer(train_state, mode=mode)
             if args.phases and hasattr(trainer, "record_phases"):
                 trainer.record_phases = True
             dev_batches = [make_batch(False) for _ in range(2)]

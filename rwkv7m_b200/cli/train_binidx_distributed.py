@@ -31,6 +31,7 @@ from ..parallel.checkpoint import (
     restore_distributed_runtime_state,
     restore_distributed_train_state,
     rotate_checkpoints,
+    normalize_backend,
     save_data_parallel_checkpoint,
 )
 from ..parallel.dp import DataParallelTrainer
@@ -87,7 +88,9 @@ def parse_args(argv=None):
     p.add_argument("--mesh-axis-names", nargs="+", default=["data"])
     p.add_argument("--mesh-axis-sizes", type=int, nargs="+", default=None)
     p.add_argument("--param-axis-name", default=None)
-    p.add_argument("--dp-mode", choices=["fused", "allreduce"], default="allreduce")
+    p.add_argument("--dp-mode", choices=["fused", "allreduce", "zero3"], default="allreduce",
+                   help="fused: sharded optimizer step over NVLink; zero3: parameters, gradients and optimizer state "
+                        "sharded with per-layer gather / reduce-scatter (single checkpoint backend)")
     p.add_argument("--device", default="auto")
     p.add_argument("--collective-timeout-s", type=float, default=600.0,
                    help="process-group timeout: a rank that stops answering ends the others' next collective with an error")
@@ -256,7 +259,10 @@ def run_distributed_training(args):
         args.seed, cfg, batch_size=B, total_steps=max(start_step + args.steps, 1), device=device,
         shard_multiple=max(world, 1) * 8, buffer_allocator=alloc,
     )
-    trainer = DataParallelTrainer(train_state, mode=mode)
+    zero3 = mode == "zero3"
+    if zero3 and normalize_backend(args.checkpoint_backend) != "single":
+        raise ValueError("--dp-mode zero3 writes checkpoints with --checkpoint-backend single")
+    trainer = DataParallelTrainer(train_state, mode="allreduce" if zero3 else mode)
     if trainer.fused is not None:
         train_state.extras["fused_optimizer"] = trainer.fused
     if args.resume:
@@ -268,6 +274,11 @@ def run_distributed_training(args):
                 runtime.rwkv_state, runtime.screen_state = st["rwkv_state"], st["screen_state"]
             elif rank == 0:
                 print("runtime state not found; carry-state resume starts from zero runtime state")
+    engine = None
+    if zero3:   # shard after a possible restore, so the pieces start from the restored masters and moments
+        from ..parallel.zero3 import Zero3Engine
+
+        engine = Zero3Engine(train_state)
 
     def say(msg):
         if rank == 0:
@@ -376,6 +387,8 @@ def run_distributed_training(args):
             last_ckpt = save(final)
         if trainer.fused is not None and trainer.fused.error_code() != 0:
             raise RuntimeError(f"a bounded wait on a peer GPU ran out (code {trainer.fused.error_code():#x})")
+        if engine is not None and engine.error_code() != 0:
+            raise RuntimeError(f"a bounded wait on a peer GPU ran out (code {engine.error_code():#x})")
         summary.update(status="completed", ended_at=_now())
         _write_summary(args, info, summary)
     except BaseException as exc:

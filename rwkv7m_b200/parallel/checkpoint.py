@@ -124,6 +124,18 @@ def save_data_parallel_checkpoint(checkpoint_dir, train_state, config, process_i
     backend = normalize_backend(backend)
     rank, world = _world(process_info)
     checkpoint_dir = Path(checkpoint_dir)
+    zero3 = train_state.extras.get("zero3")
+    if zero3 is not None:
+        # parameters and moments are sharded piece by piece: gather them into the replicated layout for the writer
+        if backend != "single":
+            raise ValueError("a ZeRO-3 train state is saved with the 'single' checkpoint backend")
+        with zero3.materialized():
+            if rank == 0:
+                save_train_checkpoint(checkpoint_dir, train_state, config, rng_key=rng_key,
+                                      dataset_position=dataset_position, metadata=metadata, runtime_state=runtime_state)
+                _patch_json(checkpoint_dir, {"backend": "single", "world_size": world})
+        _barrier(process_info)
+        return checkpoint_dir
     if world > 1:
         _sync_masters(train_state)
     if backend == "single":
