@@ -26,6 +26,7 @@ namespace {
 constexpr int kMp = 16;      // slots are padded to 16
 constexpr int kJp = 256;     // row stride of the raw projections
 constexpr int kThreads = 256;
+constexpr int kSc = 12;     // per-slot scalars: nk, nv, nw, simr, simw, relr, relw, strength, relr / nv
 
 __device__ __forceinline__ float trim_sq(float sim, float tau, float eps, float& x_out) {
   const float x = fmaxf((sim - tau) / (1.f - tau + eps), 0.f);
@@ -43,7 +44,7 @@ struct ScanSmem {
   float* qw;     // [dk]
   float* dxh;    // [ds]
   float* z;      // [dv]
-  float* sc;     // [16][8]    per-slot scalars: nk, nv, nw, simr, simw, relr, relw, strength
+  float* sc;     // [16][kSc]  per-slot scalars
   float* ages;   // [16]
   float* usage;  // [16]
   float* upd;    // [16]       squared update norm of the step
@@ -60,7 +61,7 @@ __device__ __forceinline__ ScanSmem carve(float* base, int ds, int dk, int dv) {
   s.qw = base; base += dk;
   s.dxh = base; base += ds;
   s.z = base; base += dv;
-  s.sc = base; base += kMp * 8;
+  s.sc = base; base += kMp * kSc;
   s.ages = base; base += kMp;
   s.usage = base; base += kMp;
   s.upd = base; base += kMp;
@@ -68,7 +69,7 @@ __device__ __forceinline__ ScanSmem carve(float* base, int ds, int dk, int dv) {
 }
 
 __host__ __device__ inline int scan_smem_floats(int ds, int dk, int dv) {
-  return 2 * ds * kMp + 2 * kMp * kJp + kMp * dk + 2 * dk + ds + dv + kMp * 8 + 3 * kMp;
+  return 2 * ds * kMp + 2 * kMp * kJp + kMp * dk + 2 * dk + ds + dv + kMp * kSc + 3 * kMp + 8 * kMp /*per-warp update norms*/;
 }
 
 // raw projections of all slots: P[m][j] = sum_d St[d][m] * WT[d][j]  (+ EW for the write keys)
@@ -95,34 +96,39 @@ __device__ __forceinline__ void project(const ScanSmem& s, const float* __restri
   }
 }
 
-// per-slot norms, similarities, relevances and the write strength; warp w handles slots 2w and 2w+1
+// per-slot norms, similarities, relevances and the write strength; half-warp h (16 lanes) handles slot h
+__device__ __forceinline__ float half_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 __device__ __forceinline__ void slot_scalars(const ScanSmem& s, const ScreenScanArgs& a, int warp, int lane) {
-  for (int mm = 0; mm < 2; ++mm) {
-    const int m = warp * 2 + mm;
-    const float* Pm = s.P + m * kJp;
-    float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f;
-    for (int j = lane; j < a.dk; j += 32) { const float x = Pm[j]; sk = fmaf(x, x, sk); dkq = fmaf(x, s.qr[j], dkq); }
-    for (int j = lane; j < a.dv; j += 32) { const float x = Pm[a.dk + j]; sv = fmaf(x, x, sv); }
-    if (a.write_enabled)
-      for (int j = lane; j < a.dk; j += 32) { const float x = Pm[a.dk + a.dv + j]; sw = fmaf(x, x, sw); dwq = fmaf(x, s.qw[j], dwq); }
-    sk = warp_sum(sk); dkq = warp_sum(dkq); sv = warp_sum(sv); sw = warp_sum(sw); dwq = warp_sum(dwq);
-    if (lane == 0) {
-      float* c = s.sc + m * 8;
-      const float e2 = a.eps * a.eps;
-      const float nk = sqrtf(sk + e2), nv = a.value_unit_norm ? sqrtf(sv + e2) : 1.f, nw = sqrtf(sw + e2);
-      const float simr = dkq / nk, simw = dwq / nw;
-      float xr, xw;
-      float relr = trim_sq(simr, a.tau_r, a.eps, xr);
-      if (a.age_mask) relr *= 1.f / (1.f + __expf(-(a.age_ref - s.ages[m]) / (a.age_sigma + a.eps)));
-      const bool live = m < a.M;
-      if (!live) relr = 0.f;
-      float relw = 0.f, strength = live ? a.mu[m] : 0.f;
-      if (a.write_enabled && live) {
-        relw = trim_sq(simw, a.tau_w, a.eps, xw);
-        strength *= fmaxf(relw, a.write_rel_floor);
-      }
-      c[0] = nk; c[1] = nv; c[2] = nw; c[3] = simr; c[4] = simw; c[5] = relr; c[6] = relw; c[7] = strength;
+  const int m = warp * 2 + (lane >> 4), hl = lane & 15;
+  const float* Pm = s.P + m * kJp;
+  float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f;
+  for (int j = hl; j < a.dk; j += 16) { const float x = Pm[j]; sk = fmaf(x, x, sk); dkq = fmaf(x, s.qr[j], dkq); }
+  for (int j = hl; j < a.dv; j += 16) { const float x = Pm[a.dk + j]; sv = fmaf(x, x, sv); }
+  if (a.write_enabled)
+    for (int j = hl; j < a.dk; j += 16) { const float x = Pm[a.dk + a.dv + j]; sw = fmaf(x, x, sw); dwq = fmaf(x, s.qw[j], dwq); }
+  sk = half_sum(sk); dkq = half_sum(dkq); sv = half_sum(sv); sw = half_sum(sw); dwq = half_sum(dwq);
+  if (hl == 0) {
+    float* c = s.sc + m * kSc;
+    const float e2 = a.eps * a.eps;
+    const float nk = sqrtf(sk + e2), nv = a.value_unit_norm ? sqrtf(sv + e2) : 1.f, nw = sqrtf(sw + e2);
+    const float simr = dkq / nk, simw = dwq / nw;
+    float xr, xw;
+    float relr = trim_sq(simr, a.tau_r, a.eps, xr);
+    if (a.age_mask) relr *= 1.f / (1.f + __expf(-(a.age_ref - s.ages[m]) / (a.age_sigma + a.eps)));
+    const bool live = m < a.M;
+    if (!live) relr = 0.f;
+    float relw = 0.f, strength = live ? a.mu[m] : 0.f;
+    if (a.write_enabled && live) {
+      relw = trim_sq(simw, a.tau_w, a.eps, xw);
+      strength *= fmaxf(relw, a.write_rel_floor);
     }
+    c[0] = nk; c[1] = nv; c[2] = nw; c[3] = simr; c[4] = simw; c[5] = relr; c[6] = relw; c[7] = strength;
+    c[8] = relr / nv;
   }
 }
 
@@ -148,8 +154,8 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
   if (tid < kMp) {
     s.ages[tid] = tid < a.M ? a.ages0[b * a.M + tid] : 0.f;
     s.usage[tid] = tid < a.M ? a.usage0[b * a.M + tid] : 0.f;
-    s.upd[tid] = 0.f;
   }
+  float* updw = s.upd + kMp;   // [8 warps][16] partial squared update norms of the current step
   __syncthreads();
   project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, false);   // E Wkw^T (only the write-key columns are kept)
   __syncthreads();
@@ -193,7 +199,6 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
 #pragma unroll
     for (int m = 0; m < kMp; ++m) pd[m] = n_pd[m];
     if (t + 1 < a.T) fetch(t + 1);
-    if (tid < kMp) s.upd[tid] = 0.f;
     __syncthreads();   // s.P and s.St of this step are complete (written at the end of the previous iteration)
     if (a.saved_slots != nullptr) {
       float* dst = a.saved_slots + bt * nel;
@@ -211,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     if (tid < a.dv) {
       float acc = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * 8 + 5] / s.sc[m * 8 + 1], s.P[m * kJp + a.dk + tid], acc);
+      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * kJp + a.dk + tid], acc);
       s.z[tid] = acc;
     }
     __syncthreads();
@@ -223,8 +228,8 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     if (tid < a.dv) a.u_out[bt * a.dv + tid] = f * s.z[tid];
     // ---- slot update ---------------------------------------------------------------------------------------------------------
     {
-      const int m = tid % kMp;   // every element this thread touches belongs to the same slot
-      const float strength = s.sc[m * 8 + 7];
+      const int m = tid % kMp;   // every element this thread touches belongs to the same slot (= lane & 15)
+      const float strength = s.sc[m * kSc + 7];
       float un = 0.f;
       for (int e = tid; e < nel; e += kThreads) {
         const int d = e / kMp;
@@ -234,39 +239,38 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
         s.St[e] = nw;
         un = fmaf(nw - old, nw - old, un);
       }
-      atomicAdd(&s.upd[m], un);
+      un += __shfl_xor_sync(0xffffffffu, un, 16);
+      if (lane < kMp) updw[warp * kMp + m] = un;   // per-warp partial of the squared update norm (no atomics)
     }
     if (tid < J) {   // the projections follow the same interpolation
 #pragma unroll
       for (int mm = 0; mm < kMp; ++mm) {
         const float old = s.P[mm * kJp + tid];
-        s.P[mm * kJp + tid] = fmaf(s.sc[mm * 8 + 7], pd[mm] - old, old);
+        s.P[mm * kJp + tid] = fmaf(s.sc[mm * kSc + 7], pd[mm] - old, old);
       }
     }
     __syncthreads();
-    if (tid < kMp && tid < a.M) {
-      const float relr = s.sc[tid * 8 + 5], relw = s.sc[tid * 8 + 6];
-      if (a.write_enabled) s.ages[tid] = relw > 1e-3f ? 0.f : s.ages[tid] + 1.f;
-      const float act = a.write_enabled ? fmaxf(relr, relw) : relr;
-      s.usage[tid] = a.usage_decay * s.usage[tid] + (1.f - a.usage_decay) * act;
-    }
-    if (tid == 0) {   // running sums of the logged statistics (means over slots here, over batch and time on the host)
-      float rm = 0.f, rx = 0.f, ac = 0.f, wm = 0.f, we = 0.f, un = 0.f;
-      for (int m = 0; m < a.M; ++m) {
-        const float relr = s.sc[m * 8 + 5], relw = s.sc[m * 8 + 6];
-        rm += relr; rx = fmaxf(rx, relr); ac += relr > 1e-3f ? 1.f : 0.f;
-        wm += relw; we += a.write_enabled ? fmaxf(relw, a.write_rel_floor) : relw;
-        un += sqrtf(s.upd[m]);
+    // ---- ages, usage and the logged statistics: lane m of warp 0 keeps slot m's running sums in registers -------------------
+    if (warp == 0) {
+      const int m = lane & 15;
+      const bool live = lane < kMp && m < a.M;
+      const float relr = live ? s.sc[m * kSc + 5] : 0.f, relw = live ? s.sc[m * kSc + 6] : 0.f;
+      float rx = relr;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) rx = fmaxf(rx, __shfl_xor_sync(0xffffffffu, rx, o));
+      if (live) {
+        if (a.write_enabled) s.ages[m] = relw > 1e-3f ? 0.f : s.ages[m] + 1.f;
+        const float act = a.write_enabled ? fmaxf(relr, relw) : relr;
+        const float us = a.usage_decay * s.usage[m] + (1.f - a.usage_decay) * act;
+        s.usage[m] = us;
+        float un = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) un += updw[w * kMp + m];
+        st_acc[0] += relr; st_acc[2] += relr > 1e-3f ? 1.f : 0.f;
+        st_acc[5] += relw; st_acc[6] += a.write_enabled ? fmaxf(relw, a.write_rel_floor) : relw;
+        st_acc[7] += sqrtf(un); st_acc[8] += us;
       }
-      const float im = 1.f / a.M;
-      st_acc[0] += rm * im; st_acc[1] += rx; st_acc[2] += ac; st_acc[3] += zn; st_acc[4] += f * zn;
-      st_acc[5] += wm * im; st_acc[6] += we * im; st_acc[7] += un * im;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      float um = 0.f;
-      for (int m = 0; m < a.M; ++m) um += s.usage[m];
-      st_acc[8] += um / a.M;
+      if (lane == 0) { st_acc[1] += rx; st_acc[3] += zn; st_acc[4] += f * zn; }
     }
   }
   for (int e = tid; e < nel; e += kThreads) {
@@ -274,9 +278,15 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     if (m < a.M) a.slots_out[((size_t)b * a.M + m) * a.ds + d] = s.St[e];
   }
   if (tid < a.M) { a.ages_out[b * a.M + tid] = s.ages[tid]; a.usage_out[b * a.M + tid] = s.usage[tid]; }
-  if (tid == 0) {
+  if (warp == 0) {   // per-slot sums -> means over slots (sums over steps and batch rows stay sums; the host divides)
+    const float im = 1.f / a.M;
 #pragma unroll
-    for (int i = 0; i < 9; ++i) atomicAdd(a.stats + i, st_acc[i]);
+    for (int i = 0; i < 9; ++i) {
+      float v = lane < kMp ? st_acc[i] : 0.f;
+      v = half_sum(v);
+      const bool per_slot_mean = i == 0 || i == 5 || i == 6 || i == 7 || i == 8;
+      if (lane == 0) atomicAdd(a.stats + i, per_slot_mean ? v * im : v);
+    }
   }
 }
 
@@ -320,27 +330,46 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
   float dmu_acc2 = 0.f;
   __syncthreads();
 
-  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f, n_du = 0.f;
+  // everything a step reads from global memory is fetched one step ahead into registers: the step vectors, the saved
+  // bank (elements tid + 256 i), and column tid of the saved projections and of the write target's projections
+  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f, n_du = 0.f, n_age = 0.f;
+  float n_S[16], n_P[kMp], n_PD[kMp];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) n_S[i] = 0.f;
+#pragma unroll
+  for (int m = 0; m < kMp; ++m) { n_P[m] = 0.f; n_PD[m] = 0.f; }
   auto fetch = [&](int t) {
     const size_t bt = (size_t)b * a.T + t;
     if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
     if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
     if (tid < a.dv) n_du = a.du[bt * a.dv + tid];
+    if (tid < kMp) n_age = a.saved_ages[bt * kMp + tid];
+    const float* src = a.saved_slots + bt * nel;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = tid + i * kThreads;
+      if (e < nel) n_S[i] = src[e];
+    }
+    if (tid < J) {
+      const float* sp = a.saved_P + bt * kMp * J + tid;
+      const float* pp = a.PD + bt * kMp * J + tid;
+#pragma unroll
+      for (int m = 0; m < kMp; ++m) { n_P[m] = sp[m * J]; n_PD[m] = pp[m * J]; }
+    }
   };
   fetch(a.T - 1);
   for (int t = a.T - 1; t >= 0; --t) {
     const size_t bt = (size_t)b * a.T + t;
-    {
-      const float* src = a.saved_slots + bt * nel;
-      for (int e = tid; e < nel; e += kThreads) s.St[e] = src[e];
-    }
-    if (tid < J) {   // the step's projections (saved by the forward pass) and those of its write target
-      const float* sp = a.saved_P + bt * kMp * J + tid;
-      const float* pp = a.PD + bt * kMp * J + tid;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) { s.P[m * kJp + tid] = sp[m * J]; s.PD[m * kJp + tid] = pp[m * J]; }
+    for (int i = 0; i < 16; ++i) {
+      const int e = tid + i * kThreads;
+      if (e < nel) s.St[e] = n_S[i];
     }
-    if (tid < kMp) { s.ages[tid] = a.saved_ages[bt * kMp + tid]; dstr[tid] = 0.f; }
+    if (tid < J) {
+#pragma unroll
+      for (int m = 0; m < kMp; ++m) { s.P[m * kJp + tid] = n_P[m]; s.PD[m * kJp + tid] = n_PD[m]; }
+    }
+    if (tid < kMp) { s.ages[tid] = n_age; dstr[tid] = 0.f; }
     if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
     if (tid < a.ds) s.dxh[tid] = n_dx;
     if (tid < a.dv) du[tid] = n_du;
@@ -351,13 +380,13 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
     if (tid < a.dv) {
       float acc = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * 8 + 5] / s.sc[m * 8 + 1], s.P[m * kJp + a.dk + tid], acc);
+      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * kJp + a.dk + tid], acc);
       s.z[tid] = acc;
     }
     // ---- backward of the slot update (uses the cotangent carried from step t+1) -----------------------------------------
     {
       const int m = tid % kMp;
-      const float strength = s.sc[m * 8 + 7];
+      const float strength = s.sc[m * kSc + 7];
       float dsp = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {   // constant trip count keeps dslot_acc in registers; nel is a multiple of 256
@@ -382,7 +411,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
     // ---- backward of the projection update P' = P + s (PD - P): warp w owns slots 2w and 2w+1 -------------------------------
     for (int mm = 0; mm < 2; ++mm) {
       const int m = warp * 2 + mm;
-      const float strength = s.sc[m * 8 + 7];
+      const float strength = s.sc[m * kSc + 7];
       float* gp = dPc + m * kJp;
       float* out = a.d_PD + (bt * kMp + m) * J;
       float dsp = 0.f;
@@ -409,7 +438,7 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
     // ---- per-slot scalars backward; cotangent of the raw projections (transposed into dPt[j][m]) ------------------------------
     for (int mm = 0; mm < 2; ++mm) {
       const int m = warp * 2 + mm;
-      const float* c = s.sc + m * 8;
+      const float* c = s.sc + m * kSc;
       const float nk = c[0], nv = c[1], nw = c[2], simr = c[3], simw = c[4], relr = c[5], relw = c[6];
       const float* Pm = s.P + m * kJp;
       const bool live = m < a.M;
@@ -457,8 +486,8 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
       float gr = 0.f, gw = 0.f;
 #pragma unroll
       for (int m = 0; m < kMp; ++m) {
-        gr = fmaf(dsimr[m], s.P[m * kJp + tid] / s.sc[m * 8 + 0], gr);
-        gw = fmaf(dsimw[m], s.P[m * kJp + a.dk + a.dv + tid] / s.sc[m * 8 + 2], gw);
+        gr = fmaf(dsimr[m], s.P[m * kJp + tid] / s.sc[m * kSc + 0], gr);
+        gw = fmaf(dsimw[m], s.P[m * kJp + a.dk + a.dv + tid] / s.sc[m * kSc + 2], gw);
       }
       a.d_q_r[bt * a.dk + tid] = gr;
       if (a.write_enabled) a.d_q_w[bt * a.dk + tid] = gw;
