@@ -69,6 +69,23 @@ def test_wgrad_layout_store_and_accumulate(M, N, K):
     assert torch.allclose(out, 2 * ref, atol=2e-2 + 2e-3 * K**0.5, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M,N,K,pair", [(512, 512, 8192, 1), (768, 256, 16384, 1), (128, 384, 8192, 0), (96, 2048, 4096, 0)])
+def test_wgrad_long_reduction(M, N, K, pair):
+    """Long reductions with few output tiles: in the single-CTA kernel the accumulating epilogue is reached by several
+    CTAs per tile (split-K, atomic adds); the pair kernel reads-modifies-writes.  Twice in a row to check accumulation."""
+    kk = _K()
+    a, b = _rand(K, M, seed=11), _rand(K, N, seed=12)
+    out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    kk.gemm_error_reset(a)
+    kk.gemm(a, b, out, kk.GEMM_WGRAD, kk.EPI_ACC_F32, pair)
+    ref = a.float().t() @ b.float()
+    assert kk.gemm_error_code(a) == 0
+    assert torch.allclose(out, ref, atol=1e-2 + 1e-3 * K**0.5, rtol=1e-3)
+    kk.gemm(a, b, out, kk.GEMM_WGRAD, kk.EPI_ACC_F32, pair)
+    assert kk.gemm_error_code(a) == 0
+    assert torch.allclose(out, 2 * ref, atol=2e-2 + 2e-3 * K**0.5, rtol=1e-3)
+
+
 def test_relu_sq_epilogue():
     kk = _K()
     a, b = _rand(300, 256, seed=7), _rand(520, 256, seed=8)
