@@ -143,7 +143,8 @@ Tensor& gemm_error_flag(const at::Device& dev) {
 }
 
 // D = op(A) op(B); see kernels.h for the three layouts.  D must be preallocated.
-void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue, int64_t pair) {
+void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue, int64_t pair,
+          const c10::optional<Tensor>& aux) {
   static const bool trace = [] { const char* e = getenv("RWKV7M_B200_TRACE"); return e != nullptr && e[0] == '1'; }();
   if (trace) { fprintf(stderr, "[gemm-bind] enter layout=%d epi=%d\n", (int)layout, (int)epilogue); fflush(stderr); }
   c10::cuda::CUDAGuard guard(A.device());
@@ -166,7 +167,16 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
     TORCH_CHECK(B.size(0) == p.K, "gemm wgrad: K mismatch");
   }
   TORCH_CHECK(D.size(0) == p.M && D.size(1) == p.N, "gemm: output shape mismatch");
-  const bool out_bf16 = epilogue == rk::kEpiStoreBf16 || epilogue == rk::kEpiReluSqBf16;
+  const bool two_input = epilogue == rk::kEpiMulSqrt2Bf16 || epilogue == rk::kEpiAddBf16;
+  if (two_input) {
+    TORCH_CHECK(aux.has_value() && aux->defined(), "gemm: this epilogue needs a second input");
+    TORCH_CHECK(aux->is_cuda() && aux->scalar_type() == at::kBFloat16 && aux->dim() == 2 && aux->stride(1) == 1 &&
+                    aux->size(0) == D.size(0) && aux->size(1) == D.size(1),
+                "gemm: the second epilogue input must be a bf16 matrix of the output's shape");
+    p.aux = aux->data_ptr();
+    p.ldaux = (int)aux->stride(0);
+  }
+  const bool out_bf16 = epilogue == rk::kEpiStoreBf16 || epilogue == rk::kEpiReluSqBf16 || two_input;
   TORCH_CHECK(D.scalar_type() == (out_bf16 ? at::kBFloat16 : at::kFloat), "gemm: output dtype mismatch");
   if (trace) { fprintf(stderr, "[gemm-bind] checks ok\n"); fflush(stderr); }
   p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();

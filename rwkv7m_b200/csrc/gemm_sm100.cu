@@ -66,7 +66,8 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 // Write one 32-column chunk of an accumulator row (thread = row) with the selected epilogue.
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __restrict__ Dptr, int row, int col0, int M,
-                                            int N, int ldd, bool atomic = false) {
+                                            int N, int ldd, bool atomic = false, const void* __restrict__ aux = nullptr,
+                                            int ldaux = 0) {
   if (EPI == kEpiScatterAddBf16) {
     // Reduce-scatter over time fused into the epilogue: the row belongs to the rank that owns its time slice; the
     // partial result is added straight into that rank's output buffer (peer memory over NVLink, bf16x2 atomics).
@@ -87,6 +88,43 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
         asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(out + 8 * j), "r"(pk[4 * j]),
                      "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]), "r"(pk[4 * j + 3])
                      : "memory");
+    }
+    return;
+  }
+  if (EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16) {
+    // second input tile read with the same 16-byte pieces as the output is written
+    if (row < M && col0 < N) {
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + (size_t)row * ldd + col0;
+      const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(aux) + (size_t)row * ldaux + col0;
+      if (col0 + 32 <= N) {
+        uint4 raw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) raw[j] = __ldg(reinterpret_cast<const uint4*>(ax) + j);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(raw);
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 hx = __bfloat1622float2(h2[j]);
+          float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+          if (EPI == kEpiMulSqrt2Bf16) { x0 *= 2.f * sqrtf(hx.x); x1 *= 2.f * sqrtf(hx.y); }
+          else { x0 += hx.x; x1 += hx.y; }
+          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+          pk[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < N) {
+            const float hx = __bfloat162float(ax[j]);
+            float x0 = __uint_as_float(v[j]);
+            x0 = EPI == kEpiMulSqrt2Bf16 ? x0 * 2.f * sqrtf(hx) : x0 + hx;
+            out[j] = f2bf(x0);
+          }
+        }
+      }
     }
     return;
   }
@@ -179,7 +217,7 @@ template <int BN, int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int splits,
-                 int* __restrict__ err) {
+                 const void* __restrict__ aux, int ldaux, int* __restrict__ err) {
   using TL = Tile<BN>;
   constexpr int kStages = TL::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -306,14 +344,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32(t0 + c * 32, v0);
           tmem_ld_32x32(t0 + c * 32 + 32, v1);
           tmem_ld_wait();
-          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic);
-          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic);
+          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux);
+          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux);
         }
       } else {
         uint32_t v[32];
         tmem_ld_32x32(t0, v);
         tmem_ld_wait();
-        store_chunk<EPI>(v, Dptr, row, n0, M, N, ldd, atomic);
+        store_chunk<EPI>(v, Dptr, row, n0, M, N, ldd, atomic, aux, ldaux);
       }
       tc_fence_before();
       __syncwarp();
@@ -359,7 +397,8 @@ struct PairTile {
 template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int* __restrict__ err) {
+                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m,
+                      const void* __restrict__ aux, int ldaux, int* __restrict__ err) {
   using TL = PairTile;
   constexpr int kStages = TL::kStages;
   constexpr int BN2 = 256;  // tile width of the pair
@@ -486,8 +525,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32(t0 + c * 32, v0);
         tmem_ld_32x32(t0 + c * 32 + 32, v1);
         tmem_ld_wait();
-        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd);
-        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd);
+        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux);
+        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux);
       }
       tc_fence_before();
       __syncwarp();
@@ -647,7 +686,8 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   const int work = tiles * splits;
   const int grid = work < sm_count() ? work : sm_count();
   RK_TRACE("attr ok grid=%d smem=%d splits=%d\n", grid, TL::kSmemBytes, splits);
-  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.error_flag);
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.aux, p.ldaux,
+                                                   p.error_flag);
   RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -659,6 +699,8 @@ int launch_epi(const GemmArgs& p, cudaStream_t st) {
     case kEpiReluSqBf16: return launch<BN, A_MN, B_MN, kEpiReluSqBf16>(p, st);
     case kEpiStoreF32: return launch<BN, A_MN, B_MN, kEpiStoreF32>(p, st);
     case kEpiAccumF32: return launch<BN, A_MN, B_MN, kEpiAccumF32>(p, st);
+    case kEpiMulSqrt2Bf16: return launch<BN, A_MN, B_MN, kEpiMulSqrt2Bf16>(p, st);
+    case kEpiAddBf16: return launch<BN, A_MN, B_MN, kEpiAddBf16>(p, st);
   }
   return 5;
 }
@@ -692,7 +734,8 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.error_flag);
+  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.aux, p.ldaux,
+                                                    p.error_flag);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -703,6 +746,8 @@ int launch_pair_epi(const GemmArgs& p, cudaStream_t st) {
     case kEpiReluSqBf16: return launch_pair<A_MN, B_MN, kEpiReluSqBf16>(p, st);
     case kEpiStoreF32: return launch_pair<A_MN, B_MN, kEpiStoreF32>(p, st);
     case kEpiAccumF32: return launch_pair<A_MN, B_MN, kEpiAccumF32>(p, st);
+    case kEpiMulSqrt2Bf16: return launch_pair<A_MN, B_MN, kEpiMulSqrt2Bf16>(p, st);
+    case kEpiAddBf16: return launch_pair<A_MN, B_MN, kEpiAddBf16>(p, st);
   }
   return 5;
 }
@@ -731,7 +776,9 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
     if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair<0, 0, kEpiScatterAddBf16>(p, st);
     return launch<256, 0, 0, kEpiScatterAddBf16>(p, st);
   }
-  const bool out_bf16 = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16;
+  const bool two_input = p.epilogue == kEpiMulSqrt2Bf16 || p.epilogue == kEpiAddBf16;
+  if (two_input && (p.aux == nullptr || (reinterpret_cast<uintptr_t>(p.aux) & 15) || (p.ldaux & 7))) return 6;
+  const bool out_bf16 = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16 || two_input;
   if (p.ldd & (out_bf16 ? 7 : 3)) return 6;
   if (p.error_flag == nullptr) return 7;
   // the CTA-pair kernel needs at least one full 256-row tile and a wide N to pay off

@@ -173,7 +173,11 @@ int tp_aux_words();
 
 // ---- GEMM (tcgen05) -------------------------------------------------------------
 enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
-enum GemmEpilogue { kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3, kEpiScatterAddBf16 = 4 };
+enum GemmEpilogue {
+  kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3, kEpiScatterAddBf16 = 4,
+  kEpiMulSqrt2Bf16 = 5,   // D = bf16(acc * 2 sqrt(aux)): backward of h = relu(.)^2 fused into the GEMM that produces dh
+  kEpiAddBf16 = 6         // D = bf16(acc + aux): residual add fused into the projection
+};
 // Target of the kEpiScatterAddBf16 epilogue (GEMM -> reduce-scatter over time in one kernel): rows are [B, T] tokens,
 // rank r owns tokens [r*Tl, (r+1)*Tl) of every batch row and receives them in out[r] laid out [B, Tl, N].
 struct GemmScatter {
@@ -186,6 +190,8 @@ struct GemmArgs {
   //  layout kGemmNN      : A stored [M,K] row-major, B stored [K,N] row-major      (dx = dy W)
   //  layout kGemmNT_wgrad: A stored [K,M] row-major, B stored [K,N] row-major      (dW = dy^T x)
   const void* A; const void* B; void* D;
+  const void* aux;     // bf16 [M, N] second epilogue input (kEpiMulSqrt2Bf16, kEpiAddBf16), row pitch ldaux
+  int ldaux;
   int M, N, K;
   int lda, ldb, ldd;   // leading dimensions in elements of the stored matrices
   int layout, epilogue;

@@ -152,8 +152,9 @@ class RWKV7TimeMix(nn.Module):
         with torch.no_grad():
             self.ln_x.weight.fill_(((1 + layer_idx) / L) ** 0.7)
 
-    def forward(self, x, v_first, prev_x, wkv_state):
-        """x: [B,T,C] (already LN1'd).  Returns (out, v_first, last_x fp32, final wkv state)."""
+    def forward(self, x, v_first, prev_x, wkv_state, residual=None):
+        """x: [B,T,C] (already LN1'd).  Returns (out, v_first, last_x fp32, final wkv state); with ``residual`` (no
+        tensor parallelism) ``out`` is residual + output projection, added in the GEMM epilogue."""
         cfg = self.config
         B, T, _ = x.shape
         # under tensor parallelism this rank holds H/w heads: sizes come from the (possibly sharded) parameters
@@ -196,7 +197,12 @@ class RWKV7TimeMix(nn.Module):
         y = ops.gn_bonus_gate(
             y.reshape(B, T, C), r, k_mod, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps
         )
-        out = _row_parallel_linear(self, y, self.output.weight)
+        if residual is not None and getattr(self, "tp", None) is None:
+            out = ops.linear_add(residual, y, self.output.weight)
+        else:
+            out = _row_parallel_linear(self, y, self.output.weight)
+            if residual is not None:
+                out = residual + out
         return out, v_first, x[:, -1].float(), final_state
 
 
@@ -210,10 +216,16 @@ class RWKV7ChannelMix(nn.Module):
         self.key = Linear(C, F, init=_uniform((F, C), 0.5 / math.sqrt(C)))
         self.value = Linear(F, C)
 
-    def forward(self, x, prev_x):
+    def forward(self, x, prev_x, residual=None):
         (xk,) = ops.shift_mix(x, prev_x, self.x_k.unsqueeze(0))
-        h = ops.linear_relu_sq(xk, self.key.weight)
-        out = _row_parallel_linear(self, h, self.value.weight)
+        if getattr(self, "tp", None) is None:
+            # one autograd node: relu^2, the residual add and the relu^2 backward live in GEMM epilogues
+            out = ops.ffn(xk, self.key.weight, self.value.weight, residual)
+        else:
+            h = ops.linear_relu_sq(xk, self.key.weight)
+            out = _row_parallel_linear(self, h, self.value.weight)
+            if residual is not None:
+                out = residual + out
         return out, x[:, -1].float()
 
 
@@ -235,12 +247,14 @@ class RWKV7Block(nn.Module):
         h = self.ln1(x)
         if tp is not None:  # sequence-sharded residual: gather tokens for the column-parallel projections
             h = tp.gather_seq(h)
+        if tp is None:   # the residual adds ride in the epilogues of the two output projections
+            x, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv, residual=x)
+            x, cm_x = self.ffn(self.ln2(x), state.channel_mix_x, residual=x)
+            return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)
         att_out, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv)
         # row-parallel output: sum the partial results over ranks, keep this rank's tokens, add the residual
-        x = x + att_out if tp is None else tp.reduce_scatter_add(att_out, x)
-        h = self.ln2(x)
-        if tp is not None:
-            h = tp.gather_seq(h)
+        x = tp.reduce_scatter_add(att_out, x)
+        h = tp.gather_seq(self.ln2(x))
         ffn_out, cm_x = self.ffn(h, state.channel_mix_x)
-        x = x + ffn_out if tp is None else tp.reduce_scatter_add(ffn_out, x)
+        x = tp.reduce_scatter_add(ffn_out, x)
         return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)

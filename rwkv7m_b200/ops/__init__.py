@@ -73,6 +73,21 @@ def linear_relu_sq(x, weight):
     return reference.relu_sq(reference.linear(x, weight))
 
 
+def linear_add(residual, x, weight):
+    """residual + x @ W.T (the GEMM epilogue adds the residual on CUDA)."""
+    if use_cuda(x):
+        return _cuda().linear_add(residual, x, weight)
+    return residual + reference.linear(x, weight)
+
+
+def ffn(x, w_key, w_value, residual=None):
+    """Channel mix: [residual +] relu(x @ Wk.T)**2 @ Wv.T as one autograd node on CUDA."""
+    if use_cuda(x):
+        return _cuda().ffn(x, w_key, w_value, residual)
+    out = reference.linear(reference.relu_sq(reference.linear(x, w_key)), w_value)
+    return out if residual is None else residual + out
+
+
 def lora(x, down, up, mid="none"):
     """Low-rank path act(x @ down.T) @ up.T with weights stored [out,in]; no bias."""
     if use_cuda(x):

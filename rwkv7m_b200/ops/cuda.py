@@ -23,6 +23,7 @@ WKV_CHECKPOINT_INTERVAL = 16
 # Layout / epilogue ids (csrc/kernels.h)
 GEMM_TN, GEMM_NN, GEMM_WGRAD = 0, 1, 2
 EPI_BF16, EPI_RELUSQ, EPI_F32, EPI_ACC_F32 = 0, 1, 2, 3
+EPI_MUL2SQRT, EPI_ADD = 5, 6   # two-input epilogues: acc * 2 sqrt(aux), acc + aux
 
 # "tcgen05" = this package's GEMM kernel (product path);
 # "cublas"  = torch.matmul, kept only so benchmarks can report the library baseline.
@@ -112,9 +113,10 @@ def set_gemm_pair(enabled: bool):
     GEMM_PAIR = bool(enabled)
 
 
-def gemm(a, b, out, layout, epilogue, pair=None):
-    """Raw GEMM launcher: see csrc/kernels.h for layouts.  Returns ``out``."""
-    _C.gemm(a, b, out, layout, epilogue, int(GEMM_PAIR if pair is None else pair))
+def gemm(a, b, out, layout, epilogue, pair=None, aux=None):
+    """Raw GEMM launcher: see csrc/kernels.h for layouts.  ``aux`` is the second epilogue input of
+    ``EPI_MUL2SQRT`` / ``EPI_ADD`` (bf16, shape of ``out``).  Returns ``out``."""
+    _C.gemm(a, b, out, layout, epilogue, int(GEMM_PAIR if pair is None else pair), aux)
     _count()
     return out
 
@@ -242,6 +244,124 @@ def linear(x, weight):
 
 def linear_relu_sq(x, weight):
     return _linear_any(x, weight, True)
+
+
+def _wgrad(dy2, x2, w):
+    """dW = dy^T x into the bound fp32 main gradient (returns None) or as a tensor of the weight's dtype."""
+    main = getattr(w, "_main_grad", None)
+    if main is not None and main.dtype == torch.float32:
+        gemm(dy2, x2, main, GEMM_WGRAD, EPI_ACC_F32)
+        return None
+    dw32 = torch.empty(dy2.shape[1], x2.shape[1], dtype=torch.float32, device=dy2.device)
+    gemm(dy2, x2, dw32, GEMM_WGRAD, EPI_F32)
+    return dw32.to(w.dtype)
+
+
+class LinearAddFn(torch.autograd.Function):
+    """out = residual + x @ W^T with the add in the GEMM epilogue; the residual's gradient is the incoming one."""
+
+    @staticmethod
+    def forward(ctx, residual, x, w):
+        wc = _compute_weight(w)
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        r2 = residual.reshape(-1, residual.shape[-1])
+        if not r2.is_contiguous():
+            r2 = r2.contiguous()
+        out = torch.empty_like(r2)
+        gemm(x2, wc, out, GEMM_TN, EPI_ADD, aux=r2)
+        ctx.weight, ctx.x_shape = w, x.shape
+        ctx.save_for_backward(x2, wc)
+        return out.view(residual.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, wc = ctx.saved_tensors
+        N, K = wc.shape
+        d2 = dout.reshape(-1, N)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[1]:
+            dx = torch.empty(x2.shape[0], K, dtype=torch.bfloat16, device=dout.device)
+            gemm(d2, wc, dx, GEMM_NN, EPI_BF16)
+            dx = dx.view(ctx.x_shape)
+        dw = _wgrad(d2, x2, ctx.weight) if ctx.needs_input_grad[2] else None
+        return (dout if ctx.needs_input_grad[0] else None), dx, dw
+
+
+class FfnFn(torch.autograd.Function):
+    """Channel mix in one autograd node: h = relu(x Wk^T)^2, out = [residual +] h Wv^T.
+
+    Forward: relu^2 and the residual add live in the two GEMM epilogues.  Backward: the GEMM that forms dh = dout Wv
+    multiplies by 2 sqrt(h) in its epilogue (d relu(p)^2 / dp = 2 relu(p) = 2 sqrt(h)), so the [tokens, d_ffn]
+    gradient is written once and never re-read by a separate elementwise pass."""
+
+    @staticmethod
+    def forward(ctx, x, wk, wv, residual):
+        wkc, wvc = _compute_weight(wk), _compute_weight(wv)
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M, F = x2.shape[0], wkc.shape[0]
+        h = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+        gemm(x2, wkc, h, GEMM_TN, EPI_RELUSQ)
+        out = torch.empty(M, wvc.shape[0], dtype=torch.bfloat16, device=x.device)
+        if residual is not None:
+            r2 = residual.reshape(-1, residual.shape[-1])
+            if not r2.is_contiguous():
+                r2 = r2.contiguous()
+            gemm(h, wvc, out, GEMM_TN, EPI_ADD, aux=r2)
+        else:
+            gemm(h, wvc, out, GEMM_TN, EPI_BF16)
+        ctx.wk, ctx.wv, ctx.x_shape, ctx.has_res = wk, wv, x.shape, residual is not None
+        ctx.save_for_backward(x2, wkc, wvc, h)
+        return out.view(*x.shape[:-1], wvc.shape[0])
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, wkc, wvc, h = ctx.saved_tensors
+        d2 = dout.reshape(-1, wvc.shape[0])
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dwv = _wgrad(d2, h, ctx.wv) if ctx.needs_input_grad[2] else None
+        dp = torch.empty_like(h)                      # gradient of the pre-activation
+        gemm(d2, wvc, dp, GEMM_NN, EPI_MUL2SQRT, aux=h)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(x2.shape[0], x2.shape[1], dtype=torch.bfloat16, device=dout.device)
+            gemm(dp, wkc, dx, GEMM_NN, EPI_BF16)
+            dx = dx.view(ctx.x_shape)
+        dwk = _wgrad(dp, x2, ctx.wk) if ctx.needs_input_grad[1] else None
+        return dx, dwk, dwv, (dout if (ctx.has_res and ctx.needs_input_grad[3]) else None)
+
+
+def _fused_linear_ok(x, *weights):
+    if not (GEMM_BACKEND == "tcgen05" and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
+        return False
+    for w in weights:
+        wc = _compute_weight(w)
+        if not (wc.dtype == torch.bfloat16 and wc.shape[0] % 8 == 0 and wc.shape[1] % 8 == 0 and wc.stride(1) == 1
+                and wc.stride(0) % 8 == 0 and wc.data_ptr() % 16 == 0):
+            return False
+    return True
+
+
+def linear_add(residual, x, weight):
+    """residual + x @ W^T."""
+    if _fused_linear_ok(x, weight) and residual.dtype == torch.bfloat16:
+        return LinearAddFn.apply(residual, x, weight)
+    return residual + linear(x, weight)
+
+
+def ffn(x, w_key, w_value, residual=None):
+    """[residual +] relu(x Wk^T)^2 Wv^T."""
+    if _fused_linear_ok(x, w_key, w_value) and (residual is None or residual.dtype == torch.bfloat16):
+        return FfnFn.apply(x, w_key, w_value, residual)
+    out = linear(linear_relu_sq(x, w_key), w_value)
+    return out if residual is None else residual + out
 
 
 # ---------------------------------------------------------------------------

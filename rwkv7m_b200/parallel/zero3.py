@@ -41,6 +41,30 @@ def unit_key(name: str):
     raise ValueError(f"not a bulk parameter: {name}")
 
 
+def plan_units(entries, n_bulk: int, world: int):
+    """Group the bulk entries ``(name, param, offset, numel)`` of the flat layout into units and cut every unit into
+    ``world`` equal pieces.  Returns dicts with ``key``, ``entries``, ``off`` / ``end`` (span in the flat layout),
+    ``piece`` (elements per rank, a multiple of 8 so that pieces are 16-byte aligned in bf16; the last piece may
+    run past ``end`` into padding) and ``poff`` (offset of the unit's piece in a rank's compact buffers)."""
+    units = []
+    for e in entries:
+        if e[2] >= n_bulk:
+            continue
+        key = unit_key(e[0])
+        if units and units[-1]["key"] == key:
+            units[-1]["entries"].append(e)
+        else:
+            units.append({"key": key, "entries": [e], "off": e[2]})
+    poff = 0
+    for i, u in enumerate(units):
+        u["end"] = units[i + 1]["off"] if i + 1 < len(units) else n_bulk
+        span = u["end"] - u["off"]
+        u["piece"] = (span + world * 8 - 1) // (world * 8) * 8
+        u["poff"] = poff
+        poff += u["piece"]
+    return units
+
+
 class _UnitMark(torch.autograd.Function):
     """Identity in forward; its backward tells the engine that a unit's backward is about to start (``leave`` marks,
     placed on the unit's output) or has just finished (``enter`` marks, placed on the unit's input)."""
@@ -90,35 +114,20 @@ class Zero3Engine:
 
         # ---- units and pieces ------------------------------------------------------------------------------------
         n_bulk = int(flat.n_bulk)
-        bulk = [e for e in flat.entries if e[2] < n_bulk]
-        self.units = []   # dict(key, entries, off, end, piece, poff)
-        for e in bulk:
-            key = unit_key(e[0])
-            if self.units and self.units[-1]["key"] == key:
-                self.units[-1]["entries"].append(e)
-            else:
-                self.units.append({"key": key, "entries": [e], "off": e[2]})
-        poff = 0
-        for i, u in enumerate(self.units):
-            u["end"] = self.units[i + 1]["off"] if i + 1 < len(self.units) else n_bulk
-            span = u["end"] - u["off"]
-            u["piece"] = (span + W * 8 - 1) // (W * 8) * 8
-            u["poff"] = poff
-            poff += u["piece"]
-        self.n_shard = poff
+        self.units = plan_units(flat.entries, n_bulk, W)
+        self.n_shard = sum(u["piece"] for u in self.units)
         self.max_padded = max(u["piece"] * W for u in self.units)
         self.unit_index = {u["key"]: i for i, u in enumerate(self.units)}
-        self.n_layers = sum(1 for u in self.units if u["key"][0] == "layer")
 
         # ---- buffers ---------------------------------------------------------------------------------------------
         def sym(n, dtype):
             t = symm.empty(n, dtype=dtype, device=dev)
             t.zero_()
-            return t, None
+            return t
 
-        self.shard_compute, _ = sym(self.n_shard, torch.bfloat16)
-        self.unitgrad = [sym(self.max_padded, torch.float32)[0] for _ in range(self.GRAD_SLOTS)]
-        self.aux, _ = sym(self._C.dp_aux_words(), torch.int32)
+        self.shard_compute = sym(self.n_shard, torch.bfloat16)
+        self.unitgrad = [sym(self.max_padded, torch.float32) for _ in range(self.GRAD_SLOTS)]
+        self.aux = sym(self._C.dp_aux_words(), torch.int32)
         self.h_compute = symm.rendezvous(self.shard_compute, self.group)
         self.h_grad = [symm.rendezvous(t, self.group) for t in self.unitgrad]
         self.h_aux = symm.rendezvous(self.aux, self.group)

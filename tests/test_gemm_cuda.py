@@ -122,3 +122,48 @@ def test_linear_function_gradients_match_autograd():
     assert torch.allclose(y.float(), y_ref.float(), atol=0.2, rtol=2e-2)
     assert torch.allclose(gx.float(), x.grad.float(), atol=0.3, rtol=3e-2)
     assert torch.allclose(gw.float(), w.grad.float(), atol=1.0, rtol=3e-2)
+
+
+def test_ffn_and_linear_add_functions_match_autograd():
+    """Channel mix as one node (relu^2 / residual add / relu^2 backward in GEMM epilogues) and the projection with the
+    residual add in its epilogue, against plain PyTorch fp32 autograd on the same bf16-rounded inputs."""
+    kk = _K()
+    torch.manual_seed(3)
+    M, C, F = 384, 256, 640
+    x = (torch.randn(2, M // 2, C, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    res = (torch.randn(2, M // 2, C, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    wk = (torch.randn(F, C, device="cuda") * 0.05).requires_grad_(True)
+    wv = (torch.randn(C, F, device="cuda") * 0.05).requires_grad_(True)
+    wo = (torch.randn(C, C, device="cuda") * 0.05).requires_grad_(True)
+    g = (torch.randn(2, M // 2, C, device="cuda")).bfloat16()
+
+    out = kk.ffn(x, wk, wv, res)
+    out2 = kk.linear_add(res, x, wo)
+    (out.float() * g.float()).sum().backward(retain_graph=True)
+    got = [t.grad.clone() for t in (x, res, wk, wv)]
+    for t in (x, res, wk, wv, wo):
+        t.grad = None
+    (out2.float() * g.float()).sum().backward()
+    got2 = [t.grad.clone() for t in (x, res, wo)]
+
+    xr, rr = x.detach().float().requires_grad_(True), res.detach().float().requires_grad_(True)
+    wkr, wvr, wor = (w.detach().bfloat16().float().requires_grad_(True) for w in (wk, wv, wo))
+    h = torch.relu(xr @ wkr.t()) ** 2
+    ref = rr + h.bfloat16().float() @ wvr.t()
+    ref2 = rr + xr @ wor.t()
+    (ref * g.float()).sum().backward()
+    want = [xr.grad.clone(), rr.grad.clone(), wkr.grad.clone(), wvr.grad.clone()]
+    xr.grad = rr.grad = None
+    (ref2 * g.float()).sum().backward()
+    want2 = [xr.grad, rr.grad, wor.grad]
+
+    def close(a, b, tol):
+        a, b = a.detach().float(), b.detach().float()
+        return float((a - b).norm() / (b.norm() + 1e-12)) < tol
+
+    assert close(out, ref, 1e-2) and close(out2, ref2, 1e-2)
+    for a, b in zip(got, want):
+        assert close(a, b, 2e-2)
+    for a, b in zip(got2, want2):
+        assert close(a, b, 2e-2)
+    assert kk.gemm_error_code(x) == 0

@@ -161,3 +161,34 @@ def test_scaling_planner_divides_by_model_axis():
     four = estimate_training_memory(cfg, DTypePolicy.stability(), model_axis_size=4)
     assert four.global_estimated_bytes == one.global_estimated_bytes
     assert four.per_device_estimated_bytes == math.ceil(one.per_device_estimated_bytes / 4)
+
+
+def test_zero3_unit_plan_covers_the_bulk_weights():
+    """ZeRO-3 layout arithmetic (CPU): units follow the forward order, every unit is cut into equal 16-byte-aligned
+    pieces that cover its span, and the compact per-rank offsets are the running sum of the pieces."""
+    import rwkv7m_b200 as R
+    from rwkv7m_b200.parallel.zero3 import plan_units, unit_key
+
+    cfg = R.tiny_config()
+    _, ts = R.create_train_runtime(0, cfg, batch_size=1)
+    flat = ts.optimizer.flat
+    assert flat.n_bulk > 0 and flat.n_bulk <= flat.bounds[0]
+    for world in (1, 2, 8):
+        units = plan_units(flat.entries, flat.n_bulk, world)
+        keys = [u["key"] for u in units]
+        assert keys[0] == ("emb", -1) and keys[-1][0] == "head"
+        assert [k[1] for k in keys[1:-1]] == list(range(cfg.n_layers))
+        off = 0
+        poff = 0
+        for u in units:
+            assert u["off"] == off and u["piece"] % 8 == 0 and u["piece"] * world >= u["end"] - u["off"]
+            assert u["piece"] * world - (u["end"] - u["off"]) < world * 8
+            assert u["poff"] == poff
+            for (name, p, o, n) in u["entries"]:
+                assert unit_key(name) == u["key"] and u["off"] <= o and o + n <= u["end"]
+            off, poff = u["end"], poff + u["piece"]
+        assert off == flat.n_bulk
+    bulk_names = {e[0] for u in units for e in u["entries"]}
+    assert all(".screening." not in n for n in bulk_names)
+    with pytest.raises(ValueError):
+        unit_key("layers.0.block.att.w0") if False else unit_key("ln_out.weight")
