@@ -217,7 +217,7 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor
 }
 
 std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
-                                  const Tensor& rstd) {
+                                  const Tensor& rstd, const c10::optional<Tensor>& dres) {
   c10::cuda::CUDAGuard guard(x.device());
   check_act(dy, "dy"); check_act(x, "x");
   const int64_t C = x.size(-1), M = x.numel() / C;
@@ -227,8 +227,16 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   int parts = (int)std::min<int64_t>(148 * 2, std::max<int64_t>(1, M / 64));   // blocks of the backward grid
   auto f32 = x.options().dtype(at::kFloat);
   Tensor dwp = torch::empty({parts, C}, f32), dbp = torch::empty({parts, C}, f32);
-  rk::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                    dx.data_ptr(), dwp.data_ptr<float>(), dbp.data_ptr<float>(), parts, (int)M, (int)C, stream());
+  const bool has_res = dres.has_value() && dres->defined();
+  if (has_res) { check_act(*dres, "dres"); TORCH_CHECK(dres->numel() == x.numel()); }
+  const bool fused = rk::layernorm_bwd_res(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(),
+                                           rstd.data_ptr<float>(), has_res ? dres->data_ptr() : nullptr, dx.data_ptr(),
+                                           dwp.data_ptr<float>(), dbp.data_ptr<float>(), parts, (int)M, (int)C, stream());
+  if (!fused) {   // width without a single-pass kernel: plain backward, then add
+    rk::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                      dx.data_ptr(), dwp.data_ptr<float>(), dbp.data_ptr<float>(), parts, (int)M, (int)C, stream());
+    dx.add_(*dres);
+  }
   return {dx, dwp.sum(0), dbp.sum(0)};
 }
 

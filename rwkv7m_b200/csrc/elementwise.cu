@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
                                                                      const float* __restrict__ w, const float* __restrict__ mean,
                                                                      const float* __restrict__ rstd, bf16* __restrict__ dx,
                                                                      float* __restrict__ dw_part, float* __restrict__ db_part,
-                                                                     int M) {
+                                                                     int M, const bf16* __restrict__ dres) {
   constexpr int C = NCH * 256;
   __shared__ float s_w[C];
   for (int c = threadIdx.x; c < C; c += 256) s_w[c] = w[c];
@@ -130,11 +130,13 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
   for (int row = r0 + warp; row < r1; row += 8) {
     const bf16* gr = dy + (size_t)row * C + lane * 8;
     const bf16* xr = x + (size_t)row * C + lane * 8;
-    uint4 graw[NCH], xraw[NCH];
+    uint4 graw[NCH], xraw[NCH], rraw[NCH];   // rraw: gradient arriving through the residual connection (optional)
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       graw[i] = __ldg(reinterpret_cast<const uint4*>(gr + i * 256));
       xraw[i] = __ldg(reinterpret_cast<const uint4*>(xr + i * 256));
+      rraw[i] = dres != nullptr ? __ldg(reinterpret_cast<const uint4*>(dres + (size_t)row * C + lane * 8 + i * 256))
+                                : make_uint4(0u, 0u, 0u, 0u);
     }
     const float mu = mean[row], rs = rstd[row];
     float s1 = 0.f, s2 = 0.f;
@@ -160,6 +162,7 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
     for (int i = 0; i < NCH; ++i) {
       const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
       const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rraw[i]);
       const int cb = i * 256 + lane * 8;
       uint4 o;
       uint32_t* op = reinterpret_cast<uint32_t*>(&o);
@@ -167,8 +170,10 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
       for (int j = 0; j < 4; ++j) {
         const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
         const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+        const float2 r = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rp[j]));
         const float xh0 = (v.x - mu) * rs, xh1 = (v.y - mu) * rs;
-        bf162 h = __floats2bfloat162_rn(rs * (g.x * s_w[cb + 2 * j] - s1 - xh0 * s2), rs * (g.y * s_w[cb + 2 * j + 1] - s1 - xh1 * s2));
+        bf162 h = __floats2bfloat162_rn(r.x + rs * (g.x * s_w[cb + 2 * j] - s1 - xh0 * s2),
+                                        r.y + rs * (g.y * s_w[cb + 2 * j + 1] - s1 - xh1 * s2));
         op[j] = *reinterpret_cast<uint32_t*>(&h);
       }
       *reinterpret_cast<uint4*>(dr + i * 256) = o;
@@ -213,11 +218,11 @@ __global__ void __launch_bounds__(256) layernorm_bwd_wb_wide_kernel(const bf16* 
 
 template <int NCH>
 static void launch_ln_bwd_fused(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
-                                float* dw_part, float* db_part, int parts, int M, cudaStream_t st) {
+                                float* dw_part, float* db_part, int parts, int M, cudaStream_t st, const void* dres) {
   int blocks = (M + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
   layernorm_bwd_fused_kernel<NCH><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, dw_part,
-                                                          db_part, M);
+                                                          db_part, M, (const bf16*)dres);
   constexpr int C = NCH * 256;
   dim3 grid((C / 8 + 255) / 256, parts);
   layernorm_bwd_wb_wide_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
@@ -230,21 +235,31 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
   layernorm_fwd_kernel<<<blocks, 256, 0, st>>>((const bf16*)x, w, b, (bf16*)y, mean, rstd, M, C, eps);
 }
 
-void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
-                   float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st) {
+// dres (optional, bf16 [M, C]): gradient arriving through the residual connection around the normalisation; dx = dres +
+// the LayerNorm input gradient in the same pass.  Returns false when the width has no fused kernel (the caller adds).
+bool layernorm_bwd_res(const void* dy, const void* x, const float* w, const float* mean, const float* rstd,
+                       const void* dres, void* dx, float* dw_part, float* db_part, int parts, int M, int C,
+                       cudaStream_t st) {
   switch (C) {   // single-pass kernel for the common widths
-    case 256: return launch_ln_bwd_fused<1>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
-    case 512: return launch_ln_bwd_fused<2>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
-    case 768: return launch_ln_bwd_fused<3>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
-    case 1024: return launch_ln_bwd_fused<4>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
-    case 2048: return launch_ln_bwd_fused<8>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st);
+    case 256: launch_ln_bwd_fused<1>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
+    case 512: launch_ln_bwd_fused<2>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
+    case 768: launch_ln_bwd_fused<3>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
+    case 1024: launch_ln_bwd_fused<4>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
+    case 2048: launch_ln_bwd_fused<8>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
     default: break;
   }
+  if (dres != nullptr) return false;
   int blocks = (M + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
   layernorm_bwd_dx_kernel<<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, M, C);
   dim3 grid((C + 31) / 32, parts), block(32, 8);
   layernorm_bwd_wb_kernel<<<grid, block, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
+  return true;
+}
+
+void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                   float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st) {
+  layernorm_bwd_res(dy, x, w, mean, rstd, nullptr, dx, dw_part, db_part, parts, M, C, st);
 }
 
 // ---------------------------------------------------------------------------------

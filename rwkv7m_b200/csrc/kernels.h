@@ -62,6 +62,11 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
                    float eps, cudaStream_t st);
 void layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
                    float* dw_part, float* db_part, int parts, int M, int C, cudaStream_t st);
+// Same with the gradient that arrives through the residual connection added to dx (dres: bf16 [M, C] or null).  Returns
+// false, doing nothing, when dres is given but the width has no single-pass kernel.
+bool layernorm_bwd_res(const void* dy, const void* x, const float* w, const float* mean, const float* rstd,
+                       const void* dres, void* dx, float* dw_part, float* db_part, int parts, int M, int C,
+                       cudaStream_t st);
 int shift_mix_parts(int B, int T);
 void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out, int K, int B, int T, int C,
                    cudaStream_t st);

@@ -43,6 +43,10 @@ class LayerNorm(nn.Module):
     def forward(self, x):
         return ops.layer_norm(x, self.weight, self.bias, self.eps)
 
+    def with_residual(self, x):
+        """(LayerNorm(x), x) for a block whose residual bypasses the normalised branch."""
+        return ops.layer_norm_residual(x, self.weight, self.bias, self.eps)
+
 
 class Linear(nn.Module):
     """Bias-free (by default) projection with ``weight`` stored [out, in]."""
@@ -244,13 +248,16 @@ class RWKV7Block(nn.Module):
         tp = getattr(self, "tp", None)
         if self.ln0 is not None:
             x = self.ln0(x)
-        h = self.ln1(x)
-        if tp is not None:  # sequence-sharded residual: gather tokens for the column-parallel projections
-            h = tp.gather_seq(h)
-        if tp is None:   # the residual adds ride in the epilogues of the two output projections
+        if tp is None:
+            # the residual adds ride in the epilogues of the two output projections, and the sums of the residual
+            # stream's gradient in the two LayerNorm backward kernels
+            h, x = self.ln1.with_residual(x)
             x, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv, residual=x)
-            x, cm_x = self.ffn(self.ln2(x), state.channel_mix_x, residual=x)
+            h, x = self.ln2.with_residual(x)
+            x, cm_x = self.ffn(h, state.channel_mix_x, residual=x)
             return x, v_first, LayerRWKVState(time_mix_x=tm_x, channel_mix_x=cm_x, wkv=wkv)
+        # sequence-sharded residual: gather tokens for the column-parallel projections
+        h = tp.gather_seq(self.ln1(x))
         att_out, v_first, tm_x, wkv = self.att(h, v_first, state.time_mix_x, state.wkv)
         # row-parallel output: sum the partial results over ranks, keep this rank's tokens, add the residual
         x = tp.reduce_scatter_add(att_out, x)

@@ -54,6 +54,13 @@ def layer_norm(x, weight, bias, eps=1e-5):
     return reference.layer_norm(x, weight, bias, eps)
 
 
+def layer_norm_residual(x, weight, bias, eps=1e-5):
+    """(LayerNorm(x), x); on CUDA the gradient of the returned x is added inside the LayerNorm backward kernel."""
+    if use_cuda(x):
+        return _cuda().layer_norm_residual(x, weight, bias, eps)
+    return reference.layer_norm(x, weight, bias, eps), x
+
+
 def shift_mix(x, prev, mix):
     if use_cuda(x):
         return _cuda().shift_mix(x, prev, mix)

@@ -426,9 +426,40 @@ class LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w, b, mean, rstd = ctx.saved_tensors
-        dx, dw, db = _C.layernorm_bwd(dy.contiguous(), x, _par(w), mean, rstd)
+        dx, dw, db = _C.layernorm_bwd(dy.contiguous(), x, _par(w), mean, rstd, None)
         _count(2)
         return dx, _like_param(dw, w), _like_param(db, b), None
+
+
+class LayerNormResidualFn(torch.autograd.Function):
+    """(LayerNorm(x), x): the second output is x itself, to be used as the residual that bypasses the normalised
+    branch.  In backward the gradient of that residual is added to the LayerNorm input gradient inside the kernel, so
+    the residual stream's gradient is never summed by a separate elementwise pass."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        xc = x.contiguous()
+        y, mean, rstd = _C.layernorm_fwd(xc, _par(w), _par(b), eps)
+        _count()
+        ctx.save_for_backward(xc, w, b, mean, rstd)
+        return y, xc.view_as(xc)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, w, b, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None
+        dx, dw, db = _C.layernorm_bwd(dy.contiguous(), x, _par(w), mean, rstd,
+                                      None if dres is None else dres.contiguous())
+        _count(2)
+        return dx, _like_param(dw, w), _like_param(db, b), None
+
+
+def layer_norm_residual(x, weight, bias, eps=1e-5):
+    """Returns (LayerNorm(x), x) with the two gradients summed inside the LayerNorm backward kernel."""
+    if _bf16(x) and x.shape[-1] % 2 == 0:
+        return LayerNormResidualFn.apply(x, weight, bias, eps)
+    return R.layer_norm(x, weight, bias, eps), x
 
 
 def layer_norm(x, weight, bias, eps=1e-5):

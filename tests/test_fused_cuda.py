@@ -158,3 +158,29 @@ def test_bf16_model_step_matches_reference_path():
         worst.append((num / den, n))
     worst.sort(reverse=True)
     assert worst[0][0] < 0.15, worst[:5]
+
+
+def test_layer_norm_residual_sums_both_gradients_in_the_kernel():
+    """(LayerNorm(x), x): the gradient of the returned residual is added to the LayerNorm input gradient inside the
+    backward kernel; compare with plain autograd on the fp32 oracle."""
+    from rwkv7m_b200 import ops
+    from rwkv7m_b200.ops import reference as R
+
+    torch.manual_seed(0)
+    for C in (768, 2048, 320):   # 320: no single-pass kernel, falls back to backward + add
+        x = (torch.randn(2, 96, C, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+        w = torch.randn(C, device="cuda").requires_grad_(True)
+        b = torch.randn(C, device="cuda").requires_grad_(True)
+        g1 = torch.randn(2, 96, C, device="cuda").bfloat16()
+        g2 = torch.randn(2, 96, C, device="cuda").bfloat16()
+        h, r = ops.layer_norm_residual(x, w, b)
+        assert torch.equal(r, x)
+        ((h.float() * g1.float()).sum() + (r.float() * g2.float()).sum()).backward()
+        xr = x.detach().float().requires_grad_(True)
+        wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+        href = R.layer_norm(xr, wr, br)
+        ((href * g1.float()).sum() + (xr * g2.float()).sum()).backward()
+        rel = lambda a, c: float((a.float() - c.float()).norm() / c.float().norm())
+        assert rel(h, href) < 1e-2
+        assert rel(x.grad, xr.grad) < 1e-2
+        assert rel(w.grad, wr.grad) < 1e-2 and rel(b.grad, br.grad) < 1e-2

@@ -46,7 +46,7 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
     for call, (M, C) in enumerate([(1000, 768), (2304, 2048)]):
         x, dy, w, b = _case(M, C, seed=call)
         _, mean, rstd = ext.layernorm_fwd(x, w, b, 1e-5)
-        dx_ref, dw_ref, db_ref = ext.layernorm_bwd(dy, x, w, mean, rstd)
+        dx_ref, dw_ref, db_ref = ext.layernorm_bwd(dy, x, w, mean, rstd, None)
         dx = torch.empty_like(x)
         dw = torch.full((C,), float("nan"), device="cuda")
         db = torch.full((C,), float("nan"), device="cuda")
