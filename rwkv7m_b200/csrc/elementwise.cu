@@ -114,8 +114,8 @@ __global__ void layernorm_bwd_wb_kernel(const bf16* __restrict__ dy, const bf16*
 }
 
 // dx in one pass: one warp per row with 16-byte accesses keeps the row of dy and x in registers, so nothing is read twice.
-template <int NCH>   // C = NCH * 256
-__global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+template <int NCH, bool RES>   // C = NCH * 256; RES: add the gradient that arrives through the residual connection
+__global__ void __launch_bounds__(256, (RES && NCH >= 8) ? 1 : 2) layernorm_bwd_fused_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                                                      const float* __restrict__ w, const float* __restrict__ mean,
                                                                      const float* __restrict__ rstd, bf16* __restrict__ dx,
                                                                      float* __restrict__ dw_part, float* __restrict__ db_part,
@@ -130,13 +130,11 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
   for (int row = r0 + warp; row < r1; row += 8) {
     const bf16* gr = dy + (size_t)row * C + lane * 8;
     const bf16* xr = x + (size_t)row * C + lane * 8;
-    uint4 graw[NCH], xraw[NCH], rraw[NCH];   // rraw: gradient arriving through the residual connection (optional)
+    uint4 graw[NCH], xraw[NCH];
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       graw[i] = __ldg(reinterpret_cast<const uint4*>(gr + i * 256));
       xraw[i] = __ldg(reinterpret_cast<const uint4*>(xr + i * 256));
-      rraw[i] = dres != nullptr ? __ldg(reinterpret_cast<const uint4*>(dres + (size_t)row * C + lane * 8 + i * 256))
-                                : make_uint4(0u, 0u, 0u, 0u);
     }
     const float mu = mean[row], rs = rstd[row];
     float s1 = 0.f, s2 = 0.f;
@@ -162,7 +160,14 @@ __global__ void __launch_bounds__(256, 2) layernorm_bwd_fused_kernel(const bf16*
     for (int i = 0; i < NCH; ++i) {
       const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
       const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
-      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rraw[i]);
+      // the residual-path gradient is read where it is used: keeping a third row in registers would spill at C = 2048
+      // (volatile asm: the compiler would otherwise hoist all NCH loads above the statistics)
+      uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+      if (RES)
+        asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(rr.x), "=r"(rr.y), "=r"(rr.z), "=r"(rr.w)
+                     : "l"(dres + (size_t)row * C + lane * 8 + i * 256));
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rr);
       const int cb = i * 256 + lane * 8;
       uint4 o;
       uint32_t* op = reinterpret_cast<uint32_t*>(&o);
@@ -221,8 +226,12 @@ static void launch_ln_bwd_fused(const void* dy, const void* x, const float* w, c
                                 float* dw_part, float* db_part, int parts, int M, cudaStream_t st, const void* dres) {
   int blocks = (M + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  layernorm_bwd_fused_kernel<NCH><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx, dw_part,
-                                                          db_part, M, (const bf16*)dres);
+  if (dres != nullptr)
+    layernorm_bwd_fused_kernel<NCH, true><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
+                                                                  dw_part, db_part, M, (const bf16*)dres);
+  else
+    layernorm_bwd_fused_kernel<NCH, false><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
+                                                                   dw_part, db_part, M, nullptr);
   constexpr int C = NCH * 256;
   dim3 grid((C / 8 + 255) / 256, parts);
   layernorm_bwd_wb_wide_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
