@@ -57,6 +57,59 @@ __global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const float* __
   }
 }
 
+// Single-pass forward for the common widths: one warp per row, the row stays in registers (16-byte accesses), weight and
+// bias are staged in shared memory once per block.
+template <int NCH>   // C = NCH * 256
+__global__ void __launch_bounds__(256) layernorm_fwd_wide_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
+                                                                 const float* __restrict__ b, bf16* __restrict__ y,
+                                                                 float* __restrict__ mean, float* __restrict__ rstd, int M,
+                                                                 float eps) {
+  constexpr int C = NCH * 256;
+  __shared__ float s_w[C], s_b[C];
+  for (int c = threadIdx.x; c < C; c += 256) { s_w[c] = w[c]; s_b[c] = b[c]; }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * 8 + warp; row < M; row += gridDim.x * 8) {
+    const bf16* xr = x + (size_t)row * C + lane * 8;
+    uint4 raw[NCH];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) raw[i] = __ldg(reinterpret_cast<const uint4*>(xr + i * 256));
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+        s += v.x + v.y;
+        ss += v.x * v.x + v.y * v.y;
+      }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mu = s / C;
+    const float var = fmaxf(ss / C - mu * mu, 0.f);
+    const float rs = rsqrtf(var + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+    bf16* yr = y + (size_t)row * C + lane * 8;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&raw[i]);
+      const int cb = i * 256 + lane * 8;
+      uint4 o;
+      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
+        bf162 h = __floats2bfloat162_rn((v.x - mu) * rs * s_w[cb + 2 * j] + s_b[cb + 2 * j],
+                                        (v.y - mu) * rs * s_w[cb + 2 * j + 1] + s_b[cb + 2 * j + 1]);
+        op[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(yr + i * 256) = o;
+    }
+  }
+}
+
 __global__ void layernorm_bwd_dx_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                         const float* __restrict__ w, const float* __restrict__ mean,
                                         const float* __restrict__ rstd, bf16* __restrict__ dx, int M, int C) {
@@ -241,6 +294,22 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
                    float eps, cudaStream_t st) {
   int blocks = (M + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  // few, long-lived blocks: every block stages weight and bias (8 C bytes) before its first row
+  const int wide_blocks = blocks > 148 * 4 ? 148 * 4 : blocks;
+#define RK_LN_FWD(NCH) \
+  layernorm_fwd_wide_kernel<NCH><<<wide_blocks, 256, 0, st>>>((const bf16*)x, w, b, (bf16*)y, mean, rstd, M, eps)
+  if (aligned) {
+    switch (C) {
+      case 256: RK_LN_FWD(1); return;
+      case 512: RK_LN_FWD(2); return;
+      case 768: RK_LN_FWD(3); return;
+      case 1024: RK_LN_FWD(4); return;
+      case 2048: RK_LN_FWD(8); return;
+      default: break;
+    }
+  }
+#undef RK_LN_FWD
   layernorm_fwd_kernel<<<blocks, 256, 0, st>>>((const bf16*)x, w, b, (bf16*)y, mean, rstd, M, C, eps);
 }
 
