@@ -984,6 +984,52 @@ __global__ void __launch_bounds__(256, 2) gn_bonus_gate_bwd_wide_kernel(GnParams
   for (int j = 0; j < 8; ++j) { p.dlnw_part[po + j] = aw[j]; p.dlnb_part[po + j] = ab[j]; p.drk_part[po + j] = ar[j]; }
 }
 
+// Forward with the same layout as the wide backward: thread = 8 consecutive channels (16-byte accesses), 8 lanes per head,
+// the next row's five pieces are in flight while this row is processed.  Rows [r0, r1) of one part per block.
+__global__ void __launch_bounds__(256) gn_bonus_gate_fwd_wide_kernel(GnParams p) {
+  const int c = threadIdx.x * 8;
+  float lw[8], lb[8], rk[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { lw[j] = p.ln_w[c + j]; lb[j] = p.ln_b[c + j]; rk[j] = p.r_k[c + j]; }
+  const int r0 = blockIdx.x * p.rows_per_part, r1 = min(p.M, r0 + p.rows_per_part);
+  uint4 nx[5];
+  auto fetch = [&](int row) {
+    const size_t o = (size_t)row * p.C + c;
+    nx[0] = __ldg(reinterpret_cast<const uint4*>(p.y + o)); nx[1] = __ldg(reinterpret_cast<const uint4*>(p.r + o));
+    nx[2] = __ldg(reinterpret_cast<const uint4*>(p.k + o)); nx[3] = __ldg(reinterpret_cast<const uint4*>(p.v + o));
+    nx[4] = __ldg(reinterpret_cast<const uint4*>(p.g + o));
+  };
+  auto cvt = [](const uint4& raw, float (&x)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&w[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    }
+  };
+  if (r0 < r1) fetch(r0);
+#pragma unroll 1
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    float y[8], r[8], k[8], v[8], g[8];
+    cvt(nx[0], y); cvt(nx[1], r); cvt(nx[2], k); cvt(nx[3], v); cvt(nx[4], g);
+    if (row + 1 < r1) fetch(row + 1);
+    float sy = 0.f, srk = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sy += y[j]; srk = fmaf(r[j] * k[j], rk[j], srk); }
+    const float mu = head_sum8(sy) * (1.f / 64.f);
+    const float s = head_sum8(srk);
+    float sv = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { y[j] -= mu; sv = fmaf(y[j], y[j], sv); }
+    const float rs = rsqrtf(head_sum8(sv) * (1.f / 64.f) + p.eps);
+    float out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = (y[j] * rs * lw[j] + lb[j] + s * v[j]) * g[j];
+    st8(p.out + o, out);
+  }
+}
+
 void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out, int M, int C, float eps,
                        cudaStream_t st) {
   GnParams p{};
@@ -992,6 +1038,10 @@ void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out
   p.ln_w = par[0]; p.ln_b = par[1]; p.r_k = par[2];
   p.out = (bf16*)out; p.M = M; p.C = C; p.eps = eps;
   p.rows_per_part = fwd_rows_per_part(M);
+  if (C % 64 == 0 && C / 8 <= 256 && (C / 8) % 32 == 0) {
+    gn_bonus_gate_fwd_wide_kernel<<<(M + p.rows_per_part - 1) / p.rows_per_part, C / 8, 0, st>>>(p);
+    return;
+  }
   dim3 grid((C / 64 + 7) / 8, (M + p.rows_per_part - 1) / p.rows_per_part);
   gn_bonus_gate_fwd_kernel<<<grid, 256, 0, st>>>(p);
 }
