@@ -801,6 +801,70 @@ __global__ void __launch_bounds__(256, 1) tmix_pre_bwd_wide_kernel(TmixPreParams
 
 int row_parts(int M) { return (M + kRowsPerPart - 1) / kRowsPerPart; }
 
+// Forward with 16-byte accesses: thread = 8 consecutive channels, 8 lanes per head, rows [r0, r1) of one part per block,
+// the next row's pieces in flight while this row is processed.
+template <bool HAS_V>
+__global__ void __launch_bounds__(256) tmix_pre_fwd_wide_kernel(TmixPreParams p) {
+  const int c = threadIdx.x * 8;
+  float w0[8], a0[8], v0[8], kk_[8], ka[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    w0[j] = p.w0[c + j]; a0[j] = p.a0[c + j]; kk_[j] = p.k_k[c + j]; ka[j] = p.k_a[c + j];
+    v0[j] = HAS_V ? p.v0[c + j] : 0.f;
+  }
+  const int r0 = blockIdx.x * p.rows_per_part, r1 = min(p.M, r0 + p.rows_per_part);
+  uint4 nx[HAS_V ? 6 : 4];
+  auto fetch = [&](int row) {
+    const size_t o = (size_t)row * p.C + c;
+    nx[0] = __ldg(reinterpret_cast<const uint4*>(p.k_raw + o)); nx[1] = __ldg(reinterpret_cast<const uint4*>(p.v_raw + o));
+    nx[2] = __ldg(reinterpret_cast<const uint4*>(p.w_lora + o)); nx[3] = __ldg(reinterpret_cast<const uint4*>(p.a_lora + o));
+    if (HAS_V) {
+      nx[4] = __ldg(reinterpret_cast<const uint4*>(p.vg_lora + o));
+      nx[5] = __ldg(reinterpret_cast<const uint4*>(p.v_first + o));
+    }
+  };
+  auto cvt = [](const uint4& raw, float (&x)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&w[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    }
+  };
+  if (r0 < r1) fetch(r0);
+#pragma unroll 1
+  for (int row = r0; row < r1; ++row) {
+    const size_t o = (size_t)row * p.C + c;
+    float k[8], v[8], wl[8], al[8], vg[8], vf[8];
+    cvt(nx[0], k); cvt(nx[1], v); cvt(nx[2], wl); cvt(nx[3], al);
+    if (HAS_V) { cvt(nx[4], vg); cvt(nx[5], vf); }
+    if (row + 1 < r1) fetch(row + 1);
+    float out[8], aa[8], x[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      out[j] = -softplusf_(-(w0[j] + wl[j])) - 0.5f;
+      aa[j] = sigmoidf_(a0[j] + al[j]);
+      x[j] = k[j] * kk_[j];
+      ss = fmaf(x[j], x[j], ss);
+    }
+    st8(p.w + o, out);
+    const float inv = rsqrtf(head_sum8(ss) + 1e-24f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = k[j] * (1.f + (aa[j] - 1.f) * ka[j]);
+    st8(p.k_mod + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = HAS_V ? v[j] + (vf[j] - v[j]) * sigmoidf_(v0[j] + vg[j]) : v[j];
+    st8(p.v + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { x[j] *= inv; out[j] = -x[j]; }
+    st8(p.neg_kk + o, out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = x[j] * aa[j];
+    st8(p.kka + o, out);
+  }
+}
+
 void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* out, int M, int C, cudaStream_t st) {
   TmixPreParams p{};
   p.k_raw = (const bf16*)in[0]; p.v_raw = (const bf16*)in[1]; p.w_lora = (const bf16*)in[2];
@@ -809,6 +873,12 @@ void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* o
   p.w = (bf16*)out[0]; p.k_mod = (bf16*)out[1]; p.v = (bf16*)out[2]; p.neg_kk = (bf16*)out[3]; p.kka = (bf16*)out[4];
   p.M = M; p.C = C;
   p.rows_per_part = fwd_rows_per_part(M);
+  if (C % 64 == 0 && C / 8 <= 256 && (C / 8) % 32 == 0) {
+    const int parts = (M + p.rows_per_part - 1) / p.rows_per_part;
+    if (p.vg_lora != nullptr) tmix_pre_fwd_wide_kernel<true><<<parts, C / 8, 0, st>>>(p);
+    else tmix_pre_fwd_wide_kernel<false><<<parts, C / 8, 0, st>>>(p);
+    return;
+  }
   dim3 grid((C / 64 + 7) / 8, (M + p.rows_per_part - 1) / p.rows_per_part);
   tmix_pre_fwd_kernel<<<grid, 256, 0, st>>>(p);
 }
