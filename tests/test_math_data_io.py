@@ -192,3 +192,26 @@ def test_zero3_unit_plan_covers_the_bulk_weights():
     assert all(".screening." not in n for n in bulk_names)
     with pytest.raises(ValueError):
         unit_key("layers.0.block.att.w0") if False else unit_key("ln_out.weight")
+
+
+def test_fused_op_fallbacks_match_their_compositions_on_cpu():
+    """ops.ffn / ops.linear_add / ops.layer_norm_residual on CPU are the plain compositions (same values and gradients)."""
+    from rwkv7m_b200 import ops
+    from rwkv7m_b200.ops import reference as Rf
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    res = torch.randn(2, 5, 16, requires_grad=True)
+    wk, wv, wo = (torch.randn(s, requires_grad=True) for s in ((24, 16), (16, 24), (16, 16)))
+    w, b = torch.randn(16, requires_grad=True), torch.randn(16, requires_grad=True)
+    out = ops.ffn(x, wk, wv, res) + ops.linear_add(res, x, wo)
+    h, r = ops.layer_norm_residual(out, w, b)
+    (h.sum() + (r * r).sum()).backward()
+    got = [t.grad.clone() for t in (x, res, wk, wv, wo, w, b)]
+    for t in (x, res, wk, wv, wo, w, b):
+        t.grad = None
+    ref = res + Rf.linear(Rf.relu_sq(Rf.linear(x, wk)), wv) + res + Rf.linear(x, wo)
+    (Rf.layer_norm(ref, w, b).sum() + (ref * ref).sum()).backward()
+    for a, t in zip(got, (x, res, wk, wv, wo, w, b)):   # same math, different association of the adds
+        assert float((a - t.grad).norm() / (t.grad.norm() + 1e-12)) < 1e-5
+    assert torch.equal(r, out)
