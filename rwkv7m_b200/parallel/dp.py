@@ -23,6 +23,36 @@ from ..config import normalize_phase
 from ..train.train_step import accumulate_gradients
 
 
+def global_loss_scales(batch, world: int, group=None):
+    """This rank's share of the global-batch loss as ``(ce_scale, l2_scale)``.
+
+    The reference computes one loss over the global batch (src/rwkv7m/train/nnx_train.py:334-357): cross-entropy is a
+    masked mean, so a rank's share is its mask count over the global mask count; L2Wrap is a mean over all positions,
+    so every rank's share is 1 / world.  The mask count stays on the device (a 0-d tensor): no host synchronisation.
+    """
+    mask = batch.get("mask")
+    if world == 1:
+        return 1.0, 1.0
+    if mask is None:
+        return 1.0 / world, 1.0 / world
+    local = mask.float().sum()
+    total = local.detach().clone().reshape(1)
+    dist.all_reduce(total, group=group)
+    return local / torch.clamp(total.reshape(()), min=1.0), 1.0 / world
+
+
+def reduce_loss_metrics(metrics, scales, group=None):
+    """Turn the per-rank ``loss`` / ``total_loss`` into their global-batch values with one 2-element all-reduce."""
+    ce_s, _ = scales
+    scaled_total = metrics.pop("scaled_total_loss", None)
+    if scaled_total is None:
+        scaled_total = metrics["total_loss"] * ce_s
+    pair = torch.stack([(metrics["loss"].detach() * ce_s).reshape(()).float(), scaled_total.detach().reshape(()).float()])
+    dist.all_reduce(pair, group=group)
+    metrics["loss"], metrics["total_loss"] = pair[0], pair[1]
+    return metrics
+
+
 class DataParallelTrainer:
     def __init__(self, train_state, mode: str = "allreduce", group=None):
         if mode not in ("single", "allreduce", "fused"):
@@ -88,14 +118,7 @@ class DataParallelTrainer:
         flat.sync_compute()
 
     def _loss_scale(self, batch):
-        mask = batch.get("mask")
-        B, T = batch["input_ids"].shape
-        if mask is None or self.world == 1:
-            return 1.0 / self.world
-        local = mask.float().sum().reshape(1).clone()
-        total = local.clone()
-        dist.all_reduce(total, group=self.group)
-        return float(local / torch.clamp(total, min=1.0))
+        return global_loss_scales(batch, self.world, self.group)
 
     def train_step(self, train_state, batch, rwkv_state, screen_state, *, phase="read_screening_only",
                    gradient_accumulation_steps=1):
@@ -104,7 +127,7 @@ class DataParallelTrainer:
         model.train()
         if self.mode != "fused":
             opt.zero_grad()
-        scale = 1.0 if self.world == 1 else self._loss_scale(batch)
+        scale = (1.0, 1.0) if self.world == 1 else self._loss_scale(batch)
         events = None
         if self.record_phases and opt.flat.master.is_cuda:
             events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -128,8 +151,7 @@ class DataParallelTrainer:
             self._phase_events.append(events)
         metrics["grad_norm"] = opt.grad_norm
         if self.world > 1:
-            for key in ("loss", "total_loss"):
-                t = metrics[key].detach().clone() * scale
-                dist.all_reduce(t, group=self.group)
-                metrics[key] = t
+            reduce_loss_metrics(metrics, scale, self.group)
+        else:
+            metrics.pop("scaled_total_loss", None)
         return train_state, new_rwkv, new_screen, metrics

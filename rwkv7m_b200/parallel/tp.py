@@ -235,22 +235,48 @@ class TensorParallel:
             if getattr(p, "_tp_replicated", False):
                 dist.broadcast(p.data, src=dist.get_global_rank(self.group, src), group=self.group)
 
-    def reduce_replicated_grads(self, model):
-        """Sum the gradients of replicated parameters over the group (call after backward)."""
-        grads = [p.grad for _, p in model.named_parameters()
-                 if getattr(p, "_tp_replicated", False) and p.grad is not None]
-        for g in grads:
-            dist.all_reduce(g, group=self.group)
+    @staticmethod
+    def _replicated_spans(flat):
+        """Merged ``(begin, end)`` spans of the flat gradient buffer that belong to replicated parameters."""
+        spans = []
+        for _, p, off, numel in flat.entries:
+            if not getattr(p, "_tp_replicated", False):
+                continue
+            if spans and spans[-1][1] == off:
+                spans[-1][1] = off + numel
+            else:
+                spans.append([off, off + numel])
+        return [(a, b) for a, b in spans]
 
-    def grad_norm_sq_reduce(self, model):
+    def reduce_replicated_grads(self, model, flat=None):
+        """Sum the gradients of replicated parameters over the group (call after backward).
+
+        With ``flat`` (the optimizer's :class:`FlatParams`, after ``collect_grads()``) the reduction runs over the
+        views of the flat gradient buffer, which is where the gradients live both when ``p.grad`` is bound to the
+        buffer and when it is not (bf16 parameters with fp32 accumulation fold ``p.grad`` into the buffer and reset
+        it to None).  Without ``flat`` only parameters that still carry a ``p.grad`` are reduced."""
+        if flat is not None:
+            for a, b in self._replicated_spans(flat):
+                dist.all_reduce(flat.grad[a:b], group=self.group)
+            return
+        for _, p in model.named_parameters():
+            if getattr(p, "_tp_replicated", False) and p.grad is not None:
+                dist.all_reduce(p.grad, group=self.group)
+
+    def grad_norm_sq_reduce(self, model, flat=None):
         """Callback for ``AdamWChain.step``: turns the local sum of squared gradients into the global one
-        (replicated parameters must be counted once, not once per rank)."""
+        (replicated parameters must be counted once, not once per rank).  ``flat`` as in
+        :meth:`reduce_replicated_grads`."""
 
         def reduce(norm_sq):
             rep = norm_sq.new_zeros(1)
-            for _, p in model.named_parameters():
-                if getattr(p, "_tp_replicated", False) and p.grad is not None:
-                    rep += p.grad.float().pow(2).sum()
+            if flat is not None:
+                for a, b in self._replicated_spans(flat):
+                    rep += flat.grad[a:b].float().pow(2).sum()
+            else:
+                for _, p in model.named_parameters():
+                    if getattr(p, "_tp_replicated", False) and p.grad is not None:
+                        rep += p.grad.float().pow(2).sum()
             local = norm_sq - rep * (self.world - 1) / self.world
             dist.all_reduce(local, group=self.group)
             norm_sq.copy_(local)
@@ -342,7 +368,7 @@ class TensorParallelTrainer:
             gradient_accumulation_steps=gradient_accumulation_steps,
         )
         opt.flat.collect_grads()
-        self.tp.reduce_replicated_grads(model)
-        opt.step(grad_norm_sq_reduce=self.tp.grad_norm_sq_reduce(model))
+        self.tp.reduce_replicated_grads(model, opt.flat)
+        opt.step(grad_norm_sq_reduce=self.tp.grad_norm_sq_reduce(model, opt.flat))
         metrics["grad_norm"] = opt.grad_norm
         return train_state, new_rwkv, new_screen, metrics

@@ -289,13 +289,9 @@ class Zero3Engine:
 
     # ---- optimizer step ------------------------------------------------------------------------------------------------------
     def _loss_scale(self, batch):
-        mask = batch.get("mask")
-        if mask is None:
-            return 1.0 / self.world
-        local = mask.float().sum().reshape(1).clone()
-        total = local.clone()
-        dist.all_reduce(total, group=self.group)
-        return float(local / torch.clamp(total, min=1.0))
+        from .dp import global_loss_scales
+
+        return global_loss_scales(batch, self.world, self.group)
 
     def train_step(self, train_state, batch, rwkv_state, screen_state, *, phase="read_screening_only",
                    gradient_accumulation_steps=1):
@@ -346,10 +342,9 @@ class Zero3Engine:
         self._barrier()
         self.resident = [None, None]
         metrics["grad_norm"] = self.grad_norm
-        for key in ("loss", "total_loss"):
-            tt = metrics[key].detach().clone() * scale
-            dist.all_reduce(tt, group=self.group)
-            metrics[key] = tt
+        from .dp import reduce_loss_metrics
+
+        reduce_loss_metrics(metrics, scale, self.group)
         return train_state, new_rwkv, new_screen, metrics
 
     def error_code(self) -> int:

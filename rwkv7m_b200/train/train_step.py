@@ -59,8 +59,9 @@ def initialize_train_state(seed, config: ModelConfig, *, total_steps: int = 1000
 
 
 def model_loss(model, batch, rwkv_state, screen_state, *, phase, include_l2wrap=True,
-               ce_loss_scale=1.0, l2_loss_scale=1.0):
-    """Returns (total_loss, (metrics, new_rwkv_state, new_screen_state))."""
+               ce_loss_scale=1.0, l2_loss_scale=1.0, loss_parts=None):
+    """Returns (total_loss, (metrics, new_rwkv_state, new_screen_state)).  A dict passed as ``loss_parts`` receives
+    the unscaled cross-entropy and L2Wrap terms under ``"ce"`` and ``"l2"``."""
     cfg = model.config
     input_ids = batch["input_ids"]
     T = int(input_ids.shape[1])
@@ -88,6 +89,8 @@ def model_loss(model, batch, rwkv_state, screen_state, *, phase, include_l2wrap=
     if include_l2wrap:
         total = total + l2_loss * l2_loss_scale
     metrics = {"loss": ce_loss.detach()}
+    if loss_parts is not None:
+        loss_parts["ce"], loss_parts["l2"] = ce_loss.detach(), l2_loss.detach()
     for k, v in (stats_total or {}).items():
         metrics[k] = torch.as_tensor(v).detach() / float(T)
     for k in _DEFAULT_ZERO_METRICS:
@@ -135,9 +138,12 @@ def accumulate_gradients(model, batch, rwkv_state, screen_state, *, phase, gradi
                          loss_scale=1.0):
     """Forward + backward over all micro-batches; gradients land in ``p.grad``.
 
-    ``loss_scale`` multiplies the loss before backward (data-parallel callers
-    pass their share of the global batch).  Returns (new_rwkv, new_screen,
-    metrics) with states detached.
+    ``loss_scale`` multiplies the loss before backward.  Data-parallel callers pass their share of the global
+    batch, either one number or a pair ``(ce_scale, l2_scale)``: the cross-entropy term is a masked mean over the
+    global batch (share = local mask count / global mask count) while the L2Wrap term is a mean over all positions
+    (share = 1 / world), so the two differ when ranks hold different mask counts.  Scales may be floats or 0-d
+    tensors.  Returns (new_rwkv, new_screen, metrics) with states detached; ``metrics["total_loss"]`` is the local
+    unscaled loss and ``metrics["scaled_total_loss"]`` its scaled form (this rank's term of the global loss).
     """
     B = int(batch["input_ids"].shape[0])
     T = int(batch["input_ids"].shape[1])
@@ -146,9 +152,12 @@ def accumulate_gradients(model, batch, rwkv_state, screen_state, *, phase, gradi
     mb = B // gradient_accumulation_steps
     mask = batch.get("mask")
     total_ce = float(B * T) if mask is None else torch.clamp(mask.float().sum(), min=1.0)
+    ce_s, l2_s = loss_scale if isinstance(loss_scale, (tuple, list)) else (loss_scale, loss_scale)
+    scaled = not (isinstance(ce_s, (int, float)) and isinstance(l2_s, (int, float)) and ce_s == 1.0 and l2_s == 1.0)
     new_rwkv, new_screen = [], []
     acc_metrics = None
     acc_loss = None
+    acc_scaled = None
     for micro in range(gradient_accumulation_steps):
         a, b = micro * mb, (micro + 1) * mb
         mbatch = {k: v[a:b] for k, v in batch.items()}
@@ -156,17 +165,23 @@ def accumulate_gradients(model, batch, rwkv_state, screen_state, *, phase, gradi
         micro_ce = float(mb * T) if mmask is None else mmask.float().sum()
         ce_w = micro_ce / total_ce
         pos_w = float(mb) / float(B)
+        parts = {}
         loss, (metrics, nr, ns) = model_loss(
             model, mbatch, _slice_rwkv(rwkv_state, a, b), _slice_screen(screen_state, a, b),
-            phase=phase, include_l2wrap=True, ce_loss_scale=ce_w, l2_loss_scale=pos_w,
+            phase=phase, include_l2wrap=True, ce_loss_scale=ce_w * ce_s, l2_loss_scale=pos_w * l2_s,
+            loss_parts=parts,
         )
-        (loss * loss_scale).backward()
+        loss.backward()
+        local = parts["ce"] * ce_w + parts["l2"] * pos_w
         weighted = {k: v * (ce_w if k == "loss" else pos_w) for k, v in metrics.items()}
         acc_metrics = weighted if acc_metrics is None else {k: acc_metrics[k] + weighted[k] for k in weighted}
-        acc_loss = loss.detach() if acc_loss is None else acc_loss + loss.detach()
+        acc_loss = local if acc_loss is None else acc_loss + local
+        acc_scaled = loss.detach() if acc_scaled is None else acc_scaled + loss.detach()
         new_rwkv.append(tuple(s.detach() for s in nr))
         new_screen.append(ns.detach())
     acc_metrics["total_loss"] = acc_loss
+    if scaled:
+        acc_metrics["scaled_total_loss"] = acc_scaled
     rw = new_rwkv[0] if len(new_rwkv) == 1 else _cat_rwkv(new_rwkv)
     sc = new_screen[0] if len(new_screen) == 1 else _cat_screen(new_screen)
     return rw, sc, acc_metrics

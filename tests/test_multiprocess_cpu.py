@@ -17,22 +17,26 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _cfg():
+def _cfg(param_dtype="float32"):
     cfg = R.tiny_config(use_screening=False)
     cfg.warmup_steps = 0
     cfg.lr_init = 1e-3
+    cfg.param_dtype = param_dtype
     return cfg
 
 
-def _global_batch(seed=5, B=4, T=8, V=256):
+def _global_batch(seed=5, B=4, T=8, V=256, uneven_mask=False):
     g = torch.Generator().manual_seed(seed)
     ids = torch.randint(0, V, (B, T + 1), generator=g).to(torch.int32)
-    return {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(), "mask": torch.ones(B, T)}
+    mask = torch.ones(B, T)
+    if uneven_mask:      # rows 0-1 (rank 0) keep 3 + 8 positions, rows 2-3 (rank 1) keep all 16
+        mask[0, 3:] = 0
+    return {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(), "mask": mask}
 
 
-def _single_process_params(steps=2):
-    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=4, total_steps=20)
-    batch = _global_batch()
+def _single_process_params(steps=2, param_dtype="float32", uneven_mask=False):
+    rt, ts = R.create_train_runtime(3, _cfg(param_dtype), batch_size=4, total_steps=20)
+    batch = _global_batch(uneven_mask=uneven_mask)
     losses = []
     for _ in range(steps):
         ts, m = R.train_batch(ts, batch, rt)
@@ -45,13 +49,13 @@ def _init(rank, world, port):
     dist.init_process_group("gloo", rank=rank, world_size=world)
 
 
-def _dp_worker(rank, world, port, out):
+def _dp_worker(rank, world, port, out, uneven_mask=False):
     _init(rank, world, port)
     from rwkv7m_b200.parallel import DataParallelTrainer
 
     rt, ts = R.create_train_runtime(3, _cfg(), batch_size=2, total_steps=20)
     DataParallelTrainer(ts, mode="allreduce")
-    full = _global_batch()
+    full = _global_batch(uneven_mask=uneven_mask)
     batch = {k: v[rank * 2 : (rank + 1) * 2] for k, v in full.items()}
     losses = []
     for _ in range(2):
@@ -63,12 +67,13 @@ def _dp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def _tp_worker(rank, world, port, out, vocab_parallel):
+def _tp_worker(rank, world, port, out, vocab_parallel, param_dtype="float32"):
     _init(rank, world, port)
     from rwkv7m_b200.parallel.tp import TensorParallel
 
     tp = TensorParallel.from_group(vocab_parallel=vocab_parallel)
-    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=4, total_steps=20, tp=tp)
+    rt, ts = R.create_train_runtime(3, _cfg(param_dtype), batch_size=4, total_steps=20, tp=tp)
+    assert ts.optimizer.flat.bound == (param_dtype == "float32")
     batch = _global_batch()
     losses = []
     for _ in range(2):
@@ -77,7 +82,8 @@ def _tp_worker(rank, world, port, out, vocab_parallel):
     full = tp.gather_full_parameters(ts.model)
     logits, _ = R.infer_prefill(rt, batch["input_ids"])
     if rank == 0:
-        torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "logits": logits}, out)
+        torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "logits": logits,
+                    "grad_norm": float(ts.optimizer.grad_norm)}, out)
     dist.barrier()   # leave together: a rank that tears gloo down while its peer is still in a collective aborts
     dist.destroy_process_group()
 
@@ -105,3 +111,55 @@ def test_tensor_parallel_two_ranks_matches_single_process(tmp_path, vocab_parall
     assert res["losses"] == pytest.approx(ref_losses, rel=1e-4)
     _compare(ref, res["params"], 5e-5)
     assert res["logits"].shape == (4, 8, 256)
+
+
+def test_tensor_parallel_bf16_parameters_reduce_replicated_gradients(tmp_path):
+    """bf16 parameters with fp32 accumulation: autograd's ``p.grad`` is folded into the flat buffer and reset, so the
+    sum over the group of the replicated leaves' gradients (LayerNorms, token-shift mixes, LoRA-down, embedding, head)
+    must run over the flat buffer.  One step, so the comparison is not dominated by bf16 rounding of the weights."""
+    rt, ts = R.create_train_runtime(3, _cfg("bfloat16"), batch_size=4, total_steps=20)
+    before = {n: p.detach().float().clone() for n, p in ts.model.named_parameters()}
+    ts, m = R.train_batch(ts, _global_batch(), rt)
+    ref = {n: p.detach().float().clone() for n, p in ts.model.named_parameters()}
+    ref_norm = float(ts.optimizer.grad_norm)
+    out = str(tmp_path / "tp_bf16.pt")
+    mp.spawn(_tp_worker_one_step, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["grad_norm"] == pytest.approx(ref_norm, rel=2e-3)
+    # every replicated leaf moved by the same update as in the single process (one bf16 ulp of slack)
+    for n in ref:
+        moved = (ref[n] - before[n]).abs().max()
+        diff = (res["params"][n].float() - ref[n]).abs().max()
+        assert float(diff) <= 0.02 * float(ref[n].abs().max()) + 1e-6, (n, float(diff), float(moved))
+
+
+def _tp_worker_one_step(rank, world, port, out):
+    _init(rank, world, port)
+    from rwkv7m_b200.parallel.tp import TensorParallel
+
+    tp = TensorParallel.from_group(vocab_parallel=False)
+    rt, ts = R.create_train_runtime(3, _cfg("bfloat16"), batch_size=4, total_steps=20, tp=tp)
+    assert not ts.optimizer.flat.bound
+    ts, m = R.train_batch(ts, _global_batch(), rt)
+    full = tp.gather_full_parameters(ts.model)
+    # replicated leaves must stay bit-identical across the ranks
+    for name, p in ts.model.named_parameters():
+        if getattr(p, "_tp_replicated", False):
+            mine = p.detach().float().clone()
+            other = mine.clone()
+            dist.broadcast(other, src=0)
+            assert torch.equal(mine, other), name
+    if rank == 0:
+        torch.save({"params": {n: v.clone() for n, v in full.items()}, "grad_norm": float(ts.optimizer.grad_norm)}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_data_parallel_uneven_masks_match_global_batch(tmp_path):
+    """Ranks with different mask counts: cross-entropy is weighted by the mask share, L2Wrap by 1 / world."""
+    ref, ref_losses = _single_process_params(uneven_mask=True)
+    out = str(tmp_path / "dp_mask.pt")
+    mp.spawn(_dp_worker, args=(2, _free_port(), out, True), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["losses"] == pytest.approx(ref_losses, rel=1e-4)
+    _compare(ref, res["params"], 2e-5)
