@@ -8,7 +8,13 @@ checkpoint, ``--resume`` (``--steps`` = additional updates), carry-state only
 with sequential sampling, lane-wrap resets, optional Python GC disabling.
 Throughput is device time per step (CUDA events), not host wall clock.
 ``--mesh-axis-names data`` selects data parallelism (``--dp-mode fused`` runs the
-reduce-scatter + AdamW + all-gather inside the optimizer kernels over NVLink).
+reduce-scatter + AdamW + all-gather inside the optimizer kernels over NVLink; it
+is the default on GPUs).  ``--mesh-axis-names data model --mesh-axis-sizes D M``
+builds the reference's ``data x model`` grid (src/rwkv7m/cli/train_binidx_distributed.py:434-444):
+tensor parallelism over the M adjacent ranks of a model group, every group
+consuming its own slice of the global batch.  The error words of the bounded
+device-side waits (peer barriers, GEMM and chunked-WKV pipelines) are read after
+every step and before every checkpoint; a non-zero word ends the run.
 """
 
 from __future__ import annotations
@@ -88,9 +94,14 @@ def parse_args(argv=None):
     p.add_argument("--mesh-axis-names", nargs="+", default=["data"])
     p.add_argument("--mesh-axis-sizes", type=int, nargs="+", default=None)
     p.add_argument("--param-axis-name", default=None)
-    p.add_argument("--dp-mode", choices=["fused", "allreduce", "zero3"], default="allreduce",
-                   help="fused: sharded optimizer step over NVLink; zero3: parameters, gradients and optimizer state "
+    p.add_argument("--dp-mode", choices=["auto", "fused", "allreduce", "zero3"], default="auto",
+                   help="fused: sharded optimizer step over NVLink (auto picks it on GPUs); allreduce: library "
+                        "all-reduce (auto picks it on CPU); zero3: parameters, gradients and optimizer state "
                         "sharded with per-layer gather / reduce-scatter (single checkpoint backend)")
+    p.add_argument("--tp-comm", choices=["fused", "fused-separate", "nccl"], default="fused",
+                   help="tensor-parallel collectives: reduce-scatter in the GEMM epilogue, separate NVLink kernels, or the library")
+    p.add_argument("--device-wait-limit-ms", type=float, default=2000.0,
+                   help="limit of every device-side wait on a peer GPU; a wait that runs out sets an error word")
     p.add_argument("--device", default="auto")
     p.add_argument("--collective-timeout-s", type=float, default=600.0,
                    help="process-group timeout: a rank that stops answering ends the others' next collective with an error")
@@ -179,8 +190,8 @@ def run_validation(args, model, cfg, device, info, eval_state):
     data_file = args.eval_data_file or args.data_file
     ds = create_host_binidx_dataset(
         data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size, magic_prime=None,
-        epoch_steps=max(args.eval_steps, 1), process_index=info["process_index"],
-        process_count=info["process_count"], sampling_mode=args.sampling_mode,
+        epoch_steps=max(args.eval_steps, 1), process_index=info.get("data_index", info["process_index"]),
+        process_count=info.get("data_count", info["process_count"]), sampling_mode=args.sampling_mode,
     )
     B = ds.layout.process_batch_size
     was_training = model.training
@@ -218,13 +229,30 @@ def _empty(cfg):
     return scr
 
 
+def device_error_words(trainer, engine, tp, train_state) -> dict:
+    """Current error words of every bounded device-side wait this run can reach (each read synchronises the host
+    with the device, so call it where the step has already been waited for)."""
+    from ..ops import cuda as K
+
+    words = {"gemm": K.gemm_error_code(train_state.optimizer.flat.master), "wkv_chunk": K.wkv_chunk_error_code(reset=False)}
+    fused = getattr(trainer, "fused", None)
+    if fused is not None:
+        words["dp_fused"] = fused.error_code()
+    if engine is not None:
+        words["zero3"] = engine.error_code()
+    if tp is not None and getattr(tp, "fused", None) is not None:
+        words["tp_fused"] = tp.fused.error_code()
+    return words
+
+
 def run_distributed_training(args):
     info = initialize_distributed(timeout_s=args.collective_timeout_s)
     rank, world = info["process_index"], info["process_count"]
     mesh = make_mesh(tuple(args.mesh_axis_names), args.mesh_axis_sizes, world_size=world)
-    if mesh.model_size != 1:
-        raise ValueError("this trainer drives data parallelism; tensor-parallel runs use rwkv7m_b200.parallel.tp")
-    validate_args(args, world)
+    use_tp = mesh.model_size > 1
+    data_rank, _ = mesh.coords(rank)
+    info = dict(info, data_index=data_rank, data_count=mesh.data_size)
+    validate_args(args, mesh.data_size)
     if torch.cuda.is_available() and args.device in ("auto", None):
         device = torch.device("cuda", info["local_rank"])
         torch.cuda.set_device(device)
@@ -240,30 +268,62 @@ def run_distributed_training(args):
         cfg, start_step = build_config(args), 0
     if args.ctx_len > cfg.max_seq_len:
         raise ValueError(f"ctx_len={args.ctx_len} exceeds model max_seq_len={cfg.max_seq_len}")
-    if cfg.vocab_parallel:
+    if cfg.vocab_parallel and not use_tp:
         raise ValueError("vocab_parallel requires a model-parallel mesh axis")
 
+    # every rank of a model group reads the same rows: the data axis alone divides the global batch
     dataset = create_host_binidx_dataset(
         args.data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size,
-        magic_prime=args.magic_prime, epoch_steps=max(args.steps, 1), process_index=rank, process_count=world,
-        sampling_mode=args.sampling_mode,
+        magic_prime=args.magic_prime, epoch_steps=max(args.steps, 1), process_index=data_rank,
+        process_count=mesh.data_size, sampling_mode=args.sampling_mode,
     )
     B = dataset.layout.process_batch_size
     alloc = None
-    mode = "single" if world == 1 else args.dp_mode
+    use_cuda = device.type == "cuda"
+    mode = args.dp_mode
+    if mode == "auto":
+        mode = "fused" if (use_cuda and not use_tp) else "allreduce"
+    if world == 1:
+        mode = "single"
+    if use_cuda:
+        from ..ops.build import load_extension
+
+        load_extension().dp_set_wait_limit_ms(float(args.device_wait_limit_ms))
+    tp = None
+    if use_tp:
+        if mode in ("fused", "zero3"):
+            raise ValueError("--dp-mode fused / zero3 are not combined with a model axis; use allreduce")
+        if normalize_backend(args.checkpoint_backend) != "single":
+            raise ValueError("a tensor-parallel run writes checkpoints with --checkpoint-backend single")
+        if args.ctx_len % mesh.model_size != 0:
+            raise ValueError("--ctx-len must be divisible by the model axis (the residual stream is sharded over time)")
+        from ..parallel.mesh import new_subgroups
+        from ..parallel.tp import TensorParallel, TensorParallelTrainer, parameter_partition_summary
+
+        data_group, model_group = new_subgroups(mesh)
+        tp = TensorParallel.from_group(model_group, vocab_parallel=bool(cfg.vocab_parallel))
+        if use_cuda and args.tp_comm != "nccl":
+            tp.enable_fused(B * args.ctx_len * cfg.d_model, device, gemm_epilogue_scatter=args.tp_comm == "fused")
     if mode == "fused":
         from ..parallel.fused_dp import SymmetricFlatBuffers
 
         alloc = SymmetricFlatBuffers()
     runtime, train_state = create_train_runtime(
         args.seed, cfg, batch_size=B, total_steps=max(start_step + args.steps, 1), device=device,
-        shard_multiple=max(world, 1) * 8, buffer_allocator=alloc,
+        shard_multiple=max(world, 1) * 8, buffer_allocator=alloc, tp=tp,
     )
     zero3 = mode == "zero3"
     if zero3 and normalize_backend(args.checkpoint_backend) != "single":
         raise ValueError("--dp-mode zero3 writes checkpoints with --checkpoint-backend single")
-    trainer = DataParallelTrainer(train_state, mode="allreduce" if zero3 else mode)
-    if trainer.fused is not None:
+    if use_tp:
+        trainer = TensorParallelTrainer(train_state, tp, data_group=data_group if mesh.data_size > 1 else None)
+        if mesh.data_size > 1:   # the groups start from one set of weights
+            for r in mesh.data_group_ranks(rank)[:1]:
+                torch.distributed.broadcast(train_state.optimizer.flat.master, src=r, group=data_group)
+            train_state.optimizer.flat.sync_compute()
+    else:
+        trainer = DataParallelTrainer(train_state, mode="allreduce" if zero3 else mode)
+    if getattr(trainer, "fused", None) is not None:
         train_state.extras["fused_optimizer"] = trainer.fused
     if args.resume:
         train_state, _ = restore_distributed_train_state(args.resume, train_state, info)
@@ -292,17 +352,31 @@ def run_distributed_training(args):
         "tokens_seen": 0, "checkpoint_backend": args.checkpoint_backend, "sampling_mode": args.sampling_mode,
         "carry_state": args.carry_state, "latest_checkpoint": None, "best_eval": None, "last_train": None,
         "last_eval": None, "process_info": dict(info), "dp_mode": mode,
+        "mesh": {"data": mesh.data_size, "model": mesh.model_size}, "device_error_words": {},
     }
     if args.output_dir is not None and rank == 0:
         _write_json(Path(args.output_dir) / "run_config.json", {
             "args": vars(args), "model_config": model_config_to_dict(cfg), "process_info": dict(info),
             "environment": environment_manifest(), "mesh": {"data": mesh.data_size, "model": mesh.model_size},
+            **({"partition": parameter_partition_summary(train_state.model, tp.world, tp.vocab_parallel)} if use_tp else {}),
         })
     _write_summary(args, info, summary)
+
+    def check_device_words():
+        """Error words of the bounded device-side waits; any non-zero word ends the run (and forbids a checkpoint)."""
+        if not use_cuda:
+            return
+        words = device_error_words(trainer, engine, tp, train_state)
+        bad = {k: v for k, v in words.items() if v}
+        if bad:
+            summary["device_error_words"] = {k: hex(v) for k, v in bad.items()}
+            raise RuntimeError("a bounded device-side wait ran out: " +
+                               ", ".join(f"{k}={v:#x}" for k, v in bad.items()))
 
     def save(step, extra=None):
         if args.output_dir is None:
             return None
+        check_device_words()   # never write (and rotate good checkpoints out for) a state built on partial sums
         path = checkpoint_path(args.output_dir, step)
         metadata = {
             "data_file": args.data_file, "ctx_len": args.ctx_len, "global_batch_size": args.global_batch_size,
@@ -325,7 +399,6 @@ def run_distributed_training(args):
     if args.disable_python_gc:
         gc.disable()
     eval_state = {}
-    use_cuda = device.type == "cuda"
     try:
         say(f"data_tokens={dataset.data_size} magic_prime={dataset.magic_prime} ctx_len={args.ctx_len} "
             f"global_batch_size={args.global_batch_size} world={world} dp_mode={mode} start_step={start_step}")
@@ -349,6 +422,7 @@ def run_distributed_training(args):
                 e1.record()
                 e1.synchronize()
                 elapsed = e0.elapsed_time(e1) / 1e3
+                check_device_words()   # the step has finished on the device: four 4-byte reads
             else:
                 elapsed = time.perf_counter() - t0
             done = int(train_state.step)
@@ -385,10 +459,7 @@ def run_distributed_training(args):
         final = int(train_state.step)
         if args.output_dir is not None and (last_ckpt is None or Path(last_ckpt).name != f"ckpt-{final:08d}"):
             last_ckpt = save(final)
-        if trainer.fused is not None and trainer.fused.error_code() != 0:
-            raise RuntimeError(f"a bounded wait on a peer GPU ran out (code {trainer.fused.error_code():#x})")
-        if engine is not None and engine.error_code() != 0:
-            raise RuntimeError(f"a bounded wait on a peer GPU ran out (code {engine.error_code():#x})")
+        check_device_words()
         summary.update(status="completed", ended_at=_now())
         _write_summary(args, info, summary)
     except BaseException as exc:

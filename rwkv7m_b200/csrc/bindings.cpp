@@ -693,6 +693,8 @@ void tp_gemm_reduce_scatter(const Tensor& x2, const Tensor& w, const Tensor& sca
 }
 
 int64_t dp_aux_error_word() { return rk::dp_aux_error_word(); }
+void dp_set_wait_limit_ms(double ms) { rk::dp_set_wait_limit_ms(ms); }
+double dp_wait_limit_ms() { return rk::dp_wait_limit_ms(); }
 int64_t dp_aux_words() { return rk::dp_aux_words(); }
 
 }  // namespace
@@ -746,5 +748,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_aux_error_word", []() { return (int64_t)rk::tp_aux_error_word(); });
   m.def("tp_aux_words", []() { return (int64_t)rk::tp_aux_words(); });
   m.def("dp_aux_error_word", &dp_aux_error_word);
+  m.def("dp_set_wait_limit_ms", &dp_set_wait_limit_ms);
+  m.def("dp_wait_limit_ms", &dp_wait_limit_ms);
   m.def("dp_aux_words", &dp_aux_words);
 }

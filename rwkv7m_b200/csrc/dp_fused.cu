@@ -16,7 +16,9 @@
 //   barrier            new parameters have landed everywhere
 //
 // Peers are reached with plain ld/st/red and multimem instructions only.
-// Every wait is bounded (about two seconds) and reports through an error word instead of hanging.
+// Every wait is bounded (two seconds unless dp_set_wait_limit_ms() says otherwise) and reports through an error
+// word instead of hanging; once the word is set, the reduce and AdamW kernels of the same and of later steps
+// return without touching memory, so a wait that ran out makes the step a no-op rather than a wrong update.
 // The reference has no counterpart: its data parallelism is an XLA-inserted all-reduce with
 // replicated optimizer state (src/rwkv7m/distributed/trainer.py:31-51).
 #include "common.cuh"
@@ -67,8 +69,15 @@ constexpr int kAuxNorm = 16;      // [2][kMaxRanks] partial sums of squares, dou
 constexpr int kAuxError = 48;     // non-zero after a wait ran out
 constexpr int kAuxLocalNorm = 49; // this rank's partial sum of squares of the current step
 
+uint64_t g_wait_limit_ns = 2000000000ull;   // host copy, passed to every barrier launch
+
+__device__ __forceinline__ bool dp_failed(const DpPeers& peers, int rank) {
+  return *reinterpret_cast<volatile const int*>(reinterpret_cast<const uint32_t*>(peers.aux[rank]) + kAuxError) != 0;
+}
+
 // One CTA, one thread per peer.  Optionally publishes this rank's partial norm first.
-__global__ void dp_barrier_kernel(DpPeers peers, int rank, int world, uint32_t target, int publish_parity) {
+__global__ void dp_barrier_kernel(DpPeers peers, int rank, int world, uint32_t target, int publish_parity,
+                                  uint64_t limit_ns) {
   const int p = threadIdx.x;
   if (p >= world) return;
   uint32_t* my_aux = reinterpret_cast<uint32_t*>(peers.aux[rank]);
@@ -84,7 +93,7 @@ __global__ void dp_barrier_kernel(DpPeers peers, int rank, int world, uint32_t t
   bool ok = false;
   for (uint32_t it = 0; it < (1u << 28); ++it) {
     if (ld_acquire_sys(mine) >= target) { ok = true; break; }
-    if ((it & 63u) == 63u && gtimer_ns() - t0 > 2000000000ull) break;
+    if ((it & 63u) == 63u && gtimer_ns() - t0 > limit_ns) break;
   }
   if (!ok) atomicExch(reinterpret_cast<int*>(my_aux + kAuxError), 0x20000 | p);
   __threadfence_system();
@@ -93,6 +102,7 @@ __global__ void dp_barrier_kernel(DpPeers peers, int rank, int world, uint32_t t
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(256) dp_reduce_shard_kernel(DpPeers peers, int rank, int world, int64_t begin,
                                                               int64_t end) {
+  if (dp_failed(peers, rank)) return;   // a barrier gave up: the peers' gradients may be unfinished
   float* my_grad = reinterpret_cast<float*>(peers.grad[rank]);
   float acc = 0.f;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
@@ -123,6 +133,7 @@ __global__ void __launch_bounds__(256) dp_reduce_shard_kernel(DpPeers peers, int
 
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(256) dp_adamw_allgather_kernel(DpPeers peers, DpAdamW a) {
+  if (dp_failed(peers, a.rank)) return;   // no update from partial sums
   const float* my_grad = reinterpret_cast<const float*>(peers.grad[a.rank]);
   float* my_master = reinterpret_cast<float*>(peers.master[a.rank]);
   const float* slots = reinterpret_cast<const float*>(peers.aux[a.rank]) + kAuxNorm + a.parity * kMaxRanks;
@@ -185,8 +196,14 @@ int grid_for(int64_t n) {
 }  // namespace
 
 void dp_barrier(const DpPeers& peers, int rank, int world, uint32_t target, int publish_parity, cudaStream_t st) {
-  dp_barrier_kernel<<<1, 32, 0, st>>>(peers, rank, world, target, publish_parity);
+  dp_barrier_kernel<<<1, 32, 0, st>>>(peers, rank, world, target, publish_parity, g_wait_limit_ns);
 }
+
+void dp_set_wait_limit_ms(double ms) {
+  if (ms < 1.0) ms = 1.0;
+  g_wait_limit_ns = (uint64_t)(ms * 1.0e6);
+}
+double dp_wait_limit_ms() { return (double)g_wait_limit_ns / 1.0e6; }
 
 void dp_reduce_shard(const DpPeers& peers, int rank, int world, int64_t begin, int64_t end, cudaStream_t st) {
   float* local = reinterpret_cast<float*>(peers.aux[rank]) + kAuxLocalNorm;

@@ -121,6 +121,8 @@ struct DpAdamW {
 void dp_barrier(const DpPeers& peers, int rank, int world, uint32_t target, int publish_parity, cudaStream_t st);
 void dp_reduce_shard(const DpPeers& peers, int rank, int world, int64_t begin, int64_t end, cudaStream_t st);
 void dp_adamw_allgather(const DpPeers& peers, const DpAdamW& a, cudaStream_t st);
+void dp_set_wait_limit_ms(double ms);   // limit of every device-side barrier wait (default 2000)
+double dp_wait_limit_ms();
 int dp_aux_error_word();
 int dp_aux_words();
 

@@ -124,6 +124,22 @@ def save_data_parallel_checkpoint(checkpoint_dir, train_state, config, process_i
     backend = normalize_backend(backend)
     rank, world = _world(process_info)
     checkpoint_dir = Path(checkpoint_dir)
+    tp = train_state.extras.get("tp")
+    if tp is not None:
+        # tensor-parallel shards are gathered into full tensors: the files are those of an un-sharded run
+        if backend != "single":
+            raise ValueError("a tensor-parallel train state is saved with the 'single' checkpoint backend")
+        with tp.materialized(train_state):
+            if rank == 0:
+                save_train_checkpoint(checkpoint_dir, train_state, config, rng_key=rng_key,
+                                      dataset_position=dataset_position, metadata=metadata, runtime_state=None)
+                _patch_json(checkpoint_dir, {"backend": "single", "world_size": world, "model_parallel": tp.world})
+        if runtime_state is not None:   # recurrent state holds this rank's heads: one file per rank
+            if rank != 0:
+                checkpoint_dir.mkdir(parents=True, exist_ok=True)
+            save_runtime_state(checkpoint_dir / f"runtime_state.rank{rank:05d}.safetensors", runtime_state)
+        _barrier(process_info)
+        return checkpoint_dir
     zero3 = train_state.extras.get("zero3")
     if zero3 is not None:
         # parameters and moments are sharded piece by piece: gather them into the replicated layout for the writer
@@ -205,6 +221,13 @@ def restore_distributed_train_state(checkpoint_dir, train_state_template, proces
     config, payload = load_distributed_checkpoint_raw_metadata(checkpoint_dir)
     opt = train_state_template.optimizer
     shard = _moment_shard(train_state_template)
+    tp = train_state_template.extras.get("tp")
+    if tp is not None:
+        if payload.get("backend", "single") == "sharded":
+            raise ValueError("a tensor-parallel run restores from a 'single' checkpoint")
+        tp.load_full_state(train_state_template, lambda ts: load_train_checkpoint(checkpoint_dir, ts))
+        return train_state_template, DistributedCheckpointPayload(
+            config, payload, int(payload.get("step", 0)), payload.get("dataset_position"))
     if payload.get("backend", "single") == "sharded":
         if int(payload.get("world_size", 1)) != world:
             raise ValueError(

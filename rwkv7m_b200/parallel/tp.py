@@ -20,6 +20,7 @@ after backward.  The LM head is either replicated over the sequence shards or vo
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -296,6 +297,91 @@ class TensorParallel:
             out[name] = torch.cat(parts, dim=d)
         return out
 
+    # ---- checkpoints -------------------------------------------------------------------
+    def _gather_dim(self, local, dim):
+        parts = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(parts, local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=dim)
+
+    @contextlib.contextmanager
+    def materialized(self, train_state):
+        """Within the context the train state looks un-sharded: every parameter carries its full tensor and the
+        optimizer's ``state_dict()`` returns full Adam moments, so the ordinary checkpoint writers produce the same
+        portable files as a single-process run (restorable at any model-parallel size).  Collective: every rank of
+        the group must enter."""
+        opt = train_state.optimizer
+        flat = opt.flat
+        saved, full_m, full_v = {}, {}, {}
+        for name, p, off, numel in flat.entries:
+            d = getattr(p, "_tp_shard_dim", None)
+            m = opt.exp_avg[off:off + numel].view(p.shape)
+            v = opt.exp_avg_sq[off:off + numel].view(p.shape)
+            saved[name] = p.data
+            if d is None:
+                full_m[name], full_v[name] = m, v
+            else:
+                p.data = self._gather_dim(p.data, d)
+                full_m[name], full_v[name] = self._gather_dim(m, d), self._gather_dim(v, d)
+        original = opt.state_dict
+
+        def full_state_dict():
+            out = {"count": torch.tensor(opt.count, dtype=torch.int64)}
+            for name in full_m:
+                out[f"exp_avg/{name}"] = full_m[name]
+                out[f"exp_avg_sq/{name}"] = full_v[name]
+            return out
+
+        opt.state_dict = full_state_dict
+        try:
+            yield train_state
+        finally:
+            opt.state_dict = original
+            for name, p, _, _ in flat.entries:
+                p.data = saved[name]
+
+    def load_full_state(self, train_state, loader):
+        """Restore from un-sharded tensors.  ``loader(train_state)`` must fill the parameters (``p.data``) and call
+        ``optimizer.load_state_dict`` with full-size tensors, as the single-process restore does; this method lends it
+        full-size parameter storage and a ``load_state_dict`` that keeps this rank's slices."""
+        opt = train_state.optimizer
+        flat = opt.flat
+        shards = {}
+        for name, p, off, numel in flat.entries:
+            d = getattr(p, "_tp_shard_dim", None)
+            shards[name] = p.data
+            if d is not None:
+                shape = list(p.shape)
+                shape[d] *= self.world
+                p.data = torch.zeros(shape, dtype=p.dtype, device=p.device)
+        original = opt.load_state_dict
+
+        def take(full, p_local, d):
+            if d is None:
+                return full
+            n = p_local.shape[d]
+            return full.narrow(d, self.rank * n, n)
+
+        def sharded_load_state_dict(state):
+            opt.count = int(state["count"])
+            for name, p, off, numel in flat.entries:
+                d = getattr(p, "_tp_shard_dim", None)
+                local = shards[name]
+                opt.exp_avg[off:off + numel].copy_(take(state[f"exp_avg/{name}"], local, d).reshape(-1))
+                opt.exp_avg_sq[off:off + numel].copy_(take(state[f"exp_avg_sq/{name}"], local, d).reshape(-1))
+
+        opt.load_state_dict = sharded_load_state_dict
+        try:
+            result = loader(train_state)
+        finally:
+            opt.load_state_dict = original
+            for name, p, _, _ in flat.entries:
+                d = getattr(p, "_tp_shard_dim", None)
+                full, local = p.data, shards[name]
+                local.copy_(take(full, local, d))
+                p.data = local
+        flat.sync_compute()
+        return result
+
     # ---- state -------------------------------------------------------------------------
     def init_rwkv_state(self, batch_size, config, device=None) -> tuple:
         H = config.n_heads // self.world
@@ -349,10 +435,17 @@ class TensorParallelTrainer:
     """Installs the tensor-parallel optimizer step on a train state whose model was sharded with
     :meth:`TensorParallel.shard_model`.  Every rank of the group consumes the same batch."""
 
-    def __init__(self, train_state, tp: TensorParallel):
+    def __init__(self, train_state, tp: TensorParallel, data_group=None):
+        """``data_group`` (optional): the ranks that hold the same model shard in the other model-parallel groups of a
+        ``data x model`` mesh; every group then consumes its own slice of the global batch and the gradients are
+        summed over ``data_group`` after backward (src/rwkv7m/cli/train_binidx_distributed.py:434-444 builds the
+        same grid as a named device mesh)."""
         self.tp = tp
         self.train_state = train_state
+        self.data_group = data_group
+        self.data_world = dist.get_world_size(data_group) if data_group is not None else 1
         train_state.extras["train_step"] = self.train_step
+        train_state.extras["tp"] = tp
 
     def train_step(self, train_state, batch, rwkv_state, screen_state, *, phase="read_screening_only",
                    gradient_accumulation_steps=1):
@@ -363,12 +456,23 @@ class TensorParallelTrainer:
         model, opt = train_state.model, train_state.optimizer
         model.train()
         opt.zero_grad()
+        scale = 1.0
+        if self.data_world > 1:
+            from .dp import global_loss_scales
+
+            scale = global_loss_scales(batch, self.data_world, self.data_group)
         new_rwkv, new_screen, metrics = accumulate_gradients(
             model, batch, rwkv_state, screen_state, phase=phase,
-            gradient_accumulation_steps=gradient_accumulation_steps,
+            gradient_accumulation_steps=gradient_accumulation_steps, loss_scale=scale,
         )
         opt.flat.collect_grads()
+        if self.data_world > 1:
+            dist.all_reduce(opt.flat.grad, group=self.data_group)
         self.tp.reduce_replicated_grads(model, opt.flat)
         opt.step(grad_norm_sq_reduce=self.tp.grad_norm_sq_reduce(model, opt.flat))
         metrics["grad_norm"] = opt.grad_norm
+        if self.data_world > 1:
+            from .dp import reduce_loss_metrics
+
+            reduce_loss_metrics(metrics, scale, self.data_group)
         return train_state, new_rwkv, new_screen, metrics

@@ -82,3 +82,37 @@ def test_device_barrier_wait_is_bounded_and_reports():
     assert 1000.0 < e0.elapsed_time(e1) < 10000.0                           # waited about two seconds, then returned
     assert int(aux0[C.tp_aux_error_word()].item()) == (0x50000 | 1)          # "peer 1 never arrived"
     assert torch.equal(out[:, :4], x) and float(torch.ones(4, device=dev).sum()) == 4.0   # context still healthy
+
+
+@pytest.mark.gpu
+def test_dp_barrier_limit_is_a_parameter_and_a_failed_wait_makes_the_reduce_a_noop():
+    """The data-parallel barrier gives up after the configured limit (here 200 ms instead of the default two seconds),
+    and once its error word is set the gradient reduce that follows returns without touching memory, so a wait that
+    ran out cannot turn unfinished peer gradients into an update.  The wait is on a counter nothing increments."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    dev = torch.device("cuda", 0)
+    old = C.dp_wait_limit_ms()
+    try:
+        C.dp_set_wait_limit_ms(200.0)
+        assert C.dp_wait_limit_ms() == 200.0
+        aux0 = torch.zeros(C.dp_aux_words(), dtype=torch.int32, device=dev)
+        aux1 = torch.zeros(C.dp_aux_words(), dtype=torch.int32, device=dev)     # the silent peer's scratch words
+        g0 = torch.full((1024,), 1.0, device=dev)
+        g1 = torch.full((1024,), 2.0, device=dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        C.dp_barrier_only([aux0.data_ptr(), aux1.data_ptr()], 0, 1, aux0)
+        e1.record()
+        C.zero_reduce([g0.data_ptr(), g1.data_ptr()], [aux0.data_ptr(), aux1.data_ptr()], 0, 0, 0, 1024, aux0)
+        torch.cuda.synchronize()
+        assert 100.0 < e0.elapsed_time(e1) < 1500.0
+        assert int(aux0[C.dp_aux_error_word()].item()) == (0x20000 | 1)          # "peer 1 never arrived"
+        assert float(g0.sum()) == 1024.0                                          # the reduce did not run
+        aux0.zero_()
+        C.zero_reduce([g0.data_ptr(), g1.data_ptr()], [aux0.data_ptr(), aux1.data_ptr()], 0, 0, 0, 1024, aux0)
+        torch.cuda.synchronize()
+        assert float(g0.sum()) == 3.0 * 1024                                      # with a clean word it does
+    finally:
+        C.dp_set_wait_limit_ms(old)
