@@ -7,14 +7,22 @@
 One rank per GPU, weak scaling (8 sequences x 4096 tokens per GPU), synthetic
 uniform-random token ids, random-init weights, bf16 compute with fp32 master
 weights and fp32 Adam moments, full optimizer step inside the timed region.
-Rank 0 prints ONE JSON line.  ``--impl reference`` is the arm that would run
-the unmodified reference from ``baseline/_ref``.
+Every step (warm-up, timed, end-to-end) consumes a fresh batch, so the loss stays
+near ln(vocab) and remains a sanity check.  With more than one GPU the 1.5B
+headline runs ZeRO-3 (parameters, gradients and optimizer state sharded); an
+out-of-memory error is an error, never a silent switch to layer recompute.
+The line also carries ``wkv7_fwd_bwd_tflops``: the WKV7 kernels alone at the
+model's (T, B, H, N), timed in the same process (9 N^2 useful FLOPs per token and
+head forward, 2.5x that backward).  Rank 0 prints ONE JSON line.
+``--impl reference`` drives the unmodified reference from ``baseline/_ref``
+through its own public API when that copy imports, and says why when it does not.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -37,11 +45,14 @@ def parse_args(argv=None):
     ap.add_argument("--model", default="1.5b", choices=["0.19b", "1.5b", "7b", "tiny"])
     ap.add_argument("--batch", type=int, default=8, help="sequences per GPU")
     ap.add_argument("--seq", type=int, default=4096)
-    ap.add_argument("--remat", default="auto", choices=["auto", "on", "off"])
+    ap.add_argument("--remat", default="off", choices=["auto", "on", "off"],
+                    help="off: no layer recompute, out of memory is an error (headline); on: every layer; "
+                         "auto: smallest of 0, L/3, 2L/3, L layers that fits (reported in config.remat_layers)")
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
-    ap.add_argument("--dp", default="fused", choices=["fused", "nccl", "zero3"],
+    ap.add_argument("--dp", default="auto", choices=["auto", "fused", "nccl", "zero3"],
                     help="fused: replicated weights, sharded optimizer step over NVLink; nccl: all-reduce baseline; "
-                         "zero3: parameters, gradients and optimizer state sharded, per-layer gather / reduce-scatter")
+                         "zero3: parameters, gradients and optimizer state sharded, per-layer gather / reduce-scatter; "
+                         "auto: zero3 for the 1.5b model (the configuration the headline names), fused otherwise")
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
                     help="dp: weak scaling, --batch sequences per GPU; tp: tensor parallel over all GPUs, --batch = global batch")
     ap.add_argument("--tp-comm", default="fused", choices=["fused", "fused-separate", "nccl"],
@@ -50,6 +61,7 @@ def parse_args(argv=None):
     ap.add_argument("--screening", action="store_true",
                     help="enable the screening memory of the 0.185b preset (read/write phase, carry-state streaming)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-wkv", action="store_true", help="skip the WKV7 kernel figure")
     ap.add_argument("--phases", action="store_true",
                     help="also report the mean device time of forward+backward and of gradient exchange + optimizer")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
@@ -57,24 +69,129 @@ def parse_args(argv=None):
 
 
 def reference_arm(args):
-    """The reference is JAX/Flax (Python >= 3.13, jax >= 0.10); report whether an
-    installed copy under baseline/_ref can be imported in this interpreter."""
+    """Run the unmodified reference (JAX / Flax NNX) from ``baseline/_ref`` through its own public API:
+    ``rwkv7m.api.create_train_runtime`` + ``train_batch`` (src/rwkv7m/api.py:62-91,187-220) on the same model shape,
+    batch and dtype policy, timed like the reference times itself (``block_until_ready`` around the steps,
+    src/rwkv7m/cli/train_binidx_distributed.py:581-600).  Prints the ``unavailable`` line when that copy cannot be
+    imported or has no GPU backend in this image."""
     ref = ROOT / "baseline" / "_ref"
-    reason = None
-    if not ref.exists():
-        reason = ("baseline/_ref is absent: the offline pip install of the reference fails (build backend hatchling is not "
-                  "in the wheelhouse; it also requires Python >= 3.13 and jax/flax/optax/orbax, none of which are installed)")
-    else:
-        sys.path.insert(0, str(ref))
-        try:
-            import jax  # noqa: F401
-            import rwkv7m  # noqa: F401
-        except Exception as exc:  # pragma: no cover - depends on the box
-            reason = f"reference not importable here: {type(exc).__name__}: {str(exc)[:120]}"
-    if reason is None:
-        reason = "reference imported but its JAX runtime has no CUDA backend in this image"
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    if not ref.exists() or not any(ref.iterdir()):
+        print(json.dumps({"impl": "reference", "unavailable": (
+            "baseline/_ref is absent: the offline pip install of the reference fails (build backend hatchling is not in "
+            "the wheelhouse; it also requires Python >= 3.13 and jax/flax/optax/orbax, none of which are installed)")}))
+        return 0
+    sys.path.insert(0, str(ref))
+    try:
+        import jax
+        import jax.numpy as jnp
+        import numpy as np
+        import rwkv7m
+        from rwkv7m import api as ref_api
+        from rwkv7m.model.screened_rwkv import ModelConfig as RefConfig
+    except Exception as exc:  # pragma: no cover - depends on the box
+        print(json.dumps({"impl": "reference",
+                          "unavailable": f"reference not importable here: {type(exc).__name__}: {str(exc)[:160]}"}))
+        return 0
+    try:  # pragma: no cover - needs the reference's JAX stack
+        gpus = [d for d in jax.devices() if d.platform == "gpu"]
+        if len(gpus) < args.gpus:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": f"the reference's JAX runtime sees {len(gpus)} GPU(s), {args.gpus} wanted"}))
+            return 0
+        shapes = {"0.19b": (768, 12, 12, 3072), "1.5b": (2048, 24, 32, 8192), "7b": (4096, 32, 64, 15232)}
+        if args.model not in shapes:
+            raise ValueError(f"no reference shape for --model {args.model}")
+        d_model, n_layers, n_heads, d_ffn = shapes[args.model]
+        B, T, V = args.batch * args.gpus, args.seq, 65536
+        cfg = RefConfig(d_model=d_model, d_ffn=d_ffn, n_layers=n_layers, n_heads=n_heads, head_size=64, vocab_size=V,
+                        max_seq_len=T, dtype="bfloat16", use_screening=False, lm_head_init="variance_scaled",
+                        head_chunk_size=max(1, 8192 // args.batch))
+        sharding = None
+        if args.gpus > 1:
+            from rwkv7m.distributed.mesh import make_mesh as ref_mesh
+            from rwkv7m.model.nnx_model import NNXShardingConfig
+
+            sharding = NNXShardingConfig(mesh=ref_mesh(("data",), (args.gpus,)))
+        runtime, train_state = ref_api.create_train_runtime(jax.random.PRNGKey(7), cfg, batch_size=B,
+                                                            total_steps=10_000, sharding=sharding)
+        rng = np.random.default_rng(1234)
+
+        def make_batch():
+            ids = rng.integers(0, V, size=(B, T + 1), dtype=np.int32)
+            return {"input_ids": jnp.asarray(ids[:, :-1]), "target_ids": jnp.asarray(ids[:, 1:]),
+                    "mask": jnp.ones((B, T), jnp.float32)}
+
+        batches = [make_batch() for _ in range(args.warmup + args.steps)]
+        metrics = None
+        for i in range(args.warmup):
+            train_state, metrics = ref_api.train_batch(train_state, batches[i], runtime)
+        jax.block_until_ready(metrics)
+        sampler = ClockSampler(0)
+        sampler.start()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            train_state, metrics = ref_api.train_batch(train_state, batches[args.warmup + i], runtime)
+        jax.block_until_ready((train_state.nnx_params, metrics))
+        ms = (time.perf_counter() - t0) * 1e3
+        clocks = sampler.stop()
+        tokens = B * T * args.steps
+        print(json.dumps({
+            "metric": METRIC if (args.model == "1.5b" and T == 4096) else f"train tokens/s/box at {args.model} ctx{T}",
+            "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+            "impl": "reference",
+            "config": {"model": f"rwkv7-{args.model} (d_model {d_model}, layers {n_layers}, d_ffn {d_ffn}, vocab {V})",
+                       "global_batch": B, "seq_len": T, "parallelism": f"dp{args.gpus}",
+                       "timing": "host clock around the K timed steps with block_until_ready, as the reference times itself",
+                       "rwkv7m_version": getattr(rwkv7m, "__version__", "unknown")},
+            "clocks": clocks, "last_loss": float(metrics["loss"]),
+        }))
+    except Exception as exc:
+        print(json.dumps({"impl": "reference",
+                          "unavailable": f"reference imported but failed to run: {type(exc).__name__}: {str(exc)[:200]}"}))
     return 0
+
+
+def wkv7_kernel_figure(torch, device, T, B, H, iters=5):
+    """WKV7 forward and backward kernels alone at the model's shape: CUDA events, fresh inputs larger than L2
+    (6 x B T H N bf16), useful-FLOP convention 9 N^2 per token and head forward and 2.5x that backward."""
+    from rwkv7m_b200 import ops
+
+    N = 64
+    g = torch.Generator(device=device).manual_seed(3)
+
+    def rnd(scale=1.0):
+        return (torch.randn(B, T, H, N, device=device, generator=g) * scale).to(torch.bfloat16)
+
+    r, k, v = rnd(), rnd(), rnd()
+    w = (-0.5 - torch.nn.functional.softplus(-torch.randn(B, T, H, N, device=device, generator=g))).to(torch.bfloat16)
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N, device=device, generator=g), dim=-1)
+    a = (-kk).to(torch.bfloat16)
+    b = (kk * torch.sigmoid(torch.randn(B, T, H, N, device=device, generator=g))).to(torch.bfloat16)
+    s0 = torch.zeros(B, H, N, N, device=device)
+    ins = [t.requires_grad_(True) for t in (r, w, k, v, a, b)]
+    dy = rnd()
+    fwd, bwd = [], []
+    for i in range(iters + 2):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        y, sT = ops.wkv7(*ins, s0)
+        e[1].record()
+        y.backward(dy)
+        e[2].record()
+        torch.cuda.synchronize()
+        for t in ins:
+            t.grad = None
+        if i >= 2:
+            fwd.append(e[0].elapsed_time(e[1]))
+            bwd.append(e[1].elapsed_time(e[2]))
+    f_ms, b_ms = statistics.median(fwd), statistics.median(bwd)
+    flops_f = 9.0 * N * N * T * B * H
+    return {"shape_TBHN": [T, B, H, N], "fwd_ms": f_ms, "bwd_ms": b_ms,
+            "fwd_tflops": flops_f / (f_ms * 1e-3) / 1e12,
+            "fwd_bwd_tflops": 3.5 * flops_f / ((f_ms + b_ms) * 1e-3) / 1e12,
+            "convention": "9 N^2 FLOPs per token and head forward, backward 2.5x; autograd call of ops.wkv7, CUDA events"}
 
 
 class ClockSampler:
@@ -157,6 +274,8 @@ def main(argv=None):
     from rwkv7m_b200.parallel import DataParallelTrainer
 
     K.set_gemm_backend(args.gemm)
+    if args.dp == "auto":
+        args.dp = "zero3" if (args.model == "1.5b" and args.parallel == "dp" and not args.screening) else "fused"
     if args.model == "tiny":
         cfg = tiny_config(use_screening=False, d_model=128, n_heads=2, head_size=64, vocab_size=1024)
         cfg.dtype = "bfloat16"
@@ -236,9 +355,10 @@ def main(argv=None):
                     trainer = DataParallelTrainer(train_state, mode=mode)
             if args.phases and hasattr(trainer, "record_phases"):
                 trainer.record_phases = True
-            dev_batches = [make_batch(False) for _ in range(2)]
+            # a fresh batch for every step (warm-up and timed), resident on the device before the clock starts
+            dev_batches = [make_batch(False) for _ in range(args.warmup + args.steps)]
             for i in range(args.warmup):
-                train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime, phase=phase, carry_state=carry)
+                train_state, metrics = R.train_batch(train_state, dev_batches[i], runtime, phase=phase, carry_state=carry)
             torch.cuda.synchronize()
             used_remat = remat
             break
@@ -268,7 +388,8 @@ def main(argv=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        train_state, metrics = R.train_batch(train_state, dev_batches[i % 2], runtime, phase=phase, carry_state=carry)
+        train_state, metrics = R.train_batch(train_state, dev_batches[args.warmup + i], runtime, phase=phase,
+                                             carry_state=carry)
     e1.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
@@ -280,19 +401,41 @@ def main(argv=None):
     # ---- end-to-end through the public API -------------------------------------
     e2e = None
     if not args.no_e2e:
-        host_batches = [make_batch(True) for _ in range(min(args.steps, 4))]
+        host_batches = [make_batch(True) for _ in range(args.steps)]
         h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
         sync_all()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for i in range(args.steps):
-            train_state, metrics = R.train_batch(train_state, host_batches[i % len(host_batches)], runtime,
-                                                 phase=phase, carry_state=carry)
+            train_state, metrics = R.train_batch(train_state, host_batches[i], runtime, phase=phase, carry_state=carry)
             loss_host = float(metrics["loss"])  # device -> host read of the step result
         f1.record()
         sync_all()
         e2e_ms = f0.elapsed_time(f1)
         e2e = {"ms": e2e_ms, "h2d": h2d, "d2h": 4, "loss": loss_host}
+
+    # ---- error words of every bounded device-side wait ---------------------------------
+    words = {"gemm": K.gemm_error_code(train_state.optimizer.flat.master), "wkv_chunk": K.wkv_chunk_error_code()}
+    for name, obj in (("dp_fused", getattr(trainer, "fused", None)), ("zero3", trainer if args.dp == "zero3" else None),
+                      ("tp_fused", getattr(trainer, "fused", None) if use_tp else None)):
+        if obj is not None and hasattr(obj, "error_code"):
+            words[name] = obj.error_code()
+    if any(words.values()):
+        raise SystemExit(f"a bounded device-side wait ran out during the benchmark: {words}")
+
+    # ---- WKV7 kernels alone, same process -------------------------------------------------
+    wkv = None
+    if not args.no_wkv and rank == 0 and cfg.head_size == 64:
+        try:
+            free_b, _ = torch.cuda.mem_get_info(device)
+            need = 30 * B * T * cfg.d_model * 2
+            if free_b > need:
+                wkv = wkv7_kernel_figure(torch, device, T, B, cfg.n_heads // (world if use_tp else 1))
+            else:
+                torch.cuda.empty_cache()
+                wkv = wkv7_kernel_figure(torch, device, T, B, cfg.n_heads // (world if use_tp else 1))
+        except torch.cuda.OutOfMemoryError:
+            wkv = {"skipped": "not enough free device memory beside the train state"}
 
     times = torch.tensor([ms, e2e["ms"] if e2e else 0.0], dtype=torch.float64, device=device)
     if world > 1:
@@ -332,7 +475,11 @@ def main(argv=None):
             "clocks": clocks,
             "gpu_launches": launches,
             "last_loss": last_loss,
+            "expected_loss_random_ids": math.log(V),
         }
+        if wkv is not None:
+            line["wkv7_fwd_bwd_tflops"] = wkv.get("fwd_bwd_tflops")
+            line["wkv7"] = wkv
         if phases is not None:
             line["phases"] = phases
         if e2e is not None:

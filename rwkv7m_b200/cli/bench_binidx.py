@@ -7,13 +7,13 @@ from __future__ import annotations
 import argparse
 import csv
 import sys
-import time
 
 import torch
 
 from ..api import create_train_runtime, train_batch
 from ..config import ModelConfig, ScreeningConfig
 from ..data import create_binidx_dataset
+from ..utils.timing import DeviceTimer, nvtx_range
 from .common import (
     add_execution_args,
     add_model_source_args,
@@ -61,18 +61,18 @@ def run_variant(args, variant) -> dict:
     runtime, state = create_train_runtime(args.seed, cfg, batch_size=args.batch_size, total_steps=args.steps,
                                           device=device)
     losses = []
-    start = time.perf_counter()
+    timer = DeviceTimer(device)   # CUDA events on the launching stream (host clock on CPU)
     try:
-        for step in range(args.steps):
-            state, metrics = train_batch(state, dataset.get_batch(step), runtime, phase=phase)
-            losses.append(float(metrics["loss"]))
-            if args.print_every and (step % args.print_every == 0 or step == args.steps - 1):
-                print(f"{variant} step={step} loss={losses[-1]:.6f}")
-        if device.type == "cuda":
-            torch.cuda.synchronize(device)
+        with timer:
+            for step in range(args.steps):
+                with nvtx_range(f"{variant}.step"):
+                    state, metrics = train_batch(state, dataset.get_batch(step), runtime, phase=phase)
+                losses.append(float(metrics["loss"]))
+                if args.print_every and (step % args.print_every == 0 or step == args.steps - 1):
+                    print(f"{variant} step={step} loss={losses[-1]:.6f}")
     finally:
         dataset.close()
-    elapsed = time.perf_counter() - start
+    elapsed = timer.ms / 1e3
     tokens = args.steps * args.batch_size * args.ctx_len
     return {"variant": variant, "steps": args.steps, "tokens": tokens, "seconds": elapsed,
             "tokens_per_sec": tokens / elapsed if elapsed > 0 else 0.0,

@@ -1,6 +1,7 @@
 // Allocation-free LayerNorm backward: see noalloc.h for the contract.
 #include "noalloc.h"
 
+#include <cstdint>
 #include <mutex>
 
 #include "common.cuh"
@@ -49,6 +50,11 @@ extern "C" int rwkv7m_layernorm_bwd_noalloc(const void* dy, const void* x, const
   if (dy == nullptr || x == nullptr || w == nullptr || mean == nullptr || rstd == nullptr || dx == nullptr ||
       dw == nullptr || db == nullptr)
     return RWKV7M_NOALLOC_ERR_ARG;
+  // the fused widths read and write dy, x and dx as 16-byte vectors; a misaligned row pointer would fault on the GPU
+  auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (misaligned(dy, 16) || misaligned(x, 16) || misaligned(dx, 16) || misaligned(w, 4) || misaligned(mean, 4) ||
+      misaligned(rstd, 4) || misaligned(dw, 4) || misaligned(db, 4))
+    return RWKV7M_NOALLOC_ERR_ARG;
   if (M < 1 || C < 2 || (C & 1) || C > RWKV7M_NOALLOC_MAX_C) return RWKV7M_NOALLOC_ERR_SIZE;
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
@@ -72,7 +78,8 @@ extern "C" const char* rwkv7m_noalloc_strerror(int code) {
     case RWKV7M_NOALLOC_OK: return "ok";
     case RWKV7M_NOALLOC_ERR_SIZE: return "size outside the supported range (C even, 2 <= C <= 8192, M >= 1)";
     case RWKV7M_NOALLOC_ERR_CUDA: return "CUDA runtime call failed";
-    case RWKV7M_NOALLOC_ERR_ARG: return "null pointer argument";
+    case RWKV7M_NOALLOC_ERR_ARG:
+      return "null or misaligned pointer argument (dy, x, dx: 16-byte aligned; fp32 arrays: 4-byte aligned)";
   }
   return "unknown code";
 }

@@ -11,6 +11,8 @@
 //
 // Contract
 //  * dy, x, dx: bf16 [M, C] row-major; w, mean, rstd, dw, db: fp32 ([C], [M], [M], [C], [C]).
+//  * dy, x and dx must start on a 16-byte boundary (the kernels use 16-byte vector accesses), the fp32 arrays on a
+//    4-byte boundary.  A null or misaligned pointer is rejected with RWKV7M_NOALLOC_ERR_ARG and nothing is launched.
 //  * C must be even and at most RWKV7M_NOALLOC_MAX_C; M >= 1.  Larger sizes are rejected with
 //    RWKV7M_NOALLOC_ERR_SIZE and nothing is launched.
 //  * The scratch array (RWKV7M_NOALLOC_SCRATCH_BYTES, 4 MiB) is held by every GPU that loads the
@@ -35,7 +37,7 @@ extern "C" {
 #define RWKV7M_NOALLOC_OK 0
 #define RWKV7M_NOALLOC_ERR_SIZE 1    /* M or C outside the supported range */
 #define RWKV7M_NOALLOC_ERR_CUDA 2    /* a CUDA runtime call failed (symbol lookup or launch) */
-#define RWKV7M_NOALLOC_ERR_ARG 3     /* null pointer */
+#define RWKV7M_NOALLOC_ERR_ARG 3     /* null or misaligned pointer */
 
 /* stream is a cudaStream_t passed as void* (NULL = default stream). */
 int rwkv7m_layernorm_bwd_noalloc(const void* dy, const void* x, const float* w, const float* mean,

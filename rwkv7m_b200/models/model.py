@@ -18,6 +18,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from ..config import ModelConfig, normalize_phase
 from ..state import LayerRWKVState, LayerScreenState, ModelScreenState
+from ..utils.timing import check_finite, nvtx_range
 from .rwkv7 import LayerNorm, Linear, RWKV7Block, _orthogonal, _uniform
 from .screening import StateLevelScreening
 
@@ -102,10 +103,12 @@ class ScreenedRWKVModel(nn.Module):
             if hook is not None:
                 hook.pre_forward(hook.unit_of_layer(idx))
                 x = hook.mark_enter(x, hook.unit_of_layer(idx))
-            if (cfg.remat_blocks or idx < self.remat_layer_count) and torch.is_grad_enabled():
-                x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
-            else:
-                x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)
+            with nvtx_range(f"layer.{idx}"):
+                if (cfg.remat_blocks or idx < self.remat_layer_count) and torch.is_grad_enabled():
+                    x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
+                else:
+                    x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)
+            check_finite(f"layer.{idx} output", x, rwkv_l.wkv)
             if hook is not None:
                 x = hook.mark_leave(x, hook.unit_of_layer(idx))
             new_rwkv[idx] = rwkv_l
@@ -148,9 +151,11 @@ class ScreenedRWKVModel(nn.Module):
         if hook is not None:
             hook.pre_forward(hook.unit_of("head"))
             hidden = hook.mark_enter(hidden, hook.unit_of("head"))
-        ce_total, ce_count, l2_total, l2_count = ops.head_loss(
-            hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, targets, mask, chunk, self.ln_out.eps
-        )
+        with nvtx_range("head_loss"):
+            ce_total, ce_count, l2_total, l2_count = ops.head_loss(
+                hidden, self.ln_out.weight, self.ln_out.bias, self.head.weight, targets, mask, chunk, self.ln_out.eps
+            )
+        check_finite("head_loss", ce_total, l2_total)
         if hook is not None:
             ce_total = hook.mark_leave(ce_total, hook.unit_of("head"))
         return {"ce_total": ce_total, "ce_count": ce_count, "l2_total": l2_total, "l2_count": l2_count}

@@ -21,6 +21,7 @@ import torch.distributed as dist
 
 from ..config import normalize_phase
 from ..train.train_step import accumulate_gradients
+from ..utils.timing import check_finite, nvtx_range
 
 
 def global_loss_scales(batch, world: int, group=None):
@@ -138,14 +139,16 @@ class DataParallelTrainer:
         )
         if events is not None:
             events[1].record()
-        if self.mode == "single":
-            opt.step()
-        elif self.mode == "allreduce":
-            opt.flat.collect_grads()
-            dist.all_reduce(opt.flat.grad, group=self.group)
-            opt.step()
-        else:
-            self.fused.step()
+        with nvtx_range(f"exchange_optimizer.{self.mode}"):
+            if self.mode == "single":
+                opt.step()
+            elif self.mode == "allreduce":
+                opt.flat.collect_grads()
+                dist.all_reduce(opt.flat.grad, group=self.group)
+                opt.step()
+            else:
+                self.fused.step()
+        check_finite("gradient norm", opt.grad_norm)
         if events is not None:
             events[2].record()
             self._phase_events.append(events)

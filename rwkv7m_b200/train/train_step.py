@@ -17,6 +17,7 @@ from ..config import ModelConfig, normalize_phase
 from ..models.model import ScreenedRWKVModel, initialize_model
 from ..state import LayerRWKVState, LayerScreenState, ModelScreenState
 from .optimizer import AdamWChain, create_optimizer
+from ..utils.timing import check_finite, nvtx_range
 
 _DEFAULT_ZERO_METRICS = (
     "rel_read_mean",
@@ -166,12 +167,15 @@ def accumulate_gradients(model, batch, rwkv_state, screen_state, *, phase, gradi
         ce_w = micro_ce / total_ce
         pos_w = float(mb) / float(B)
         parts = {}
-        loss, (metrics, nr, ns) = model_loss(
-            model, mbatch, _slice_rwkv(rwkv_state, a, b), _slice_screen(screen_state, a, b),
-            phase=phase, include_l2wrap=True, ce_loss_scale=ce_w * ce_s, l2_loss_scale=pos_w * l2_s,
-            loss_parts=parts,
-        )
-        loss.backward()
+        with nvtx_range("forward"):
+            loss, (metrics, nr, ns) = model_loss(
+                model, mbatch, _slice_rwkv(rwkv_state, a, b), _slice_screen(screen_state, a, b),
+                phase=phase, include_l2wrap=True, ce_loss_scale=ce_w * ce_s, l2_loss_scale=pos_w * l2_s,
+                loss_parts=parts,
+            )
+        with nvtx_range("backward"):
+            loss.backward()
+        check_finite("loss", loss)
         local = parts["ce"] * ce_w + parts["l2"] * pos_w
         weighted = {k: v * (ce_w if k == "loss" else pos_w) for k, v in metrics.items()}
         acc_metrics = weighted if acc_metrics is None else {k: acc_metrics[k] + weighted[k] for k in weighted}
@@ -198,7 +202,9 @@ def train_step(train_state: TrainState, batch, rwkv_state, screen_state, *, phas
         model, batch, rwkv_state, screen_state, phase=phase,
         gradient_accumulation_steps=gradient_accumulation_steps,
     )
-    opt.step()
+    with nvtx_range("optimizer"):
+        opt.step()
+    check_finite("gradient norm", opt.grad_norm)
     metrics["grad_norm"] = opt.grad_norm
     return train_state, new_rwkv, new_screen, metrics
 

@@ -21,8 +21,25 @@ def debug_sync_enabled() -> bool:
     return os.environ.get("RWKV7M_B200_DEBUG_SYNC", "0") == "1"
 
 
+def ranges_enabled() -> bool:
+    """NVTX ranges are emitted with RWKV7M_B200_NVTX=1 (and always in the debug-sync mode)."""
+    return os.environ.get("RWKV7M_B200_NVTX", "0") == "1" or debug_sync_enabled()
+
+
+RANGE_LOG = None   # a list here records every range name that was entered (tests, quick textual traces)
+
+
 @contextlib.contextmanager
 def nvtx_range(name: str):
+    """Named range around a phase of a step (a layer's forward, the head loss, the optimizer ...).  Off by default:
+    the body runs with no extra work.  With RWKV7M_B200_NVTX=1 the range is pushed to NVTX, where a timeline
+    profiler shows it; with RWKV7M_B200_DEBUG_SYNC=1 the exit also synchronises the device, so an asynchronous
+    kernel fault or a bounded wait that ran out surfaces in the range that caused it."""
+    if not ranges_enabled():
+        yield
+        return
+    if RANGE_LOG is not None:
+        RANGE_LOG.append(name)
     use = torch.cuda.is_available()
     if use:
         torch.cuda.nvtx.range_push(name)

@@ -215,3 +215,28 @@ def test_fused_op_fallbacks_match_their_compositions_on_cpu():
     for a, t in zip(got, (x, res, wk, wv, wo, w, b)):   # same math, different association of the adds
         assert float((a - t.grad).norm() / (t.grad.norm() + 1e-12)) < 1e-5
     assert torch.equal(r, out)
+
+
+def test_debug_ranges_and_finite_checks_are_wired_into_a_step(monkeypatch):
+    """RWKV7M_B200_DEBUG_SYNC=1: every layer, the head loss, backward and the optimizer run inside a named range, and a
+    NaN in a layer output is caught where it appears."""
+    import rwkv7m_b200 as R
+    from rwkv7m_b200.utils import timing
+
+    cfg = R.tiny_config(use_screening=False)
+    rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=5)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 256, (2, 9), generator=g).to(torch.int32)
+    batch = {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(), "mask": torch.ones(2, 8)}
+    monkeypatch.setattr(timing, "RANGE_LOG", [])
+    ts, _ = R.train_batch(ts, batch, rt)
+    assert timing.RANGE_LOG == []                       # off by default
+    monkeypatch.setenv("RWKV7M_B200_DEBUG_SYNC", "1")
+    ts, _ = R.train_batch(ts, batch, rt)
+    names = timing.RANGE_LOG
+    assert [f"layer.{i}" for i in range(cfg.n_layers)] == [n for n in names if n.startswith("layer.")]
+    assert {"forward", "head_loss", "backward", "optimizer"} <= set(names)
+    with torch.no_grad():
+        ts.model.layers[1].block.ln1.weight.fill_(float("nan"))
+    with pytest.raises(FloatingPointError, match="layer.1"):
+        R.train_batch(ts, batch, rt)

@@ -43,11 +43,13 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
     ext = load_extension()
     lib, fn = _lib()
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (M, C) in enumerate([(1000, 768), (2304, 2048)]):
+    # fused widths (768, 2048), generic widths (1000 and the 7B shape 4096), one row block (M < 256) and the
+    # 64-block clamp (M >= 16384)
+    for call, (M, C) in enumerate([(1000, 768), (2304, 2048), (100, 1000), (300, 4096), (20000, 256)]):
         x, dy, w, b = _case(M, C, seed=call)
         _, mean, rstd = ext.layernorm_fwd(x, w, b, 1e-5)
         dx_ref, dw_ref, db_ref = ext.layernorm_bwd(dy, x, w, mean, rstd, None)
-        dx = torch.empty_like(x)
+        dx = torch.full_like(x, float("nan"))
         dw = torch.full((C,), float("nan"), device="cuda")
         db = torch.full((C,), float("nan"), device="cuda")
         rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
@@ -55,8 +57,9 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
         assert rc == 0, lib.rwkv7m_noalloc_strerror(rc)
         torch.cuda.synchronize()
         assert torch.equal(dx, dx_ref)
-        assert torch.allclose(dw, dw_ref, rtol=1e-4, atol=1e-3)
-        assert torch.allclose(db, db_ref, rtol=1e-4, atol=1e-3)
+        tol = 1e-3 * max(1.0, (M / 1000.0) ** 0.5)   # sums over M rows, accumulated in a different order
+        assert torch.allclose(dw, dw_ref, rtol=1e-4, atol=tol)
+        assert torch.allclose(db, db_ref, rtol=1e-4, atol=tol)
 
 
 def test_rejects_sizes_beyond_the_static_scratch():
@@ -67,3 +70,23 @@ def test_rejects_sizes_beyond_the_static_scratch():
             dummy.data_ptr(), dummy.data_ptr(), 8, 16384, None)
     assert rc == 1
     assert b"size" in lib.rwkv7m_noalloc_strerror(rc)
+
+
+def test_rejects_bad_arguments_without_launching():
+    """Odd widths, null pointers and misaligned row pointers come back as error codes; nothing reaches the GPU."""
+    lib, fn = _lib()
+    x, dy, w, b = _case(8, 64, seed=4)
+    f = torch.zeros(64, device="cuda")
+    good = [dy.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr()]
+    assert fn(*good, 8, 63, None) == 1                                   # odd C
+    assert fn(*good, 0, 64, None) == 1                                   # no rows
+    for i in range(8):                                                   # each pointer null in turn
+        args = list(good)
+        args[i] = None
+        assert fn(*args, 8, 64, None) == 3
+    for i in (0, 1, 5):                                                  # dy, x, dx two bytes off a 16-byte boundary
+        args = list(good)
+        args[i] = good[i] + 2
+        assert fn(*args, 8, 64, None) == 3
+    assert b"misaligned" in lib.rwkv7m_noalloc_strerror(3)
+    torch.cuda.synchronize()
