@@ -49,17 +49,20 @@ std::vector<Tensor> wkv7_fwd(const Tensor& r, const Tensor& w, const Tensor& k, 
   Tensor sT = torch::empty_like(s0);
   Tensor sa, ckpt;
   p.y = y.data_ptr(); p.sT = sT.data_ptr<float>();
+  if (save) p.sa = reinterpret_cast<void*>(1);   // placeholder: "training forward" for the support query below
+  const bool use_chunk = chunked && rk::wkv7_chunk_supported(p);
   if (save) {
     auto f32 = r.options().dtype(at::kFloat);
-    sa = torch::empty(r.sizes(), f32);
+    // the chunked kernels keep U only as a bf16 tensor-core operand, so they save it in bf16
+    sa = torch::empty(r.sizes(), use_chunk ? r.options() : f32);
     const int64_t nck = (p.T + interval - 1) / interval;
     ckpt = torch::empty({nck, (int64_t)p.B * p.H, (int64_t)p.N, (int64_t)p.N}, f32);
-    p.sa = sa.data_ptr<float>(); p.ckpt = ckpt.data_ptr<float>();
+    p.sa = sa.data_ptr(); p.ckpt = ckpt.data_ptr<float>();
   } else {
     sa = torch::empty({0}, r.options().dtype(at::kFloat));
     ckpt = sa;
   }
-  if (chunked && rk::wkv7_chunk_supported(p)) {
+  if (use_chunk) {
     TORCH_CHECK(rk::wkv7_chunk_forward(p, stream()) == 0, "wkv7_chunk_forward: launch failed");
   } else {
     TORCH_CHECK(rk::wkv7_forward(p, stream()) == 0, "wkv7_forward: unsupported shape");
@@ -73,14 +76,17 @@ std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, 
   c10::cuda::CUDAGuard guard(r.device());
   rk::WkvArgs p = wkv_args(r, w, k, v, a, b, s0, interval);
   check_vec(dy, r, "dy");
-  TORCH_CHECK(sa.is_contiguous() && sa.scalar_type() == at::kFloat && sa.numel() == r.numel(), "bad sa");
+  const bool use_chunk = chunked && rk::wkv7_chunk_bwd_supported(p);
+  TORCH_CHECK(sa.is_contiguous() && sa.numel() == r.numel() &&
+                  sa.scalar_type() == (use_chunk ? at::kBFloat16 : at::kFloat),
+              "bad sa: the chunked backward takes the bf16 rows saved by the chunked forward, the scan backward fp32 rows");
   const int64_t nck = (p.T + interval - 1) / interval;
   TORCH_CHECK(ckpt.is_contiguous() && ckpt.scalar_type() == at::kFloat &&
                   ckpt.numel() == nck * p.B * p.H * p.N * p.N, "bad checkpoints");
   Tensor dr = torch::empty_like(r), dw = torch::empty_like(r), dk = torch::empty_like(r), dv = torch::empty_like(r),
          da = torch::empty_like(r), db = torch::empty_like(r);
   Tensor ds0 = torch::empty_like(s0);
-  p.sa = const_cast<float*>(sa.data_ptr<float>()); p.ckpt = const_cast<float*>(ckpt.data_ptr<float>());
+  p.sa = sa.data_ptr(); p.ckpt = const_cast<float*>(ckpt.data_ptr<float>());
   p.dy = dy.data_ptr();
   Tensor dsT_c;
   if (dsT.has_value() && dsT->defined()) {
@@ -90,7 +96,7 @@ std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, 
   }
   p.dr = dr.data_ptr(); p.dw = dw.data_ptr(); p.dk = dk.data_ptr(); p.dv = dv.data_ptr();
   p.da = da.data_ptr(); p.db = db.data_ptr(); p.ds0 = ds0.data_ptr<float>();
-  if (chunked && rk::wkv7_chunk_bwd_supported(p)) {
+  if (use_chunk) {
     TORCH_CHECK(rk::wkv7_chunk_backward(p, stream()) == 0, "wkv7_chunk_backward: launch failed");
   } else {
     TORCH_CHECK(rk::wkv7_backward(p, stream()) == 0, "wkv7_backward: unsupported shape");

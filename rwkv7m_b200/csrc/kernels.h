@@ -17,7 +17,8 @@ struct WkvArgs {
   const float* s0;                      // [B,H,N,N]
   void* y;                              // [B,T,H,N]
   float* sT;                            // [B,H,N,N]
-  float* sa;                            // [B,T,H,N] fp32, nullptr = inference forward
+  void* sa;                             // [B,T,H,N]: fp32 for the scan kernels, bf16 for the chunked kernels (which only
+                                        // ever use it as a bf16 tensor-core operand); nullptr = inference forward
   float* ckpt;                          // [ceil(T/interval), B*H, N, N]
   // backward only
   const void* dy;
@@ -31,7 +32,7 @@ int wkv7_backward(const WkvArgs& p, cudaStream_t st);
 bool wkv7_chunk_supported(const WkvArgs& p);
 int wkv7_chunk_forward(const WkvArgs& p, cudaStream_t st);
 int wkv7_chunk_error(bool reset);   // non-zero after a bounded wait ran out inside the chunked forward kernel
-// Chunked tensor-core backward: consumes sa (= U) and the 16-step state checkpoints written by either forward.
+// Chunked tensor-core backward: consumes the bf16 sa (= U) rows and the per-chunk states written by the chunked forward.
 bool wkv7_chunk_bwd_supported(const WkvArgs& p);
 int wkv7_chunk_backward(const WkvArgs& p, cudaStream_t st);
 int wkv7_chunk_bwd_error(bool reset);

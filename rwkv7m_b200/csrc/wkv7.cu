@@ -429,7 +429,7 @@ static int launch_fwd_n(const WkvArgs& p, cudaStream_t st) {
   if (p.sa != nullptr) {
     auto kern = wkv7_fwd_kernel<T, N, true>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, 4 * N / RPT, smem, st>>>(src, p.s0, (T*)p.y, p.sT, p.sa, p.ckpt, p.T, p.H);
+    kern<<<grid, 4 * N / RPT, smem, st>>>(src, p.s0, (T*)p.y, p.sT, (float*)p.sa, p.ckpt, p.T, p.H);
   } else {
     auto kern = wkv7_fwd_kernel<T, N, false>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -447,7 +447,7 @@ static int launch_bwd_n(const WkvArgs& p, cudaStream_t st) {
   auto kern = wkv7_bwd_kernel<T, N>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(p.B * p.H);
-  kern<<<grid, 8 * N / RPT, smem, st>>>(src, p.sa, p.ckpt, p.s0, p.dsT, (T*)p.dr, (T*)p.dw, (T*)p.dk, (T*)p.dv, (T*)p.da,
+  kern<<<grid, 8 * N / RPT, smem, st>>>(src, (const float*)p.sa, p.ckpt, p.s0, p.dsT, (T*)p.dr, (T*)p.dw, (T*)p.dk, (T*)p.dv, (T*)p.da,
                                  (T*)p.db, p.ds0, p.T, p.H);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

@@ -6,18 +6,18 @@
 // the recurrence  S_t = S_{t-1} diag(d_t) + (S_{t-1} a_t) b_t^T + v_t k_t^T,  y_t = S_t r_t  becomes, per chunk,
 //   A_ab = tril<(A~ B~^T)   A_ak = tril<(A~ K~^T)   A_rb = tril<=(R~ B~^T)   A_rk = tril<=(R~ K~^T)      (one MMA)
 //   Z    = A~ S0^T + A_ak V                                                                            (MMA)
-//   U    = (I - A_ab)^-1 Z          forward substitution in fp32 on the CUDA cores; U_t = S_{t-1} a_t
+//   U    = (I - A_ab)^-1 Z          the inverse is formed blockwise in fp32 (CUDA cores, overlapped with the Z
+//                                   product) and applied as one more MMA; U_t = S_{t-1} a_t
 //   Y    = R~ S0^T + A_rk V + A_rb U                                                                   (MMA)
 //   S1^T = diag(P_L) S0^T + B^^T U + K^^T V                                                            (MMA)
 // One CTA of 8 warps per (batch, head) walks the chunks in order; two CTAs share an SM.  Every product is a
 // tcgen05.mma with M = 128 (two 64-row operands stacked, or 64 useful rows plus 64 ignored ones), bf16
 // operands written into shared memory in the 128-byte-swizzled canonical layout, fp32 accumulators in tensor
 // memory.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
-// S^T); its bf16 image is the B operand of the next chunk.  The substitution runs on two threads per value
-// column (rows split by parity, one shuffle per step).  Decay is bounded below by exp(-exp(-0.5)) = 0.545
+// S^T); its bf16 image is the B operand of the next chunk.  Decay is bounded below by exp(-exp(-0.5)) = 0.545
 // per step, so every scale factor stays inside the fp32 / bf16 exponent range over 64 steps.
 //
-// In training mode the kernel also writes U (the `sa` vectors) and the state after every chunk, which is what
+// In training mode the kernel also writes U (the `sa` vectors, bf16) and the state after every chunk, which is what
 // the chunked backward kernel consumes.  Reference semantics: src/rwkv7m/model/rwkv_core.py:54-86,
 // src/rwkv7m/kernels/wkv_pallas_gpu.py:66-164.
 #include "common.cuh"
@@ -37,18 +37,21 @@ constexpr int kFStride = 68; // row stride (floats) of the fp32 scratch matrices
 
 // shared memory map (byte offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffAR = 0;                    // [128][64] bf16: rows 0-63 A~, 64-127 R~
-constexpr uint32_t kOffBK = kOffAR + 16384;       // [128][64] bf16: B~ | K~; later A_ak | A_rk; later Z fp32 [64][68]
-constexpr uint32_t kOffBKe = kOffBK + 18432;      // [128][64] bf16: rows 0-63 B^, 64-127 K^
-constexpr uint32_t kOffUV = kOffBKe + 16384;      // [128][64] bf16: rows 0-63 U, 64-127 V
+constexpr uint32_t kOffBK = kOffAR + 16384;       // [128][64] bf16: B~ | K~; later A_ak | A_rk; later Z (rows 0-63)
+constexpr uint32_t kOffBKe = kOffBK + 16384;      // [128][64] bf16: rows 0-63 B^, 64-127 K^
+constexpr uint32_t kOffUV = kOffBKe + 16384;      // [128][64] bf16: rows 0-63 (I - A_ab)^-1, then U; rows 64-127 V
 constexpr uint32_t kOffX2 = kOffUV + 16384;       // [64][64] bf16: A_rb (rows 64-127 of an operand that starts 8 KB earlier)
 constexpr uint32_t kOffS = kOffX2 + 8192;         // [64][64] bf16: S^T
-constexpr uint32_t kOffF = kOffS + 8192;          // fp32 [64][68]: A_ab^T with the row index split by parity
-constexpr uint32_t kOffPL = kOffF + L * kFStride * 4;   // fp32 [64]: P_L
-constexpr uint32_t kOffBar = kOffPL + NH * 4;     // 3 mbarriers, tmem slot, failure flag
+constexpr uint32_t kOffF = kOffS + 8192;          // fp32 [64][68]: A_ab, overwritten by its inverse
+constexpr uint32_t kOffW = kOffF + L * kFStride * 4;    // fp32 scratch of the blocked inverse
+constexpr uint32_t kOffPL = kOffW + kInvWorkFloats * 4; // fp32 [64]: P_L
+constexpr uint32_t kOffBar = kOffPL + NH * 4;     // 4 mbarriers, tmem slot, failure flag
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;    // + alignment slack
 
+static_assert(kFStride == kInvStride, "the inverse routine reads the A_ab scratch with its own row stride");
+
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColD1 = 0;    // 128 columns: A matrices; later the state products (first 64)
+constexpr uint32_t kColD1 = 0;    // 128 columns: A matrices; then U (first 64, lanes 0-63); then the state products
 constexpr uint32_t kColD2 = 128;  // 64 columns: Z (lanes 0-63) and Y (lanes 64-127)
 
 __device__ int g_wkv_chunk_error = 0;
@@ -71,7 +74,8 @@ struct ChunkPtrs {
   const __nv_bfloat16 *r, *w, *k, *v, *a, *b;
   __nv_bfloat16* y;
   const float* s0;
-  float *sT, *sa, *ckpt;
+  float *sT, *ckpt;
+  __nv_bfloat16* sa;
 };
 
 template <bool SAVE>
@@ -81,10 +85,10 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(sm);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 32);
-  volatile int* failed = reinterpret_cast<volatile int*>(sm + kOffBar + 40);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 48);
+  volatile int* failed = reinterpret_cast<volatile int*>(sm + kOffBar + 56);
   float* F = reinterpret_cast<float*>(sm + kOffF);
-  float* Zs = reinterpret_cast<float*>(sm + kOffBK);
+  float* Wk = reinterpret_cast<float*>(sm + kOffW);
   float* PL = reinterpret_cast<float*>(sm + kOffPL);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, bi = bh / H, hi = bh - bi * H;
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
     *failed = 0;
     mbar_fence_init();
   }
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
         for (int j = 0; j < 8; ++j) {
           e1[j] = __expf(lp[i][j]);                 // P_t
           e0[j] = __expf(lp[i][j] - ld[i][j]);      // P_{t-1}
-          inv[j] = __frcp_rn(e1[j]);
+          inv[j] = __expf(-lp[i][j]);
         }
         unpack8(ra[i], x);
 #pragma unroll
@@ -272,11 +276,13 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
       tmem_ld_wait();
       const int s0 = q * 32;
       if (lower) {
-        if (ch == 0) {  // A_ab, strictly lower, fp32, stored transposed with the row index split by parity:
-                        // F[s][(t & 1) * 32 + (t >> 1)] = A_ab[t][s]
-          float* dst = F + s0 * kFStride + (trow & 1) * 32 + (trow >> 1);
+        if (ch == 0) {  // A_ab, strictly lower, fp32: F[t][s], the input of the blocked inverse
+          float* dst = F + trow * kFStride + s0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) dst[j * kFStride] = s0 + j < trow ? __uint_as_float(v[j]) : 0.f;
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(
+                s0 + j < trow ? __uint_as_float(v[j]) : 0.f, s0 + j + 1 < trow ? __uint_as_float(v[j + 1]) : 0.f,
+                s0 + j + 2 < trow ? __uint_as_float(v[j + 2]) : 0.f, s0 + j + 3 < trow ? __uint_as_float(v[j + 3]) : 0.f);
         } else {        // A_ak, strictly lower
           store_masked_bf16(sm + kOffBK, trow, q * 4, v, s0, [&](int s) { return s < trow; });
         }
@@ -302,55 +308,52 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
         umma_bf16(tmem + kColD2, desc_k(sbase + kOffBK + k * 32), desc_mn(sbase + kOffUV + 8192 + k * 2048, 8192), idesc, 1);
       umma_commit(&bars[1]);
     }
+    // the inverse of I - A_ab on the CUDA cores while the tensor cores form Z; it lands in the U slot as a bf16 operand
+    unit_lower_inverse_64(F, Wk, sm + kOffUV, tid);
+    PROF_MARK(11);
     if (!mbar_wait(&bars[1], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(3);
-    if (lower) {  // Z rows -> shared memory, 32 columns per thread
+    if (lower) {  // Z rows -> bf16 operand tile over the dead A_ak slot, 32 columns per thread
       uint32_t v[32];
       tmem_ld_32x32(tmem + lane_base + kColD2 + ch * 32, v);
       tmem_ld_wait();
-      float* dst = Zs + trow * kFStride + ch * 32;
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      store_masked_bf16(sm + kOffBK, trow, ch * 4, v, 0, [](int) { return true; });
     }
     tc_fence_before();
+    fence_proxy_async_smem();
     __syncthreads();
+    if (*failed) { ok = false; break; }
     PROF_MARK(4);
-    if (tid < 128) {
-      // Forward substitution on two threads per value column: thread (vcol, h) owns the rows of parity h.  Once u_s
-      // is final its owner broadcasts it with one shuffle and both threads push it into their later rows, so all
-      // updates of a step are independent.  Rows at or above the diagonal meet a stored zero.
-      const int vcol = tid >> 1, h = tid & 1;
-      float u[32];
+    // ---- MMA U: U = (I - A_ab)^-1 Z (lanes 0-63; lanes 64-127 multiply the V rows that follow the inverse: ignored) ------
+    if (tid == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 64, 0, 1);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) u[i] = Zs[(2 * i + h) * kFStride + vcol];
-      const float* Fh = F + 32 * h;
+      for (int k = 0; k < 4; ++k)
+        umma_bf16(tmem + kColD1, desc_k(sbase + kOffUV + k * 32), desc_mn(sbase + kOffBK + k * 2048, 8192), idesc, k > 0);
+      umma_commit(&bars[3]);
+    }
+    if (!mbar_wait(&bars[3], par, failed)) { *failed = 1; }
+    tc_fence_after();
+    if (lower) {  // U rows -> bf16 operand tile (over the inverse, which the finished MMA no longer reads) and, in
+                  // training, the same bf16 rows for the backward pass
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + kColD1 + ch * 32, v);
+      tmem_ld_wait();
+      const bool keep = SAVE && t0 + trow < T;
+      __nv_bfloat16* dst = g.sa + base + (size_t)(t0 + trow) * stride_t + ch * 32;
 #pragma unroll
-      for (int s_ = 0; s_ < L - 1; ++s_) {
-        const float us = __shfl_sync(0xffffffffu, u[s_ >> 1], (lane & ~1) | (s_ & 1));
-        constexpr int kDummy = 0;
-        (void)kDummy;
+      for (int p = 0; p < 4; ++p) {
+        float x[8];
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          if (4 * i4 + 3 >= ((s_ + 1) >> 1)) {   // this group of four rows holds a row index 2i+h that can exceed s
-            const float4 A = *reinterpret_cast<const float4*>(Fh + s_ * kFStride + 4 * i4);
-            if (4 * i4 + 0 >= (s_ >> 1)) u[4 * i4 + 0] = fmaf(A.x, us, u[4 * i4 + 0]);
-            if (4 * i4 + 1 >= (s_ >> 1)) u[4 * i4 + 1] = fmaf(A.y, us, u[4 * i4 + 1]);
-            if (4 * i4 + 2 >= (s_ >> 1)) u[4 * i4 + 2] = fmaf(A.z, us, u[4 * i4 + 2]);
-            if (4 * i4 + 3 >= (s_ >> 1)) u[4 * i4 + 3] = fmaf(A.w, us, u[4 * i4 + 3]);
-          }
-        }
-      }
-      PROF_MARK(11);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int t = 2 * i + h;
-        *reinterpret_cast<__nv_bfloat16*>(sm + kOffUV + sw128(t, vcol >> 3) + (vcol & 7) * 2) = f2bf(u[i]);
-        if (SAVE && t0 + t < T) g.sa[base + (size_t)(t0 + t) * stride_t + vcol] = u[i];
+        for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[8 * p + j]);
+        const uint4 packed = pack8(x);
+        *reinterpret_cast<uint4*>(sm + kOffUV + sw128(trow, ch * 4 + p)) = packed;
+        if (keep) *reinterpret_cast<uint4*>(dst + 8 * p) = packed;
       }
     }
+    tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
@@ -432,7 +435,7 @@ int wkv7_chunk_forward(const WkvArgs& p, cudaStream_t st) {
   ChunkPtrs g;
   g.r = (const __nv_bfloat16*)p.r; g.w = (const __nv_bfloat16*)p.w; g.k = (const __nv_bfloat16*)p.k;
   g.v = (const __nv_bfloat16*)p.v; g.a = (const __nv_bfloat16*)p.a; g.b = (const __nv_bfloat16*)p.b;
-  g.y = (__nv_bfloat16*)p.y; g.s0 = p.s0; g.sT = p.sT; g.sa = p.sa; g.ckpt = p.ckpt;
+  g.y = (__nv_bfloat16*)p.y; g.s0 = p.s0; g.sT = p.sT; g.sa = (__nv_bfloat16*)p.sa; g.ckpt = p.ckpt;
   const int BH = p.B * p.H;
   if (p.sa != nullptr) {
     auto kern = wkv7_chunk_fwd_kernel<true>;

@@ -3,7 +3,8 @@
 // Per chunk of 64 steps (notation of wkv7_chunk.cu; S0 / S1 = state before / after the chunk, U saved by the
 // forward pass, G = diag(P_L) dS1^T):
 //   dUdir = A_rb^T dY + B~ G            dVp = A_rk^T dY + K~ G                         (one accumulator, M = 128)
-//   dZ    = (I - A_ab)^-T dUdir         backward substitution in fp32 on the CUDA cores
+//   dZ    = (I - A_ab)^-T dUdir         the inverse is formed blockwise in fp32 on the CUDA cores (while the tensor
+//                                       cores form dUdir) and applied, transposed, by one more MMA
 //   dV    = dVp + A_ak^T dZ
 //   dA_ab = tril<(dZ U^T)  dA_ak = tril<(dZ V^T)  dA_rb = tril<=(dY U^T)  dA_rk = tril<=(dY V^T)   (one MMA)
 //   dA~   = dZ S0 + dA_ab B~ + dA_ak K~      dR~ = dY S0 + dA_rb B~ + dA_rk K~
@@ -14,7 +15,10 @@
 //   dw_t = logd_t * sum_{t' >= t} dlogP_t'
 // One CTA of 8 warps per (batch, head) walks the chunks from last to first; the fp32 master copy of dS lives in
 // registers (32 values per thread).  Every product is a tcgen05.mma with M = 128 over 128-byte-swizzled bf16 tiles in
-// shared memory, accumulators in tensor memory.  All waits are bounded.
+// shared memory, accumulators in tensor memory.  The raw tiles of the next chunk (the previous one in time) are
+// fetched with asynchronous copies while the second half of the current chunk runs: dY, V and U land directly in
+// their operand slots, which the remaining products no longer read, the five tiles that are rescaled go to a
+// staging area.  All waits are bounded.
 #include "common.cuh"
 #include "kernels.h"
 #include "wkv7_chunk.cuh"
@@ -37,13 +41,16 @@ constexpr uint32_t kOffZY = kOffUV + 16384;          // [128][64] bf16: dZ | dY
 constexpr uint32_t kOffS0 = kOffZY + 16384;          // [64][64] bf16: S0^T  (row = key channel)
 constexpr uint32_t kOffG = kOffS0 + 8192;            // [64][64] bf16: G = diag(P_L) dS1^T
 constexpr uint32_t kOffX = kOffG + 8192;             // [128][128] bf16 as two [128][64] column blocks: A then dA matrices
-constexpr uint32_t kOffF = kOffX + 32768;            // fp32 [64][68]: A_ab (columns split by parity); later (a~ dA~)
-constexpr uint32_t kOffZ = kOffF + L * kFStride * 4; // fp32 [64][68]: dUdir; later the dlogP terms
+                                                     // (rows 0-63 of block 0 hold (I - A_ab)^-1 instead of A_ab)
+constexpr uint32_t kOffF = kOffX + 32768;            // fp32 [64][68]: A_ab, then its inverse; later (a~ dA~)
+constexpr uint32_t kOffZ = kOffF + L * kFStride * 4; // fp32 [64][68]: the dlogP terms
 constexpr uint32_t kOffLP = kOffZ + L * kFStride * 4;// fp32 [64][68]: inclusive cumulative log decay
 constexpr uint32_t kOffPL = kOffLP + L * kFStride * 4; // fp32 [64]: P_L
 constexpr uint32_t kOffLT = kOffPL + NH * 4;         // fp32 [2][64]: halves of <dS1, S1>
 constexpr uint32_t kOffBS = kOffLT + 2 * NH * 4;     // fp32 [4][64]: block sums of the decay-gradient scan
-constexpr uint32_t kOffBar = kOffBS + 4 * NH * 4;
+constexpr uint32_t kOffW = kOffBS + 4 * NH * 4;      // fp32 scratch of the blocked inverse
+constexpr uint32_t kOffStage = (kOffW + kInvWorkFloats * 4 + 1023u) & ~1023u;   // raw a | r | b | k | w tiles of the next chunk
+constexpr uint32_t kOffBar = kOffStage + 5 * 8192;
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;
 
 constexpr uint32_t kTmemCols = 512;
@@ -51,11 +58,13 @@ constexpr uint32_t kC1 = 0;     // 128: A matrices, later dA matrices
 constexpr uint32_t kC2 = 128;   // 64: dUdir (lanes 0-63) | dV (lanes 64-127)
 constexpr uint32_t kC3 = 192;   // 64: dA~ | dR~
 constexpr uint32_t kC4 = 256;   // 64: DB | DK
-constexpr uint32_t kC6 = 320;   // 64: R~^T dY + A~^T dZ (lanes 0-63)
+constexpr uint32_t kC6 = 320;   // 64: dZ (lanes 0-63), then R~^T dY + A~^T dZ (lanes 0-63)
+
+static_assert(kFStride == kInvStride, "the inverse routine reads the A_ab scratch with its own row stride");
 
 struct BwdPtrs {
-  const __nv_bfloat16 *r, *w, *k, *v, *a, *b, *dy;
-  const float *sa, *s0, *ckpt, *dsT;
+  const __nv_bfloat16 *r, *w, *k, *v, *a, *b, *dy, *sa;
+  const float *s0, *ckpt, *dsT;
   __nv_bfloat16 *dr, *dw, *dk, *dv, *da, *db;
   float* ds0;
 };
@@ -86,9 +95,10 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(sm);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 32);
-  volatile int* failed = reinterpret_cast<volatile int*>(sm + kOffBar + 40);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 48);
+  volatile int* failed = reinterpret_cast<volatile int*>(sm + kOffBar + 56);
   float* F = reinterpret_cast<float*>(sm + kOffF);
+  float* Wk = reinterpret_cast<float*>(sm + kOffW);
   float* Zs = reinterpret_cast<float*>(sm + kOffZ);
   float* LP = reinterpret_cast<float*>(sm + kOffLP);
   float* PL = reinterpret_cast<float*>(sm + kOffPL);
@@ -101,7 +111,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
     *failed = 0;
     mbar_fence_init();
   }
@@ -129,57 +139,51 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
 #endif
+  // Asynchronous copies of one chunk's raw tiles (8 lanes per 128-byte row, swizzled like the operand tiles): dY, V
+  // and the saved U rows go straight into their operand slots, a / r / b / k / w into the staging area.
+  auto fetch_chunk = [&](int cc) {
+    const int tc = cc * L;
+    const int p8 = tid & 7;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = (tid >> 3) + 32 * i;
+      const uint32_t off = sw128(row, p8);
+      const size_t go = base + (size_t)(tc + row) * stride_t + p8 * 8;
+      if (tc + row < T) {
+        cp_async16(sm + kOffStage + off, g.a + go);
+        cp_async16(sm + kOffStage + 8192 + off, g.r + go);
+        cp_async16(sm + kOffStage + 16384 + off, g.b + go);
+        cp_async16(sm + kOffStage + 24576 + off, g.k + go);
+        cp_async16(sm + kOffStage + 32768 + off, g.w + go);
+        cp_async16(sm + kOffUV + off, g.sa + go);
+        cp_async16(sm + kOffUV + 8192 + off, g.v + go);
+        cp_async16(sm + kOffZY + 8192 + off, g.dy + go);
+      } else {
+        *reinterpret_cast<uint4*>(sm + kOffStage + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffStage + 8192 + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffStage + 16384 + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffStage + 24576 + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffStage + 32768 + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffUV + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = zero;
+        *reinterpret_cast<uint4*>(sm + kOffZY + 8192 + off) = zero;
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (tid < 128) {   // the state before that chunk (fp32, converted at the top of its iteration): pull it into L2
+      const float* s_in = cc == 0 ? g.s0 + (size_t)bh * NH * NH : g.ckpt + ((size_t)(cc - 1) * BH + bh) * NH * NH;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(s_in + tid * 32));
+    }
+  };
+  fetch_chunk(nchunks - 1);
   uint32_t par = 0;
   for (int c = nchunks - 1; c >= 0; --c, par ^= 1u) {
     const int t0 = c * L;
     const float* S0g = c == 0 ? g.s0 + (size_t)bh * NH * NH : g.ckpt + ((size_t)(c - 1) * BH + bh) * NH * NH;
     const float* S1g = g.ckpt + ((size_t)c * BH + bh) * NH * NH;
-    // ---- raw tiles: coalesced asynchronous copies straight into tile slots (8 lanes per 128-byte row); w and the
-    //      fp32 U rows are parked in the score-matrix region, which is free until the first readout ----------------
+    // ---- the raw tiles of this chunk were requested one chunk ago (before the loop for the first one) -------------------
     {
-      const int p8 = tid & 7;
-      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int row = (tid >> 3) + 32 * i;
-        const uint32_t off = sw128(row, p8);
-        const size_t go = base + (size_t)(t0 + row) * stride_t + p8 * 8;
-        uint8_t* urow = sm + kOffX + 8192 + row * 256 + p8 * 32;   // fp32 U, plain row-major
-        if (t0 + row < T) {
-          cp_async16(sm + kOffAR + off, g.a + go);
-          cp_async16(sm + kOffAR + 8192 + off, g.r + go);
-          cp_async16(sm + kOffBK + off, g.b + go);
-          cp_async16(sm + kOffBK + 8192 + off, g.k + go);
-          cp_async16(sm + kOffX + off, g.w + go);
-          cp_async16(sm + kOffUV + 8192 + off, g.v + go);
-          cp_async16(sm + kOffZY + 8192 + off, g.dy + go);
-          cp_async16(urow, g.sa + go);
-          cp_async16(urow + 16, g.sa + go + 4);
-        } else {
-          *reinterpret_cast<uint4*>(sm + kOffAR + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffAR + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffBK + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffBK + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffX + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffZY + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(urow) = zero;
-          *reinterpret_cast<uint4*>(urow + 16) = zero;
-        }
-      }
-      if (c > 0) {  // pull the previous chunk's rows (processed next) into L2, one 128-byte line per request
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int e = tid + 256 * j;
-          const int which = e >> 6, row = e & 63;
-          if (e < 448) {
-            const __nv_bfloat16* src = which == 0 ? g.a : which == 1 ? g.r : which == 2 ? g.b : which == 3 ? g.k
-                                       : which == 4 ? g.w : which == 5 ? g.v : g.dy;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(src + base + (size_t)(t0 - L + row) * stride_t));
-          }
-        }
-        if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(g.sa + base + (size_t)(t0 - L + (tid >> 1)) * stride_t + (tid & 1) * 32));
-      }
       // S0^T tile: thread (k, vq) converts S0[16 vq .. 16 vq + 15][k]
       {
         const int k = tid & 63, vq = tid >> 6;
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         for (int j = 0; j < 32; ++j) lt = fmaf(ds[j], S1g[(size_t)(32 * ch + j) * NH + trow], lt);
         LT[ch * NH + trow] = lt;
       }
-      cp_async_wait_all();
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncthreads();
     }
     PROF_MARK(12);
@@ -206,19 +210,15 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
     {
       const int piece = warp;
       uint4 rw[2], ra[2], rr[2], rb[2], rk[2];
-      float4 u0[2], u1[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int row = lane + 32 * i;
         const uint32_t off = sw128(row, piece);
-        rw[i] = *reinterpret_cast<const uint4*>(sm + kOffX + off);
-        ra[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + off);
-        rr[i] = *reinterpret_cast<const uint4*>(sm + kOffAR + 8192 + off);
-        rb[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + off);
-        rk[i] = *reinterpret_cast<const uint4*>(sm + kOffBK + 8192 + off);
-        const float* urow = reinterpret_cast<const float*>(sm + kOffX + 8192 + row * 256 + piece * 32);
-        u0[i] = *reinterpret_cast<const float4*>(urow);
-        u1[i] = *reinterpret_cast<const float4*>(urow + 4);
+        ra[i] = *reinterpret_cast<const uint4*>(sm + kOffStage + off);
+        rr[i] = *reinterpret_cast<const uint4*>(sm + kOffStage + 8192 + off);
+        rb[i] = *reinterpret_cast<const uint4*>(sm + kOffStage + 16384 + off);
+        rk[i] = *reinterpret_cast<const uint4*>(sm + kOffStage + 24576 + off);
+        rw[i] = *reinterpret_cast<const uint4*>(sm + kOffStage + 32768 + off);
       }
       float ld[2][8], lp[2][8];
 #pragma unroll
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         for (int j = 0; j < 8; ++j) {
           e1[j] = __expf(lp[i][j]);
           e0[j] = __expf(lp[i][j] - ld[i][j]);
-          inv[j] = __frcp_rn(e1[j]);
+          inv[j] = __expf(-lp[i][j]);
         }
         float* lpd = LP + row * kFStride + piece * 8;
         *reinterpret_cast<float4*>(lpd) = make_float4(lp[i][0], lp[i][1], lp[i][2], lp[i][3]);
@@ -273,9 +273,6 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * inv[j];
         *reinterpret_cast<uint4*>(sm + kOffBK + 8192 + off) = pack8(y);
-        y[0] = u0[i].x; y[1] = u0[i].y; y[2] = u0[i].z; y[3] = u0[i].w;
-        y[4] = u1[i].x; y[5] = u1[i].y; y[6] = u1[i].z; y[7] = u1[i].w;
-        *reinterpret_cast<uint4*>(sm + kOffUV + off) = pack8(y);
       }
     }
     fence_proxy_async_smem();
@@ -312,20 +309,16 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
       const int s0 = q * 32;
       uint8_t* blk = sm + kOffX + ch * 16384;
       if (lower) {
-        if (ch == 0) {  // A_ab also in fp32 for the substitution, columns split by parity: F[t][(s & 1) * 32 + (s >> 1)]
-          float* de = F + trow * kFStride + (s0 >> 1);
-          float* dd = de + 32;
+        if (ch == 0) {  // A_ab in fp32, F[t][s]: the input of the blocked inverse (its bf16 slot receives the inverse)
+          float* dst = F + trow * kFStride + s0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            *reinterpret_cast<float4*>(de + (j >> 1)) =
-                make_float4(s0 + j < trow ? __uint_as_float(v[j]) : 0.f, s0 + j + 2 < trow ? __uint_as_float(v[j + 2]) : 0.f,
-                            s0 + j + 4 < trow ? __uint_as_float(v[j + 4]) : 0.f, s0 + j + 6 < trow ? __uint_as_float(v[j + 6]) : 0.f);
-            *reinterpret_cast<float4*>(dd + (j >> 1)) =
-                make_float4(s0 + j + 1 < trow ? __uint_as_float(v[j + 1]) : 0.f, s0 + j + 3 < trow ? __uint_as_float(v[j + 3]) : 0.f,
-                            s0 + j + 5 < trow ? __uint_as_float(v[j + 5]) : 0.f, s0 + j + 7 < trow ? __uint_as_float(v[j + 7]) : 0.f);
-          }
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(
+                s0 + j < trow ? __uint_as_float(v[j]) : 0.f, s0 + j + 1 < trow ? __uint_as_float(v[j + 1]) : 0.f,
+                s0 + j + 2 < trow ? __uint_as_float(v[j + 2]) : 0.f, s0 + j + 3 < trow ? __uint_as_float(v[j + 3]) : 0.f);
+        } else {
+          store_masked_bf16(blk, trow, q * 4, v, s0, [&](int s) { return s < trow; });   // A_ak
         }
-        store_masked_bf16(blk, trow, q * 4, v, s0, [&](int s) { return s < trow; });
       } else {
         store_masked_bf16(blk, 64 + trow, q * 4, v, s0, [&](int s) { return s <= trow; });
       }
@@ -349,48 +342,40 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         umma_bf16(tmem + kC2, desc_k(sbase + kOffBK + k * 32), desc_mn(sbase + kOffG + k * 2048, 8192), id_km, 1);
       umma_commit(&bars[1]);
     }
+    // the inverse of I - A_ab on the CUDA cores while the tensor cores form dUdir; it lands in the A_ab operand slot
+    unit_lower_inverse_64(F, Wk, sm + kOffX, tid);
     if (!mbar_wait(&bars[1], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(3);
-    if (lower) {
+    if (lower) {   // dUdir rows -> bf16 operand tile in the dZ slot
       uint32_t v[32];
       tmem_ld_32x32(tmem + lane_base + kC2 + ch * 32, v);
       tmem_ld_wait();
-      float* dst = Zs + trow * kFStride + ch * 32;
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      store_masked_bf16(sm + kOffZY, trow, ch * 4, v, 0, [](int) { return true; });
     }
     tc_fence_before();
+    fence_proxy_async_smem();
     __syncthreads();
+    if (*failed) { ok = false; break; }
     PROF_MARK(4);
-    if (tid < 128) {
-      // Backward substitution on two threads per value column: thread (vcol, h) owns the rows of parity h.  Once dZ_t
-      // is final its owner broadcasts it with one shuffle and both threads push it into their earlier rows.
-      const int vcol = tid >> 1, h = tid & 1;
-      float z[32];
+    // ---- MMA dZ: dZ = (I - A_ab)^-T dUdir (lanes 0-63; lanes 64-127 receive A_ak^T dUdir, ignored) ----------------------
+    if (tid == 0) {
+      tc_fence_after();
+      constexpr uint32_t id_mm = umma_idesc_bf16(128, 64, 1, 1);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) z[i] = Zs[(2 * i + h) * kFStride + vcol];
-      const float* Fh = F + 32 * h;
-#pragma unroll
-      for (int t = L - 1; t > 0; --t) {
-        const float zt = __shfl_sync(0xffffffffu, z[t >> 1], (lane & ~1) | (t & 1));
-#pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          if (4 * i4 <= ((t - 1) >> 1)) {   // rows 2i+h < t; an entry at or above the diagonal is a stored zero
-            const float4 A = *reinterpret_cast<const float4*>(Fh + t * kFStride + 4 * i4);
-            if (4 * i4 + 0 <= ((t - 1) >> 1)) z[4 * i4 + 0] = fmaf(A.x, zt, z[4 * i4 + 0]);
-            if (4 * i4 + 1 <= ((t - 1) >> 1)) z[4 * i4 + 1] = fmaf(A.y, zt, z[4 * i4 + 1]);
-            if (4 * i4 + 2 <= ((t - 1) >> 1)) z[4 * i4 + 2] = fmaf(A.z, zt, z[4 * i4 + 2]);
-            if (4 * i4 + 3 <= ((t - 1) >> 1)) z[4 * i4 + 3] = fmaf(A.w, zt, z[4 * i4 + 3]);
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        *reinterpret_cast<__nv_bfloat16*>(sm + kOffZY + sw128(2 * i + h, vcol >> 3) + (vcol & 7) * 2) = f2bf(z[i]);
+      for (int k = 0; k < 4; ++k)
+        umma_bf16(tmem + kC6, desc_mn(sbase + kOffX + k * 2048, 16384), desc_mn(sbase + kOffZY + k * 2048, 8192), id_mm, k > 0);
+      umma_commit(&bars[4]);
     }
+    if (!mbar_wait(&bars[4], par, failed)) { *failed = 1; }
+    tc_fence_after();
+    if (lower) {   // dZ rows -> bf16 operand tile, over dUdir (the finished MMA no longer reads it)
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + kC6 + ch * 32, v);
+      tmem_ld_wait();
+      store_masked_bf16(sm + kOffZY, trow, ch * 4, v, 0, [](int) { return true; });
+    }
+    tc_fence_before();
     fence_proxy_async_smem();
     __syncthreads();
     if (*failed) { ok = false; break; }
@@ -421,6 +406,9 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
     if (!mbar_wait(&bars[2], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(6);
+    // U, V and dY are dead from here on (the products still to come read the score tiles and A~ / R~ / B~ / K~ only)
+    // and the staging area was emptied by the rescale pass: request the previous chunk's tiles now
+    if (c > 0) fetch_chunk(c - 1);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {   // dA matrices, masked, into column block ch of X
       uint32_t v[32];
@@ -495,11 +483,20 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         unpack8(*reinterpret_cast<const uint4*>(arow + sw128(trow, ch * 4 + p)), av);
         unpack8(*reinterpret_cast<const uint4*>(brow + sw128(trow, ch * 4 + p)), bv);
         const float* lp = LP + trow * kFStride + k0;
+        const float4 c0 = *reinterpret_cast<const float4*>(lp), c1 = *reinterpret_cast<const float4*>(lp + 4);
+        const float cur[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float prv[8];   // cumulative log decay of the row before (lower lanes: da needs P_{t-1}); row 0 has none
+        if (lower && trow > 0) {
+          const float4 q0 = *reinterpret_cast<const float4*>(lp - kFStride), q1 = *reinterpret_cast<const float4*>(lp - kFStride + 4);
+          prv[0] = q0.x; prv[1] = q0.y; prv[2] = q0.z; prv[3] = q0.w; prv[4] = q1.x; prv[5] = q1.y; prv[6] = q1.z; prv[7] = q1.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) prv[j] = lower ? 0.f : cur[j];
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float x = lp[j];
-          const float s4 = __expf(-x);                                                           // 1 / P_t
-          const float s3 = lower ? (trow > 0 ? __expf(lp[j - kFStride]) : 1.f) : __expf(x);      // P_{t-1} or P_t
+          const float s4 = __expf(-cur[j]);     // 1 / P_t
+          const float s3 = __expf(prv[j]);      // P_{t-1} (da) or P_t (dr)
           o3[j] = d3[p * 8 + j] * s3;
           o4[j] = d4[p * 8 + j] * s4;
         }
@@ -579,7 +576,7 @@ int wkv7_chunk_backward(const WkvArgs& p, cudaStream_t st) {
   BwdPtrs g;
   g.r = (const __nv_bfloat16*)p.r; g.w = (const __nv_bfloat16*)p.w; g.k = (const __nv_bfloat16*)p.k;
   g.v = (const __nv_bfloat16*)p.v; g.a = (const __nv_bfloat16*)p.a; g.b = (const __nv_bfloat16*)p.b;
-  g.dy = (const __nv_bfloat16*)p.dy; g.sa = p.sa; g.s0 = p.s0; g.ckpt = p.ckpt; g.dsT = p.dsT;
+  g.dy = (const __nv_bfloat16*)p.dy; g.sa = (const __nv_bfloat16*)p.sa; g.s0 = p.s0; g.ckpt = p.ckpt; g.dsT = p.dsT;
   g.dr = (__nv_bfloat16*)p.dr; g.dw = (__nv_bfloat16*)p.dw; g.dk = (__nv_bfloat16*)p.dk;
   g.dv = (__nv_bfloat16*)p.dv; g.da = (__nv_bfloat16*)p.da; g.db = (__nv_bfloat16*)p.db; g.ds0 = p.ds0;
   const int BH = p.B * p.H;

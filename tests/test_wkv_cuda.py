@@ -116,7 +116,8 @@ def test_chunked_tensor_core_forward_matches_sequential_kernel(T, save):
         assert float((chk[0].float() - seq[0].float()).norm() / y_ref.norm()) < 8e-3
         assert float((chk[1] - sT_ref).norm() / sT_ref.norm()) < 5e-3
         if save:
-            assert float((chk[2] - seq[2]).norm() / seq[2].norm()) < 8e-3       # U
+            assert chk[2].dtype == torch.bfloat16                                # the chunked kernels keep U in bf16
+            assert float((chk[2].float() - seq[2]).norm() / seq[2].norm()) < 8e-3       # U
             assert chk[3].shape[0] == (T + 63) // 64
             for c in range(chk[3].shape[0]):
                 want = seq[3][min(4 * c + 3, seq[3].shape[0] - 1)]
@@ -170,3 +171,60 @@ def test_chunked_path_through_autograd_function():
     for name, a, s_, b in zip("r w k v a b".split(), got, seq, want):
         assert float((a - b).norm() / (b.norm() + 1e-9)) < 1.5e-2, name
         assert float((s_ - b).norm() / (b.norm() + 1e-9)) < 1.5e-2, name
+
+
+def test_chunked_kernels_at_the_strongest_decay():
+    """w = -0.5 on every channel and step: the per-chunk scale factors 1 / P_t reach 0.545^-64 = 7e16, the largest
+    value the rescaled operands can take.  Forward and all gradients against the fp32 recurrence."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    B, T, H = 1, 256, 2
+    vecs, s0 = _inputs(B, T, H, 64, torch.bfloat16, seed=77)
+    vecs[1] = torch.full_like(vecs[1], -0.5)
+    g = torch.Generator().manual_seed(2)
+    dy = (torch.randn(B, T, H, 64, generator=g) * 0.5).cuda().bfloat16()
+    dsT = (torch.randn(B, H, 64, 64, generator=g) * 0.1).cuda()
+    leaves = [t.float().clone().requires_grad_(True) for t in vecs] + [s0.clone().requires_grad_(True)]
+    y_ref, sT_ref = R.wkv7(*leaves)
+    ((y_ref * dy.float()).sum() + (sT_ref * dsT).sum()).backward()
+    y, sT, sa, ckpt = C.wkv7_fwd(*vecs, s0, True, 64, True)
+    got = C.wkv7_bwd(*vecs, s0, sa, ckpt, dy, dsT, 64, True)
+    torch.cuda.synchronize()
+    assert C.wkv7_chunk_error(True) == 0
+    assert float((y.float() - y_ref).norm() / y_ref.norm()) < 8e-3
+    assert float((sT - sT_ref).norm() / sT_ref.norm()) < 5e-3
+    for name, a, leaf in zip("r w k v a b s0".split(), got, leaves):
+        assert torch.isfinite(a).all(), name
+        rel = float((a.float() - leaf.grad).norm() / (leaf.grad.norm() + 1e-9))
+        assert rel < 1.5e-2, (name, rel)
+
+
+def test_chunked_kernels_at_the_training_shape():
+    """(T, B, H) = (4096, 8, 32): 256 sequences, more than the 148 SMs hold at once, 64 chunks each.  Forward against
+    the fp32 recurrence; backward against the fp32 scan kernels (a separate implementation that the small cases tie
+    to autograd), since autograd through 4096 steps would keep every intermediate state."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    B, T, H = 8, 4096, 32
+    vecs, s0 = _inputs(B, T, H, 64, torch.bfloat16, seed=4096)
+    g = torch.Generator().manual_seed(3)
+    dy = (torch.randn(B, T, H, 64, generator=g) * 0.5).cuda().bfloat16()
+    dsT = (torch.randn(B, H, 64, 64, generator=g) * 0.1).cuda()
+    with torch.no_grad():
+        y_ref, sT_ref = R.wkv7(*[t.float() for t in vecs], s0)
+    y, sT, sa, ckpt = C.wkv7_fwd(*vecs, s0, True, 64, True)
+    got = C.wkv7_bwd(*vecs, s0, sa, ckpt, dy, dsT, 64, True)
+    torch.cuda.synchronize()
+    assert C.wkv7_chunk_error(True) == 0
+    assert float((y.float() - y_ref).norm() / y_ref.norm()) < 8e-3
+    assert float((sT - sT_ref).norm() / sT_ref.norm()) < 8e-3
+    del y_ref
+    f32 = [t.float() for t in vecs]
+    _, _, sa32, ckpt32 = C.wkv7_fwd(*f32, s0, True, 16, False)
+    want = C.wkv7_bwd(*f32, s0, sa32, ckpt32, dy.float(), dsT, 16, False)
+    torch.cuda.synchronize()
+    for name, a, b in zip("r w k v a b s0".split(), got, want):
+        rel = float((a.float() - b.float()).norm() / (b.float().norm() + 1e-9))
+        assert rel < 1.5e-2, (name, rel)
