@@ -13,7 +13,8 @@
 // One CTA of 8 warps per (batch, head) walks the chunks in order; two CTAs share an SM.  Every product is a
 // tcgen05.mma with M = 128 (two 64-row operands stacked, or 64 useful rows plus 64 ignored ones), bf16
 // operands written into shared memory in the 128-byte-swizzled canonical layout, fp32 accumulators in tensor
-// memory.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
+// memory.  The raw tiles of the next chunk are requested with asynchronous copies as soon as the last product that
+// reads a slot has completed, so their latency hides behind the rest of the current chunk.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
 // S^T); its bf16 image is the B operand of the next chunk.  Decay is bounded below by exp(-exp(-0.5)) = 0.545
 // per step, so every scale factor stays inside the fp32 / bf16 exponent range over 64 steps.
 //
@@ -129,51 +130,36 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
 
   const int nchunks = (T + L - 1) / L;
   bool ok = true;
+  // Coalesced asynchronous copy of one raw [64][64] bf16 tile of chunk cc straight into an operand slot (8 lanes per
+  // 128-byte row, swizzled like the operand tiles; rows past the end of the sequence are zero-filled).  Each slot of
+  // the next chunk is requested as soon as the last product that reads the current contents has completed.
+  auto fetch_tile = [&](uint32_t slot, const __nv_bfloat16* src, int cc) {
+    const int p8 = tid & 7;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = (tid >> 3) + 32 * i;
+      const uint32_t off = sw128(row, p8);
+      if (cc * L + row < T) cp_async16(sm + slot + off, src + base + (size_t)(cc * L + row) * stride_t + p8 * 8);
+      else *reinterpret_cast<uint4*>(sm + slot + off) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch_tile(kOffAR, g.a, 0);
+  fetch_tile(kOffAR + 8192, g.r, 0);
+  fetch_tile(kOffBK, g.b, 0);
+  fetch_tile(kOffBK + 8192, g.k, 0);
+  fetch_tile(kOffBKe, g.w, 0);
+  fetch_tile(kOffUV + 8192, g.v, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
 #endif
   for (int c = 0; c < nchunks; ++c) {
+    const bool more = c + 1 < nchunks;
     const int t0 = c * L;
     const uint32_t par = (uint32_t)(c & 1);
-    // ---- raw tiles: coalesced asynchronous copies straight into the operand tile slots (8 lanes per 128-byte row) ----
-    {
-      const int p8 = tid & 7;
-      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int row = (tid >> 3) + 32 * i;
-        const uint32_t off = sw128(row, p8);
-        const size_t go = base + (size_t)(t0 + row) * stride_t + p8 * 8;
-        if (t0 + row < T) {
-          cp_async16(sm + kOffAR + off, g.a + go);
-          cp_async16(sm + kOffAR + 8192 + off, g.r + go);
-          cp_async16(sm + kOffBK + off, g.b + go);
-          cp_async16(sm + kOffBK + 8192 + off, g.k + go);
-          cp_async16(sm + kOffBKe + off, g.w + go);
-          cp_async16(sm + kOffUV + 8192 + off, g.v + go);
-        } else {
-          *reinterpret_cast<uint4*>(sm + kOffAR + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffAR + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffBK + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffBK + 8192 + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffBKe + off) = zero;
-          *reinterpret_cast<uint4*>(sm + kOffUV + 8192 + off) = zero;
-        }
-      }
-      if (c + 1 < nchunks) {  // pull the next chunk's rows (one 128-byte line each) into L2
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int e = tid + 256 * j;
-          const int which = e >> 6, row = e & 63;
-          if (e < 384 && t0 + L + row < T) {
-            const __nv_bfloat16* src = which == 0 ? g.a : which == 1 ? g.r : which == 2 ? g.b : which == 3 ? g.k : which == 4 ? g.w : g.v;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(src + base + (size_t)(t0 + L + row) * stride_t));
-          }
-        }
-      }
-      cp_async_wait_all();
-      __syncthreads();
-    }
+    // ---- raw tiles: requested during the previous chunk (before the loop for the first one) -------------------------
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
     PROF_MARK(8);
     // ---- rescale in place: warp w owns the 16-byte column piece w, lane l owns rows l and l + 32 ----------------------
     {
@@ -314,6 +300,12 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     if (!mbar_wait(&bars[1], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(3);
+    if (more) {   // A~, R~ and A_rk have been consumed: their slots take the next chunk's raw a, r and k
+      fetch_tile(kOffAR, g.a, c + 1);
+      fetch_tile(kOffAR + 8192, g.r, c + 1);
+      fetch_tile(kOffBK + 8192, g.k, c + 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     if (lower) {  // Z rows -> bf16 operand tile over the dead A_ak slot, 32 columns per thread
       uint32_t v[32];
       tmem_ld_32x32(tmem + lane_base + kColD2 + ch * 32, v);
@@ -336,6 +328,10 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     }
     if (!mbar_wait(&bars[3], par, failed)) { *failed = 1; }
     tc_fence_after();
+    if (more) {   // Z has been consumed: its slot takes the next chunk's raw b
+      fetch_tile(kOffBK, g.b, c + 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     if (lower) {  // U rows -> bf16 operand tile (over the inverse, which the finished MMA no longer reads) and, in
                   // training, the same bf16 rows for the backward pass
       uint32_t v[32];
@@ -375,6 +371,11 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     if (!mbar_wait(&bars[2], par, failed)) { *failed = 1; }
     tc_fence_after();
     PROF_MARK(6);
+    if (more) {   // B^ and V have been consumed: their slots take the next chunk's raw w and v
+      fetch_tile(kOffBKe, g.w, c + 1);
+      fetch_tile(kOffUV + 8192, g.v, c + 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     {
       uint32_t v[32];
       if (!lower) {  // output row t, columns [32 ch, 32 ch + 32)

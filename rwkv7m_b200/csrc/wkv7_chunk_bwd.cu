@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
 
   const int nchunks = (T + L - 1) / L;
   bool ok = true;
+  float lt_next = 0.f;
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
 #endif
@@ -197,10 +198,12 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         *reinterpret_cast<uint4*>(sm + kOffS0 + sw128(k, 2 * vq + 1)) = pack8(y1);
       }
       if (lower) {   // <dS1, S1> per key channel, one half of the value columns per thread
-        float lt = 0.f;
+        if (c == nchunks - 1) {   // last chunk: S1 is the final state; later chunks took it from the bf16 S0 tile
+          lt_next = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) lt = fmaf(ds[j], S1g[(size_t)(32 * ch + j) * NH + trow], lt);
-        LT[ch * NH + trow] = lt;
+          for (int j = 0; j < 32; ++j) lt_next = fmaf(ds[j], S1g[(size_t)(32 * ch + j) * NH + trow], lt_next);
+        }
+        LT[ch * NH + trow] = lt_next;
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncthreads();
@@ -439,6 +442,15 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         const float pl = PL[trow];
 #pragma unroll
         for (int j = 0; j < 32; ++j) ds[j] = fmaf(pl, ds[j], __uint_as_float(v[j]));
+        // <dS0, S0> of this chunk is the <dS1, S1> term of the next one: S0 is still in its operand tile (bf16)
+        lt_next = 0.f;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          float x[8];
+          unpack8(*reinterpret_cast<const uint4*>(sm + kOffS0 + sw128(trow, 4 * ch + p)), x);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) lt_next = fmaf(ds[8 * p + j], x[j], lt_next);
+        }
       }
     }
     tc_fence_before();
