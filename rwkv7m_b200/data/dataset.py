@@ -57,26 +57,40 @@ class BinIdxConfig:
     sampling_mode: str = "magic"
 
 
+def _check(condition: bool, message: str):
+    if not condition:
+        raise ValueError(message)
+
+
 class BinIdxBatchDataset:
-    """Returns ``{"input_ids","target_ids","mask"}`` batches (int32/int32/fp32, host tensors)."""
+    """Returns ``{"input_ids","target_ids","mask"}`` batches (int32/int32/fp32, host tensors).
+
+    Offsets of a whole step are computed at once (``step_offsets``) and the rows are gathered from the
+    memory-mapped stream with one indexed read, so a batch costs one NumPy call whatever its size."""
 
     def __init__(self, config: BinIdxConfig):
-        if config.ctx_len <= 0:
-            raise ValueError("ctx_len must be positive")
-        if config.batch_size <= 0:
-            raise ValueError("batch_size must be positive")
-        if config.world_size <= 0:
-            raise ValueError("world_size must be positive")
-        if not 0 <= config.rank < config.world_size:
-            raise ValueError("rank must satisfy 0 <= rank < world_size")
-        if config.sampling_mode not in ("magic", "sequential"):
-            raise ValueError("sampling_mode must be 'magic' or 'sequential'")
-        self.config = config
-        self.data = MMapIndexedDataset(config.data_file)
+        cfg = self.config = config
+        _check(cfg.ctx_len > 0 and cfg.batch_size > 0 and cfg.world_size > 0,
+               f"ctx_len, batch_size and world_size must be positive (got {cfg.ctx_len}, {cfg.batch_size}, {cfg.world_size})")
+        _check(0 <= cfg.rank < cfg.world_size, f"rank {cfg.rank} is outside a world of {cfg.world_size}")
+        _check(cfg.sampling_mode in ("magic", "sequential"), f"unknown sampling_mode {cfg.sampling_mode!r}")
+        self.data = MMapIndexedDataset(cfg.data_file)
         self.data_size = self.data.data_size
-        self.dataset_slot = (self.data_size - 1) // config.ctx_len
-        self.magic_prime = config.magic_prime or find_magic_prime(self.data_size, config.ctx_len)
-        self._validate()
+        self.dataset_slot = (self.data_size - 1) // cfg.ctx_len     # whole ctx_len windows that still have a next token
+        self.magic_prime = cfg.magic_prime or find_magic_prime(self.data_size, cfg.ctx_len)
+        self.lanes = cfg.batch_size * cfg.world_size
+        self._golden = int(self.magic_prime * ((math.sqrt(5) - 1) / 2))
+        self._window = np.arange(cfg.ctx_len + 1, dtype=np.int64)
+        self._mask = torch.ones(cfg.batch_size, cfg.ctx_len, dtype=torch.float32)
+        p = self.magic_prime
+        _check(self.data_size >= cfg.ctx_len + 1, f"the stream holds {self.data_size} tokens, fewer than ctx_len + 1")
+        _check(is_prime(p) and p % 3 == 2, f"magic_prime {p} is not a prime of the form 3n + 2 (the cubic map would not be a permutation)")
+        _check(0.9 < p / max(self.dataset_slot, 1) <= 1.0,
+               f"magic_prime {p} covers {p / max(self.dataset_slot, 1):.4f} of the {self.dataset_slot} windows; it has to cover more than 0.9 and at most all of them")
+        _check(p * cfg.ctx_len + 1 <= self.data_size, f"magic_prime {p} reaches past the end of the stream")
+        if cfg.sampling_mode == "sequential":
+            _check(self.dataset_slot >= self.lanes,
+                   f"{self.lanes} stream lanes need at least one window each, the stream has {self.dataset_slot}")
 
     def close(self):
         if getattr(self, "data", None) is not None:
@@ -88,96 +102,68 @@ class BinIdxBatchDataset:
         except Exception:
             pass
 
-    def _validate(self):
-        cfg = self.config
-        if not is_prime(self.magic_prime):
-            raise ValueError("magic_prime must be prime")
-        if self.magic_prime % 3 != 2:
-            raise ValueError("magic_prime must satisfy magic_prime % 3 == 2")
-        ratio = self.magic_prime / max(self.dataset_slot, 1)
-        if ratio <= 0.9 or ratio > 1.0:
-            raise ValueError(f"magic_prime must be close to data_size // ctx_len (got ratio {ratio:.4f})")
-        if self.data_size < cfg.ctx_len + 1:
-            raise ValueError("binidx dataset is smaller than ctx_len + 1")
-        if self.magic_prime * cfg.ctx_len + 1 > self.data_size:
-            raise ValueError("magic_prime can sample beyond the end of the dataset")
-        if cfg.sampling_mode == "sequential" and self.dataset_slot < cfg.batch_size * cfg.world_size:
-            raise ValueError(
-                "sequential sampling requires at least one ctx_len slot per stream lane "
-                f"(dataset_slot={self.dataset_slot}, lanes={cfg.batch_size * cfg.world_size})"
-            )
-
+    # ---- sampling plan -------------------------------------------------------------------------------------------
     @property
     def samples_per_epoch(self) -> int:
         cfg = self.config
-        if cfg.epoch_steps is not None:
-            return cfg.epoch_steps * cfg.batch_size * cfg.world_size
-        return self.dataset_slot
+        return self.dataset_slot if cfg.epoch_steps is None else cfg.epoch_steps * self.lanes
 
     @property
     def sequential_lane_length(self):
-        cfg = self.config
-        if cfg.sampling_mode != "sequential":
-            return None
-        return self.dataset_slot // (cfg.batch_size * cfg.world_size)
+        return self.dataset_slot // self.lanes if self.config.sampling_mode == "sequential" else None
 
     def should_reset_state_before_step(self, step) -> bool:
+        """Sequential lanes wrap every ``lane_length`` steps; carried state must not cross the wrap."""
         lane = self.sequential_lane_length
-        if lane is None:
-            return False
-        step = int(step)
-        return step > 0 and step % lane == 0
+        return lane is not None and int(step) > 0 and int(step) % lane == 0
+
+    def offsets(self, sample_indices, *, epoch=0) -> np.ndarray:
+        """Token offsets of the given per-rank sample indices (any integer array)."""
+        cfg = self.config
+        idx = np.asarray(sample_indices, dtype=np.int64)
+        if cfg.sampling_mode == "sequential":
+            lane_len = self.dataset_slot // self.lanes
+            lane = cfg.rank * cfg.batch_size + idx % cfg.batch_size
+            walked = (int(epoch) * lane_len + idx // cfg.batch_size) % lane_len
+            return (lane * lane_len + walked) * cfg.ctx_len
+        p = np.uint64(self.magic_prime)
+        ii = (np.int64(1 + int(epoch) * self.samples_per_epoch) + idx * cfg.world_size + cfg.rank).astype(np.uint64) % p
+        cube = (ii * ii % p) * ii % p                      # every factor is below 2^31, so no product overflows
+        return ((np.uint64(self._golden % self.magic_prime) * cube) % p).astype(np.int64) * cfg.ctx_len
 
     def sample_offset(self, sample_index, *, epoch=0) -> int:
-        cfg = self.config
-        sample_index = int(sample_index)
-        if cfg.sampling_mode == "sequential":
-            row = sample_index % cfg.batch_size
-            step_in_lane = sample_index // cfg.batch_size
-            lane = cfg.rank * cfg.batch_size + row
-            lane_len = self.dataset_slot // (cfg.world_size * cfg.batch_size)
-            chunk = lane * lane_len + (int(epoch) * lane_len + step_in_lane) % lane_len
-            return chunk * cfg.ctx_len
-        ii = 1 + int(epoch) * self.samples_per_epoch + sample_index * cfg.world_size + cfg.rank
-        factor = int(self.magic_prime * ((math.sqrt(5) - 1) / 2))
-        return ((factor * ii * ii * ii) % self.magic_prime) * cfg.ctx_len
+        return int(self.offsets([int(sample_index)], epoch=epoch)[0])
+
+    def step_offsets(self, step, *, epoch=0) -> np.ndarray:
+        b = self.config.batch_size
+        return self.offsets(int(step) * b + np.arange(b), epoch=epoch)
+
+    # ---- reads ---------------------------------------------------------------------------------------------------------
+    def _gather(self, offsets: np.ndarray) -> np.ndarray:
+        return np.asarray(self.data._bin[offsets[:, None] + self._window[None, :]]).astype(np.int32)
 
     def get_sequence(self, sample_index, *, epoch=0):
-        off = self.sample_offset(sample_index, epoch=epoch)
-        return self.data.get_global(offset=off, length=self.config.ctx_len + 1).astype(np.int32)
+        return self._gather(self.offsets([int(sample_index)], epoch=epoch))[0]
 
     def get_example(self, sample_index, *, epoch=0):
         tokens = self.get_sequence(sample_index, epoch=epoch)
         return tokens[:-1], tokens[1:]
 
     def get_batch(self, step, *, epoch=0, pin_memory=False):
-        cfg = self.config
-        tokens = np.empty((cfg.batch_size, cfg.ctx_len + 1), dtype=np.int32)
-        start = int(step) * cfg.batch_size
-        for row in range(cfg.batch_size):
-            tokens[row] = self.get_sequence(start + row, epoch=epoch)
-        tok = torch.from_numpy(tokens)
-        batch = {
-            "input_ids": tok[:, :-1].contiguous(),
-            "target_ids": tok[:, 1:].contiguous(),
-            "mask": torch.ones(cfg.batch_size, cfg.ctx_len, dtype=torch.float32),
-        }
+        tok = torch.from_numpy(self._gather(self.step_offsets(step, epoch=epoch)))
+        batch = {"input_ids": tok[:, :-1].contiguous(), "target_ids": tok[:, 1:].contiguous(), "mask": self._mask.clone()}
         if pin_memory and torch.cuda.is_available():
             batch = {k: v.pin_memory() for k, v in batch.items()}
         return batch
 
     def iter_batches(self, *, epoch=0, steps=None):
-        if steps is None:
-            steps = self.samples_per_epoch // self.config.batch_size
-        for step in range(int(steps)):
+        total = self.samples_per_epoch // self.config.batch_size if steps is None else int(steps)
+        for step in range(total):
             yield self.get_batch(step, epoch=epoch)
 
 
 def create_binidx_dataset(data_file, *, ctx_len, batch_size=1, magic_prime=None, epoch_steps=None,
                           rank=0, world_size=1, sampling_mode="magic") -> BinIdxBatchDataset:
-    return BinIdxBatchDataset(
-        BinIdxConfig(
-            data_file=str(data_file), ctx_len=ctx_len, batch_size=batch_size, magic_prime=magic_prime,
-            epoch_steps=epoch_steps, rank=rank, world_size=world_size, sampling_mode=sampling_mode,
-        )
-    )
+    return BinIdxBatchDataset(BinIdxConfig(
+        data_file=str(data_file), ctx_len=ctx_len, batch_size=batch_size, magic_prime=magic_prime,
+        epoch_steps=epoch_steps, rank=rank, world_size=world_size, sampling_mode=sampling_mode))

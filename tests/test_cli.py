@@ -174,3 +174,38 @@ def test_distributed_trainer_accepts_a_model_axis(tiny_binidx, tmp_path):
     ts, _, s2 = train_binidx_distributed.run_distributed_training(
         train_binidx_distributed.parse_args(["--steps", "1", "--resume", str(out / "ckpt-00000002")] + common))
     assert s2["status"] == "completed" and int(ts.step) == 3
+
+
+def test_upstream_single_device_trainer_protocol(tiny_binidx, tmp_path):
+    """The upstream-protocol loop: learning-rate rule, optimizer groups, sampler, artefacts, weights that move."""
+    from rwkv7m_b200.cli import train_upstream_single_gpu as up
+    from rwkv7m_b200.data.dataset import create_binidx_dataset
+
+    assert up.upstream_learning_rate(0, lr_init=1e-3, lr_final=1e-5, warmup_steps=10, total_steps=100) == pytest.approx(1e-5)
+    assert up.upstream_learning_rate(10, lr_init=1e-3, lr_final=1e-5, warmup_steps=10, total_steps=100) == pytest.approx(1e-3)
+    assert up.upstream_learning_rate(100, lr_init=1e-3, lr_final=1e-5, warmup_steps=10, total_steps=100) == pytest.approx(1e-5)
+    assert up.optimizer_group("blocks.0.att.w0", 1, 0.001) == "2x"
+    assert up.optimizer_group("blocks.0.att.key.weight", 2, 0.001) == "decay"
+    assert up.optimizer_group("blocks.0.att.key.weight", 2, 0.0) == "1x"
+    assert up.optimizer_group("blocks.0.att.w1", 2, 0.001) == "1x"
+    ds = create_binidx_dataset(tiny_binidx, ctx_len=4)
+    prime = ds.magic_prime
+    # the trainer's sampler walks the same cubic permutation as the framework's dataset
+    assert [up.sample_offset(i, magic_prime=prime, ctx_len=4) for i in range(5)] == [ds.sample_offset(i) for i in range(5)]
+    ds.close()
+    out = tmp_path / "up"
+    last = up.main(["--data-file", tiny_binidx, "--output-dir", str(out), "--steps", "12", "--global-batch-size", "4",
+                    "--micro-batch-size", "2", "--ctx-len", "4", "--magic-prime", str(prime), "--n-layer", "2",
+                    "--n-embd", "32", "--dim-ffn", "64", "--vocab-size", "300", "--head-size", "16", "--precision", "fp32",
+                    "--warmup-steps", "2", "--lr-init", "3e-3", "--device", "cpu", "--save-every", "6"])
+    rows = [json.loads(l) for l in (out / "metrics.jsonl").read_text().splitlines()]
+    assert len(rows) == 12 and rows[-1]["step"] == 12
+    assert all(r["loss"] == r["loss"] and r["loss"] < 7.0 and r["grad_norm"] > 0 for r in rows)   # near ln(300) = 5.7
+    assert rows[0]["lr"] == pytest.approx(3e-3 * 0.01) and rows[2]["lr"] == pytest.approx(3e-3)
+    w0, w1 = torch.load(out / "rwkv-init.pth"), torch.load(out / "rwkv-final.pth")
+    assert set(w0) == set(w1) and float((w0["blocks.0.att.key.weight"] - w1["blocks.0.att.key.weight"]).abs().max()) > 0
+    cfg = json.loads((out / "run_config.json").read_text())
+    assert cfg["gradient_accumulation_steps"] == 2 and "blocks.0.att.w0" in cfg["optimizer_groups"]["2x"]
+    assert (out / "rwkv-6.pth").exists() and (out / "rwkv-final.pth").exists()
+    assert json.loads((out / "run_summary.json").read_text())["status"] == "completed"
+    assert last["tokens"] == 12 * 4 * 4
