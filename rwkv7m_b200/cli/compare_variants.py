@@ -1,17 +1,22 @@
 """``rwkv7m-compare-variants``: the four-variant screening experiment matrix and its summary.
 
-Re-statement in Python of the reference's shell harness (comparison.sh: parameter planner 560-650,
-variant matrix 925-960, summaries / AUC / time-to-loss 1038-1245).  Three sub-commands:
+Re-statement in Python of the reference's shell harness (comparison.sh: corpus preparation 360-395, parameter
+planner 560-650, variant matrix 925-960, upstream run 700-900, summaries / AUC / time-to-loss 1038-1245).
+Sub-commands:
 
+  corpus      tokenise a local JSONL / plain-text corpus into train and validation binidx files (the reference
+              downloads MiniPile; here the text comes from ``--corpus-file``) and print their magic primes
   plan        exact trainable-parameter counts of the variants and the widened-FFN control that
               matches the largest screening variant (counted on the meta device, not by formula)
   run         train every variant with identical data, sampler, optimizer and precision settings
-              through the distributed trainer, one output directory per variant
+              through the distributed trainer, one output directory per variant; ``--with-upstream`` adds the
+              ``upstream_rwkv_lm_v7`` arm: the upstream-protocol loop on an upstream-layout x070 model with the core
+              baseline's shape (``rwkv7m-train-upstream-single-gpu``)
   summarize   per-variant final / best eval loss, eval-loss AUC over tokens, first step / tokens /
               seconds at which each loss target is reached, mean tokens/s; CSV + JSON
 
-Corpus download and the upstream-repository run of the reference script need network access and are
-not part of this command; ``--data-file`` takes an existing binidx prefix.
+Nothing here needs network access: the official repository's own CUDA model is replaced by the plain-PyTorch x070
+network of ``backends/upstream_x070.py``.
 """
 
 from __future__ import annotations
@@ -28,6 +33,72 @@ from . import train_binidx_distributed as trainer
 from .common import build_config
 
 VARIANT_ORDER = ("local_core_baseline", "local_read_screening", "local_mechanism", "local_param_control")
+UPSTREAM_VARIANT = "upstream_rwkv_lm_v7"
+
+
+def prepare_corpus(corpus_file, root, *, ctx_len, validation_fraction=0.05, epochs=1, seed=42, vocab_file=None) -> dict:
+    """Split a corpus (JSONL rows with a ``text`` field, or plain text with one document per non-empty line) into train
+    and validation parts and tokenise both into binidx files under ``root/data``."""
+    import random
+
+    from ..data import find_magic_prime
+    from .make_binidx import build_binidx
+
+    root = Path(root) / "data"
+    root.mkdir(parents=True, exist_ok=True)
+    docs = []
+    for line in Path(corpus_file).read_text(encoding="utf-8").splitlines():
+        line = line.strip()
+        if not line:
+            continue
+        try:
+            row = json.loads(line)
+            text = row["text"] if isinstance(row, dict) and "text" in row else line
+        except json.JSONDecodeError:
+            text = line
+        docs.append(text)
+    if len(docs) < 2:
+        raise ValueError("the corpus needs at least two documents (one for validation)")
+    random.Random(seed).shuffle(docs)
+    n_val = max(1, int(round(len(docs) * validation_fraction)))
+    out = {}
+    for split, part, ep in (("validation", docs[:n_val], 1), ("train", docs[n_val:], epochs)):
+        jsonl = root / f"{split}.jsonl"
+        jsonl.write_text("".join(json.dumps({"text": t}) + "\n" for t in part), encoding="utf-8")
+        stats = build_binidx(jsonl, root / split, vocab_file=vocab_file, epochs=ep, seed=seed)
+        stats["prefix"] = str(root / split)
+        stats["documents"] = len(part)
+        stats["magic_prime"] = find_magic_prime(stats["tokens"], ctx_len) if stats["tokens"] >= ctx_len + 1 else None
+        out[split] = stats
+    (root / "corpus.json").write_text(json.dumps(out, indent=2, sort_keys=True) + "\n")
+    return out
+
+
+def run_upstream_arm(root, passthrough, *, d_ffn) -> dict:
+    """The upstream arm: same data, context, batch, steps, seed and optimizer constants as the local variants, model
+    shape of the core baseline, trained by the upstream-protocol loop."""
+    from . import train_upstream_single_gpu as up
+
+    a = _trainer_args(passthrough, ["--no-screening", "--screened-layers"])
+    cfg = build_config(a)
+    from ..data import find_magic_prime
+    from ..data.binidx import MMapIndexedDataset
+
+    data = MMapIndexedDataset(a.data_file)
+    prime = a.magic_prime or find_magic_prime(data.data_size, a.ctx_len)
+    data.close()
+    micro = max(1, a.global_batch_size // max(a.gradient_accumulation_steps, 1))
+    argv = ["--data-file", a.data_file, "--output-dir", str(Path(root) / UPSTREAM_VARIANT), "--steps", str(a.steps),
+            "--global-batch-size", str(a.global_batch_size), "--micro-batch-size", str(micro),
+            "--ctx-len", str(a.ctx_len), "--magic-prime", str(prime), "--n-layer", str(cfg.n_layers),
+            "--n-embd", str(cfg.d_model), "--dim-ffn", str(d_ffn), "--vocab-size", str(cfg.vocab_size),
+            "--head-size", str(cfg.head_size), "--precision", "bf16" if cfg.dtype == "bfloat16" else "fp32",
+            "--lr-init", str(cfg.lr_init), "--lr-final", str(cfg.lr_final),
+            "--warmup-steps", str(min(cfg.warmup_steps, max(a.steps - 1, 0))), "--beta1", str(cfg.adam_beta1),
+            "--beta2", str(cfg.adam_beta2), "--adam-eps", str(cfg.adam_eps), "--weight-decay", str(cfg.weight_decay),
+            "--grad-clip", str(cfg.max_grad_norm), "--seed", str(a.seed), "--device", str(a.device), "--allow-any-batch"]
+    last = up.main(argv)
+    return {"status": "completed", "last_train": last}
 
 
 def _trainer_args(passthrough, extra):
@@ -68,7 +139,7 @@ def plan_variants(passthrough, mechanism_phase="read_write") -> dict:
     return {"variants": rows, "param_target": target, "screening_extra_params": mech - baseline}
 
 
-def run_variants(root, passthrough, *, mechanism_phase="read_write", variants=VARIANT_ORDER) -> dict:
+def run_variants(root, passthrough, *, mechanism_phase="read_write", variants=VARIANT_ORDER, with_upstream=False) -> dict:
     root = Path(root)
     root.mkdir(parents=True, exist_ok=True)
     plan = plan_variants(passthrough, mechanism_phase)
@@ -87,6 +158,8 @@ def run_variants(root, passthrough, *, mechanism_phase="read_write", variants=VA
         args = _trainer_args(passthrough, extra)
         _, _, summary = trainer.run_distributed_training(args)
         summaries[name] = summary
+    if with_upstream:
+        summaries[UPSTREAM_VARIANT] = run_upstream_arm(root, passthrough, d_ffn=plan["variants"]["local_core_baseline"]["d_ffn"])
     return {"plan": plan, "summaries": summaries}
 
 
@@ -131,7 +204,7 @@ def _first_hit(evals, target, seconds, tokens_per_step):
 def summarize(root, *, tokens_per_step, loss_targets=()) -> dict:
     root = Path(root)
     payload = {}
-    for name in VARIANT_ORDER:
+    for name in VARIANT_ORDER + (UPSTREAM_VARIANT,):
         recs = _records(root / name / "metrics.jsonl")
         if not recs:
             continue
@@ -172,16 +245,26 @@ def summarize(root, *, tokens_per_step, loss_targets=()) -> dict:
 
 def main(argv=None):
     p = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    p.add_argument("command", choices=["plan", "run", "summarize"])
+    p.add_argument("command", choices=["corpus", "plan", "run", "summarize"])
+    p.add_argument("--corpus-file", default=None)
+    p.add_argument("--validation-fraction", type=float, default=0.05)
+    p.add_argument("--corpus-epochs", type=int, default=1)
+    p.add_argument("--corpus-ctx-len", type=int, default=512)
+    p.add_argument("--with-upstream", action="store_true")
     p.add_argument("--root", default="comparison_runs")
     p.add_argument("--mechanism-phase", choices=["read_screening_only", "read_write"], default="read_write")
     p.add_argument("--loss-targets", type=float, nargs="*", default=[])
     p.add_argument("--tokens-per-step", type=int, default=None)
     args, passthrough = p.parse_known_args(argv)
-    if args.command == "plan":
+    if args.command == "corpus":
+        if args.corpus_file is None:
+            p.error("corpus needs --corpus-file (JSONL with a text field, or one document per line)")
+        print(json.dumps(prepare_corpus(args.corpus_file, args.root, ctx_len=args.corpus_ctx_len,
+                                        validation_fraction=args.validation_fraction, epochs=args.corpus_epochs), indent=2))
+    elif args.command == "plan":
         print(json.dumps(plan_variants(passthrough, args.mechanism_phase), indent=2))
     elif args.command == "run":
-        out = run_variants(args.root, passthrough, mechanism_phase=args.mechanism_phase)
+        out = run_variants(args.root, passthrough, mechanism_phase=args.mechanism_phase, with_upstream=args.with_upstream)
         print(json.dumps({k: v.get("status") for k, v in out["summaries"].items()}, indent=2))
     else:
         if args.tokens_per_step is None:

@@ -136,6 +136,29 @@ def test_compare_variants_plan_run_summarize(tiny_binidx, tmp_path):
     assert (root / "summary.csv").exists() and (root / "parameter_counts.csv").exists()
 
 
+def test_compare_variants_corpus_and_upstream_arm(tmp_path):
+    """``corpus`` tokenises a local text file into train / validation binidx; ``--with-upstream`` adds the
+    upstream-protocol arm next to the local variants and the summary lists it."""
+    from rwkv7m_b200.cli import compare_variants
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(f"document {i}: the quick brown fox jumps over the lazy dog {i} times." for i in range(40)))
+    root = tmp_path / "cmp2"
+    stats = compare_variants.prepare_corpus(corpus, root, ctx_len=8, validation_fraction=0.1, epochs=2)
+    assert stats["validation"]["documents"] == 4 and stats["train"]["documents"] == 36
+    assert stats["train"]["items"] == 72 and stats["train"]["magic_prime"] % 3 == 2
+    model = ["--d-model", "32", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64",
+             "--vocab-size", "65536", "--n-slots", "4", "--d-slot", "16", "--d-k", "8", "--d-v", "8", "--screened-layers", "1"]
+    train = ["--data-file", stats["train"]["prefix"], "--ctx-len", "8",
+             "--global-batch-size", "2", "--steps", "3", "--print-every", "0", "--eval-every", "3", "--summary-every", "0",
+             "--device", "cpu"]
+    out = compare_variants.run_variants(root, model + train, variants=("local_core_baseline",), with_upstream=True)
+    assert out["summaries"][compare_variants.UPSTREAM_VARIANT]["status"] == "completed"
+    summary = compare_variants.summarize(root, tokens_per_step=16)
+    assert set(summary) == {"local_core_baseline", compare_variants.UPSTREAM_VARIANT}
+    assert summary[compare_variants.UPSTREAM_VARIANT]["train_steps"] == 3
+
+
 def test_distributed_trainer_accepts_a_model_axis(tiny_binidx, tmp_path):
     """``--mesh-axis-names data model --mesh-axis-sizes 1 2``: two gloo ranks train tensor-parallel through the
     trainer CLI, write an un-sharded checkpoint, and a single process resumes from it."""
