@@ -479,7 +479,9 @@ def main(argv=None):
             "clocks": clocks,
             "gpu_launches": launches,
             "last_loss": last_loss,
-            "expected_loss_random_ids": math.log(V),
+            # uniform-random targets: ln(V) plus half the variance of the initial logits (the variance-scaled LM-head
+            # initialisation of the large presets gives logits of standard deviation 0.5 sqrt(V / C))
+            "expected_loss_random_ids": math.log(V) + (0.125 * V / cfg.d_model if cfg.lm_head_init != "orthogonal" else 0.125),
         }
         if wkv is not None:
             line["wkv7_fwd_bwd_tflops"] = wkv.get("fwd_bwd_tflops")

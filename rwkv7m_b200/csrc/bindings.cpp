@@ -6,6 +6,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <mutex>
 
 #include "kernels.h"
 
@@ -148,9 +150,31 @@ Tensor& gemm_error_flag(const at::Device& dev) {
   return f;
 }
 
+// Workspace of the decode-sized GEMM (fp32 partial sums [64, cols] + one counter per 128 columns), one per device and
+// stream: calls on one stream are ordered and leave it zeroed, calls on different streams (the parallel projection
+// branches of a decode step) must not share it.  Allocated and zeroed on first use, regrown when a wider output comes.
+static bool g_decode_gemm = true;
+static bool decode_gemm_enabled() { return g_decode_gemm; }
+void set_decode_gemm(bool on) { g_decode_gemm = on; }
+struct DecodeWorkspace { Tensor partial, counters; int64_t cols = 0; };
+static DecodeWorkspace& decode_workspace(const c10::Device& dev, cudaStream_t st, int64_t n_cols) {
+  static std::mutex mu;
+  static std::map<std::pair<int, uintptr_t>, DecodeWorkspace> cache;
+  std::lock_guard<std::mutex> g(mu);
+  DecodeWorkspace& w = cache[{(int)dev.index(), reinterpret_cast<uintptr_t>(st)}];
+  if (w.cols < n_cols) {
+    const int64_t cols = std::max<int64_t>((n_cols + 127) / 128 * 128, 8192);
+    auto o = torch::TensorOptions().device(dev);
+    w.partial = torch::zeros({64, cols}, o.dtype(at::kFloat));
+    w.counters = torch::zeros({cols / 128}, o.dtype(at::kInt));
+    w.cols = cols;
+  }
+  return w;
+}
+
 // D = op(A) op(B); see kernels.h for the three layouts.  D must be preallocated.
 void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue, int64_t pair,
-          const c10::optional<Tensor>& aux) {
+          const c10::optional<Tensor>& aux, int64_t act) {
   static const bool trace = [] { const char* e = getenv("RWKV7M_B200_TRACE"); return e != nullptr && e[0] == '1'; }();
   if (trace) { fprintf(stderr, "[gemm-bind] enter layout=%d epi=%d\n", (int)layout, (int)epilogue); fflush(stderr); }
   c10::cuda::CUDAGuard guard(A.device());
@@ -162,6 +186,9 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = D.data_ptr();
   p.lda = (int)A.stride(0); p.ldb = (int)B.stride(0); p.ldd = (int)D.stride(0);
   p.layout = (int)layout; p.epilogue = (int)epilogue; p.pair = (int)pair;
+  TORCH_CHECK(act >= 0 && act <= 2 && (act == 0 || epilogue == rk::kEpiStoreBf16 || epilogue == rk::kEpiMulSqrt2Bf16),
+              "gemm: an activation selector goes with the bf16 store or the derivative-factor epilogue only");
+  p.act = (int)act;
   if (layout == rk::kGemmTN) {
     p.M = (int)A.size(0); p.K = (int)A.size(1); p.N = (int)B.size(0);
     TORCH_CHECK(B.size(1) == p.K, "gemm TN: K mismatch");
@@ -187,6 +214,12 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   if (trace) { fprintf(stderr, "[gemm-bind] checks ok\n"); fflush(stderr); }
   p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();
   if (trace) { fprintf(stderr, "[gemm-bind] flag ok\n"); fflush(stderr); }
+  if (decode_gemm_enabled() && rk::gemm_decode_eligible(p)) {
+    DecodeWorkspace& w = decode_workspace(A.device(), stream(), p.N);
+    p.ws_partial = w.partial.data_ptr<float>();
+    p.ws_counters = reinterpret_cast<unsigned*>(w.counters.data_ptr<int>());
+    p.ws_ld = (int)w.cols;
+  }
   const int rc = rk::gemm_bf16(p, stream());
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
 }
@@ -392,6 +425,34 @@ Tensor relusq_bwd(const Tensor& dh, const Tensor& h) {
   return out;
 }
 
+Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
+  c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(ids.is_cuda() && ids.is_contiguous() && ids.scalar_type() == at::kInt, "ids must be contiguous int32 CUDA");
+  TORCH_CHECK(table.is_cuda() && table.is_contiguous() && table.dim() == 2 &&
+                  (table.scalar_type() == at::kBFloat16 || table.scalar_type() == at::kFloat),
+              "embedding table must be a contiguous bf16 or fp32 matrix");
+  const int64_t M = ids.numel(), V = table.size(0), C = table.size(1);
+  TORCH_CHECK(C % 8 == 0 && M < ((int64_t)1 << 31), "embedding width must be a multiple of 8");
+  auto shape = ids.sizes().vec();
+  shape.push_back(C);
+  Tensor out = torch::empty(shape, table.options().dtype(at::kBFloat16));
+  if (M > 0)
+    rk::embedding_fwd(ids.data_ptr<int>(), table.data_ptr(), table.scalar_type() == at::kBFloat16, out.data_ptr(), (int)M,
+                      (int)C, (int)V, stream());
+  return out;
+}
+
+void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor grad) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  TORCH_CHECK(ids.is_cuda() && ids.is_contiguous() && ids.scalar_type() == at::kInt, "ids must be contiguous int32 CUDA");
+  check_act(dout, "dout");
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && grad.scalar_type() == at::kFloat && grad.dim() == 2,
+              "table gradient must be a contiguous fp32 matrix");
+  const int64_t M = ids.numel(), V = grad.size(0), C = grad.size(1);
+  TORCH_CHECK(C % 8 == 0 && dout.numel() == M * C, "gradient rows do not match the ids");
+  if (M > 0) rk::embedding_bwd(ids.data_ptr<int>(), dout.data_ptr(), grad.data_ptr<float>(), (int)M, (int)C, (int)V, stream());
+}
+
 std::vector<Tensor> ce_fwd(const Tensor& logits, const Tensor& targets) {
   c10::cuda::CUDAGuard guard(logits.device());
   check_act(logits, "logits");
@@ -582,10 +643,11 @@ std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const 
                                     const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
-                                    bool save) {
+                                    bool save, const c10::optional<Tensor>& tau_dev) {
   c10::cuda::CUDAGuard guard(q_r.device());
   rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
                                      write_enabled, value_unit_norm, age_mask);
+  if (tau_dev.has_value() && tau_dev->defined()) { TORCH_CHECK(tau_dev->numel() == 2); a.tau_dev = fptr(*tau_dev); }
   auto o = q_r.options();
   const int J = 2 * a.dk + a.dv;
   Tensor u = torch::empty({a.B, a.T, a.dv}, o);
@@ -610,10 +672,11 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
                                     const Tensor& saved, const Tensor& saved_ages, const Tensor& saved_P, const Tensor& du,
-                                    const c10::optional<Tensor>& dslots_out) {
+                                    const c10::optional<Tensor>& dslots_out, const c10::optional<Tensor>& tau_dev) {
   c10::cuda::CUDAGuard guard(q_r.device());
   rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
                                      write_enabled, value_unit_norm, age_mask);
+  if (tau_dev.has_value() && tau_dev->defined()) { TORCH_CHECK(tau_dev->numel() == 2); a.tau_dev = fptr(*tau_dev); }
   auto o = q_r.options();
   const int J = 2 * a.dk + a.dv;
   TORCH_CHECK(saved_P.numel() == (int64_t)a.B * a.T * 16 * J && saved.numel() == (int64_t)a.B * a.T * a.ds * 16,
@@ -727,7 +790,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
   m.def("grad_norm_sq", &grad_norm_sq);
   m.def("adamw_flat", &adamw_flat);
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("D"), py::arg("layout"), py::arg("epilogue"), py::arg("pair"),
+        py::arg("aux") = py::none(), py::arg("act") = 0);
   m.def("gemm_error", &gemm_error);
   m.def("gemm_error_reset", &gemm_error_reset);
   m.def("layernorm_fwd", &layernorm_fwd);
@@ -738,7 +802,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tmix_pre_bwd", &tmix_pre_bwd);
   m.def("gn_bonus_gate_fwd", &gn_bonus_gate_fwd);
   m.def("gn_bonus_gate_bwd", &gn_bonus_gate_bwd);
+  m.def("set_decode_gemm", &set_decode_gemm);
   m.def("relusq_bwd", &relusq_bwd);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("dp_step", &dp_step);

@@ -9,6 +9,8 @@
 //   relusq_bwd           derivative of relu(x)^2 from the saved output
 //
 // Math: src/rwkv7m/model/nnx_model.py:592-798 of the reference.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -1160,6 +1162,74 @@ void relusq_bwd(const void* dh, const void* h, void* out, int64_t n, cudaStream_
   int64_t want = (n / 8 + 255) / 256;
   int blocks = (int)(want > 148 * 32 ? 148 * 32 : (want < 1 ? 1 : want));
   relusq_bwd_kernel<<<blocks, 256, 0, st>>>((const bf16*)dh, (const bf16*)h, (bf16*)out, n);
+}
+
+// ---------------------------------------------------------------------------------
+// Embedding: out[m] = table[ids[m]] (bf16 out, bf16 or fp32 table) and its transpose, the scatter-add of the output
+// gradient rows into the fp32 gradient of the table.  One warp per token row, 16-byte accesses; the scatter uses one
+// vector reduction (red.global.add.v4.f32) per four channels, so rows that repeat a token id add up in any order.
+// Ids outside [0, V) produce a zero row forward and are skipped backward.
+// ---------------------------------------------------------------------------------
+template <typename TT>
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
+                                                            bf16* __restrict__ out, int M, int C, int V) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; m < M; m += warps) {
+    const int id = ids[m];
+    const bool ok = id >= 0 && id < V;
+    const TT* src = table + (size_t)(ok ? id : 0) * C;
+    bf16* dst = out + (size_t)m * C;
+    for (int c = lane * 8; c < C; c += 256) {
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);
+      if (ok) {
+        if constexpr (sizeof(TT) == 2) {
+          o = *reinterpret_cast<const uint4*>(src + c);
+        } else {
+          const float4 a = *reinterpret_cast<const float4*>(src + c), b = *reinterpret_cast<const float4*>(src + c + 4);
+          bf162* po = reinterpret_cast<bf162*>(&o);
+          po[0] = __floats2bfloat162_rn(a.x, a.y); po[1] = __floats2bfloat162_rn(a.z, a.w);
+          po[2] = __floats2bfloat162_rn(b.x, b.y); po[3] = __floats2bfloat162_rn(b.z, b.w);
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + c) = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const int* __restrict__ ids, const bf16* __restrict__ dout,
+                                                            float* __restrict__ grad, int M, int C, int V) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; m < M; m += warps) {
+    const int id = ids[m];
+    if (id < 0 || id >= V) continue;
+    const bf16* src = dout + (size_t)m * C;
+    float* dst = grad + (size_t)id * C;
+    for (int c = lane * 8; c < C; c += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + c);
+      const bf162* pr = reinterpret_cast<const bf162*>(&raw);
+      const float2 a = __bfloat1622float2(pr[0]), b = __bfloat1622float2(pr[1]);
+      const float2 e = __bfloat1622float2(pr[2]), f = __bfloat1622float2(pr[3]);
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c), "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y)
+                   : "memory");
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c + 4), "f"(e.x), "f"(e.y), "f"(f.x), "f"(f.y)
+                   : "memory");
+    }
+  }
+}
+
+void embedding_fwd(const int* ids, const void* table, bool table_bf16, void* out, int M, int C, int V, cudaStream_t st) {
+  const int blocks = std::min(148 * 8, (M + 7) / 8);
+  if (table_bf16)
+    embedding_fwd_kernel<bf16><<<blocks, 256, 0, st>>>(ids, (const bf16*)table, (bf16*)out, M, C, V);
+  else
+    embedding_fwd_kernel<float><<<blocks, 256, 0, st>>>(ids, (const float*)table, (bf16*)out, M, C, V);
+}
+
+void embedding_bwd(const int* ids, const void* dout, float* grad, int M, int C, int V, cudaStream_t st) {
+  const int blocks = std::min(148 * 8, (M + 7) / 8);
+  embedding_bwd_kernel<<<blocks, 256, 0, st>>>(ids, (const bf16*)dout, grad, M, C, V);
 }
 
 }  // namespace rk

@@ -63,11 +63,26 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   return false;
 }
 
+// Activation of the kEpiStoreBf16 epilogue (act 1 = tanh, 2 = sigmoid) and the factor of the kEpiMulSqrt2Bf16 epilogue,
+// the derivative of the producing activation expressed through its saved output h: act 0 = relu(.)^2 -> 2 sqrt(h),
+// 1 = tanh -> 1 - h^2, 2 = sigmoid -> h (1 - h).
+__device__ __forceinline__ float act_apply(float x, int act) {
+  if (act == 1) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  return __fdividef(1.f, 1.f + __expf(-x));
+}
+__device__ __forceinline__ float act_grad(float h, int act) {
+  return act == 0 ? 2.f * sqrtf(h) : (act == 1 ? 1.f - h * h : h * (1.f - h));
+}
+
 // Write one 32-column chunk of an accumulator row (thread = row) with the selected epilogue.
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __restrict__ Dptr, int row, int col0, int M,
                                             int N, int ldd, bool atomic = false, const void* __restrict__ aux = nullptr,
-                                            int ldaux = 0) {
+                                            int ldaux = 0, int act = 0) {
   if (EPI == kEpiScatterAddBf16) {
     // Reduce-scatter over time fused into the epilogue: the row belongs to the rank that owns its time slice; the
     // partial result is added straight into that rank's output buffer (peer memory over NVLink, bf16x2 atomics).
@@ -106,7 +121,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
         for (int j = 0; j < 16; ++j) {
           const float2 hx = __bfloat1622float2(h2[j]);
           float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-          if (EPI == kEpiMulSqrt2Bf16) { x0 *= 2.f * sqrtf(hx.x); x1 *= 2.f * sqrtf(hx.y); }
+          if (EPI == kEpiMulSqrt2Bf16) { x0 *= act_grad(hx.x, act); x1 *= act_grad(hx.y, act); }
           else { x0 += hx.x; x1 += hx.y; }
           __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
           pk[j] = *reinterpret_cast<uint32_t*>(&h);
@@ -120,7 +135,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
           if (col0 + j < N) {
             const float hx = __bfloat162float(ax[j]);
             float x0 = __uint_as_float(v[j]);
-            x0 = EPI == kEpiMulSqrt2Bf16 ? x0 * 2.f * sqrtf(hx) : x0 + hx;
+            x0 = EPI == kEpiMulSqrt2Bf16 ? x0 * act_grad(hx, act) : x0 + hx;
             out[j] = f2bf(x0);
           }
         }
@@ -137,6 +152,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
               for (int j = 0; j < 16; ++j) {
                 float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
                 if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1; }
+                else if (act != 0) { x0 = act_apply(x0, act); x1 = act_apply(x1, act); }
                 __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
                 pk[j] = *reinterpret_cast<uint32_t*>(&h);
               }
@@ -149,6 +165,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
               for (int j = 0; j < 32; ++j) {
                 float x0 = __uint_as_float(v[j]);
                 if (EPI == kEpiReluSqBf16) { x0 = fmaxf(x0, 0.f); x0 *= x0; }
+                else if (act != 0) x0 = act_apply(x0, act);
                 if (col0 + j < N) out[j] = f2bf(x0);
               }
             }
@@ -217,7 +234,7 @@ template <int BN, int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int splits,
-                 const void* __restrict__ aux, int ldaux, int* __restrict__ err) {
+                 const void* __restrict__ aux, int ldaux, int act, int* __restrict__ err) {
   using TL = Tile<BN>;
   constexpr int kStages = TL::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -344,14 +361,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32(t0 + c * 32, v0);
           tmem_ld_32x32(t0 + c * 32 + 32, v1);
           tmem_ld_wait();
-          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux);
-          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux);
+          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux, act);
+          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux, act);
         }
       } else {
         uint32_t v[32];
         tmem_ld_32x32(t0, v);
         tmem_ld_wait();
-        store_chunk<EPI>(v, Dptr, row, n0, M, N, ldd, atomic, aux, ldaux);
+        store_chunk<EPI>(v, Dptr, row, n0, M, N, ldd, atomic, aux, ldaux, act);
       }
       tc_fence_before();
       __syncwarp();
@@ -398,7 +415,7 @@ template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m,
-                      const void* __restrict__ aux, int ldaux, int* __restrict__ err) {
+                      const void* __restrict__ aux, int ldaux, int act, int* __restrict__ err) {
   using TL = PairTile;
   constexpr int kStages = TL::kStages;
   constexpr int BN2 = 256;  // tile width of the pair
@@ -525,8 +542,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32(t0 + c * 32, v0);
         tmem_ld_32x32(t0 + c * 32 + 32, v1);
         tmem_ld_wait();
-        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux);
-        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux);
+        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux, act);
+        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux, act);
       }
       tc_fence_before();
       __syncwarp();
@@ -687,7 +704,7 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   const int grid = work < sm_count() ? work : sm_count();
   RK_TRACE("attr ok grid=%d smem=%d splits=%d\n", grid, TL::kSmemBytes, splits);
   kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.aux, p.ldaux,
-                                                   p.error_flag);
+                                                   p.act, p.error_flag);
   RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -735,7 +752,7 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.aux, p.ldaux,
-                                                    p.error_flag);
+                                                    p.act, p.error_flag);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -752,6 +769,165 @@ int launch_pair_epi(const GemmArgs& p, cudaStream_t st) {
   return 5;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode-sized GEMM: y[M <= 64, N] = x[M, K] W[N, K]^T, the shape of every projection of a T = 1 serving step.  The work
+// is streaming the weight matrix once, so the roles of the operands are swapped: a CTA takes 128 rows of W as the
+// 128-row tensor-core operand and the (zero-padded) 64 activation rows as the 64-column operand, and the reduction is
+// split over enough CTAs that every SM pulls its share of W.  Partial sums meet in an fp32 workspace through
+// red.global.add; the CTA that arrives last at a tile's counter applies the epilogue (activation, relu^2 or the second
+// input), writes the bf16 result and leaves workspace and counter zeroed for the next call on the same stream.
+// No CTA waits for another one.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kDecStages = 4;
+constexpr int kDecWBytes = 128 * BK * 2, kDecXBytes = 64 * BK * 2, kDecStageBytes = kDecWBytes + kDecXBytes;
+constexpr int kDecSmemBytes = kDecStages * kDecStageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   float* __restrict__ partial, int ldp, unsigned* __restrict__ counters, __nv_bfloat16* __restrict__ out,
+                   int ldd, const __nv_bfloat16* __restrict__ aux, int ldaux, int M, int N, int K, int kb_per, int splits,
+                   int epi, int act, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecStages * kDecStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kDecStages;
+  uint64_t* tfull_bar = bars + 2 * kDecStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kDecStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (N + 127) / 128;
+  const int tn = blockIdx.x % tiles_n, split = blockIdx.x / tiles_n;
+  const int n0 = tn * 128;
+  const int num_kb = (K + BK - 1) / BK;
+  const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX); }
+  if (warp == 1) { tmem_alloc(tmem_slot, 64); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+        uint8_t* sw = smem + stage * kDecStageBytes;
+        mbar_expect_tx(&full_bar[stage], kDecStageBytes);
+        tma_load_2d(sw, &tmW, &full_bar[stage], kb * BK, n0);
+        tma_load_2d(sw + kDecWBytes, &tmX, &full_bar[stage], kb * BK, 0);
+        if (++stage == kDecStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x60000 | 1); }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 64, 0, 0);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sw = smem_u32(smem + stage * kDecStageBytes);
+        const uint32_t sx = sw + kDecWBytes;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(tmem_base, umma_smem_desc_sw128(sw + k * 32, 16, 1024), umma_smem_desc_sw128(sx + k * 32, 16, 1024),
+                    idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[stage]);
+        if (++stage == kDecStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(tfull_bar);
+      else { *abort_flag = 1; atomicExch(err, 0x60000 | 2); }
+    }
+  } else {
+    // ---- epilogue warps: lane = output channel n, 64 accumulator columns = the activation rows ------------------------
+    const int q = warp & 3;
+    const int n = n0 + q * 32 + lane;
+    bool ok = kb1 > kb0 ? wait_bar(tfull_bar, 0, abort_flag) : true;
+    if (ok && kb1 > kb0) {
+      tc_fence_after();
+      uint32_t v0[32], v1[32];
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16);
+      tmem_ld_32x32(t0, v0);
+      tmem_ld_32x32(t0 + 32, v1);
+      tmem_ld_wait();
+      if (n < N) {
+        float* dst = partial + n;
+#pragma unroll
+        for (int m = 0; m < 32; ++m)
+          if (m < M) asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)m * ldp), "f"(__uint_as_float(v0[m])) : "memory");
+#pragma unroll
+        for (int m = 0; m < 32; ++m)
+          if (32 + m < M) asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)(32 + m) * ldp), "f"(__uint_as_float(v1[m])) : "memory");
+      }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x60000 | 3); }
+    // all four epilogue warps have issued their partial sums: one thread takes a ticket at the tile's counter
+    __threadfence();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == kEpiWarp0 && lane == 0) {
+      const unsigned ticket = atomicAdd(counters + tn, 1u);
+      *last_flag = ticket == (unsigned)(splits - 1) ? 1 : 0;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*last_flag != 0) {
+      __threadfence();
+      if (n < N) {
+        for (int m = 0; m < M; ++m) {
+          float* src = partial + (size_t)m * ldp + n;
+          float x = __ldcg(src);
+          *src = 0.f;
+          if (epi == kEpiReluSqBf16) { x = fmaxf(x, 0.f); x *= x; }
+          else if (epi == kEpiAddBf16) x += bf2f(aux[(size_t)m * ldaux + n]);
+          else if (act != 0) x = act_apply(x, act);
+          out[(size_t)m * ldd + n] = f2bf(x);
+        }
+      }
+      if (warp == kEpiWarp0 && lane == 0) counters[tn] = 0u;
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 64);
+}
+
+int launch_decode(const GemmArgs& p, cudaStream_t st) {
+  alignas(64) CUtensorMap tw;
+  alignas(64) CUtensorMap tx;
+  if (!make_map(&tw, p.B, p.N, p.K, p.ldb, 128)) return 2;
+  if (!make_map(&tx, p.A, p.M, p.K, p.lda, 64)) return 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess)
+      return 3;
+    attr_set = true;
+  }
+  const int tiles_n = (p.N + 127) / 128;
+  const int num_kb = (p.K + BK - 1) / BK;
+  int splits = (2 * sm_count() + tiles_n - 1) / tiles_n;        // two CTAs per SM stream the weights
+  if (splits > num_kb) splits = num_kb;
+  if (splits < 1) splits = 1;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;                        // no empty split
+  gemm_decode_kernel<<<tiles_n * splits, kThreads, kDecSmemBytes, st>>>(
+      tw, tx, p.ws_partial, p.ws_ld, p.ws_counters, reinterpret_cast<__nv_bfloat16*>(p.D), p.ldd,
+      reinterpret_cast<const __nv_bfloat16*>(p.aux), p.ldaux, p.M, p.N, p.K, kb_per, splits, p.epilogue, p.act, p.error_flag);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
   switch (p.layout) {
     case kGemmTN: return launch_pair_epi<0, 0>(p, st);
@@ -762,6 +938,11 @@ int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
 }
 
 }  // namespace
+
+bool gemm_decode_eligible(const GemmArgs& p) {
+  const bool epi_ok = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16 || p.epilogue == kEpiAddBf16;
+  return p.layout == kGemmTN && p.M <= 64 && p.N >= 64 && p.K >= 64 && epi_ok;
+}
 
 int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return 1;
@@ -785,7 +966,9 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   // (with a short reduction the epilogue dominates and two independent CTAs drain their tiles faster: measured 59 vs
   // 72 us at 32768 x 2048 x 128)
   if (p.pair != 0 && p.M >= 256 && p.N >= 256 && p.K >= 512) return launch_pair_layout(p, st);
-  // decode-sized problems (one m-tile): narrow n-tiles so that the weight matrix is streamed by many SMs at once
+  // decode-sized problems: swap-AB split-K kernel when the caller provided its workspace
+  if (gemm_decode_eligible(p) && p.ws_partial != nullptr && p.ws_counters != nullptr && p.ws_ld >= p.N) return launch_decode(p, st);
+  // otherwise (one m-tile): narrow n-tiles so that the weight matrix is streamed by many SMs at once
   if (p.layout == kGemmTN && p.M <= BM && p.N >= 1024) return launch_epi<32, 0, 0>(p, st);
   if (p.N > 128) return launch_layout<256>(p, st);
   return launch_layout<128>(p, st);

@@ -89,6 +89,10 @@ void gn_bonus_gate_fwd(const void* const* in, const float* const* par, void* out
 void gn_bonus_gate_bwd(const void* const* in, const float* const* par, const void* dout, void* const* gin,
                        float* const* gpar_part, int M, int C, float eps, cudaStream_t st);
 void relusq_bwd(const void* dh, const void* h, void* out, int64_t n, cudaStream_t st);
+// Embedding row gather (bf16 output; table bf16 or fp32, C a multiple of 8) and the scatter-add of bf16 output-gradient
+// rows into the fp32 table gradient.
+void embedding_fwd(const int* ids, const void* table, bool table_bf16, void* out, int M, int C, int V, cudaStream_t st);
+void embedding_bwd(const int* ids, const void* dout, float* grad, int M, int C, int V, cudaStream_t st);
 
 // ---- loss ---------------------------------------------------------------------------
 void ce_fwd(const void* logits, const int* targets, float* lse, float* maxv, int* argmax, float* nll, int rows, int V,
@@ -141,6 +145,8 @@ struct ScreenScanArgs {
   const float* mu;              // [M] per-slot write rate
   const float *slots0, *ages0, *usage0;   // [B,M,ds], [B,M], [B,M]
   float tau_r, tau_w, eps, cap, write_rel_floor, usage_decay, age_ref, age_sigma;
+  const float* tau_dev;         // [2] tau_r, tau_w on the device; when set it replaces the two host values above, so the
+                                // learned thresholds never have to be read back to the host
   bool write_enabled, value_unit_norm, age_mask;
   // forward outputs
   float* u_out;                 // [B,T,dv]
@@ -200,12 +206,19 @@ struct GemmArgs {
   const void* A; const void* B; void* D;
   const void* aux;     // bf16 [M, N] second epilogue input (kEpiMulSqrt2Bf16, kEpiAddBf16), row pitch ldaux
   int ldaux;
+  int act;             // kEpiStoreBf16: 0 = none, 1 = tanh, 2 = sigmoid applied to the result;
+                       // kEpiMulSqrt2Bf16: factor 2 sqrt(aux) (0), 1 - aux^2 (1), aux (1 - aux) (2)
   int M, N, K;
   int lda, ldb, ldd;   // leading dimensions in elements of the stored matrices
   int layout, epilogue;
   int pair;            // non-zero: use the CTA-pair (cta_group::2) kernel when the shape allows
   int* error_flag;     // device int, set non-zero if a bounded wait ran out
+  // Workspace of the decode-sized kernel (M <= 64, layout kGemmTN): fp32 [64, ws_ld] partial sums and one counter per
+  // 128 output channels, both zero on entry and left zero on exit; calls that share a workspace must be ordered by
+  // their stream.  Without it such shapes take the general kernel.
+  float* ws_partial; unsigned* ws_counters; int ws_ld;
 };
 int gemm_bf16(const GemmArgs& p, cudaStream_t st);
+bool gemm_decode_eligible(const GemmArgs& p);
 
 }  // namespace rk

@@ -135,6 +135,7 @@ __device__ __forceinline__ void slot_scalars(const ScanSmem& s, const ScreenScan
 template <bool SMEM_W>
 __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
+  if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
   const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x;
@@ -301,6 +302,7 @@ __host__ __device__ inline int scan_bwd_smem_floats(int ds, int dk, int dv) {
 template <bool SMEM_W>
 __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
+  if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
   const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
   float* extra = smem_f + scan_smem_floats(a.ds, a.dk, a.dv);
   float* dSt = extra; extra += a.ds * kMp;      // [ds][16] cotangent of the bank after the current step

@@ -24,6 +24,10 @@ WKV_CHECKPOINT_INTERVAL = 16
 GEMM_TN, GEMM_NN, GEMM_WGRAD = 0, 1, 2
 EPI_BF16, EPI_RELUSQ, EPI_F32, EPI_ACC_F32 = 0, 1, 2, 3
 EPI_MUL2SQRT, EPI_ADD = 5, 6   # two-input epilogues: acc * 2 sqrt(aux), acc + aux
+# activation selector: with EPI_BF16 the result goes through tanh / sigmoid; with EPI_MUL2SQRT the factor becomes the
+# derivative of that activation written through its saved output (1 - aux^2, aux (1 - aux))
+ACT_NONE, ACT_TANH, ACT_SIGMOID = 0, 1, 2
+_ACT = {"none": ACT_NONE, "tanh": ACT_TANH, "sigmoid": ACT_SIGMOID}
 
 # "tcgen05" = this package's GEMM kernel (product path);
 # "cublas"  = torch.matmul, kept only so benchmarks can report the library baseline.
@@ -113,10 +117,10 @@ def set_gemm_pair(enabled: bool):
     GEMM_PAIR = bool(enabled)
 
 
-def gemm(a, b, out, layout, epilogue, pair=None, aux=None):
+def gemm(a, b, out, layout, epilogue, pair=None, aux=None, act=ACT_NONE):
     """Raw GEMM launcher: see csrc/kernels.h for layouts.  ``aux`` is the second epilogue input of
-    ``EPI_MUL2SQRT`` / ``EPI_ADD`` (bf16, shape of ``out``).  Returns ``out``."""
-    _C.gemm(a, b, out, layout, epilogue, int(GEMM_PAIR if pair is None else pair), aux)
+    ``EPI_MUL2SQRT`` / ``EPI_ADD`` (bf16, shape of ``out``), ``act`` the activation selector.  Returns ``out``."""
+    _C.gemm(a, b, out, layout, epilogue, int(GEMM_PAIR if pair is None else pair), aux, int(act))
     _count()
     return out
 
@@ -383,25 +387,41 @@ def _bf16(x):
 
 
 class EmbeddingFn(torch.autograd.Function):
-    """Row gather from the bf16 shadow of the table; backward scatters into the fp32 main gradient."""
+    """Row gather from the bf16 shadow of the table (csrc/elementwise.cu: embedding_fwd_kernel); backward scatter-adds
+    the output-gradient rows into the fp32 main gradient (embedding_bwd_kernel, vector reductions)."""
 
     @staticmethod
     def forward(ctx, ids, weight, dtype):
         src = getattr(weight, "_compute", None)
         if src is None or src.dtype != dtype:
             src = weight.detach()
-        out = torch.nn.functional.embedding(ids.long(), src)
+        ids32 = ids.to(torch.int32).contiguous()
+        kernel = (dtype == torch.bfloat16 and src.is_cuda and src.is_contiguous() and src.shape[1] % 8 == 0
+                  and src.dtype in (torch.bfloat16, torch.float32))
+        if kernel:
+            out = _C.embedding_fwd(ids32, src)
+            _count()
+        else:
+            out = torch.nn.functional.embedding(ids.long(), src)
+            out = out if out.dtype == dtype else out.to(dtype)
         ctx.weight = weight
-        ctx.save_for_backward(ids)
-        return out if out.dtype == dtype else out.to(dtype)
+        ctx.kernel = kernel
+        ctx.save_for_backward(ids32)
+        return out
 
     @staticmethod
     def backward(ctx, dout):
         (ids,) = ctx.saved_tensors
         w = ctx.weight
         main = getattr(w, "_main_grad", None)
-        flat_ids = ids.reshape(-1).long()
         d2 = dout.reshape(-1, dout.shape[-1])
+        if ctx.kernel and d2.dtype == torch.bfloat16:
+            acc = main if (main is not None and main.dtype == torch.float32 and main.is_contiguous()) else \
+                torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            _C.embedding_bwd(ids.reshape(-1), d2.contiguous(), acc)
+            _count()
+            return None, (None if acc is main else acc.to(w.dtype)), None
+        flat_ids = ids.reshape(-1).long()
         if main is not None:
             main.index_add_(0, flat_ids, d2.to(main.dtype))
             return None, None, None
@@ -494,13 +514,55 @@ def shift_mix(x, prev, mix):
     return R.shift_mix(x, prev, mix)
 
 
+class LoraFn(torch.autograd.Function):
+    """Low-rank pair in one autograd node: h = act(x D^T), y = h U^T (``down`` = D [rank, C], ``up`` = U [C_out, rank]).
+
+    The activation (tanh for the decay branch, sigmoid for the gate, none for the others) is applied in the epilogue of
+    the down-projection GEMM; in backward the GEMM that forms dh = dy U multiplies by the activation's derivative,
+    written through the saved h, in its epilogue.  No elementwise pass touches the [tokens, rank] tensors
+    (reference: src/rwkv7m/model/nnx_model.py:616-682)."""
+
+    @staticmethod
+    def forward(ctx, x, down, up, act):
+        dc, uc = _compute_weight(down), _compute_weight(up)
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        h = torch.empty(M, dc.shape[0], dtype=torch.bfloat16, device=x.device)
+        gemm(x2, dc, h, GEMM_TN, EPI_BF16, act=act)
+        y = torch.empty(M, uc.shape[0], dtype=torch.bfloat16, device=x.device)
+        gemm(h, uc, y, GEMM_TN, EPI_BF16)
+        ctx.down, ctx.up, ctx.act, ctx.x_shape = down, up, act, x.shape
+        ctx.save_for_backward(x2, dc, uc, h)
+        return y.view(*x.shape[:-1], uc.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, dc, uc, h = ctx.saved_tensors
+        d2 = dy.reshape(-1, uc.shape[0])
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dup = _wgrad(d2, h, ctx.up) if ctx.needs_input_grad[2] else None
+        dpre = torch.empty_like(h)
+        if ctx.act == ACT_NONE:
+            gemm(d2, uc, dpre, GEMM_NN, EPI_BF16)
+        else:
+            gemm(d2, uc, dpre, GEMM_NN, EPI_MUL2SQRT, aux=h, act=ctx.act)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(x2.shape[0], x2.shape[1], dtype=torch.bfloat16, device=dy.device)
+            gemm(dpre, dc, dx, GEMM_NN, EPI_BF16)
+            dx = dx.view(ctx.x_shape)
+        ddown = _wgrad(dpre, x2, ctx.down) if ctx.needs_input_grad[1] else None
+        return dx, ddown, dup, None
+
+
 def lora(x, down, up, mid="none"):
-    h = linear(x, down)
-    if mid == "tanh":
-        h = torch.tanh(h)
-    elif mid == "sigmoid":
-        h = torch.sigmoid(h)
-    return linear(h, up)
+    if _fused_linear_ok(x, down, up):
+        return LoraFn.apply(x, down, up, _ACT[mid])
+    return R.lora(x, down, up, mid=mid)
 
 
 class TmixPreFn(torch.autograd.Function):
@@ -696,16 +758,18 @@ class ScreenScanFn(torch.autograd.Function):
         W = torch.cat([f32(w_kr), f32(w_v), f32(w_kw)], dim=0).contiguous()
         WT = W.t().contiguous()
         dk, dv = w_kr.shape[0], w_v.shape[0]
-        floats = [float(tau_r), float(tau_w), settings["eps"], settings["cap"], settings["floor"],
+        # the learned thresholds stay on the device (two floats read by the kernels): no host synchronisation
+        tau = torch.stack([tau_r.detach().float().reshape(()), tau_w.detach().float().reshape(())]).contiguous()
+        floats = [0.0, 0.0, settings["eps"], settings["cap"], settings["floor"],
                   settings["usage_decay"], settings["age_ref"], settings["age_sigma"]]
         flags = (bool(settings["write_enabled"]), bool(settings["value_unit_norm"]), bool(settings["age_mask"]))
         dxh32, dds32, E32 = f32(delta_xh), f32(delta_slot), f32(slot_embed)
         _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv)
         tensors = [f32(q_r), f32(q_w), dxh32, dds32, E32, WT, PD, f32(mu), f32(slots0), f32(ages0), f32(usage0)]
         need_grad = any(ctx.needs_input_grad)
-        u, so, ao, uo, stats, saved, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad)
+        u, so, ao, uo, stats, saved, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad, tau)
         _count()
-        ctx.floats, ctx.flags = floats, flags
+        ctx.floats, ctx.flags, ctx.tau = floats, flags, tau
         ctx.dk, ctx.dv, ctx.M = dk, dv, slots0.shape[1]
         ctx.dtypes = [t.dtype for t in (q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, slots0)]
         if need_grad:
@@ -717,7 +781,7 @@ class ScreenScanFn(torch.autograd.Function):
     def backward(ctx, du, dso, *_):
         *tensors, W, saved, saved_ages, saved_P = ctx.saved_tensors
         dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0 = _C.screen_scan_bwd(
-            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, saved_P, du.float().contiguous(), dso)
+            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, saved_P, du.float().contiguous(), dso, ctx.tau)
         _count()
         delta_xh, delta_slot, slot_embed, slots0 = tensors[2], tensors[3], tensors[4], tensors[8]
         dk, dv, M = ctx.dk, ctx.dv, ctx.M

@@ -184,3 +184,24 @@ def test_layer_norm_residual_sums_both_gradients_in_the_kernel():
         assert rel(h, href) < 1e-2
         assert rel(x.grad, xr.grad) < 1e-2
         assert rel(w.grad, wr.grad) < 1e-2 and rel(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("table_dtype", [torch.bfloat16, torch.float32])
+def test_embedding_kernels_match_torch(table_dtype):
+    """Gather and scatter-add kernels of the embedding against torch, with repeated ids."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    C = load_extension()
+    g = torch.Generator().manual_seed(0)
+    V, W, B, T = 1000, 256, 3, 50
+    table = torch.randn(V, W, generator=g).cuda().to(table_dtype)
+    ids = torch.randint(0, 40, (B, T), generator=g).to(torch.int32).cuda()      # few distinct ids: many collisions
+    out = C.embedding_fwd(ids, table)
+    want = torch.nn.functional.embedding(ids.long(), table).bfloat16()
+    assert out.shape == (B, T, W) and torch.equal(out, want)
+    dout = torch.randn(B, T, W, generator=g).cuda().bfloat16()
+    grad = torch.ones(V, W, device="cuda")
+    for _ in range(2):
+        C.embedding_bwd(ids.reshape(-1), dout.reshape(-1, W), grad)
+    ref = torch.ones(V, W, device="cuda").index_add_(0, ids.reshape(-1).long(), 2 * dout.reshape(-1, W).float())
+    assert torch.allclose(grad, ref, atol=1e-4, rtol=1e-5)

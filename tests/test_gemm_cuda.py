@@ -167,3 +167,70 @@ def test_ffn_and_linear_add_functions_match_autograd():
     for a, b in zip(got2, want2):
         assert close(a, b, 2e-2)
     assert kk.gemm_error_code(x) == 0
+
+
+@pytest.mark.parametrize("mid", ["none", "tanh", "sigmoid"])
+def test_lora_pair_with_activation_epilogues(mid):
+    """The low-rank pair as one autograd node: activation in the down-projection's epilogue, its derivative in the
+    epilogue of the GEMM that forms dh.  Forward and all three gradients against the fp32 PyTorch statement."""
+    from rwkv7m_b200 import ops
+    from rwkv7m_b200.ops import cuda as kk
+    from rwkv7m_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(4)
+    M, C, rank = 640, 256, 96
+    x = (torch.randn(2, M // 2, C, generator=g) * 0.7).cuda().bfloat16()
+    down = (torch.randn(rank, C, generator=g) * 0.08).cuda().bfloat16()
+    up = (torch.randn(C, rank, generator=g) * 0.1).cuda().bfloat16()
+    dy = torch.randn(2, M // 2, C, generator=g).cuda().bfloat16()
+
+    def run(fn, cast):
+        leaves = [cast(t).clone().requires_grad_(True) for t in (x, down, up)]
+        y = fn(*leaves, mid=mid)
+        (y.float() * dy.float()).sum().backward()
+        return [y.detach().float()] + [l.grad.float() for l in leaves]
+
+    before = kk.LAUNCH_COUNT
+    got = run(ops.lora, lambda t: t)
+    assert kk.LAUNCH_COUNT - before == 6          # two forward GEMMs, four backward GEMMs, no elementwise pass
+    want = run(lambda a, b, c, mid: R.lora(a, b, c, mid=mid), lambda t: t.float())
+    for name, a, b in zip("y dx ddown dup".split(), got, want):
+        rel = float((a - b).norm() / (b.norm() + 1e-9))
+        assert rel < 1.5e-2, (mid, name, rel)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 2048, 2048), (64, 8192, 2048), (64, 2048, 8192), (17, 96, 256), (64, 320, 160), (1, 4096, 2048)])
+@pytest.mark.parametrize("epi", ["bf16", "relusq", "add", "tanh"])
+def test_decode_sized_gemm_matches_fp32(M, N, K, epi):
+    """The swap-AB split-K kernel for M <= 64 (weights streamed once by all SMs, partial sums met in an fp32 workspace,
+    last CTA per tile finishes): every epilogue, ragged sizes, twice in a row on the same workspace."""
+    from rwkv7m_b200.ops import cuda as kk
+
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) * 0.5).cuda().bfloat16()
+    w = (torch.randn(N, K, generator=g) * (1.0 / K ** 0.5)).cuda().bfloat16()
+    aux = torch.randn(M, N, generator=g).cuda().bfloat16() if epi == "add" else None
+    ref = x.float() @ w.float().t()
+    if epi == "relusq":
+        ref = torch.relu(ref) ** 2
+    elif epi == "add":
+        ref = ref + aux.float()
+    elif epi == "tanh":
+        ref = torch.tanh(ref)
+    code = {"bf16": kk.EPI_BF16, "relusq": kk.EPI_RELUSQ, "add": kk.EPI_ADD, "tanh": kk.EPI_BF16}[epi]
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        kk.gemm(x, w, out, kk.GEMM_TN, code, aux=aux, act=kk.ACT_TANH if epi == "tanh" else kk.ACT_NONE)
+        torch.cuda.synchronize()
+        assert kk.gemm_error_code(x) == 0
+        err = float((out.float() - ref).abs().max())
+        assert err < 2e-2 * max(1.0, float(ref.abs().max())), err
+    # the general kernel gives the same result when the decode kernel is switched off
+    kk._C.set_decode_gemm(False)
+    try:
+        out2 = torch.empty_like(out)
+        kk.gemm(x, w, out2, kk.GEMM_TN, code, aux=aux, act=kk.ACT_TANH if epi == "tanh" else kk.ACT_NONE)
+        torch.cuda.synchronize()
+    finally:
+        kk._C.set_decode_gemm(True)
+    assert float((out.float() - out2.float()).abs().max()) < 2e-2 * max(1.0, float(ref.abs().max()))
