@@ -150,27 +150,8 @@ Tensor& gemm_error_flag(const at::Device& dev) {
   return f;
 }
 
-// Workspace of the decode-sized GEMM (fp32 partial sums [64, cols] + one counter per 128 columns), one per device and
-// stream: calls on one stream are ordered and leave it zeroed, calls on different streams (the parallel projection
-// branches of a decode step) must not share it.  Allocated and zeroed on first use, regrown when a wider output comes.
 static bool g_decode_gemm = true;
-static bool decode_gemm_enabled() { return g_decode_gemm; }
 void set_decode_gemm(bool on) { g_decode_gemm = on; }
-struct DecodeWorkspace { Tensor partial, counters; int64_t cols = 0; };
-static DecodeWorkspace& decode_workspace(const c10::Device& dev, cudaStream_t st, int64_t n_cols) {
-  static std::mutex mu;
-  static std::map<std::pair<int, uintptr_t>, DecodeWorkspace> cache;
-  std::lock_guard<std::mutex> g(mu);
-  DecodeWorkspace& w = cache[{(int)dev.index(), reinterpret_cast<uintptr_t>(st)}];
-  if (w.cols < n_cols) {
-    const int64_t cols = std::max<int64_t>((n_cols + 127) / 128 * 128, 8192);
-    auto o = torch::TensorOptions().device(dev);
-    w.partial = torch::zeros({64, cols}, o.dtype(at::kFloat));
-    w.counters = torch::zeros({cols / 128}, o.dtype(at::kInt));
-    w.cols = cols;
-  }
-  return w;
-}
 
 // D = op(A) op(B); see kernels.h for the three layouts.  D must be preallocated.
 void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t epilogue, int64_t pair,
@@ -214,12 +195,7 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   if (trace) { fprintf(stderr, "[gemm-bind] checks ok\n"); fflush(stderr); }
   p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();
   if (trace) { fprintf(stderr, "[gemm-bind] flag ok\n"); fflush(stderr); }
-  if (decode_gemm_enabled() && rk::gemm_decode_eligible(p)) {
-    DecodeWorkspace& w = decode_workspace(A.device(), stream(), p.N);
-    p.ws_partial = w.partial.data_ptr<float>();
-    p.ws_counters = reinterpret_cast<unsigned*>(w.counters.data_ptr<int>());
-    p.ws_ld = (int)w.cols;
-  }
+  p.decode_kernel = g_decode_gemm ? 1 : 0;
   const int rc = rk::gemm_bf16(p, stream());
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
 }

@@ -771,22 +771,31 @@ int launch_pair_epi(const GemmArgs& p, cudaStream_t st) {
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Decode-sized GEMM: y[M <= 64, N] = x[M, K] W[N, K]^T, the shape of every projection of a T = 1 serving step.  The work
-// is streaming the weight matrix once, so the roles of the operands are swapped: a CTA takes 128 rows of W as the
-// 128-row tensor-core operand and the (zero-padded) 64 activation rows as the 64-column operand, and the reduction is
-// split over enough CTAs that every SM pulls its share of W.  Partial sums meet in an fp32 workspace through
-// red.global.add; the CTA that arrives last at a tile's counter applies the epilogue (activation, relu^2 or the second
-// input), writes the bf16 result and leaves workspace and counter zeroed for the next call on the same stream.
-// No CTA waits for another one.
+// is streaming the weight matrix once, and with one m-tile a long reduction is a serial chain of dependent MMAs, so the
+// roles of the operands are swapped and the reduction is split: a CTA takes 128 rows of W as the 128-row tensor-core
+// operand, the (zero-padded) 64 activation rows as the 64-column operand and one slice of K; the CTAs that share an
+// n-tile form a thread-block cluster (up to 8) and meet their partial sums through distributed shared memory: every
+// CTA parks its fp32 tile in its own shared memory, and after a cluster barrier CTA r sums rows [r 64/S, (r+1) 64/S)
+// over all members, applies the epilogue (activation, relu^2 or the second input) and writes bf16.  No global
+// workspace, no atomics, and no CTA spins on another one (cluster barriers are hardware barriers between co-scheduled
+// CTAs).
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kDecStages = 4;
 constexpr int kDecWBytes = 128 * BK * 2, kDecXBytes = 64 * BK * 2, kDecStageBytes = kDecWBytes + kDecXBytes;
 constexpr int kDecSmemBytes = kDecStages * kDecStageBytes + 1024 + 256;
+constexpr int kDecRStride = 132;   // floats per activation row of the parked tile [64][128]
+static_assert(64 * kDecRStride * 4 <= kDecStages * kDecStageBytes, "the parked tile reuses the pipeline stages");
+
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                   float* __restrict__ partial, int ldp, unsigned* __restrict__ counters, __nv_bfloat16* __restrict__ out,
-                   int ldd, const __nv_bfloat16* __restrict__ aux, int ldaux, int M, int N, int K, int kb_per, int splits,
-                   int epi, int act, int* __restrict__ err) {
+                   __nv_bfloat16* __restrict__ out, int ldd, const __nv_bfloat16* __restrict__ aux, int ldaux, int M, int N,
+                   int K, int kb_per, int splits, int epi, int act, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecStages * kDecStageBytes);
@@ -795,10 +804,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* tfull_bar = bars + 2 * kDecStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kDecStages + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  float* R = reinterpret_cast<float*>(smem);     // parked partial tile, valid once this CTA's MMAs have completed
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (N + 127) / 128;
-  const int tn = blockIdx.x % tiles_n, split = blockIdx.x / tiles_n;
+  const int tn = blockIdx.x / splits, split = blockIdx.x - tn * splits;   // consecutive CTAs = one cluster = one n-tile
   const int n0 = tn * 128;
   const int num_kb = (K + BK - 1) / BK;
   const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
@@ -807,7 +815,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     for (int s = 0; s < kDecStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(tfull_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     mbar_fence_init();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX); }
@@ -852,55 +859,58 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       else { *abort_flag = 1; atomicExch(err, 0x60000 | 2); }
     }
   } else {
-    // ---- epilogue warps: lane = output channel n, 64 accumulator columns = the activation rows ------------------------
+    // ---- epilogue warps: lane = output channel, 64 accumulator columns = the activation rows; park the tile ----------------
     const int q = warp & 3;
-    const int n = n0 + q * 32 + lane;
-    bool ok = kb1 > kb0 ? wait_bar(tfull_bar, 0, abort_flag) : true;
-    if (ok && kb1 > kb0) {
+    const int nl = q * 32 + lane;
+    const bool ok = wait_bar(tfull_bar, 0, abort_flag);
+    uint32_t v0[32], v1[32];
+    if (ok) {
       tc_fence_after();
-      uint32_t v0[32], v1[32];
       const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16);
       tmem_ld_32x32(t0, v0);
       tmem_ld_32x32(t0 + 32, v1);
       tmem_ld_wait();
-      if (n < N) {
-        float* dst = partial + n;
+    } else {
+      if (lane == 0) { *abort_flag = 1; atomicExch(err, 0x60000 | 3); }
 #pragma unroll
-        for (int m = 0; m < 32; ++m)
-          if (m < M) asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)m * ldp), "f"(__uint_as_float(v0[m])) : "memory");
+      for (int m = 0; m < 32; ++m) { v0[m] = 0u; v1[m] = 0u; }
+    }
+    // every MMA of this CTA has completed (or was given up), so the pipeline stages are free to hold the tile
 #pragma unroll
-        for (int m = 0; m < 32; ++m)
-          if (32 + m < M) asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)(32 + m) * ldp), "f"(__uint_as_float(v1[m])) : "memory");
-      }
-    }
-    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x60000 | 3); }
-    // all four epilogue warps have issued their partial sums: one thread takes a ticket at the tile's counter
-    __threadfence();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (warp == kEpiWarp0 && lane == 0) {
-      const unsigned ticket = atomicAdd(counters + tn, 1u);
-      *last_flag = ticket == (unsigned)(splits - 1) ? 1 : 0;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (*last_flag != 0) {
-      __threadfence();
-      if (n < N) {
-        for (int m = 0; m < M; ++m) {
-          float* src = partial + (size_t)m * ldp + n;
-          float x = __ldcg(src);
-          *src = 0.f;
-          if (epi == kEpiReluSqBf16) { x = fmaxf(x, 0.f); x *= x; }
-          else if (epi == kEpiAddBf16) x += bf2f(aux[(size_t)m * ldaux + n]);
-          else if (act != 0) x = act_apply(x, act);
-          out[(size_t)m * ldd + n] = f2bf(x);
-        }
-      }
-      if (warp == kEpiWarp0 && lane == 0) counters[tn] = 0u;
-    }
+    for (int m = 0; m < 32; ++m) { R[m * kDecRStride + nl] = __uint_as_float(v0[m]); R[(32 + m) * kDecRStride + nl] = __uint_as_float(v1[m]); }
   }
-  __syncwarp();
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();                                   // every member's tile is parked and visible
+  if (warp >= kEpiWarp0) {
+    const int nl = (warp & 3) * 32 + lane, n = n0 + nl;
+    const int rows = 64 / splits, m_lo = split * rows;
+    const uint32_t my = smem_u32(R);
+    // four rows at a time, every member's values requested before the first one is used: the latency of a remote
+    // shared-memory read is paid once per group, not once per element
+#pragma unroll 1
+    for (int mb = m_lo; mb < m_lo + rows && mb < M; mb += 4) {
+      float part[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[j][r] = (r < splits && mb + j < m_lo + rows)
+                           ? ld_cluster_f32(map_to_cta(my + (uint32_t)((mb + j) * kDecRStride + nl) * 4u, (uint32_t)r)) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int m = mb + j;
+        float acc = ((part[j][0] + part[j][1]) + (part[j][2] + part[j][3])) + ((part[j][4] + part[j][5]) + (part[j][6] + part[j][7]));
+        if (n < N && m < M && m < m_lo + rows) {
+          if (epi == kEpiReluSqBf16) { acc = fmaxf(acc, 0.f); acc *= acc; }
+          else if (epi == kEpiAddBf16) acc += bf2f(aux[(size_t)m * ldaux + n]);
+          else if (act != 0) acc = act_apply(acc, act);
+          out[(size_t)m * ldd + n] = f2bf(acc);
+        }
+      }
+    }
+  }
+  cluster_sync_all();                                   // nobody leaves while a peer may still read its tile
   if (warp == 1) tmem_dealloc(tmem_base, 64);
 }
 
@@ -917,15 +927,26 @@ int launch_decode(const GemmArgs& p, cudaStream_t st) {
   }
   const int tiles_n = (p.N + 127) / 128;
   const int num_kb = (p.K + BK - 1) / BK;
-  int splits = (2 * sm_count() + tiles_n - 1) / tiles_n;        // two CTAs per SM stream the weights
-  if (splits > num_kb) splits = num_kb;
-  if (splits < 1) splits = 1;
+  // cluster size = K slices per n-tile: a power of two up to 8, enough that about every SM streams part of W
+  int splits = 1;
+  while (splits < 8 && tiles_n * splits < sm_count() && 2 * splits <= num_kb) splits *= 2;
   const int kb_per = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kb_per - 1) / kb_per;                        // no empty split
-  gemm_decode_kernel<<<tiles_n * splits, kThreads, kDecSmemBytes, st>>>(
-      tw, tx, p.ws_partial, p.ws_ld, p.ws_counters, reinterpret_cast<__nv_bfloat16*>(p.D), p.ldd,
-      reinterpret_cast<const __nv_bfloat16*>(p.aux), p.ldaux, p.M, p.N, p.K, kb_per, splits, p.epilogue, p.act, p.error_flag);
-  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+  if ((splits - 1) * kb_per >= num_kb) return -1;   // a member would get no k-block: let the general kernel run
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles_n * splits, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kDecSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D);
+  const __nv_bfloat16* aux = reinterpret_cast<const __nv_bfloat16*>(p.aux);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel, tw, tx, out, p.ldd, aux, p.ldaux, p.M, p.N, p.K, kb_per,
+                                           splits, p.epilogue, p.act, p.error_flag);
+  return e == cudaSuccess ? 0 : 4;
 }
 
 int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
@@ -941,7 +962,9 @@ int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
 
 bool gemm_decode_eligible(const GemmArgs& p) {
   const bool epi_ok = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16 || p.epilogue == kEpiAddBf16;
-  return p.layout == kGemmTN && p.M <= 64 && p.N >= 64 && p.K >= 64 && epi_ok;
+  // with a short reduction (the up-projection of a low-rank pair) there is no chain of dependent MMAs to split and the
+  // general kernel's single pass is faster (measured 3.8 against 7 us at K = 128)
+  return p.layout == kGemmTN && p.M <= 64 && p.N >= 64 && p.K >= 512 && epi_ok;
 }
 
 int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
@@ -967,7 +990,10 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
   // 72 us at 32768 x 2048 x 128)
   if (p.pair != 0 && p.M >= 256 && p.N >= 256 && p.K >= 512) return launch_pair_layout(p, st);
   // decode-sized problems: swap-AB split-K kernel when the caller provided its workspace
-  if (gemm_decode_eligible(p) && p.ws_partial != nullptr && p.ws_counters != nullptr && p.ws_ld >= p.N) return launch_decode(p, st);
+  if (p.decode_kernel != 0 && gemm_decode_eligible(p)) {
+    const int rc = launch_decode(p, st);
+    if (rc >= 0) return rc;
+  }
   // otherwise (one m-tile): narrow n-tiles so that the weight matrix is streamed by many SMs at once
   if (p.layout == kGemmTN && p.M <= BM && p.N >= 1024) return launch_epi<32, 0, 0>(p, st);
   if (p.N > 128) return launch_layout<256>(p, st);

@@ -213,10 +213,7 @@ struct GemmArgs {
   int layout, epilogue;
   int pair;            // non-zero: use the CTA-pair (cta_group::2) kernel when the shape allows
   int* error_flag;     // device int, set non-zero if a bounded wait ran out
-  // Workspace of the decode-sized kernel (M <= 64, layout kGemmTN): fp32 [64, ws_ld] partial sums and one counter per
-  // 128 output channels, both zero on entry and left zero on exit; calls that share a workspace must be ordered by
-  // their stream.  Without it such shapes take the general kernel.
-  float* ws_partial; unsigned* ws_counters; int ws_ld;
+  int decode_kernel;   // non-zero: shapes with M <= 64 (layout kGemmTN) take the swap-AB cluster split-K kernel
 };
 int gemm_bf16(const GemmArgs& p, cudaStream_t st);
 bool gemm_decode_eligible(const GemmArgs& p);
