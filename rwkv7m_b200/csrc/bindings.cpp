@@ -74,7 +74,8 @@ std::vector<Tensor> wkv7_fwd(const Tensor& r, const Tensor& w, const Tensor& k, 
 
 std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, const Tensor& v, const Tensor& a,
                              const Tensor& b, const Tensor& s0, const Tensor& sa, const Tensor& ckpt,
-                             const Tensor& dy, const c10::optional<Tensor>& dsT, int64_t interval, bool chunked) {
+                             const Tensor& dy, const c10::optional<Tensor>& dsT, int64_t interval, bool chunked,
+                             const c10::optional<std::vector<Tensor>>& add) {
   c10::cuda::CUDAGuard guard(r.device());
   rk::WkvArgs p = wkv_args(r, w, k, v, a, b, s0, interval);
   check_vec(dy, r, "dy");
@@ -98,6 +99,11 @@ std::vector<Tensor> wkv7_bwd(const Tensor& r, const Tensor& w, const Tensor& k, 
   }
   p.dr = dr.data_ptr(); p.dw = dw.data_ptr(); p.dk = dk.data_ptr(); p.dv = dv.data_ptr();
   p.da = da.data_ptr(); p.db = db.data_ptr(); p.ds0 = ds0.data_ptr<float>();
+  if (add.has_value() && !add->empty()) {
+    TORCH_CHECK(use_chunk && add->size() == 3, "gradients to add go with the chunked backward, as (dr, dk, dv)");
+    for (const Tensor& t : *add) check_vec(t, r, "add");
+    p.dr_add = (*add)[0].data_ptr(); p.dk_add = (*add)[1].data_ptr(); p.dv_add = (*add)[2].data_ptr();
+  }
   if (use_chunk) {
     TORCH_CHECK(rk::wkv7_chunk_backward(p, stream()) == 0, "wkv7_chunk_backward: launch failed");
   } else {
@@ -746,7 +752,9 @@ int64_t dp_aux_words() { return rk::dp_aux_words(); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wkv7_fwd", &wkv7_fwd);
-  m.def("wkv7_bwd", &wkv7_bwd);
+  m.def("wkv7_bwd", &wkv7_bwd, py::arg("r"), py::arg("w"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"),
+        py::arg("s0"), py::arg("sa"), py::arg("ckpt"), py::arg("dy"), py::arg("dsT"), py::arg("interval"), py::arg("chunked"),
+        py::arg("add") = py::none());
   m.def("wkv7_chunk_error", [](bool reset) { return rk::wkv7_chunk_error(reset) | rk::wkv7_chunk_bwd_error(reset); });
 #ifdef RK_WKV_PROF
   m.def("wkv7_chunk_bwd_prof", [](bool reset) {

@@ -25,6 +25,9 @@ struct WkvArgs {
   const float* dsT;                     // may be nullptr
   void *dr, *dw, *dk, *dv, *da, *db;
   float* ds0;
+  // chunked backward only, all three or none: bf16 [B,T,H,N] gradients that reach r, k and v through another consumer of
+  // the same tensors (the bonus term of the output normalisation); the kernel adds them to dr, dk, dv as it writes them
+  const void *dr_add, *dk_add, *dv_add;
 };
 int wkv7_forward(const WkvArgs& p, cudaStream_t st);
 int wkv7_backward(const WkvArgs& p, cudaStream_t st);

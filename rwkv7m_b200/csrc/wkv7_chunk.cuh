@@ -67,7 +67,8 @@ __device__ __forceinline__ void cp_async_wait_all() {
 //        holds the inverse (unit diagonal, zeros above it).
 // work:  kInvWorkFloats floats of scratch.
 // tile:  receives the inverse as bf16 in the 128-byte-swizzled [64][64] operand layout (row = t, column = s).
-// All 256 threads of the CTA must call it; it ends with every thread's stores issued but not yet fenced.
+// Every thread of the CTA must call it (the barriers inside are CTA-wide); threads 0..255 do the work, any further
+// warps only take part in the barriers.  It ends with every thread's stores issued but not yet fenced.
 constexpr int kInvStride = 68;
 constexpr int kInvTmStride = 40;   // row stride of the product scratch: 16-byte aligned rows, conflict-free B fragments
 constexpr int kInvWorkFloats = 4 * 256 + 32 * kInvTmStride;
@@ -115,7 +116,10 @@ __device__ __forceinline__ void unit_lower_inverse_64(float* F, float* work, uin
     for (int r = 0; r < 16; ++r) D[blk * 256 + r * 16 + j] = x[r];
   }
   __syncthreads();
-  if (warp < 4) {   // level 1a: Tm[p] = A(2p+1, 2p) X(2p, 2p), one 16 x 8 tile per warp
+  const bool worker = tid < 256;
+  if (!worker) {
+    // no role at levels 1 and 2: fall through to the barriers
+  } else if (warp < 4) {   // level 1a: Tm[p] = A(2p+1, 2p) X(2p, 2p), one 16 x 8 tile per warp
     const int p = warp >> 1, n0 = (warp & 1) * 8;
     float c[4];
     mma_tile_tf32<2>(F + (32 * p + 16) * kInvStride + 32 * p, kInvStride, D + (2 * p) * 256 + n0, 16, c, lane);
@@ -140,8 +144,8 @@ __device__ __forceinline__ void unit_lower_inverse_64(float* F, float* work, uin
     *reinterpret_cast<float2*>(dst + (g + 8) * kInvStride) = make_float2(c[2], c[3]);
   }
   __syncthreads();
-  const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 8;   // level 2: 32 x 32 outputs, one 16 x 8 tile per warp
-  {   // level 2a: Tm = A(32:64, 0:32) X(0:32, 0:32)
+  const int m0 = ((warp >> 2) & 1) * 16, n0 = (warp & 3) * 8;   // level 2: 32 x 32 outputs, one 16 x 8 tile per warp
+  if (worker) {   // level 2a: Tm = A(32:64, 0:32) X(0:32, 0:32)
     float c[4];
     mma_tile_tf32<4>(F + (32 + m0) * kInvStride, kInvStride, F + n0, kInvStride, c, lane);
     float* dst = Tm + m0 * kInvTmStride + n0 + 2 * t4;
@@ -149,7 +153,7 @@ __device__ __forceinline__ void unit_lower_inverse_64(float* F, float* work, uin
     *reinterpret_cast<float2*>(dst + (g + 8) * kInvTmStride) = make_float2(c[2], c[3]);
   }
   __syncthreads();
-  {   // level 2b: X(32:64, 0:32) = X(32:64, 32:64) Tm, written over A(32:64, 0:32)
+  if (worker) {   // level 2b: X(32:64, 0:32) = X(32:64, 32:64) Tm, written over A(32:64, 0:32)
     float c[4];
     mma_tile_tf32<4>(F + (32 + m0) * kInvStride + 32, kInvStride, Tm + n0, kInvTmStride, c, lane);
     float* dst = F + (32 + m0) * kInvStride + n0 + 2 * t4;
@@ -157,7 +161,7 @@ __device__ __forceinline__ void unit_lower_inverse_64(float* F, float* work, uin
     *reinterpret_cast<float2*>(dst + (g + 8) * kInvStride) = make_float2(c[2], c[3]);
   }
   __syncthreads();
-  {   // bf16 operand tile: thread -> (row tid >> 2, 16 columns)
+  if (worker) {   // bf16 operand tile: thread -> (row tid >> 2, 16 columns)
     const int row = tid >> 2, q = tid & 3;
     const float* src = F + row * kInvStride + 16 * q;
 #pragma unroll

@@ -84,7 +84,8 @@ class ScreenedRWKVModel(nn.Module):
         if tp is not None:
             if cfg.screening_active:
                 raise NotImplementedError("screening memory is not sharded yet: run screened models data-parallel")
-            input_ids = tp.local_time_slice(input_ids)  # the residual stream is sharded over time
+            tp.set_sequence_length(int(input_ids.shape[1]))
+            input_ids = tp.local_time_slice(input_ids)  # the residual stream is sharded over time (when T divides)
         # parameter-sharding engine (ZeRO-3): told before a unit's weights are used; marks on the residual stream tell it
         # when a unit's backward starts and ends
         hook = getattr(self, "unit_hook", None)

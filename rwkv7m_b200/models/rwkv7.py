@@ -189,17 +189,10 @@ class RWKV7TimeMix(nn.Module):
         )
         if self.layer_idx == 0:
             v_first = v
-        y, final_state = ops.wkv7(
-            r.view(B, T, H, N),
-            w.view(B, T, H, N),
-            k_mod.view(B, T, H, N),
-            v.view(B, T, H, N),
-            neg_kk.view(B, T, H, N),
-            kka.view(B, T, H, N),
-            wkv_state,
-        )
-        y = ops.gn_bonus_gate(
-            y.reshape(B, T, C), r, k_mod, v, g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps
+        y, final_state = ops.wkv7_gn(
+            r.view(B, T, H, N), w.view(B, T, H, N), k_mod.view(B, T, H, N), v.view(B, T, H, N),
+            neg_kk.view(B, T, H, N), kka.view(B, T, H, N), wkv_state,
+            g, self.ln_x.weight, self.ln_x.bias, self.r_k, H, self.ln_x.eps,
         )
         if residual is not None and getattr(self, "tp", None) is None:
             out = ops.linear_add(residual, y, self.output.weight)

@@ -122,6 +122,19 @@ def wkv7(r, w, k, v, a, b, state0):
     return reference.wkv7(r, w, k, v, a, b, state0)
 
 
+def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+    """WKV7 followed by GroupNorm + bonus + gate: ``(out [B,T,C], final_state)``.  On the GPU the two are one autograd
+    node, so the gradients that r, k and v receive from both halves are summed inside the WKV7 backward kernel."""
+    if use_cuda(r):
+        return _cuda().wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps)
+    B, T, H, N = r.shape
+    y, sT = reference.wkv7(r, w, k, v, a, b, state0)
+    C = H * N
+    out = reference.gn_bonus_gate(y.reshape(B, T, C), r.reshape(B, T, C), k.reshape(B, T, C), v.reshape(B, T, C), g,
+                                  ln_w, ln_b, r_k, n_heads, eps)
+    return out, sT
+
+
 def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
     if use_cuda(y):
         return _cuda().gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps)
@@ -161,6 +174,7 @@ def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **s
 __all__ = [
     "screening_scan",
     "embedding",
+    "wkv7_gn",
     "reference",
     "reference_mode",
     "use_cuda",

@@ -630,6 +630,60 @@ class GnBonusGateFn(torch.autograd.Function):
         return dy, dr, dk, dv, dg, _like_param(dlw, ln_w), _like_param(dlb, ln_b), _like_param(drk, r_k), None
 
 
+class WkvGnFn(torch.autograd.Function):
+    """WKV7 recurrence followed by GroupNorm + bonus + gate as one autograd node.
+
+    r, k and v feed both halves (the recurrence and the bonus term), so autograd would sum two gradients for each of
+    them with separate elementwise passes.  Here the backward of the normalisation runs first and the chunked WKV7
+    backward adds its r / k / v gradients to its own as it writes them (src/rwkv7m/model/nnx_model.py:684-730 is the
+    reference's statement of the two halves)."""
+
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, s0, g, ln_w, ln_b, r_k, eps):
+        B, T, H, N = r.shape
+        r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
+        s0 = s0.contiguous().float()
+        need_grad = any(ctx.needs_input_grad)
+        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHUNK_LEN, True)
+        C = H * N
+        g2 = g.contiguous()
+        acts = [y.view(B, T, C), r.view(B, T, C), k.view(B, T, C), v.view(B, T, C), g2.view(B, T, C)]
+        out = _C.gn_bonus_gate_fwd(acts, [_par(ln_w), _par(ln_b), _par(r_k)], eps)
+        _count(2)
+        ctx.eps = eps
+        if need_grad:
+            ctx.save_for_backward(r, w, k, v, a, b, s0, sa, ckpt, y, g2, ln_w, ln_b, r_k)
+        return out, sT
+
+    @staticmethod
+    def backward(ctx, dout, dsT):
+        r, w, k, v, a, b, s0, sa, ckpt, y, g, ln_w, ln_b, r_k = ctx.saved_tensors
+        B, T, H, N = r.shape
+        C = H * N
+        acts = [y.view(B, T, C), r.view(B, T, C), k.view(B, T, C), v.view(B, T, C), g.view(B, T, C)]
+        gin, dlw, dlb, drk = _C.gn_bonus_gate_bwd(acts, [_par(ln_w), _par(ln_b), _par(r_k)], dout.contiguous(), ctx.eps)
+        dy, dr_b, dk_b, dv_b, dg = (t.view(B, T, H, N) for t in gin.unbind(0))
+        dr, dw, dk, dv, da, db, ds0 = _C.wkv7_bwd(r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, WKV_CHUNK_LEN, True,
+                                                  [dr_b, dk_b, dv_b])
+        _count(2)
+        return (dr, dw, dk, dv, da, db, ds0, dg.view(g.shape), _like_param(dlw, ln_w), _like_param(dlb, ln_b),
+                _like_param(drk, r_k), None)
+
+
+def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+    """(GroupNorm(wkv7(...)) + bonus) * g and the final state; r, w, k, v, a, b are [B,T,H,N], g is [B,T,C]."""
+    B, T, H, N = r.shape
+    fused = (WKV_IMPL == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64 and r.is_cuda
+             and g.dtype == torch.bfloat16)
+    if fused:
+        return WkvGnFn.apply(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, eps)
+    y, sT = wkv7(r, w, k, v, a, b, state0)
+    C = H * N
+    out = gn_bonus_gate(y.reshape(B, T, C), r.reshape(B, T, C), k.reshape(B, T, C), v.reshape(B, T, C), g, ln_w, ln_b,
+                        r_k, n_heads, eps)
+    return out, sT
+
+
 def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
     if _bf16(y) and y.shape[-1] == 64 * n_heads:
         return GnBonusGateFn.apply(y, r, k, v, g, ln_w, ln_b, r_k, eps)

@@ -138,6 +138,10 @@ class TensorParallel:
     rank: int
     vocab_parallel: bool = False
     fused: object = None   # FusedSeqCollectives: the framework's own NVLink kernels instead of NCCL
+    # True while a forward pass runs on a sequence that cannot be split over the group (T = 1 decode steps, short
+    # prompts): every rank then carries the whole residual stream, the gathers are identities and the row-parallel
+    # projections end in an all-reduce instead of a reduce-scatter over time.  Inference only.
+    replicated_sequence: bool = False
 
     @classmethod
     def from_group(cls, group=None, vocab_parallel=False):
@@ -155,9 +159,19 @@ class TensorParallel:
         return self.fused
 
     def _use_fused(self, x):
-        return self.fused is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3
+        return (self.fused is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3
+                and not self.replicated_sequence)
+
+    def set_sequence_length(self, T: int):
+        """Called by the model at the start of a forward pass: picks the sequence-sharded layout when ``T`` divides by
+        the group size and the replicated layout otherwise (which has no backward: training always shards)."""
+        self.replicated_sequence = T % self.world != 0
+        if self.replicated_sequence and torch.is_grad_enabled():
+            raise ValueError(f"sequence length {T} must be divisible by the model-parallel size {self.world} for training")
 
     def gather_seq(self, x):
+        if self.replicated_sequence:
+            return x
         if self._use_fused(x):
             from .tp_fused import _FusedGather
 
@@ -181,7 +195,12 @@ class TensorParallel:
         return ops.linear(x, weight)
 
     def reduce_scatter_add(self, partial, residual):
-        """residual + reduce-scatter over time of the row-parallel partial result."""
+        """residual + reduce-scatter over time of the row-parallel partial result (an all-reduce when every rank
+        carries the whole sequence)."""
+        if self.replicated_sequence:
+            total = partial.clone()
+            dist.all_reduce(total, group=self.group)
+            return residual + total
         if isinstance(partial, _DeferredLinear):
             from .tp_fused import _FusedLinearReduceScatterAdd
 
@@ -202,6 +221,8 @@ class TensorParallel:
     def local_time_slice(self, t):
         """This rank's contiguous chunk of the time axis of a [B, T, ...] tensor."""
         T = t.shape[1]
+        if self.replicated_sequence:
+            return t
         if T % self.world != 0:
             raise ValueError(f"sequence length {T} must be divisible by the model-parallel size {self.world}")
         n = T // self.world

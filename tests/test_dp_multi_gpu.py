@@ -22,10 +22,17 @@ def _run(world, multicast):
     return json.loads(line)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+
+
+@pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("multicast", [False, True])
-def test_fused_step_matches_allreduce(multicast):
-    res = _run(2, multicast)
+def test_fused_step_matches_allreduce(multicast, world):
+    _need(world)
+    res = _run(world, multicast)
+    assert res["world"] == world
     assert res["error_code"] == 0
     assert res["rank_spread"] == 0.0
     assert res["master_stale_before_gather"] is True   # bulk fp32 masters stay with their owner between gathers
@@ -38,9 +45,12 @@ def test_fused_step_matches_allreduce(multicast):
         assert abs(a - b) < 5e-3 * abs(a)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_matches_single_gpu():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+@pytest.mark.parametrize("world", [2, 8])
+def test_tensor_parallel_matches_single_gpu(world):
+    """Includes the reduce-scatter in the GEMM epilogue (bf16 vector reductions into the owner's buffer) against an
+    fp32 all-reduce of the same partial products, at 2 and at 8 contributors per element."""
+    _need(world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29533", str(Path(__file__).with_name("tp_worker.py"))]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
@@ -56,12 +66,13 @@ def test_tensor_parallel_matches_single_gpu():
         assert r["gemm_rs_max_err"] < 0.02 * r["gemm_rs_scale"] + 0.05, res
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("accum", [1, 2])
-def test_zero3_matches_allreduce(accum):
+def test_zero3_matches_allreduce(accum, world):
     import os
 
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    _need(world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29535", str(Path(__file__).with_name("zero3_worker.py"))]
     env = dict(os.environ, ZERO3_ACCUM=str(accum), NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
@@ -77,3 +88,4 @@ def test_zero3_matches_allreduce(accum):
         assert abs(a - b) < 5e-3 * abs(a)
     # every rank holds its pieces of the bulk weights plus the replicated small leaves, not the whole model
     assert res["master_elements_held"] < 0.75 * res["master_elements_replicated"]
+    assert res["world"] == world

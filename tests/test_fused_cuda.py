@@ -205,3 +205,41 @@ def test_embedding_kernels_match_torch(table_dtype):
         C.embedding_bwd(ids.reshape(-1), dout.reshape(-1, W), grad)
     ref = torch.ones(V, W, device="cuda").index_add_(0, ids.reshape(-1).long(), 2 * dout.reshape(-1, W).float())
     assert torch.allclose(grad, ref, atol=1e-4, rtol=1e-5)
+
+
+def test_wkv_and_output_norm_as_one_node_sums_the_shared_gradients():
+    """ops.wkv7_gn against wkv7 followed by gn_bonus_gate: same forward, and the gradients of r, k, v (which feed both
+    halves) equal the sums that autograd forms for the two-node version."""
+    from rwkv7m_b200 import ops
+
+    g = torch.Generator().manual_seed(8)
+    B, T, H, N = 2, 128, 2, 64
+    C = H * N
+    r, k, v = ((torch.randn(B, T, H, N, generator=g) * 0.5).cuda().bfloat16() for _ in range(3))
+    w = (-torch.nn.functional.softplus(-torch.randn(B, T, H, N, generator=g)) - 0.5).cuda().bfloat16()
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N, generator=g), dim=-1)
+    a, b = (-kk).cuda().bfloat16(), (kk * torch.sigmoid(torch.randn(B, T, H, N, generator=g))).cuda().bfloat16()
+    gate = torch.randn(B, T, C, generator=g).cuda().bfloat16()
+    s0 = (torch.randn(B, H, N, N, generator=g) * 0.1).cuda()
+    ln_w = (torch.rand(C, generator=g) + 0.5).cuda()
+    ln_b = (torch.randn(C, generator=g) * 0.1).cuda()
+    r_k = (torch.randn(H, N, generator=g) * 0.1).cuda()
+    dout = torch.randn(B, T, C, generator=g).cuda().bfloat16()
+
+    def run(fused):
+        leaves = [t.clone().requires_grad_(True) for t in (r, w, k, v, a, b, gate, ln_w, ln_b, r_k)]
+        lr, lw, lk, lv, la, lb, lg, lnw, lnb, lrk = leaves
+        if fused:
+            out, sT = ops.wkv7_gn(lr, lw, lk, lv, la, lb, s0, lg, lnw, lnb, lrk, H)
+        else:
+            y, sT = ops.wkv7(lr, lw, lk, lv, la, lb, s0)
+            out = ops.gn_bonus_gate(y.reshape(B, T, C), lr.reshape(B, T, C), lk.reshape(B, T, C), lv.reshape(B, T, C), lg,
+                                    lnw, lnb, lrk, H)
+        (out.float() * dout.float()).sum().backward()
+        return [out.detach().float(), sT] + [l.grad.float() for l in leaves]
+
+    got, want = run(True), run(False)
+    names = "out sT dr dw dk dv da db dg dln_w dln_b dr_k".split()
+    for name, x, y in zip(names, got, want):
+        rel = float((x - y).norm() / (y.norm() + 1e-9))
+        assert rel < (1e-2 if name in ("dr", "dk", "dv") else 1e-5), (name, rel)   # the sums round once instead of twice

@@ -44,6 +44,17 @@ def _single_process_params(steps=2, param_dtype="float32", uneven_mask=False):
     return {n: p.detach().clone() for n, p in ts.model.named_parameters()}, losses
 
 
+def _leave():
+    """Leave together, then end the process without running destructors: tearing the gloo group down while its
+    background threads are still winding up aborts now and then (std::terminate from a joinable thread)."""
+    import sys
+
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def _init(rank, world, port):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -63,8 +74,7 @@ def _dp_worker(rank, world, port, out, uneven_mask=False):
         losses.append(float(m["loss"]))
     if rank == 0:
         torch.save({"params": {n: p.detach().clone() for n, p in ts.model.named_parameters()}, "losses": losses}, out)
-    dist.barrier()   # leave together: a rank that tears gloo down while its peer is still in a collective aborts
-    dist.destroy_process_group()
+    _leave()
 
 
 def _tp_worker(rank, world, port, out, vocab_parallel, param_dtype="float32"):
@@ -84,8 +94,7 @@ def _tp_worker(rank, world, port, out, vocab_parallel, param_dtype="float32"):
     if rank == 0:
         torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "logits": logits,
                     "grad_norm": float(ts.optimizer.grad_norm)}, out)
-    dist.barrier()   # leave together: a rank that tears gloo down while its peer is still in a collective aborts
-    dist.destroy_process_group()
+    _leave()
 
 
 def _compare(ref, got, tol):
@@ -151,8 +160,7 @@ def _tp_worker_one_step(rank, world, port, out):
             assert torch.equal(mine, other), name
     if rank == 0:
         torch.save({"params": {n: v.clone() for n, v in full.items()}, "grad_norm": float(ts.optimizer.grad_norm)}, out)
-    dist.barrier()
-    dist.destroy_process_group()
+    _leave()
 
 
 def test_data_parallel_uneven_masks_match_global_batch(tmp_path):
@@ -163,3 +171,43 @@ def test_data_parallel_uneven_masks_match_global_batch(tmp_path):
     res = torch.load(out)
     assert res["losses"] == pytest.approx(ref_losses, rel=1e-4)
     _compare(ref, res["params"], 2e-5)
+
+
+def _decode_trace(rt, steps=3):
+    """Prefill an 8-token prompt, then greedy T = 1 steps; returns the logits of every step."""
+    prompt = _global_batch()["input_ids"]
+    logits, _ = R.infer_prefill(rt, prompt)
+    trace = [logits[:, -1].float().clone()]
+    for _ in range(steps):
+        tok = trace[-1].argmax(-1, keepdim=True).to(torch.int32)
+        last, _ = R.infer_next(rt, tok)
+        trace.append(last.float().clone())
+    return torch.stack(trace)
+
+
+def _tp_decode_worker(rank, world, port, out, vocab_parallel):
+    _init(rank, world, port)
+    from rwkv7m_b200.parallel.tp import TensorParallel
+
+    tp = TensorParallel.from_group(vocab_parallel=vocab_parallel)
+    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=4, total_steps=20, tp=tp)
+    ts.model.eval()
+    trace = _decode_trace(rt)
+    assert tp.replicated_sequence          # the T = 1 steps ran with the whole (one-token) sequence on every rank
+    if rank == 0:
+        torch.save(trace, out)
+    _leave()
+
+
+@pytest.mark.parametrize("vocab_parallel", [False, True])
+def test_tensor_parallel_decode_matches_single_process(tmp_path, vocab_parallel):
+    """Prefill (sequence-sharded) followed by T = 1 decode steps (replicated sequence, row-parallel projections end in
+    an all-reduce) under two-rank tensor parallelism against the single-process model."""
+    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=4, total_steps=20)
+    ts.model.eval()
+    ref = _decode_trace(rt)
+    out = str(tmp_path / "tp_decode.pt")
+    mp.spawn(_tp_decode_worker, args=(2, _free_port(), out, vocab_parallel), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got.shape == ref.shape == (4, 4, 256)
+    assert float((got - ref).abs().max()) < 1e-4

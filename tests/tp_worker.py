@@ -28,8 +28,11 @@ def main():
     import rwkv7m_b200 as R
     from rwkv7m_b200.parallel.tp import TensorParallel
 
-    cfg = R.ModelConfig(d_model=256, d_ffn=512, n_layers=2, n_heads=4, head_size=64, vocab_size=512,
+    # heads, FFN width, vocabulary and sequence length must all divide by the group size
+    heads = 4 if world <= 4 else 8
+    cfg = R.ModelConfig(d_model=64 * heads, d_ffn=128 * heads, n_layers=2, n_heads=heads, head_size=64, vocab_size=512,
                         max_seq_len=64, dtype="bfloat16", use_screening=False, warmup_steps=0, lr_init=1e-3)
+    C = cfg.d_model
     g = torch.Generator().manual_seed(11)
     ids = torch.randint(0, 512, (2, 65), generator=g).to(torch.int32)
     batch = {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(), "mask": torch.ones(2, 64)}
@@ -53,14 +56,14 @@ def main():
     # the same step with the sequence collectives on this framework's own NVLink kernels
     for mc, push in ((True, True), (False, False)):
         tpf = TensorParallel.from_group(vocab_parallel=False)
-        comm = tpf.enable_fused(2 * 64 * 256, dev, use_multicast=mc, gemm_epilogue_scatter=push)
+        comm = tpf.enable_fused(2 * 64 * C, dev, use_multicast=mc, gemm_epilogue_scatter=push)
         # collectives against NCCL first
         g = torch.Generator().manual_seed(5 + rank)
-        xl = torch.randn(2, 64 // world, 256, generator=g).to(dev).bfloat16()
+        xl = torch.randn(2, 64 // world, C, generator=g).to(dev).bfloat16()
         full = comm.gather(xl)
         ref_full = torch.cat([t for t in _all_gather(xl, world)], dim=1)
-        part = torch.randn(2, 64, 256, generator=g).to(dev).bfloat16()
-        res = torch.randn(2, 64 // world, 256, generator=g).to(dev).bfloat16()
+        part = torch.randn(2, 64, C, generator=g).to(dev).bfloat16()
+        res = torch.randn(2, 64 // world, C, generator=g).to(dev).bfloat16()
         got_rs = comm.reduce_scatter_add(part, res)
         tot = part.float().clone()
         dist.all_reduce(tot)
@@ -71,7 +74,7 @@ def main():
         den = sum(float(ref[k].pow(2).sum()) for k in ref) ** 0.5
         # GEMM with the reduce-scatter in its epilogue against all-reduce + slice
         xg = torch.randn(2, 64, 128, generator=g).to(dev).bfloat16()
-        wg = torch.randn(256, 128, generator=g).to(dev).bfloat16() * 0.1
+        wg = torch.randn(C, 128, generator=g).to(dev).bfloat16() * 0.1
         got_g = comm.gemm_reduce_scatter(xg.reshape(128, 128), wg, res, 2, 64)
         tot_g = (xg.float() @ wg.float().t())
         dist.all_reduce(tot_g)
