@@ -77,12 +77,21 @@ def _no_screen(config):
     return scr
 
 
-def create_runtime(rng_key, config, *, batch_size: int = 1, device=None) -> RWKV7MRuntime:
+def create_runtime(rng_key, config, *, batch_size: int = 1, device=None, tp=None) -> RWKV7MRuntime:
+    """``tp`` (a :class:`rwkv7m_b200.parallel.tp.TensorParallel`) shards the model over that group for serving: prompts
+    whose length divides by the group size are prefilled sequence-sharded, T = 1 decode steps run with the token
+    replicated and one all-reduce per row-parallel projection."""
     config = load_model_config(config)
     model = initialize_model(_seed(rng_key), config, device=_default_device(device))
+    if tp is not None:
+        tp.shard_model(model)
+        tp.sync_replicated(model)
     model.eval()
     _attach_inference_weights(model)
-    return _make_runtime(model, config, batch_size)
+    runtime = _make_runtime(model, config, batch_size)
+    if tp is not None:
+        runtime.rwkv_state = runtime.initial_rwkv_state = tp.init_rwkv_state(batch_size, config, device=runtime.device)
+    return runtime
 
 
 def _attach_inference_weights(model):
@@ -254,7 +263,9 @@ def reset_runtime_state(runtime: RWKV7MRuntime, config: ModelConfig | None = Non
     config = config or runtime.config
     batch_size = batch_size or runtime.batch_size
     device = runtime.device
-    runtime.rwkv_state = init_rwkv_state(batch_size, config, device=device)
+    tp = getattr(runtime.model, "tp", None)   # a sharded model keeps only its own heads' recurrent state
+    runtime.rwkv_state = (tp.init_rwkv_state(batch_size, config, device=device) if tp is not None
+                          else init_rwkv_state(batch_size, config, device=device))
     runtime.screen_state = init_screen_state(
         batch_size, config.screening if config.use_screening else _no_screen(config), device=device
     )

@@ -24,16 +24,38 @@ def main(argv=None):
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--streams", type=int, default=3, help="side streams for the independent time-mix projections (0 = one stream)")
     ap.add_argument("--repeats", type=int, default=2)
+    ap.add_argument("--tp", action="store_true",
+                    help="tensor parallel over all ranks of the torchrun launch (every rank serves the same batch); "
+                         "the step is launched eagerly unless --tp-graph is given")
+    ap.add_argument("--tp-graph", action="store_true", help="with --tp: replay the step from a CUDA graph")
     args = ap.parse_args(argv)
+    if args.tp and not args.tp_graph:
+        args.no_graph = True
 
     import rwkv7m_b200 as R
     from rwkv7m_b200.config import bench_config
     from rwkv7m_b200.infer.generate import GraphDecoder, prefill_last, sample_next
     from rwkv7m_b200.ops import cuda as K
 
-    dev = torch.device("cuda", 0)
+    import os
+
+    tp, rank, world = None, 0, 1
+    if args.tp:
+        import torch.distributed as dist
+
+        from rwkv7m_b200.parallel.tp import TensorParallel
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        rank, world = dist.get_rank(), dist.get_world_size()
+        tp = TensorParallel.from_group()
+    else:
+        dev = torch.device("cuda", 0)
     cfg = bench_config(args.model)
-    rt = R.create_runtime(0, cfg, batch_size=args.batch, device=dev)
+    rt = R.create_runtime(0, cfg, batch_size=args.batch, device=dev, tp=tp)
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt), generator=g, dtype=torch.int64).to(torch.int32).to(dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -68,14 +90,26 @@ def main(argv=None):
                         "decode_ms": e1.elapsed_time(e2), "launches": K.LAUNCH_COUNT - launches0,
                         "checksum": int(out.sum().item())})
     best = min(results, key=lambda r: r["decode_ms"])
-    print(json.dumps({
+    if tp is not None:   # the slowest rank sets the pace
+        import torch.distributed as dist
+
+        t = torch.tensor([best["decode_ms"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        best = dict(best, decode_ms=float(t))
+    if rank == 0:
+      print(json.dumps({
         "metric": f"batched recurrent decode at {args.model}", "batch": args.batch, "prompt_tokens": args.prompt,
+        "parallelism": f"tp{world}" if tp is not None else "1 gpu",
         "new_tokens": args.new_tokens, "cuda_graph": not args.no_graph, "side_streams": args.streams,
         "decode_tokens_per_s": args.batch * args.new_tokens / (best["decode_ms"] / 1e3),
         "decode_ms_per_step": best["decode_ms"] / args.new_tokens,
         "prefill_plus_setup_ms": best["prefill_ms"], "runs": results,
         "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1), "dtype": "bf16",
-    }))
+      }))
+    if tp is not None:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
     return 0
 
 

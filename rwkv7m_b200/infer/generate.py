@@ -120,7 +120,10 @@ class GraphDecoder:
 def _graph_ok(model, prompt_ids):
     cfg = model.config
     screened = bool(cfg.use_screening and cfg.screening.screened_layers)
-    return (prompt_ids.is_cuda and not screened and getattr(model, "tp", None) is None
+    tp = getattr(model, "tp", None)
+    # the framework's own NVLink collectives pass their barrier targets as launch arguments, which a replayed graph would
+    # repeat; under tensor parallelism the graph therefore carries the library all-reduces (replicated-sequence mode)
+    return (prompt_ids.is_cuda and not screened and (tp is None or tp.fused is None)
             and next(model.parameters()).dtype is not None)
 
 

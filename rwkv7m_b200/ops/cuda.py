@@ -630,6 +630,12 @@ class GnBonusGateFn(torch.autograd.Function):
         return dy, dr, dk, dv, dg, _like_param(dlw, ln_w), _like_param(dlb, ln_b), _like_param(drk, r_k), None
 
 
+# RWKV7M_B200_WKV_GN=1 makes the recurrence and the output normalisation one autograd node.  Off by default: the
+# extra 16-byte reads in the latency-bound backward kernel cost more than the three elementwise sums they replace
+# (measured on one box, 1.5B step: 383-385 ms fused against 381-382 ms)
+WKV_GN_FUSED = os.environ.get("RWKV7M_B200_WKV_GN", "0") == "1"
+
+
 class WkvGnFn(torch.autograd.Function):
     """WKV7 recurrence followed by GroupNorm + bonus + gate as one autograd node.
 
@@ -673,8 +679,8 @@ class WkvGnFn(torch.autograd.Function):
 def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
     """(GroupNorm(wkv7(...)) + bonus) * g and the final state; r, w, k, v, a, b are [B,T,H,N], g is [B,T,C]."""
     B, T, H, N = r.shape
-    fused = (WKV_IMPL == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64 and r.is_cuda
-             and g.dtype == torch.bfloat16)
+    fused = (WKV_GN_FUSED and WKV_IMPL == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64
+             and r.is_cuda and g.dtype == torch.bfloat16)
     if fused:
         return WkvGnFn.apply(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, eps)
     y, sT = wkv7(r, w, k, v, a, b, state0)

@@ -55,6 +55,8 @@ def test_tensor_parallel_matches_single_gpu(world):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    for key in ("decode_graph0", "decode_graph1"):   # serving: prefill + T = 1 steps, eager and graph-replayed
+        assert res[key]["max_err"] < 0.03 * res[key]["scale"] + 0.03, res
     for key in ("vp0", "vp1", "fused_mc1", "fused_mc0"):
         r = res[key]
         assert r["rel_l2"] < 3e-3, res

@@ -44,10 +44,43 @@ def main():
             ts, m = R.train_batch(ts, batch, rt)
             losses.append(float(m["loss"]))
         params = tp.gather_full_parameters(ts.model) if tp is not None else dict(ts.model.named_parameters())
-        return {n: p.detach().float().clone() for n, p in params.items()}, losses, float(ts.optimizer.grad_norm)
+        params = {n: p.detach().float().clone() for n, p in params.items()}
+        if tp is None or tp.fused is None:
+            traces["ref" if tp is None else f"tp_vp{int(tp.vocab_parallel)}"] = [
+                decode_trace(ts.model, rt.initial_rwkv_state, graph) for graph in ((False,) if tp is None else (False, True))]
+        return params, losses, float(ts.optimizer.grad_norm)
+
+    traces = {}
+
+    def decode_trace(model, state0, graph):
+        """Prefill (sequence-sharded under TP) + greedy T = 1 steps (replicated sequence, all-reduce per row-parallel
+        projection), eagerly or with the step replayed from a CUDA graph.  Runs on a model that has been trained for a
+        few steps: a freshly initialised one has zero output projections, which would hide the row-parallel sums."""
+        from rwkv7m_b200.infer.generate import GraphDecoder, decode_one, prefill_last
+
+        was_training = model.training
+        model.eval()
+        R.api._attach_inference_weights(model)
+        prompt = ids[:, :64].to(dev)
+        last, rs, ss = prefill_last(model, prompt, state0, R.init_screen_state(2, cfg.screening, device=dev))
+        trace = [last.float().clone()]
+        dec = GraphDecoder(model, rs, parallel_streams=2) if graph else None
+        toks = decode_tokens
+        for i in range(4):
+            tok = toks[i].to(dev)
+            if graph:
+                last = dec.step(tok)
+            else:
+                last, rs, ss, _ = decode_one(model, tok, rs, ss)
+            trace.append(last.float().clone())
+        model.train(was_training)
+        return torch.stack(trace)
+
+    decode_tokens = [torch.randint(0, 512, (2, 1), generator=g).to(torch.int32) for _ in range(4)]   # same on every rank
 
     ref, l_ref, n_ref = run(None)
     out = {}
+
     for vp in (False, True):
         got, l_tp, n_tp = run(TensorParallel.from_group(vocab_parallel=vp))
         num = sum(float((ref[n] - got[n]).pow(2).sum()) for n in ref) ** 0.5
@@ -84,6 +117,10 @@ def main():
             "rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "multicast_used": bool(comm.use_multicast),
             "gather_exact": bool(torch.equal(full, ref_full)),
             "rs_max_err": float((got_rs.float() - want_rs).abs().max()), "error_code": comm.error_code()}
+    d_ref = traces["ref"][0]
+    for graph in (0, 1):
+        d_tp = traces["tp_vp0"][graph]
+        out[f"decode_graph{graph}"] = {"max_err": float((d_tp - d_ref).abs().max()), "scale": float(d_ref.abs().max())}
     if rank == 0:
         print(json.dumps(out))
     dist.destroy_process_group()
