@@ -245,7 +245,9 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   check_par(w, C, "weight"); check_par(mean, M, "mean"); check_par(rstd, M, "rstd");
   TORCH_CHECK(dy.numel() == x.numel());
   Tensor dx = torch::empty_like(x);
-  int parts = (int)std::min<int64_t>(148 * 2, std::max<int64_t>(1, M / 64));   // blocks of the backward grid
+  // blocks of the backward grid (one row of partial weight / bias gradients each): several resident blocks per SM keep
+  // enough 16-byte loads in flight for the one-pass kernel
+  int parts = (int)std::min<int64_t>(148 * 6, std::max<int64_t>(1, M / 16));
   auto f32 = x.options().dtype(at::kFloat);
   Tensor dwp = torch::empty({parts, C}, f32), dbp = torch::empty({parts, C}, f32);
   const bool has_res = dres.has_value() && dres->defined();

@@ -168,108 +168,96 @@ __global__ void layernorm_bwd_wb_kernel(const bf16* __restrict__ dy, const bf16*
   }
 }
 
-// dx in one pass: one warp per row with 16-byte accesses keeps the row of dy and x in registers, so nothing is read twice.
-template <int NCH, bool RES>   // C = NCH * 256; RES: add the gradient that arrives through the residual connection
-__global__ void __launch_bounds__(256, (RES && NCH >= 8) ? 1 : 2) layernorm_bwd_fused_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                                                                     const float* __restrict__ w, const float* __restrict__ mean,
-                                                                     const float* __restrict__ rstd, bf16* __restrict__ dx,
-                                                                     float* __restrict__ dw_part, float* __restrict__ db_part,
-                                                                     int M, const bf16* __restrict__ dres) {
-  constexpr int C = NCH * 256;
-  __shared__ float s_w[C];
-  for (int c = threadIdx.x; c < C; c += 256) s_w[c] = w[c];
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rows_per = (M + gridDim.x - 1) / gridDim.x;
-  const int r0 = blockIdx.x * rows_per, r1 = min(M, r0 + rows_per);
-  for (int row = r0 + warp; row < r1; row += 8) {
-    const bf16* gr = dy + (size_t)row * C + lane * 8;
-    const bf16* xr = x + (size_t)row * C + lane * 8;
-    uint4 graw[NCH], xraw[NCH];
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-      graw[i] = __ldg(reinterpret_cast<const uint4*>(gr + i * 256));
-      xraw[i] = __ldg(reinterpret_cast<const uint4*>(xr + i * 256));
-    }
-    const float mu = mean[row], rs = rstd[row];
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-      const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
-      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
-      const float* wp = s_w + i * 256 + lane * 8;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
-        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
-        const float g0 = g.x * wp[2 * j], g1 = g.y * wp[2 * j + 1];
-        s1 += g0 + g1;
-        s2 = fmaf(g0, (v.x - mu) * rs, s2);
-        s2 = fmaf(g1, (v.y - mu) * rs, s2);
-      }
-    }
-    s1 = warp_sum(s1) * (1.f / C);
-    s2 = warp_sum(s2) * (1.f / C);
-    bf16* dr = dx + (size_t)row * C + lane * 8;
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-      const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw[i]);
-      const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw[i]);
-      // the residual-path gradient is read where it is used: keeping a third row in registers would spill at C = 2048
-      // (volatile asm: the compiler would otherwise hoist all NCH loads above the statistics)
-      uint4 rr = make_uint4(0u, 0u, 0u, 0u);
-      if (RES)
-        asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(rr.x), "=r"(rr.y), "=r"(rr.z), "=r"(rr.w)
-                     : "l"(dres + (size_t)row * C + lane * 8 + i * 256));
-      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rr);
-      const int cb = i * 256 + lane * 8;
-      uint4 o;
-      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
-        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
-        const float2 r = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rp[j]));
-        const float xh0 = (v.x - mu) * rs, xh1 = (v.y - mu) * rs;
-        bf162 h = __floats2bfloat162_rn(r.x + rs * (g.x * s_w[cb + 2 * j] - s1 - xh0 * s2),
-                                        r.y + rs * (g.y * s_w[cb + 2 * j + 1] - s1 - xh1 * s2));
-        op[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      *reinterpret_cast<uint4*>(dr + i * 256) = o;
-    }
+// LayerNorm backward in one pass over dy and x: a block of C / 8 threads walks rows two at a time, every thread owns 8
+// consecutive channels of every row its block sees, so the input gradient (row statistics through one block reduction
+// per row pair), the optional residual-path gradient and the per-block partial sums of the weight / bias gradients
+// (16 registers per thread) all come from the same 16-byte loads.  dw_part / db_part receive one row per block.
+template <int NT, bool RES>
+__global__ void __launch_bounds__(NT, (NT >= 256 ? 3 : 4)) layernorm_bwd_onepass_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                   const float* __restrict__ w, const float* __restrict__ mean,
+                                                                   const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                                                   float* __restrict__ dw_part, float* __restrict__ db_part,
+                                                                   int M, const bf16* __restrict__ dres) {
+  constexpr int C = NT * 8, NW = NT / 32;
+  __shared__ float red[2][NW][4];
+  const int c = threadIdx.x * 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float w8[8], aw[8], ab[8];
+  {
+    const float4 a = *reinterpret_cast<const float4*>(w + c), b = *reinterpret_cast<const float4*>(w + c + 4);
+    w8[0] = a.x; w8[1] = a.y; w8[2] = a.z; w8[3] = a.w; w8[4] = b.x; w8[5] = b.y; w8[6] = b.z; w8[7] = b.w;
   }
-}
-
-// dw / db partial sums with 16-byte accesses: thread = 8 consecutive channels, block row p sums the rows of part p.
-__global__ void __launch_bounds__(256) layernorm_bwd_wb_wide_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                                                                    const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                    float* __restrict__ dw_part, float* __restrict__ db_part,
-                                                                    int M, int C) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c >= C) return;
-  const int rows_per = (M + gridDim.y - 1) / gridDim.y;
-  const int r0 = blockIdx.y * rows_per, r1 = min(M, r0 + rows_per);
-  float aw[8], ab[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { aw[j] = 0.f; ab[j] = 0.f; }
-#pragma unroll 4
-  for (int r = r0; r < r1; ++r) {
-    const uint4 graw = __ldg(reinterpret_cast<const uint4*>(dy + (size_t)r * C + c));
-    const uint4 xraw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * C + c));
-    const float mu = __ldg(mean + r), rs = __ldg(rstd + r);
-    const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw);
-    const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xraw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(&gp[j]));
-      const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(&xp[j]));
-      aw[2 * j] = fmaf(g.x, (v.x - mu) * rs, aw[2 * j]); aw[2 * j + 1] = fmaf(g.y, (v.y - mu) * rs, aw[2 * j + 1]);
-      ab[2 * j] += g.x; ab[2 * j + 1] += g.y;
+  int it = 0;
+  for (int row = 2 * blockIdx.x; row < M; row += 2 * gridDim.x, it ^= 1) {
+    const bool two = row + 1 < M;
+    const size_t o0 = (size_t)row * C + c, o1 = o0 + C;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 g0r = __ldg(reinterpret_cast<const uint4*>(dy + o0)), x0r = __ldg(reinterpret_cast<const uint4*>(x + o0));
+    const uint4 g1r = two ? __ldg(reinterpret_cast<const uint4*>(dy + o1)) : zero;
+    const uint4 x1r = two ? __ldg(reinterpret_cast<const uint4*>(x + o1)) : zero;
+    uint4 d0r = zero, d1r = zero;
+    if (RES) {
+      d0r = __ldg(reinterpret_cast<const uint4*>(dres + o0));
+      if (two) d1r = __ldg(reinterpret_cast<const uint4*>(dres + o1));
     }
+    const float mu0 = mean[row], rs0 = rstd[row];
+    const float mu1 = two ? mean[row + 1] : 0.f, rs1 = two ? rstd[row + 1] : 0.f;
+    float g0[8], h0[8], g1[8], h1[8];
+    {
+      const bf162* gp = reinterpret_cast<const bf162*>(&g0r);
+      const bf162* xp = reinterpret_cast<const bf162*>(&x0r);
+      const bf162* gq = reinterpret_cast<const bf162*>(&g1r);
+      const bf162* xq = reinterpret_cast<const bf162*>(&x1r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 a = __bfloat1622float2(gp[j]), b = __bfloat1622float2(xp[j]);
+        g0[2 * j] = a.x; g0[2 * j + 1] = a.y; h0[2 * j] = (b.x - mu0) * rs0; h0[2 * j + 1] = (b.y - mu0) * rs0;
+        a = __bfloat1622float2(gq[j]); b = __bfloat1622float2(xq[j]);
+        g1[2 * j] = a.x; g1[2 * j + 1] = a.y; h1[2 * j] = (b.x - mu1) * rs1; h1[2 * j + 1] = (b.y - mu1) * rs1;
+      }
+    }
+    float s[4] = {0.f, 0.f, 0.f, 0.f};   // sum(g w), sum(g w xhat) of the two rows
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = g0[j] * w8[j], b = g1[j] * w8[j];
+      s[0] += a; s[1] = fmaf(a, h0[j], s[1]);
+      s[2] += b; s[3] = fmaf(b, h1[j], s[3]);
+      aw[j] = fmaf(g0[j], h0[j], aw[j]); aw[j] = fmaf(g1[j], h1[j], aw[j]);
+      ab[j] += g0[j] + g1[j];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = warp_sum(s[i]);
+    if (NW > 1) {
+      if (lane == 0) { red[it][warp][0] = s[0]; red[it][warp][1] = s[1]; red[it][warp][2] = s[2]; red[it][warp][3] = s[3]; }
+      __syncthreads();   // one barrier per row pair: the buffer alternates, and the barrier of the next pair separates
+                         // these reads from the writes of the pair after it
+      s[0] = s[1] = s[2] = s[3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < NW; ++k) { s[0] += red[it][k][0]; s[1] += red[it][k][1]; s[2] += red[it][k][2]; s[3] += red[it][k][3]; }
+    }
+    const float inv = 1.f / C;
+    const float a1 = s[0] * inv, a2 = s[1] * inv, b1 = s[2] * inv, b2 = s[3] * inv;
+    uint4 o0r, o1r;
+    {
+      bf162* op = reinterpret_cast<bf162*>(&o0r);
+      bf162* oq = reinterpret_cast<bf162*>(&o1r);
+      const bf162* dp = reinterpret_cast<const bf162*>(&d0r);
+      const bf162* dq = reinterpret_cast<const bf162*>(&d1r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 r0 = __bfloat1622float2(dp[j]), r1 = __bfloat1622float2(dq[j]);
+        op[j] = __floats2bfloat162_rn(r0.x + rs0 * (g0[2 * j] * w8[2 * j] - a1 - h0[2 * j] * a2),
+                                      r0.y + rs0 * (g0[2 * j + 1] * w8[2 * j + 1] - a1 - h0[2 * j + 1] * a2));
+        oq[j] = __floats2bfloat162_rn(r1.x + rs1 * (g1[2 * j] * w8[2 * j] - b1 - h1[2 * j] * b2),
+                                      r1.y + rs1 * (g1[2 * j + 1] * w8[2 * j + 1] - b1 - h1[2 * j + 1] * b2));
+      }
+    }
+    *reinterpret_cast<uint4*>(dx + o0) = o0r;
+    if (two) *reinterpret_cast<uint4*>(dx + o1) = o1r;
   }
-  float* dwp = dw_part + (size_t)blockIdx.y * C + c;
-  float* dbp = db_part + (size_t)blockIdx.y * C + c;
+  float* dwp = dw_part + (size_t)blockIdx.x * C + c;
+  float* dbp = db_part + (size_t)blockIdx.x * C + c;
   *reinterpret_cast<float4*>(dwp) = make_float4(aw[0], aw[1], aw[2], aw[3]);
   *reinterpret_cast<float4*>(dwp + 4) = make_float4(aw[4], aw[5], aw[6], aw[7]);
   *reinterpret_cast<float4*>(dbp) = make_float4(ab[0], ab[1], ab[2], ab[3]);
@@ -279,17 +267,13 @@ __global__ void __launch_bounds__(256) layernorm_bwd_wb_wide_kernel(const bf16* 
 template <int NCH>
 static void launch_ln_bwd_fused(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
                                 float* dw_part, float* db_part, int parts, int M, cudaStream_t st, const void* dres) {
-  int blocks = (M + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  constexpr int NT = NCH * 32;   // C / 8 threads
   if (dres != nullptr)
-    layernorm_bwd_fused_kernel<NCH, true><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
-                                                                  dw_part, db_part, M, (const bf16*)dres);
+    layernorm_bwd_onepass_kernel<NT, true><<<parts, NT, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
+                                                                 dw_part, db_part, M, (const bf16*)dres);
   else
-    layernorm_bwd_fused_kernel<NCH, false><<<blocks, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
-                                                                   dw_part, db_part, M, nullptr);
-  constexpr int C = NCH * 256;
-  dim3 grid((C / 8 + 255) / 256, parts);
-  layernorm_bwd_wb_wide_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, dw_part, db_part, M, C);
+    layernorm_bwd_onepass_kernel<NT, false><<<parts, NT, 0, st>>>((const bf16*)dy, (const bf16*)x, w, mean, rstd, (bf16*)dx,
+                                                                  dw_part, db_part, M, nullptr);
 }
 
 void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int M, int C,
@@ -425,95 +409,103 @@ __global__ void shift_mix_bwd_kernel(ShiftGrads<K> dout, const bf16* __restrict_
   }
 }
 
-// Wide variant of the backward: thread = 4 consecutive channels (8-byte accesses), the loads of the next (earlier)
-// token are issued before the current one is processed.
-__device__ __forceinline__ void ld4(const bf16* p, float (&x)[4]) {
-  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+// Wide variant of the backward: thread = 4 consecutive channels (8-byte accesses).  Tokens are handled two per iteration
+// and the packed loads of the pair after it are issued first, so every thread keeps 14 loads in flight; the mixing
+// coefficients sit in shared memory to leave the registers to those loads and to the K x 4 coefficient-gradient sums.
+__device__ __forceinline__ void unpack4(const uint2 raw, float (&x)[4]) {
   const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.x));
   const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.y));
   x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
 }
+__device__ __forceinline__ uint2 ldraw4(const bf16* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
 
 template <int K>
-__global__ void __launch_bounds__(128) shift_mix_bwd_wide_kernel(ShiftGrads<K> dout, const bf16* __restrict__ x,
-                                                                 const float* __restrict__ prev, const float* __restrict__ mix,
-                                                                 bf16* __restrict__ dx, float* __restrict__ dprev,
-                                                                 float* __restrict__ dmix_part, int B, int T, int C) {
+__global__ void __launch_bounds__(128, 4) shift_mix_bwd_wide_kernel(ShiftGrads<K> dout, const bf16* __restrict__ x,
+                                                                    const float* __restrict__ prev, const float* __restrict__ mix,
+                                                                    bf16* __restrict__ dx, float* __restrict__ dprev,
+                                                                    float* __restrict__ dmix_part, int B, int T, int C) {
+  __shared__ __align__(16) float s_m[K][512];
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (c >= C) return;
+  if (c >= C) return;   // no block-wide barrier below: every thread reads only the coefficients it stored itself
   const int b = blockIdx.z;
   const int t0 = blockIdx.y * kShiftSeg;
   const int t1 = min(T, t0 + kShiftSeg);
-  float m[K][4], acc[K][4];
+  float acc[K][4];
 #pragma unroll
-  for (int z = 0; z < K; ++z)
+  for (int z = 0; z < K; ++z) {
+    *reinterpret_cast<float4*>(&s_m[z][threadIdx.x * 4]) = *reinterpret_cast<const float4*>(mix + (size_t)z * C + c);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { m[z][j] = mix[z * C + c + j]; acc[z][j] = 0.f; }
+    for (int j = 0; j < 4; ++j) acc[z][j] = 0.f;
+  }
   float carry[4] = {0.f, 0.f, 0.f, 0.f};   // sum_z dout_z[t+1] * mix_z
   if (t1 < T) {
     const size_t o = ((size_t)b * T + t1) * C + c;
 #pragma unroll
     for (int z = 0; z < K; ++z) {
       float g[4];
-      ld4(dout.p[z] + o, g);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) carry[j] = fmaf(g[j], m[z][j], carry[j]);
+      unpack4(ldraw4(dout.p[z] + o), g);
+      const float4 m = *reinterpret_cast<const float4*>(&s_m[z][threadIdx.x * 4]);
+      carry[0] = fmaf(g[0], m.x, carry[0]); carry[1] = fmaf(g[1], m.y, carry[1]);
+      carry[2] = fmaf(g[2], m.z, carry[2]); carry[3] = fmaf(g[3], m.w, carry[3]);
     }
   }
-  float cur[4], g[K][4], pv[4];
-  ld4(x + ((size_t)b * T + t1 - 1) * C + c, cur);
-  {
-    const size_t o = ((size_t)b * T + t1 - 1) * C + c;
-#pragma unroll
-    for (int z = 0; z < K; ++z) ld4(dout.p[z] + o, g[z]);
-    if (t1 - 1 == 0) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) pv[j] = prev[(size_t)b * C + c + j];
-    } else {
-      ld4(x + o - C, pv);
-    }
-  }
-  for (int t = t1 - 1; t >= t0; --t) {
+  const bf16* xb = x + (size_t)b * T * C + c;
+  float cur[4];
+  unpack4(ldraw4(xb + (size_t)(t1 - 1) * C), cur);
+  const uint2 zero2 = make_uint2(0u, 0u);
+  // ga / xa: gradients of token t and x[t-1]; gb / xq: gradients of token t-1 and x[t-2]
+  uint2 ga[K], gb[K], xa = zero2, xq = zero2;
+  auto fetch = [&](int t, uint2 (&g)[K], uint2& xp) {
+    if (t < t0) return;
     const size_t o = ((size_t)b * T + t) * C + c;
-    float gn[K][4], pn[4];
-    const bool more = t - 1 >= t0;
-    if (more) {   // next iteration's token (t - 1): gradients and its predecessor
 #pragma unroll
-      for (int z = 0; z < K; ++z) ld4(dout.p[z] + o - C, gn[z]);
-      if (t - 1 == 0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pn[j] = prev[(size_t)b * C + c + j];
-      } else {
-        ld4(x + o - 2 * (size_t)C, pn);
-      }
+    for (int z = 0; z < K; ++z) g[z] = ldraw4(dout.p[z] + o);
+    if (t > 0) xp = ldraw4(xb + (size_t)(t - 1) * C);
+  };
+  auto step = [&](int t, const uint2 (&g)[K], const uint2 xp) {
+    float pv[4];
+    if (t == 0) {
+      const float4 p = *reinterpret_cast<const float4*>(prev + (size_t)b * C + c);
+      pv[0] = p.x; pv[1] = p.y; pv[2] = p.z; pv[3] = p.w;
+    } else {
+      unpack4(xp, pv);
     }
     float s[4] = {0.f, 0.f, 0.f, 0.f}, n[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int z = 0; z < K; ++z)
+    for (int z = 0; z < K; ++z) {
+      float gv[4];
+      unpack4(g[z], gv);
+      const float4 m4 = *reinterpret_cast<const float4*>(&s_m[z][threadIdx.x * 4]);
+      const float m[4] = {m4.x, m4.y, m4.z, m4.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float gv = g[z][j];
-        s[j] = fmaf(gv, 1.f - m[z][j], s[j]);
-        n[j] = fmaf(gv, m[z][j], n[j]);
-        acc[z][j] = fmaf(gv, pv[j] - cur[j], acc[z][j]);
+        s[j] += gv[j];
+        n[j] = fmaf(gv[j], m[j], n[j]);
+        acc[z][j] = fmaf(gv[j], pv[j] - cur[j], acc[z][j]);
       }
-    {
-      bf162 h0 = __floats2bfloat162_rn(s[0] + carry[0], s[1] + carry[1]);
-      bf162 h1 = __floats2bfloat162_rn(s[2] + carry[2], s[3] + carry[3]);
-      uint2 o2;
-      o2.x = *reinterpret_cast<uint32_t*>(&h0); o2.y = *reinterpret_cast<uint32_t*>(&h1);
-      *reinterpret_cast<uint2*>(dx + o) = o2;
     }
+    // sum_z g (1 - mix) = sum_z g - sum_z g mix
+    bf162 h0 = __floats2bfloat162_rn(s[0] - n[0] + carry[0], s[1] - n[1] + carry[1]);
+    bf162 h1 = __floats2bfloat162_rn(s[2] - n[2] + carry[2], s[3] - n[3] + carry[3]);
+    uint2 o2;
+    o2.x = *reinterpret_cast<uint32_t*>(&h0); o2.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(dx + ((size_t)b * T + t) * C + c) = o2;
 #pragma unroll
     for (int j = 0; j < 4; ++j) { carry[j] = n[j]; cur[j] = pv[j]; }
-    if (more) {
+  };
+  fetch(t1 - 1, ga, xa);
+  fetch(t1 - 2, gb, xq);
+  for (int t = t1 - 1; t >= t0; t -= 2) {
+    uint2 na[K], nb[K], nxa = zero2, nxq = zero2;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) pv[j] = pn[j];
+    for (int z = 0; z < K; ++z) { na[z] = zero2; nb[z] = zero2; }
+    fetch(t - 2, na, nxa);
+    fetch(t - 3, nb, nxq);
+    step(t, ga, xa);
+    if (t - 1 >= t0) step(t - 1, gb, xq);
 #pragma unroll
-      for (int z = 0; z < K; ++z)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) g[z][j] = gn[z][j];
-    }
+    for (int z = 0; z < K; ++z) { ga[z] = na[z]; gb[z] = nb[z]; }
+    xa = nxa; xq = nxq;
   }
   if (t0 == 0) {
 #pragma unroll
@@ -522,8 +514,7 @@ __global__ void __launch_bounds__(128) shift_mix_bwd_wide_kernel(ShiftGrads<K> d
   const int part = blockIdx.z * gridDim.y + blockIdx.y;
 #pragma unroll
   for (int z = 0; z < K; ++z)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) dmix_part[((size_t)part * K + z) * C + c + j] = acc[z][j];
+    *reinterpret_cast<float4*>(dmix_part + ((size_t)part * K + z) * C + c) = make_float4(acc[z][0], acc[z][1], acc[z][2], acc[z][3]);
 }
 
 int shift_mix_parts(int B, int T) { return B * ((T + kShiftSeg - 1) / kShiftSeg); }

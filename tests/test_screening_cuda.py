@@ -66,3 +66,44 @@ def test_scan_kernel_matches_reference(phase, n_slots, d_slot, age_mask):
         a, b = g[name], g_ref[name]
         scale = float(b.abs().max()) + 1e-6
         assert float((a - b).abs().max()) / scale < 5e-3, (name, float((a - b).abs().max()), scale)
+
+
+def test_scan_kernel_long_sequence_default_slot_shape():
+    """T = 1024 steps at the default bank shape of the small presets (16 slots x 128, d_k = d_v = 64, read/write phase):
+    the one-step-ahead prefetch, the carried projections and the per-step saves run for many steps, and the forward
+    results plus the parameter gradients still follow the step-by-step fp32 scan."""
+    torch.manual_seed(5)
+    C, T, B = 128, 1024, 2
+    cfg = ScreeningConfig(d_model=C, d_slot=128, d_k=64, d_v=64, n_slots=16, screened_layers=(0,),
+                          bank_ids=(0,) * 8 + (1,) * 4 + (2,) * 4, use_write_screening=True, write_rel_floor=1e-3)
+    mod = StateLevelScreening(cfg).cuda()
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+        mod.lambda_raw.fill_(0.5)
+    x = torch.randn(B, T, C, device="cuda")
+    h = torch.randn(B, T, C, device="cuda")
+    st = LayerScreenState(slots=torch.randn(B, 16, 128, device="cuda") * 0.3, ages=torch.zeros(B, 16, device="cuda"),
+                          usage_ema=torch.zeros(B, 16, device="cuda"))
+    wy = torch.randn_like(h)
+
+    def run(reference):
+        for p in mod.parameters():
+            p.grad = None
+        xs = x.clone().requires_grad_(True)
+        s0 = LayerScreenState(st.slots.clone(), st.ages.clone(), st.usage_ema.clone())
+        if reference:
+            with ops.reference_mode():
+                out, ns, _ = mod(xs, h, s0, phase="read_write")
+        else:
+            out, ns, _ = mod(xs, h, s0, phase="read_write")
+        (out * wy).sum().backward()
+        return out.detach(), ns.slots.detach(), xs.grad, {n: p.grad.clone() for n, p in mod.named_parameters() if p.grad is not None}
+
+    o_ref, s_ref, gx_ref, g_ref = run(True)
+    o, s, gx, g = run(False)
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-9))
+    assert rel(o, o_ref) < 1e-3 and rel(s, s_ref) < 1e-3
+    assert rel(gx, gx_ref) < 1e-2
+    for name in g_ref:
+        assert rel(g[name], g_ref[name]) < 2e-2, (name, rel(g[name], g_ref[name]))
