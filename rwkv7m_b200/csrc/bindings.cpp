@@ -237,6 +237,16 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor
   return {y, mean, rstd};
 }
 
+// Sum over the partial-row axis of a contiguous fp32 [groups, parts, cols] tensor with this extension's fixed-order kernel.
+static Tensor sum_parts(const Tensor& t) {
+  TORCH_CHECK(t.dim() == 3 && t.is_contiguous() && t.scalar_type() == at::kFloat);
+  const int64_t G = t.size(0), P = t.size(1), C = t.size(2);
+  if (C % 4 != 0) return t.sum(1);
+  Tensor out = torch::empty({G, C}, t.options());
+  rk::partial_sum(t.data_ptr<float>(), out.data_ptr<float>(), (int)G, (int)P, (int)C, (size_t)C, (size_t)(P * C), stream());
+  return out;
+}
+
 std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
                                   const Tensor& rstd, const c10::optional<Tensor>& dres) {
   c10::cuda::CUDAGuard guard(x.device());
@@ -249,7 +259,8 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   // enough 16-byte loads in flight for the one-pass kernel
   int parts = (int)std::min<int64_t>(148 * 6, std::max<int64_t>(1, M / 16));
   auto f32 = x.options().dtype(at::kFloat);
-  Tensor dwp = torch::empty({parts, C}, f32), dbp = torch::empty({parts, C}, f32);
+  Tensor dwb = torch::empty({2, parts, C}, f32);
+  Tensor dwp = dwb[0], dbp = dwb[1];
   const bool has_res = dres.has_value() && dres->defined();
   if (has_res) { check_act(*dres, "dres"); TORCH_CHECK(dres->numel() == x.numel()); }
   const bool fused = rk::layernorm_bwd_res(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), mean.data_ptr<float>(),
@@ -260,7 +271,8 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
                       dx.data_ptr(), dwp.data_ptr<float>(), dbp.data_ptr<float>(), parts, (int)M, (int)C, stream());
     dx.add_(*dres);
   }
-  return {dx, dwp.sum(0), dbp.sum(0)};
+  Tensor sums = sum_parts(dwb);
+  return {dx, sums[0], sums[1]};
 }
 
 Tensor shift_mix_fwd(const Tensor& x, const Tensor& prev, const Tensor& mix) {
@@ -297,7 +309,7 @@ std::vector<Tensor> shift_mix_bwd(const std::vector<Tensor>& dout, const Tensor&
   Tensor dmp = torch::empty({parts, K, C}, f32);
   rk::shift_mix_bwd(gp, x.data_ptr(), prev.data_ptr<float>(), mix.data_ptr<float>(), dx.data_ptr(),
                     dprev.data_ptr<float>(), dmp.data_ptr<float>(), (int)K, (int)B, (int)T, (int)C, stream());
-  return {dx, dprev, dmp.sum(0)};
+  return {dx, dprev, sum_parts(dmp.view({1, parts, K * C})).view({K, C})};
 }
 
 // tmix_pre: acts = [k_raw, v_raw, w_lora, a_lora] (+ [vg_lora, v_first] past layer 0); pars = [w0, a0, k_k, k_a] (+ [v0])
@@ -355,7 +367,7 @@ std::vector<Tensor> tmix_pre_bwd(const std::vector<Tensor>& acts, const std::vec
   // kernel order: dw0, da0, dv0, dk_k, dk_a
   float* gpar[5] = {gpp, gpp + pp, gpp + 4 * pp, gpp + 2 * pp, gpp + 3 * pp};
   rk::tmix_pre_bwd(in, par, gout, gins, gpar, (int)M, (int)C, stream());
-  Tensor sums = gp.sum(1);  // [5, C]: dw0, da0, dk_k, dk_a, dv0
+  Tensor sums = sum_parts(gp);  // [5, C]: dw0, da0, dk_k, dk_a, dv0
   std::vector<Tensor> out = {gin, sums[0], sums[1], sums[2], sums[3]};
   if (has_v) out.push_back(sums[4]);
   return out;
@@ -396,7 +408,7 @@ std::vector<Tensor> gn_bonus_gate_bwd(const std::vector<Tensor>& acts, const std
   const size_t pp = (size_t)parts * C;
   float* gpar[3] = {gpp, gpp + pp, gpp + 2 * pp};
   rk::gn_bonus_gate_bwd(in, par, dout.data_ptr(), gins, gpar, (int)M, (int)C, (float)eps, stream());
-  Tensor sums = gp.sum(1);
+  Tensor sums = sum_parts(gp);
   return {gin, sums[0], sums[1], sums[2]};
 }
 

@@ -1223,4 +1223,65 @@ void embedding_bwd(const int* ids, const void* dout, float* grad, int M, int C, 
   embedding_bwd_kernel<<<blocks, 256, 0, st>>>(ids, (const bf16*)dout, grad, M, C, V);
 }
 
+// ---------------------------------------------------------------------------------
+// Sum of per-block partial rows: in [groups, parts, cols] (row stride `row_stride` floats, group stride `group_stride`)
+// -> out [groups, cols].  One block owns 64 columns of one group: 16 threads across (16-byte loads) by 32 down, the 32
+// row lanes meet in shared memory.  Fixed summation order, so a gradient does not depend on scheduling.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512) partial_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts,
+                                                          int cols, size_t row_stride, size_t group_stride) {
+  __shared__ float4 red[32][17];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int c = blockIdx.x * 64 + tx * 4;
+  const float* src = in + (size_t)blockIdx.y * group_stride;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  if (c + 3 < cols) {
+    int r = ty;
+    for (; r + 32 < parts; r += 64) {
+      const float4 u = __ldg(reinterpret_cast<const float4*>(src + (size_t)r * row_stride + c));
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src + (size_t)(r + 32) * row_stride + c));
+      a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+      b.x += v.x; b.y += v.y; b.z += v.z; b.w += v.w;
+    }
+    if (r < parts) {
+      const float4 u = __ldg(reinterpret_cast<const float4*>(src + (size_t)r * row_stride + c));
+      a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+    }
+  } else {
+    for (int r = ty; r < parts; r += 32) {
+      const float* p = src + (size_t)r * row_stride;
+      if (c < cols) a.x += p[c];
+      if (c + 1 < cols) a.y += p[c + 1];
+      if (c + 2 < cols) a.z += p[c + 2];
+    }
+  }
+  red[ty][tx] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+  __syncthreads();
+  for (int half = 16; half >= 1; half >>= 1) {
+    if (ty < half) {
+      const float4 u = red[ty][tx], v = red[ty + half][tx];
+      red[ty][tx] = make_float4(u.x + v.x, u.y + v.y, u.z + v.z, u.w + v.w);
+    }
+    __syncthreads();
+  }
+  if (ty == 0) {
+    const float4 t = red[0][tx];
+    float* o = out + (size_t)blockIdx.y * cols;
+    if (c + 3 < cols) {
+      *reinterpret_cast<float4*>(o + c) = t;
+    } else {
+      if (c < cols) o[c] = t.x;
+      if (c + 1 < cols) o[c + 1] = t.y;
+      if (c + 2 < cols) o[c + 2] = t.z;
+    }
+  }
+}
+
+// cols and both strides must be multiples of 4 floats and the pointers 16-byte aligned (the callers allocate them so)
+void partial_sum(const float* in, float* out, int groups, int parts, int cols, size_t row_stride, size_t group_stride,
+                 cudaStream_t st) {
+  dim3 grid((cols + 63) / 64, groups);
+  partial_sum_kernel<<<grid, 512, 0, st>>>(in, out, parts, cols, row_stride, group_stride);
+}
+
 }  // namespace rk

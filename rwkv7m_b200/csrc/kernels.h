@@ -78,6 +78,9 @@ void shift_mix_fwd(const void* x, const float* prev, const float* mix, void* out
 void shift_mix_bwd(const void* const* dout, const void* x, const float* prev, const float* mix, void* dx,
                    float* dprev, float* dmix_part, int K, int B, int T, int C, cudaStream_t st);
 int row_parts(int M);
+// out[g, c] = sum_p in[g * group_stride + p * row_stride + c]; cols and the strides are multiples of 4 floats
+void partial_sum(const float* in, float* out, int groups, int parts, int cols, size_t row_stride, size_t group_stride,
+                 cudaStream_t st);
 // in: k_raw, v_raw, w_lora, a_lora, vg_lora, v_first (last two null on layer 0); par: w0, a0, v0, k_k, k_a;
 // out: w, k_mod, v, neg_kk, kka
 void tmix_pre_fwd(const void* const* in, const float* const* par, void* const* out, int M, int C, cudaStream_t st);

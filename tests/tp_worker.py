@@ -29,7 +29,7 @@ def main():
     from rwkv7m_b200.parallel.tp import TensorParallel
 
     # heads, FFN width, vocabulary and sequence length must all divide by the group size
-    heads = 4 if world <= 4 else 8
+    heads = int(os.environ.get("TP_TEST_HEADS", 4 if world <= 4 else 8))
     cfg = R.ModelConfig(d_model=64 * heads, d_ffn=128 * heads, n_layers=2, n_heads=heads, head_size=64, vocab_size=512,
                         max_seq_len=64, dtype="bfloat16", use_screening=False, warmup_steps=0, lr_init=1e-3)
     C = cfg.d_model
