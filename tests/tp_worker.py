@@ -40,11 +40,15 @@ def main():
     def run(tp):
         rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=50, device=dev, tp=tp)
         losses = []
-        for _ in range(3):
+        for step in range(3):
             ts, m = R.train_batch(ts, batch, rt)
             losses.append(float(m["loss"]))
-        params = tp.gather_full_parameters(ts.model) if tp is not None else dict(ts.model.named_parameters())
-        params = {n: p.detach().float().clone() for n, p in params.items()}
+            if step == 0:
+                # parameters are compared after the first update: this toy memorises its one batch within a step (the
+                # loss falls from 6.3 to 0.3 and then overshoots), and from there bf16 rounding differences between
+                # the two partitions of the same sums grow from step to step
+                params = tp.gather_full_parameters(ts.model) if tp is not None else dict(ts.model.named_parameters())
+                params = {n: p.detach().float().clone() for n, p in params.items()}
         if tp is None or tp.fused is None:
             traces["ref" if tp is None else f"tp_vp{int(tp.vocab_parallel)}"] = [
                 decode_trace(ts.model, rt.initial_rwkv_state, graph) for graph in ((False,) if tp is None else (False, True))]
