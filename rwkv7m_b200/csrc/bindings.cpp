@@ -620,7 +620,7 @@ rk::ScreenScanArgs screen_args(const Tensor& q_r, const Tensor& q_w, const Tenso
   a.M = (int)slots0.size(1); a.ds = (int)slots0.size(2);
   a.dv = (int)WT.size(1) - 2 * a.dk;
   const int J = (int)WT.size(1);
-  TORCH_CHECK(f.size() == 8, "expected 8 scalar settings");
+  TORCH_CHECK(f.size() == 8 || f.size() == 11, "expected 8 scalar settings (+ leaky flag, alpha, gamma)");
   TORCH_CHECK(WT.size(0) == a.ds && a.dv >= 1, "weight shapes");
   TORCH_CHECK(PD.dim() == 4 && PD.size(0) == a.B && PD.size(1) == a.T && PD.size(2) == 16 && PD.size(3) == J,
               "PD must be [B, T, 16, J]");
@@ -630,11 +630,12 @@ rk::ScreenScanArgs screen_args(const Tensor& q_r, const Tensor& q_w, const Tenso
   a.tau_r = (float)f[0]; a.tau_w = (float)f[1]; a.eps = (float)f[2]; a.cap = (float)f[3]; a.write_rel_floor = (float)f[4];
   a.usage_decay = (float)f[5]; a.age_ref = (float)f[6]; a.age_sigma = (float)f[7];
   a.write_enabled = write_enabled; a.value_unit_norm = value_unit_norm; a.age_mask = age_mask;
+  if (f.size() == 11) { a.leaky = f[8] != 0.0; a.leaky_alpha = (float)f[9]; a.leaky_gamma = (float)f[10]; }
   TORCH_CHECK(rk::screen_scan_supported(a), "screening scan: unsupported sizes");
   return a;
 }
 
-// returns u, slots_out, ages_out, usage_out, stats[9], saved_slots, saved_ages, saved_P
+// returns u, slots_out, ages_out, usage_out, stats[9], strength [B,T,16], saved_ages, saved_P
 std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const Tensor& delta_xh, const Tensor& delta_slot,
                                     const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
@@ -649,16 +650,16 @@ std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const 
   Tensor u = torch::empty({a.B, a.T, a.dv}, o);
   Tensor so = torch::empty_like(slots0), ao = torch::empty_like(ages0), uo = torch::empty_like(usage0);
   Tensor stats = torch::zeros({9}, o);
-  Tensor saved = save ? torch::empty({a.B, a.T, a.ds, 16}, o) : torch::empty({0}, o);
+  Tensor strength = torch::empty({a.B, a.T, 16}, o);
   Tensor saved_ages = save ? torch::empty({a.B, a.T, 16}, o) : torch::empty({0}, o);
   Tensor saved_P = save ? torch::empty({a.B, a.T, 16, J}, o) : torch::empty({0}, o);
   a.u_out = u.data_ptr<float>(); a.slots_out = so.data_ptr<float>(); a.ages_out = ao.data_ptr<float>();
   a.usage_out = uo.data_ptr<float>(); a.stats = stats.data_ptr<float>();
-  a.saved_slots = save ? saved.data_ptr<float>() : nullptr;
+  a.strength = strength.data_ptr<float>();
   a.saved_ages = save ? saved_ages.data_ptr<float>() : nullptr;
   a.saved_P = save ? saved_P.data_ptr<float>() : nullptr;
   TORCH_CHECK(rk::screen_scan_forward(a, stream()) == 0, "screen_scan_forward failed");
-  return {u, so, ao, uo, stats, saved, saved_ages, saved_P};
+  return {u, so, ao, uo, stats, strength, saved_ages, saved_P};
 }
 
 // returns d q_r, d q_w, d delta_xh (direct part), d delta_slot (direct part), d slots0 (direct part), d mu,
@@ -667,7 +668,7 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
                                     const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
-                                    const Tensor& saved, const Tensor& saved_ages, const Tensor& saved_P, const Tensor& du,
+                                    const Tensor& strength, const Tensor& saved_ages, const Tensor& saved_P, const Tensor& du,
                                     const c10::optional<Tensor>& dslots_out, const c10::optional<Tensor>& tau_dev) {
   c10::cuda::CUDAGuard guard(q_r.device());
   rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
@@ -675,18 +676,29 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
   if (tau_dev.has_value() && tau_dev->defined()) { TORCH_CHECK(tau_dev->numel() == 2); a.tau_dev = fptr(*tau_dev); }
   auto o = q_r.options();
   const int J = 2 * a.dk + a.dv;
-  TORCH_CHECK(saved_P.numel() == (int64_t)a.B * a.T * 16 * J && saved.numel() == (int64_t)a.B * a.T * a.ds * 16,
-              "saved tensors do not match the problem size");
-  Tensor dqr = torch::empty_like(q_r), dqw = torch::zeros_like(q_r), dxh = torch::empty_like(delta_xh);
-  Tensor dds = torch::zeros_like(delta_slot), ds0 = torch::empty_like(slots0), dmu = torch::zeros_like(mu);
+  TORCH_CHECK(saved_P.numel() == (int64_t)a.B * a.T * 16 * J && strength.numel() == (int64_t)a.B * a.T * 16 &&
+                  saved_ages.numel() == (int64_t)a.B * a.T * 16, "saved tensors do not match the problem size");
+  const bool bank = dslots_out.has_value() && dslots_out->defined();
+  Tensor dqr = torch::empty_like(q_r), dqw = torch::zeros_like(q_r);
+  // without a cotangent for the final bank nothing reaches delta_xh, delta_slot or the initial bank directly
+  Tensor dxh = bank ? torch::empty_like(delta_xh) : torch::zeros_like(delta_xh);
+  Tensor ds0 = bank ? torch::empty_like(slots0) : torch::zeros_like(slots0);
+  Tensor dds = torch::zeros_like(delta_slot), dmu = torch::zeros_like(mu);
   Tensor dsc = torch::zeros({2}, o);
   Tensor dPD = torch::empty({a.B, a.T, 16, J}, o);
   Tensor dP0 = torch::empty({a.B, 16, J}, o);
-  a.saved_slots = const_cast<float*>(fptr(saved)); a.saved_ages = const_cast<float*>(fptr(saved_ages));
+  a.strength = const_cast<float*>(fptr(strength)); a.saved_ages = const_cast<float*>(fptr(saved_ages));
   a.saved_P = const_cast<float*>(fptr(saved_P));
   a.du = fptr(du);
-  Tensor dso;
-  if (dslots_out.has_value() && dslots_out->defined()) { dso = dslots_out->contiguous().to(at::kFloat); a.dslots_out = dso.data_ptr<float>(); }
+  Tensor dso, ws;
+  if (bank) {
+    dso = dslots_out->contiguous().to(at::kFloat);
+    TORCH_CHECK(dso.numel() == slots0.numel(), "final-bank cotangent must match the bank");
+    a.dslots_out = dso.data_ptr<float>();
+    ws = torch::empty({3 * (int64_t)a.B * a.T * 16 + (int64_t)a.B * 16}, o);
+    const int64_t n = (int64_t)a.B * a.T * 16;
+    a.ws_h = ws.data_ptr<float>(); a.ws_G = a.ws_h + n; a.ws_coef = a.ws_G + n; a.ws_c0 = a.ws_coef + n;
+  }
   a.d_q_r = dqr.data_ptr<float>(); a.d_q_w = dqw.data_ptr<float>(); a.d_delta_xh = dxh.data_ptr<float>();
   a.d_PD = dPD.data_ptr<float>(); a.d_P0 = dP0.data_ptr<float>();
   a.d_delta_slot = dds.data_ptr<float>(); a.d_slots0 = ds0.data_ptr<float>();

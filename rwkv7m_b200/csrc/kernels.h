@@ -154,16 +154,21 @@ struct ScreenScanArgs {
   const float* tau_dev;         // [2] tau_r, tau_w on the device; when set it replaces the two host values above, so the
                                 // learned thresholds never have to be read back to the host
   bool write_enabled, value_unit_norm, age_mask;
+  bool leaky;                   // read relevance = (1 - alpha) trim_square + alpha sigmoid(gamma (sim - tau_r))
+  float leaky_alpha, leaky_gamma;
   // forward outputs
   float* u_out;                 // [B,T,dv]
   float *slots_out, *ages_out, *usage_out;
   float* stats;                 // [9] running sums over batch rows and steps
-  float* saved_slots;           // [B,T,ds,16] bank before each step (nullptr = inference)
-  float* saved_ages;            // [B,T,16]
+  float* strength;              // [B,T,16] write strength of every step and slot (forward output, backward input)
+  float* saved_ages;            // [B,T,16]   ages before each step (nullptr with saved_P = inference)
   float* saved_P;               // [B,T,16,J] raw projections before each step
   // backward
   const float* du;              // [B,T,dv]
-  const float* dslots_out;      // [B,M,ds] or nullptr
+  const float* dslots_out;      // [B,M,ds] cotangent of the final bank, or nullptr (then d_delta_xh, d_delta_slot and
+                                // d_slots0 are left untouched: the caller zeroes them)
+  float *ws_h, *ws_G, *ws_coef; // [B,T,16] workspaces of the bank path (needed with dslots_out)
+  float* ws_c0;                 // [B,16]
   float *d_q_r, *d_q_w, *d_delta_xh;      // [B,T,dk], [B,T,dk], [B,T,ds]
   float* d_PD;                  // [B,T,16,J] cotangent of PD
   float* d_P0;                  // [B,16,J]   cotangent of the projections of the initial bank

@@ -1,21 +1,27 @@
-// State-level screening memory: the slot-dependent part of the layer, sequential over time, as one kernel per
-// direction.  One CTA (256 threads) owns one batch row and walks the T steps; the slot bank S [M, ds] lives in
-// shared memory (transposed, [ds][16]).
+// State-level screening memory: the slot-dependent part of the layer as kernels.
 //
 // Per step t (names follow src/rwkv7m/model/nnx_model.py:1024-1159 and src/rwkv7m/model/screening.py:11-88):
 //   k_r[m] = unit(S[m] Wk^T)   val[m] = unit(S[m] Wv^T)   k_w[m] = unit((S[m] + E[m]) Wkw^T)
 //   rel_r[m] = trim_square(q_r[t] . k_r[m], tau_r) (* age mask)      rel_w[m] = trim_square(q_w[t] . k_w[m], tau_w)
 //   u[t]    = tanh_norm(sum_m rel_r[m] val[m])                       (output; the out-projection is a GEMM outside)
-//   S[m]   += mu[m] * max(rel_w[m], floor) * (tanh(dxh[t] + dslot[m]) - S[m])     (rate mu[m] alone without write screening)
-// The raw projections P[m] = S[m] W^T (+ E[m] Wkw^T for the write keys; W^T [ds][J], J = dk + dv + dk) are never
-// recomputed inside the loop.  The slot update is an interpolation towards a vector that does not depend on the state,
-//   S_{t+1}[m] = S_t[m] + s_m (D_t[m] - S_t[m]),   D_t[m] = tanh(dxh[t] + dslot[m]),
-// and the projections are linear, so they obey the same recurrence:
-//   P_{t+1}[m] = P_t[m] + s_m (PD_t[m] - P_t[m]),  PD_t[m] = D_t[m] W^T (+ E[m] Wkw^T),
-// where PD for all steps is one GEMM done by the caller before the scan.  A step therefore costs O(M (ds + J)) instead
-// of O(M ds J).  The backward kernel walks the steps in reverse from the saved per-step S and P, carries the cotangents
-// of both, and returns the gradients of q_r, q_w, dxh, dslot (direct part), PD, the initial S and P, and the scalars;
-// the caller turns d PD into weight / dxh / dslot gradients with GEMMs over all steps at once.
+//   S[m]   += s_t[m] (tanh(dxh[t] + dslot[m]) - S[m]),   s_t[m] = mu[m] * max(rel_w[m], floor)   (mu[m] alone without
+//                                                                                                  write screening)
+// Two observations split the work into one sequential kernel of width J = dk + dv + dk and a few parallel ones of
+// width ds (the slot width, up to 1024):
+//  (1) The update interpolates towards a target D_t[m] = tanh(dxh[t] + dslot[m]) that does not depend on the state, and
+//      the raw projections P[m] = S[m] W^T (+ E[m] Wkw^T on the write keys) are linear in S, so they obey
+//        P_{t+1}[m] = P_t[m] + s_t[m] (PD_t[m] - P_t[m]),   PD_t[m] = D_t[m] W^T (+ E[m] Wkw^T),
+//      where PD for all steps is one GEMM done by the caller.  Everything a step decides (norms, similarities,
+//      relevances, the read-out, the write strengths) follows from P alone: the sequential kernel carries only P.
+//  (2) Given the strengths s_t[m] the bank itself is an independent scalar recurrence per element: a parallel kernel
+//      over (batch, slot, d) produces the final bank and the update-norm statistic.  In backward the bank's cotangent is
+//      dS_{t+1}[m] = c_{t+1}[m] dS_T[m] with c the suffix products of (1 - s), so the strength cotangent that comes
+//      through the bank is c_{t+1}[m] (h_t[m] - e_t[m]) with h_t[m] = <dS_T[m], D_t[m]> (parallel over all steps) and
+//      e_t[m] = <dS_T[m], S_t[m]>, which follows the same scalar recurrence as the bank.  The sequential backward
+//      kernel receives that number per (step, slot) and never touches a ds-wide vector; the dxh / dslot / initial-bank
+//      gradients of the bank path are one more parallel kernel.
+// The sequential kernels run one CTA of 16 warps per batch row: warp m owns slot m in the per-slot phases, thread j owns
+// columns j and j + 512 of the projections in the per-column phases.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -23,108 +29,148 @@ namespace rk {
 
 namespace {
 
-constexpr int kMp = 16;      // slots are padded to 16
-constexpr int kJp = 256;     // row stride of the raw projections
-constexpr int kThreads = 256;
-constexpr int kSc = 12;     // per-slot scalars: nk, nv, nw, simr, simw, relr, relw, strength, relr / nv
+constexpr int kMp = 16;            // slots are padded to 16
+constexpr int kSeqThreads = 512;   // 16 warps
+constexpr int kSc = 12;            // per-slot scalars: nk, nv, nw, simr, simw, relr, relw, strength, relr / nv
+constexpr int kTileD = 64;         // rows of the bank staged at a time for the initial projections
 
-__device__ __forceinline__ float trim_sq(float sim, float tau, float eps, float& x_out) {
+__device__ __forceinline__ float trim_sq(float sim, float tau, float eps) {
   const float x = fmaxf((sim - tau) / (1.f - tau + eps), 0.f);
-  x_out = x;
   return x * x;
 }
 
-struct ScanSmem {
-  float* St;     // [ds][16]   slots, transposed
-  float* DSt;    // [ds][16]   delta_slot, transposed
-  float* P;      // [16][256]  raw projections of the current step
-  float* PD;     // [16][256]  projections of the step's write target
-  float* EW;     // [16][dk]   slot_embed Wkw^T
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// read relevance before the age mask, and its derivatives with respect to the similarity and the threshold
+__device__ __forceinline__ float read_relevance(float sim, const ScreenScanArgs& a) {
+  if (!a.leaky) return trim_sq(sim, a.tau_r, a.eps);
+  return (1.f - a.leaky_alpha) * trim_sq(sim, a.tau_r, 1e-6f) + a.leaky_alpha * sigmoidf_(a.leaky_gamma * (sim - a.tau_r));
+}
+
+__device__ __forceinline__ void read_relevance_grad(float sim, const ScreenScanArgs& a, float& d_sim, float& d_tau) {
+  const float e = a.leaky ? 1e-6f : a.eps;
+  const float den = 1.f - a.tau_r + e;
+  const float x = fmaxf((sim - a.tau_r) / den, 0.f);
+  d_sim = 2.f * x / den;
+  d_tau = 2.f * x * (sim - 1.f - e) / (den * den);
+  if (a.leaky) {
+    const float sg = sigmoidf_(a.leaky_gamma * (sim - a.tau_r));
+    const float ds = a.leaky_gamma * sg * (1.f - sg);
+    d_sim = (1.f - a.leaky_alpha) * d_sim + a.leaky_alpha * ds;
+    d_tau = (1.f - a.leaky_alpha) * d_tau - a.leaky_alpha * ds;
+  }
+}
+
+__host__ __device__ inline int padded_J(int J) { return (J + 3) & ~3; }
+
+struct SeqSmem {
+  float* P;      // [16][Jp]  raw projections of the current step (backward: two copies, alternating by step parity)
+  float* PD;     // [16][Jp]  backward: projections of the step's write target
+  float* dP;     // [16][Jp]  backward: cotangent of the carried projections
+  float* EW;     // [16][dk]  forward: slot_embed Wkw^T
+  float* tile;   // [64][16]  forward: rows of the bank staged for the initial projections
   float* qr;     // [dk]
   float* qw;     // [dk]
-  float* dxh;    // [ds]
   float* z;      // [dv]
-  float* sc;     // [16][kSc]  per-slot scalars
+  float* du;     // [dv]      backward
+  float* dz;     // [dv]      backward
+  float* sc;     // [16][kSc] per-slot scalars
   float* ages;   // [16]
   float* usage;  // [16]
-  float* upd;    // [16]       squared update norm of the step
+  float* dstr;   // [16]      backward: cotangent of the write strength
+  float* dsimr;  // [16]
+  float* dsimw;  // [16]
 };
 
-__device__ __forceinline__ ScanSmem carve(float* base, int ds, int dk, int dv) {
-  ScanSmem s;
-  s.St = base; base += ds * kMp;
-  s.DSt = base; base += ds * kMp;
-  s.P = base; base += kMp * kJp;
-  s.PD = base; base += kMp * kJp;
-  s.EW = base; base += kMp * dk;
+__host__ __device__ inline int seq_smem_floats(int J, int dk, int dv, bool backward) {
+  const int Jp = padded_J(J);
+  int n = kMp * Jp * (backward ? 4 : 1) + 2 * dk + dv + kMp * kSc + 2 * kMp;
+  n += backward ? 2 * dv + 3 * kMp : kMp * dk + kTileD * kMp;
+  return n + 8;
+}
+
+__device__ __forceinline__ SeqSmem carve(float* base, int J, int dk, int dv, bool backward) {
+  const int Jp = padded_J(J);
+  SeqSmem s{};
+  s.P = base; base += kMp * Jp * (backward ? 2 : 1);
+  if (backward) {
+    s.PD = base; base += kMp * Jp;
+    s.dP = base; base += kMp * Jp;
+    s.du = base; base += dv;
+    s.dz = base; base += dv;
+    s.dstr = base; base += kMp;
+    s.dsimr = base; base += kMp;
+    s.dsimw = base; base += kMp;
+  } else {
+    s.EW = base; base += kMp * dk;
+    s.tile = base; base += kTileD * kMp;
+  }
   s.qr = base; base += dk;
   s.qw = base; base += dk;
-  s.dxh = base; base += ds;
   s.z = base; base += dv;
   s.sc = base; base += kMp * kSc;
   s.ages = base; base += kMp;
   s.usage = base; base += kMp;
-  s.upd = base; base += kMp;
   return s;
 }
 
-__host__ __device__ inline int scan_smem_floats(int ds, int dk, int dv) {
-  return 2 * ds * kMp + 2 * kMp * kJp + kMp * dk + 2 * dk + ds + dv + kMp * kSc + 3 * kMp + 8 * kMp /*per-warp update norms*/;
-}
-
-// raw projections of all slots: P[m][j] = sum_d St[d][m] * WT[d][j]  (+ EW for the write keys)
-template <bool SMEM_W>
-__device__ __forceinline__ void project(const ScanSmem& s, const float* __restrict__ WT, int wstride, int ds, int J, int dk,
-                                        int dv, int tid, bool add_ew) {
-  if (tid < J) {
-    float acc[kMp];
+// acc[c][m] = sum_d src[m][d] * WT[d][j], j = tid + c * 512: the [M, ds] source is staged 64 rows of d at a time
+template <int CPT>
+__device__ __forceinline__ void project_rows(const float* __restrict__ src, const ScreenScanArgs& a, float* tile, int J,
+                                             int tid, float (&acc)[CPT][kMp]) {
 #pragma unroll
-    for (int m = 0; m < kMp; ++m) acc[m] = 0.f;
-#pragma unroll 4
-    for (int d = 0; d < ds; ++d) {
-      const float w = SMEM_W ? WT[d * wstride + tid] : __ldg(WT + (size_t)d * wstride + tid);
-      const float4* sp = reinterpret_cast<const float4*>(s.St + d * kMp);
-      const float4 a = sp[0], b = sp[1], c = sp[2], e = sp[3];
-      acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
-      acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]); acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
-      acc[8] = fmaf(w, c.x, acc[8]); acc[9] = fmaf(w, c.y, acc[9]); acc[10] = fmaf(w, c.z, acc[10]); acc[11] = fmaf(w, c.w, acc[11]);
-      acc[12] = fmaf(w, e.x, acc[12]); acc[13] = fmaf(w, e.y, acc[13]); acc[14] = fmaf(w, e.z, acc[14]); acc[15] = fmaf(w, e.w, acc[15]);
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) acc[c][m] = 0.f;
+  for (int d0 = 0; d0 < a.ds; d0 += kTileD) {
+    __syncthreads();
+    for (int e = tid; e < kTileD * kMp; e += kSeqThreads) {
+      const int dd = e / kMp, m = e % kMp;
+      tile[e] = (m < a.M && d0 + dd < a.ds) ? __ldg(src + (size_t)m * a.ds + d0 + dd) : 0.f;
     }
-    const bool is_kw = tid >= dk + dv;
+    __syncthreads();
+    const int nd = min(kTileD, a.ds - d0);
 #pragma unroll
-    for (int m = 0; m < kMp; ++m) s.P[m * kJp + tid] = acc[m] + ((add_ew && is_kw) ? s.EW[m * dk + tid - dk - dv] : 0.f);
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j >= J) continue;
+      for (int dd = 0; dd < nd; ++dd) {
+        const float w = __ldg(a.WT + (size_t)(d0 + dd) * J + j);
+        const float4* sp = reinterpret_cast<const float4*>(tile + dd * kMp);
+        const float4 p = sp[0], q = sp[1], r = sp[2], t = sp[3];
+        acc[c][0] = fmaf(w, p.x, acc[c][0]); acc[c][1] = fmaf(w, p.y, acc[c][1]); acc[c][2] = fmaf(w, p.z, acc[c][2]);
+        acc[c][3] = fmaf(w, p.w, acc[c][3]); acc[c][4] = fmaf(w, q.x, acc[c][4]); acc[c][5] = fmaf(w, q.y, acc[c][5]);
+        acc[c][6] = fmaf(w, q.z, acc[c][6]); acc[c][7] = fmaf(w, q.w, acc[c][7]); acc[c][8] = fmaf(w, r.x, acc[c][8]);
+        acc[c][9] = fmaf(w, r.y, acc[c][9]); acc[c][10] = fmaf(w, r.z, acc[c][10]); acc[c][11] = fmaf(w, r.w, acc[c][11]);
+        acc[c][12] = fmaf(w, t.x, acc[c][12]); acc[c][13] = fmaf(w, t.y, acc[c][13]); acc[c][14] = fmaf(w, t.z, acc[c][14]);
+        acc[c][15] = fmaf(w, t.w, acc[c][15]);
+      }
+    }
   }
 }
 
-// per-slot norms, similarities, relevances and the write strength; half-warp h (16 lanes) handles slot h
-__device__ __forceinline__ float half_sum(float v) {
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-
-__device__ __forceinline__ void slot_scalars(const ScanSmem& s, const ScreenScanArgs& a, int warp, int lane) {
-  const int m = warp * 2 + (lane >> 4), hl = lane & 15;
-  const float* Pm = s.P + m * kJp;
+// norms, similarities, relevances and the write strength of slot m from its row of raw projections (one warp)
+__device__ __forceinline__ void slot_scalars(const float* __restrict__ Pm, const SeqSmem& s, const ScreenScanArgs& a, int m,
+                                             int lane) {
   float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f;
-  for (int j = hl; j < a.dk; j += 16) { const float x = Pm[j]; sk = fmaf(x, x, sk); dkq = fmaf(x, s.qr[j], dkq); }
-  for (int j = hl; j < a.dv; j += 16) { const float x = Pm[a.dk + j]; sv = fmaf(x, x, sv); }
+  for (int j = lane; j < a.dk; j += 32) { const float x = Pm[j]; sk = fmaf(x, x, sk); dkq = fmaf(x, s.qr[j], dkq); }
+  for (int j = lane; j < a.dv; j += 32) { const float x = Pm[a.dk + j]; sv = fmaf(x, x, sv); }
   if (a.write_enabled)
-    for (int j = hl; j < a.dk; j += 16) { const float x = Pm[a.dk + a.dv + j]; sw = fmaf(x, x, sw); dwq = fmaf(x, s.qw[j], dwq); }
-  sk = half_sum(sk); dkq = half_sum(dkq); sv = half_sum(sv); sw = half_sum(sw); dwq = half_sum(dwq);
-  if (hl == 0) {
+    for (int j = lane; j < a.dk; j += 32) { const float x = Pm[a.dk + a.dv + j]; sw = fmaf(x, x, sw); dwq = fmaf(x, s.qw[j], dwq); }
+  sk = warp_sum(sk); dkq = warp_sum(dkq); sv = warp_sum(sv);
+  if (a.write_enabled) { sw = warp_sum(sw); dwq = warp_sum(dwq); }
+  if (lane == 0) {
     float* c = s.sc + m * kSc;
     const float e2 = a.eps * a.eps;
     const float nk = sqrtf(sk + e2), nv = a.value_unit_norm ? sqrtf(sv + e2) : 1.f, nw = sqrtf(sw + e2);
     const float simr = dkq / nk, simw = dwq / nw;
-    float xr, xw;
-    float relr = trim_sq(simr, a.tau_r, a.eps, xr);
-    if (a.age_mask) relr *= 1.f / (1.f + __expf(-(a.age_ref - s.ages[m]) / (a.age_sigma + a.eps)));
+    float relr = read_relevance(simr, a);
+    if (a.age_mask) relr *= sigmoidf_((a.age_ref - s.ages[m]) / (a.age_sigma + a.eps));
     const bool live = m < a.M;
     if (!live) relr = 0.f;
     float relw = 0.f, strength = live ? a.mu[m] : 0.f;
     if (a.write_enabled && live) {
-      relw = trim_sq(simw, a.tau_w, a.eps, xw);
+      relw = trim_sq(simw, a.tau_w, a.eps);
       strength *= fmaxf(relw, a.write_rel_floor);
     }
     c[0] = nk; c[1] = nv; c[2] = nw; c[3] = simr; c[4] = simw; c[5] = relr; c[6] = relw; c[7] = strength;
@@ -132,94 +178,103 @@ __device__ __forceinline__ void slot_scalars(const ScanSmem& s, const ScreenScan
   }
 }
 
-template <bool SMEM_W>
-__global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArgs a) {
+// ------------------------------------------------------------------------------------------------------------------
+// Sequential forward: u, the write strengths, ages, usage and the logged statistics; saves P and the ages per step.
+// ------------------------------------------------------------------------------------------------------------------
+template <int CPT>
+__global__ void __launch_bounds__(kSeqThreads) screen_seq_fwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
   if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
-  const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
+  const int J = 2 * a.dk + a.dv, Jp = padded_J(J);
+  const SeqSmem s = carve(smem_f, J, a.dk, a.dv, false);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x;
-  const int J = 2 * a.dk + a.dv;
-  const int nel = a.ds * kMp;
-  // the projection weights are only needed for the initial bank: they stream through L1 / L2 once
-  const float* WTp = a.WT;
-  const int wstride = J;
 
-  // ---- load the bank, delta_slot and the slot embedding (all transposed to [d][16]) ----------------------------------
-  for (int e = tid; e < nel; e += kThreads) {
-    const int d = e / kMp, m = e % kMp;
-    const bool live = m < a.M;
-    s.St[e] = live ? a.slot_embed[m * a.ds + d] : 0.f;
-    s.DSt[e] = live ? a.delta_slot[m * a.ds + d] : 0.f;
-  }
   if (tid < kMp) {
     s.ages[tid] = tid < a.M ? a.ages0[b * a.M + tid] : 0.f;
     s.usage[tid] = tid < a.M ? a.usage0[b * a.M + tid] : 0.f;
   }
-  float* updw = s.upd + kMp;   // [8 warps][16] partial squared update norms of the current step
-  __syncthreads();
-  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, false);   // E Wkw^T (only the write-key columns are kept)
-  __syncthreads();
-  for (int e = tid; e < kMp * a.dk; e += kThreads) s.EW[e] = s.P[(e / a.dk) * kJp + a.dk + a.dv + e % a.dk];
-  __syncthreads();
-  for (int e = tid; e < nel; e += kThreads) {
-    const int d = e / kMp, m = e % kMp;
-    s.St[e] = m < a.M ? a.slots0[((size_t)b * a.M + m) * a.ds + d] : 0.f;
+  {
+    float acc[CPT][kMp];
+    // E Wkw^T: only the write-key columns are kept
+    project_rows<CPT>(a.slot_embed, a, s.tile, J, tid, acc);
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j >= a.dk + a.dv && j < J) {
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) s.EW[m * a.dk + j - a.dk - a.dv] = acc[c][m];
+      }
+    }
+    // projections of the initial bank (the only pass over the weights); afterwards they follow the slot recurrence
+    project_rows<CPT>(a.slots0 + (size_t)b * a.M * a.ds, a, s.tile, J, tid, acc);
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j < J) {
+        const bool is_kw = j >= a.dk + a.dv;   // this thread wrote these EW entries itself
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) s.P[m * Jp + j] = acc[c][m] + (is_kw ? s.EW[m * a.dk + j - a.dk - a.dv] : 0.f);
+      }
+    }
   }
   float st_acc[9];
 #pragma unroll
   for (int i = 0; i < 9; ++i) st_acc[i] = 0.f;
-  __syncthreads();
 
-  // projections of the initial bank (the only pass over the weights); afterwards they follow the slot recurrence
-  project<SMEM_W>(s, WTp, wstride, a.ds, J, a.dk, a.dv, tid, true);
-
-  // the step's vectors are fetched one step ahead into registers (thread tid: q_r / q_w element tid, delta_xh element tid,
-  // column tid of the write target's projections for all 16 slots)
-  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f;
-  float n_pd[kMp];
+  // the step's vectors are fetched one step ahead into registers
+  float n_qr = 0.f, n_qw = 0.f;
+  float n_pd[CPT][kMp];
 #pragma unroll
-  for (int m = 0; m < kMp; ++m) n_pd[m] = 0.f;
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) n_pd[c][m] = 0.f;
   auto fetch = [&](int t) {
     const size_t bt = (size_t)b * a.T + t;
     if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
-    if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
-    if (tid < J) {
-      const float* src = a.PD + bt * kMp * J + tid;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) n_pd[m] = src[m * J];
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j < J) {
+        const float* src = a.PD + bt * kMp * J + j;
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) n_pd[c][m] = src[m * J];
+      }
     }
   };
   fetch(0);
   for (int t = 0; t < a.T; ++t) {
     const size_t bt = (size_t)b * a.T + t;
-    // ---- stage the step's vectors; save the bank and its projections for the backward pass -------------------------------
     if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
-    if (tid < a.ds) s.dxh[tid] = n_dx;
-    float pd[kMp];
+    float pd[CPT][kMp];
 #pragma unroll
-    for (int m = 0; m < kMp; ++m) pd[m] = n_pd[m];
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+      for (int m = 0; m < kMp; ++m) pd[c][m] = n_pd[c][m];
     if (t + 1 < a.T) fetch(t + 1);
-    __syncthreads();   // s.P and s.St of this step are complete (written at the end of the previous iteration)
-    if (a.saved_slots != nullptr) {
-      float* dst = a.saved_slots + bt * nel;
-      for (int e = tid; e < nel; e += kThreads) dst[e] = s.St[e];
+    __syncthreads();   // P of this step is complete (written at the end of the previous iteration); q staged
+    if (a.saved_P != nullptr) {
       if (tid < kMp) a.saved_ages[bt * kMp + tid] = s.ages[tid];
-      if (tid < J) {
-        float* dp = a.saved_P + bt * kMp * J + tid;
 #pragma unroll
-        for (int m = 0; m < kMp; ++m) dp[m * J] = s.P[m * kJp + tid];
+      for (int c = 0; c < CPT; ++c) {
+        const int j = tid + c * kSeqThreads;
+        if (j < J) {
+          float* dp = a.saved_P + bt * kMp * J + j;
+#pragma unroll
+          for (int m = 0; m < kMp; ++m) dp[m * J] = s.P[m * Jp + j];
+        }
       }
     }
-    slot_scalars(s, a, warp, lane);
+    slot_scalars(s.P + warp * Jp, s, a, warp, lane);
     __syncthreads();
-    // ---- read-out ----------------------------------------------------------------------------------------------------------
+    // ---- read-out -------------------------------------------------------------------------------------------------
     if (tid < a.dv) {
       float acc = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * kJp + a.dk + tid], acc);
+      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * Jp + a.dk + tid], acc);
       s.z[tid] = acc;
     }
+    if (tid < kMp) a.strength[bt * kMp + tid] = s.sc[tid * kSc + 7];
     __syncthreads();
     float zn2 = 0.f;
     for (int v = lane; v < a.dv; v += 32) zn2 = fmaf(s.z[v], s.z[v], zn2);
@@ -227,31 +282,19 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
     const float zn = sqrtf(zn2 + a.eps * a.eps);
     const float f = a.cap * tanhf(zn / a.cap) / zn;
     if (tid < a.dv) a.u_out[bt * a.dv + tid] = f * s.z[tid];
-    // ---- slot update ---------------------------------------------------------------------------------------------------------
-    {
-      const int m = tid % kMp;   // every element this thread touches belongs to the same slot (= lane & 15)
-      const float strength = s.sc[m * kSc + 7];
-      float un = 0.f;
-      for (int e = tid; e < nel; e += kThreads) {
-        const int d = e / kMp;
-        const float old = s.St[e];
-        const float delta = tanhf(s.dxh[d] + s.DSt[e]);
-        const float nw = old + strength * (delta - old);
-        s.St[e] = nw;
-        un = fmaf(nw - old, nw - old, un);
-      }
-      un += __shfl_xor_sync(0xffffffffu, un, 16);
-      if (lane < kMp) updw[warp * kMp + m] = un;   // per-warp partial of the squared update norm (no atomics)
-    }
-    if (tid < J) {   // the projections follow the same interpolation
+    // ---- the projections follow the slot interpolation ----------------------------------------------------------------
 #pragma unroll
-      for (int mm = 0; mm < kMp; ++mm) {
-        const float old = s.P[mm * kJp + tid];
-        s.P[mm * kJp + tid] = fmaf(s.sc[mm * kSc + 7], pd[mm] - old, old);
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j < J) {
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) {
+          const float old = s.P[m * Jp + j];
+          s.P[m * Jp + j] = fmaf(s.sc[m * kSc + 7], pd[c][m] - old, old);
+        }
       }
     }
-    __syncthreads();
-    // ---- ages, usage and the logged statistics: lane m of warp 0 keeps slot m's running sums in registers -------------------
+    // ---- ages, usage and the logged statistics: lane m of warp 0 keeps slot m's running sums in registers ------------
     if (warp == 0) {
       const int m = lane & 15;
       const bool live = lane < kMp && m < a.M;
@@ -264,197 +307,313 @@ __global__ void __launch_bounds__(kThreads) screen_scan_fwd_kernel(ScreenScanArg
         const float act = a.write_enabled ? fmaxf(relr, relw) : relr;
         const float us = a.usage_decay * s.usage[m] + (1.f - a.usage_decay) * act;
         s.usage[m] = us;
-        float un = 0.f;
-#pragma unroll
-        for (int w = 0; w < kThreads / 32; ++w) un += updw[w * kMp + m];
         st_acc[0] += relr; st_acc[2] += relr > 1e-3f ? 1.f : 0.f;
         st_acc[5] += relw; st_acc[6] += a.write_enabled ? fmaxf(relw, a.write_rel_floor) : relw;
-        st_acc[7] += sqrtf(un); st_acc[8] += us;
+        st_acc[8] += us;
       }
       if (lane == 0) { st_acc[1] += rx; st_acc[3] += zn; st_acc[4] += f * zn; }
     }
   }
-  for (int e = tid; e < nel; e += kThreads) {
-    const int d = e / kMp, m = e % kMp;
-    if (m < a.M) a.slots_out[((size_t)b * a.M + m) * a.ds + d] = s.St[e];
-  }
+  __syncthreads();
   if (tid < a.M) { a.ages_out[b * a.M + tid] = s.ages[tid]; a.usage_out[b * a.M + tid] = s.usage[tid]; }
   if (warp == 0) {   // per-slot sums -> means over slots (sums over steps and batch rows stay sums; the host divides)
     const float im = 1.f / a.M;
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
+      if (i == 7) continue;   // the update norm comes from the bank kernel
       float v = lane < kMp ? st_acc[i] : 0.f;
-      v = half_sum(v);
-      const bool per_slot_mean = i == 0 || i == 5 || i == 6 || i == 7 || i == 8;
+      v = warp_sum(v);
+      const bool per_slot_mean = i == 0 || i == 5 || i == 6 || i == 8;
       if (lane == 0) atomicAdd(a.stats + i, per_slot_mean ? v * im : v);
     }
   }
 }
 
-}  // namespace
-
-namespace {
-
-__host__ __device__ inline int scan_bwd_smem_floats(int ds, int dk, int dv) {
-  return scan_smem_floats(ds, dk, dv) + ds * kMp /*dSt*/ + kJp * kMp /*dPc*/ + 2 * dv /*du, dz*/ + kMp * 4 /*dstr, dsimr, dsimw, pad*/;
+// ------------------------------------------------------------------------------------------------------------------
+// Bank recurrence given the strengths: block (slot m, batch row b), thread d.  Writes the final bank and adds the
+// update-norm statistic sum_t |S_{t+1}[m] - S_t[m]| / M to stats[7].
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) screen_bank_fwd_kernel(ScreenScanArgs a) {
+  __shared__ float part[32][33];   // [warp][step within a group of 32]
+  const int m = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int warp = d >> 5, lane = d & 31, nw = blockDim.x >> 5;
+  const bool on = d < a.ds;
+  float S = on ? a.slots0[((size_t)b * a.M + m) * a.ds + d] : 0.f;
+  const float dsl = on ? a.delta_slot[(size_t)m * a.ds + d] : 0.f;
+  const float* str = a.strength + (size_t)b * a.T * kMp + m;
+  const float* xh = a.delta_xh + (size_t)b * a.T * a.ds + d;
+  float norm_acc = 0.f;
+  for (int t0 = 0; t0 < a.T; t0 += 32) {
+    const int n = min(32, a.T - t0);
+    // the 32 steps' inputs are requested together: nothing in the recurrence decides an address
+    float xv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) xv[i] = (on && i < n) ? __ldg(xh + (size_t)(t0 + i) * a.ds) : 0.f;
+    const float sv = lane < n ? __ldg(str + (size_t)(t0 + lane) * kMp) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float sg = __shfl_sync(0xffffffffu, sv, i);   // 0 beyond the last step: the bank stays put
+      float diff = 0.f;
+      if (on) {
+        const float target = tanhf(xv[i] + dsl);
+        diff = sg * (target - S);
+        S += diff;
+      }
+      const float q = warp_sum(diff * diff);
+      if (lane == 0) part[warp][i] = q;
+    }
+    __syncthreads();
+    if (warp == 0 && lane < n) {
+      float tot = 0.f;
+      for (int w = 0; w < nw; ++w) tot += part[w][lane];
+      norm_acc += sqrtf(tot);
+    }
+    __syncthreads();
+  }
+  if (on) a.slots_out[((size_t)b * a.M + m) * a.ds + d] = S;
+  if (warp == 0) {
+    norm_acc = warp_sum(norm_acc);
+    if (lane == 0) atomicAdd(a.stats + 7, norm_acc / a.M);
+  }
 }
 
-template <bool SMEM_W>
-__global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArgs a) {
+// ------------------------------------------------------------------------------------------------------------------
+// Backward, bank path.  (1) h[b,t,m] = <dS_T[b,m], tanh(dxh[b,t] + dslot[m])>: block (step tile, slot, batch row), a warp
+// per step, lanes over d.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kDotTile = 256;   // steps per block
+constexpr int kDotMaxPerLane = 32;   // ds <= 1024
+
+__global__ void __launch_bounds__(256) screen_target_dot_kernel(ScreenScanArgs a) {
+  const int m = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float g[kDotMaxPerLane], dsl[kDotMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kDotMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    const bool on = d < a.ds;
+    g[i] = on ? a.dslots_out[((size_t)b * a.M + m) * a.ds + d] : 0.f;
+    dsl[i] = on ? a.delta_slot[(size_t)m * a.ds + d] : 0.f;
+  }
+  const int t_end = min(a.T, (int)(blockIdx.x + 1) * kDotTile);
+  for (int t = blockIdx.x * kDotTile + warp; t < t_end; t += 8) {
+    const float* xh = a.delta_xh + ((size_t)b * a.T + t) * a.ds;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kDotMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < a.ds) acc = fmaf(g[i], tanhf(__ldg(xh + d) + dsl[i]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) a.ws_h[((size_t)b * a.T + t) * kMp + m] = acc;
+  }
+}
+
+// (2) Scalar recurrences per (batch row, slot), one warp each: e_{t+1} = e_t + s_t (h_t - e_t) forwards from
+// e_0 = <dS_T, S_0>, the suffix products c backwards.  Writes G[t] = c_{t+1} (h_t - e_t) (the strength cotangent that
+// arrives through the bank), coef[t] = s_t c_{t+1} (the factor of dS_T in the target's cotangent) and c_0.
+__global__ void __launch_bounds__(32) screen_bank_scalars_kernel(ScreenScanArgs a) {
+  const int m = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  float e = 0.f;
+  for (int d = lane; d < a.ds; d += 32) {
+    const size_t o = ((size_t)b * a.M + m) * a.ds + d;
+    e = fmaf(a.dslots_out[o], a.slots0[o], e);
+  }
+  e = warp_sum(e);
+  const size_t base = (size_t)b * a.T * kMp + m;
+  for (int t0 = 0; t0 < a.T; t0 += 32) {   // forwards: G <- h_t - e_t
+    const int t = t0 + lane;
+    const bool on = t < a.T;
+    const float h = on ? a.ws_h[base + (size_t)t * kMp] : 0.f;
+    const float sg = on ? a.strength[base + (size_t)t * kMp] : 0.f;
+    float mine = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float hi = __shfl_sync(0xffffffffu, h, i), si = __shfl_sync(0xffffffffu, sg, i);
+      const float diff = hi - e;
+      if (lane == i) mine = diff;
+      e = fmaf(si, diff, e);   // lanes beyond T carry s = 0
+    }
+    if (on) a.ws_G[base + (size_t)t * kMp] = mine;
+  }
+  float c = 1.f;   // c_T
+  for (int t0 = ((a.T - 1) / 32) * 32; t0 >= 0; t0 -= 32) {   // backwards
+    const int t = t0 + lane;
+    const bool on = t < a.T;
+    const float sg = on ? a.strength[base + (size_t)t * kMp] : 0.f;
+    const float diff = on ? a.ws_G[base + (size_t)t * kMp] : 0.f;
+    float c_next = 0.f;   // c_{t+1} of this lane's step
+#pragma unroll
+    for (int i = 31; i >= 0; --i) {
+      const float si = __shfl_sync(0xffffffffu, sg, i);
+      if (lane == i) c_next = c;
+      c *= 1.f - si;
+    }
+    if (on) {
+      a.ws_G[base + (size_t)t * kMp] = c_next * diff;
+      a.ws_coef[base + (size_t)t * kMp] = sg * c_next;
+    }
+  }
+  if (lane == 0) a.ws_c0[b * kMp + m] = c;
+}
+
+// (3) d dxh[b,t,d] = sum_m coef[b,t,m] dS_T[b,m,d] (1 - D^2), d dslot[m,d] += the same term summed over (b, t), and the
+// initial bank's direct cotangent c_0 dS_T.  Block (chunk of 256 d, step tile, batch row), thread d.
+constexpr int kBankBwdTile = 128;
+
+__global__ void __launch_bounds__(256) screen_bank_bwd_kernel(ScreenScanArgs a) {
+  __shared__ float coef[kBankBwdTile][kMp];
+  const int d = blockIdx.x * 256 + threadIdx.x, b = blockIdx.z;
+  const int t0 = blockIdx.y * kBankBwdTile, n = min(kBankBwdTile, a.T - t0);
+  for (int e = threadIdx.x; e < n * kMp; e += 256) coef[e / kMp][e % kMp] = a.ws_coef[((size_t)b * a.T + t0) * kMp + e];
+  __syncthreads();
+  if (d >= a.ds) return;
+  float g[kMp], dsl[kMp], acc[kMp];
+#pragma unroll
+  for (int m = 0; m < kMp; ++m) {
+    const bool live = m < a.M;
+    g[m] = live ? a.dslots_out[((size_t)b * a.M + m) * a.ds + d] : 0.f;
+    dsl[m] = live ? a.delta_slot[(size_t)m * a.ds + d] : 0.f;
+    acc[m] = 0.f;
+  }
+  for (int i = 0; i < n; ++i) {
+    const size_t o = ((size_t)b * a.T + t0 + i) * a.ds + d;
+    const float x = __ldg(a.delta_xh + o);
+    float sum = 0.f;
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) {
+      const float D = tanhf(x + dsl[m]);
+      const float term = coef[i][m] * g[m] * (1.f - D * D);
+      acc[m] += term;
+      sum += term;
+    }
+    a.d_delta_xh[o] = sum;
+  }
+#pragma unroll
+  for (int m = 0; m < kMp; ++m)
+    if (m < a.M) atomicAdd(a.d_delta_slot + (size_t)m * a.ds + d, acc[m]);
+  if (blockIdx.y == 0) {
+#pragma unroll
+    for (int m = 0; m < kMp; ++m)
+      if (m < a.M) a.d_slots0[((size_t)b * a.M + m) * a.ds + d] = a.ws_c0[b * kMp + m] * g[m];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Sequential backward over the saved projections: cotangents of q_r, q_w, PD, the initial projections, mu and the two
+// thresholds.  ws_G (optional) is the strength cotangent that arrives through the bank.
+// ------------------------------------------------------------------------------------------------------------------
+template <int CPT>
+__global__ void __launch_bounds__(kSeqThreads) screen_seq_bwd_kernel(ScreenScanArgs a) {
   extern __shared__ float smem_f[];
   if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
-  const ScanSmem s = carve(smem_f, a.ds, a.dk, a.dv);
-  float* extra = smem_f + scan_smem_floats(a.ds, a.dk, a.dv);
-  float* dSt = extra; extra += a.ds * kMp;      // [ds][16] cotangent of the bank after the current step
-  float* dPc = extra; extra += kJp * kMp;       // [16][256] cotangent of the carried raw projections
-  float* du = extra; extra += a.dv;
-  float* dz = extra; extra += a.dv;
-  float* dstr = extra; extra += kMp;            // cotangent of the write strength
-  float* dsimr = extra; extra += kMp;
-  float* dsimw = extra; extra += kMp;
+  const int J = 2 * a.dk + a.dv, Jp = padded_J(J);
+  const SeqSmem s = carve(smem_f, J, a.dk, a.dv, true);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x;
-  const int J = 2 * a.dk + a.dv;
-  const int nel = a.ds * kMp;
   const float e2 = a.eps * a.eps;
 
-  for (int e = tid; e < nel; e += kThreads) {
-    const int d = e / kMp, m = e % kMp;
-    const bool live = m < a.M;
-    s.DSt[e] = live ? a.delta_slot[m * a.ds + d] : 0.f;
-    dSt[e] = (live && a.dslots_out != nullptr) ? a.dslots_out[((size_t)b * a.M + m) * a.ds + d] : 0.f;
-  }
-  for (int e = tid; e < kMp * kJp; e += kThreads) dPc[e] = 0.f;   // the projections after the last step feed nothing
-  float dslot_acc[16];          // this thread's elements of d(delta_slot): e = tid + 256 i
-#pragma unroll
-  for (int i = 0; i < 16; ++i) dslot_acc[i] = 0.f;
-  float dmu_acc = 0.f, dtaur_acc = 0.f, dtauw_acc = 0.f;   // lane 0 of warp w: slots 2w, 2w+1 (dmu kept per slot below)
-  float dmu_acc2 = 0.f;
-  __syncthreads();
+  for (int e = tid; e < kMp * Jp; e += kSeqThreads) s.dP[e] = 0.f;   // the projections after the last step feed nothing
+  float dmu_acc = 0.f, dtaur_acc = 0.f, dtauw_acc = 0.f;   // lane 0 of warp m: slot m
 
-  // everything a step reads from global memory is fetched one step ahead into registers: the step vectors, the saved
-  // bank (elements tid + 256 i), and column tid of the saved projections and of the write target's projections
-  float n_qr = 0.f, n_qw = 0.f, n_dx = 0.f, n_du = 0.f, n_age = 0.f;
-  float n_S[16], n_P[kMp], n_PD[kMp];
+  // everything a step reads from global memory is fetched one step ahead into registers
+  float n_qr = 0.f, n_qw = 0.f, n_du = 0.f, n_age = 0.f, n_G = 0.f;
+  float n_P[CPT][kMp], n_PD[CPT][kMp];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) n_S[i] = 0.f;
+  for (int c = 0; c < CPT; ++c)
 #pragma unroll
-  for (int m = 0; m < kMp; ++m) { n_P[m] = 0.f; n_PD[m] = 0.f; }
+    for (int m = 0; m < kMp; ++m) { n_P[c][m] = 0.f; n_PD[c][m] = 0.f; }
   auto fetch = [&](int t) {
     const size_t bt = (size_t)b * a.T + t;
     if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
-    if (tid < a.ds) n_dx = a.delta_xh[bt * a.ds + tid];
     if (tid < a.dv) n_du = a.du[bt * a.dv + tid];
-    if (tid < kMp) n_age = a.saved_ages[bt * kMp + tid];
-    const float* src = a.saved_slots + bt * nel;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int e = tid + i * kThreads;
-      if (e < nel) n_S[i] = src[e];
+    if (tid < kMp) {
+      n_age = a.saved_ages[bt * kMp + tid];
+      n_G = a.ws_G != nullptr ? a.ws_G[bt * kMp + tid] : 0.f;
     }
-    if (tid < J) {
-      const float* sp = a.saved_P + bt * kMp * J + tid;
-      const float* pp = a.PD + bt * kMp * J + tid;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) { n_P[m] = sp[m * J]; n_PD[m] = pp[m * J]; }
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j < J) {
+        const float* sp = a.saved_P + bt * kMp * J + j;
+        const float* pp = a.PD + bt * kMp * J + j;
+#pragma unroll
+        for (int m = 0; m < kMp; ++m) { n_P[c][m] = sp[m * J]; n_PD[c][m] = pp[m * J]; }
+      }
     }
   };
   fetch(a.T - 1);
   for (int t = a.T - 1; t >= 0; --t) {
     const size_t bt = (size_t)b * a.T + t;
+    // P alternates between two buffers: the query cotangents at the end of a step still read this step's copy while
+    // the next step's staging writes the other one
+    float* P = s.P + (t & 1) * kMp * Jp;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int e = tid + i * kThreads;
-      if (e < nel) s.St[e] = n_S[i];
-    }
-    if (tid < J) {
+    for (int c = 0; c < CPT; ++c) {
+      const int j = tid + c * kSeqThreads;
+      if (j < J) {
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) { s.P[m * kJp + tid] = n_P[m]; s.PD[m * kJp + tid] = n_PD[m]; }
+        for (int m = 0; m < kMp; ++m) { P[m * Jp + j] = n_P[c][m]; s.PD[m * Jp + j] = n_PD[c][m]; }
+      }
     }
-    if (tid < kMp) { s.ages[tid] = n_age; dstr[tid] = 0.f; }
+    if (tid < kMp) { s.ages[tid] = n_age; s.dstr[tid] = n_G; }
     if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
-    if (tid < a.ds) s.dxh[tid] = n_dx;
-    if (tid < a.dv) du[tid] = n_du;
+    if (tid < a.dv) s.du[tid] = n_du;
     if (t > 0) fetch(t - 1);
     __syncthreads();
-    slot_scalars(s, a, warp, lane);
+    const float* Pm = P + warp * Jp;
+    slot_scalars(Pm, s, a, warp, lane);
     __syncthreads();
     if (tid < a.dv) {
       float acc = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * kJp + a.dk + tid], acc);
+      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], P[m * Jp + a.dk + tid], acc);
       s.z[tid] = acc;
     }
-    // ---- backward of the slot update (uses the cotangent carried from step t+1) -----------------------------------------
+    // ---- backward of the projection update P' = P + s (PD - P): warp m owns slot m ------------------------------------
     {
-      const int m = tid % kMp;
+      const int m = warp;
       const float strength = s.sc[m * kSc + 7];
-      float dsp = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {   // constant trip count keeps dslot_acc in registers; nel is a multiple of 256
-        const int e = tid + i * kThreads;
-        if (e >= nel) break;
-        const int d = e / kMp;
-        const float old = s.St[e];
-        const float delta = tanhf(s.dxh[d] + s.DSt[e]);
-        const float g = dSt[e];
-        dsp = fmaf(g, delta - old, dsp);
-        const float dpre = strength * g * (1.f - delta * delta);
-        dSt[e] = (1.f - strength) * g;
-        dslot_acc[i] += dpre;
-        // sum of dpre over the 16 slots of this d: the 16 lanes of a half-warp share d
-        float r = dpre;
-        r += __shfl_xor_sync(0xffffffffu, r, 1); r += __shfl_xor_sync(0xffffffffu, r, 2);
-        r += __shfl_xor_sync(0xffffffffu, r, 4); r += __shfl_xor_sync(0xffffffffu, r, 8);
-        if (m == 0) a.d_delta_xh[bt * a.ds + d] = r;
-      }
-      atomicAdd(&dstr[m], dsp);
-    }
-    // ---- backward of the projection update P' = P + s (PD - P): warp w owns slots 2w and 2w+1 -------------------------------
-    for (int mm = 0; mm < 2; ++mm) {
-      const int m = warp * 2 + mm;
-      const float strength = s.sc[m * kSc + 7];
-      float* gp = dPc + m * kJp;
+      float* gp = s.dP + m * Jp;
       float* out = a.d_PD + (bt * kMp + m) * J;
       float dsp = 0.f;
       for (int j = lane; j < J; j += 32) {
         const float g = gp[j];
-        dsp = fmaf(g, s.PD[m * kJp + j] - s.P[m * kJp + j], dsp);
+        dsp = fmaf(g, s.PD[m * Jp + j] - Pm[j], dsp);
         out[j] = strength * g;
         gp[j] = (1.f - strength) * g;
       }
       dsp = warp_sum(dsp);
-      if (lane == 0) atomicAdd(&dstr[m], dsp);
+      if (lane == 0) s.dstr[m] += dsp;   // this warp is the only writer of dstr[m] after the staging above
     }
     __syncthreads();
-    // ---- cotangent of z from the cotangent of u = f(n) z ---------------------------------------------------------------------
+    // ---- cotangent of z from the cotangent of u = f(n) z -------------------------------------------------------------
     float zn2 = 0.f, zdu = 0.f;
-    for (int v = lane; v < a.dv; v += 32) { zn2 = fmaf(s.z[v], s.z[v], zn2); zdu = fmaf(s.z[v], du[v], zdu); }
+    for (int v = lane; v < a.dv; v += 32) { zn2 = fmaf(s.z[v], s.z[v], zn2); zdu = fmaf(s.z[v], s.du[v], zdu); }
     zn2 = warp_sum(zn2); zdu = warp_sum(zdu);
     const float n2 = zn2 + e2, zn = sqrtf(n2);
     const float th = tanhf(zn / a.cap);
     const float f = a.cap * th / zn;
     const float coef = zdu * ((1.f - th * th) - f) / n2;
-    if (tid < a.dv) dz[tid] = f * du[tid] + coef * s.z[tid];
+    if (tid < a.dv) s.dz[tid] = f * s.du[tid] + coef * s.z[tid];
     __syncthreads();
-    // ---- per-slot scalars backward; cotangent of the raw projections (transposed into dPt[j][m]) ------------------------------
-    for (int mm = 0; mm < 2; ++mm) {
-      const int m = warp * 2 + mm;
+    // ---- per-slot scalars backward; cotangent of the raw projections ---------------------------------------------------
+    {
+      const int m = warp;
       const float* c = s.sc + m * kSc;
       const float nk = c[0], nv = c[1], nw = c[2], simr = c[3], simw = c[4], relr = c[5], relw = c[6];
-      const float* Pm = s.P + m * kJp;
       const bool live = m < a.M;
       float drelr = 0.f;
-      for (int v = lane; v < a.dv; v += 32) drelr = fmaf(dz[v], Pm[a.dk + v] / nv, drelr);
+      for (int v = lane; v < a.dv; v += 32) drelr = fmaf(s.dz[v], Pm[a.dk + v] / nv, drelr);
       drelr = warp_sum(drelr);
       float mask = 1.f;
-      if (a.age_mask) mask = 1.f / (1.f + __expf(-(a.age_ref - s.ages[m]) / (a.age_sigma + a.eps)));
-      const float den_r = 1.f - a.tau_r + a.eps;
-      const float xr = fmaxf((simr - a.tau_r) / den_r, 0.f);
+      if (a.age_mask) mask = sigmoidf_((a.age_ref - s.ages[m]) / (a.age_sigma + a.eps));
+      float g_sim, g_tau;
+      read_relevance_grad(simr, a, g_sim, g_tau);
       const float dtrim = live ? drelr * mask : 0.f;
-      const float dsr = dtrim * 2.f * xr / den_r;
+      const float dsr = dtrim * g_sim;
       float dsw = 0.f, gate_w = 1.f;
-      const float ds_m = dstr[m];
+      const float ds_m = s.dstr[m];
       if (a.write_enabled && live) {
         gate_w = fmaxf(relw, a.write_rel_floor);
         const float drelw = relw > a.write_rel_floor ? ds_m * a.mu[m] : 0.f;
@@ -463,84 +622,103 @@ __global__ void __launch_bounds__(kThreads) screen_scan_bwd_kernel(ScreenScanArg
         dsw = drelw * 2.f * xw / den_w;
         if (lane == 0) dtauw_acc += drelw * 2.f * xw * (simw - 1.f - a.eps) / (den_w * den_w);
       }
-      if (lane == 0 && live) {
-        dtaur_acc += dtrim * 2.f * xr * (simr - 1.f - a.eps) / (den_r * den_r);
-        if (mm == 0) dmu_acc += ds_m * gate_w; else dmu_acc2 += ds_m * gate_w;
-        dsimr[m] = dsr; dsimw[m] = dsw;
-      } else if (lane == 0) {
-        dsimr[m] = 0.f; dsimw[m] = 0.f;
+      if (lane == 0) {
+        if (live) { dtaur_acc += dtrim * g_tau; dmu_acc += ds_m * gate_w; }
+        s.dsimr[m] = live ? dsr : 0.f;
+        s.dsimw[m] = live ? dsw : 0.f;
       }
-      float* gp = dPc + m * kJp;   // same warp and lanes as the scaling above: no barrier needed in between
-      for (int j = lane; j < a.dk; j += 32) {   // read keys: k = x / nk, sim = q . k
-        if (live) gp[j] += dsr * (s.qr[j] - Pm[j] / nk * simr) / nk;
-      }
-      for (int v = lane; v < a.dv; v += 32) {   // values
-        const float val = Pm[a.dk + v] / nv;
-        if (live) gp[a.dk + v] += a.value_unit_norm ? relr * (dz[v] - val * drelr) / nv : relr * dz[v];
-      }
-      for (int j = lane; j < a.dk; j += 32) {   // write keys
-        if (live && a.write_enabled) gp[a.dk + a.dv + j] += dsw * (s.qw[j] - Pm[a.dk + a.dv + j] / nw * simw) / nw;
+      float* gp = s.dP + m * Jp;   // same warp and lanes as the scaling above: no barrier needed in between
+      if (live) {
+        for (int j = lane; j < a.dk; j += 32)   // read keys: k = x / nk, sim = q . k
+          gp[j] += dsr * (s.qr[j] - Pm[j] / nk * simr) / nk;
+        for (int v = lane; v < a.dv; v += 32) {   // values
+          const float val = Pm[a.dk + v] / nv;
+          gp[a.dk + v] += a.value_unit_norm ? relr * (s.dz[v] - val * drelr) / nv : relr * s.dz[v];
+        }
+        if (a.write_enabled)
+          for (int j = lane; j < a.dk; j += 32)   // write keys
+            gp[a.dk + a.dv + j] += dsw * (s.qw[j] - Pm[a.dk + a.dv + j] / nw * simw) / nw;
       }
     }
     __syncthreads();
-    // ---- cotangents of the queries --------------------------------------------------------------------------------------------
+    // ---- cotangents of the queries -------------------------------------------------------------------------------------
     if (tid < a.dk) {
       float gr = 0.f, gw = 0.f;
 #pragma unroll
       for (int m = 0; m < kMp; ++m) {
-        gr = fmaf(dsimr[m], s.P[m * kJp + tid] / s.sc[m * kSc + 0], gr);
-        gw = fmaf(dsimw[m], s.P[m * kJp + a.dk + a.dv + tid] / s.sc[m * kSc + 2], gw);
+        gr = fmaf(s.dsimr[m], P[m * Jp + tid] / s.sc[m * kSc + 0], gr);
+        gw = fmaf(s.dsimw[m], P[m * Jp + a.dk + a.dv + tid] / s.sc[m * kSc + 2], gw);
       }
       a.d_q_r[bt * a.dk + tid] = gr;
       if (a.write_enabled) a.d_q_w[bt * a.dk + tid] = gw;
     }
-    __syncthreads();
+    // no barrier here: the next step's staging touches the other P buffer, PD (last read two barriers ago) and the step
+    // vectors, none of which the query cotangents read; sc, dsimr and dsimw are rewritten only after the next barrier
   }
+  __syncthreads();
   // cotangent of the initial projections: the caller folds it into d slots0, d W and d slot_embed
-  if (tid < J) {
 #pragma unroll
-    for (int m = 0; m < kMp; ++m) a.d_P0[((size_t)b * kMp + m) * J + tid] = dPc[m * kJp + tid];
-  }
-  for (int e = tid; e < nel; e += kThreads) {
-    const int d = e / kMp, m = e % kMp;
-    if (m < a.M) a.d_slots0[((size_t)b * a.M + m) * a.ds + d] = dSt[e];
-  }
+  for (int c = 0; c < CPT; ++c) {
+    const int j = tid + c * kSeqThreads;
+    if (j < J) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int e = tid + i * kThreads;
-    if (e < nel) {
-      const int d = e / kMp, m = e % kMp;
-      if (m < a.M) atomicAdd(a.d_delta_slot + m * a.ds + d, dslot_acc[i]);
+      for (int m = 0; m < kMp; ++m) a.d_P0[((size_t)b * kMp + m) * J + j] = s.dP[m * Jp + j];
     }
   }
   if (lane == 0) {
     atomicAdd(a.d_scalars + 0, dtaur_acc);
     atomicAdd(a.d_scalars + 1, dtauw_acc);
-    if (warp * 2 < a.M) atomicAdd(a.d_mu + warp * 2, dmu_acc);
-    if (warp * 2 + 1 < a.M) atomicAdd(a.d_mu + warp * 2 + 1, dmu_acc2);
+    if (warp < a.M) atomicAdd(a.d_mu + warp, dmu_acc);
   }
 }
+
+int columns_per_thread(int J) { return (J + kSeqThreads - 1) / kSeqThreads; }
 
 }  // namespace
 
 bool screen_scan_supported(const ScreenScanArgs& a) {
-  return a.M >= 1 && a.M <= kMp && a.ds % 4 == 0 && a.ds >= 16 && a.ds <= 256 && kThreads % a.ds == 0 && a.dk >= 1 &&
-         a.dv >= 1 && 2 * a.dk + a.dv <= kJp && a.dk <= kThreads && a.dv <= kThreads;
+  const int J = 2 * a.dk + a.dv;
+  return a.M >= 1 && a.M <= kMp && a.ds >= 1 && a.ds <= 32 * kDotMaxPerLane && a.dk >= 1 && a.dv >= 1 &&
+         a.dk <= kSeqThreads && a.dv <= kSeqThreads && J <= 2 * kSeqThreads &&
+         (size_t)seq_smem_floats(J, a.dk, a.dv, true) * sizeof(float) <= 227 * 1024 &&
+         (size_t)seq_smem_floats(J, a.dk, a.dv, false) * sizeof(float) <= 227 * 1024;
 }
 
 int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a) || a.PD == nullptr) return 1;
-  const size_t bytes = (size_t)scan_smem_floats(a.ds, a.dk, a.dv) * sizeof(float);
-  cudaFuncSetAttribute(screen_scan_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  screen_scan_fwd_kernel<false><<<a.B, kThreads, bytes, st>>>(a);
+  if (!screen_scan_supported(a) || a.PD == nullptr || a.strength == nullptr) return 1;
+  const int J = 2 * a.dk + a.dv;
+  const size_t bytes = (size_t)seq_smem_floats(J, a.dk, a.dv, false) * sizeof(float);
+  if (columns_per_thread(J) == 1) {
+    cudaFuncSetAttribute(screen_seq_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    screen_seq_fwd_kernel<1><<<a.B, kSeqThreads, bytes, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(screen_seq_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    screen_seq_fwd_kernel<2><<<a.B, kSeqThreads, bytes, st>>>(a);
+  }
+  const int threads = ((a.ds + 31) / 32) * 32;
+  screen_bank_fwd_kernel<<<dim3(a.M, a.B), threads, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a) || a.PD == nullptr || a.saved_P == nullptr) return 1;
-  const size_t bytes = (size_t)(scan_bwd_smem_floats(a.ds, a.dk, a.dv) + kMp) * sizeof(float);
-  cudaFuncSetAttribute(screen_scan_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  screen_scan_bwd_kernel<false><<<a.B, kThreads, bytes, st>>>(a);
+  if (!screen_scan_supported(a) || a.PD == nullptr || a.saved_P == nullptr || a.strength == nullptr) return 1;
+  const int J = 2 * a.dk + a.dv;
+  const bool bank = a.dslots_out != nullptr;
+  if (bank) {
+    if (a.ws_h == nullptr || a.ws_G == nullptr || a.ws_coef == nullptr || a.ws_c0 == nullptr) return 1;
+    screen_target_dot_kernel<<<dim3((a.T + kDotTile - 1) / kDotTile, a.M, a.B), 256, 0, st>>>(a);
+    screen_bank_scalars_kernel<<<dim3(a.M, a.B), 32, 0, st>>>(a);
+  }
+  const size_t bytes = (size_t)seq_smem_floats(J, a.dk, a.dv, true) * sizeof(float);
+  if (columns_per_thread(J) == 1) {
+    cudaFuncSetAttribute(screen_seq_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    screen_seq_bwd_kernel<1><<<a.B, kSeqThreads, bytes, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(screen_seq_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    screen_seq_bwd_kernel<2><<<a.B, kSeqThreads, bytes, st>>>(a);
+  }
+  if (bank)
+    screen_bank_bwd_kernel<<<dim3((a.ds + 255) / 256, (a.T + kBankBwdTile - 1) / kBankBwdTile, a.B), 256, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -821,28 +821,29 @@ class ScreenScanFn(torch.autograd.Function):
         # the learned thresholds stay on the device (two floats read by the kernels): no host synchronisation
         tau = torch.stack([tau_r.detach().float().reshape(()), tau_w.detach().float().reshape(())]).contiguous()
         floats = [0.0, 0.0, settings["eps"], settings["cap"], settings["floor"],
-                  settings["usage_decay"], settings["age_ref"], settings["age_sigma"]]
+                  settings["usage_decay"], settings["age_ref"], settings["age_sigma"],
+                  1.0 if settings.get("leaky") else 0.0, settings.get("leaky_alpha", 0.0), settings.get("leaky_gamma", 8.0)]
         flags = (bool(settings["write_enabled"]), bool(settings["value_unit_norm"]), bool(settings["age_mask"]))
         dxh32, dds32, E32 = f32(delta_xh), f32(delta_slot), f32(slot_embed)
         _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv)
         tensors = [f32(q_r), f32(q_w), dxh32, dds32, E32, WT, PD, f32(mu), f32(slots0), f32(ages0), f32(usage0)]
         need_grad = any(ctx.needs_input_grad)
-        u, so, ao, uo, stats, saved, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad, tau)
-        _count()
+        u, so, ao, uo, stats, strength, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad, tau)
+        _count(2)
         ctx.floats, ctx.flags, ctx.tau = floats, flags, tau
         ctx.dk, ctx.dv, ctx.M = dk, dv, slots0.shape[1]
         ctx.dtypes = [t.dtype for t in (q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, slots0)]
         if need_grad:
-            ctx.save_for_backward(*tensors, W, saved, saved_ages, saved_P)
+            ctx.save_for_backward(*tensors, W, strength, saved_ages, saved_P)
         ctx.mark_non_differentiable(ao, uo, stats)
         return u, so, ao, uo, stats
 
     @staticmethod
     def backward(ctx, du, dso, *_):
-        *tensors, W, saved, saved_ages, saved_P = ctx.saved_tensors
+        *tensors, W, strength, saved_ages, saved_P = ctx.saved_tensors
         dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0 = _C.screen_scan_bwd(
-            *tensors, ctx.floats, *ctx.flags, saved, saved_ages, saved_P, du.float().contiguous(), dso, ctx.tau)
-        _count()
+            *tensors, ctx.floats, *ctx.flags, strength, saved_ages, saved_P, du.float().contiguous(), dso, ctx.tau)
+        _count(1 if dso is None else 4)
         delta_xh, delta_slot, slot_embed, slots0 = tensors[2], tensors[3], tensors[4], tensors[8]
         dk, dv, M = ctx.dk, ctx.dv, ctx.M
         B, T, ds = delta_xh.shape
@@ -872,8 +873,8 @@ class ScreenScanFn(torch.autograd.Function):
 def _screen_kernel_ok(mod, q_r, h_base, write_enabled):
     cfg = mod.config
     ds, dk, dv, M = cfg.d_slot, cfg.d_k, cfg.d_v, cfg.n_slots
-    return (not cfg.use_leaky_warmup and M <= 16 and ds in (16, 32, 64, 128, 256) and 2 * dk + dv <= 256
-            and dk <= 256 and dv <= 256 and q_r.is_cuda)
+    # the sequential backward keeps four [16, J] fp32 tiles in shared memory (J = 2 dk + dv)
+    return M <= 16 and ds <= 1024 and 2 * dk + dv <= 832 and dk <= 512 and dv <= 512 and q_r.is_cuda
 
 
 def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars):
@@ -893,6 +894,7 @@ def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **s
         w_kw, qw = torch.zeros_like(mod.k_proj_r.weight), torch.zeros_like(q_r)
     settings = {"eps": cfg.eps, "cap": cfg.tanh_norm_cap, "floor": cfg.write_rel_floor, "usage_decay": cfg.usage_ema_decay,
                 "age_ref": cfg.age_ref, "age_sigma": cfg.age_sigma, "write_enabled": write_enabled,
+                "leaky": cfg.use_leaky_warmup, "leaky_alpha": cfg.leaky_alpha, "leaky_gamma": cfg.leaky_gamma,
                 "value_unit_norm": cfg.use_value_unit_norm, "age_mask": cfg.use_age_mask}
     u, slots, ages, usage, st = ScreenScanFn.apply(
         q_r, qw, delta_xh, delta_slot, mod.slot_embed, mod.k_proj_r.weight, mod.v_proj.weight, w_kw, mu,

@@ -11,12 +11,12 @@ from rwkv7m_b200.state import LayerScreenState
 pytestmark = pytest.mark.gpu
 
 
-def _setup(phase, n_slots=4, d_slot=32, age_mask=False, seed=0):
+def _setup(phase, n_slots=4, d_slot=32, age_mask=False, seed=0, d_k=16, d_v=16, leaky=False):
     torch.manual_seed(seed)
     C = 64
-    cfg = ScreeningConfig(d_model=C, d_slot=d_slot, d_k=16, d_v=16, n_slots=n_slots, screened_layers=(0,),
+    cfg = ScreeningConfig(d_model=C, d_slot=d_slot, d_k=d_k, d_v=d_v, n_slots=n_slots, screened_layers=(0,),
                           bank_ids=tuple(i % 3 for i in range(n_slots)), use_write_screening=phase == "read_write",
-                          use_age_mask=age_mask, write_rel_floor=1e-3)
+                          use_age_mask=age_mask, write_rel_floor=1e-3, use_leaky_warmup=leaky, leaky_alpha=0.3 if leaky else 0.0)
     mod = StateLevelScreening(cfg).cuda()
     with torch.no_grad():
         for p in mod.parameters():   # away from the zero / identity initialisations so every path carries gradient
@@ -31,10 +31,15 @@ def _setup(phase, n_slots=4, d_slot=32, age_mask=False, seed=0):
     return mod, x, h, st
 
 
+# the last three rows are the bank shapes of the 1b / 3b / 7b presets (two projection columns per thread from J > 512);
+# (5, 48, ...) has a slot width that is no multiple of 32 and a leaky read relevance
 @pytest.mark.parametrize("phase", ["read_screening_only", "read_write"])
-@pytest.mark.parametrize("n_slots,d_slot,age_mask", [(4, 32, False), (16, 64, True)])
-def test_scan_kernel_matches_reference(phase, n_slots, d_slot, age_mask):
-    mod, x, h, st = _setup(phase, n_slots, d_slot, age_mask)
+@pytest.mark.parametrize("n_slots,d_slot,age_mask,d_k,d_v,leaky", [
+    (4, 32, False, 16, 16, False), (16, 64, True, 16, 16, False), (5, 48, True, 24, 40, True),
+    (16, 384, False, 96, 192, False), (16, 640, True, 128, 320, False), (16, 1024, False, 128, 512, True)])
+def test_scan_kernel_matches_reference(phase, n_slots, d_slot, age_mask, d_k, d_v, leaky):
+    mod, x, h, st = _setup(phase, n_slots, d_slot, age_mask, d_k=d_k, d_v=d_v, leaky=leaky)
+    assert ops._cuda()._screen_kernel_ok(mod, x, h, phase == "read_write")   # the kernels, not the PyTorch scan
     wy = torch.randn_like(h)
     ws = torch.randn_like(st.slots)
 
