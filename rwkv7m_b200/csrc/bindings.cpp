@@ -635,7 +635,7 @@ rk::ScreenScanArgs screen_args(const Tensor& q_r, const Tensor& q_w, const Tenso
   return a;
 }
 
-// returns u, slots_out, ages_out, usage_out, stats[9], strength [B,T,16], saved_ages, saved_P
+// returns u, slots_out, ages_out, usage_out, stats[9], strength [B,T,16], saved_ages, saved_P, rel_c [B,T,16]
 std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const Tensor& delta_xh, const Tensor& delta_slot,
                                     const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
@@ -650,16 +650,21 @@ std::vector<Tensor> screen_scan_fwd(const Tensor& q_r, const Tensor& q_w, const 
   Tensor u = torch::empty({a.B, a.T, a.dv}, o);
   Tensor so = torch::empty_like(slots0), ao = torch::empty_like(ages0), uo = torch::empty_like(usage0);
   Tensor stats = torch::zeros({9}, o);
-  Tensor strength = torch::empty({a.B, a.T, 16}, o);
-  Tensor saved_ages = save ? torch::empty({a.B, a.T, 16}, o) : torch::empty({0}, o);
-  Tensor saved_P = save ? torch::empty({a.B, a.T, 16, J}, o) : torch::empty({0}, o);
+  Tensor strength = torch::empty({a.B, a.T, 16}, o), rel_c = torch::empty({a.B, a.T, 16}, o);
+  Tensor rel_r = torch::empty({a.B, a.T, 16}, o);
+  // the rows of P are written in inference too: the read-out kernel forms u from them
+  Tensor saved_ages = torch::empty({a.B, a.T, 16}, o);
+  Tensor saved_P = torch::empty({a.B, a.T, 16, J}, o);
   a.u_out = u.data_ptr<float>(); a.slots_out = so.data_ptr<float>(); a.ages_out = ao.data_ptr<float>();
   a.usage_out = uo.data_ptr<float>(); a.stats = stats.data_ptr<float>();
-  a.strength = strength.data_ptr<float>();
-  a.saved_ages = save ? saved_ages.data_ptr<float>() : nullptr;
-  a.saved_P = save ? saved_P.data_ptr<float>() : nullptr;
+  a.strength = strength.data_ptr<float>(); a.rel_c = rel_c.data_ptr<float>(); a.rel_r = rel_r.data_ptr<float>();
+  a.saved_ages = saved_ages.data_ptr<float>();
+  a.saved_P = saved_P.data_ptr<float>();
+  Tensor rows = torch::empty({a.B, a.T, J}, o);
+  a.ws_rows = rows.data_ptr<float>();
   TORCH_CHECK(rk::screen_scan_forward(a, stream()) == 0, "screen_scan_forward failed");
-  return {u, so, ao, uo, stats, strength, saved_ages, saved_P};
+  if (!save) return {u, so, ao, uo, stats, torch::empty({0}, o), torch::empty({0}, o), torch::empty({0}, o), torch::empty({0}, o)};
+  return {u, so, ao, uo, stats, strength, saved_ages, saved_P, rel_c};
 }
 
 // returns d q_r, d q_w, d delta_xh (direct part), d delta_slot (direct part), d slots0 (direct part), d mu,
@@ -668,7 +673,8 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
                                     const Tensor& slot_embed, const Tensor& WT, const Tensor& PD, const Tensor& mu,
                                     const Tensor& slots0, const Tensor& ages0, const Tensor& usage0,
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
-                                    const Tensor& strength, const Tensor& saved_ages, const Tensor& saved_P, const Tensor& du,
+                                    const Tensor& strength, const Tensor& saved_ages, const Tensor& saved_P,
+                                    const Tensor& rel_c, const Tensor& du,
                                     const c10::optional<Tensor>& dslots_out, const c10::optional<Tensor>& tau_dev) {
   c10::cuda::CUDAGuard guard(q_r.device());
   rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
@@ -687,7 +693,11 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
   Tensor dsc = torch::zeros({2}, o);
   Tensor dPD = torch::empty({a.B, a.T, 16, J}, o);
   Tensor dP0 = torch::empty({a.B, 16, J}, o);
+  TORCH_CHECK(rel_c.numel() == (int64_t)a.B * a.T * 16 && du.numel() == (int64_t)a.B * a.T * a.dv, "saved tensors do not match");
   a.strength = const_cast<float*>(fptr(strength)); a.saved_ages = const_cast<float*>(fptr(saved_ages));
+  a.rel_c = const_cast<float*>(fptr(rel_c));
+  Tensor ws2 = torch::empty({(int64_t)a.B * a.T * (J + 32)}, o);
+  a.ws_rows = ws2.data_ptr<float>(); a.ws_a = a.ws_rows + (int64_t)a.B * a.T * J; a.ws_b = a.ws_a + (int64_t)a.B * a.T * 16;
   a.saved_P = const_cast<float*>(fptr(saved_P));
   a.du = fptr(du);
   Tensor dso, ws;

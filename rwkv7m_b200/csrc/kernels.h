@@ -161,14 +161,19 @@ struct ScreenScanArgs {
   float *slots_out, *ages_out, *usage_out;
   float* stats;                 // [9] running sums over batch rows and steps
   float* strength;              // [B,T,16] write strength of every step and slot (forward output, backward input)
-  float* saved_ages;            // [B,T,16]   ages before each step (nullptr with saved_P = inference)
-  float* saved_P;               // [B,T,16,J] raw projections before each step
+  float* rel_c;                 // [B,T,16] read coefficient rel_r / |value| (forward output, backward input)
+  float* rel_r;                 // [B,T,16] read relevance (forward only: statistics)
+  float* saved_ages;            // [B,T,16]   ages before each step
+  float* saved_P;               // [B,T,16,J] raw projections before each step (always written: the read-out kernel
+                                //            forms u from it)
   // backward
   const float* du;              // [B,T,dv]
   const float* dslots_out;      // [B,M,ds] cotangent of the final bank, or nullptr (then d_delta_xh, d_delta_slot and
                                 // d_slots0 are left untouched: the caller zeroes them)
   float *ws_h, *ws_G, *ws_coef; // [B,T,16] workspaces of the bank path (needed with dslots_out)
   float* ws_c0;                 // [B,16]
+  float* ws_rows;               // [B,T,J] packed per-step rows [q_r | 0 or dz | q_w] (workspace of both directions)
+  float *ws_a, *ws_b;           // [B,T,16] per-slot factors of the query cotangents (backward workspace)
   float *d_q_r, *d_q_w, *d_delta_xh;      // [B,T,dk], [B,T,dk], [B,T,ds]
   float* d_PD;                  // [B,T,16,J] cotangent of PD
   float* d_P0;                  // [B,16,J]   cotangent of the projections of the initial bank

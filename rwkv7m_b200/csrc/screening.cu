@@ -6,22 +6,27 @@
 //   u[t]    = tanh_norm(sum_m rel_r[m] val[m])                       (output; the out-projection is a GEMM outside)
 //   S[m]   += s_t[m] (tanh(dxh[t] + dslot[m]) - S[m]),   s_t[m] = mu[m] * max(rel_w[m], floor)   (mu[m] alone without
 //                                                                                                  write screening)
-// Two observations split the work into one sequential kernel of width J = dk + dv + dk and a few parallel ones of
-// width ds (the slot width, up to 1024):
+// Three observations take the recurrence apart:
 //  (1) The update interpolates towards a target D_t[m] = tanh(dxh[t] + dslot[m]) that does not depend on the state, and
-//      the raw projections P[m] = S[m] W^T (+ E[m] Wkw^T on the write keys) are linear in S, so they obey
-//        P_{t+1}[m] = P_t[m] + s_t[m] (PD_t[m] - P_t[m]),   PD_t[m] = D_t[m] W^T (+ E[m] Wkw^T),
-//      where PD for all steps is one GEMM done by the caller.  Everything a step decides (norms, similarities,
-//      relevances, the read-out, the write strengths) follows from P alone: the sequential kernel carries only P.
-//  (2) Given the strengths s_t[m] the bank itself is an independent scalar recurrence per element: a parallel kernel
-//      over (batch, slot, d) produces the final bank and the update-norm statistic.  In backward the bank's cotangent is
+//      the raw projections P[m] = S[m] W^T (+ E[m] Wkw^T on the write keys; J = dk + dv + dk columns) are linear in S,
+//      so they obey P_{t+1}[m] = P_t[m] + s_t[m] (PD_t[m] - P_t[m]) with PD_t[m] = D_t[m] W^T (+ E[m] Wkw^T), where PD
+//      for all steps is one GEMM done by the caller.  Everything a step decides follows from P alone.
+//  (2) Slot m's strength depends only on slot m's own projections and on the step's queries: the slots do not interact
+//      inside the recurrence.  The sequential kernels therefore run ONE WARP per (batch row, slot), the row of P in
+//      registers (column j = lane + 32 i), no shared memory and no block barrier: a step is a few fused multiply-adds
+//      per lane, one butterfly of shuffles for all the sums, and scalar arithmetic.  What couples the slots (the
+//      read-out z = sum_m rel_r[m] val[m] and its tanh-norm, the per-step maximum for the statistics, the query
+//      cotangents in backward) does not feed back into the recurrence, so parallel kernels over all (batch, step) pairs
+//      compute it from the saved per-step rows of P and per-slot scalars.
+//  (3) Given the strengths the bank itself is an independent scalar recurrence per element: a parallel kernel over
+//      (batch, slot, d) produces the final bank and the update-norm statistic.  In backward the bank's cotangent is
 //      dS_{t+1}[m] = c_{t+1}[m] dS_T[m] with c the suffix products of (1 - s), so the strength cotangent that comes
 //      through the bank is c_{t+1}[m] (h_t[m] - e_t[m]) with h_t[m] = <dS_T[m], D_t[m]> (parallel over all steps) and
 //      e_t[m] = <dS_T[m], S_t[m]>, which follows the same scalar recurrence as the bank.  The sequential backward
 //      kernel receives that number per (step, slot) and never touches a ds-wide vector; the dxh / dslot / initial-bank
 //      gradients of the bank path are one more parallel kernel.
-// The sequential kernels run one CTA of 16 warps per batch row: warp m owns slot m in the per-slot phases, thread j owns
-// columns j and j + 512 of the projections in the per-column phases.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -29,10 +34,7 @@ namespace rk {
 
 namespace {
 
-constexpr int kMp = 16;            // slots are padded to 16
-constexpr int kSeqThreads = 512;   // 16 warps
-constexpr int kSc = 12;            // per-slot scalars: nk, nv, nw, simr, simw, relr, relw, strength, relr / nv
-constexpr int kTileD = 64;         // rows of the bank staged at a time for the initial projections
+constexpr int kMp = 16;   // slots are padded to 16 in the [B, T, 16, ...] tensors
 
 __device__ __forceinline__ float trim_sq(float sim, float tau, float eps) {
   const float x = fmaxf((sim - tau) / (1.f - tau + eps), 0.f);
@@ -61,270 +63,238 @@ __device__ __forceinline__ void read_relevance_grad(float sim, const ScreenScanA
   }
 }
 
-__host__ __device__ inline int padded_J(int J) { return (J + 3) & ~3; }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-struct SeqSmem {
-  float* P;      // [16][Jp]  raw projections of the current step (backward: two copies, alternating by step parity)
-  float* PD;     // [16][Jp]  backward: projections of the step's write target
-  float* dP;     // [16][Jp]  backward: cotangent of the carried projections
-  float* EW;     // [16][dk]  forward: slot_embed Wkw^T
-  float* tile;   // [64][16]  forward: rows of the bank staged for the initial projections
-  float* qr;     // [dk]
-  float* qw;     // [dk]
-  float* z;      // [dv]
-  float* du;     // [dv]      backward
-  float* dz;     // [dv]      backward
-  float* sc;     // [16][kSc] per-slot scalars
-  float* ages;   // [16]
-  float* usage;  // [16]
-  float* dstr;   // [16]      backward: cotangent of the write strength
-  float* dsimr;  // [16]
-  float* dsimw;  // [16]
-};
+constexpr int kAhead = 6;   // steps ahead of the register prefetch that a step's rows are pulled into L2
 
-__host__ __device__ inline int seq_smem_floats(int J, int dk, int dv, bool backward) {
-  const int Jp = padded_J(J);
-  int n = kMp * Jp * (backward ? 4 : 1) + 2 * dk + dv + kMp * kSc + 2 * kMp;
-  n += backward ? 2 * dv + 3 * kMp : kMp * dk + kTileD * kMp;
-  return n + 8;
-}
+// Which of the three column groups register i of this lane belongs to (column j = lane + 32 i), as bit masks.
+struct ColumnMasks { uint32_t key, val, wkey; };
 
-__device__ __forceinline__ SeqSmem carve(float* base, int J, int dk, int dv, bool backward) {
-  const int Jp = padded_J(J);
-  SeqSmem s{};
-  s.P = base; base += kMp * Jp * (backward ? 2 : 1);
-  if (backward) {
-    s.PD = base; base += kMp * Jp;
-    s.dP = base; base += kMp * Jp;
-    s.du = base; base += dv;
-    s.dz = base; base += dv;
-    s.dstr = base; base += kMp;
-    s.dsimr = base; base += kMp;
-    s.dsimw = base; base += kMp;
-  } else {
-    s.EW = base; base += kMp * dk;
-    s.tile = base; base += kTileD * kMp;
+template <int JPL>
+__device__ __forceinline__ ColumnMasks column_masks(int lane, int dk, int dv, int J) {
+  ColumnMasks c{0u, 0u, 0u};
+#pragma unroll
+  for (int i = 0; i < JPL; ++i) {
+    const int j = lane + 32 * i;
+    if (j < dk) c.key |= 1u << i;
+    else if (j < dk + dv) c.val |= 1u << i;
+    else if (j < J) c.wkey |= 1u << i;
   }
-  s.qr = base; base += dk;
-  s.qw = base; base += dk;
-  s.z = base; base += dv;
-  s.sc = base; base += kMp * kSc;
-  s.ages = base; base += kMp;
-  s.usage = base; base += kMp;
-  return s;
+  return c;
 }
 
-// acc[c][m] = sum_d src[m][d] * WT[d][j], j = tid + c * 512: the [M, ds] source is staged 64 rows of d at a time
-template <int CPT>
-__device__ __forceinline__ void project_rows(const float* __restrict__ src, const ScreenScanArgs& a, float* tile, int J,
-                                             int tid, float (&acc)[CPT][kMp]) {
-#pragma unroll
-  for (int c = 0; c < CPT; ++c)
-#pragma unroll
-    for (int m = 0; m < kMp; ++m) acc[c][m] = 0.f;
-  for (int d0 = 0; d0 < a.ds; d0 += kTileD) {
-    __syncthreads();
-    for (int e = tid; e < kTileD * kMp; e += kSeqThreads) {
-      const int dd = e / kMp, m = e % kMp;
-      tile[e] = (m < a.M && d0 + dd < a.ds) ? __ldg(src + (size_t)m * a.ds + d0 + dd) : 0.f;
-    }
-    __syncthreads();
-    const int nd = min(kTileD, a.ds - d0);
-#pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j >= J) continue;
-      for (int dd = 0; dd < nd; ++dd) {
-        const float w = __ldg(a.WT + (size_t)(d0 + dd) * J + j);
-        const float4* sp = reinterpret_cast<const float4*>(tile + dd * kMp);
-        const float4 p = sp[0], q = sp[1], r = sp[2], t = sp[3];
-        acc[c][0] = fmaf(w, p.x, acc[c][0]); acc[c][1] = fmaf(w, p.y, acc[c][1]); acc[c][2] = fmaf(w, p.z, acc[c][2]);
-        acc[c][3] = fmaf(w, p.w, acc[c][3]); acc[c][4] = fmaf(w, q.x, acc[c][4]); acc[c][5] = fmaf(w, q.y, acc[c][5]);
-        acc[c][6] = fmaf(w, q.z, acc[c][6]); acc[c][7] = fmaf(w, q.w, acc[c][7]); acc[c][8] = fmaf(w, r.x, acc[c][8]);
-        acc[c][9] = fmaf(w, r.y, acc[c][9]); acc[c][10] = fmaf(w, r.z, acc[c][10]); acc[c][11] = fmaf(w, r.w, acc[c][11]);
-        acc[c][12] = fmaf(w, t.x, acc[c][12]); acc[c][13] = fmaf(w, t.y, acc[c][13]); acc[c][14] = fmaf(w, t.z, acc[c][14]);
-        acc[c][15] = fmaf(w, t.w, acc[c][15]);
-      }
-    }
+// The per-slot scalars of a step from the five (already warp-reduced) sums.
+struct SlotScalars { float nk, nv, nw, simr, simw, relr, relw, strength, mask; };
+
+__device__ __forceinline__ SlotScalars slot_scalars(float sk, float dkq, float sv, float sw, float dwq, float age, float mu_m,
+                                                    const ScreenScanArgs& a) {
+  SlotScalars c;
+  const float e2 = a.eps * a.eps;
+  c.nk = sqrtf(sk + e2);
+  c.nv = a.value_unit_norm ? sqrtf(sv + e2) : 1.f;
+  c.nw = sqrtf(sw + e2);
+  c.simr = dkq / c.nk;
+  c.simw = dwq / c.nw;
+  c.mask = a.age_mask ? sigmoidf_((a.age_ref - age) / (a.age_sigma + a.eps)) : 1.f;
+  c.relr = read_relevance(c.simr, a) * c.mask;
+  c.relw = 0.f;
+  c.strength = mu_m;
+  if (a.write_enabled) {
+    c.relw = trim_sq(c.simw, a.tau_w, a.eps);
+    c.strength *= fmaxf(c.relw, a.write_rel_floor);
   }
+  return c;
 }
 
-// norms, similarities, relevances and the write strength of slot m from its row of raw projections (one warp)
-__device__ __forceinline__ void slot_scalars(const float* __restrict__ Pm, const SeqSmem& s, const ScreenScanArgs& a, int m,
-                                             int lane) {
-  float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f;
-  for (int j = lane; j < a.dk; j += 32) { const float x = Pm[j]; sk = fmaf(x, x, sk); dkq = fmaf(x, s.qr[j], dkq); }
-  for (int j = lane; j < a.dv; j += 32) { const float x = Pm[a.dk + j]; sv = fmaf(x, x, sv); }
-  if (a.write_enabled)
-    for (int j = lane; j < a.dk; j += 32) { const float x = Pm[a.dk + a.dv + j]; sw = fmaf(x, x, sw); dwq = fmaf(x, s.qw[j], dwq); }
-  sk = warp_sum(sk); dkq = warp_sum(dkq); sv = warp_sum(sv);
-  if (a.write_enabled) { sw = warp_sum(sw); dwq = warp_sum(dwq); }
-  if (lane == 0) {
-    float* c = s.sc + m * kSc;
-    const float e2 = a.eps * a.eps;
-    const float nk = sqrtf(sk + e2), nv = a.value_unit_norm ? sqrtf(sv + e2) : 1.f, nw = sqrtf(sw + e2);
-    const float simr = dkq / nk, simw = dwq / nw;
-    float relr = read_relevance(simr, a);
-    if (a.age_mask) relr *= sigmoidf_((a.age_ref - s.ages[m]) / (a.age_sigma + a.eps));
-    const bool live = m < a.M;
-    if (!live) relr = 0.f;
-    float relw = 0.f, strength = live ? a.mu[m] : 0.f;
-    if (a.write_enabled && live) {
-      relw = trim_sq(simw, a.tau_w, a.eps);
-      strength *= fmaxf(relw, a.write_rel_floor);
-    }
-    c[0] = nk; c[1] = nv; c[2] = nw; c[3] = simr; c[4] = simw; c[5] = relr; c[6] = relw; c[7] = strength;
-    c[8] = relr / nv;
+// Packed per-step rows laid out like the columns of P: [q_r | 0 | q_w] (the value columns receive dz in backward).
+__global__ void __launch_bounds__(256) screen_pack_rows_kernel(ScreenScanArgs a) {
+  const int J = 2 * a.dk + a.dv;
+  const size_t n = (size_t)a.B * a.T * J;
+  for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < n; e += (size_t)gridDim.x * 256) {
+    const size_t bt = e / J;
+    const int j = (int)(e - bt * J);
+    float v = 0.f;
+    if (j < a.dk) v = a.q_r[bt * a.dk + j];
+    else if (j >= a.dk + a.dv && a.write_enabled) v = a.q_w[bt * a.dk + j - a.dk - a.dv];
+    a.ws_rows[e] = v;
   }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// Sequential forward: u, the write strengths, ages, usage and the logged statistics; saves P and the ages per step.
+// Sequential forward, one warp per (slot, batch row): write strengths, read coefficients, ages, usage, the per-slot
+// statistics, and the row of P before every step.
 // ------------------------------------------------------------------------------------------------------------------
-template <int CPT>
-__global__ void __launch_bounds__(kSeqThreads) screen_seq_fwd_kernel(ScreenScanArgs a) {
-  extern __shared__ float smem_f[];
+template <int JPL>
+__global__ void __launch_bounds__(32) screen_slot_fwd_kernel(ScreenScanArgs a) {
   if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
-  const int J = 2 * a.dk + a.dv, Jp = padded_J(J);
-  const SeqSmem s = carve(smem_f, J, a.dk, a.dv, false);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.x;
+  const int m = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  const int J = 2 * a.dk + a.dv;
+  const ColumnMasks cm = column_masks<JPL>(lane, a.dk, a.dv, J);
+  const uint32_t any = cm.key | cm.val | cm.wkey;
 
-  if (tid < kMp) {
-    s.ages[tid] = tid < a.M ? a.ages0[b * a.M + tid] : 0.f;
-    s.usage[tid] = tid < a.M ? a.usage0[b * a.M + tid] : 0.f;
-  }
+  // projections of the initial bank (the only pass over the weights): P[j] = sum_d (S0[d] + [write key] E[d]) WT[d][j]
+  float P[JPL];
+#pragma unroll
+  for (int i = 0; i < JPL; ++i) P[i] = 0.f;
   {
-    float acc[CPT][kMp];
-    // E Wkw^T: only the write-key columns are kept
-    project_rows<CPT>(a.slot_embed, a, s.tile, J, tid, acc);
+    const float* s0 = a.slots0 + ((size_t)b * a.M + m) * a.ds;
+    const float* em = a.slot_embed + (size_t)m * a.ds;
+#pragma unroll 4
+    for (int d = 0; d < a.ds; ++d) {
+      const float sv = __ldg(s0 + d), se = sv + __ldg(em + d);
+      const float* w = a.WT + (size_t)d * J;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j >= a.dk + a.dv && j < J) {
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) s.EW[m * a.dk + j - a.dk - a.dv] = acc[c][m];
-      }
-    }
-    // projections of the initial bank (the only pass over the weights); afterwards they follow the slot recurrence
-    project_rows<CPT>(a.slots0 + (size_t)b * a.M * a.ds, a, s.tile, J, tid, acc);
-#pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j < J) {
-        const bool is_kw = j >= a.dk + a.dv;   // this thread wrote these EW entries itself
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) s.P[m * Jp + j] = acc[c][m] + (is_kw ? s.EW[m * a.dk + j - a.dk - a.dv] : 0.f);
-      }
+      for (int i = 0; i < JPL; ++i) P[i] = fmaf((cm.wkey >> i) & 1u ? se : sv, __ldg(w + min(lane + 32 * i, J - 1)), P[i]);
     }
   }
-  float st_acc[9];
-#pragma unroll
-  for (int i = 0; i < 9; ++i) st_acc[i] = 0.f;
+  float age = a.ages0[b * a.M + m], usage = a.usage0[b * a.M + m];
+  const float mu_m = a.mu[m];
+  float acc_relr = 0.f, acc_active = 0.f, acc_relw = 0.f, acc_eff = 0.f, acc_usage = 0.f;
 
-  // the step's vectors are fetched one step ahead into registers
-  float n_qr = 0.f, n_qw = 0.f;
-  float n_pd[CPT][kMp];
-#pragma unroll
-  for (int c = 0; c < CPT; ++c)
-#pragma unroll
-    for (int m = 0; m < kMp; ++m) n_pd[c][m] = 0.f;
+  const size_t row0 = ((size_t)b * a.T * kMp + m) * J;   // row of step 0; a step advances by 16 J
+  const size_t step = (size_t)kMp * J;
+  // Loads are unconditional (a register past the last column re-reads column J - 1 and is ignored by every sum and
+  // store): a select on a loaded value would make the warp wait for the load right where it is issued.  The queries
+  // come as one packed row [q_r | 0 | q_w] laid out like the columns of P.
+  float n_pd[JPL], n_q[JPL];
   auto fetch = [&](int t) {
-    const size_t bt = (size_t)b * a.T + t;
-    if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
+    const float* pd = a.PD + row0 + (size_t)t * step;
+    const float* rr = a.ws_rows + ((size_t)b * a.T + t) * J;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j < J) {
-        const float* src = a.PD + bt * kMp * J + j;
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) n_pd[c][m] = src[m * J];
-      }
+    for (int i = 0; i < JPL; ++i) {
+      const int j = min(lane + 32 * i, J - 1);
+      n_pd[i] = pd[j];
+      n_q[i] = rr[j];
     }
   };
+  auto pull = [&](int t) {   // towards L2, several steps ahead of the register prefetch
+    if (t >= a.T) return;
+    const float* pd = a.PD + row0 + (size_t)t * step + lane;
+#pragma unroll
+    for (int i = 0; i < JPL; ++i)
+      if ((any >> i) & 1u) prefetch_l2(pd + 32 * i);
+  };
+  for (int t = 1; t < kAhead; ++t) pull(t);
   fetch(0);
   for (int t = 0; t < a.T; ++t) {
     const size_t bt = (size_t)b * a.T + t;
-    if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
-    float pd[CPT][kMp];
+    float pd[JPL], q[JPL];
 #pragma unroll
-    for (int c = 0; c < CPT; ++c)
-#pragma unroll
-      for (int m = 0; m < kMp; ++m) pd[c][m] = n_pd[c][m];
+    for (int i = 0; i < JPL; ++i) { pd[i] = n_pd[i]; q[i] = n_q[i]; }
     if (t + 1 < a.T) fetch(t + 1);
-    __syncthreads();   // P of this step is complete (written at the end of the previous iteration); q staged
-    if (a.saved_P != nullptr) {
-      if (tid < kMp) a.saved_ages[bt * kMp + tid] = s.ages[tid];
+    pull(t + kAhead);
+    {
+      float* dst = a.saved_P + row0 + (size_t)t * step + lane;
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) {
-        const int j = tid + c * kSeqThreads;
-        if (j < J) {
-          float* dp = a.saved_P + bt * kMp * J + j;
-#pragma unroll
-          for (int m = 0; m < kMp; ++m) dp[m * J] = s.P[m * Jp + j];
-        }
-      }
+      for (int i = 0; i < JPL; ++i)
+        if ((any >> i) & 1u) dst[32 * i] = P[i];
     }
-    slot_scalars(s.P + warp * Jp, s, a, warp, lane);
-    __syncthreads();
-    // ---- read-out -------------------------------------------------------------------------------------------------
-    if (tid < a.dv) {
-      float acc = 0.f;
+    float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], s.P[m * Jp + a.dk + tid], acc);
-      s.z[tid] = acc;
+    for (int i = 0; i < JPL; ++i) {
+      const float x = P[i], xx = x * x, xq = x * q[i];
+      if ((cm.key >> i) & 1u) { sk += xx; dkq += xq; }
+      if ((cm.val >> i) & 1u) sv += xx;
+      if ((cm.wkey >> i) & 1u) { sw += xx; dwq += xq; }
     }
-    if (tid < kMp) a.strength[bt * kMp + tid] = s.sc[tid * kSc + 7];
-    __syncthreads();
-    float zn2 = 0.f;
-    for (int v = lane; v < a.dv; v += 32) zn2 = fmaf(s.z[v], s.z[v], zn2);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {   // one butterfly for all five sums: the shuffles of a stage overlap
+      sk += __shfl_xor_sync(0xffffffffu, sk, o); dkq += __shfl_xor_sync(0xffffffffu, dkq, o);
+      sv += __shfl_xor_sync(0xffffffffu, sv, o); sw += __shfl_xor_sync(0xffffffffu, sw, o);
+      dwq += __shfl_xor_sync(0xffffffffu, dwq, o);
+    }
+    const SlotScalars c = slot_scalars(sk, dkq, sv, sw, dwq, age, mu_m, a);
+    if (lane == 0) {
+      a.strength[bt * kMp + m] = c.strength;
+      a.rel_c[bt * kMp + m] = c.relr / c.nv;
+      a.rel_r[bt * kMp + m] = c.relr;
+      a.saved_ages[bt * kMp + m] = age;
+    }
+#pragma unroll
+    for (int i = 0; i < JPL; ++i) P[i] = fmaf(c.strength, pd[i] - P[i], P[i]);
+    if (a.write_enabled) age = c.relw > 1e-3f ? 0.f : age + 1.f;
+    const float act = a.write_enabled ? fmaxf(c.relr, c.relw) : c.relr;
+    usage = a.usage_decay * usage + (1.f - a.usage_decay) * act;
+    acc_relr += c.relr; acc_active += c.relr > 1e-3f ? 1.f : 0.f;
+    acc_relw += c.relw; acc_eff += a.write_enabled ? fmaxf(c.relw, a.write_rel_floor) : c.relw;
+    acc_usage += usage;
+  }
+  if (lane == 0) {
+    a.ages_out[b * a.M + m] = age;
+    a.usage_out[b * a.M + m] = usage;
+    const float im = 1.f / a.M;   // means over slots; sums over steps and batch rows stay sums (the host divides)
+    atomicAdd(a.stats + 0, acc_relr * im);
+    atomicAdd(a.stats + 2, acc_active);
+    atomicAdd(a.stats + 5, acc_relw * im);
+    atomicAdd(a.stats + 6, acc_eff * im);
+    atomicAdd(a.stats + 8, acc_usage * im);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Read-out over all (batch row, step) pairs, a warp per step: z = sum_m (rel_r[m] / nv[m]) P_t[m][values],
+// u = tanh_norm(z).  BWD = false writes u and the cross-slot statistics; BWD = true reads du and writes
+// dz = f du + z <z, du> ((1 - th^2) - f) / n^2, the cotangent of z, into the value columns of the packed rows.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kReadTile = 64;   // steps per block of 8 warps
+constexpr int kMaxVPL = 16;     // dv <= 512
+
+template <bool BWD>
+__global__ void __launch_bounds__(256) screen_readout_kernel(ScreenScanArgs a) {
+  __shared__ float red[8][3];
+  const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int J = 2 * a.dk + a.dv;
+  const int t_end = min(a.T, (int)(blockIdx.x + 1) * kReadTile);
+  float st_max = 0.f, st_zn = 0.f, st_un = 0.f;
+  for (int t = blockIdx.x * kReadTile + warp; t < t_end; t += 8) {
+    const size_t bt = (size_t)b * a.T + t;
+    const float c_l = lane < a.M ? a.rel_c[bt * kMp + lane] : 0.f;
+    float z[kMaxVPL];
+#pragma unroll
+    for (int i = 0; i < kMaxVPL; ++i) z[i] = 0.f;
+    const float* Pt = a.saved_P + bt * kMp * J + a.dk + lane;
+    for (int m = 0; m < a.M; ++m) {
+      const float c = __shfl_sync(0xffffffffu, c_l, m);
+#pragma unroll
+      for (int i = 0; i < kMaxVPL; ++i)
+        if (lane + 32 * i < a.dv) z[i] = fmaf(c, Pt[(size_t)m * J + 32 * i], z[i]);
+    }
+    float zn2 = 0.f, zdu = 0.f;
+    float du[kMaxVPL];
+#pragma unroll
+    for (int i = 0; i < kMaxVPL; ++i) {
+      du[i] = 0.f;
+      if (BWD && lane + 32 * i < a.dv) du[i] = a.du[bt * a.dv + lane + 32 * i];
+      zn2 = fmaf(z[i], z[i], zn2);
+      zdu = fmaf(z[i], du[i], zdu);
+    }
     zn2 = warp_sum(zn2);
-    const float zn = sqrtf(zn2 + a.eps * a.eps);
-    const float f = a.cap * tanhf(zn / a.cap) / zn;
-    if (tid < a.dv) a.u_out[bt * a.dv + tid] = f * s.z[tid];
-    // ---- the projections follow the slot interpolation ----------------------------------------------------------------
+    const float n2 = zn2 + a.eps * a.eps, zn = sqrtf(n2);
+    const float th = tanhf(zn / a.cap);
+    const float f = a.cap * th / zn;
+    if (BWD) {
+      zdu = warp_sum(zdu);
+      const float coef = zdu * ((1.f - th * th) - f) / n2;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j < J) {
+      for (int i = 0; i < kMaxVPL; ++i)
+        if (lane + 32 * i < a.dv) a.ws_rows[bt * J + a.dk + lane + 32 * i] = f * du[i] + coef * z[i];
+    } else {
 #pragma unroll
-        for (int m = 0; m < kMp; ++m) {
-          const float old = s.P[m * Jp + j];
-          s.P[m * Jp + j] = fmaf(s.sc[m * kSc + 7], pd[c][m] - old, old);
-        }
-      }
-    }
-    // ---- ages, usage and the logged statistics: lane m of warp 0 keeps slot m's running sums in registers ------------
-    if (warp == 0) {
-      const int m = lane & 15;
-      const bool live = lane < kMp && m < a.M;
-      const float relr = live ? s.sc[m * kSc + 5] : 0.f, relw = live ? s.sc[m * kSc + 6] : 0.f;
-      float rx = relr;
+      for (int i = 0; i < kMaxVPL; ++i)
+        if (lane + 32 * i < a.dv) a.u_out[bt * a.dv + lane + 32 * i] = f * z[i];
+      float rx = lane < a.M ? a.rel_r[bt * kMp + lane] : 0.f;
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) rx = fmaxf(rx, __shfl_xor_sync(0xffffffffu, rx, o));
-      if (live) {
-        if (a.write_enabled) s.ages[m] = relw > 1e-3f ? 0.f : s.ages[m] + 1.f;
-        const float act = a.write_enabled ? fmaxf(relr, relw) : relr;
-        const float us = a.usage_decay * s.usage[m] + (1.f - a.usage_decay) * act;
-        s.usage[m] = us;
-        st_acc[0] += relr; st_acc[2] += relr > 1e-3f ? 1.f : 0.f;
-        st_acc[5] += relw; st_acc[6] += a.write_enabled ? fmaxf(relw, a.write_rel_floor) : relw;
-        st_acc[8] += us;
-      }
-      if (lane == 0) { st_acc[1] += rx; st_acc[3] += zn; st_acc[4] += f * zn; }
+      for (int o = 16; o > 0; o >>= 1) rx = fmaxf(rx, __shfl_xor_sync(0xffffffffu, rx, o));
+      st_max += rx; st_zn += zn; st_un += f * zn;
     }
   }
-  __syncthreads();
-  if (tid < a.M) { a.ages_out[b * a.M + tid] = s.ages[tid]; a.usage_out[b * a.M + tid] = s.usage[tid]; }
-  if (warp == 0) {   // per-slot sums -> means over slots (sums over steps and batch rows stay sums; the host divides)
-    const float im = 1.f / a.M;
-#pragma unroll
-    for (int i = 0; i < 9; ++i) {
-      if (i == 7) continue;   // the update norm comes from the bank kernel
-      float v = lane < kMp ? st_acc[i] : 0.f;
-      v = warp_sum(v);
-      const bool per_slot_mean = i == 0 || i == 5 || i == 6 || i == 8;
-      if (lane == 0) atomicAdd(a.stats + i, per_slot_mean ? v * im : v);
+  if (!BWD) {
+    if (lane == 0) { red[warp][0] = st_max; red[warp][1] = st_zn; red[warp][2] = st_un; }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+      float v = 0.f;
+      for (int w = 0; w < 8; ++w) v += red[w][threadIdx.x];
+      atomicAdd(a.stats + (threadIdx.x == 0 ? 1 : threadIdx.x == 1 ? 3 : 4), v);
     }
   }
 }
@@ -482,10 +452,12 @@ __global__ void __launch_bounds__(256) screen_bank_bwd_kernel(ScreenScanArgs a) 
     float sum = 0.f;
 #pragma unroll
     for (int m = 0; m < kMp; ++m) {
-      const float D = tanhf(x + dsl[m]);
-      const float term = coef[i][m] * g[m] * (1.f - D * D);
-      acc[m] += term;
-      sum += term;
+      if (m < a.M) {   // rows of the workspaces beyond the live slots are never written
+        const float D = tanhf(x + dsl[m]);
+        const float term = coef[i][m] * g[m] * (1.f - D * D);
+        acc[m] += term;
+        sum += term;
+      }
     }
     a.d_delta_xh[o] = sum;
   }
@@ -500,208 +472,211 @@ __global__ void __launch_bounds__(256) screen_bank_bwd_kernel(ScreenScanArgs a) 
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// Sequential backward over the saved projections: cotangents of q_r, q_w, PD, the initial projections, mu and the two
-// thresholds.  ws_G (optional) is the strength cotangent that arrives through the bank.
+// Sequential backward, one warp per (slot, batch row), over the saved rows of P: cotangents of PD and of the initial
+// projections, of mu and the two thresholds, and the per-step factors of the query cotangents.  ws_G (optional) is the
+// strength cotangent that arrives through the bank; the value columns of the packed rows hold the cotangent of z.
 // ------------------------------------------------------------------------------------------------------------------
-template <int CPT>
-__global__ void __launch_bounds__(kSeqThreads) screen_seq_bwd_kernel(ScreenScanArgs a) {
-  extern __shared__ float smem_f[];
+template <int JPL>
+__global__ void __launch_bounds__(32) screen_slot_bwd_kernel(ScreenScanArgs a) {
   if (a.tau_dev != nullptr) { a.tau_r = a.tau_dev[0]; a.tau_w = a.tau_dev[1]; }
-  const int J = 2 * a.dk + a.dv, Jp = padded_J(J);
-  const SeqSmem s = carve(smem_f, J, a.dk, a.dv, true);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.x;
-  const float e2 = a.eps * a.eps;
-
-  for (int e = tid; e < kMp * Jp; e += kSeqThreads) s.dP[e] = 0.f;   // the projections after the last step feed nothing
-  float dmu_acc = 0.f, dtaur_acc = 0.f, dtauw_acc = 0.f;   // lane 0 of warp m: slot m
-
-  // everything a step reads from global memory is fetched one step ahead into registers
-  float n_qr = 0.f, n_qw = 0.f, n_du = 0.f, n_age = 0.f, n_G = 0.f;
-  float n_P[CPT][kMp], n_PD[CPT][kMp];
+  const int m = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  const int J = 2 * a.dk + a.dv;
+  const ColumnMasks cm = column_masks<JPL>(lane, a.dk, a.dv, J);
+  const uint32_t any = cm.key | cm.val | cm.wkey;
+  const float mu_m = a.mu[m];
+  float g[JPL];   // cotangent of the carried row of P; the projections after the last step feed nothing
 #pragma unroll
-  for (int c = 0; c < CPT; ++c)
-#pragma unroll
-    for (int m = 0; m < kMp; ++m) { n_P[c][m] = 0.f; n_PD[c][m] = 0.f; }
-  auto fetch = [&](int t) {
+  for (int i = 0; i < JPL; ++i) g[i] = 0.f;
+  float dmu_acc = 0.f, dtaur_acc = 0.f, dtauw_acc = 0.f;
+
+  const size_t row0 = ((size_t)b * a.T * kMp + m) * J;
+  const size_t step = (size_t)kMp * J;
+  // per step: the saved row of P, the row of PD, and one row r = [q_r | dz | q_w] laid out like the columns of P
+  float n_P[JPL], n_pd[JPL], n_r[JPL], n_age = 0.f, n_G = 0.f;
+  const float* Gp = a.ws_G != nullptr ? a.ws_G : a.strength;   // without a bank cotangent: finite numbers, times zero
+  const float g_on = a.ws_G != nullptr ? 1.f : 0.f;
+  auto fetch = [&](int t) {   // unconditional loads, as in the forward kernel
     const size_t bt = (size_t)b * a.T + t;
-    if (tid < a.dk) { n_qr = a.q_r[bt * a.dk + tid]; n_qw = a.write_enabled ? a.q_w[bt * a.dk + tid] : 0.f; }
-    if (tid < a.dv) n_du = a.du[bt * a.dv + tid];
-    if (tid < kMp) {
-      n_age = a.saved_ages[bt * kMp + tid];
-      n_G = a.ws_G != nullptr ? a.ws_G[bt * kMp + tid] : 0.f;
-    }
+    const float* sp = a.saved_P + row0 + (size_t)t * step;
+    const float* pd = a.PD + row0 + (size_t)t * step;
+    const float* rr = a.ws_rows + bt * J;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j < J) {
-        const float* sp = a.saved_P + bt * kMp * J + j;
-        const float* pp = a.PD + bt * kMp * J + j;
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) { n_P[c][m] = sp[m * J]; n_PD[c][m] = pp[m * J]; }
-      }
+    for (int i = 0; i < JPL; ++i) {
+      const int j = min(lane + 32 * i, J - 1);
+      n_P[i] = sp[j];
+      n_pd[i] = pd[j];
+      n_r[i] = rr[j];
     }
+    n_age = a.saved_ages[bt * kMp + m];
+    n_G = Gp[bt * kMp + m];
   };
+  auto pull = [&](int t) {
+    if (t < 0) return;
+    const float* sp = a.saved_P + row0 + (size_t)t * step + lane;
+    const float* pd = a.PD + row0 + (size_t)t * step + lane;
+#pragma unroll
+    for (int i = 0; i < JPL; ++i)
+      if ((any >> i) & 1u) { prefetch_l2(sp + 32 * i); prefetch_l2(pd + 32 * i); }
+  };
+  for (int t = a.T - 2; t > a.T - 1 - kAhead; --t) pull(t);
   fetch(a.T - 1);
   for (int t = a.T - 1; t >= 0; --t) {
     const size_t bt = (size_t)b * a.T + t;
-    // P alternates between two buffers: the query cotangents at the end of a step still read this step's copy while
-    // the next step's staging writes the other one
-    float* P = s.P + (t & 1) * kMp * Jp;
+    float P[JPL], pd[JPL], r[JPL];
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-      const int j = tid + c * kSeqThreads;
-      if (j < J) {
-#pragma unroll
-        for (int m = 0; m < kMp; ++m) { P[m * Jp + j] = n_P[c][m]; s.PD[m * Jp + j] = n_PD[c][m]; }
-      }
-    }
-    if (tid < kMp) { s.ages[tid] = n_age; s.dstr[tid] = n_G; }
-    if (tid < a.dk) { s.qr[tid] = n_qr; s.qw[tid] = n_qw; }
-    if (tid < a.dv) s.du[tid] = n_du;
+    for (int i = 0; i < JPL; ++i) { P[i] = n_P[i]; pd[i] = n_pd[i]; r[i] = n_r[i]; }
+    const float age = n_age, G = n_G * g_on;
     if (t > 0) fetch(t - 1);
-    __syncthreads();
-    const float* Pm = P + warp * Jp;
-    slot_scalars(Pm, s, a, warp, lane);
-    __syncthreads();
-    if (tid < a.dv) {
-      float acc = 0.f;
+    pull(t - kAhead);
+    float sk = 0.f, dkq = 0.f, sv = 0.f, sw = 0.f, dwq = 0.f, sdz = 0.f, dsp = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) acc = fmaf(s.sc[m * kSc + 8], P[m * Jp + a.dk + tid], acc);
-      s.z[tid] = acc;
+    for (int i = 0; i < JPL; ++i) {
+      const float x = P[i], xx = x * x, xr = x * r[i];
+      if ((cm.key >> i) & 1u) { sk += xx; dkq += xr; }
+      if ((cm.val >> i) & 1u) { sv += xx; sdz += xr; }
+      if ((cm.wkey >> i) & 1u) { sw += xx; dwq += xr; }
+      dsp = fmaf(g[i], pd[i] - x, dsp);
     }
-    // ---- backward of the projection update P' = P + s (PD - P): warp m owns slot m ------------------------------------
-    {
-      const int m = warp;
-      const float strength = s.sc[m * kSc + 7];
-      float* gp = s.dP + m * Jp;
-      float* out = a.d_PD + (bt * kMp + m) * J;
-      float dsp = 0.f;
-      for (int j = lane; j < J; j += 32) {
-        const float g = gp[j];
-        dsp = fmaf(g, s.PD[m * Jp + j] - Pm[j], dsp);
-        out[j] = strength * g;
-        gp[j] = (1.f - strength) * g;
-      }
-      dsp = warp_sum(dsp);
-      if (lane == 0) s.dstr[m] += dsp;   // this warp is the only writer of dstr[m] after the staging above
-    }
-    __syncthreads();
-    // ---- cotangent of z from the cotangent of u = f(n) z -------------------------------------------------------------
-    float zn2 = 0.f, zdu = 0.f;
-    for (int v = lane; v < a.dv; v += 32) { zn2 = fmaf(s.z[v], s.z[v], zn2); zdu = fmaf(s.z[v], s.du[v], zdu); }
-    zn2 = warp_sum(zn2); zdu = warp_sum(zdu);
-    const float n2 = zn2 + e2, zn = sqrtf(n2);
-    const float th = tanhf(zn / a.cap);
-    const float f = a.cap * th / zn;
-    const float coef = zdu * ((1.f - th * th) - f) / n2;
-    if (tid < a.dv) s.dz[tid] = f * s.du[tid] + coef * s.z[tid];
-    __syncthreads();
-    // ---- per-slot scalars backward; cotangent of the raw projections ---------------------------------------------------
-    {
-      const int m = warp;
-      const float* c = s.sc + m * kSc;
-      const float nk = c[0], nv = c[1], nw = c[2], simr = c[3], simw = c[4], relr = c[5], relw = c[6];
-      const bool live = m < a.M;
-      float drelr = 0.f;
-      for (int v = lane; v < a.dv; v += 32) drelr = fmaf(s.dz[v], Pm[a.dk + v] / nv, drelr);
-      drelr = warp_sum(drelr);
-      float mask = 1.f;
-      if (a.age_mask) mask = sigmoidf_((a.age_ref - s.ages[m]) / (a.age_sigma + a.eps));
-      float g_sim, g_tau;
-      read_relevance_grad(simr, a, g_sim, g_tau);
-      const float dtrim = live ? drelr * mask : 0.f;
-      const float dsr = dtrim * g_sim;
-      float dsw = 0.f, gate_w = 1.f;
-      const float ds_m = s.dstr[m];
-      if (a.write_enabled && live) {
-        gate_w = fmaxf(relw, a.write_rel_floor);
-        const float drelw = relw > a.write_rel_floor ? ds_m * a.mu[m] : 0.f;
-        const float den_w = 1.f - a.tau_w + a.eps;
-        const float xw = fmaxf((simw - a.tau_w) / den_w, 0.f);
-        dsw = drelw * 2.f * xw / den_w;
-        if (lane == 0) dtauw_acc += drelw * 2.f * xw * (simw - 1.f - a.eps) / (den_w * den_w);
-      }
-      if (lane == 0) {
-        if (live) { dtaur_acc += dtrim * g_tau; dmu_acc += ds_m * gate_w; }
-        s.dsimr[m] = live ? dsr : 0.f;
-        s.dsimw[m] = live ? dsw : 0.f;
-      }
-      float* gp = s.dP + m * Jp;   // same warp and lanes as the scaling above: no barrier needed in between
-      if (live) {
-        for (int j = lane; j < a.dk; j += 32)   // read keys: k = x / nk, sim = q . k
-          gp[j] += dsr * (s.qr[j] - Pm[j] / nk * simr) / nk;
-        for (int v = lane; v < a.dv; v += 32) {   // values
-          const float val = Pm[a.dk + v] / nv;
-          gp[a.dk + v] += a.value_unit_norm ? relr * (s.dz[v] - val * drelr) / nv : relr * s.dz[v];
-        }
-        if (a.write_enabled)
-          for (int j = lane; j < a.dk; j += 32)   // write keys
-            gp[a.dk + a.dv + j] += dsw * (s.qw[j] - Pm[a.dk + a.dv + j] / nw * simw) / nw;
-      }
-    }
-    __syncthreads();
-    // ---- cotangents of the queries -------------------------------------------------------------------------------------
-    if (tid < a.dk) {
-      float gr = 0.f, gw = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMp; ++m) {
-        gr = fmaf(s.dsimr[m], P[m * Jp + tid] / s.sc[m * kSc + 0], gr);
-        gw = fmaf(s.dsimw[m], P[m * Jp + a.dk + a.dv + tid] / s.sc[m * kSc + 2], gw);
-      }
-      a.d_q_r[bt * a.dk + tid] = gr;
-      if (a.write_enabled) a.d_q_w[bt * a.dk + tid] = gw;
+    for (int o = 16; o > 0; o >>= 1) {
+      sk += __shfl_xor_sync(0xffffffffu, sk, o); dkq += __shfl_xor_sync(0xffffffffu, dkq, o);
+      sv += __shfl_xor_sync(0xffffffffu, sv, o); sw += __shfl_xor_sync(0xffffffffu, sw, o);
+      dwq += __shfl_xor_sync(0xffffffffu, dwq, o); sdz += __shfl_xor_sync(0xffffffffu, sdz, o);
+      dsp += __shfl_xor_sync(0xffffffffu, dsp, o);
     }
-    // no barrier here: the next step's staging touches the other P buffer, PD (last read two barriers ago) and the step
-    // vectors, none of which the query cotangents read; sc, dsimr and dsimw are rewritten only after the next barrier
+    const SlotScalars c = slot_scalars(sk, dkq, sv, sw, dwq, age, mu_m, a);
+    // ---- backward of the projection update P' = P + s (PD - P) -------------------------------------------------------
+    const float dstr = G + dsp;
+    {
+      float* out = a.d_PD + row0 + (size_t)t * step + lane;
+#pragma unroll
+      for (int i = 0; i < JPL; ++i) {
+        if ((any >> i) & 1u) out[32 * i] = c.strength * g[i];
+        g[i] *= 1.f - c.strength;
+      }
+    }
+    // ---- per-slot scalars backward ----------------------------------------------------------------------------------------
+    const float drelr = sdz / c.nv;   // cotangent of rel_r: sum_v dz[v] val[v]
+    float g_sim, g_tau;
+    read_relevance_grad(c.simr, a, g_sim, g_tau);
+    const float dtrim = drelr * c.mask;
+    const float dsr = dtrim * g_sim;
+    dtaur_acc += dtrim * g_tau;
+    float dsw = 0.f, gate_w = 1.f;
+    if (a.write_enabled) {
+      gate_w = fmaxf(c.relw, a.write_rel_floor);
+      const float drelw = c.relw > a.write_rel_floor ? dstr * mu_m : 0.f;
+      const float den_w = 1.f - a.tau_w + a.eps;
+      const float xw = fmaxf((c.simw - a.tau_w) / den_w, 0.f);
+      dsw = drelw * 2.f * xw / den_w;
+      dtauw_acc += drelw * 2.f * xw * (c.simw - 1.f - a.eps) / (den_w * den_w);
+    }
+    dmu_acc += dstr * gate_w;
+    if (lane == 0) {   // factors of the query cotangents: dq_r = sum_m (dsim_r / nk) P[m][keys], likewise for q_w
+      a.ws_a[bt * kMp + m] = dsr / c.nk;
+      a.ws_b[bt * kMp + m] = dsw / c.nw;
+    }
+    // ---- cotangent of this step's row of P ----------------------------------------------------------------------------------
+    const float kr = dsr / c.nk, kr2 = kr * c.simr / c.nk;        // keys:   dsr (q - (P / nk) simr) / nk
+    const float kw = dsw / c.nw, kw2 = kw * c.simw / c.nw;        // write keys
+    const float relr_nv = c.relr / c.nv, vv = relr_nv * drelr / c.nv;   // values: relr (dz - (P / nv) drelr) / nv
+#pragma unroll
+    for (int i = 0; i < JPL; ++i) {
+      if ((cm.key >> i) & 1u) g[i] += kr * r[i] - kr2 * P[i];
+      if ((cm.val >> i) & 1u) g[i] += a.value_unit_norm ? relr_nv * r[i] - vv * P[i] : c.relr * r[i];
+      if (((cm.wkey >> i) & 1u) && a.write_enabled) g[i] += kw * r[i] - kw2 * P[i];
+    }
   }
-  __syncthreads();
-  // cotangent of the initial projections: the caller folds it into d slots0, d W and d slot_embed
+  {   // cotangent of the initial projections: the caller folds it into d slots0, d W and d slot_embed
+    float* out = a.d_P0 + ((size_t)b * kMp + m) * J + lane;
 #pragma unroll
-  for (int c = 0; c < CPT; ++c) {
-    const int j = tid + c * kSeqThreads;
-    if (j < J) {
-#pragma unroll
-      for (int m = 0; m < kMp; ++m) a.d_P0[((size_t)b * kMp + m) * J + j] = s.dP[m * Jp + j];
-    }
+    for (int i = 0; i < JPL; ++i)
+      if ((any >> i) & 1u) out[32 * i] = g[i];
   }
   if (lane == 0) {
     atomicAdd(a.d_scalars + 0, dtaur_acc);
     atomicAdd(a.d_scalars + 1, dtauw_acc);
-    if (warp < a.M) atomicAdd(a.d_mu + warp, dmu_acc);
+    atomicAdd(a.d_mu + m, dmu_acc);
   }
 }
 
-int columns_per_thread(int J) { return (J + kSeqThreads - 1) / kSeqThreads; }
+// Query cotangents over all (batch row, step) pairs, a warp per step: dq_r[j] = sum_m ws_a[m] P_t[m][j],
+// dq_w[j] = sum_m ws_b[m] P_t[m][dk + dv + j].
+__global__ void __launch_bounds__(256) screen_query_grad_kernel(ScreenScanArgs a) {
+  const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int J = 2 * a.dk + a.dv;
+  const int t_end = min(a.T, (int)(blockIdx.x + 1) * kReadTile);
+  for (int t = blockIdx.x * kReadTile + warp; t < t_end; t += 8) {
+    const size_t bt = (size_t)b * a.T + t;
+    const float a_l = lane < a.M ? a.ws_a[bt * kMp + lane] : 0.f;
+    const float b_l = lane < a.M ? a.ws_b[bt * kMp + lane] : 0.f;
+    const float* Pt = a.saved_P + bt * kMp * J;
+    for (int j = lane; j < a.dk; j += 32) {
+      float gr = 0.f, gw = 0.f;
+      for (int m = 0; m < a.M; ++m) {
+        gr = fmaf(__shfl_sync(0xffffffffu, a_l, m), Pt[(size_t)m * J + j], gr);
+        if (a.write_enabled) gw = fmaf(__shfl_sync(0xffffffffu, b_l, m), Pt[(size_t)m * J + a.dk + a.dv + j], gw);
+      }
+      a.d_q_r[bt * a.dk + j] = gr;
+      if (a.write_enabled) a.d_q_w[bt * a.dk + j] = gw;
+    }
+  }
+}
+
+template <template <int> class Launcher>
+int dispatch_jpl(int J, const ScreenScanArgs& a, cudaStream_t st) {
+  const int jpl = (J + 31) / 32;
+  if (jpl <= 2) return Launcher<2>::run(a, st);
+  if (jpl <= 4) return Launcher<4>::run(a, st);
+  if (jpl <= 6) return Launcher<6>::run(a, st);
+  if (jpl <= 8) return Launcher<8>::run(a, st);
+  if (jpl <= 12) return Launcher<12>::run(a, st);
+  if (jpl <= 18) return Launcher<18>::run(a, st);
+  if (jpl <= 24) return Launcher<24>::run(a, st);
+  if (jpl <= 32) return Launcher<32>::run(a, st);
+  return 1;
+}
+
+template <int JPL> struct FwdLauncher {
+  static int run(const ScreenScanArgs& a, cudaStream_t st) {
+    screen_slot_fwd_kernel<JPL><<<dim3(a.M, a.B), 32, 0, st>>>(a);
+    return 0;
+  }
+};
+template <int JPL> struct BwdLauncher {
+  static int run(const ScreenScanArgs& a, cudaStream_t st) {
+    screen_slot_bwd_kernel<JPL><<<dim3(a.M, a.B), 32, 0, st>>>(a);
+    return 0;
+  }
+};
 
 }  // namespace
 
 bool screen_scan_supported(const ScreenScanArgs& a) {
   const int J = 2 * a.dk + a.dv;
   return a.M >= 1 && a.M <= kMp && a.ds >= 1 && a.ds <= 32 * kDotMaxPerLane && a.dk >= 1 && a.dv >= 1 &&
-         a.dk <= kSeqThreads && a.dv <= kSeqThreads && J <= 2 * kSeqThreads &&
-         (size_t)seq_smem_floats(J, a.dk, a.dv, true) * sizeof(float) <= 227 * 1024 &&
-         (size_t)seq_smem_floats(J, a.dk, a.dv, false) * sizeof(float) <= 227 * 1024;
+         a.dv <= 32 * kMaxVPL && J <= 1024;
 }
 
 int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a) || a.PD == nullptr || a.strength == nullptr) return 1;
+  if (!screen_scan_supported(a) || a.PD == nullptr || a.strength == nullptr || a.saved_P == nullptr ||
+      a.saved_ages == nullptr || a.rel_c == nullptr || a.rel_r == nullptr)
+    return 1;
   const int J = 2 * a.dk + a.dv;
-  const size_t bytes = (size_t)seq_smem_floats(J, a.dk, a.dv, false) * sizeof(float);
-  if (columns_per_thread(J) == 1) {
-    cudaFuncSetAttribute(screen_seq_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    screen_seq_fwd_kernel<1><<<a.B, kSeqThreads, bytes, st>>>(a);
-  } else {
-    cudaFuncSetAttribute(screen_seq_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    screen_seq_fwd_kernel<2><<<a.B, kSeqThreads, bytes, st>>>(a);
-  }
+  if (a.ws_rows == nullptr) return 1;
+  const int pack_blocks = (int)std::min<size_t>(148 * 8, ((size_t)a.B * a.T * J + 255) / 256);
+  screen_pack_rows_kernel<<<pack_blocks, 256, 0, st>>>(a);
+  if (dispatch_jpl<FwdLauncher>(J, a, st) != 0) return 1;
+  screen_readout_kernel<false><<<dim3((a.T + kReadTile - 1) / kReadTile, a.B), 256, 0, st>>>(a);
   const int threads = ((a.ds + 31) / 32) * 32;
   screen_bank_fwd_kernel<<<dim3(a.M, a.B), threads, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st) {
-  if (!screen_scan_supported(a) || a.PD == nullptr || a.saved_P == nullptr || a.strength == nullptr) return 1;
+  if (!screen_scan_supported(a) || a.PD == nullptr || a.saved_P == nullptr || a.strength == nullptr ||
+      a.rel_c == nullptr || a.ws_rows == nullptr || a.ws_a == nullptr || a.ws_b == nullptr)
+    return 1;
   const int J = 2 * a.dk + a.dv;
   const bool bank = a.dslots_out != nullptr;
   if (bank) {
@@ -709,14 +684,11 @@ int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st) {
     screen_target_dot_kernel<<<dim3((a.T + kDotTile - 1) / kDotTile, a.M, a.B), 256, 0, st>>>(a);
     screen_bank_scalars_kernel<<<dim3(a.M, a.B), 32, 0, st>>>(a);
   }
-  const size_t bytes = (size_t)seq_smem_floats(J, a.dk, a.dv, true) * sizeof(float);
-  if (columns_per_thread(J) == 1) {
-    cudaFuncSetAttribute(screen_seq_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    screen_seq_bwd_kernel<1><<<a.B, kSeqThreads, bytes, st>>>(a);
-  } else {
-    cudaFuncSetAttribute(screen_seq_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    screen_seq_bwd_kernel<2><<<a.B, kSeqThreads, bytes, st>>>(a);
-  }
+  const int pack_blocks = (int)std::min<size_t>(148 * 8, ((size_t)a.B * a.T * J + 255) / 256);
+  screen_pack_rows_kernel<<<pack_blocks, 256, 0, st>>>(a);
+  screen_readout_kernel<true><<<dim3((a.T + kReadTile - 1) / kReadTile, a.B), 256, 0, st>>>(a);
+  if (dispatch_jpl<BwdLauncher>(J, a, st) != 0) return 1;
+  screen_query_grad_kernel<<<dim3((a.T + kReadTile - 1) / kReadTile, a.B), 256, 0, st>>>(a);
   if (bank)
     screen_bank_bwd_kernel<<<dim3((a.ds + 255) / 256, (a.T + kBankBwdTile - 1) / kBankBwdTile, a.B), 256, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

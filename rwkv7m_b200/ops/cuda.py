@@ -828,22 +828,26 @@ class ScreenScanFn(torch.autograd.Function):
         _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv)
         tensors = [f32(q_r), f32(q_w), dxh32, dds32, E32, WT, PD, f32(mu), f32(slots0), f32(ages0), f32(usage0)]
         need_grad = any(ctx.needs_input_grad)
-        u, so, ao, uo, stats, strength, saved_ages, saved_P = _C.screen_scan_fwd(*tensors, floats, *flags, need_grad, tau)
-        _count(2)
+        u, so, ao, uo, stats, strength, saved_ages, saved_P, rel_c = _C.screen_scan_fwd(*tensors, floats, *flags,
+                                                                                          need_grad, tau)
+        _count(3)
+        ctx.set_materialize_grads(False)   # an unused final bank must not turn into a zero cotangent: it selects kernels
         ctx.floats, ctx.flags, ctx.tau = floats, flags, tau
         ctx.dk, ctx.dv, ctx.M = dk, dv, slots0.shape[1]
         ctx.dtypes = [t.dtype for t in (q_r, q_w, delta_xh, delta_slot, slot_embed, w_kr, w_v, w_kw, mu, slots0)]
         if need_grad:
-            ctx.save_for_backward(*tensors, W, strength, saved_ages, saved_P)
+            ctx.save_for_backward(*tensors, W, strength, saved_ages, saved_P, rel_c)
         ctx.mark_non_differentiable(ao, uo, stats)
         return u, so, ao, uo, stats
 
     @staticmethod
     def backward(ctx, du, dso, *_):
-        *tensors, W, strength, saved_ages, saved_P = ctx.saved_tensors
+        *tensors, W, strength, saved_ages, saved_P, rel_c = ctx.saved_tensors
+        if du is None:
+            du = torch.zeros(*tensors[0].shape[:2], ctx.dv, dtype=torch.float32, device=tensors[0].device)
         dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0 = _C.screen_scan_bwd(
-            *tensors, ctx.floats, *ctx.flags, strength, saved_ages, saved_P, du.float().contiguous(), dso, ctx.tau)
-        _count(1 if dso is None else 4)
+            *tensors, ctx.floats, *ctx.flags, strength, saved_ages, saved_P, rel_c, du.float().contiguous(), dso, ctx.tau)
+        _count(3 if dso is None else 6)
         delta_xh, delta_slot, slot_embed, slots0 = tensors[2], tensors[3], tensors[4], tensors[8]
         dk, dv, M = ctx.dk, ctx.dv, ctx.M
         B, T, ds = delta_xh.shape
