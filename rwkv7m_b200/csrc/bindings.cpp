@@ -675,7 +675,8 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
                                     const std::vector<double>& f, bool write_enabled, bool value_unit_norm, bool age_mask,
                                     const Tensor& strength, const Tensor& saved_ages, const Tensor& saved_P,
                                     const Tensor& rel_c, const Tensor& du,
-                                    const c10::optional<Tensor>& dslots_out, const c10::optional<Tensor>& tau_dev) {
+                                    const c10::optional<Tensor>& dslots_out, const c10::optional<Tensor>& tau_dev,
+                                    bool dpd_bf16) {
   c10::cuda::CUDAGuard guard(q_r.device());
   rk::ScreenScanArgs a = screen_args(q_r, q_w, delta_xh, delta_slot, slot_embed, WT, PD, mu, slots0, ages0, usage0, f,
                                      write_enabled, value_unit_norm, age_mask);
@@ -691,7 +692,9 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
   Tensor ds0 = bank ? torch::empty_like(slots0) : torch::zeros_like(slots0);
   Tensor dds = torch::zeros_like(delta_slot), dmu = torch::zeros_like(mu);
   Tensor dsc = torch::zeros({2}, o);
-  Tensor dPD = torch::empty({a.B, a.T, 16, J}, o);
+  // rows of dead slots are not written by the kernel: zero them when the tensor feeds a GEMM over all 16 rows
+  auto od = dpd_bf16 ? o.dtype(at::kBFloat16) : o;
+  Tensor dPD = (dpd_bf16 && a.M < 16) ? torch::zeros({a.B, a.T, 16, J}, od) : torch::empty({a.B, a.T, 16, J}, od);
   Tensor dP0 = torch::empty({a.B, 16, J}, o);
   TORCH_CHECK(rel_c.numel() == (int64_t)a.B * a.T * 16 && du.numel() == (int64_t)a.B * a.T * a.dv, "saved tensors do not match");
   a.strength = const_cast<float*>(fptr(strength)); a.saved_ages = const_cast<float*>(fptr(saved_ages));
@@ -710,11 +713,32 @@ std::vector<Tensor> screen_scan_bwd(const Tensor& q_r, const Tensor& q_w, const 
     a.ws_h = ws.data_ptr<float>(); a.ws_G = a.ws_h + n; a.ws_coef = a.ws_G + n; a.ws_c0 = a.ws_coef + n;
   }
   a.d_q_r = dqr.data_ptr<float>(); a.d_q_w = dqw.data_ptr<float>(); a.d_delta_xh = dxh.data_ptr<float>();
-  a.d_PD = dPD.data_ptr<float>(); a.d_P0 = dP0.data_ptr<float>();
+  if (dpd_bf16) a.d_PD_bf16 = dPD.data_ptr(); else a.d_PD = dPD.data_ptr<float>();
+  a.d_P0 = dP0.data_ptr<float>();
   a.d_delta_slot = dds.data_ptr<float>(); a.d_slots0 = ds0.data_ptr<float>();
   a.d_mu = dmu.data_ptr<float>(); a.d_scalars = dsc.data_ptr<float>();
   TORCH_CHECK(rk::screen_scan_backward(a, stream()) == 0, "screen_scan_backward failed");
   return {dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0};
+}
+
+// D = tanh(delta_xh[:, :, None] + delta_slot[None, None]) as bf16 [B, T, 16, ds]; rows of slots >= M are zero
+Tensor screen_targets_fwd(const Tensor& delta_xh, const Tensor& delta_slot) {
+  c10::cuda::CUDAGuard guard(delta_xh.device());
+  const int64_t B = delta_xh.size(0), T = delta_xh.size(1), ds = delta_xh.size(2), M = delta_slot.size(0);
+  TORCH_CHECK(M <= 16 && delta_slot.size(1) == ds);
+  Tensor D = torch::empty({B, T, 16, ds}, delta_xh.options().dtype(at::kBFloat16));
+  rk::screen_targets_forward(fptr(delta_xh), fptr(delta_slot), D.data_ptr(), (int)B, (int)T, (int)M, (int)ds, stream());
+  return D;
+}
+
+// g_dxh += sum_m dD (1 - D^2), g_dslot += the same over (batch, step); both fp32, updated in place
+void screen_targets_bwd(const Tensor& dD, const Tensor& delta_xh, const Tensor& delta_slot, Tensor& g_dxh, Tensor& g_dslot) {
+  c10::cuda::CUDAGuard guard(delta_xh.device());
+  const int64_t B = delta_xh.size(0), T = delta_xh.size(1), ds = delta_xh.size(2), M = delta_slot.size(0);
+  TORCH_CHECK(dD.scalar_type() == at::kBFloat16 && dD.is_contiguous() && dD.numel() == B * T * 16 * ds);
+  TORCH_CHECK(g_dxh.numel() == delta_xh.numel() && g_dslot.numel() == delta_slot.numel());
+  rk::screen_targets_backward(dD.data_ptr(), fptr(delta_xh), fptr(delta_slot), const_cast<float*>(fptr(g_dxh)),
+                              const_cast<float*>(fptr(g_dslot)), (int)B, (int)T, (int)M, (int)ds, stream());
 }
 
 rk::TpPeers make_tp_peers(const std::vector<int64_t>& buf, int64_t buf_mc, const std::vector<int64_t>& aux, int64_t rank) {
@@ -835,6 +859,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("zero_reduce", &zero_reduce);
   m.def("screen_scan_fwd", &screen_scan_fwd);
   m.def("screen_scan_bwd", &screen_scan_bwd);
+  m.def("screen_targets_fwd", &screen_targets_fwd);
+  m.def("screen_targets_bwd", &screen_targets_bwd);
   m.def("tp_gather_seq", &tp_gather_seq);
   m.def("tp_gemm_reduce_scatter", &tp_gemm_reduce_scatter);
   m.def("tp_reduce_scatter_add", &tp_reduce_scatter_add);

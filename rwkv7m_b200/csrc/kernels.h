@@ -175,7 +175,8 @@ struct ScreenScanArgs {
   float* ws_rows;               // [B,T,J] packed per-step rows [q_r | 0 or dz | q_w] (workspace of both directions)
   float *ws_a, *ws_b;           // [B,T,16] per-slot factors of the query cotangents (backward workspace)
   float *d_q_r, *d_q_w, *d_delta_xh;      // [B,T,dk], [B,T,dk], [B,T,ds]
-  float* d_PD;                  // [B,T,16,J] cotangent of PD
+  float* d_PD;                  // [B,T,16,J] cotangent of PD (rows of dead slots are not written)
+  void* d_PD_bf16;              // when set, the same cotangent is written here in bf16 instead
   float* d_P0;                  // [B,16,J]   cotangent of the projections of the initial bank
   float* d_delta_slot;          // [M,ds]  accumulated with atomics (zeroed by the caller)
   float* d_slots0;              // [B,M,ds]
@@ -185,6 +186,11 @@ struct ScreenScanArgs {
 bool screen_scan_supported(const ScreenScanArgs& a);
 int screen_scan_forward(const ScreenScanArgs& a, cudaStream_t st);
 int screen_scan_backward(const ScreenScanArgs& a, cudaStream_t st);
+// D[b,t,m,d] = tanh(dxh[b,t,d] + dslot[m,d]) as bf16 [B,T,16,ds] (rows m >= M zero), and its backward: g_dxh[b,t,d] +=
+// sum_m dD (1 - D^2), g_dslot[m,d] += the same term over (b, t) (atomics); D is recomputed
+void screen_targets_forward(const float* dxh, const float* dslot, void* D, int B, int T, int M, int ds, cudaStream_t st);
+void screen_targets_backward(const void* dD, const float* dxh, const float* dslot, float* g_dxh, float* g_dslot, int B, int T,
+                             int M, int ds, cudaStream_t st);
 
 // ---- tensor-parallel sequence collectives over symmetric memory ---------------------------
 struct TpPeers {

@@ -34,6 +34,8 @@ namespace rk {
 
 namespace {
 
+using bf16 = __nv_bfloat16;
+
 constexpr int kMp = 16;   // slots are padded to 16 in the [B, T, 16, ...] tensors
 
 __device__ __forceinline__ float trim_sq(float sim, float tau, float eps) {
@@ -548,12 +550,19 @@ __global__ void __launch_bounds__(32) screen_slot_bwd_kernel(ScreenScanArgs a) {
     // ---- backward of the projection update P' = P + s (PD - P) -------------------------------------------------------
     const float dstr = G + dsp;
     {
-      float* out = a.d_PD + row0 + (size_t)t * step + lane;
+      if (a.d_PD_bf16 != nullptr) {   // as the operand of the tensor-core products that follow
+        bf16* out = reinterpret_cast<bf16*>(a.d_PD_bf16) + row0 + (size_t)t * step + lane;
 #pragma unroll
-      for (int i = 0; i < JPL; ++i) {
-        if ((any >> i) & 1u) out[32 * i] = c.strength * g[i];
-        g[i] *= 1.f - c.strength;
+        for (int i = 0; i < JPL; ++i)
+          if ((any >> i) & 1u) out[32 * i] = __float2bfloat16(c.strength * g[i]);
+      } else {
+        float* out = a.d_PD + row0 + (size_t)t * step + lane;
+#pragma unroll
+        for (int i = 0; i < JPL; ++i)
+          if ((any >> i) & 1u) out[32 * i] = c.strength * g[i];
       }
+#pragma unroll
+      for (int i = 0; i < JPL; ++i) g[i] *= 1.f - c.strength;
     }
     // ---- per-slot scalars backward ----------------------------------------------------------------------------------------
     const float drelr = sdz / c.nv;   // cotangent of rel_r: sum_v dz[v] val[v]
@@ -623,6 +632,60 @@ __global__ void __launch_bounds__(256) screen_query_grad_kernel(ScreenScanArgs a
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Write targets for the tensor-core projections: D[b,t,m,d] = tanh(dxh[b,t,d] + dslot[m,d]) in bf16, rows m >= M zero.
+// Block (chunk of 256 d, tile of 64 steps, batch row), thread d.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kTargetTile = 64;
+
+__global__ void __launch_bounds__(256) screen_targets_fwd_kernel(const float* __restrict__ dxh, const float* __restrict__ dslot,
+                                                                 bf16* __restrict__ D, int T, int M, int ds) {
+  const int d = blockIdx.x * 256 + threadIdx.x, b = blockIdx.z;
+  if (d >= ds) return;
+  const int t0 = blockIdx.y * kTargetTile, n = min(kTargetTile, T - t0);
+  float dsl[kMp];
+#pragma unroll
+  for (int m = 0; m < kMp; ++m) dsl[m] = m < M ? dslot[(size_t)m * ds + d] : 0.f;
+  for (int i = 0; i < n; ++i) {
+    const size_t bt = (size_t)b * T + t0 + i;
+    const float x = __ldg(dxh + bt * ds + d);
+    bf16* out = D + bt * kMp * ds + d;
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) out[(size_t)m * ds] = __float2bfloat16(m < M ? tanhf(x + dsl[m]) : 0.f);
+  }
+}
+
+// d dxh[b,t,d] += sum_m dD[b,t,m,d] (1 - D^2), d dslot[m,d] += the same term summed over (b, t); D is recomputed.
+__global__ void __launch_bounds__(256) screen_targets_bwd_kernel(const bf16* __restrict__ dD, const float* __restrict__ dxh,
+                                                                 const float* __restrict__ dslot, float* __restrict__ g_dxh,
+                                                                 float* __restrict__ g_dslot, int T, int M, int ds) {
+  const int d = blockIdx.x * 256 + threadIdx.x, b = blockIdx.z;
+  if (d >= ds) return;
+  const int t0 = blockIdx.y * kTargetTile, n = min(kTargetTile, T - t0);
+  float dsl[kMp], acc[kMp];
+#pragma unroll
+  for (int m = 0; m < kMp; ++m) { dsl[m] = m < M ? dslot[(size_t)m * ds + d] : 0.f; acc[m] = 0.f; }
+  for (int i = 0; i < n; ++i) {
+    const size_t bt = (size_t)b * T + t0 + i;
+    const float x = __ldg(dxh + bt * ds + d);
+    const bf16* src = dD + bt * kMp * ds + d;
+    float sum = 0.f;
+#pragma unroll
+    for (int m = 0; m < kMp; ++m) {
+      if (m < M) {
+        const float D = tanhf(x + dsl[m]);
+        const float term = __bfloat162float(src[(size_t)m * ds]) * (1.f - D * D);
+        acc[m] += term;
+        sum += term;
+      }
+    }
+    g_dxh[bt * ds + d] += sum;
+  }
+#pragma unroll
+  for (int m = 0; m < kMp; ++m)
+    if (m < M) atomicAdd(g_dslot + (size_t)m * ds + d, acc[m]);
+}
+
 template <template <int> class Launcher>
 int dispatch_jpl(int J, const ScreenScanArgs& a, cudaStream_t st) {
   const int jpl = (J + 31) / 32;
@@ -651,6 +714,17 @@ template <int JPL> struct BwdLauncher {
 };
 
 }  // namespace
+
+void screen_targets_forward(const float* dxh, const float* dslot, void* D, int B, int T, int M, int ds, cudaStream_t st) {
+  screen_targets_fwd_kernel<<<dim3((ds + 255) / 256, (T + kTargetTile - 1) / kTargetTile, B), 256, 0, st>>>(
+      dxh, dslot, (bf16*)D, T, M, ds);
+}
+
+void screen_targets_backward(const void* dD, const float* dxh, const float* dslot, float* g_dxh, float* g_dslot, int B, int T,
+                             int M, int ds, cudaStream_t st) {
+  screen_targets_bwd_kernel<<<dim3((ds + 255) / 256, (T + kTargetTile - 1) / kTargetTile, B), 256, 0, st>>>(
+      (const bf16*)dD, dxh, dslot, g_dxh, g_dslot, T, M, ds);
+}
 
 bool screen_scan_supported(const ScreenScanArgs& a) {
   const int J = 2 * a.dk + a.dv;

@@ -785,18 +785,27 @@ def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
     return totals
 
 
-def _screen_write_targets(delta_xh, delta_slot, slot_embed, W, dk, dv):
-    """D[b,t,m] = tanh(delta_xh[b,t] + delta_slot[m]) and its raw projections PD = D W^T, with slot_embed Wkw^T added
-    on the write-key columns and the slot axis zero-padded to 16 (the layout the scan kernels read)."""
+def _screen_write_targets(delta_xh, delta_slot, slot_embed, W, dk, dv, tensor_core=False):
+    """D[b,t,m] = tanh(delta_xh[b,t] + delta_slot[m]) and its raw projections PD = D W^T (fp32), with slot_embed Wkw^T
+    added on the write-key columns and the slot axis zero-padded to 16 (the layout the scan kernels read).
+
+    ``tensor_core``: the model computes in bf16, so the targets are written in bf16 by one kernel and projected by the
+    tcgen05 GEMM with fp32 accumulation and output (the precision at which the step-by-step scan projects the bank);
+    otherwise everything stays fp32 (library GEMM)."""
     B, T, ds = delta_xh.shape
     M, J = delta_slot.shape[0], W.shape[0]
-    D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])          # [B,T,M,ds]
     PD = torch.empty(B, T, 16, J, dtype=torch.float32, device=delta_xh.device)
-    if M == 16:
-        torch.matmul(D.view(B * T * 16, ds), W.t(), out=PD.view(B * T * 16, J))
+    if tensor_core:
+        D = _C.screen_targets_fwd(delta_xh, delta_slot)                              # [B,T,16,ds] bf16
+        gemm(D.view(B * T * 16, ds), W.to(torch.bfloat16), PD.view(B * T * 16, J), GEMM_TN, EPI_F32)
+        _count()
     else:
-        PD[:, :, :M] = D @ W.t()
-        PD[:, :, M:] = 0
+        D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])      # [B,T,M,ds]
+        if M == 16:
+            torch.matmul(D.view(B * T * 16, ds), W.t(), out=PD.view(B * T * 16, J))
+        else:
+            PD[:, :, :M] = D @ W.t()
+            PD[:, :, M:] = 0
     PD[:, :, :M, dk + dv:] += slot_embed @ W[dk + dv:].t()
     return D, PD
 
@@ -825,7 +834,9 @@ class ScreenScanFn(torch.autograd.Function):
                   1.0 if settings.get("leaky") else 0.0, settings.get("leaky_alpha", 0.0), settings.get("leaky_gamma", 8.0)]
         flags = (bool(settings["write_enabled"]), bool(settings["value_unit_norm"]), bool(settings["age_mask"]))
         dxh32, dds32, E32 = f32(delta_xh), f32(delta_slot), f32(slot_embed)
-        _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv)
+        fast = bool(settings.get("tensor_core")) and dxh32.shape[2] % 8 == 0 and W.shape[0] % 8 == 0
+        _, PD = _screen_write_targets(dxh32, dds32, E32, W, dk, dv, tensor_core=fast)
+        ctx.fast = fast
         tensors = [f32(q_r), f32(q_w), dxh32, dds32, E32, WT, PD, f32(mu), f32(slots0), f32(ages0), f32(usage0)]
         need_grad = any(ctx.needs_input_grad)
         u, so, ao, uo, stats, strength, saved_ages, saved_P, rel_c = _C.screen_scan_fwd(*tensors, floats, *flags,
@@ -846,25 +857,38 @@ class ScreenScanFn(torch.autograd.Function):
         if du is None:
             du = torch.zeros(*tensors[0].shape[:2], ctx.dv, dtype=torch.float32, device=tensors[0].device)
         dqr, dqw, dxh, dds, ds0, dmu, dsc, dPD, dP0 = _C.screen_scan_bwd(
-            *tensors, ctx.floats, *ctx.flags, strength, saved_ages, saved_P, rel_c, du.float().contiguous(), dso, ctx.tau)
+            *tensors, ctx.floats, *ctx.flags, strength, saved_ages, saved_P, rel_c, du.float().contiguous(), dso, ctx.tau,
+            ctx.fast)
         _count(3 if dso is None else 6)
         delta_xh, delta_slot, slot_embed, slots0 = tensors[2], tensors[3], tensors[4], tensors[8]
         dk, dv, M = ctx.dk, ctx.dv, ctx.M
         B, T, ds = delta_xh.shape
         J = W.shape[0]
         kw = slice(dk + dv, J)
-        D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])       # recomputed, [B,T,M,ds]
         g = dPD[:, :, :M]                                                              # [B,T,M,J]
-        g2, D2 = g.reshape(-1, J), D.reshape(-1, ds)
         # targets: PD = D W^T (+ E Wkw^T); initial bank: P0 = S0 W^T (+ E Wkw^T)
         g0 = dP0[:, :M]                                                                # [B,M,J]
-        dW = g2.t() @ D2 + g0.reshape(-1, J).t() @ slots0.reshape(-1, ds)
-        dD = (g2 @ W).view(B, T, M, ds)
-        dpre = dD * (1.0 - D * D)
-        dxh = dxh + dpre.sum(dim=2)
-        dds = dds + dpre.sum(dim=(0, 1))
+        if ctx.fast:   # dPD arrives in bf16 over all 16 rows: both products on the tcgen05 GEMM, D recomputed in bf16
+            D16 = _C.screen_targets_fwd(delta_xh, delta_slot).view(B * T * 16, ds)
+            g16 = dPD.view(B * T * 16, J)
+            dW = torch.empty(J, ds, dtype=torch.float32, device=dPD.device)
+            gemm(g16, D16, dW, GEMM_WGRAD, EPI_F32)
+            dD16 = torch.empty(B * T * 16, ds, dtype=torch.bfloat16, device=dPD.device)
+            gemm(g16, W.to(torch.bfloat16), dD16, GEMM_NN, EPI_BF16)
+            del D16
+            _C.screen_targets_bwd(dD16, delta_xh, delta_slot, dxh, dds)              # dxh, dds += ... in place
+            _count(2)
+            dW = dW + g0.reshape(-1, J).t() @ slots0.reshape(-1, ds)
+        else:
+            D = torch.tanh(delta_xh[:, :, None, :] + delta_slot[None, None, :, :])   # recomputed, [B,T,M,ds]
+            g2, D2 = g.reshape(-1, J), D.reshape(-1, ds)
+            dW = g2.t() @ D2 + g0.reshape(-1, J).t() @ slots0.reshape(-1, ds)
+            dD = (g2 @ W).view(B, T, M, ds)
+            dpre = dD * (1.0 - D * D)
+            dxh = dxh + dpre.sum(dim=2)
+            dds = dds + dpre.sum(dim=(0, 1))
         ds0 = ds0 + g0 @ W
-        dEW = g[..., kw].sum(dim=(0, 1)) + g0[..., kw].sum(dim=0)                     # [M, dk]
+        dEW = g[..., kw].sum(dim=(0, 1), dtype=torch.float32) + g0[..., kw].sum(dim=0)   # [M, dk]
         dW[kw] += dEW.t() @ slot_embed
         dE = dEW @ W[kw]
         dt = ctx.dtypes
@@ -899,6 +923,7 @@ def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **s
     settings = {"eps": cfg.eps, "cap": cfg.tanh_norm_cap, "floor": cfg.write_rel_floor, "usage_decay": cfg.usage_ema_decay,
                 "age_ref": cfg.age_ref, "age_sigma": cfg.age_sigma, "write_enabled": write_enabled,
                 "leaky": cfg.use_leaky_warmup, "leaky_alpha": cfg.leaky_alpha, "leaky_gamma": cfg.leaky_gamma,
+                "tensor_core": compute == torch.bfloat16,
                 "value_unit_norm": cfg.use_value_unit_norm, "age_mask": cfg.use_age_mask}
     u, slots, ages, usage, st = ScreenScanFn.apply(
         q_r, qw, delta_xh, delta_slot, mod.slot_embed, mod.k_proj_r.weight, mod.v_proj.weight, w_kw, mu,

@@ -112,3 +112,48 @@ def test_scan_kernel_long_sequence_default_slot_shape():
     assert rel(gx, gx_ref) < 1e-2
     for name in g_ref:
         assert rel(g[name], g_ref[name]) < 2e-2, (name, rel(g[name], g_ref[name]))
+
+
+@pytest.mark.parametrize("d_slot,d_k,d_v,n_slots", [(128, 64, 64, 16), (384, 96, 192, 12)])
+def test_scan_kernel_bf16_model_uses_tensor_core_projections(d_slot, d_k, d_v, n_slots):
+    """A bf16 model projects the write targets with the tcgen05 GEMM (bf16 operands, fp32 accumulation) and receives the
+    cotangent of those projections in bf16; the step-by-step scan of the same bf16 model projects the bank in bf16 at
+    every step, so the two agree at bf16 level."""
+    torch.manual_seed(3)
+    C, T, B = 128, 256, 2
+    cfg = ScreeningConfig(d_model=C, d_slot=d_slot, d_k=d_k, d_v=d_v, n_slots=n_slots, screened_layers=(0,),
+                          bank_ids=tuple(i % 3 for i in range(n_slots)), use_write_screening=True, write_rel_floor=1e-3)
+    mod = StateLevelScreening(cfg).cuda()
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+        mod.lambda_raw.fill_(0.5)
+    mod = mod.to(torch.bfloat16)
+    x = torch.randn(B, T, C, device="cuda").bfloat16()
+    h = torch.randn(B, T, C, device="cuda").bfloat16()
+    st = LayerScreenState(slots=torch.randn(B, n_slots, d_slot, device="cuda") * 0.3,
+                          ages=torch.zeros(B, n_slots, device="cuda"), usage_ema=torch.zeros(B, n_slots, device="cuda"))
+    wy = torch.randn(B, T, C, device="cuda")
+    ws = torch.randn_like(st.slots)
+
+    def run(reference):
+        for p in mod.parameters():
+            p.grad = None
+        xs = x.clone().requires_grad_(True)
+        s0 = LayerScreenState(st.slots.clone().requires_grad_(True), st.ages.clone(), st.usage_ema.clone())
+        if reference:
+            with ops.reference_mode():
+                out, ns, _ = mod(xs, h, s0, phase="read_write")
+        else:
+            out, ns, _ = mod(xs, h, s0, phase="read_write")
+        ((out.float() * wy).sum() + (ns.slots * ws).sum()).backward()
+        grads = {n: p.grad.float().clone() for n, p in mod.named_parameters() if p.grad is not None}
+        grads["x"], grads["slots0"] = xs.grad.float(), s0.slots.grad.float()
+        return out.float().detach(), ns.slots.detach(), grads
+
+    o_ref, s_ref, g_ref = run(True)
+    o, s, g = run(False)
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-9))
+    assert rel(o, o_ref) < 2e-2 and rel(s, s_ref) < 2e-2, (rel(o, o_ref), rel(s, s_ref))
+    worst = max((rel(g[n], g_ref[n]), n) for n in g_ref)
+    assert worst[0] < 8e-2, worst
