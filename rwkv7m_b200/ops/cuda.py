@@ -871,8 +871,10 @@ class ScreenScanFn(torch.autograd.Function):
         if ctx.fast:   # dPD arrives in bf16 over all 16 rows: both products on the tcgen05 GEMM, D recomputed in bf16
             D16 = _C.screen_targets_fwd(delta_xh, delta_slot).view(B * T * 16, ds)
             g16 = dPD.view(B * T * 16, J)
-            dW = torch.empty(J, ds, dtype=torch.float32, device=dPD.device)
-            gemm(g16, D16, dW, GEMM_WGRAD, EPI_F32)
+            # [J, ds] has a handful of output tiles and a reduction over every (batch, step, slot) row: the accumulating
+            # epilogue splits it along K over all SMs
+            dW = torch.zeros(J, ds, dtype=torch.float32, device=dPD.device)
+            gemm(g16, D16, dW, GEMM_WGRAD, EPI_ACC_F32)
             dD16 = torch.empty(B * T * 16, ds, dtype=torch.bfloat16, device=dPD.device)
             gemm(g16, W.to(torch.bfloat16), dD16, GEMM_NN, EPI_BF16)
             del D16
