@@ -195,17 +195,18 @@ def bench_loss(M, C, V, iters=5):
     return [{"kernel": "head_loss fwd+bwd", "M": M, "C": C, "V": V, "ms": t["median_ms"], "tflops": flops / t["median_ms"] / 1e9}]
 
 
-def bench_screening(B, T, iters=3):
-    """Screening slot scan (0.185b preset sizes: 16 slots x 128, d_k = d_v = 64), read/write phase, forward and backward."""
+def bench_screening(B, T, iters=3, preset="0.185b", dtype=torch.bfloat16):
+    """Screening layer at a preset's bank shape (0.185b: 16 slots x 128, d_k = d_v = 64; 7b: 16 x 1024, 128 / 512),
+    read/write phase, forward and backward.  A bf16 module projects the write targets on the tensor cores."""
     from rwkv7m_b200.config import model_preset
     from rwkv7m_b200.models.screening import StateLevelScreening
     from rwkv7m_b200.state import LayerScreenState
 
-    cfg = model_preset("0.185b").screening
-    mod = StateLevelScreening(cfg).cuda()
+    cfg = model_preset(preset).screening
+    mod = StateLevelScreening(cfg).cuda().to(dtype)
     C = cfg.d_model
-    x = torch.randn(B, T, C, device="cuda").requires_grad_(True)
-    h = torch.randn(B, T, C, device="cuda")
+    x = torch.randn(B, T, C, device="cuda", dtype=dtype).requires_grad_(True)
+    h = torch.randn(B, T, C, device="cuda", dtype=dtype)
     st = LayerScreenState(torch.zeros(B, cfg.n_slots, cfg.d_slot, device="cuda"), torch.zeros(B, cfg.n_slots, device="cuda"),
                           torch.zeros(B, cfg.n_slots, device="cuda"))
 
@@ -218,10 +219,11 @@ def bench_screening(B, T, iters=3):
         for p in mod.parameters():
             p.grad = None
         out, _, _ = mod(x, h, st, phase="read_write")
-        out.sum().backward()
+        out.float().sum().backward()
 
     tf, tb = _time(fwd, iters), _time(fb, iters)
-    return [{"kernel": "screening layer (fp32 module, slot scan kernels)", "B": B, "T": T, "slots": cfg.n_slots, "d_slot": cfg.d_slot,
+    return [{"kernel": "screening layer (%s module, slot kernels)" % str(dtype).split(".")[-1], "preset": preset, "B": B, "T": T,
+             "slots": cfg.n_slots, "d_slot": cfg.d_slot, "d_k": cfg.d_k, "d_v": cfg.d_v,
              "fwd_ms": tf["median_ms"], "fwd_bwd_ms": tb["median_ms"], "us_per_step_fwd": 1e3 * tf["median_ms"] / T}]
 
 
@@ -234,6 +236,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json-out", default=None)
     ap.add_argument("--small", action="store_true", help="small shapes only (profiling captures)")
+    ap.add_argument("--screen-preset", default="0.185b", help="preset whose bank shape the screening case uses")
+    ap.add_argument("--screen-steps", type=int, default=None, help="sequence length of the screening case")
     args = ap.parse_args(argv)
     results = []
     if args.wkv_impl:
@@ -257,7 +261,8 @@ def main(argv=None):
     if "loss" in args.what:
         results += bench_loss(4096 if args.small else 32768, 2048, 65536, iters=min(args.iters, 5))
     if "screening" in args.what:
-        results += bench_screening(8, 256 if args.small else 4096, iters=min(args.iters, 3))
+        steps = args.screen_steps or (256 if args.small else 4096)
+        results += bench_screening(8, steps, iters=min(args.iters, 3), preset=args.screen_preset)
     if "optim" in args.what:
         results += bench_optimizer((64 if args.small else 512) * 1024 * 1024, iters=args.iters)
     for r in results:
