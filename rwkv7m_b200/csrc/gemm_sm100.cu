@@ -208,6 +208,41 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
         }
 }
 
+// bf16 output through shared memory: the four epilogue warps write their 128 rows x 64 columns (two accumulator chunks
+// per thread = 128 bytes = one row of the box) into a 16 KB staging buffer in the 128-byte-swizzled layout, and one
+// thread hands the box to the copy engine (cp.async.bulk.tensor store), which writes full lines and clips at the matrix
+// edge.  Two buffers alternate; the issuing thread lets the previous store finish reading its buffer before the barrier
+// that precedes the next one, so a buffer is free again by the time the warps return to it.
+constexpr int kOutStageBytes = 128 * 128;   // 128 rows x 64 bf16
+
+__device__ __forceinline__ void epilogue_named_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int EPI>
+__device__ __forceinline__ void stage_round(const uint32_t (&v0)[32], const uint32_t (&v1)[32], uint8_t* buf, int tile_row,
+                                            int act) {
+  uint32_t pk[32];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float x0 = __uint_as_float(v0[2 * j]), x1 = __uint_as_float(v0[2 * j + 1]);
+    float y0 = __uint_as_float(v1[2 * j]), y1 = __uint_as_float(v1[2 * j + 1]);
+    if (EPI == kEpiReluSqBf16) {
+      x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1;
+      y0 = fmaxf(y0, 0.f); y0 *= y0; y1 = fmaxf(y1, 0.f); y1 *= y1;
+    } else if (act != 0) {
+      x0 = act_apply(x0, act); x1 = act_apply(x1, act); y0 = act_apply(y0, act); y1 = act_apply(y1, act);
+    }
+    __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1), g = __floats2bfloat162_rn(y0, y1);
+    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+    pk[16 + j] = *reinterpret_cast<uint32_t*>(&g);
+  }
+  uint8_t* dst = buf + tile_row * 128;
+  const int sw = tile_row & 7;   // 16-byte piece j of row r sits at piece j ^ (r mod 8)
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(dst + ((j ^ sw) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+  fence_proxy_async_smem();
+}
+
 // Tile order: blocks of kRasterM consecutive m-tiles sweep all n-tiles before the next block starts, so the
 // CTAs that run at the same time share a few A row-panels and B column-panels and both stay in L2.
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int raster_m, int& tm, int& tn) {
@@ -227,12 +262,13 @@ struct Tile {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = BN == 256 ? 512 : (BN == 128 ? 256 : 128);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * 16384 /*output staging*/ + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 template <int BN, int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, int tma_out,
                  void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int splits,
                  const void* __restrict__ aux, int ldaux, int act, int* __restrict__ err) {
   using TL = Tile<BN>;
@@ -240,7 +276,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * TL::kStageBytes);
+  uint8_t* out_stage = smem + kStages * TL::kStageBytes;   // 2 x 16 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + 2 * kOutStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tfull_bar = bars + 2 * kStages;
@@ -264,7 +301,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); if (tma_out) tma_prefetch_desc(&tmD); }
   if (warp == 1) { tmem_alloc(tmem_slot, TL::kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -345,6 +382,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     const bool atomic = splits > 1;
+    constexpr bool kCanStage = (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && BN >= 64;
+    const bool staged = kCanStage && tma_out != 0;
+    const bool issuer = warp == 2 && lane == 0;   // the one thread whose bulk groups track the output stores
+    int obuf = 0;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
       int tm, tn;
       tile_coords(work % num_tiles, tiles_m, tiles_n, raster_m, tm, tn);
@@ -361,8 +402,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32(t0 + c * 32, v0);
           tmem_ld_32x32(t0 + c * 32 + 32, v1);
           tmem_ld_wait();
-          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux, act);
-          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux, act);
+          if (kCanStage && staged) {
+            if (n0 + c * 32 < N) {   // same for all 128 threads
+              uint8_t* buf = out_stage + obuf * kOutStageBytes;
+              stage_round<EPI>(v0, v1, buf, q * 32 + lane, act);
+              if (issuer) tma_store_wait_read<0>();
+              epilogue_named_barrier();
+              if (issuer) { tma_store_2d(&tmD, buf, n0 + c * 32, m0); tma_store_commit(); }
+              obuf ^= 1;
+            }
+          } else {
+            store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux, act);
+            store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux, act);
+          }
         }
       } else {
         uint32_t v[32];
@@ -375,6 +427,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
+    if (staged && issuer) tma_store_wait<0>();   // the staging buffers are read until the last store has drained
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x10000 | 3); }
   }
 
@@ -408,12 +461,13 @@ struct PairTile {
   static constexpr int kBBytes = 128 * BK * 2;       // this CTA's 128 columns of B
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 512;              // two 256-column accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * 16384 /*output staging*/ + 1024 + 256;
 };
 
 template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmD, int tma_out,
                       void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m,
                       const void* __restrict__ aux, int ldaux, int act, int* __restrict__ err) {
   using TL = PairTile;
@@ -422,7 +476,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * TL::kStageBytes);
+  uint8_t* out_stage = smem + kStages * TL::kStageBytes;   // 2 x 16 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + 2 * kOutStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tfull_bar = bars + 2 * kStages;
@@ -447,7 +502,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); if (tma_out) tma_prefetch_desc(&tmD); }
   if (warp == 1) { tmem_alloc_pair(tmem_slot, TL::kTmemCols); tmem_relinquish_pair(); }
   tc_fence_before();
   __syncthreads();
@@ -528,6 +583,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
+    constexpr bool kCanStage = EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16;
+    const bool staged = kCanStage && tma_out != 0;
+    const bool issuer = warp == 2 && lane == 0;
+    int obuf = 0;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
@@ -542,14 +601,26 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32(t0 + c * 32, v0);
         tmem_ld_32x32(t0 + c * 32 + 32, v1);
         tmem_ld_wait();
-        store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux, act);
-        store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux, act);
+        if (kCanStage && staged) {
+          if (n0 + c * 32 < N && m0 < M) {   // same for all 128 threads
+            uint8_t* buf = out_stage + obuf * kOutStageBytes;
+            stage_round<EPI>(v0, v1, buf, q * 32 + lane, act);
+            if (issuer) tma_store_wait_read<0>();
+            epilogue_named_barrier();
+            if (issuer) { tma_store_2d(&tmD, buf, n0 + c * 32, m0); tma_store_commit(); }
+            obuf ^= 1;
+          }
+        } else {
+          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux, act);
+          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux, act);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
+    if (staged && issuer) tma_store_wait<0>();
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x30000 | 3); }
   }
 
@@ -662,6 +733,13 @@ int raster_rows(const GemmArgs& p) {
   return 16;
 }
 
+// RWKV7M_B200_GEMM_TMA_STORE=0 keeps the per-thread 16-byte stores of the bf16 epilogues (for comparisons).
+bool tma_store_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("RWKV7M_B200_GEMM_TMA_STORE"); on = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  return on == 1;
+}
+
 #define RK_TRACE(...) do { if (trace_on()) { fprintf(stderr, "[gemm] " __VA_ARGS__); fflush(stderr); } } while (0)
 bool trace_on() {
   static int on = -1;
@@ -681,6 +759,12 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   if (!ok) return 2;
   if (B_MN == 0) ok = make_map(&tb, p.B, p.N, p.K, p.ldb, BN); else ok = make_map(&tb, p.B, p.K, p.N, p.ldb, BK);
   if (!ok) return 2;
+  // bf16 store epilogues hand finished boxes to the copy engine when the output rows are 16-byte aligned
+  alignas(64) CUtensorMap td = ta;
+  int tma_out = 0;
+  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && BN >= 64 && tma_store_enabled() &&
+      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0)
+    tma_out = make_map(&td, p.D, p.M, p.N, p.ldd, BM) ? 1 : 0;
   RK_TRACE("maps ok\n");
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
   static bool attr_set = false;
@@ -703,8 +787,8 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   const int work = tiles * splits;
   const int grid = work < sm_count() ? work : sm_count();
   RK_TRACE("attr ok grid=%d smem=%d splits=%d\n", grid, TL::kSmemBytes, splits);
-  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.aux, p.ldaux,
-                                                   p.act, p.error_flag);
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(ta, tb, td, tma_out, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits, p.aux,
+                                               p.ldaux, p.act, p.error_flag);
   RK_TRACE("launched\n");
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -742,6 +826,11 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   if (!ok) return 2;
   if (B_MN == 0) ok = make_map(&tb, p.B, p.N, p.K, p.ldb, 128); else ok = make_map(&tb, p.B, p.K, p.N, p.ldb, BK);
   if (!ok) return 2;
+  alignas(64) CUtensorMap td = ta;
+  int tma_out = 0;
+  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && tma_store_enabled() &&
+      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0)
+    tma_out = make_map(&td, p.D, p.M, p.N, p.ldd, BM) ? 1 : 0;
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -751,8 +840,8 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.aux, p.ldaux,
-                                                    p.act, p.error_flag);
+  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, td, tma_out, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.aux,
+                                                    p.ldaux, p.act, p.error_flag);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
