@@ -252,7 +252,9 @@ def main(argv=None):
     if "gemm" in args.what:
         shapes = [(4096, 2048, 2048)] if args.small else [
             (32768, 2048, 2048), (32768, 8192, 2048), (32768, 2048, 8192), (8192, 65536, 2048), (32768, 128, 2048),
-            (32768, 768, 768), (8192, 8192, 8192)]
+            (32768, 768, 768), (8192, 8192, 8192),
+            # the weight gradients of a training step: small output, reduction over all tokens (the wgrad_* columns)
+            (2048, 2048, 32768), (2048, 8192, 32768)]
         if args.gemm_shape:
             shapes = [tuple(int(x) for x in args.gemm_shape.split(","))]
         results += bench_gemm(shapes, iters=args.iters)

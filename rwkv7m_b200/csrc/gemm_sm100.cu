@@ -217,15 +217,30 @@ constexpr int kOutStageBytes = 128 * 128;   // 128 rows x 64 bf16
 
 __device__ __forceinline__ void epilogue_named_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// aux_row (two-input epilogues): this thread's 64 bf16 of the second input, or nullptr for a row past the matrix edge
 template <int EPI>
 __device__ __forceinline__ void stage_round(const uint32_t (&v0)[32], const uint32_t (&v1)[32], uint8_t* buf, int tile_row,
-                                            int act) {
+                                            int act, const __nv_bfloat16* aux_row) {
   uint32_t pk[32];
+  uint4 raw[8];
+  if (EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      raw[j] = aux_row != nullptr ? __ldg(reinterpret_cast<const uint4*>(aux_row) + j) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(raw);   // pairs 0-15: first chunk, 16-31: second
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     float x0 = __uint_as_float(v0[2 * j]), x1 = __uint_as_float(v0[2 * j + 1]);
     float y0 = __uint_as_float(v1[2 * j]), y1 = __uint_as_float(v1[2 * j + 1]);
-    if (EPI == kEpiReluSqBf16) {
+    if (EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16) {
+      const float2 a = __bfloat1622float2(h2[j]), b = __bfloat1622float2(h2[16 + j]);
+      if (EPI == kEpiMulSqrt2Bf16) {
+        x0 *= act_grad(a.x, act); x1 *= act_grad(a.y, act); y0 *= act_grad(b.x, act); y1 *= act_grad(b.y, act);
+      } else {
+        x0 += a.x; x1 += a.y; y0 += b.x; y1 += b.y;
+      }
+    } else if (EPI == kEpiReluSqBf16) {
       x0 = fmaxf(x0, 0.f); x0 *= x0; x1 = fmaxf(x1, 0.f); x1 *= x1;
       y0 = fmaxf(y0, 0.f); y0 *= y0; y1 = fmaxf(y1, 0.f); y1 *= y1;
     } else if (act != 0) {
@@ -382,7 +397,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     const bool atomic = splits > 1;
-    constexpr bool kCanStage = (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && BN >= 64;
+    constexpr bool kTwoInput = EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16;
+    constexpr bool kCanStage = (EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16 || kTwoInput) && BN >= 64;
     const bool staged = kCanStage && tma_out != 0;
     const bool issuer = warp == 2 && lane == 0;   // the one thread whose bulk groups track the output stores
     int obuf = 0;
@@ -405,7 +421,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (kCanStage && staged) {
             if (n0 + c * 32 < N) {   // same for all 128 threads
               uint8_t* buf = out_stage + obuf * kOutStageBytes;
-              stage_round<EPI>(v0, v1, buf, q * 32 + lane, act);
+              const __nv_bfloat16* ax = nullptr;   // the host stages two-input epilogues only when N is a multiple of 64
+              if (kTwoInput && row < M) ax = reinterpret_cast<const __nv_bfloat16*>(aux) + (size_t)row * ldaux + n0 + c * 32;
+              stage_round<EPI>(v0, v1, buf, q * 32 + lane, act, ax);
               if (issuer) tma_store_wait_read<0>();
               epilogue_named_barrier();
               if (issuer) { tma_store_2d(&tmD, buf, n0 + c * 32, m0); tma_store_commit(); }
@@ -468,7 +486,7 @@ template <int A_MN, int B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmD, int tma_out,
-                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m,
+                      void* __restrict__ Dptr, int M, int N, int K, int ldd, int raster_m, int splits,
                       const void* __restrict__ aux, int ldaux, int act, int* __restrict__ err) {
   using TL = PairTile;
   constexpr int kStages = TL::kStages;
@@ -495,6 +513,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int tiles_n = (N + BN2 - 1) / BN2;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K (accumulating epilogue only): work item w covers k-blocks [kb0, kb1) of tile w % num_tiles, so the pairs
+  // that run at the same time work on the same k-range of different tiles and share operand panels in L2
+  const int num_work = num_tiles * splits;
+  const int kb_per = (num_kb + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -515,12 +537,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      for (int work = pair_id; work < num_work && ok; work += num_pairs) {
+        const int tile = work % num_tiles, split = work / num_tiles;
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
         const int m0 = tm * 2 * BM + (int)cta * BM;   // this CTA's rows
         const int n0 = tn * BN2 + (int)cta * 128;     // this CTA's columns of B
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = tiles + stage * TL::kStageBytes;
           uint8_t* sb = sa + TL::kABytes;
@@ -552,11 +576,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      for (int work = pair_id; work < num_work && ok; work += num_pairs) {
         if (!wait_bar(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (work / num_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * TL::kStageBytes);
@@ -567,7 +592,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                           : umma_smem_desc_sw128(sa + k * 2048, BK * 128, 1024);
             const uint64_t db = B_MN == 0 ? umma_smem_desc_sw128(sb + k * 32, 16, 1024)
                                           : umma_smem_desc_sw128(sb + k * 2048, BK * 128, 1024);
-            umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -583,13 +608,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
-    constexpr bool kCanStage = EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16;
+    constexpr bool kTwoInput = EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16;
+    constexpr bool kCanStage = EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16 || kTwoInput;
     const bool staged = kCanStage && tma_out != 0;
     const bool issuer = warp == 2 && lane == 0;
     int obuf = 0;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+    const bool atomic = splits > 1;
+    for (int work = pair_id; work < num_work && ok; work += num_pairs) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, raster_m, tm, tn);
+      tile_coords(work % num_tiles, tiles_m, tiles_n, raster_m, tm, tn);
       const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN2;
       if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -604,15 +631,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (kCanStage && staged) {
           if (n0 + c * 32 < N && m0 < M) {   // same for all 128 threads
             uint8_t* buf = out_stage + obuf * kOutStageBytes;
-            stage_round<EPI>(v0, v1, buf, q * 32 + lane, act);
+            const __nv_bfloat16* ax = nullptr;
+            if (kTwoInput && row < M) ax = reinterpret_cast<const __nv_bfloat16*>(aux) + (size_t)row * ldaux + n0 + c * 32;
+            stage_round<EPI>(v0, v1, buf, q * 32 + lane, act, ax);
             if (issuer) tma_store_wait_read<0>();
             epilogue_named_barrier();
             if (issuer) { tma_store_2d(&tmD, buf, n0 + c * 32, m0); tma_store_commit(); }
             obuf ^= 1;
           }
         } else {
-          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, false, aux, ldaux, act);
-          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, false, aux, ldaux, act);
+          store_chunk<EPI>(v0, Dptr, row, n0 + c * 32, M, N, ldd, atomic, aux, ldaux, act);
+          store_chunk<EPI>(v1, Dptr, row, n0 + c * 32 + 32, M, N, ldd, atomic, aux, ldaux, act);
         }
       }
       tc_fence_before();
@@ -740,6 +769,13 @@ bool tma_store_enabled() {
   return on == 1;
 }
 
+// RWKV7M_B200_GEMM_PAIR_SPLITK=0 keeps one CTA pair per output tile of the accumulating epilogue (for comparisons).
+bool pair_splitk_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("RWKV7M_B200_GEMM_PAIR_SPLITK"); on = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  return on == 1;
+}
+
 #define RK_TRACE(...) do { if (trace_on()) { fprintf(stderr, "[gemm] " __VA_ARGS__); fflush(stderr); } } while (0)
 bool trace_on() {
   static int on = -1;
@@ -762,8 +798,10 @@ int launch(const GemmArgs& p, cudaStream_t st) {
   // bf16 store epilogues hand finished boxes to the copy engine when the output rows are 16-byte aligned
   alignas(64) CUtensorMap td = ta;
   int tma_out = 0;
-  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && BN >= 64 && tma_store_enabled() &&
-      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0)
+  constexpr bool kTwoInput = EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16;
+  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16 || kTwoInput) && BN >= 64 && tma_store_enabled() &&
+      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0 &&
+      (!kTwoInput || (p.N % 64 == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0 && p.ldaux % 8 == 0)))
     tma_out = make_map(&td, p.D, p.M, p.N, p.ldd, BM) ? 1 : 0;
   RK_TRACE("maps ok\n");
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
@@ -828,8 +866,10 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   if (!ok) return 2;
   alignas(64) CUtensorMap td = ta;
   int tma_out = 0;
-  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16) && tma_store_enabled() &&
-      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0)
+  constexpr bool kTwoInput = EPI == kEpiMulSqrt2Bf16 || EPI == kEpiAddBf16;
+  if ((EPI == kEpiStoreBf16 || EPI == kEpiReluSqBf16 || kTwoInput) && tma_store_enabled() &&
+      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0 &&
+      (!kTwoInput || (p.N % 64 == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0 && p.ldaux % 8 == 0)))
     tma_out = make_map(&td, p.D, p.M, p.N, p.ldd, BM) ? 1 : 0;
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, EPI>;
   static bool attr_set = false;
@@ -839,9 +879,24 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   }
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
   const int max_pairs = sm_count() / 2;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, td, tma_out, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), p.aux,
-                                                    p.ldaux, p.act, p.error_flag);
+  // split-K for the accumulating epilogue: a weight gradient has few tiles and a long reduction, and 64 or 256 tiles
+  // on 74 pairs leave the last round of tiles mostly idle.  The split count that minimises rounds / splits wins (ties
+  // to the smaller count: every split adds one pass of atomic adds over the output).
+  int splits = 1;
+  if (EPI == kEpiAccumF32 && pair_splitk_enabled()) {
+    const int num_kb = (p.K + BK - 1) / BK;
+    double best = (double)((tiles + max_pairs - 1) / max_pairs);
+    for (int s = 2; s <= 8 && num_kb / s >= 32; ++s) {
+      const double cost = (double)((tiles * s + max_pairs - 1) / max_pairs) / s;
+      if (cost < best * 0.97) { best = cost; splits = s; }
+    }
+    const int per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + per - 1) / per;   // no empty split
+  }
+  const int work = tiles * splits;
+  const int pairs = work < max_pairs ? work : max_pairs;
+  kern<<<2 * pairs, kThreads, TL::kSmemBytes, st>>>(ta, tb, td, tma_out, p.D, p.M, p.N, p.K, p.ldd, raster_rows(p), splits,
+                                                    p.aux, p.ldaux, p.act, p.error_flag);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
