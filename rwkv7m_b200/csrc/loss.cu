@@ -3,6 +3,8 @@
 //   forward : per row  lse = logsumexp(x), max, argmax, nll = lse - x[target]          (fp32 math)
 //   backward: in place dlogits = g_ce * mask * (softmax - onehot(target))
 //                                + g_l2 * 1e-4 * max * onehot(argmax)
+//             with lse / max / argmax as given: the caller may pass the statistics of a wider row of which these V
+//             columns are a slice (vocabulary-parallel head)
 // which is the gradient of  sum(mask * nll)  and  0.5e-4 * sum(max^2)
 // (src/rwkv7m/model/losses.py:21-69 of the reference).  One CTA per row.
 #include "common.cuh"
@@ -77,8 +79,9 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(bf16* __restrict__ logits, 
   bf16* x = logits + (size_t)row * V;
   const float gce = g_ce[0] * (mask != nullptr ? mask[row] : 1.0f);
   const float l = lse[row];
-  int t = targets[row];
-  t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+  // a target or arg-max outside [0, V) matches no column: under a vocabulary split the row's target (or its largest
+  // logit) may live on another rank, and this rank then contributes only the softmax term
+  const int t = targets[row];
   const int am = argmax[row];
   const float gl2 = g_l2[0] * 1e-4f * maxv[row];
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {

@@ -170,7 +170,9 @@ class ScreenedRWKVModel(nn.Module):
             T = h.shape[1]
             step = chunk or T
             totals = None
-            for s0 in range(0, T, step):
+            if ops.use_cuda(h):   # chunked head GEMM + loss kernels on the local vocabulary slice, one gather of row statistics
+                totals = ops._cuda().vocab_parallel_head_loss(h, self.head.weight, targets, mask, chunk, tp)
+            for s0 in range(0, T, step) if totals is None else ():
                 logits = ops.linear(h[:, s0 : s0 + step], self.head.weight)
                 part = vocab_parallel_cross_entropy(
                     logits, targets[:, s0 : s0 + step], None if mask is None else mask[:, s0 : s0 + step], tp)

@@ -767,6 +767,77 @@ class HeadLossFn(torch.autograd.Function):
         return dh.view(ctx.h_shape), dw, None, None, None
 
 
+class VocabParallelHeadLossFn(torch.autograd.Function):
+    """LM head + cross-entropy + L2Wrap over a vocabulary-sharded head without keeping logits.
+
+    Every rank runs the chunked head GEMM on its [V / w, C] slice and the loss kernel on the local logits, which leaves
+    three numbers per row (local log-sum-exp, local maximum, the target's logit if this rank owns the target column).
+    One all-gather of those [3, rows] statistics replaces the per-chunk all-reduces of the logits' maximum, sum of
+    exponentials and target logit; the global log-sum-exp and maximum then drive the same in-place backward kernel on
+    the recomputed local logits (softmax against the global normaliser, the one-hot terms only where the column is
+    local).  The returned dh is this rank's partial sum over its vocabulary slice: the caller's sequence gather sums it
+    in its backward (reference: src/rwkv7m/model/nnx_model.py:1295-1308, src/rwkv7m/model/losses.py:21-69)."""
+
+    @staticmethod
+    def forward(ctx, h, head_w, targets, mask, chunk_rows, group, rank, world):
+        import torch.distributed as dist
+
+        wc = _compute_weight(head_w)
+        C = h.shape[-1]
+        h2 = h.reshape(-1, C)
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        M, Vl = h2.shape[0], wc.shape[0]
+        lo = rank * Vl
+        t_loc = targets.reshape(-1).to(torch.int32) - lo
+        owned = (t_loc >= 0) & (t_loc < Vl)
+        t_read = t_loc.clamp(0, Vl - 1).contiguous()
+        msk = None if mask is None else mask.reshape(-1).float().contiguous()
+        chunk_rows = min(chunk_rows, M)
+        buf = torch.empty(chunk_rows, Vl, dtype=torch.bfloat16, device=h.device)
+        stats = torch.empty(3, M, dtype=torch.float32, device=h.device)   # local lse, local max, owned target logit
+        am = torch.empty(M, dtype=torch.int32, device=h.device)
+        for s in range(0, M, chunk_rows):
+            e = min(M, s + chunk_rows)
+            logits = buf[: e - s]
+            gemm(h2[s:e], wc, logits, GEMM_TN, EPI_BF16)
+            l, m, a, n = _C.ce_fwd(logits, t_read[s:e])
+            _count()
+            stats[0, s:e], stats[1, s:e], am[s:e] = l, m, a
+            stats[2, s:e] = torch.where(owned[s:e], l - n, torch.zeros_like(l))
+        every = torch.empty(world, 3, M, dtype=torch.float32, device=h.device)
+        dist.all_gather_into_tensor(every.view(world * 3, M), stats, group=group)
+        lse = torch.logsumexp(every[:, 0], dim=0)
+        gmax = every[:, 1].max(dim=0).values
+        owner = (every[:, 1] >= gmax.unsqueeze(0)).float().argmax(dim=0)      # lowest rank that holds the maximum
+        nll = lse - every[:, 2].sum(dim=0)
+        ce_total = (nll * msk).sum() if msk is not None else nll.sum()
+        ce_count = msk.sum() if msk is not None else torch.tensor(float(M), device=h.device)
+        l2_total = 0.5e-4 * (gmax * gmax).sum()
+        l2_count = torch.tensor(float(M), device=h.device)
+        ctx.weight, ctx.chunk_rows, ctx.h_shape = head_w, chunk_rows, h.shape
+        t_bwd = torch.where(owned, t_loc, torch.full_like(t_loc, -1)).contiguous()
+        am_bwd = torch.where(owner == rank, am, torch.full_like(am, -1)).contiguous()
+        ctx.save_for_backward(h2, wc, t_bwd, msk, lse.contiguous(), gmax.contiguous(), am_bwd)
+        ctx.mark_non_differentiable(ce_count, l2_count)
+        return ce_total, ce_count, l2_total, l2_count
+
+    @staticmethod
+    def backward(ctx, g_ce, _g1, g_l2, _g2):
+        grads = HeadLossFn.backward(ctx, g_ce, _g1, g_l2, _g2)   # same recompute / in-place gradient / two GEMMs per chunk
+        return grads[0], grads[1], None, None, None, None, None, None
+
+
+def vocab_parallel_head_loss(h, head_w, targets, mask, chunk, tp):
+    """Loss pieces from the gathered hidden states [B, T, C] and this rank's slice of the head; None when the shapes
+    or dtypes need the eager path."""
+    B, T, C = h.shape
+    if not (_bf16(h) and GEMM_BACKEND == "tcgen05" and head_w.shape[0] % 8 == 0 and C % 8 == 0):
+        return None
+    rows = 8192 if chunk is None else max(1, int(chunk)) * B
+    return VocabParallelHeadLossFn.apply(h, head_w, targets, mask, min(rows, 8192), tp.group, tp.rank, tp.world)
+
+
 def head_loss(hidden, ln_w, ln_b, head_w, targets, mask, chunk=None, eps=1e-5):
     B, T, C = hidden.shape
     if _bf16(hidden) and GEMM_BACKEND == "tcgen05" and head_w.shape[0] % 8 == 0 and C % 8 == 0:

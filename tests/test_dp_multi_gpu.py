@@ -66,7 +66,9 @@ def test_tensor_parallel_matches_single_gpu(world):
             assert abs(a - b) < tol * abs(a), res
     for key in ("fused_mc1", "fused_mc0"):   # in-kernel NVLink collectives: multimem.ld_reduce and plain peer loads
         r = res[key]
-        assert r["gather_exact"] and r["rs_max_err"] < 0.05 and r["error_code"] == 0, res
+        # the in-switch sum is accumulated in fp32 but returned in bf16, and adding the residual rounds once more: up to
+        # one bf16 unit in the last place at the largest output magnitude (2^-7 of it), whatever the number of ranks
+        assert r["gather_exact"] and r["rs_max_err"] <= r["rs_scale"] / 128 and r["error_code"] == 0, res
         assert r["gemm_rs_max_err"] < 0.02 * r["gemm_rs_scale"] + 0.05, res
 
 

@@ -120,7 +120,8 @@ def main():
             "gemm_rs_max_err": float((got_g.float() - want_g).abs().max()), "gemm_rs_scale": float(want_g.abs().max()),
             "rel_l2": num / den, "loss_ref": l_ref, "loss_tp": l_tp, "multicast_used": bool(comm.use_multicast),
             "gather_exact": bool(torch.equal(full, ref_full)),
-            "rs_max_err": float((got_rs.float() - want_rs).abs().max()), "error_code": comm.error_code()}
+            "rs_max_err": float((got_rs.float() - want_rs).abs().max()), "rs_scale": float(want_rs.abs().max()),
+            "error_code": comm.error_code()}
     d_ref = traces["ref"][0]
     for graph in (0, 1):
         d_tp = traces["tp_vp0"][graph]
