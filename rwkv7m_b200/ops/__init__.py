@@ -115,8 +115,25 @@ def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_hea
     return reference.tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
 
 
+def _check_wkv_inputs(r, w, k, v, a, b, state0):
+    """Shape and dtype contract of the recurrence (reference: src/rwkv7m/kernels/wkv.py validates the same way)."""
+    if r.dim() != 4:
+        raise ValueError(f"wkv7 vectors must be [B, T, H, N], got {tuple(r.shape)}")
+    for name, t in (("w", w), ("k", k), ("v", v), ("a", a), ("b", b)):
+        if t.shape != r.shape:
+            raise ValueError(f"wkv7: {name} has shape {tuple(t.shape)}, r has {tuple(r.shape)}")
+        if t.dtype != r.dtype:
+            raise TypeError(f"wkv7: {name} is {t.dtype}, r is {r.dtype}")
+    if not r.is_floating_point():
+        raise TypeError(f"wkv7 needs floating-point vectors, got {r.dtype}")
+    B, _, H, N = r.shape
+    if tuple(state0.shape) != (B, H, N, N):
+        raise ValueError(f"wkv7: initial state must be [B, H, N, N] = {(B, H, N, N)}, got {tuple(state0.shape)}")
+
+
 def wkv7(r, w, k, v, a, b, state0):
     """WKV7 recurrence on [B,T,H,N] vectors with an fp32 [B,H,N,N] initial state."""
+    _check_wkv_inputs(r, w, k, v, a, b, state0)
     if use_cuda(r):
         return _cuda().wkv7(r, w, k, v, a, b, state0)
     return reference.wkv7(r, w, k, v, a, b, state0)

@@ -1,0 +1,477 @@
+"""Behavioural contracts of the helper layers, one small CPU test per rule: screening math, the WKV7 call contract,
+tokenizer identity, config / checkpoint round trips, the single-process side of the distributed helpers, planner,
+partition rules, metrics, checkpoint rotation and the upstream-protocol rules.  The scenarios follow the reference's test
+strategy (tests/test_screening_math.py, test_wkv_api.py, test_distributed_skeleton.py, test_scaling.py,
+test_upstream_single_gpu_runner.py, ... of the reference project); the assertions are written against this package."""
+
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import rwkv7m_b200 as R
+from rwkv7m_b200 import ops
+from rwkv7m_b200.ops import reference as F
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# screening math
+# ---------------------------------------------------------------------------------------------------------------------
+def test_unit_norm_rows_have_norm_one_and_zero_rows_stay_finite():
+    x = torch.randn(5, 7)
+    x[2] = 0
+    y = F.unit_norm(x)
+    norms = y.norm(dim=-1)
+    assert torch.allclose(norms[[0, 1, 3, 4]], torch.ones(4), atol=1e-4)
+    assert torch.isfinite(y).all() and float(y[2].abs().max()) == 0.0
+
+
+def test_bounded_tau_range_zero_and_round_trip():
+    theta = torch.linspace(-12, 12, 49)
+    tau = F.bounded_tau(theta)
+    assert float(tau.min()) > -1.0 and float(tau.max()) < 1.0
+    assert float(F.bounded_tau(torch.zeros(()))) == 0.0
+    for t in (-0.5, 0.0, 0.3, 0.9):
+        assert abs(float(F.bounded_tau(F.theta_from_tau(t))) - t) < 1e-5
+
+
+def test_trim_square_threshold_one_and_sign():
+    tau = torch.tensor(0.4)
+    assert float(F.trim_square(torch.tensor(0.4), tau)) == 0.0
+    assert float(F.trim_square(torch.tensor(-0.7), tau)) == 0.0
+    assert abs(float(F.trim_square(torch.tensor(1.0), tau)) - 1.0) < 1e-4
+    assert float(F.trim_square(torch.linspace(-1, 1, 101), tau).min()) >= 0.0
+
+
+def test_tanh_norm_is_bounded_by_the_cap_and_is_the_identity_for_small_vectors():
+    z = torch.randn(16, 8) * 50
+    assert float(F.tanh_norm(z, cap=2.0).norm(dim=-1).max()) <= 2.0 + 1e-4
+    small = torch.randn(4, 8) * 1e-3
+    assert torch.allclose(F.tanh_norm(small, cap=1.0), small, rtol=1e-3, atol=1e-7)
+
+
+def test_leaky_relevance_interpolates_between_the_hard_and_the_soft_rule():
+    sim, tau = torch.linspace(-1, 1, 21), torch.tensor(0.2)
+    hard = F.trim_square(sim, tau)
+    assert torch.allclose(F.relevance_with_warmup(sim, tau, 0.0), hard)
+    soft = F.relevance_with_warmup(sim, tau, 1.0, gamma=8.0)
+    assert torch.allclose(soft, torch.sigmoid(8.0 * (sim - tau)))
+    mid = F.relevance_with_warmup(sim, tau, 0.25, gamma=8.0)
+    assert torch.allclose(mid, 0.75 * hard + 0.25 * soft)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
+def test_split_slot_delta_equals_the_concatenated_projection(dtype, tol):
+    torch.manual_seed(0)
+    B, C, M, ds = 3, 8, 4, 6
+    x, h = torch.randn(B, C), torch.randn(B, C)
+    E = torch.randn(M, ds)
+    kernel = torch.randn(2 * C + ds, ds) * 0.3
+    bias = torch.randn(ds) * 0.1
+    cat = torch.cat([x[:, None].expand(B, M, C), h[:, None].expand(B, M, C), E[None].expand(B, M, ds)], dim=-1)
+    want = torch.tanh(cat @ kernel + bias)
+    got = F.compute_slot_delta(x.to(dtype), h.to(dtype), E.to(dtype), kernel.to(dtype), bias.to(dtype)).float()
+    assert got.shape == (B, M, ds)
+    assert float((got - want).abs().max()) < tol
+
+
+def test_split_slot_delta_gradients_equal_the_concatenated_projection():
+    torch.manual_seed(1)
+    B, C, M, ds = 2, 5, 3, 4
+    base = [torch.randn(B, C), torch.randn(B, C), torch.randn(M, ds), torch.randn(2 * C + ds, ds) * 0.3, torch.randn(ds)]
+    w = torch.randn(B, M, ds)
+
+    def grads(split):
+        x, h, E, k, b = (t.clone().requires_grad_(True) for t in base)
+        if split:
+            out = F.compute_slot_delta(x, h, E, k, b)
+        else:
+            cat = torch.cat([x[:, None].expand(B, M, C), h[:, None].expand(B, M, C), E[None].expand(B, M, ds)], dim=-1)
+            out = torch.tanh(cat @ k + b)
+        (out * w).sum().backward()
+        return [t.grad for t in (x, h, E, k, b)]
+
+    for a, b in zip(grads(True), grads(False)):
+        assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_slot_delta_rejects_mismatched_widths():
+    with pytest.raises(ValueError):
+        F.compute_slot_delta(torch.zeros(1, 4), torch.zeros(1, 5), torch.zeros(2, 3), torch.zeros(11, 3), torch.zeros(3))
+    with pytest.raises(ValueError):
+        F.compute_slot_delta(torch.zeros(1, 4), torch.zeros(1, 4), torch.zeros(2, 3), torch.zeros(10, 3), torch.zeros(3))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# WKV7 call contract
+# ---------------------------------------------------------------------------------------------------------------------
+def _wkv_inputs(B=1, T=6, H=2, N=4, dtype=torch.float32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    r, k, v = (torch.randn(B, T, H, N, generator=g).to(dtype) * 0.5 for _ in range(3))
+    w = (-0.5 - 3.0 * torch.rand(B, T, H, N, generator=g)).to(dtype)   # decay = exp(-exp(w))
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N, generator=g), dim=-1)
+    a = (-kk).to(dtype)
+    b = (kk * torch.rand(B, T, H, N, generator=g)).to(dtype)
+    s0 = torch.randn(B, H, N, N, generator=g) * 0.1
+    return r, w, k, v, a, b, s0
+
+
+def _step_recurrence(r, w, k, v, a, b, s0):
+    """S_t = S_{t-1} (diag(decay_t) + a_t b_t^T) + v_t k_t^T, y_t = S_t r_t, written step by step in the input dtype."""
+    S = s0
+    ys = []
+    for t in range(r.shape[1]):
+        decay = torch.exp(-torch.exp(w[:, t]))                         # [B,H,N] per key channel
+        sa = torch.einsum("bhij,bhj->bhi", S, a[:, t])
+        S = S * decay[:, :, None, :] + sa[..., None] * b[:, t][:, :, None, :] + v[:, t][..., None] * k[:, t][:, :, None, :]
+        ys.append(torch.einsum("bhij,bhj->bhi", S, r[:, t]))
+    return torch.stack(ys, dim=1), S
+
+
+def test_wkv7_equals_the_step_recurrence_and_keeps_the_state_in_fp32():
+    r, w, k, v, a, b, s0 = _wkv_inputs()
+    y, sT = ops.wkv7(r, w, k, v, a, b, s0)
+    want, S = _step_recurrence(r, w, k, v, a, b, s0)
+    assert torch.allclose(y, want, atol=1e-5) and torch.allclose(sT, S, atol=1e-5)
+    yb, sb = ops.wkv7(*(t.bfloat16() for t in (r, w, k, v, a, b)), s0)
+    assert yb.dtype == torch.bfloat16 and sb.dtype == torch.float32
+
+
+def test_wkv7_gradients_agree_with_an_independent_fp64_recurrence():
+    inputs = _wkv_inputs(T=5, N=3, seed=3)
+    wy = torch.randn(1, 5, 2, 3)
+
+    def grads(fn, dtype):
+        args = [t.detach().clone().to(dtype).requires_grad_(True) for t in inputs]
+        y, sT = fn(*args)
+        ((y * wy.to(dtype)).sum() + 0.1 * sT.sum()).backward()
+        return [t.grad.double() for t in args]
+
+    got = grads(ops.wkv7, torch.float32)
+    want = grads(_step_recurrence, torch.float64)
+    for name, g, h in zip("r w k v a b s0".split(), got, want):
+        assert float((g - h).abs().max()) < 1e-4 * max(1.0, float(h.abs().max())), name
+
+
+def test_wkv7_rejects_bad_shapes_and_dtypes():
+    r, w, k, v, a, b, s0 = _wkv_inputs()
+    with pytest.raises((ValueError, RuntimeError)):
+        ops.wkv7(r[:, :-1], w, k, v, a, b, s0)
+    with pytest.raises((ValueError, RuntimeError)):
+        ops.wkv7(r, w, k, v, a, b, s0[:, :, :-1])
+    with pytest.raises((ValueError, RuntimeError, TypeError)):
+        ops.wkv7(r.long(), w, k, v, a, b, s0)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# tokenizer, configs, checkpoints
+# ---------------------------------------------------------------------------------------------------------------------
+def test_default_vocabulary_exists_and_is_identified_by_its_hash():
+    from rwkv7m_b200.tokenizer.rwkv_tokenizer import RWKVTokenizer, default_vocab_path, tokenizer_metadata
+
+    assert default_vocab_path().is_file()
+    meta = tokenizer_metadata()
+    assert meta["tokenizer_format"] == "rwkv_vocab" and len(meta["tokenizer_vocab_sha256"]) == 64
+    assert int(meta["tokenizer_vocab_bytes"]) == default_vocab_path().stat().st_size
+    tok = RWKVTokenizer()
+    ids = tok.encode("hello world", add_eos=True)
+    assert ids[-1] == RWKVTokenizer.EOS and tok.encode("hello world") == ids[:-1]
+    assert tok.decode(ids[:-1]) == "hello world"
+    assert tok.vocab_size <= 65536
+
+
+def test_model_config_round_trips_through_dict_json_and_file(tmp_path):
+    from rwkv7m_b200.config import load_model_config, model_config_from_dict, model_config_to_dict, save_model_config
+
+    cfg = R.model_preset("0.3b")
+    d = model_config_to_dict(cfg)
+    assert model_config_to_dict(model_config_from_dict(json.loads(json.dumps(d)))) == d
+    path = tmp_path / "cfg.json"
+    save_model_config(cfg, path)
+    assert model_config_to_dict(load_model_config(path)) == d
+    assert model_config_to_dict(load_model_config(d)) == d
+    assert model_config_to_dict(load_model_config(cfg)) == d
+
+
+def test_train_checkpoint_round_trip_restores_parameters_moments_and_step(tmp_path):
+    from rwkv7m_b200.io.checkpoint import load_train_checkpoint, load_train_checkpoint_metadata, save_train_checkpoint
+
+    cfg = R.tiny_config()
+    rt, ts = R.create_train_runtime(0, cfg, batch_size=2, total_steps=10)
+    batch = R.generate_toy_batch(1, 2, 8, cfg.vocab_size)
+    for _ in range(2):
+        ts, _ = R.train_batch(ts, batch, rt)
+    save_train_checkpoint(tmp_path / "ck", ts, cfg)
+    saved_cfg, meta = load_train_checkpoint_metadata(tmp_path / "ck")
+    assert saved_cfg.d_model == cfg.d_model and int(meta["step"]) == 2
+    rt2, fresh = R.create_train_runtime(5, cfg, batch_size=2, total_steps=10)
+    restored = load_train_checkpoint(tmp_path / "ck", fresh)
+    restored = restored[0] if isinstance(restored, tuple) else restored
+    for (n, p), (_, q) in zip(ts.model.named_parameters(), restored.model.named_parameters()):
+        assert torch.equal(p, q), n
+    a, _ = R.train_batch(ts, batch, rt)
+    b, _ = R.train_batch(restored, batch, rt2)
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-7), n   # the moments and the update count came back too
+
+
+def test_torch_artifact_names_use_dots():
+    from rwkv7m_b200.io.torch_backend import torch_parameter_name
+
+    assert torch_parameter_name("layers/0/att/key/kernel") == "layers.0.att.key.kernel"
+    assert torch_parameter_name("emb") == "emb"
+
+
+def test_recurrent_and_screen_state_round_trip_through_flat_dicts():
+    from rwkv7m_b200.state import (init_rwkv_state, init_screen_state, rwkv_state_from_dict, rwkv_state_to_dict,
+                                   screen_state_from_dict, screen_state_to_dict)
+
+    cfg = R.tiny_config()
+    fields = ("time_mix_x", "channel_mix_x", "wkv")
+    rs = tuple(type(s)(*(torch.randn_like(getattr(s, f)) for f in fields)) for s in init_rwkv_state(2, cfg))
+    back = rwkv_state_from_dict(rwkv_state_to_dict(rs), cfg.n_layers)
+    for a, b in zip(rs, back):
+        assert all(torch.equal(getattr(a, f), getattr(b, f)) for f in fields)
+    ss = init_screen_state(2, cfg.screening)
+    d = screen_state_to_dict(ss)
+    back = screen_state_from_dict(d, len(cfg.screening.screened_layers))
+    assert screen_state_to_dict(back).keys() == d.keys()
+    assert all(v.dtype == torch.float32 for v in d.values())
+
+
+def test_bf16_compute_keeps_states_and_loss_pieces_in_fp32():
+    cfg = R.tiny_config()
+    cfg.dtype = "bfloat16"
+    rt, ts = R.create_train_runtime(0, cfg, batch_size=2, total_steps=10)
+    batch = R.generate_toy_batch(2, 2, 8, cfg.vocab_size)
+    ts, m = R.train_batch(ts, batch, rt)
+    assert m["loss"].dtype == torch.float32 and math.isfinite(float(m["loss"]))
+    logits, _ = R.infer_prefill(rt, batch["input_ids"])
+    for layer_state in rt.rwkv_state:
+        assert layer_state.wkv.dtype == torch.float32 and layer_state.time_mix_x.dtype == torch.float32
+    assert all(s.slots.dtype == torch.float32 for s in rt.screen_state.layers)
+    assert logits.shape[-1] == cfg.vocab_size
+
+
+def test_generate_text_runs_from_a_tokenizer_prompt():
+    cfg = R.tiny_config(vocab_size=65536)
+    rt = R.create_runtime(0, cfg, batch_size=1)
+    text = R.generate_text(rt, "hi", max_new_tokens=3, temperature=0.0)
+    assert isinstance(text, str)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# single-process side of the distributed helpers
+# ---------------------------------------------------------------------------------------------------------------------
+def test_process_info_describes_a_single_local_process():
+    from rwkv7m_b200.parallel.mesh import process_info
+
+    info = process_info()
+    assert info["process_index"] == 0 and info["process_count"] == 1 and info["local_rank"] == 0
+
+
+def test_make_mesh_checks_axis_names_and_sizes():
+    from rwkv7m_b200.parallel.mesh import make_mesh
+
+    mesh = make_mesh(("data", "model"), (2, 4), world_size=8)
+    assert mesh.size == 8 and mesh.coords(5) == (1, 1)
+    assert mesh.model_group_ranks(5) == [4, 5, 6, 7] and mesh.data_group_ranks(5) == [1, 5]
+    with pytest.raises(ValueError):
+        make_mesh(("data", "model"), (3, 4), world_size=8)
+    with pytest.raises(ValueError):
+        make_mesh(("rows", "cols"), (2, 4), world_size=8)
+    with pytest.raises(ValueError):
+        mesh.coords(8)
+
+
+def test_batch_layout_divisibility_rules():
+    from rwkv7m_b200.parallel.input_pipeline import compute_batch_layout
+
+    lay = compute_batch_layout(16, process_count=2, local_device_count=4)
+    assert (lay.process_batch_size, lay.per_device_batch_size) == (8, 2)
+    for bad in (dict(global_batch_size=15, process_count=2), dict(global_batch_size=16, process_count=0),
+                dict(global_batch_size=0, process_count=1), dict(global_batch_size=6, process_count=2, local_device_count=2)):
+        with pytest.raises(ValueError):
+            compute_batch_layout(bad.pop("global_batch_size"), **bad)
+
+
+def _write_corpus(tmp_path, n_docs=40, doc_len=23, vocab=200):
+    from rwkv7m_b200.data.binidx import MMapIndexedDatasetBuilder
+
+    prefix = tmp_path / "corpus"
+    builder = MMapIndexedDatasetBuilder(str(prefix) + ".bin", dtype=np.uint16)
+    rng = np.random.default_rng(0)
+    for _ in range(n_docs):
+        builder.add_item(rng.integers(1, vocab, size=doc_len).astype(np.uint16))
+        builder.end_document()
+    builder.finalize(str(prefix) + ".idx")
+    return prefix
+
+
+def test_host_dataset_slices_the_global_batch_by_process_rank(tmp_path):
+    from rwkv7m_b200.data.dataset import create_binidx_dataset
+    from rwkv7m_b200.parallel.input_pipeline import create_host_binidx_dataset
+
+    prefix = _write_corpus(tmp_path)
+    whole = create_binidx_dataset(prefix, ctx_len=8, batch_size=4)
+    full = {tuple(row) for row in np.asarray(whole.get_batch(3)["input_ids"]).tolist()}
+    seen = set()
+    for rank in (0, 1):
+        host = create_host_binidx_dataset(prefix, ctx_len=8, global_batch_size=4, process_index=rank, process_count=2)
+        assert host.layout.process_batch_size == 2
+        got = np.asarray(host.dataset.get_batch(3)["input_ids"])
+        assert got.shape == (2, 8)
+        rows = {tuple(row) for row in got.tolist()}
+        assert not (rows & seen)     # the ranks' samples are disjoint ...
+        seen |= rows
+    assert seen == full              # ... and together they are the global batch of the step
+    with pytest.raises(ValueError):
+        create_host_binidx_dataset(prefix, ctx_len=8, global_batch_size=4, process_index=2, process_count=2)
+
+
+def test_prefetched_batches_arrive_in_step_order(tmp_path):
+    from rwkv7m_b200.parallel.input_pipeline import create_host_binidx_dataset, iter_prefetched_global_batches
+
+    prefix = _write_corpus(tmp_path)
+    host = create_host_binidx_dataset(prefix, ctx_len=8, global_batch_size=2, process_index=0, process_count=1)
+    seen = list(iter_prefetched_global_batches(host, None, start_step=2, steps=3, prefetch_size=2))
+    assert len(seen) == 3
+    for offset, item in enumerate(seen):
+        batch = item[1] if isinstance(item, tuple) else item
+        want = host.dataset.get_batch(2 + offset)
+        assert np.array_equal(np.asarray(batch["input_ids"].cpu()), np.asarray(want["input_ids"]))
+        assert batch["target_ids"].shape == (2, 8)
+
+
+def test_single_item_view_reuses_the_token_file(tmp_path):
+    from rwkv7m_b200.cli.prepare_upstream_binidx import prepare_single_item_view
+    from rwkv7m_b200.data.binidx import MMapIndexedDataset, data_file_path
+
+    prefix = _write_corpus(tmp_path, n_docs=5, doc_len=11)
+    out = tmp_path / "flat"
+    total = prepare_single_item_view(prefix, out)
+    assert total == 55
+    view = MMapIndexedDataset(str(out))
+    assert len(view) == 1 and len(view[0]) == 55
+    src = MMapIndexedDataset(str(prefix))
+    assert np.array_equal(np.asarray(view[0][:11]), np.asarray(src[0]))
+    from pathlib import Path
+
+    assert Path(data_file_path(out)).exists()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# planner, environment, partition rules
+# ---------------------------------------------------------------------------------------------------------------------
+def test_planner_counts_the_7b_preset_and_orders_the_dtype_policies():
+    from rwkv7m_b200.parallel.scaling import DTypePolicy, abstract_parameter_summary, estimate_training_memory
+
+    cfg = R.model_preset("7b")
+    summary = abstract_parameter_summary(cfg)
+    assert summary.total == 6_994_788_376
+    light = estimate_training_memory(cfg, DTypePolicy(param_storage_dtype="bfloat16"), model_axis_size=8)
+    safe = estimate_training_memory(cfg, DTypePolicy.stability(), model_axis_size=8)
+    assert light.parameter_storage_bytes < safe.parameter_storage_bytes
+    wide = estimate_training_memory(cfg, DTypePolicy(param_storage_dtype="bfloat16"), model_axis_size=1)
+    assert wide.per_device_estimated_bytes > light.per_device_estimated_bytes
+    assert light.global_estimated_bytes >= light.per_device_estimated_bytes
+
+
+def test_environment_manifest_names_the_runtime():
+    from rwkv7m_b200.parallel.environment import environment_manifest
+
+    env = environment_manifest()
+    text = json.dumps(env)
+    assert "torch" in text and "python" in text.lower()
+
+
+def test_partition_rules_for_known_weights_and_indivisible_fallback():
+    from rwkv7m_b200.parallel.tp import parameter_partition_summary, shard_dim
+
+    assert shard_dim("layers.0.block.att.receptance.weight") == 0       # column-parallel: output rows
+    assert shard_dim("layers.0.block.att.output.weight") == 1           # row-parallel: input columns
+    assert shard_dim("layers.3.block.ffn.key.weight") == 0 and shard_dim("layers.3.block.ffn.value.weight") == 1
+    assert shard_dim("layers.0.block.ln1.weight") is None
+    assert shard_dim("head.weight") is None and shard_dim("head.weight", vocab_parallel=True) == 0
+    model = R.RWKV7M(R.tiny_config()) if hasattr(R, "RWKV7M") else R.create_train_runtime(0, R.tiny_config(), batch_size=1)[1].model
+    summary = parameter_partition_summary(model, 2)
+    assert summary["world"] == 2 and summary["sharded_elements_per_rank"] > 0 and summary["replicated_elements"] > 0
+    by_name = {row["name"]: row["shard_dim"] for row in summary["parameters"]}
+    assert by_name["layers.0.block.att.key.weight"] == 0 and by_name["layers.0.block.att.output.weight"] == 1
+    total = sum(p.numel() for p in model.parameters())
+    assert summary["sharded_elements_per_rank"] + summary["replicated_elements"] == total
+
+
+def test_collective_text_audit_counts_operation_names():
+    from rwkv7m_b200.parallel.collectives import audit_collectives, ownership_table
+
+    text = "x = all-reduce(a)\ny = all-gather(b)\nz = all-reduce(c)\nw = reduce-scatter(d)\nq = all-to-all(e)"
+    counts = audit_collectives(text)
+    flat = json.dumps(counts)
+    assert counts.get("all-reduce", counts.get("all_reduce")) == 2, flat
+    assert counts.get("all-gather", counts.get("all_gather")) == 1
+    rows = ownership_table()
+    assert len(rows) >= 3 and all(isinstance(r, dict) for r in rows)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# metrics and checkpoint rotation
+# ---------------------------------------------------------------------------------------------------------------------
+def test_metric_records_go_to_jsonl_and_csv(tmp_path):
+    from rwkv7m_b200.parallel.metrics import mean_metric_dict, metrics_to_host_dict, write_metric_record
+
+    host = metrics_to_host_dict({"loss": torch.tensor(2.5), "step": 3})
+    assert host["loss"] == 2.5 and host["step"] == 3
+    mean = mean_metric_dict([{"loss": 1.0, "acc": 0.5}, {"loss": 3.0, "acc": 1.0}])
+    assert mean["loss"] == 2.0 and mean["acc"] == 0.75
+    j, c = tmp_path / "m.jsonl", tmp_path / "m.csv"
+    for step in (1, 2):
+        write_metric_record(j, c, {"step": step, "loss": 1.0 / step})
+    lines = j.read_text().strip().splitlines()
+    assert [json.loads(l)["step"] for l in lines] == [1, 2]
+    rows = c.read_text().strip().splitlines()
+    assert rows[0].split(",")[0:2] == ["step", "loss"] or "step" in rows[0]
+    assert len(rows) == 3
+
+
+def test_checkpoint_directories_are_named_listed_and_rotated(tmp_path):
+    from rwkv7m_b200.parallel.checkpoint import checkpoint_path, list_checkpoint_dirs, normalize_backend, rotate_checkpoints
+
+    assert checkpoint_path(tmp_path, 12).name == "ckpt-00000012"
+    assert normalize_backend("flax") == normalize_backend("single") and normalize_backend("orbax") == normalize_backend("sharded")
+    with pytest.raises(ValueError):
+        normalize_backend("tape")
+    for step in (1, 2, 3, 4):
+        d = checkpoint_path(tmp_path, step)
+        d.mkdir()
+        (d / "checkpoint.json").write_text("{}")
+    assert [p.name for p in list_checkpoint_dirs(tmp_path)] == [f"ckpt-0000000{i}" for i in (1, 2, 3, 4)]
+    info = {"process_index": 0, "process_count": 1}
+    removed = rotate_checkpoints(tmp_path, 2, info, protected_paths=[checkpoint_path(tmp_path, 1)])
+    left = [p.name for p in list_checkpoint_dirs(tmp_path)]
+    assert left == ["ckpt-00000001", "ckpt-00000003", "ckpt-00000004"]
+    assert [p.name if hasattr(p, "name") else str(p).rsplit("/", 1)[-1] for p in removed] == ["ckpt-00000002"]
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# upstream-protocol rules (rule level; the CLI run is in test_cli.py)
+# ---------------------------------------------------------------------------------------------------------------------
+def test_upstream_learning_rate_warms_up_and_decays_to_the_final_value():
+    from rwkv7m_b200.cli.train_upstream_single_gpu import upstream_learning_rate
+
+    kw = dict(lr_init=6e-4, lr_final=6e-5, warmup_steps=10, total_steps=110)
+    lrs = [upstream_learning_rate(s, **kw) for s in range(0, 111)]
+    assert lrs[0] < lrs[5] < lrs[10] and abs(lrs[10] - 6e-4) < 6e-4 * 0.05
+    assert all(a >= b - 1e-12 for a, b in zip(lrs[10:], lrs[11:]))
+    assert abs(lrs[-1] - 6e-5) < 6e-5 * 0.05
+
+
+def test_upstream_optimizer_groups_and_the_sample_boundary():
+    from rwkv7m_b200.cli.train_upstream_single_gpu import epoch_and_index, optimizer_group
+
+    assert optimizer_group("blocks.0.att.w0", 1, 0.1) != optimizer_group("blocks.0.att.a0", 1, 0.1)   # 2x rate for the decay vector
+    assert optimizer_group("blocks.0.att.key.weight", 2, 0.1) != optimizer_group("blocks.0.ln1.weight", 1, 0.1)
+    assert optimizer_group("blocks.0.att.key.weight", 2, 0.0) == optimizer_group("blocks.0.ln1.weight", 1, 0.0)
+    assert epoch_and_index(40319) == (0, 40319) and epoch_and_index(40320) == (1, 0)
