@@ -304,7 +304,11 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
 bool layernorm_bwd_res(const void* dy, const void* x, const float* w, const float* mean, const float* rstd,
                        const void* dres, void* dx, float* dw_part, float* db_part, int parts, int M, int C,
                        cudaStream_t st) {
-  switch (C) {   // single-pass kernel for the common widths
+  // the single-pass kernel reads dy, x, dres and the weight and writes dx with 16-byte accesses
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
+                         reinterpret_cast<uintptr_t>(dres) | reinterpret_cast<uintptr_t>(w) |
+                         reinterpret_cast<uintptr_t>(dw_part) | reinterpret_cast<uintptr_t>(db_part)) & 15) == 0;
+  switch (aligned ? C : 0) {   // single-pass kernel for the common widths
     case 256: launch_ln_bwd_fused<1>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
     case 512: launch_ln_bwd_fused<2>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;
     case 768: launch_ln_bwd_fused<3>(dy, x, w, mean, rstd, dx, dw_part, db_part, parts, M, st, dres); return true;

@@ -62,6 +62,33 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
         assert torch.allclose(db, db_ref, rtol=1e-4, atol=tol)
 
 
+def test_weight_on_a_four_byte_boundary_takes_the_generic_kernels():
+    """The contract asks 16 bytes of dy, x and dx only: a weight vector that starts 4 bytes into an allocation must
+    give the same result (the one-pass kernel, which reads the weight 16 bytes at a time, is not chosen for it)."""
+    from rwkv7m_b200.ops.build import load_extension
+
+    ext = load_extension()
+    lib, fn = _lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    M, C = 512, 768
+    x, dy, w, b = _case(M, C, seed=7)
+    _, mean, rstd = ext.layernorm_fwd(x, w, b, 1e-5)
+    dx_ref, dw_ref, db_ref = ext.layernorm_bwd(dy, x, w, mean, rstd, None)
+    shifted = torch.empty(C + 4, device="cuda")
+    w_off = shifted[1:C + 1]
+    w_off.copy_(w)
+    assert w_off.data_ptr() % 16 == 4
+    dx = torch.full_like(x, float("nan"))
+    dw = torch.full((C,), float("nan"), device="cuda")
+    db = torch.full((C,), float("nan"), device="cuda")
+    rc = fn(dy.data_ptr(), x.data_ptr(), w_off.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+            dw.data_ptr(), db.data_ptr(), M, C, stream)
+    assert rc == 0, lib.rwkv7m_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    assert float((dx.float() - dx_ref.float()).abs().max()) <= 2 ** -7 * float(dx_ref.float().abs().max())
+    assert torch.allclose(dw, dw_ref, rtol=1e-4, atol=1e-3) and torch.allclose(db, db_ref, rtol=1e-4, atol=1e-3)
+
+
 def test_rejects_sizes_beyond_the_static_scratch():
     lib, fn = _lib()
     x, dy, w, b = _case(8, 64, seed=3)
