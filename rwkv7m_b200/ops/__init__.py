@@ -115,6 +115,15 @@ def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_hea
     return reference.tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
 
 
+def flush_deferred():
+    """Issue any weight-gradient GEMM that the CUDA path held back during backward (no-op otherwise)."""
+    import sys
+
+    mod = sys.modules.get(__name__ + ".cuda")
+    if mod is not None:
+        mod.flush_deferred()
+
+
 def _check_wkv_inputs(r, w, k, v, a, b, state0):
     """Shape and dtype contract of the recurrence (reference: src/rwkv7m/kernels/wkv.py validates the same way)."""
     if r.dim() != 4:

@@ -71,6 +71,28 @@ def wkv_chunk_error_code(reset: bool = True) -> int:
     return int(_C.wkv7_chunk_error(reset))
 
 
+# RWKV7M_B200_WGRAD_OVERLAP=1: the chunked WKV7 backward runs one CTA per SM, so the 256 sequences of the 1.5B shape take
+# two rounds on 148 SMs and 40 SMs idle through the second one.  The weight gradient of the time-mix output projection,
+# which autograd reaches just before, does not depend on it: it is held back and issued on the main stream while the
+# recurrence runs on a high-priority side stream, so its CTAs take the SMs the recurrence leaves free.
+WGRAD_OVERLAP = os.environ.get("RWKV7M_B200_WGRAD_OVERLAP", "0") == "1"
+_DEFERRED_WGRADS = []
+_HIGH_STREAMS = {}
+
+
+def _high_priority_stream(device):
+    st = _HIGH_STREAMS.get(device)
+    if st is None:
+        st = _HIGH_STREAMS[device] = torch.cuda.Stream(device=device, priority=-1)
+    return st
+
+
+def flush_deferred():
+    """Run weight-gradient GEMMs that were held back for a kernel to hide behind and found none."""
+    while _DEFERRED_WGRADS:
+        _DEFERRED_WGRADS.pop(0)()
+
+
 class Wkv7Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r, w, k, v, a, b, s0):
@@ -92,6 +114,16 @@ class Wkv7Fn(torch.autograd.Function):
     def backward(ctx, dy, dsT):
         r, w, k, v, a, b, s0, sa, ckpt = ctx.saved_tensors
         dy = dy.contiguous()
+        if _DEFERRED_WGRADS and ctx.chunked:
+            main = torch.cuda.current_stream()
+            high = _high_priority_stream(dy.device)
+            high.wait_stream(main)
+            with torch.cuda.stream(high):
+                grads = _C.wkv7_bwd(r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, ctx.interval, ctx.chunked)
+            flush_deferred()            # on the main stream, next to the recurrence
+            main.wait_stream(high)      # everything after this node sees the recurrence's gradients
+            _count()
+            return tuple(grads)
         dr, dw, dk, dv, da, db, ds0 = _C.wkv7_bwd(
             r, w, k, v, a, b, s0, sa, ckpt, dy, dsT, ctx.interval, ctx.chunked
         )
@@ -291,7 +323,14 @@ class LinearAddFn(torch.autograd.Function):
             dx = torch.empty(x2.shape[0], K, dtype=torch.bfloat16, device=dout.device)
             gemm(d2, wc, dx, GEMM_NN, EPI_BF16)
             dx = dx.view(ctx.x_shape)
-        dw = _wgrad(d2, x2, ctx.weight) if ctx.needs_input_grad[2] else None
+        dw = None
+        if ctx.needs_input_grad[2]:
+            w = ctx.weight
+            main_grad = getattr(w, "_main_grad", None)
+            if WGRAD_OVERLAP and main_grad is not None and main_grad.dtype == torch.float32:
+                _DEFERRED_WGRADS.append(lambda: _wgrad(d2, x2, w))   # accumulates into the bound fp32 gradient
+            else:
+                dw = _wgrad(d2, x2, w)
         return (dout if ctx.needs_input_grad[0] else None), dx, dw
 
 

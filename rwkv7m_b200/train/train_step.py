@@ -13,6 +13,7 @@ from dataclasses import dataclass, field
 
 import torch
 
+from .. import ops
 from ..config import ModelConfig, normalize_phase
 from ..models.model import ScreenedRWKVModel, initialize_model
 from ..state import LayerRWKVState, LayerScreenState, ModelScreenState
@@ -175,6 +176,7 @@ def accumulate_gradients(model, batch, rwkv_state, screen_state, *, phase, gradi
             )
         with nvtx_range("backward"):
             loss.backward()
+            ops.flush_deferred()
         check_finite("loss", loss)
         local = parts["ce"] * ce_w + parts["l2"] * pos_w
         weighted = {k: v * (ce_w if k == "loss" else pos_w) for k, v in metrics.items()}
