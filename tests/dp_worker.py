@@ -1,6 +1,7 @@
 """Worker for the multi-GPU data-parallel tests (launched with torch.distributed.run)."""
 
 import json
+import time
 import os
 import sys
 from pathlib import Path
@@ -39,6 +40,9 @@ def main():
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
         for step in range(4):
+            # a different host-side delay on every rank and step: the device barriers and flags of the exchange must
+            # absorb ranks that arrive tens of milliseconds apart
+            time.sleep(float(torch.rand(1, generator=g)) * 0.04)
             ids = torch.randint(0, 512, (2, 33), generator=g).to(torch.int32)
             batch = {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(),
                      "mask": torch.ones(2, 32)}
