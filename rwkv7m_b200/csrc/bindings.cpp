@@ -206,6 +206,33 @@ void gemm(const Tensor& A, const Tensor& B, Tensor D, int64_t layout, int64_t ep
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
 }
 
+// Head GEMM whose epilogue keeps only cross-entropy statistics: logits = A [M,K] B [V,K]^T are never written.  Returns
+// lse, max, argmax, nll per row (the same four tensors as ce_fwd on stored bf16 logits).
+std::vector<Tensor> gemm_ce_stats(const Tensor& A, const Tensor& B, const Tensor& targets, int64_t pair) {
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 &&
+                  A.dim() == 2 && B.dim() == 2 && A.stride(1) == 1 && B.stride(1) == 1 && A.size(1) == B.size(1),
+              "gemm_ce_stats: bf16 row-major A [M,K] and B [V,K]");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kInt && targets.is_contiguous() && targets.numel() == A.size(0),
+              "gemm_ce_stats: int32 targets, one per row");
+  const int64_t M = A.size(0), V = B.size(0), tiles = (V + 255) / 256;
+  auto f32 = A.options().dtype(at::kFloat);
+  Tensor stats = torch::empty({M, tiles, 4}, f32);
+  rk::GemmArgs p{};
+  p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = stats.data_ptr(); p.aux = targets.data_ptr();
+  p.lda = (int)A.stride(0); p.ldb = (int)B.stride(0); p.ldd = (int)(tiles * 4);
+  p.M = (int)M; p.N = (int)V; p.K = (int)A.size(1);
+  p.layout = rk::kGemmTN; p.epilogue = rk::kEpiCeStats; p.pair = (int)pair;
+  p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();
+  const int rc = rk::gemm_bf16(p, stream());
+  TORCH_CHECK(rc == 0, "gemm_ce_stats launch failed with code ", rc);
+  Tensor lse = torch::empty({M}, f32), maxv = torch::empty({M}, f32), nll = torch::empty({M}, f32);
+  Tensor argmax = torch::empty({M}, A.options().dtype(at::kInt));
+  rk::ce_combine(stats.data_ptr<float>(), (int)tiles, lse.data_ptr<float>(), maxv.data_ptr<float>(), argmax.data_ptr<int>(),
+                 nll.data_ptr<float>(), (int)M, stream());
+  return {lse, maxv, argmax, nll};
+}
+
 int64_t gemm_error(const Tensor& like) {
   return gemm_error_flag(like.device()).item<int>();
 }
@@ -851,6 +878,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_fwd", &ce_fwd);
+  m.def("gemm_ce_stats", &gemm_ce_stats);
   m.def("ce_bwd", &ce_bwd);
   m.def("dp_step", &dp_step);
   m.def("dp_step_timings", &dp_step_timings);

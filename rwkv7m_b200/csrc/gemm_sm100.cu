@@ -208,6 +208,28 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], void* __res
         }
 }
 
+// Cross-entropy statistics of one output row over the columns of a tile (kEpiCeStats): the logits are rounded to bf16
+// first, so the numbers equal those of a pass over a stored bf16 logits matrix, which the backward recomputes.
+struct CeRow { float m, s, tl; int am; };
+
+__device__ __forceinline__ void ce_row_update(CeRow& st, const uint32_t (&v)[32], int col0, int N, int tgt) {
+  if (col0 >= N) return;
+  float x[32];
+  float cm = -INFINITY;
+  int ci = col0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float f = __bfloat162float(__float2bfloat16(__uint_as_float(v[j])));
+    if (col0 + j >= N) f = -INFINITY;
+    x[j] = f;
+    if (f > cm) { cm = f; ci = col0 + j; }      // strict: the lowest column among equal values
+    if (col0 + j == tgt) st.tl = f;
+  }
+  if (cm > st.m) { st.s *= __expf(st.m - cm); st.m = cm; st.am = ci; }   // first chunk: s = 0 and exp(-inf) = 0
+#pragma unroll
+  for (int j = 0; j < 32; ++j) st.s += __expf(x[j] - st.m);
+}
+
 // bf16 output through shared memory: the four epilogue warps write their 128 rows x 64 columns (two accumulator chunks
 // per thread = 128 bytes = one row of the box) into a 16 KB staging buffer in the 128-byte-swizzled layout, and one
 // thread hands the box to the copy engine (cp.async.bulk.tensor store), which writes full lines and clips at the matrix
@@ -410,7 +432,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      if constexpr (BN >= 64) {
+      if constexpr (EPI == kEpiCeStats) {
+        CeRow st{-INFINITY, 0.f, -INFINITY, 0};
+        const int tgt = row < M ? reinterpret_cast<const int*>(aux)[row] : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c += 2) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(t0 + c * 32, v0);
+          tmem_ld_32x32(t0 + c * 32 + 32, v1);
+          tmem_ld_wait();
+          ce_row_update(st, v0, n0 + c * 32, N, tgt);
+          ce_row_update(st, v1, n0 + c * 32 + 32, N, tgt);
+        }
+        if (row < M)
+          reinterpret_cast<float4*>(Dptr)[(size_t)row * (ldd / 4) + tn] = make_float4(st.m, st.s, __int_as_float(st.am), st.tl);
+      } else if constexpr (BN >= 64) {
         // two 32-column chunks per round: the second load is in flight while the first chunk is converted and stored
 #pragma unroll 1
         for (int c = 0; c < BN / 32; c += 2) {
@@ -622,6 +658,21 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * BN2;
+      if constexpr (EPI == kEpiCeStats) {
+        CeRow st{-INFINITY, 0.f, -INFINITY, 0};
+        const int tgt = row < M ? reinterpret_cast<const int*>(aux)[row] : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN2 / 32; c += 2) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(t0 + c * 32, v0);
+          tmem_ld_32x32(t0 + c * 32 + 32, v1);
+          tmem_ld_wait();
+          ce_row_update(st, v0, n0 + c * 32, N, tgt);
+          ce_row_update(st, v1, n0 + c * 32 + 32, N, tgt);
+        }
+        if (row < M)
+          reinterpret_cast<float4*>(Dptr)[(size_t)row * (ldd / 4) + tn] = make_float4(st.m, st.s, __int_as_float(st.am), st.tl);
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN2 / 32; c += 2) {   // two chunks per round: the second load overlaps the first chunk's stores
         uint32_t v0[32], v1[32];
@@ -1123,6 +1174,13 @@ int gemm_bf16(const GemmArgs& p, cudaStream_t st) {
     if (p.error_flag == nullptr) return 7;
     if (p.pair != 0 && p.M >= 256 && p.N >= 256) return launch_pair<0, 0, kEpiScatterAddBf16>(p, st);
     return launch<256, 0, 0, kEpiScatterAddBf16>(p, st);
+  }
+  if (p.epilogue == kEpiCeStats) {
+    // D is float [M, ceil(N / 256), 4] (row pitch ldd floats), aux the int32 targets: both tile shapes are 256 wide
+    if (p.layout != kGemmTN || p.aux == nullptr || (p.ldd & 3) || p.ldd < 4 * ((p.N + 255) / 256)) return 6;
+    if (p.error_flag == nullptr) return 7;
+    if (p.pair != 0 && p.M >= 256 && p.N >= 256 && p.K >= 512) return launch_pair<0, 0, kEpiCeStats>(p, st);
+    return launch<256, 0, 0, kEpiCeStats>(p, st);
   }
   const bool two_input = p.epilogue == kEpiMulSqrt2Bf16 || p.epilogue == kEpiAddBf16;
   if (two_input && (p.aux == nullptr || (reinterpret_cast<uintptr_t>(p.aux) & 15) || (p.ldaux & 7))) return 6;

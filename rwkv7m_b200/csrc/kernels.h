@@ -103,6 +103,8 @@ void embedding_bwd(const int* ids, const void* dout, float* grad, int M, int C, 
 // ---- loss ---------------------------------------------------------------------------
 void ce_fwd(const void* logits, const int* targets, float* lse, float* maxv, int* argmax, float* nll, int rows, int V,
             cudaStream_t st);
+// rows of per-tile statistics written by the kEpiCeStats GEMM epilogue -> lse, max, argmax, nll = lse - target logit
+void ce_combine(const float* stats, int tiles, float* lse, float* maxv, int* argmax, float* nll, int rows, cudaStream_t st);
 void ce_bwd(void* logits, const int* targets, const float* mask, const float* lse, const float* maxv,
             const int* argmax, const float* g_ce, const float* g_l2, int rows, int V, cudaStream_t st);
 
@@ -212,7 +214,10 @@ enum GemmLayout { kGemmTN = 0, kGemmNN = 1, kGemmNT_wgrad = 2 };
 enum GemmEpilogue {
   kEpiStoreBf16 = 0, kEpiReluSqBf16 = 1, kEpiStoreF32 = 2, kEpiAccumF32 = 3, kEpiScatterAddBf16 = 4,
   kEpiMulSqrt2Bf16 = 5,   // D = bf16(acc * 2 sqrt(aux)): backward of h = relu(.)^2 fused into the GEMM that produces dh
-  kEpiAddBf16 = 6         // D = bf16(acc + aux): residual add fused into the projection
+  kEpiAddBf16 = 6,        // D = bf16(acc + aux): residual add fused into the projection
+  kEpiCeStats = 7         // no matrix output: per (row, 256-column tile) the cross-entropy statistics of the bf16-rounded
+                          // result (maximum, sum of exp(x - maximum), arg-max column, logit of the row's target if it
+                          // lies in the tile) as float4 into D [M, ceil(N / 256), 4]; aux = int32 targets [M].  Layout TN.
 };
 // Target of the kEpiScatterAddBf16 epilogue (GEMM -> reduce-scatter over time in one kernel): rows are [B, T] tokens,
 // rank r owns tokens [r*Tl, (r+1)*Tl) of every batch row and receives them in out[r] laid out [B, Tl, N].

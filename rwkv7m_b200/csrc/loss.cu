@@ -111,6 +111,43 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(bf16* __restrict__ logits, 
   }
 }
 
+// One warp per row folds the per-tile statistics of the head GEMM's epilogue: running maximum with rescaled sums, the
+// lowest arg-max column among equal maxima, and the target logit (finite in exactly one tile).
+__global__ void __launch_bounds__(256) ce_combine_kernel(const float4* __restrict__ stats, int tiles, float* __restrict__ lse,
+                                                         float* __restrict__ maxv, int* __restrict__ argmax,
+                                                         float* __restrict__ nll, int rows) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float m = -INFINITY, s = 0.f, tl = -INFINITY;
+  int am = 0x7fffffff;
+  for (int t = lane; t < tiles; t += 32) {
+    const float4 v = stats[(size_t)row * tiles + t];
+    const int vi = __float_as_int(v.z);
+    if (v.x > m) { s = s * __expf(m - v.x) + v.y; m = v.x; am = vi; }
+    else { s += v.y * __expf(v.x - m); if (v.x == m && vi < am) am = vi; }
+    tl = fmaxf(tl, v.w);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float t2 = __shfl_xor_sync(0xffffffffu, tl, o);
+    const int a2 = __shfl_xor_sync(0xffffffffu, am, o);
+    const float mm = fmaxf(m, m2);
+    const float e1 = m == -INFINITY ? 0.f : s * __expf(m - mm), e2 = m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm);
+    am = (m2 > m || (m2 == m && a2 < am)) ? a2 : am;
+    m = mm; s = e1 + e2; tl = fmaxf(tl, t2);
+  }
+  if (lane == 0) {
+    const float l = m + logf(s);
+    lse[row] = l; maxv[row] = m; argmax[row] = am; nll[row] = l - tl;
+  }
+}
+
+void ce_combine(const float* stats, int tiles, float* lse, float* maxv, int* argmax, float* nll, int rows, cudaStream_t st) {
+  if (rows <= 0) return;
+  ce_combine_kernel<<<(rows + 7) / 8, 256, 0, st>>>(reinterpret_cast<const float4*>(stats), tiles, lse, maxv, argmax, nll, rows);
+}
+
 void ce_fwd(const void* logits, const int* targets, float* lse, float* maxv, int* argmax, float* nll, int rows, int V,
             cudaStream_t st) {
   if (rows <= 0) return;

@@ -735,13 +735,31 @@ def gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
     return R.gn_bonus_gate(y, r, k, v, g, ln_w, ln_b, r_k, n_heads, eps)
 
 
+# RWKV7M_B200_HEAD_STATS=0 writes every logits chunk in forward and reads it back with ce_fwd_kernel (for comparisons).
+HEAD_STATS_EPILOGUE = os.environ.get("RWKV7M_B200_HEAD_STATS", "1") != "0"
+
+
+def _head_chunk_stats(h_rows, wc, targets_rows, buf):
+    """lse, max, argmax, nll of one chunk of rows of the head.  The GEMM's own epilogue reduces every 256-column tile to
+    (maximum, sum of exponentials, arg-max, target logit) of the bf16-rounded logits and a small kernel folds the tiles,
+    so forward writes no logits at all; ``buf`` is only used by the two-pass variant."""
+    if HEAD_STATS_EPILOGUE:
+        out = _C.gemm_ce_stats(h_rows, wc, targets_rows, int(GEMM_PAIR))
+        _count(2)
+        return out
+    logits = buf[: h_rows.shape[0]]
+    gemm(h_rows, wc, logits, GEMM_TN, EPI_BF16)
+    out = _C.ce_fwd(logits, targets_rows)
+    _count()
+    return out
+
+
 class HeadLossFn(torch.autograd.Function):
     """LM head + cross-entropy + L2Wrap without keeping the logits.
 
-    Forward runs the head GEMM chunk by chunk into one reusable [rows, V] bf16
-    buffer and keeps only per-row log-sum-exp / max / argmax.  Backward
-    recomputes each logits chunk, turns it into its own gradient in place and
-    feeds the two gradient GEMMs.
+    Forward runs the head GEMM chunk by chunk with the cross-entropy statistics in its epilogue and keeps only per-row
+    log-sum-exp / max / argmax (no logits leave the kernel).  Backward recomputes each logits chunk into one reusable
+    [rows, V] bf16 buffer, turns it into its own gradient in place and feeds the two gradient GEMMs.
     """
 
     @staticmethod
@@ -755,17 +773,14 @@ class HeadLossFn(torch.autograd.Function):
         tgt = targets.reshape(-1).to(torch.int32).contiguous()
         msk = None if mask is None else mask.reshape(-1).float().contiguous()
         chunk_rows = min(chunk_rows, M)
-        buf = torch.empty(chunk_rows, V, dtype=torch.bfloat16, device=h.device)
+        buf = None if HEAD_STATS_EPILOGUE else torch.empty(chunk_rows, V, dtype=torch.bfloat16, device=h.device)
         lse = torch.empty(M, dtype=torch.float32, device=h.device)
         mx = torch.empty_like(lse)
         nll = torch.empty_like(lse)
         am = torch.empty(M, dtype=torch.int32, device=h.device)
         for s in range(0, M, chunk_rows):
             e = min(M, s + chunk_rows)
-            logits = buf[: e - s]
-            gemm(h2[s:e], wc, logits, GEMM_TN, EPI_BF16)
-            l, m, a, n = _C.ce_fwd(logits, tgt[s:e])
-            _count()
+            l, m, a, n = _head_chunk_stats(h2[s:e], wc, tgt[s:e], buf)
             lse[s:e], mx[s:e], am[s:e], nll[s:e] = l, m, a, n
         ce_total = (nll * msk).sum() if msk is not None else nll.sum()
         ce_count = msk.sum() if msk is not None else torch.tensor(float(M), device=h.device)
@@ -833,15 +848,12 @@ class VocabParallelHeadLossFn(torch.autograd.Function):
         t_read = t_loc.clamp(0, Vl - 1).contiguous()
         msk = None if mask is None else mask.reshape(-1).float().contiguous()
         chunk_rows = min(chunk_rows, M)
-        buf = torch.empty(chunk_rows, Vl, dtype=torch.bfloat16, device=h.device)
+        buf = None if HEAD_STATS_EPILOGUE else torch.empty(chunk_rows, Vl, dtype=torch.bfloat16, device=h.device)
         stats = torch.empty(3, M, dtype=torch.float32, device=h.device)   # local lse, local max, owned target logit
         am = torch.empty(M, dtype=torch.int32, device=h.device)
         for s in range(0, M, chunk_rows):
             e = min(M, s + chunk_rows)
-            logits = buf[: e - s]
-            gemm(h2[s:e], wc, logits, GEMM_TN, EPI_BF16)
-            l, m, a, n = _C.ce_fwd(logits, t_read[s:e])
-            _count()
+            l, m, a, n = _head_chunk_stats(h2[s:e], wc, t_read[s:e], buf)
             stats[0, s:e], stats[1, s:e], am[s:e] = l, m, a
             stats[2, s:e] = torch.where(owned[s:e], l - n, torch.zeros_like(l))
         every = torch.empty(world, 3, M, dtype=torch.float32, device=h.device)

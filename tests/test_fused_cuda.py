@@ -123,6 +123,28 @@ def test_head_loss_matches_materialised_logits():
     _close(gw1, gw2, 5e-2, "dhead")
 
 
+@pytest.mark.parametrize("M,V,K", [(300, 1000, 128), (512, 4096, 512), (1000, 65536, 256)])
+def test_head_statistics_epilogue_equals_a_pass_over_stored_logits(M, V, K):
+    """The GEMM epilogue that keeps only per-tile cross-entropy statistics (single-CTA kernel for K < 512, CTA pair
+    otherwise; V = 1000 ends inside a tile) against the bf16 store epilogue followed by the loss kernel's forward."""
+    from rwkv7m_b200.ops import cuda as K_
+    from rwkv7m_b200.ops.build import load_extension
+
+    ext = load_extension()
+    h = _t(M, K, seed=70).bfloat16()
+    w = _t(V, K, seed=71, scale=0.3).bfloat16()
+    g = torch.Generator().manual_seed(72)
+    targets = torch.randint(0, V, (M,), generator=g).to(torch.int32).cuda()
+    logits = torch.empty(M, V, dtype=torch.bfloat16, device="cuda")
+    K_.gemm(h, w, logits, K_.GEMM_TN, K_.EPI_BF16)
+    lse0, max0, am0, nll0 = ext.ce_fwd(logits, targets)
+    lse1, max1, am1, nll1 = ext.gemm_ce_stats(h, w, targets, 1)
+    assert torch.equal(max0, max1)
+    assert torch.equal(am0, am1)
+    assert torch.allclose(lse0, lse1, atol=2e-5, rtol=1e-6) and torch.allclose(nll0, nll1, atol=2e-5, rtol=1e-5)
+    assert K_.gemm_error_code(h) == 0
+
+
 def test_bf16_model_step_matches_reference_path():
     import rwkv7m_b200 as RW
     from rwkv7m_b200.train import generate_toy_batch, model_loss
