@@ -13,7 +13,7 @@ import torch
 from ..api import create_train_runtime, train_batch
 from ..config import ModelConfig, ScreeningConfig
 from ..data import create_binidx_dataset
-from ..utils.timing import DeviceTimer, nvtx_range
+from ..utils.timing import DeviceTimer, nvtx_range, timeline_trace
 from .common import (
     add_execution_args,
     add_model_source_args,
@@ -63,7 +63,7 @@ def run_variant(args, variant) -> dict:
     losses = []
     timer = DeviceTimer(device)   # CUDA events on the launching stream (host clock on CPU)
     try:
-        with timer:
+        with timeline_trace(args.trace_dir, variant), timer:
             for step in range(args.steps):
                 with nvtx_range(f"{variant}.step"):
                     state, metrics = train_batch(state, dataset.get_batch(step), runtime, phase=phase)
@@ -74,7 +74,7 @@ def run_variant(args, variant) -> dict:
         dataset.close()
     elapsed = timer.ms / 1e3
     tokens = args.steps * args.batch_size * args.ctx_len
-    return {"variant": variant, "steps": args.steps, "tokens": tokens, "seconds": elapsed,
+    return {"variant": variant, "steps": args.steps, "tokens": tokens, "seconds": elapsed, "traced": args.trace_dir is not None,
             "tokens_per_sec": tokens / elapsed if elapsed > 0 else 0.0,
             "first_loss": losses[0], "last_loss": losses[-1]}
 
@@ -103,6 +103,8 @@ def parse_args(argv=None):
     p.add_argument("--n-slots", type=int, default=4)
     p.add_argument("--screened-layers", type=int, nargs="*", default=[])
     p.add_argument("--print-every", type=int, default=1)
+    p.add_argument("--trace-dir", default=None,
+                   help="write a Chrome-trace timeline per variant here (torch.profiler; the reported time is then not a benchmark figure)")
     p.add_argument("--device", default="auto")
     return parse_args_with_config(p, argv)
 

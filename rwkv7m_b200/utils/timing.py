@@ -84,3 +84,26 @@ class DeviceTimer:
         else:
             self.ms = (time.perf_counter() - self._t0) * 1e3
         return False
+
+
+@contextlib.contextmanager
+def timeline_trace(out_dir, name: str = "trace"):
+    """Optional timeline export: with a directory, the body runs under ``torch.profiler`` (host activity, plus device
+    activity when CUDA and its tracing library are present) and a Chrome-trace JSON ``<name>.json`` is written there;
+    with ``None`` the body runs untouched.  A number measured under a profiler is not a benchmark figure: the callers
+    report the timing of the run but mark it as traced."""
+    if out_dir is None:
+        yield None
+        return
+    from pathlib import Path
+
+    from torch.profiler import ProfilerActivity, profile
+
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    acts = [ProfilerActivity.CPU]
+    if torch.cuda.is_available():
+        acts.append(ProfilerActivity.CUDA)
+    with profile(activities=acts) as prof:
+        yield prof
+    prof.export_chrome_trace(str(out / f"{name}.json"))

@@ -121,3 +121,19 @@ def test_eval_tool_carry_state_rules_and_run(tiny_binidx, tmp_path):
     carried = eval_binidx.evaluate_binidx(eval_binidx.parse_args(base + ["--sampling-mode", "sequential", "--carry-state"]))
     assert plain["loss"] > 0 and carried["loss"] > 0
     assert plain["loss"] != carried["loss"]     # the carried state changes what the model sees after the first batch
+
+
+def test_bench_tool_times_variants_and_can_export_a_timeline(tiny_binidx, tmp_path, capsys):
+    from rwkv7m_b200.cli import bench_binidx
+
+    argv = ["--data-file", tiny_binidx, "--ctx-len", "4", "--batch-size", "2", "--steps", "2", "--vocab-size", "300",
+            "--d-model", "32", "--d-ffn", "64", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-slot", "16",
+            "--d-k", "8", "--d-v", "8", "--n-slots", "4", "--screened-layers", "1", "--print-every", "0", "--device", "cpu",
+            "--trace-dir", str(tmp_path / "tl")]
+    rows = bench_binidx.main(argv)
+    assert [r["variant"] for r in rows] == ["baseline", "screening", "read_write"]
+    assert all(r["tokens"] == 16 and r["traced"] and r["tokens_per_sec"] > 0 for r in rows)
+    assert "variant,steps,tokens" in capsys.readouterr().out
+    traces = sorted(p.name for p in (tmp_path / "tl").iterdir())
+    assert traces == ["baseline.json", "read_write.json", "screening.json"]
+    assert json.loads((tmp_path / "tl" / "baseline.json").read_text())["traceEvents"]
