@@ -931,7 +931,7 @@ int launch_pair(const GemmArgs& p, cudaStream_t st) {
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
   const int max_pairs = sm_count() / 2;
   // split-K for the accumulating epilogue: a weight gradient has few tiles and a long reduction, and 64 or 256 tiles
-  // on 74 pairs leave the last round of tiles mostly idle.  The split count that minimises rounds / splits wins (ties
+  // on 74 pairs leave the last wave of tiles mostly idle.  The split count that minimises waves / splits wins (ties
   // to the smaller count: every split adds one pass of atomic adds over the output).
   int splits = 1;
   if (EPI == kEpiAccumF32 && pair_splitk_enabled()) {

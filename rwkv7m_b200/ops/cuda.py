@@ -72,7 +72,7 @@ def wkv_chunk_error_code(reset: bool = True) -> int:
 
 
 # RWKV7M_B200_WGRAD_OVERLAP=1: the chunked WKV7 backward runs one CTA per SM, so the 256 sequences of the 1.5B shape take
-# two rounds on 148 SMs and 40 SMs idle through the second one.  The weight gradient of the time-mix output projection,
+# two waves on 148 SMs and 40 SMs idle through the second one.  The weight gradient of the time-mix output projection,
 # which autograd reaches just before, does not depend on it: it is held back and issued on the main stream while the
 # recurrence runs on a high-priority side stream, so its CTAs take the SMs the recurrence leaves free.
 WGRAD_OVERLAP = os.environ.get("RWKV7M_B200_WGRAD_OVERLAP", "0") == "1"
