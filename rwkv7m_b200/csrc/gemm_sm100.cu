@@ -1155,6 +1155,26 @@ int launch_pair_layout(const GemmArgs& p, cudaStream_t st) {
 
 }  // namespace
 
+bool tma_encode_bf16_3d(void* map, const void* ptr, unsigned long long d0, unsigned long long d1, unsigned long long d2,
+                        unsigned long long stride1, unsigned long long stride2, unsigned box0, unsigned box1) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  static thread_local bool context_bound = false;   // the driver entry point needs a current context on this thread
+  if (!context_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess)
+      return false;
+    context_bound = true;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2};
+  cuuint64_t strides[2] = {(cuuint64_t)stride1, (cuuint64_t)stride2};
+  cuuint32_t box[3] = {box0, box1, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  return fn(reinterpret_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool gemm_decode_eligible(const GemmArgs& p) {
   const bool epi_ok = p.epilogue == kEpiStoreBf16 || p.epilogue == kEpiReluSqBf16 || p.epilogue == kEpiAddBf16;
   // with a short reduction (the up-projection of a low-rank pair) there is no chain of dependent MMAs to split and the

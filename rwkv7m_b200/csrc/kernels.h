@@ -243,6 +243,11 @@ struct GemmArgs {
   int decode_kernel;   // non-zero: shapes with M <= 64 (layout kGemmTN) take the swap-AB cluster split-K kernel
 };
 int gemm_bf16(const GemmArgs& p, cudaStream_t st);
+// Tiled tensor map (128 bytes at `map`, 64-byte aligned) over a bf16 array of logical shape [d2][d1][d0], d0 contiguous,
+// with byte strides stride1 / stride2 for the two outer dimensions; box = box0 x box1 x 1 elements, 128-byte swizzle,
+// zero fill outside the array.  Used for operand tiles that land in shared memory in the tensor cores' canonical layout.
+bool tma_encode_bf16_3d(void* map, const void* ptr, unsigned long long d0, unsigned long long d1, unsigned long long d2,
+                        unsigned long long stride1, unsigned long long stride2, unsigned box0, unsigned box1);
 bool gemm_decode_eligible(const GemmArgs& p);
 
 }  // namespace rk

@@ -13,14 +13,21 @@
 // One CTA of 8 warps per (batch, head) walks the chunks in order; two CTAs share an SM.  Every product is a
 // tcgen05.mma with M = 128 (two 64-row operands stacked, or 64 useful rows plus 64 ignored ones), bf16
 // operands written into shared memory in the 128-byte-swizzled canonical layout, fp32 accumulators in tensor
-// memory.  The raw tiles of the next chunk are requested with asynchronous copies as soon as the last product that
-// reads a slot has completed, so their latency hides behind the rest of the current chunk.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
+// memory.  The raw [64 steps][64 channels] tiles of the next chunk are requested as soon as the last product that
+// reads a slot has completed, so their latency hides behind the rest of the current chunk: one thread issues
+// cp.async.bulk.tensor loads over 3-D tensor maps of the [B, T, H * 64] inputs (the copy engine writes the 128-byte
+// swizzled operand layout directly and zero-fills steps past the end of the sequence) and an mbarrier counts the
+// bytes; a cp.async variant with per-thread 16-byte copies remains as the fallback when no tensor map can be made.  The fp32 master copy of the state lives in registers (thread (k, half) holds 32 values of row k of
 // S^T); its bf16 image is the B operand of the next chunk.  Decay is bounded below by exp(-exp(-0.5)) = 0.545
 // per step, so every scale factor stays inside the fp32 / bf16 exponent range over 64 steps.
 //
 // In training mode the kernel also writes U (the `sa` vectors, bf16) and the state after every chunk, which is what
 // the chunked backward kernel consumes.  Reference semantics: src/rwkv7m/model/rwkv_core.py:54-86,
 // src/rwkv7m/kernels/wkv_pallas_gpu.py:66-164.
+#include <cuda.h>
+
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "wkv7_chunk.cuh"
@@ -46,7 +53,7 @@ constexpr uint32_t kOffS = kOffX2 + 8192;         // [64][64] bf16: S^T
 constexpr uint32_t kOffF = kOffS + 8192;          // fp32 [64][68]: A_ab, overwritten by its inverse
 constexpr uint32_t kOffW = kOffF + L * kFStride * 4;    // fp32 scratch of the blocked inverse
 constexpr uint32_t kOffPL = kOffW + kInvWorkFloats * 4; // fp32 [64]: P_L
-constexpr uint32_t kOffBar = kOffPL + NH * 4;     // 4 mbarriers, tmem slot, failure flag
+constexpr uint32_t kOffBar = kOffPL + NH * 4;     // 5 mbarriers (4 MMA groups, tile loads), tmem slot, failure flag
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;    // + alignment slack
 
 static_assert(kFStride == kInvStride, "the inverse routine reads the A_ab scratch with its own row stride");
@@ -71,6 +78,9 @@ __device__ long long g_wkv_chunk_prof[16];
 #define PROF_MARK(i) do { } while (0)
 #endif
 
+// tensor maps of the six inputs in slot order: a, r, b, k, w, v
+struct ChunkMaps { CUtensorMap m[6]; };
+
 struct ChunkPtrs {
   const __nv_bfloat16 *r, *w, *k, *v, *a, *b;
   __nv_bfloat16* y;
@@ -80,7 +90,8 @@ struct ChunkPtrs {
 };
 
 template <bool SAVE>
-__global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g, int T, int H, int BH) {
+__global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g, const __grid_constant__ ChunkMaps maps,
+                                                                     int use_tma, int T, int H, int BH) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by adding an offset (not by casting through an integer) so accesses stay in the shared address space
   uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -99,8 +110,13 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+    mbar_init(&bars[4], 3);   // tile loads: three request groups per chunk, each one arrival plus its bytes
     *failed = 0;
     mbar_fence_init();
+    if (use_tma) {
+#pragma unroll
+      for (int i = 0; i < 6; ++i) tma_prefetch_desc(&maps.m[i]);
+    }
   }
   if (warp == 0) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
@@ -133,6 +149,14 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
   // Coalesced asynchronous copy of one raw [64][64] bf16 tile of chunk cc straight into an operand slot (8 lanes per
   // 128-byte row, swizzled like the operand tiles; rows past the end of the sequence are zero-filled).  Each slot of
   // the next chunk is requested as soon as the last product that reads the current contents has completed.
+  // bulk-tensor variant: one thread announces the bytes of a request group and issues one copy per tile
+  auto fetch_group = [&](int cc, int first, int count) {   // tiles first .. first + count - 1 in the order a, r, b, k, w, v
+    constexpr uint32_t slot_of[6] = {kOffAR, kOffAR + 8192, kOffBK, kOffBK + 8192, kOffBKe, kOffUV + 8192};
+    if (tid == 0) {
+      mbar_expect_tx(&bars[4], (uint32_t)count * 8192u);
+      for (int i = first; i < first + count; ++i) tma_load_3d(sm + slot_of[i], &maps.m[i], &bars[4], hi * NH, cc * L, bi);
+    }
+  };
   auto fetch_tile = [&](uint32_t slot, const __nv_bfloat16* src, int cc) {
     const int p8 = tid & 7;
 #pragma unroll
@@ -143,13 +167,19 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
       else *reinterpret_cast<uint4*>(sm + slot + off) = make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  fetch_tile(kOffAR, g.a, 0);
-  fetch_tile(kOffAR + 8192, g.r, 0);
-  fetch_tile(kOffBK, g.b, 0);
-  fetch_tile(kOffBK + 8192, g.k, 0);
-  fetch_tile(kOffBKe, g.w, 0);
-  fetch_tile(kOffUV + 8192, g.v, 0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
+  if (use_tma) {
+    fetch_group(0, 0, 2);   // the same three groups as inside the loop: (a, r, k), (b), (w, v)
+    fetch_group(0, 2, 2);
+    fetch_group(0, 4, 2);
+  } else {
+    fetch_tile(kOffAR, g.a, 0);
+    fetch_tile(kOffAR + 8192, g.r, 0);
+    fetch_tile(kOffBK, g.b, 0);
+    fetch_tile(kOffBK + 8192, g.k, 0);
+    fetch_tile(kOffBKe, g.w, 0);
+    fetch_tile(kOffUV + 8192, g.v, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
 #ifdef RK_WKV_PROF
   long long prof_t = clock64();
 #endif
@@ -158,8 +188,13 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     const int t0 = c * L;
     const uint32_t par = (uint32_t)(c & 1);
     // ---- raw tiles: requested during the previous chunk (before the loop for the first one) -------------------------
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (use_tma) {
+      if (!mbar_wait(&bars[4], par, failed)) { *failed = 1; }
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    if (*failed) { ok = false; break; }
     PROF_MARK(8);
     // ---- rescale in place: warp w owns the 16-byte column piece w, lane l owns rows l and l + 32 ----------------------
     {
@@ -301,10 +336,19 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     tc_fence_after();
     PROF_MARK(3);
     if (more) {   // A~, R~ and A_rk have been consumed: their slots take the next chunk's raw a, r and k
-      fetch_tile(kOffAR, g.a, c + 1);
-      fetch_tile(kOffAR + 8192, g.r, c + 1);
-      fetch_tile(kOffBK + 8192, g.k, c + 1);
-      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (use_tma) {
+        if (tid == 0) {
+          mbar_expect_tx(&bars[4], 3u * 8192u);
+          tma_load_3d(sm + kOffAR, &maps.m[0], &bars[4], hi * NH, (c + 1) * L, bi);
+          tma_load_3d(sm + kOffAR + 8192, &maps.m[1], &bars[4], hi * NH, (c + 1) * L, bi);
+          tma_load_3d(sm + kOffBK + 8192, &maps.m[3], &bars[4], hi * NH, (c + 1) * L, bi);
+        }
+      } else {
+        fetch_tile(kOffAR, g.a, c + 1);
+        fetch_tile(kOffAR + 8192, g.r, c + 1);
+        fetch_tile(kOffBK + 8192, g.k, c + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
     }
     if (lower) {  // Z rows -> bf16 operand tile over the dead A_ak slot, 32 columns per thread
       uint32_t v[32];
@@ -329,8 +373,12 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     if (!mbar_wait(&bars[3], par, failed)) { *failed = 1; }
     tc_fence_after();
     if (more) {   // Z has been consumed: its slot takes the next chunk's raw b
-      fetch_tile(kOffBK, g.b, c + 1);
-      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (use_tma) {
+        fetch_group(c + 1, 2, 1);
+      } else {
+        fetch_tile(kOffBK, g.b, c + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
     }
     if (lower) {  // U rows -> bf16 operand tile (over the inverse, which the finished MMA no longer reads) and, in
                   // training, the same bf16 rows for the backward pass
@@ -372,9 +420,13 @@ __global__ void __launch_bounds__(kThreads, 2) wkv7_chunk_fwd_kernel(ChunkPtrs g
     tc_fence_after();
     PROF_MARK(6);
     if (more) {   // B^ and V have been consumed: their slots take the next chunk's raw w and v
-      fetch_tile(kOffBKe, g.w, c + 1);
-      fetch_tile(kOffUV + 8192, g.v, c + 1);
-      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (use_tma) {
+        fetch_group(c + 1, 4, 2);
+      } else {
+        fetch_tile(kOffBKe, g.w, c + 1);
+        fetch_tile(kOffUV + 8192, g.v, c + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
     }
     {
       uint32_t v[32];
@@ -438,14 +490,27 @@ int wkv7_chunk_forward(const WkvArgs& p, cudaStream_t st) {
   g.v = (const __nv_bfloat16*)p.v; g.a = (const __nv_bfloat16*)p.a; g.b = (const __nv_bfloat16*)p.b;
   g.y = (__nv_bfloat16*)p.y; g.s0 = p.s0; g.sT = p.sT; g.sa = (__nv_bfloat16*)p.sa; g.ckpt = p.ckpt;
   const int BH = p.B * p.H;
+  // tensor maps over the [B, T, H * 64] inputs; RWKV7M_B200_WKV_TMA=0 keeps the per-thread copies (for comparisons)
+  alignas(64) ChunkMaps maps;
+  static const bool want_tma = [] { const char* e = getenv("RWKV7M_B200_WKV_TMA"); return e == nullptr || e[0] != '0'; }();
+  int use_tma = want_tma ? 1 : 0;
+  const void* src[6] = {p.a, p.r, p.b, p.k, p.w, p.v};
+  const unsigned long long row_bytes = (unsigned long long)p.H * NH * 2;
+  for (int i = 0; i < 6 && use_tma; ++i) {
+    if ((reinterpret_cast<uintptr_t>(src[i]) & 15) != 0 ||
+        !tma_encode_bf16_3d(&maps.m[i], src[i], (unsigned long long)p.H * NH, (unsigned long long)p.T, (unsigned long long)p.B,
+                            row_bytes, row_bytes * p.T, NH, L))
+      use_tma = 0;
+  }
+  if (!use_tma) memset(&maps, 0, sizeof(maps));
   if (p.sa != nullptr) {
     auto kern = wkv7_chunk_fwd_kernel<true>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    kern<<<BH, kThreads, kSmemBytes, st>>>(g, p.T, p.H, BH);
+    kern<<<BH, kThreads, kSmemBytes, st>>>(g, maps, use_tma, p.T, p.H, BH);
   } else {
     auto kern = wkv7_chunk_fwd_kernel<false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    kern<<<BH, kThreads, kSmemBytes, st>>>(g, p.T, p.H, BH);
+    kern<<<BH, kThreads, kSmemBytes, st>>>(g, maps, use_tma, p.T, p.H, BH);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
