@@ -20,6 +20,11 @@
 // fetched with asynchronous copies while the second half of the current chunk runs: dY, V and U land directly in
 // their operand slots, which the remaining products no longer read, the five tiles that are rescaled go to a
 // staging area.  All waits are bounded.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "wkv7_chunk.cuh"
@@ -64,6 +69,9 @@ constexpr uint32_t kC6 = 320;   // 64: dZ (lanes 0-63), then R~^T dY + A~^T dZ (
 
 static_assert(kFStride == kInvStride, "the inverse routine reads the A_ab scratch with its own row stride");
 
+// tensor maps of the eight per-chunk tiles in destination order: a, r, b, k, w (staging area), saved U, v, dY
+struct BwdMaps { CUtensorMap m[8]; };
+
 struct BwdPtrs {
   const __nv_bfloat16 *r, *w, *k, *v, *a, *b, *dy, *sa;
   const __nv_bfloat16 *dr_add, *dk_add, *dv_add;   // optional: gradients that reach r, k, v by another path, summed here
@@ -104,7 +112,8 @@ __device__ __forceinline__ void store16_bf16(uint8_t* tile, int row, int p0, con
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, int T, int H, int BH) {
+__global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, const __grid_constant__ BwdMaps maps,
+                                                                     int use_tma, int T, int H, int BH) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(sm);
@@ -127,6 +136,11 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    mbar_init(&bars[5], 1);   // tile loads: one request per chunk, its arrival plus the bytes of eight tiles
+    if (use_tma) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tma_prefetch_desc(&maps.m[i]);
+    }
     *failed = 0;
     mbar_fence_init();
   }
@@ -161,6 +175,22 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
   // and the saved U rows go straight into their operand slots, a / r / b / k / w into the staging area.
   auto fetch_chunk = [&](int cc) {
     const int tc = cc * L;
+    if (use_tma) {
+      // one thread hands the eight [64 steps][64 channels] boxes to the copy engine, which writes the swizzled operand
+      // layout and zero-fills steps past the end of the sequence; the mbarrier counts the bytes
+      if (tid == 0) {
+        mbar_expect_tx(&bars[5], 8u * 8192u);
+        const int x = hi * NH;
+        tma_load_3d(sm + kOffStage, &maps.m[0], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffStage + 8192, &maps.m[1], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffStage + 16384, &maps.m[2], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffStage + 24576, &maps.m[3], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffStage + 32768, &maps.m[4], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffUV, &maps.m[5], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffUV + 8192, &maps.m[6], &bars[5], x, tc, bi);
+        tma_load_3d(sm + kOffZY + 8192, &maps.m[7], &bars[5], x, tc, bi);
+      }
+    } else {
     const int p8 = tid & 7, row = tid >> 3;
     const uint32_t off = sw128(row, p8);
     const size_t go = base + (size_t)(tc + row) * stride_t + p8 * 8;
@@ -185,6 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
       *reinterpret_cast<uint4*>(sm + kOffZY + 8192 + off) = zero;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     if (tid < 128) {   // the state before that chunk (fp32, converted at the top of its iteration): pull it into L2
       const float* s_in = cc == 0 ? g.s0 + (size_t)bh * NH * NH : g.ckpt + ((size_t)(cc - 1) * BH + bh) * NH * NH;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(s_in + tid * 32));
@@ -214,9 +245,14 @@ __global__ void __launch_bounds__(kThreads, 1) wkv7_chunk_bwd_kernel(BwdPtrs g, 
         }
         LT[ch * NH + trow] = lt_next;
       }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if (use_tma) {
+        if (!mbar_wait(&bars[5], par, failed)) { *failed = 1; }
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
       __syncthreads();
     }
+    if (*failed) { ok = false; break; }
     PROF_MARK(12);
     // ---- rescale: warp w owns the 16-byte column piece w % 8 of rows 32 (w / 8) .. 32 (w / 8) + 31, lane = row ---------
     {
@@ -626,9 +662,22 @@ int wkv7_chunk_backward(const WkvArgs& p, cudaStream_t st) {
   g.dv = (__nv_bfloat16*)p.dv; g.da = (__nv_bfloat16*)p.da; g.db = (__nv_bfloat16*)p.db; g.ds0 = p.ds0;
   g.dr_add = (const __nv_bfloat16*)p.dr_add; g.dk_add = (const __nv_bfloat16*)p.dk_add; g.dv_add = (const __nv_bfloat16*)p.dv_add;
   const int BH = p.B * p.H;
+  // tensor maps over the [B, T, H * 64] tensors; RWKV7M_B200_WKV_TMA=0 keeps the per-thread copies (for comparisons)
+  alignas(64) BwdMaps maps;
+  static const bool want_tma = [] { const char* e = getenv("RWKV7M_B200_WKV_TMA"); return e == nullptr || e[0] != '0'; }();
+  int use_tma = want_tma ? 1 : 0;
+  const void* src[8] = {p.a, p.r, p.b, p.k, p.w, p.sa, p.v, p.dy};
+  const unsigned long long row_bytes = (unsigned long long)p.H * NH * 2;
+  for (int i = 0; i < 8 && use_tma; ++i) {
+    if ((reinterpret_cast<uintptr_t>(src[i]) & 15) != 0 ||
+        !tma_encode_bf16_3d(&maps.m[i], src[i], (unsigned long long)p.H * NH, (unsigned long long)p.T, (unsigned long long)p.B,
+                            row_bytes, row_bytes * p.T, NH, L))
+      use_tma = 0;
+  }
+  if (!use_tma) memset(&maps, 0, sizeof(maps));
   auto kern = wkv7_chunk_bwd_kernel;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-  kern<<<BH, kThreads, kSmemBytes, st>>>(g, p.T, p.H, BH);
+  kern<<<BH, kThreads, kSmemBytes, st>>>(g, maps, use_tma, p.T, p.H, BH);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
