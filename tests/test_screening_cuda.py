@@ -31,11 +31,12 @@ def _setup(phase, n_slots=4, d_slot=32, age_mask=False, seed=0, d_k=16, d_v=16, 
     return mod, x, h, st
 
 
-# the last three rows are the bank shapes of the 1b / 3b / 7b presets (two projection columns per thread from J > 512);
+# the last three rows are the bank shapes of the 1b / 3b / 7b presets (12 / 18 / 24 projection columns per lane);
 # (5, 48, ...) has a slot width that is no multiple of 32 and a leaky read relevance
 @pytest.mark.parametrize("phase", ["read_screening_only", "read_write"])
 @pytest.mark.parametrize("n_slots,d_slot,age_mask,d_k,d_v,leaky", [
     (4, 32, False, 16, 16, False), (16, 64, True, 16, 16, False), (5, 48, True, 24, 40, True),
+    (16, 256, False, 64, 128, False),   # the 0.3b preset's bank (8 projection columns per lane)
     (16, 384, False, 96, 192, False), (16, 640, True, 128, 320, False), (16, 1024, False, 128, 512, True)])
 def test_scan_kernel_matches_reference(phase, n_slots, d_slot, age_mask, d_k, d_v, leaky):
     mod, x, h, st = _setup(phase, n_slots, d_slot, age_mask, d_k=d_k, d_v=d_v, leaky=leaky)
