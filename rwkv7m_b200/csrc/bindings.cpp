@@ -43,12 +43,16 @@ rk::WkvArgs wkv_args(const Tensor& r, const Tensor& w, const Tensor& k, const Te
 }
 
 std::vector<Tensor> wkv7_fwd(const Tensor& r, const Tensor& w, const Tensor& k, const Tensor& v, const Tensor& a,
-                             const Tensor& b, const Tensor& s0, bool save, int64_t interval, bool chunked) {
+                             const Tensor& b, const Tensor& s0, bool save, int64_t interval, bool chunked,
+                             bool inplace_state) {
   c10::cuda::CUDAGuard guard(r.device());
   TORCH_CHECK(interval >= 1, "checkpoint interval must be positive");
   rk::WkvArgs p = wkv_args(r, w, k, v, a, b, s0, interval);
   Tensor y = torch::empty_like(r);
-  Tensor sT = torch::empty_like(s0);
+  // serving: the scan kernel holds a sequence's whole state in registers between its first load and its last store,
+  // so the final state may overwrite the initial one (the returned state is then `s0` itself)
+  const bool in_place = inplace_state && !save && !(chunked && rk::wkv7_chunk_supported(p));
+  Tensor sT = in_place ? s0 : torch::empty_like(s0);
   Tensor sa, ckpt;
   p.y = y.data_ptr(); p.sT = sT.data_ptr<float>();
   if (save) p.sa = reinterpret_cast<void*>(1);   // placeholder: "training forward" for the support query below
@@ -838,7 +842,8 @@ int64_t dp_aux_words() { return rk::dp_aux_words(); }
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("wkv7_fwd", &wkv7_fwd);
+  m.def("wkv7_fwd", &wkv7_fwd, py::arg("r"), py::arg("w"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"),
+        py::arg("s0"), py::arg("save"), py::arg("interval"), py::arg("chunked"), py::arg("inplace_state") = false);
   m.def("wkv7_bwd", &wkv7_bwd, py::arg("r"), py::arg("w"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"),
         py::arg("s0"), py::arg("sa"), py::arg("ckpt"), py::arg("dy"), py::arg("dsT"), py::arg("interval"), py::arg("chunked"),
         py::arg("add") = py::none());

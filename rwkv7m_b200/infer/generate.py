@@ -102,9 +102,14 @@ class GraphDecoder:
             self.logits = self._body()
 
     def _body(self):
-        logits, new_state, _, _ = self.model(self.ids, self.state, self.screen, phase=self.phase)
+        from .. import ops
+
+        with ops.inplace_wkv_state():   # the recurrence writes its new state over the static buffer it read
+            logits, new_state, _, _ = self.model(self.ids, self.state, self.screen, phase=self.phase)
         for dst, src in zip(self.state, new_state):
-            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x); dst.wkv.copy_(src.wkv)
+            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x)
+            if src.wkv.data_ptr() != dst.wkv.data_ptr():
+                dst.wkv.copy_(src.wkv)
         return logits[:, -1, :]
 
     def load_state(self, rwkv_state):

@@ -115,6 +115,19 @@ def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_hea
     return reference.tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads)
 
 
+class inplace_wkv_state:
+    """Context: inference calls of the T = 1 recurrence on CUDA update their state argument in place (no-op on CPU)."""
+
+    def __enter__(self):
+        self.inner = _cuda().inplace_wkv_state() if torch.cuda.is_available() else None
+        if self.inner is not None:
+            self.inner.__enter__()
+
+    def __exit__(self, *exc):
+        if self.inner is not None:
+            self.inner.__exit__(*exc)
+
+
 def flush_deferred():
     """Issue any weight-gradient GEMM that the CUDA path held back during backward (no-op otherwise)."""
     import sys

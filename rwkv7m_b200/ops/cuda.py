@@ -93,6 +93,23 @@ def flush_deferred():
         _DEFERRED_WGRADS.pop(0)()
 
 
+# Serving with static state buffers (a captured decode step): the T = 1 scan kernel writes the new state over the old
+# one, so the step does not copy 16 KB per (sequence, head) back into the static buffer afterwards.
+WKV_INPLACE_STATE = False
+
+
+class inplace_wkv_state:
+    """``with inplace_wkv_state():`` lets inference calls of the scan kernel update their state argument in place."""
+
+    def __enter__(self):
+        global WKV_INPLACE_STATE
+        self.prev, WKV_INPLACE_STATE = WKV_INPLACE_STATE, True
+
+    def __exit__(self, *exc):
+        global WKV_INPLACE_STATE
+        WKV_INPLACE_STATE = self.prev
+
+
 class Wkv7Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r, w, k, v, a, b, s0):
@@ -103,7 +120,8 @@ class Wkv7Fn(torch.autograd.Function):
                    and r.shape[-1] == 64)
         # the chunk kernels keep one state per 64-step chunk, the scan kernels one per 16 steps
         ctx.interval = WKV_CHUNK_LEN if chunked else WKV_CHECKPOINT_INTERVAL
-        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, ctx.interval, chunked)
+        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, ctx.interval, chunked,
+                                      WKV_INPLACE_STATE and not need_grad)
         _count()
         ctx.chunked = chunked
         if need_grad:
@@ -689,7 +707,7 @@ class WkvGnFn(torch.autograd.Function):
         r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
         s0 = s0.contiguous().float()
         need_grad = any(ctx.needs_input_grad)
-        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHUNK_LEN, True)
+        y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, WKV_CHUNK_LEN, True, False)
         C = H * N
         g2 = g.contiguous()
         acts = [y.view(B, T, C), r.view(B, T, C), k.view(B, T, C), v.view(B, T, C), g2.view(B, T, C)]
