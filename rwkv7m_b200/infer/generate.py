@@ -107,9 +107,10 @@ class GraphDecoder:
         with ops.inplace_wkv_state():   # the recurrence writes its new state over the static buffer it read
             logits, new_state, _, _ = self.model(self.ids, self.state, self.screen, phase=self.phase)
         for dst, src in zip(self.state, new_state):
-            dst.time_mix_x.copy_(src.time_mix_x); dst.channel_mix_x.copy_(src.channel_mix_x)
-            if src.wkv.data_ptr() != dst.wkv.data_ptr():
-                dst.wkv.copy_(src.wkv)
+            for name in ("time_mix_x", "channel_mix_x", "wkv"):   # whatever the step did not update in place
+                a, b = getattr(dst, name), getattr(src, name)
+                if a.data_ptr() != b.data_ptr():
+                    a.copy_(b)
         return logits[:, -1, :]
 
     def load_state(self, rwkv_state):

@@ -200,7 +200,7 @@ class RWKV7TimeMix(nn.Module):
             out = _row_parallel_linear(self, y, self.output.weight)
             if residual is not None:
                 out = residual + out
-        return out, v_first, x[:, -1].float(), final_state
+        return out, v_first, ops.last_token_state(x, prev_x), final_state
 
 
 class RWKV7ChannelMix(nn.Module):
@@ -223,7 +223,7 @@ class RWKV7ChannelMix(nn.Module):
             out = _row_parallel_linear(self, h, self.value.weight)
             if residual is not None:
                 out = residual + out
-        return out, x[:, -1].float()
+        return out, ops.last_token_state(x, prev_x)
 
 
 class RWKV7Block(nn.Module):

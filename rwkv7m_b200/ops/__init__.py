@@ -128,6 +128,24 @@ class inplace_wkv_state:
             self.inner.__exit__(*exc)
 
 
+def inplace_state_active() -> bool:
+    import sys
+
+    mod = sys.modules.get(__name__ + ".cuda")
+    return bool(mod is not None and mod.WKV_INPLACE_STATE)
+
+
+def last_token_state(x, prev):
+    """fp32 copy of the last position of x [B, T, C] (the token-shift state of the next call).  Inside
+    ``inplace_wkv_state()`` the previous state tensor is overwritten and returned, one kernel instead of a conversion
+    plus a copy back into a static buffer; the caller must have consumed ``prev`` already."""
+    if inplace_state_active() and prev is not None and prev.dtype == torch.float32 and prev.shape == x[:, -1].shape \
+            and not torch.is_grad_enabled():
+        prev.copy_(x[:, -1])
+        return prev
+    return x[:, -1].float()
+
+
 def flush_deferred():
     """Issue any weight-gradient GEMM that the CUDA path held back during backward (no-op otherwise)."""
     import sys
