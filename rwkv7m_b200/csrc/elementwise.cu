@@ -292,6 +292,7 @@ void layernorm_fwd(const void* x, const float* w, const float* b, void* y, float
       case 768: RK_LN_FWD(3); return;
       case 1024: RK_LN_FWD(4); return;
       case 2048: RK_LN_FWD(8); return;
+      case 4096: RK_LN_FWD(16); return;
       default: break;
     }
   }
