@@ -46,9 +46,10 @@ def _compare(fn_cuda, fn_ref, acts, pars, tol=3e-2):
         _close(a, b, tol, f"grad{i}")
 
 
-def test_layernorm():
-    x = _t(3, 50, 256, seed=1)
-    w, b = _t(256, seed=2) * 0.1 + 1.0, _t(256, seed=3) * 0.1
+@pytest.mark.parametrize("C", [256, 1000, 2048, 4096])   # one-pass kernels, a width without one, the 1.5B and 7B widths
+def test_layernorm(C):
+    x = _t(3, 50, C, seed=1)
+    w, b = _t(C, seed=2) * 0.1 + 1.0, _t(C, seed=3) * 0.1
     _compare(lambda x, w, b: ops.layer_norm(x, w, b, 1e-5), lambda x, w, b: R.layer_norm(x, w, b, 1e-5), [x], [w, b])
 
 
