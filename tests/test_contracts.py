@@ -475,3 +475,38 @@ def test_upstream_optimizer_groups_and_the_sample_boundary():
     assert optimizer_group("blocks.0.att.key.weight", 2, 0.1) != optimizer_group("blocks.0.ln1.weight", 1, 0.1)
     assert optimizer_group("blocks.0.att.key.weight", 2, 0.0) == optimizer_group("blocks.0.ln1.weight", 1, 0.0)
     assert epoch_and_index(40319) == (0, 40319) and epoch_and_index(40320) == (1, 0)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# tracked configuration examples (configs/*.json.example)
+# ---------------------------------------------------------------------------------------------------------------------
+def _configs_dir():
+    from pathlib import Path
+
+    return Path(__file__).resolve().parents[1] / "configs"
+
+
+@pytest.mark.parametrize("preset", ["0.185b", "0.3b", "1b", "3b", "7b"])
+def test_tracked_model_examples_are_the_named_presets(preset):
+    from rwkv7m_b200.config import load_model_config, model_config_to_dict
+
+    tracked = load_model_config(_configs_dir() / f"rwkv7m-{preset}.json.example")
+    assert model_config_to_dict(tracked) == model_config_to_dict(R.model_preset(preset))
+
+
+def test_tracked_run_examples_are_accepted_by_their_tools(monkeypatch):
+    from rwkv7m_b200.cli import plan_scale, train_binidx, train_binidx_distributed
+    from rwkv7m_b200.cli.common import build_config
+
+    monkeypatch.chdir(_configs_dir().parent)     # the examples name each other by repository-relative paths
+    a = train_binidx.parse_args(["--config", "configs/corpus-smoke.json.example"])
+    assert a.ctx_len == 512 and build_config(a).d_model == 128
+    b = train_binidx_distributed.parse_args(["--config", "configs/rwkv7m-7b-b200-train.json.example"])
+    assert b.mesh_axis_names == ["data", "model"] and b.mesh_axis_sizes == [1, 8]
+    cfg = build_config(b)
+    assert cfg.d_model == 4096 and cfg.screening.d_slot == 1024
+    # the planner sees the same 7B model that the trainer would build
+    est = plan_scale.main(["--model-config", "configs/rwkv7m-7b.json.example", "--model-axis-size", "8"])
+    assert est.parameter_summary.total == 6_994_788_376
+    c = train_binidx_distributed.parse_args(["--config", "configs/rwkv7m-1.5b-b200-zero3.json.example"])
+    assert c.dp_mode == "zero3" and build_config(c).n_layers == 24 and not build_config(c).use_screening
