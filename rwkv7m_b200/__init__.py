@@ -47,12 +47,30 @@ from .models import (
     StateLevelScreening,
     initialize_model,
 )
-from .ops import wkv7
+from .config import RWKV7Config
+from .models.model import create_model_variables
+from .ops import wkv7, wkv7_sharded
+from .ops.backends import (
+    WKVBackend,
+    WKVFFIBackend,
+    available_wkv_backends,
+    register_wkv_ffi_backend,
+    require_wkv_ffi_backend,
+    resolve_wkv_backend,
+    set_wkv_backend,
+    unregister_wkv_ffi_backend,
+)
+from .ops.reference import cross_entropy_components, cross_entropy_loss
 from .ops.reference import wkv7 as wkv7_reference
+from .parallel.mesh import Mesh, ShardingConfig, make_mesh
 from .state import LayerRWKVState, LayerScreenState, ModelScreenState, init_rwkv_state, init_screen_state
 from .tokenizer import RWKVTokenizer, tokenizer_metadata
 from .train.train_loop import run_toy_training
 from .train.train_step import generate_toy_batch, initialize_train_state, train_step
+
+# names under which the reference exposes the same objects
+NNXScreenedRWKVModel = ScreenedRWKVModel
+NNXShardingConfig = ShardingConfig
 
 __version__ = "0.1.0"
 

@@ -168,6 +168,31 @@ class ModelConfig:
         return {"decay": rank(2.5), "aaa": rank(2.5), "mv": rank(1.7), "gate": rank(5.0)}
 
 
+@dataclass
+class RWKV7Config:
+    """Configuration of the plain RWKV-7 stack without screening memory (the reference keeps the same small record for
+    its core model, src/rwkv7m/model/rwkv_core.py:16-24).  ``d_ffn <= 0`` means four times the model width."""
+
+    d_model: int = 768
+    d_ffn: int = -1
+    n_layers: int = 12
+    n_heads: int = 12
+    head_size: int = 64
+    vocab_size: int = 50257
+    max_seq_len: int = 4096
+    dtype: str = "bfloat16"
+
+    @property
+    def ffn_dim(self) -> int:
+        return int(self.d_ffn) if int(self.d_ffn) > 0 else 4 * int(self.d_model)
+
+    def to_model_config(self, **overrides) -> "ModelConfig":
+        """The full model configuration with screening switched off."""
+        return ModelConfig(d_model=self.d_model, d_ffn=self.ffn_dim, n_layers=self.n_layers, n_heads=self.n_heads,
+                           head_size=self.head_size, vocab_size=self.vocab_size, max_seq_len=self.max_seq_len,
+                           dtype=self.dtype, use_screening=False, **overrides)
+
+
 def model_config_to_dict(config: ModelConfig) -> dict:
     data = asdict(config)
     data["screening"]["screened_layers"] = list(data["screening"]["screened_layers"])

@@ -240,6 +240,20 @@ def initialize_model(seed_or_generator, config: ModelConfig, device=None) -> Scr
     return model
 
 
+def create_model_variables(seed, config, batch_size: int = 1, device=None):
+    """``(variables, model)``: the initialised model and its parameters as a name -> tensor mapping, which is what the
+    reference returns from a Flax ``init`` (src/rwkv7m/model/screened_rwkv.py:273-290).  ``config`` may be a
+    ``ModelConfig`` or the plain ``RWKV7Config``; ``batch_size`` is accepted for signature compatibility (PyTorch
+    modules need no example batch to initialise)."""
+    from ..config import RWKV7Config
+
+    del batch_size
+    if isinstance(config, RWKV7Config):
+        config = config.to_model_config()
+    model = initialize_model(seed, config, device=device)
+    return dict(model.named_parameters()), model
+
+
 def count_parameters(model_or_config) -> dict:
     """Parameter totals split into core and screening."""
     if isinstance(model_or_config, ModelConfig):

@@ -174,21 +174,38 @@ def _check_wkv_inputs(r, w, k, v, a, b, state0):
 def wkv7(r, w, k, v, a, b, state0):
     """WKV7 recurrence on [B,T,H,N] vectors with an fp32 [B,H,N,N] initial state."""
     _check_wkv_inputs(r, w, k, v, a, b, state0)
-    if use_cuda(r):
-        return _cuda().wkv7(r, w, k, v, a, b, state0)
+    from . import backends
+
+    choice = backends.explicit_wkv_backend()      # None: automatic (kernels on CUDA tensors, PyTorch statement on CPU)
+    if choice == "ffi" and not _FORCE_REFERENCE:
+        return backends.external_wkv7(r, w, k, v, a, b, state0)
+    if use_cuda(r) and choice != "reference":
+        return _cuda().wkv7(r, w, k, v, a, b, state0, impl=choice)
     return reference.wkv7(r, w, k, v, a, b, state0)
+
+
+def wkv7_sharded(r, w, k, v, neg_kk, kka, initial_state, *, mesh=None, data_axis: str = "data", model_axis: str = "model"):
+    """WKV7 on this process's shard of a ``data x model`` layout.  The recurrence never mixes heads or batch rows, so
+    with one process per GPU the tensors a rank holds (its batch rows and its heads) are a complete problem: the call is
+    the local recurrence, and the mesh arguments only document the partition (the reference needs an explicit shard-map
+    boundary here, src/rwkv7m/model/wkv.py:82-130)."""
+    del mesh, data_axis, model_axis
+    return wkv7(r, w, k, v, neg_kk, kka, initial_state)
 
 
 def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
     """WKV7 followed by GroupNorm + bonus + gate: ``(out [B,T,C], final_state)``.  On the GPU the two are one autograd
     node, so the gradients that r, k and v receive from both halves are summed inside the WKV7 backward kernel."""
-    if use_cuda(r):
-        return _cuda().wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps)
+    from . import backends
+
+    choice = backends.explicit_wkv_backend()
+    if use_cuda(r) and choice not in ("ffi", "reference"):
+        return _cuda().wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps, impl=choice)
     B, T, H, N = r.shape
-    y, sT = reference.wkv7(r, w, k, v, a, b, state0)
+    y, sT = wkv7(r, w, k, v, a, b, state0)      # the PyTorch statement, or the backend chosen for the process
     C = H * N
-    out = reference.gn_bonus_gate(y.reshape(B, T, C), r.reshape(B, T, C), k.reshape(B, T, C), v.reshape(B, T, C), g,
-                                  ln_w, ln_b, r_k, n_heads, eps)
+    out = gn_bonus_gate(y.reshape(B, T, C), r.reshape(B, T, C), k.reshape(B, T, C), v.reshape(B, T, C), g,
+                        ln_w, ln_b, r_k, n_heads, eps)
     return out, sT
 
 

@@ -149,8 +149,16 @@ class Wkv7Fn(torch.autograd.Function):
         return dr, dw, dk, dv, da, db, ds0
 
 
-def wkv7(r, w, k, v, a, b, state0):
-    return Wkv7Fn.apply(r, w, k, v, a, b, state0)
+def wkv7(r, w, k, v, a, b, state0, impl=None):
+    """``impl``: "chunked" / "sequential" for this call (the process-wide backend choice), None = ``WKV_IMPL``."""
+    global WKV_IMPL
+    if impl in (None, WKV_IMPL) or impl not in ("chunked", "sequential"):
+        return Wkv7Fn.apply(r, w, k, v, a, b, state0)
+    previous, WKV_IMPL = WKV_IMPL, impl
+    try:
+        return Wkv7Fn.apply(r, w, k, v, a, b, state0)
+    finally:
+        WKV_IMPL = previous
 
 
 # ---------------------------------------------------------------------------
@@ -733,14 +741,14 @@ class WkvGnFn(torch.autograd.Function):
                 _like_param(drk, r_k), None)
 
 
-def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5):
+def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5, impl=None):
     """(GroupNorm(wkv7(...)) + bonus) * g and the final state; r, w, k, v, a, b are [B,T,H,N], g is [B,T,C]."""
     B, T, H, N = r.shape
     fused = (WKV_GN_FUSED and WKV_IMPL == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64
              and r.is_cuda and g.dtype == torch.bfloat16)
     if fused:
         return WkvGnFn.apply(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, eps)
-    y, sT = wkv7(r, w, k, v, a, b, state0)
+    y, sT = wkv7(r, w, k, v, a, b, state0, impl=impl)
     C = H * N
     out = gn_bonus_gate(y.reshape(B, T, C), r.reshape(B, T, C), k.reshape(B, T, C), v.reshape(B, T, C), g, ln_w, ln_b,
                         r_k, n_heads, eps)

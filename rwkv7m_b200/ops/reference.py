@@ -149,6 +149,19 @@ def cross_entropy_l2wrap(logits, targets, mask=None):
     return ce_total, ce_count, l2_total, l2_count
 
 
+def cross_entropy_components(logits, targets, mask=None):
+    """Masked negative log-likelihood as a reducible pair (numerator, denominator), fp32
+    (src/rwkv7m/model/losses.py:21-69)."""
+    ce_total, ce_count, _, _ = cross_entropy_l2wrap(logits, targets, mask)
+    return ce_total, ce_count
+
+
+def cross_entropy_loss(logits, targets, mask=None):
+    """Mean masked cross-entropy (src/rwkv7m/model/losses.py:11-18)."""
+    total, count = cross_entropy_components(logits, targets, mask)
+    return total / torch.clamp(count, min=1.0)
+
+
 # ---- screening helpers (src/rwkv7m/model/screening.py:21-88) -----------------
 
 

@@ -105,3 +105,40 @@ def new_subgroups(mesh: Mesh):
         if rank in ranks:
             model_group = g
     return data_group, model_group
+
+
+@dataclass(frozen=True)
+class ShardingConfig:
+    """Mesh contract of a model call: which named axis splits the batch and which the model dimension.  The reference
+    hands the same record to its model constructor (src/rwkv7m/model/nnx_model.py:54-100) and derives partition specs
+    from it; with one process per GPU the specs are descriptive (tuples of axis names per tensor dimension) and the
+    placement itself is done by ``parallel.tp.TensorParallel`` / the data-parallel trainers."""
+
+    mesh: Mesh
+    data_axis: str = "data"
+    model_axis: str = "model"
+
+    def __post_init__(self):
+        for axis in (self.data_axis, self.model_axis):
+            if axis not in self.mesh.axis_names:
+                raise ValueError(f"axis {axis!r} is not an axis of the mesh {self.mesh.axis_names}")
+
+    def named(self, *axes):
+        """Partition spec: one entry per tensor dimension, an axis name or None (replicated)."""
+        for axis in axes:
+            if axis is not None and axis not in self.mesh.axis_names:
+                raise ValueError(f"unknown mesh axis {axis!r}")
+        return tuple(axes)
+
+    def activation(self, rank: int, *, model_sharded: bool):
+        """Spec of a [batch, ..., features] activation: batch over the data axis, features over the model axis if sharded."""
+        if rank < 1:
+            raise ValueError(f"activation rank must be positive, got {rank}")
+        axes = [self.data_axis] + [None] * (rank - 1)
+        if model_sharded:
+            axes[-1] = self.model_axis
+        return self.named(*axes)
+
+    def recurrent_state(self):
+        """Spec of the [batch, heads, N, N] WKV state: heads follow the model axis."""
+        return self.named(self.data_axis, self.model_axis, None, None)

@@ -510,3 +510,120 @@ def test_tracked_run_examples_are_accepted_by_their_tools(monkeypatch):
     assert est.parameter_summary.total == 6_994_788_376
     c = train_binidx_distributed.parse_args(["--config", "configs/rwkv7m-1.5b-b200-zero3.json.example"])
     assert c.dp_mode == "zero3" and build_config(c).n_layers == 24 and not build_config(c).use_screening
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# WKV backend selection, external backend boundary, small public helpers
+# ---------------------------------------------------------------------------------------------------------------------
+def test_wkv_backend_resolution_rules(monkeypatch):
+    monkeypatch.delenv("RWKV7M_B200_WKV_BACKEND", raising=False)
+    R.set_wkv_backend(None)
+    assert set(R.available_wkv_backends()) == {"chunked", "sequential", "reference", "ffi"}
+    assert R.resolve_wkv_backend(device_type="cpu") == "reference"
+    assert R.resolve_wkv_backend(device_type="cuda") == "chunked"      # an external backend is never automatic
+    assert R.resolve_wkv_backend("Sequential") == "sequential"
+    with pytest.raises(ValueError, match="unknown WKV backend"):
+        R.resolve_wkv_backend("pallas")
+    monkeypatch.setenv("RWKV7M_B200_WKV_BACKEND", "reference")
+    assert R.resolve_wkv_backend(device_type="cuda") == "reference"    # process-level override
+    R.set_wkv_backend("sequential")
+    assert R.resolve_wkv_backend(device_type="cuda") == "sequential"   # the explicit call wins over the environment
+    R.set_wkv_backend("auto")
+
+
+def test_external_wkv_backend_registration_and_dispatch():
+    calls = []
+
+    def fwd(r, w, k, v, a, b, s0):
+        calls.append("fwd")
+        return F.wkv7(r, w, k, v, a, b, s0)
+
+    def fwd_aux(r, w, k, v, a, b, s0):
+        calls.append("fwd_aux")
+        return F.wkv7(r, w, k, v, a, b, s0), (torch.ones(1),)
+
+    def bwd(r, w, k, v, a, b, s0, dy, dsT, marker):
+        calls.append("bwd")
+        assert float(marker) == 1.0
+        with torch.enable_grad():     # a backward callable runs with gradient recording switched off
+            args = [t.detach().clone().requires_grad_(True) for t in (r, w, k, v, a, b, s0)]
+            y, sT = F.wkv7(*args)
+            loss = (y * dy).sum() + (0 if dsT is None else (sT * dsT).sum())
+            return torch.autograd.grad(loss, args)
+
+    backend = R.WKVFFIBackend(forward=fwd, forward_with_aux=fwd_aux, backward=bwd)
+    R.unregister_wkv_ffi_backend()
+    with pytest.raises(RuntimeError, match="no FFI backend"):
+        R.require_wkv_ffi_backend()
+    R.register_wkv_ffi_backend(backend)
+    with pytest.raises(RuntimeError, match="already registered"):
+        R.register_wkv_ffi_backend(backend)
+    R.register_wkv_ffi_backend(backend, replace=True)
+    inputs = _wkv_inputs(T=4, N=3, seed=9)
+    try:
+        R.set_wkv_backend("ffi")
+        with torch.no_grad():
+            y0, _ = ops.wkv7(*inputs)
+        args = [t.clone().requires_grad_(True) for t in inputs]
+        y1, sT1 = ops.wkv7(*args)
+        (y1.sum() + sT1.sum()).backward()
+    finally:
+        R.set_wkv_backend(None)
+        R.unregister_wkv_ffi_backend()
+    assert calls == ["fwd", "fwd_aux", "bwd"]
+    ref = [t.clone().requires_grad_(True) for t in inputs]
+    y2, sT2 = ops.wkv7(*ref)
+    (y2.sum() + sT2.sum()).backward()
+    assert torch.allclose(y0, y2) and torch.allclose(y1, y2)
+    for a, b in zip(args, ref):
+        assert torch.allclose(a.grad, b.grad, atol=1e-6)
+    with pytest.raises(RuntimeError):
+        R.set_wkv_backend("ffi")
+        try:
+            ops.wkv7(*inputs)
+        finally:
+            R.set_wkv_backend(None)
+
+
+def test_cross_entropy_helpers_equal_the_library_definition():
+    logits = torch.randn(3, 5, 11)
+    targets = torch.randint(0, 11, (3, 5))
+    mask = (torch.rand(3, 5) > 0.3).float()
+    want = torch.nn.functional.cross_entropy(logits.view(-1, 11), targets.view(-1), reduction="none").view(3, 5)
+    total, count = R.cross_entropy_components(logits, targets, mask)
+    assert torch.allclose(total, (want * mask).sum(), atol=1e-5) and float(count) == float(mask.sum())
+    assert torch.allclose(R.cross_entropy_loss(logits, targets), want.mean(), atol=1e-5)
+    assert float(R.cross_entropy_loss(logits, targets, torch.zeros(3, 5))) == 0.0   # an empty mask does not divide by zero
+
+
+def test_plain_rwkv7_config_and_model_variables():
+    core = R.RWKV7Config(d_model=64, n_layers=2, n_heads=4, head_size=16, vocab_size=97, dtype="float32")
+    assert core.ffn_dim == 256
+    cfg = core.to_model_config()
+    assert cfg.use_screening is False and cfg.d_ffn == 256 and cfg.vocab_size == 97
+    variables, model = R.create_model_variables(3, core, batch_size=2)
+    assert isinstance(model, R.NNXScreenedRWKVModel) and set(variables) == {n for n, _ in model.named_parameters()}
+    again, _ = R.create_model_variables(3, cfg)
+    assert all(torch.equal(variables[n], again[n]) for n in variables)     # same seed, same initialisation
+    logits, _, _, _ = model(torch.zeros(2, 4, dtype=torch.int32), R.init_rwkv_state(2, cfg), R.init_screen_state(2, cfg.screening))
+    assert logits.shape == (2, 4, 97)
+
+
+def test_sharding_contract_and_local_wkv():
+    mesh = R.make_mesh(("data", "model"), (2, 4), world_size=8)
+    sh = R.NNXShardingConfig(mesh)
+    assert sh.activation(3, model_sharded=False) == ("data", None, None)
+    assert sh.activation(3, model_sharded=True) == ("data", None, "model")
+    assert sh.recurrent_state() == ("data", "model", None, None)
+    with pytest.raises(ValueError):
+        sh.activation(0, model_sharded=False)
+    with pytest.raises(ValueError):
+        sh.named("rows")
+    with pytest.raises(ValueError):
+        R.ShardingConfig(mesh, model_axis="tensor")
+    inputs = _wkv_inputs(T=5, H=4, N=4, seed=2)
+    y, sT = R.wkv7_sharded(*inputs, mesh=mesh)
+    # a rank that holds heads 2-3 of the same batch row gets exactly those heads of the full result
+    part = [t[:, :, 2:4].contiguous() for t in inputs[:6]] + [inputs[6][:, 2:4].contiguous()]
+    yp, sp = R.wkv7_sharded(*part, mesh=mesh)
+    assert torch.allclose(yp, y[:, :, 2:4], atol=1e-6) and torch.allclose(sp, sT[:, 2:4], atol=1e-6)
