@@ -744,7 +744,7 @@ class WkvGnFn(torch.autograd.Function):
 def wkv7_gn(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, n_heads, eps=64e-5, impl=None):
     """(GroupNorm(wkv7(...)) + bonus) * g and the final state; r, w, k, v, a, b are [B,T,H,N], g is [B,T,C]."""
     B, T, H, N = r.shape
-    fused = (WKV_GN_FUSED and WKV_IMPL == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64
+    fused = (WKV_GN_FUSED and (impl or WKV_IMPL) == "chunked" and T >= WKV_CHUNK_MIN_T and r.dtype == torch.bfloat16 and N == 64
              and r.is_cuda and g.dtype == torch.bfloat16)
     if fused:
         return WkvGnFn.apply(r, w, k, v, a, b, state0, g, ln_w, ln_b, r_k, eps)

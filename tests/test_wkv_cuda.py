@@ -228,3 +228,31 @@ def test_chunked_kernels_at_the_training_shape():
     for name, a, b in zip("r w k v a b s0".split(), got, want):
         rel = float((a.float() - b.float()).norm() / (b.float().norm() + 1e-9))
         assert rel < 1.5e-2, (name, rel)
+
+
+def test_backend_selection_on_the_gpu():
+    """The process-wide backend choice reaches both the plain WKV call and the fused WKV + GroupNorm call of the model;
+    the scan kernels, the chunked kernels and the PyTorch statement agree at bf16 level, and with gradients."""
+    from rwkv7m_b200.ops import backends
+
+    B, T, H, N = 2, 128, 2, 64
+    vecs, s0 = _inputs(B, T, H, N, torch.bfloat16, seed=11)
+    C = H * N
+    g = torch.randn(B, T, C, device="cuda").bfloat16()
+    ln_w, ln_b = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
+    r_k = torch.randn(H, N, device="cuda") * 0.1
+    outs = {}
+    try:
+        for name in ("chunked", "sequential", "reference"):
+            backends.set_wkv_backend(name)
+            leaves = [t.detach().clone().requires_grad_(True) for t in vecs]
+            y, sT = ops.wkv7(*leaves, s0)
+            o, sT2 = ops.wkv7_gn(*leaves, s0, g, ln_w, ln_b, r_k, H)
+            (y.float().sum() + o.float().pow(2).sum()).backward()
+            outs[name] = (y.float(), sT.float(), o.float(), leaves[3].grad.float())
+    finally:
+        backends.set_wkv_backend(None)
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-9))
+    for name in ("chunked", "sequential"):
+        for got, want in zip(outs[name], outs["reference"]):
+            assert rel(got, want) < 3e-2, (name, rel(got, want))
