@@ -627,3 +627,20 @@ def test_sharding_contract_and_local_wkv():
     part = [t[:, :, 2:4].contiguous() for t in inputs[:6]] + [inputs[6][:, 2:4].contiguous()]
     yp, sp = R.wkv7_sharded(*part, mesh=mesh)
     assert torch.allclose(yp, y[:, :, 2:4], atol=1e-6) and torch.allclose(sp, sT[:, 2:4], atol=1e-6)
+
+
+def test_every_console_script_resolves_and_the_reference_command_names_exist():
+    """Each command of the package's script table imports and is callable; the eleven command names of the reference
+    (pyproject.toml:23-34 there) are all in the table, so a shell script written for it keeps working."""
+    import importlib
+    import tomllib
+    from pathlib import Path
+
+    table = tomllib.loads((Path(__file__).resolve().parents[1] / "pyproject.toml").read_text())["project"]["scripts"]
+    for name, target in table.items():
+        module, func = target.split(":")
+        assert callable(getattr(importlib.import_module(module), func)), name
+    for name in ("rwkv7m-train-binidx", "rwkv7m-train-binidx-dp", "rwkv7m-audit-dp-run", "rwkv7m-make-binidx",
+                 "rwkv7m-bench-binidx", "rwkv7m-eval-binidx", "rwkv7m-generate", "rwkv7m-verify-upstream-rwkv7",
+                 "rwkv7m-plan-scale", "rwkv7m-verify-nnx-lifecycle", "rwkv7m-audit-nnx-model-parallel"):
+        assert name in table, name
