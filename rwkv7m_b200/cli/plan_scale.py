@@ -7,6 +7,7 @@ import argparse
 import json
 
 from ..config import MODEL_PRESET_NAMES, load_model_config, model_preset
+from ..parallel.environment import runtime_version_manifest
 from ..parallel.scaling import DTypePolicy, estimate_training_memory
 
 
@@ -16,20 +17,30 @@ def parse_args(argv=None):
     src.add_argument("--model-config")
     src.add_argument("--model-preset", choices=MODEL_PRESET_NAMES)
     p.add_argument("--model-axis-size", type=int, required=True)
-    p.add_argument("--dtype-policy", choices=["config", "stability", "memory"], default="config")
+    p.add_argument("--dtype-profile", "--dtype-policy", dest="dtype_profile", choices=["config", "stability", "memory"],
+                   default="config")
     p.add_argument("--optimizer-shards", type=int, default=1)
     p.add_argument("--tokens-per-device", type=int, default=0)
     return p.parse_args(argv)
 
 
-def main(argv=None):
-    args = parse_args(argv)
+def build_estimate(args):
     cfg = load_model_config(args.model_config) if args.model_config else model_preset(args.model_preset)
     policy = {"config": DTypePolicy.from_config(cfg), "stability": DTypePolicy.stability(),
-              "memory": DTypePolicy.memory()}[args.dtype_policy]
-    est = estimate_training_memory(cfg, policy, model_axis_size=args.model_axis_size,
-                                   optimizer_shards=args.optimizer_shards, tokens_per_device=args.tokens_per_device)
-    print(json.dumps(est.to_dict(), indent=2, sort_keys=True))
+              "memory": DTypePolicy.memory()}[args.dtype_profile]
+    return estimate_training_memory(cfg, policy, model_axis_size=args.model_axis_size,
+                                    optimizer_shards=args.optimizer_shards, tokens_per_device=args.tokens_per_device)
+
+
+def build_report(args):
+    """The printed document: the software environment next to the estimate, as the reference prints it."""
+    return {"environment": runtime_version_manifest(), "estimate": build_estimate(args).to_dict()}
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    est = build_estimate(args)
+    print(json.dumps({"environment": runtime_version_manifest(), "estimate": est.to_dict()}, indent=2, sort_keys=True))
     return est
 
 

@@ -37,3 +37,16 @@ def environment_manifest() -> dict:
 
     info["rwkv7m_b200"] = __version__
     return info
+
+
+def runtime_version_manifest() -> dict:
+    """The reference's name for the manifest (src/rwkv7m/distributed/environment.py:25-45): the same record, plus the
+    keys a reader of the reference's reports looks for (``packages``, ``process_count``, ``device_kinds``)."""
+    import torch
+
+    info = environment_manifest()
+    info["packages"] = {k: info[k] for k in ("torch", "numpy", "safetensors") if info.get(k) is not None}
+    dist = torch.distributed
+    info["process_count"] = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    info["device_kinds"] = sorted({d["name"] for d in info["devices"]}) or ["cpu"]
+    return info

@@ -128,3 +128,28 @@ def test_collective_ownership_and_counter():
         assert c["calls"]["all_reduce"] == 2 and c["bytes"]["all_reduce"] == 64
     finally:
         dist.destroy_process_group()
+
+
+def test_lifecycle_tool_accepts_the_reference_flags(tmp_path, capsys):
+    """``--mode`` / ``--checkpoint-dir`` / ``--width`` / ``--learning-rate`` / ``--seed`` as in the reference's tool
+    (src/rwkv7m/cli/verify_nnx_lifecycle.py:21-35), and its report keys."""
+    from rwkv7m_b200.cli import verify_lifecycle
+
+    d = str(tmp_path / "ref_flags")
+    base = ["--checkpoint-dir", d, "--width", "16", "--learning-rate", "0.002", "--seed", "3"]
+    assert verify_lifecycle.main(["--mode", "create"] + base) == 0
+    created = json.loads(capsys.readouterr().out)
+    assert verify_lifecycle.main(["--mode", "restore"] + base) == 0
+    restored = json.loads(capsys.readouterr().out)
+    for report in (created, restored):
+        assert {"mode", "loss", "optimizer_step", "mesh", "sharding_before", "sharding_after", "environment",
+                "checkpoint_dir"} <= set(report)
+    assert created["optimizer_step"] == 1 and restored["optimizer_step"] == 2
+    assert created["sharding_before"]["model/in_proj.weight"]["shape"] == [16, 16]
+    assert "optimizer/exp_avg/in_proj.weight" not in created["sharding_before"]      # no moments before the first step
+    assert "optimizer/exp_avg/in_proj.weight" in restored["sharding_before"]         # the restore brought them back
+    assert restored["ok"] and restored["train_state"]["ok"]
+    with pytest.raises(SystemExit):
+        verify_lifecycle.parse_args(["--checkpoint-dir", d])                          # no mode
+    with pytest.raises(ValueError, match="width"):
+        verify_lifecycle.main(["--mode", "restore", "--checkpoint-dir", d, "--width", "8"])

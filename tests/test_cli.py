@@ -86,7 +86,11 @@ def test_plan_scale_outputs_exact_counts(capsys):
     est = plan_scale.main(["--model-preset", "0.185b", "--model-axis-size", "1", "--optimizer-shards", "8"])
     assert est.parameter_summary.total == 184_985_222
     assert est.optimizer_state_bytes == -(-184_985_222 * 2 * 4 // 8)
-    assert "limitations" in json.loads(capsys.readouterr().out)
+    report = json.loads(capsys.readouterr().out)
+    assert "limitations" in report["estimate"] and "torch" in json.dumps(report["environment"])
+    memory = plan_scale.build_report(plan_scale.parse_args(["--model-preset", "0.185b", "--model-axis-size", "2",
+                                                            "--dtype-profile", "stability"]))
+    assert memory["estimate"]["dtype_policy"] != report["estimate"]["dtype_policy"]
 
 
 def test_distributed_trainer_single_process_artifacts(tiny_binidx, tmp_path):

@@ -1,5 +1,6 @@
 """Two-rank CPU (gloo) runs: data parallelism and tensor parallelism reproduce the single-process step."""
 
+import json
 import os
 import socket
 
@@ -211,3 +212,39 @@ def test_tensor_parallel_decode_matches_single_process(tmp_path, vocab_parallel)
     got = torch.load(out)
     assert got.shape == ref.shape == (4, 4, 256)
     assert float((got - ref).abs().max()) < 1e-4
+
+
+def _probe_worker(rank, world, port, directory, mode, out):
+    _init(rank, world, port)
+    from rwkv7m_b200.parallel.lifecycle import run_sharding_probe
+
+    report = run_sharding_probe(directory, mode, width=8 if mode == "create" else None)
+    if rank == 0:
+        with open(out, "w") as f:
+            json.dump(report, f)
+    _leave()
+
+
+def test_sharded_lifecycle_probe_across_process_counts(tmp_path):
+    """Two processes create (each holds half of the columns / rows and writes its own shard file); the restore reproduces
+    the recorded next loss with two processes (every process reads its own file) and with one (slices cut again from
+    both files), and the two-process model is the one-process model (same loss at the first step)."""
+    from rwkv7m_b200.parallel.lifecycle import run_sharding_probe
+
+    d = str(tmp_path / "probe")
+    out = str(tmp_path / "r.pt")
+    mp.spawn(_probe_worker, args=(2, _free_port(), d, "create", out), nprocs=2, join=True)
+    created = json.load(open(out))
+    assert created["mesh"]["shape"] == {"data": 1, "model": 2} and created["optimizer_step"] == 1
+    row = created["sharding_after"]["optimizer/exp_avg/in_proj.weight"]
+    assert row["shape"] == [8, 8] and row["local_shape"] == [4, 8] and row["logical_axes"] == ["model", None]
+    assert sorted(p.name for p in (tmp_path / "probe").iterdir()) == [
+        "shard-00000-of-00002.safetensors", "shard-00001-of-00002.safetensors", "sharding_probe.json"]
+    mp.spawn(_probe_worker, args=(2, _free_port(), d, "restore", out), nprocs=2, join=True)
+    two = json.load(open(out))
+    one = run_sharding_probe(d, "restore")
+    for r in (two, one):
+        assert r["ok"] and r["optimizer_step"] == 2
+        assert r["loss"] == pytest.approx(created["expected_next_loss"], rel=1e-5)
+    single = run_sharding_probe(str(tmp_path / "single"), "create", width=8)
+    assert single["loss"] == pytest.approx(created["loss"], rel=1e-5)
