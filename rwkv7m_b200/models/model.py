@@ -37,7 +37,17 @@ class ScreenedRWKVLayer(nn.Module):
 
     def forward(self, x, v_first, rwkv_state, screen_state, phase):
         h_base, v_first, new_rwkv = self.block(x, v_first, rwkv_state)
-        if self.has_screening:
+        tp = getattr(self.block, "tp", None)
+        if self.has_screening and tp is not None and not tp.replicated_sequence:
+            # Tensor parallelism shards the residual stream over time, and the memory is a recurrence over the whole
+            # sequence: every rank gathers the layer input and the block output, runs the scan on the full sequence with
+            # its (replicated) parameters and keeps its own time slice of the result.  The bank state after the last
+            # token is the same on every rank.  In backward the slice hands the scan a cotangent that is zero outside
+            # this rank's tokens, the gathers sum the input cotangents over the group, and the parameter gradients are
+            # summed with those of the other replicated leaves.
+            h_full, new_screen, stats = self.screening(tp.gather_seq(x), tp.gather_seq(h_base), screen_state, phase=phase)
+            h = tp.local_time_slice(h_full)
+        elif self.has_screening:
             h, new_screen, stats = self.screening(x, h_base, screen_state, phase=phase)
         else:
             h, new_screen, stats = h_base, screen_state, {}
@@ -82,8 +92,6 @@ class ScreenedRWKVModel(nn.Module):
         phase = normalize_phase(phase)
         tp = getattr(self, "tp", None)
         if tp is not None:
-            if cfg.screening_active:
-                raise NotImplementedError("screening memory is not sharded yet: run screened models data-parallel")
             tp.set_sequence_length(int(input_ids.shape[1]))
             input_ids = tp.local_time_slice(input_ids)  # the residual stream is sharded over time (when T divides)
         # parameter-sharding engine (ZeRO-3): told before a unit's weights are used; marks on the residual stream tell it

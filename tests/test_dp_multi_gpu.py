@@ -72,6 +72,25 @@ def test_tensor_parallel_matches_single_gpu(world):
         assert r["gemm_rs_max_err"] < 0.02 * r["gemm_rs_scale"] + 0.05, res
 
 
+def test_tensor_parallel_with_screening_memory_matches_single_gpu():
+    """A screened layer (read / write phase, carried bank) under tensor parallelism, with the sequence collectives on
+    NCCL and on this framework's peer-memory kernels: parameters after the first update (the memory's own included),
+    both losses and the carried bank follow the single-GPU run at bf16 level."""
+    _need(2)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29537", str(Path(__file__).with_name("tp_screening_worker.py"))]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    for key in ("nccl", "fused"):
+        r = res[key]
+        assert r["rel_l2"] < 3e-3 and r["screening_rel_l2"] < 2e-2, res
+        for a, b, tol in zip(r["loss_ref"], r["loss_tp"], (1e-2, 2e-2)):
+            assert abs(a - b) < tol * abs(a), res
+        assert r["slots_err"] < 0.03 * r["slots_scale"] + 0.03, res
+    assert res["fused"]["error_code"] == 0, res
+
+
 @pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("accum", [1, 2])
 def test_zero3_matches_allreduce(accum, world):

@@ -248,3 +248,90 @@ def test_sharded_lifecycle_probe_across_process_counts(tmp_path):
         assert r["loss"] == pytest.approx(created["expected_next_loss"], rel=1e-5)
     single = run_sharding_probe(str(tmp_path / "single"), "create", width=8)
     assert single["loss"] == pytest.approx(created["loss"], rel=1e-5)
+
+
+def _screened_cfg():
+    cfg = R.tiny_config(use_screening=True)
+    cfg.warmup_steps = 0
+    cfg.lr_init = 1e-3
+    return cfg
+
+
+def _screened_single(steps=2):
+    torch.manual_seed(0)
+    rt, ts = R.create_train_runtime(3, _screened_cfg(), batch_size=4, total_steps=20)
+    _perturb_screening(ts.model)
+    batch = _global_batch()
+    losses = []
+    for _ in range(steps):
+        ts, m = R.train_batch(ts, batch, rt, phase="read_write", carry_state=True)
+        losses.append(float(m["loss"]))
+    return {n: p.detach().clone() for n, p in ts.model.named_parameters()}, losses, rt
+
+
+def _perturb_screening(model):
+    """Move the memory's parameters off their zero / identity start so that its read and write paths carry gradient."""
+    g = torch.Generator().manual_seed(11)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if ".screening." in name:
+                p.add_(torch.randn(p.shape, generator=g).to(p) * 0.1)
+
+
+def _tp_screened_worker(rank, world, port, out):
+    _init(rank, world, port)
+    from rwkv7m_b200.parallel.tp import TensorParallel
+
+    tp = TensorParallel.from_group()
+    rt, ts = R.create_train_runtime(3, _screened_cfg(), batch_size=4, total_steps=20, tp=tp)
+    _perturb_screening(ts.model)
+    batch = _global_batch()
+    losses = []
+    for _ in range(2):
+        ts, m = R.train_batch(ts, batch, rt, phase="read_write", carry_state=True)
+        losses.append(float(m["loss"]))
+    full = tp.gather_full_parameters(ts.model)
+    slots = rt.screen_state.layers[0].slots.clone() if rt.screen_state.layers else None
+    if rank == 0:
+        torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "slots": slots}, out)
+    _leave()
+
+
+def test_tensor_parallel_with_screening_memory_matches_single_process(tmp_path):
+    """Screened layers under tensor parallelism: each rank scans the gathered sequence with replicated memory parameters
+    and keeps its time slice.  Losses, every parameter after two read/write steps (memory parameters included) and the
+    carried bank agree with one process."""
+    ref, ref_losses, rt = _screened_single()
+    assert any(".screening." in n for n in ref)
+    out = str(tmp_path / "tps.pt")
+    mp.spawn(_tp_screened_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["losses"] == pytest.approx(ref_losses, rel=1e-4)
+    _compare(ref, res["params"], 5e-5)
+    moved = max(float((ref[n]).abs().max()) for n in ref if ".screening." in n)
+    assert moved > 0
+    if res["slots"] is not None and rt.screen_state.layers:
+        assert torch.allclose(res["slots"], rt.screen_state.layers[0].slots, atol=1e-5)
+
+
+def test_model_parallel_audit_on_a_data_by_model_mesh_with_screening(tmp_path):
+    """The audit tool with the reference's flags (src/rwkv7m/cli/audit_nnx_model_parallel.py:27-52): four CPU processes
+    as a 2 x 2 ``data x model`` mesh, a screened layer in the read / write phase; the report names both axes, a
+    replicated bank, both kinds of sharded kernels and collectives in forward and in the step."""
+    import subprocess
+    import sys
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), "-m", "rwkv7m_b200.cli.audit_model_parallel", "--cpu", "--model-axis-size", "2",
+           "--screening", "--write-screening", "--vocab-parallel"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    text = out.stdout[out.stdout.index("{"):]
+    rep = json.loads(text[: text.rindex("}") + 1])
+    assert rep["mesh"]["shape"] == {"data": 2, "model": 2}
+    assert rep["states"]["screening_slots"]["layout"] == "replicated"
+    assert rep["contract"] == {"has_row_parallel_kernel": True, "has_column_parallel_kernel": True,
+                               "model_parallel_exercised": True}
+    assert rep["forward"]["finite"] and rep["train_step"]["finite"] and rep["train_step"]["optimizer_step"] == 1
+    assert rep["forward"]["collectives"]["calls"] and rep["train_step"]["collectives"]["calls"]
+    assert any(".screening." in n and v["layout"] == "replicated" for n, v in rep["parameters"].items())
