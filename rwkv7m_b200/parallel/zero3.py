@@ -100,8 +100,10 @@ class Zero3Engine:
         flat = opt.flat
         if flat.compute is None or flat.master.dtype != torch.float32 or flat.grad.dtype != torch.float32:
             raise ValueError("ZeRO-3 expects fp32 master parameters, fp32 gradient accumulation and a bf16 compute copy")
-        if getattr(model, "tp", None) is not None or model.config.remat_blocks or model.remat_layer_count:
-            raise ValueError("ZeRO-3 is not combined with tensor parallelism or layer recompute")
+        if getattr(model, "tp", None) is not None:
+            raise ValueError("ZeRO-3 is not combined with tensor parallelism")
+        # Layer recompute needs nothing from the engine: the recomputation of a layer runs inside that layer's backward,
+        # after the "leave" mark has made the unit's weights resident and before the "enter" mark queues its reduction.
         dev = flat.master.device
         self.device = dev
         enable = getattr(symm, "enable_symm_mem_for_group", None)

@@ -91,15 +91,16 @@ def test_tensor_parallel_with_screening_memory_matches_single_gpu():
     assert res["fused"]["error_code"] == 0, res
 
 
-@pytest.mark.parametrize("world", [2, 8])
-@pytest.mark.parametrize("accum", [1, 2])
-def test_zero3_matches_allreduce(accum, world):
+@pytest.mark.parametrize("world,accum,remat", [(2, 1, 0), (2, 2, 0), (2, 1, 2), (8, 1, 0), (8, 2, 0)])
+def test_zero3_matches_allreduce(accum, world, remat):
+    """``remat``: the first two of the four layers are recomputed in backward (the recomputation runs between the marks
+    that make the unit's weights resident and queue its gradient reduction)."""
     import os
 
     _need(world)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29535", str(Path(__file__).with_name("zero3_worker.py"))]
-    env = dict(os.environ, ZERO3_ACCUM=str(accum), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, ZERO3_ACCUM=str(accum), ZERO3_REMAT=str(remat), NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])

@@ -32,6 +32,7 @@ def main():
     def run(mode):
         rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=50, device=dev, shard_multiple=world * 8)
         names = [n for n, _ in ts.model.named_parameters()]
+        ts.model.remat_layer_count = int(os.environ.get("ZERO3_REMAT", "0"))   # recompute the first k layers in backward
         if mode == "zero3":
             DataParallelTrainer(ts, mode="allreduce").broadcast_parameters()
             engine = Zero3Engine(ts)
