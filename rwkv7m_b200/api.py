@@ -77,11 +77,22 @@ def _no_screen(config):
     return scr
 
 
-def create_runtime(rng_key, config, *, batch_size: int = 1, device=None, tp=None) -> RWKV7MRuntime:
-    """``tp`` (a :class:`rwkv7m_b200.parallel.tp.TensorParallel`) shards the model over that group for serving: prompts
-    whose length divides by the group size are prefilled sequence-sharded, T = 1 decode steps run with the token
-    replicated and one all-reduce per row-parallel projection."""
+def _tp_from_sharding(sharding, config, tp):
+    """``sharding`` (the reference's keyword, src/rwkv7m/api.py:38-91): a ``ShardingConfig`` whose model axis becomes the
+    tensor-parallel group of this process.  An explicit ``tp`` wins."""
+    if sharding is None or tp is not None:
+        return tp, None
+    from .parallel.mesh import tensor_parallel_from_sharding
+
+    return tensor_parallel_from_sharding(sharding, vocab_parallel=bool(getattr(config, "vocab_parallel", False)))
+
+
+def create_runtime(rng_key, config, *, batch_size: int = 1, sharding=None, device=None, tp=None) -> RWKV7MRuntime:
+    """``tp`` (a :class:`rwkv7m_b200.parallel.tp.TensorParallel`), or a ``sharding`` whose mesh has a model axis, shards
+    the model over that group for serving: prompts whose length divides by the group size are prefilled
+    sequence-sharded, T = 1 decode steps run with the token replicated and one all-reduce per row-parallel projection."""
     config = load_model_config(config)
+    tp, _ = _tp_from_sharding(sharding, config, tp)
     model = initialize_model(_seed(rng_key), config, device=_default_device(device))
     if tp is not None:
         tp.shard_model(model)
@@ -106,9 +117,12 @@ def _attach_inference_weights(model):
             p._compute = p.detach().to(torch.bfloat16)
 
 
-def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, device=None,
+def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int = 10000, sharding=None, device=None,
                          shard_multiple: int = 1, buffer_allocator=None, tp=None):
+    """``sharding``: a ``ShardingConfig``; its model axis (if larger than one) makes this a tensor-parallel train state whose
+    step also sums gradients over the data axis.  ``batch_size`` is the batch of one model-parallel group."""
     config = load_model_config(config)
+    tp, data_group = _tp_from_sharding(sharding, config, tp)
     train_state = initialize_train_state(
         _seed(rng_key) + 1, config, total_steps=total_steps, device=_default_device(device),
         shard_multiple=shard_multiple, buffer_allocator=buffer_allocator, tp=tp,
@@ -118,7 +132,7 @@ def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int =
         from .parallel.tp import TensorParallelTrainer
 
         runtime.rwkv_state = runtime.initial_rwkv_state = tp.init_rwkv_state(batch_size, config, device=runtime.device)
-        TensorParallelTrainer(train_state, tp)
+        TensorParallelTrainer(train_state, tp, data_group=data_group)
     return runtime, train_state
 
 

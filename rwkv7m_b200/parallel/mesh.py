@@ -142,3 +142,33 @@ class ShardingConfig:
     def recurrent_state(self):
         """Spec of the [batch, heads, N, N] WKV state: heads follow the model axis."""
         return self.named(self.data_axis, self.model_axis, None, None)
+
+
+_GROUP_CACHE: dict = {}
+
+
+def mesh_groups(mesh: Mesh):
+    """``(data_group, model_group)`` of this process for ``mesh``, created once per mesh shape (group creation is a
+    collective on every process, so all of them must ask for the same meshes in the same order)."""
+    key = (mesh.data_size, mesh.model_size)
+    if key not in _GROUP_CACHE:
+        _GROUP_CACHE[key] = new_subgroups(mesh)
+    return _GROUP_CACHE[key]
+
+
+def tensor_parallel_from_sharding(sharding: "ShardingConfig", *, vocab_parallel: bool = False):
+    """What a ``ShardingConfig`` means for this process: ``(tp, data_group)``.  ``tp`` is the tensor-parallel context over
+    the mesh's model axis (None when that axis has one process or no process group is up), ``data_group`` the processes
+    that hold the same shard in the other model-parallel groups (None when the data axis has one process)."""
+    mesh = sharding.mesh
+    if not (dist.is_available() and dist.is_initialized()) or mesh.size == 1:
+        return None, None
+    if mesh.size != dist.get_world_size():
+        raise ValueError(f"mesh {mesh.data_size}x{mesh.model_size} does not match the {dist.get_world_size()} processes")
+    data_group, model_group = mesh_groups(mesh)
+    tp = None
+    if mesh.model_size > 1:
+        from .tp import TensorParallel
+
+        tp = TensorParallel.from_group(model_group, vocab_parallel=vocab_parallel)
+    return tp, (data_group if mesh.data_size > 1 else None)

@@ -335,3 +335,45 @@ def test_model_parallel_audit_on_a_data_by_model_mesh_with_screening(tmp_path):
     assert rep["forward"]["finite"] and rep["train_step"]["finite"] and rep["train_step"]["optimizer_step"] == 1
     assert rep["forward"]["collectives"]["calls"] and rep["train_step"]["collectives"]["calls"]
     assert any(".screening." in n and v["layout"] == "replicated" for n, v in rep["parameters"].items())
+
+
+def _sharding_keyword_worker(rank, world, port, out):
+    _init(rank, world, port)
+    from rwkv7m_b200.parallel.mesh import ShardingConfig, make_mesh
+
+    sharding = ShardingConfig(make_mesh(("data", "model"), (1, 2)))
+    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=4, total_steps=20, sharding=sharding)
+    batch = _global_batch()
+    losses = []
+    for _ in range(2):
+        ts, m = R.train_batch(ts, batch, rt)
+        losses.append(float(m["loss"]))
+    full = ts.model.tp.gather_full_parameters(ts.model)
+    serving = R.create_runtime(3, _cfg(), batch_size=4, sharding=sharding)
+    logits, _ = R.infer_prefill(serving, batch["input_ids"])
+    if rank == 0:
+        torch.save({"params": {n: v.clone() for n, v in full.items()}, "losses": losses, "logits": logits,
+                    "heads": int(ts.model.layers[0].block.att.receptance.weight.shape[0])}, out)
+    _leave()
+
+
+def test_sharding_keyword_builds_the_tensor_parallel_runtime(tmp_path):
+    """``create_train_runtime(..., sharding=ShardingConfig(mesh))`` and ``create_runtime(..., sharding=...)``, the
+    reference's way to ask for a model-parallel runtime (src/rwkv7m/api.py:38-91): a 1 x 2 mesh gives each process half of
+    the projections, the two steps match one process, and the serving runtime prefills through the same shards."""
+    ref, ref_losses = _single_process_params()
+    out = str(tmp_path / "sk.pt")
+    mp.spawn(_sharding_keyword_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["losses"] == pytest.approx(ref_losses, rel=1e-4)
+    _compare(ref, res["params"], 5e-5)
+    assert res["heads"] == 32 and res["logits"].shape == (4, 8, 256)    # half of the 64 receptance output rows
+    rt = R.create_runtime(3, _cfg(), batch_size=4)
+    want, _ = R.infer_prefill(rt, _global_batch()["input_ids"])
+    assert torch.allclose(res["logits"], want, atol=1e-4)
+    # one process: the keyword is accepted and changes nothing
+    from rwkv7m_b200.parallel.mesh import ShardingConfig, make_mesh
+
+    alone = R.create_runtime(3, _cfg(), batch_size=4, sharding=ShardingConfig(make_mesh(("data", "model"), (1, 1), world_size=1)))
+    got, _ = R.infer_prefill(alone, _global_batch()["input_ids"])
+    assert torch.equal(got, want)
