@@ -142,3 +142,47 @@ def flatten(tree: dict, prefix: str = "") -> dict:
         else:
             out[name] = value
     return out
+
+
+def _flat_portable(params: dict) -> dict:
+    """A nested tree or a ``/``-joined mapping as the flat ``a/b/c -> tensor`` mapping (a top-level ``params`` is unwrapped)."""
+    if set(params) == {"params"} and isinstance(params["params"], dict):
+        params = params["params"]
+    return flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
+
+
+def assert_portable_parameter_contract(model, params: dict) -> None:
+    """Path and shape parity between a portable parameter tree and ``model``, changing neither (the reference's check
+    between its two model implementations, src/rwkv7m/model/nnx_conversion.py:23-41,76-79): every portable name the model
+    defines must be present with the shape the model would export, and nothing else."""
+    flat = _flat_portable(params)
+    own = {}
+    named = dict(model.named_parameters())
+    for internal, portable, tf in portable_entries(model.config):
+        p = named[internal]
+        shape = tuple(p.shape)
+        if tf == "T":
+            shape = shape[::-1]
+        elif tf == "vec3":
+            shape = (1, 1, p.numel())
+        elif tf.startswith("mix:"):
+            shape = (1, 1, p.shape[-1]) if len(tuple(torch.as_tensor(flat.get(portable, p[0])).shape)) == 3 else tuple(p[0].shape)
+        own[portable] = shape
+    missing, extra = sorted(set(own) - set(flat)), sorted(set(flat) - set(own))
+    if missing or extra:
+        raise ValueError(f"parameter paths differ: missing_in_tree={missing}, extra_in_tree={extra}")
+    bad = [f"{k}: tree {tuple(torch.as_tensor(flat[k]).shape)}, model {own[k]}" for k in sorted(own)
+           if tuple(torch.as_tensor(flat[k]).shape) != own[k]]
+    if bad:
+        raise ValueError("parameter shapes differ: " + "; ".join(bad))
+
+
+def load_portable_params(model, params: dict):
+    """Load a complete portable tree into ``model`` in place; partial trees are refused."""
+    from_portable(model, _flat_portable(params), strict=True)
+    return model
+
+
+def portable_params(model) -> dict:
+    """The model's parameters as the nested portable tree."""
+    return nest(to_portable(model))

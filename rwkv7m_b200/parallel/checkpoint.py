@@ -119,8 +119,22 @@ def _gather_moments_into_optimizer(train_state, process_info):
     return True
 
 
-def save_data_parallel_checkpoint(checkpoint_dir, train_state, config, process_info, *, backend="single",
-                                  rng_key=None, dataset_position=None, metadata=None, runtime_state=None):
+def save_data_parallel_checkpoint(*args, **kwargs):
+    """Two call forms.  ``(checkpoint_dir, train_state, config, process_info, *, backend=..., ...)`` writes into the
+    directory given.  ``(output_dir, step, dist_objects, config, process_info, ...)`` is the reference's
+    (src/rwkv7m/distributed/checkpoint.py:208-302): the directory is ``output_dir/ckpt-%08d``, the train state is taken
+    from the placed objects, and ``output_dir=None`` saves nothing."""
+    if len(args) >= 2 and isinstance(args[1], int) and not isinstance(args[1], bool):
+        output_dir, step, objects = args[0], args[1], args[2]
+        if output_dir is None:
+            return None
+        train_state = getattr(objects, "train_state", objects)
+        return _save_checkpoint_dir(checkpoint_path(output_dir, step), train_state, *args[3:], **kwargs)
+    return _save_checkpoint_dir(*args, **kwargs)
+
+
+def _save_checkpoint_dir(checkpoint_dir, train_state, config, process_info, *, backend="single",
+                         rng_key=None, dataset_position=None, metadata=None, runtime_state=None):
     backend = normalize_backend(backend)
     rank, world = _world(process_info)
     checkpoint_dir = Path(checkpoint_dir)
@@ -308,3 +322,39 @@ def rotate_checkpoints(output_dir, keep_last, process_info, *, protected_paths=N
     for p in doomed:
         shutil.rmtree(p)
     return doomed
+
+
+# ---- the reference's names for the sharded backend --------------------------------------------------------------------
+def _info(process_info):
+    if process_info is not None:
+        return process_info
+    from .mesh import process_info as current
+
+    return current()
+
+
+def save_orbax_train_state(checkpoint_dir, train_state, *, force=True, process_info=None, config=None):
+    """Every process writes its part of the train state (the ``sharded`` backend: the optimizer moments that this rank
+    owns; rank 0 adds the model files and ``checkpoint.json``).  Named after the reference's sharded writer
+    (src/rwkv7m/distributed/checkpoint.py:146-163); ``force`` is accepted, existing files are always replaced."""
+    return _save_checkpoint_dir(checkpoint_dir, train_state, config if config is not None else train_state.config,
+                                _info(process_info), backend="sharded")
+
+
+def load_orbax_train_state(checkpoint_dir, train_state_template, *, process_info=None):
+    """Restore what :func:`save_orbax_train_state` wrote into ``train_state_template`` (same process count)."""
+    return restore_distributed_train_state(checkpoint_dir, train_state_template, _info(process_info))[0]
+
+
+def save_orbax_runtime_state(checkpoint_dir, runtime_state, *, force=True, process_info=None):
+    """This process's carried recurrent and memory state as ``runtime_state.rank<r>.safetensors``."""
+    checkpoint_dir = Path(checkpoint_dir)
+    checkpoint_dir.mkdir(parents=True, exist_ok=True)
+    rank, _ = _world(_info(process_info))
+    path = checkpoint_dir / f"runtime_state.rank{rank:05d}.safetensors"
+    save_runtime_state(path, runtime_state)
+    return path
+
+
+def load_orbax_runtime_state(checkpoint_dir, runtime_state_template, *, process_info=None):
+    return restore_distributed_runtime_state(checkpoint_dir, runtime_state_template, _info(process_info))

@@ -37,9 +37,52 @@ OWNERSHIP = (
 _HLO_KINDS = ("all-reduce", "all-gather", "all-to-all", "collective-permute", "reduce-scatter")
 
 
-def audit_collectives(text: str) -> dict:
+class CollectiveAudit(dict):
+    """Counts per collective kind; a mapping (``audit["all-reduce"]``) with the reference's record interface on top
+    (``counts``, ``total``, ``to_dict()``; src/rwkv7m/distributed/collectives.py:19-29)."""
+
+    @property
+    def counts(self) -> dict:
+        return dict(self)
+
+    @property
+    def total(self) -> int:
+        return sum(self.values())
+
+    def to_dict(self) -> dict:
+        return {"counts": dict(self), "total": self.total}
+
+
+def audit_collectives(text: str) -> CollectiveAudit:
     """Count collective op names in a textual program dump (kept for parity with HLO-based audits)."""
-    return {kind: len(re.findall(rf"\b{re.escape(kind)}(?:-start)?\b", text)) for kind in _HLO_KINDS}
+    return CollectiveAudit({kind: len(re.findall(rf"\b{re.escape(kind)}(?:-start)?\b", text)) for kind in _HLO_KINDS})
+
+
+def compiler_ir_text(program, *, dialect: str = "hlo") -> str:
+    """Text of a program to audit.  Accepts a string, an object with ``as_text()`` / ``compiler_ir()`` (a lowered or
+    compiled computation of a tracing compiler), or the record of :func:`count_collectives`, whose calls are written one
+    per line under their HLO names so that the same text audit reads both."""
+    if isinstance(program, str):
+        return program
+    if isinstance(program, dict) and "calls" in program:
+        names = {"all_reduce": "all-reduce", "all_gather": "all-gather", "all_gather_into_tensor": "all-gather",
+                 "reduce_scatter_tensor": "reduce-scatter", "all_to_all_single": "all-to-all", "broadcast": "broadcast"}
+        lines = []
+        for call, n in sorted(program["calls"].items()):
+            lines += [f"%c = {names.get(call, call)}(%x)"] * int(n)
+        return "\n".join(lines)
+    if hasattr(program, "compiler_ir"):
+        ir = program.compiler_ir(dialect=dialect)
+        as_hlo_text = getattr(ir, "as_hlo_text", None)
+        return as_hlo_text() if as_hlo_text is not None else str(ir)
+    as_text = getattr(program, "as_text", None)
+    if as_text is None:
+        raise TypeError("object exposes neither compiler_ir() nor as_text()")
+    return as_text()
+
+
+def audit_lowered_collectives(program, *, dialect: str = "hlo") -> CollectiveAudit:
+    return audit_collectives(compiler_ir_text(program, dialect=dialect))
 
 
 def ownership_table(parallelism: str | None = None) -> list:

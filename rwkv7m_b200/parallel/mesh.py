@@ -71,8 +71,19 @@ class Mesh:
         return [d * self.model_size + m for d in range(self.data_size)]
 
 
-def make_mesh(axis_names=("data", "model"), axis_sizes=None, world_size: int | None = None) -> Mesh:
-    """``axis_sizes`` may leave one axis as -1 to absorb the remaining ranks."""
+def make_mesh(axis_names=("data", "model"), axis_sizes=None, world_size: int | None = None, *, devices=None,
+              axis_types=None) -> Mesh:
+    """``axis_sizes`` may leave one axis as -1 to absorb the remaining ranks.  ``devices`` (a list; only its length is
+    used: one process drives one GPU) and ``axis_types`` are accepted for call compatibility with the reference
+    (src/rwkv7m/distributed/mesh.py:50-88)."""
+    if isinstance(axis_names, str):
+        axis_names = (axis_names,)
+    if not tuple(axis_names):
+        raise ValueError("axis_names must not be empty")
+    if devices is not None and world_size is None:
+        world_size = len(list(devices))
+    if axis_sizes is not None and len(tuple(axis_sizes)) != len(tuple(axis_names)):
+        raise ValueError("axis_sizes must have the same length as axis_names")
     world = world_size if world_size is not None else process_info()["process_count"]
     names = tuple(axis_names)
     if set(names) - {"data", "model"}:
@@ -172,3 +183,24 @@ def tensor_parallel_from_sharding(sharding: "ShardingConfig", *, vocab_parallel:
 
         tp = TensorParallel.from_group(model_group, vocab_parallel=vocab_parallel)
     return tp, (data_group if mesh.data_size > 1 else None)
+
+
+def make_1d_mesh(axis_name: str = "data", devices=None) -> Mesh:
+    """Every process along one axis."""
+    return make_mesh((axis_name,), devices=devices)
+
+
+def initialize_jax_distributed(*, coordinator_address=None, num_processes=None, process_id=None, local_device_ids=None):
+    """The reference's start-up call (src/rwkv7m/distributed/mesh.py:17-43) under its own name: the three values, when
+    given, are what ``torch.distributed`` reads as MASTER_ADDR:MASTER_PORT, WORLD_SIZE and RANK; without them the
+    launcher's environment decides, and a lone process stays un-initialised."""
+    if coordinator_address is not None:
+        host, _, port = str(coordinator_address).rpartition(":")
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = (host or "127.0.0.1"), (port or "29500")
+    if num_processes is not None:
+        os.environ["WORLD_SIZE"] = str(int(num_processes))
+    if process_id is not None:
+        os.environ["RANK"] = str(int(process_id))
+    if local_device_ids is not None and len(list(local_device_ids)) > 0:
+        os.environ["LOCAL_RANK"] = str(int(list(local_device_ids)[0]))
+    return initialize_distributed()

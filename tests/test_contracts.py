@@ -644,3 +644,107 @@ def test_every_console_script_resolves_and_the_reference_command_names_exist():
                  "rwkv7m-bench-binidx", "rwkv7m-eval-binidx", "rwkv7m-generate", "rwkv7m-verify-upstream-rwkv7",
                  "rwkv7m-plan-scale", "rwkv7m-verify-nnx-lifecycle", "rwkv7m-audit-nnx-model-parallel"):
         assert name in table, name
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# subpackage surfaces under the reference's names
+# ---------------------------------------------------------------------------------------------------------------------
+_REFERENCE_SUBPACKAGE_NAMES = {
+    "rwkv7m_b200.models": """LayerRWKVState LayerScreenState ModelScreenState init_screen_state init_rwkv_state ScreeningConfig
+        normalize_phase ModelConfig RWKV7Config wkv7 wkv7_reference wkv7_sharded NNXShardingConfig NNXRWKV7Block
+        NNXRWKV7ChannelMix NNXRWKV7TimeMix NNXScreenedRWKVLayer NNXScreenedRWKVModel NNXStateLevelScreening
+        initialize_nnx_model assert_nnx_linen_parameter_contract load_linen_params_into_nnx nnx_params_to_linen
+        MODEL_PRESET_NAMES MODEL_PRESET_PARAMETER_COUNTS MODEL_PRESET_RECOMMENDED_MODEL_AXIS_SIZES
+        canonical_model_preset_name model_preset""",
+    "rwkv7m_b200.train": """build_train_state compute_aux_losses run_toy_training NNXTrainState create_nnx_train_state
+        initialize_nnx_train_state nnx_train_step train_step TrainState create_optimizer generate_toy_batch""",
+    "rwkv7m_b200.data": """MMapIndexedDataset MMapIndexedDatasetBuilder BinIdxBatchDataset BinIdxConfig
+        create_binidx_dataset find_magic_prime is_prime data_file_path index_file_path""",
+    "rwkv7m_b200.ops": """WKVBackend WKVFFIBackend available_wkv_backends register_wkv_ffi_backend resolve_wkv_backend
+        unregister_wkv_ffi_backend""",
+    "rwkv7m_b200.parallel": """BatchLayout HostBinIdxDataset compute_batch_layout create_host_binidx_dataset
+        iter_prefetched_global_batches DistributedRunAuditIssue DistributedRunAuditReport audit_distributed_run
+        audit_report_to_dict DistributedCheckpointPayload checkpoint_path list_checkpoint_dirs
+        load_distributed_checkpoint_metadata load_orbax_train_state load_orbax_runtime_state
+        restore_distributed_train_state restore_distributed_runtime_state rotate_checkpoints save_data_parallel_checkpoint
+        save_orbax_train_state save_orbax_runtime_state aggregate_metrics mean_metric_dict metrics_to_host_dict
+        write_metric_record runtime_version_manifest CollectiveAudit audit_collectives audit_lowered_collectives
+        compiler_ir_text DTypePolicy ParameterSummary TrainingMemoryEstimate abstract_parameter_summary
+        estimate_training_memory NNXShardingProbe initialize_nnx_probe nnx_state_sharding_summary
+        restore_nnx_probe_checkpoint save_nnx_probe_checkpoint train_nnx_probe_step mesh_axis_size
+        parameter_partition_summary parameter_partition_spec parameter_sharding place_parameter_tree
+        initialize_jax_distributed make_1d_mesh make_mesh process_info axis_sharding data_parallel_sharding
+        model_parallel_sharding mesh_has_axis replicated_sharding put_to_devices put_tree_auto_model_parallel
+        local_data_to_global_array host_batch_to_global_arrays DistributedTrainObjects place_train_objects
+        replicate_train_objects train_batch_data_parallel train_global_batch_data_parallel evaluate_batch_data_parallel
+        evaluate_batch_data_parallel_with_state evaluate_global_batch_data_parallel
+        evaluate_global_batch_data_parallel_with_state""",
+}
+
+
+@pytest.mark.parametrize("module", sorted(_REFERENCE_SUBPACKAGE_NAMES))
+def test_subpackages_export_the_reference_names(module):
+    """``from rwkv7m.<sub> import X`` of the reference reads ``from rwkv7m_b200.<sub> import X`` here (model -> models,
+    distributed -> parallel, kernels -> ops)."""
+    import importlib
+
+    mod = importlib.import_module(module)
+    missing = [n for n in _REFERENCE_SUBPACKAGE_NAMES[module].split() if not hasattr(mod, n)]
+    assert not missing, missing
+
+
+def test_portable_parameter_contract_checks_paths_and_shapes():
+    from rwkv7m_b200 import models as M
+
+    cfg = R.tiny_config()
+    a = M.initialize_nnx_model(0, cfg)
+    b = M.initialize_nnx_model(1, cfg)
+    same = M.initialize_nnx_model(torch.tensor([0, 0]), cfg)              # a key tensor: its last word is the seed
+    assert all(torch.equal(p, q) for p, q in zip(a.parameters(), same.parameters()))
+    tree = M.nnx_params_to_linen(a)
+    assert "token_embedding" in tree and tree["lm_head"]["kernel"].shape == (cfg.d_model, cfg.vocab_size)
+    M.assert_nnx_linen_parameter_contract(b, tree)                       # nested
+    M.assert_nnx_linen_parameter_contract(b, {"params": tree})           # wrapped as a variables record
+    M.load_linen_params_into_nnx(b, tree)
+    assert all(torch.equal(p, q) for p, q in zip(a.parameters(), b.parameters()))
+    from rwkv7m_b200.io.names import flatten
+
+    flat = flatten(tree)
+    short = dict(flat)
+    gone = sorted(short)[0]
+    del short[gone]
+    with pytest.raises(ValueError, match="missing_in_tree"):
+        M.assert_nnx_linen_parameter_contract(b, short)
+    with pytest.raises(KeyError):
+        M.load_linen_params_into_nnx(b, short)                           # a partial tree is refused
+    extra = dict(flat, **{"blocks_0/att/not_a_weight": torch.zeros(1)})
+    with pytest.raises(ValueError, match="extra_in_tree"):
+        M.assert_nnx_linen_parameter_contract(b, extra)
+    wrong = dict(flat)
+    wrong["lm_head/kernel"] = torch.zeros(cfg.vocab_size, cfg.d_model)    # transposed
+    with pytest.raises(ValueError, match="shapes differ"):
+        M.assert_nnx_linen_parameter_contract(b, wrong)
+
+
+def test_train_state_builders_and_step_under_the_reference_names(capsys):
+    from rwkv7m_b200 import models as M, train as T
+
+    cfg = R.tiny_config()
+    cfg.warmup_steps = 0
+    model = M.initialize_nnx_model(3, cfg)
+    state = T.build_train_state(None, model, {"params": None}, cfg, total_steps=10)
+    assert isinstance(state, T.NNXTrainState) and state.model is model and int(state.step) == 0
+    other = T.initialize_nnx_train_state(3, cfg, total_steps=10)
+    assert all(torch.equal(p, q) for p, q in zip(state.model.parameters(), other.model.parameters()))
+    batch = T.generate_toy_batch(1, 2, 6, cfg.vocab_size)
+    rs, ss = R.init_rwkv_state(2, cfg), R.init_screen_state(2, cfg.screening)
+    state, _, _, m = T.nnx_train_step(state, batch, rs, ss)
+    other, _, _, m2 = T.train_step(other, batch, rs, ss)
+    assert int(state.step) == 1 and float(m["loss"]) == float(m2["loss"])
+    aux = T.compute_aux_losses({}, phase="read_write")
+    assert set(aux) == {"dead_slot", "diversity", "total"} and all(float(v) == 0 for v in aux.values())
+    # the reference's positional form of the toy loop returns (losses, train_state) and prints the last step
+    losses, ts = T.run_toy_training(0, cfg, 2, 6, 5, 2)
+    assert len(losses) == 5 and int(ts.step) == 5 and "step=4" in capsys.readouterr().out
+    as_dict = T.run_toy_training(cfg, num_steps=3, batch_size=2, seq_len=6)
+    assert len(as_dict["losses"]) == 3
