@@ -148,7 +148,7 @@ def screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, 
         else:
             rel_r = R.trim_square(sim_r, tau_r, eps=cfg.eps)
         if cfg.use_age_mask:
-            rel_r = rel_r * torch.sigmoid((cfg.age_ref - ages) / (cfg.age_sigma + cfg.eps))
+            rel_r = rel_r * R.compute_age_mask(ages, cfg)
         z = torch.einsum("bm,bmv->bv", rel_r, values)
         u = R.tanh_norm(z, cap=cfg.tanh_norm_cap, eps=cfg.eps)
         read_out = R.linear(u.to(compute), mod.out_proj.weight)

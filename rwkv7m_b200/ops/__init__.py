@@ -245,11 +245,11 @@ def screening_scan(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **s
     return screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state, **scalars)
 
 
-from .backends import (WKVBackend, WKVFFIBackend, available_wkv_backends, register_wkv_ffi_backend,  # noqa: E402
+from .backends import (WKVBackend, WKVFFIBackend, WKVGPUConfig, available_wkv_backends, register_wkv_ffi_backend,  # noqa: E402
                        resolve_wkv_backend, set_wkv_backend, unregister_wkv_ffi_backend)
 
 __all__ = [
-    "WKVBackend", "WKVFFIBackend", "available_wkv_backends", "register_wkv_ffi_backend", "resolve_wkv_backend",
+    "WKVBackend", "WKVFFIBackend", "WKVGPUConfig", "available_wkv_backends", "register_wkv_ffi_backend", "resolve_wkv_backend",
     "set_wkv_backend", "unregister_wkv_ffi_backend", "wkv7_sharded",
     "screening_scan",
     "embedding",

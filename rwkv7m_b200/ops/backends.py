@@ -115,3 +115,27 @@ class _ExternalWkvFn(torch.autograd.Function):
 
 def external_wkv7(r, w, k, v, a, b, state0):
     return _ExternalWkvFn.apply(r, w, k, v, a, b, state0)
+
+
+@dataclass(frozen=True)
+class WKVGPUConfig:
+    """Tunables of the in-tree WKV7 kernels as one record (the reference's kernel configuration,
+    src/rwkv7m/kernels/wkv_pallas_gpu.py:23-26, holds a checkpoint interval and a launch shape).  ``impl``: "chunked"
+    (tcgen05, 64-step chunks, bf16 vectors, head size 64, T >= ``chunk_min_t``) or "sequential" (register-state scan; head
+    sizes up to 64, fp32 or bf16); ``checkpoint_interval``: steps between saved states of the scan kernels (the chunk
+    kernels save one state per chunk)."""
+
+    impl: str = "chunked"
+    checkpoint_interval: int = 16
+    chunk_len: int = 64
+    chunk_min_t: int = 64
+
+    def __post_init__(self):
+        if self.impl not in ("chunked", "sequential"):
+            raise ValueError("impl must be 'chunked' or 'sequential'")
+        if self.checkpoint_interval <= 0 or self.chunk_len != 64 or self.chunk_min_t < self.chunk_len:
+            raise ValueError("checkpoint_interval must be positive, chunk_len is 64 and chunk_min_t at least one chunk")
+
+    def takes_chunked_path(self, r) -> bool:
+        return (self.impl == "chunked" and r.shape[1] >= self.chunk_min_t and r.dtype == torch.bfloat16
+                and r.shape[-1] == 64)

@@ -149,6 +149,62 @@ class Wkv7Fn(torch.autograd.Function):
         return dr, dw, dk, dv, da, db, ds0
 
 
+from .backends import WKVGPUConfig  # noqa: E402  (the record is importable without the extension)
+
+
+def current_wkv_config() -> WKVGPUConfig:
+    """The process-wide kernel settings as a record."""
+    return WKVGPUConfig(impl=WKV_IMPL, checkpoint_interval=WKV_CHECKPOINT_INTERVAL, chunk_len=WKV_CHUNK_LEN,
+                        chunk_min_t=WKV_CHUNK_MIN_T)
+
+
+def wkv7_cuda_forward(r, w, k, v, a, b, state0, config: WKVGPUConfig | None = None):
+    """Inference entry point of the kernels: ``(y, final_state)``, nothing kept for a backward pass."""
+    (y, sT), _ = _wkv7_cuda_launch(r, w, k, v, a, b, state0, config, need_grad=False)
+    return y, sT
+
+
+def wkv7_cuda_forward_with_aux(r, w, k, v, a, b, state0, config: WKVGPUConfig | None = None):
+    """Training entry point: ``((y, final_state), aux)``; ``aux`` is what :func:`wkv7_cuda_backward` needs besides the
+    inputs (the per-step ``S a`` products or their chunked form, the saved states, and the path that was taken)."""
+    return _wkv7_cuda_launch(r, w, k, v, a, b, state0, config, need_grad=True)
+
+
+def _wkv7_cuda_launch(r, w, k, v, a, b, state0, config, need_grad):
+    cfg = config if config is not None else current_wkv_config()
+    r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
+    s0 = state0.contiguous().float()
+    chunked = cfg.takes_chunked_path(r)
+    interval = cfg.chunk_len if chunked else cfg.checkpoint_interval
+    y, sT, sa, ckpt = _C.wkv7_fwd(r, w, k, v, a, b, s0, need_grad, interval, chunked, False)
+    _count()
+    flag = torch.tensor([interval, int(chunked)], dtype=torch.int64)
+    return (y, sT), ((sa, ckpt, flag) if need_grad else ())
+
+
+def wkv7_cuda_backward(r, w, k, v, a, b, state0, dy, dsT, sa, ckpt, flag):
+    """The seven input cotangents from the inputs, the two output cotangents (``dsT`` may be None) and the ``aux`` tuple."""
+    interval, chunked = int(flag[0]), bool(int(flag[1]))
+    r, w, k, v, a, b = (t.contiguous() for t in (r, w, k, v, a, b))
+    if dy is None:
+        dy = torch.zeros_like(r)
+    grads = _C.wkv7_bwd(r, w, k, v, a, b, state0.contiguous().float(), sa, ckpt, dy.contiguous(), dsT, interval, chunked)
+    _count()
+    return tuple(grads)
+
+
+def builtin_wkv_ffi_backend(config: WKVGPUConfig | None = None):
+    """The in-tree kernels behind the external-backend contract (``ops.backends.WKVFFIBackend``): what a kernel library has
+    to provide to replace them, and a way to run the ``ffi`` dispatch path on a GPU without a second library."""
+    from .backends import WKVFFIBackend
+
+    return WKVFFIBackend(
+        forward=lambda *xs: wkv7_cuda_forward(*xs, config=config),
+        forward_with_aux=lambda *xs: wkv7_cuda_forward_with_aux(*xs, config=config),
+        backward=wkv7_cuda_backward,
+    )
+
+
 def wkv7(r, w, k, v, a, b, state0, impl=None):
     """``impl``: "chunked" / "sequential" for this call (the process-wide backend choice), None = ``WKV_IMPL``."""
     global WKV_IMPL

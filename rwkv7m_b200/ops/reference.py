@@ -103,6 +103,16 @@ def wkv7(r, w, k, v, a, b, state0):
     return y, S
 
 
+def wkv_step(state, r_t, w_t, k_t, v_t, neg_kk_t, kka_t):
+    """One step of the recurrence as a pure function (src/rwkv7m/model/rwkv_core.py:54-90): ``state`` [B,H,N,N],
+    the six vectors [B,H,N]; returns ``(new_state, y_t)``, all math in fp32 whatever the storage dtype."""
+    S = state.float()
+    r_t, w_t, k_t, v_t, a_t, b_t = (t.float() for t in (r_t, w_t, k_t, v_t, neg_kk_t, kka_t))
+    sa = torch.einsum("bhij,bhj->bhi", S, a_t)
+    S = S * torch.exp(-torch.exp(w_t)).unsqueeze(-2) + sa.unsqueeze(-1) * b_t.unsqueeze(-2) + v_t.unsqueeze(-1) * k_t.unsqueeze(-2)
+    return S, torch.einsum("bhij,bhj->bhi", S, r_t)
+
+
 def group_norm_heads(y, weight, bias, n_heads, eps=64e-5):
     """GroupNorm with one group per head over [.., C]; fp32 statistics."""
     shape = y.shape
@@ -160,6 +170,27 @@ def cross_entropy_loss(logits, targets, mask=None):
     """Mean masked cross-entropy (src/rwkv7m/model/losses.py:11-18)."""
     total, count = cross_entropy_components(logits, targets, mask)
     return total / torch.clamp(count, min=1.0)
+
+
+L2WRAP_FACTOR = 1e-4
+
+
+def l2wrap_components(logits, factor=L2WRAP_FACTOR):
+    """The L2Wrap numerator ``0.5 * factor * sum(max_v logit^2)`` and the position count, fp32
+    (src/rwkv7m/model/losses.py:62-69)."""
+    max_logit = logits.float().max(dim=-1).values
+    return 0.5 * factor * (max_logit * max_logit).sum(), torch.tensor(float(max_logit.numel()), device=logits.device)
+
+
+def l2wrap_loss(logits, factor=L2WRAP_FACTOR):
+    total, count = l2wrap_components(logits, factor=factor)
+    return total / count
+
+
+def compute_age_mask(ages, cfg):
+    """Soft age gate of the read relevance: ``sigmoid((age_ref - age) / (age_sigma + eps))``
+    (src/rwkv7m/model/screening.py:378-380)."""
+    return torch.sigmoid((cfg.age_ref - ages) / (cfg.age_sigma + cfg.eps))
 
 
 # ---- screening helpers (src/rwkv7m/model/screening.py:21-88) -----------------

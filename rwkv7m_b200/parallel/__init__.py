@@ -23,7 +23,7 @@ from .mesh import (Mesh, ShardingConfig, initialize_distributed, initialize_jax_
 from .metrics import aggregate_metrics, mean_metric_dict, metrics_to_host_dict, write_metric_record
 from .partitioning import (mesh_axis_size, parameter_partition_spec, parameter_partition_summary, parameter_sharding,
                            place_parameter_tree)
-from .placement import (DistributedTrainObjects, evaluate_batch_data_parallel, evaluate_batch_data_parallel_with_state,
+from .placement import (DistributedTrainObjects, eval_step_data_parallel, evaluate_batch_data_parallel, evaluate_batch_data_parallel_with_state,
                         evaluate_global_batch_data_parallel, evaluate_global_batch_data_parallel_with_state,
                         place_train_objects, replicate_train_objects, train_batch_data_parallel,
                         train_global_batch_data_parallel)

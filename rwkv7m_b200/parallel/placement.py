@@ -161,6 +161,23 @@ def _eval_step(d: DistributedTrainObjects, batch, rwkv_state, screen_state, phas
     return metrics, new_rwkv, new_screen
 
 
+@torch.no_grad()
+def eval_step_data_parallel(train_state, batch, rwkv_state, screen_state, phase="read_screening_only"):
+    """The evaluation step on this process's batch, without any exchange: ``(metrics, new_rwkv_state, new_screen_state)``
+    (src/rwkv7m/distributed/trainer.py:117-135)."""
+    from ..train.train_step import model_loss
+
+    model = train_state.model
+    was_training = model.training
+    model.eval()
+    try:
+        _, (metrics, new_rwkv, new_screen) = model_loss(model, batch, rwkv_state, screen_state, phase=phase,
+                                                        include_l2wrap=False)
+    finally:
+        model.train(was_training)
+    return metrics, new_rwkv, new_screen
+
+
 def evaluate_global_batch_data_parallel(dist_objects, global_batch, *, phase="read_screening_only", carry_state=False):
     rwkv_state, screen_state = _state_inputs(dist_objects, carry_state)
     metrics, _, _ = _eval_step(dist_objects, _local_rows(dist_objects, global_batch), rwkv_state, screen_state, phase)

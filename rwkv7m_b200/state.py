@@ -118,3 +118,8 @@ def screen_state_from_dict(data, n_screened) -> ModelScreenState:
             for i in range(n_screened)
         )
     )
+
+
+def tuple_set(xs: tuple, i: int, x) -> tuple:
+    """``xs`` with element ``i`` replaced (per-layer state tuples are immutable)."""
+    return xs[:i] + (x,) + xs[i + 1:]

@@ -84,6 +84,34 @@ def is_w0(name: str) -> bool:
     return name.endswith(".w0")
 
 
+def _named(params) -> dict:
+    if hasattr(params, "named_parameters"):
+        return dict(params.named_parameters())
+    flat = {}
+
+    def walk(tree, prefix):
+        for key, value in tree.items():
+            name = f"{prefix}{key}"
+            if isinstance(value, dict):
+                walk(value, name + ".")
+            else:
+                flat[name] = value
+
+    walk(params, "")
+    return flat
+
+
+def decay_mask_fn(params) -> dict:
+    """``name -> bool`` over a model (or a mapping / nested tree of tensors): True where decoupled weight decay applies, i.e.
+    on true matrix weights and the embedding only (src/rwkv7m/train/train_state.py:38-55)."""
+    return {name: decay_mask(name, p) for name, p in _named(params).items()}
+
+
+def rwkv_w0_mask_fn(params) -> dict:
+    """``name -> bool``: the decay anchors ``w0`` that train at twice the base rate (src/rwkv7m/train/train_state.py:58-66)."""
+    return {name: is_w0(name) for name in _named(params)}
+
+
 def _round_up(n, m):
     return (n + m - 1) // m * m
 

@@ -60,6 +60,23 @@ def initialize_train_state(seed, config: ModelConfig, *, total_steps: int = 1000
     return TrainState(model=model, optimizer=optimizer, config=config)
 
 
+@dataclass
+class TrainMetrics:
+    """The scalars every step reports (src/rwkv7m/train/train_step.py:11-16); ``from_dict`` picks them out of a step's
+    metric mapping, with zeros for the memory statistics of a model without screened layers."""
+
+    loss: torch.Tensor
+    total_loss: torch.Tensor
+    rel_read_mean: torch.Tensor
+    active_slots_mean: torch.Tensor
+    u_norm_mean: torch.Tensor
+
+    @classmethod
+    def from_dict(cls, metrics: dict) -> "TrainMetrics":
+        zero = torch.zeros(())
+        return cls(**{f: torch.as_tensor(metrics.get(f, zero)) for f in cls.__dataclass_fields__})
+
+
 def model_loss(model, batch, rwkv_state, screen_state, *, phase, include_l2wrap=True,
                ce_loss_scale=1.0, l2_loss_scale=1.0, loss_parts=None):
     """Returns (total_loss, (metrics, new_rwkv_state, new_screen_state)).  A dict passed as ``loss_parts`` receives
@@ -222,3 +239,6 @@ def generate_toy_batch(seed, batch_size, seq_len, vocab_size, device=None):
     if device is not None:
         batch = {k: v.to(device) for k, v in batch.items()}
     return batch
+
+
+nnx_model_loss = model_loss   # the reference's name of the production model's loss (src/rwkv7m/train/nnx_train.py:165)

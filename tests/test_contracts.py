@@ -748,3 +748,59 @@ def test_train_state_builders_and_step_under_the_reference_names(capsys):
     assert len(losses) == 5 and int(ts.step) == 5 and "step=4" in capsys.readouterr().out
     as_dict = T.run_toy_training(cfg, num_steps=3, batch_size=2, seq_len=6)
     assert len(as_dict["losses"]) == 3
+
+
+def test_small_helpers_under_the_reference_names():
+    from rwkv7m_b200.io.torch_backend import flax_key_to_torch_key, is_torch_available, require_torch
+    from rwkv7m_b200.ops import WKVGPUConfig, reference as ref
+    from rwkv7m_b200.parallel import eval_step_data_parallel
+    from rwkv7m_b200.state import tuple_set
+    from rwkv7m_b200.train.optimizer import decay_mask_fn, rwkv_w0_mask_fn
+    from rwkv7m_b200.train.train_step import TrainMetrics, nnx_model_loss
+
+    # one recurrence step is one step of the sequence oracle
+    torch.manual_seed(0)
+    B, T, H, N = 2, 3, 2, 8
+    r, w, k, v, a, b = (torch.randn(B, T, H, N) * 0.3 for _ in range(6))
+    S = torch.randn(B, H, N, N) * 0.1
+    y_seq, S_seq = ref.wkv7(r, w, k, v, a, b, S)
+    for t in range(T):
+        S, y_t = ref.wkv_step(S, r[:, t], w[:, t], k[:, t], v[:, t], a[:, t], b[:, t])
+        assert torch.allclose(y_t, y_seq[:, t], atol=1e-6)
+    assert torch.allclose(S, S_seq, atol=1e-6)
+    # L2Wrap: 0.5e-4 * mean over positions of the squared maximum logit
+    logits = torch.randn(2, 5, 11)
+    total, count = ref.l2wrap_components(logits)
+    assert float(count) == 10 and float(total) == pytest.approx(0.5e-4 * float(logits.max(-1).values.pow(2).sum()), rel=1e-6)
+    assert float(ref.l2wrap_loss(logits)) == pytest.approx(float(total) / 10, rel=1e-6)
+    _, _, l2_total, l2_count = ref.cross_entropy_l2wrap(logits, torch.zeros(2, 5, dtype=torch.long))
+    assert float(l2_total) == pytest.approx(float(total), rel=1e-6) and float(l2_count) == 10
+    # age gate: one half at the reference age, falling with age
+    cfg = R.tiny_config().screening
+    gate = ref.compute_age_mask(torch.tensor([0.0, cfg.age_ref, cfg.age_ref + 10 * cfg.age_sigma]), cfg)
+    assert float(gate[1]) == pytest.approx(0.5) and float(gate[0]) > 0.5 > float(gate[2])
+    assert tuple_set((1, 2, 3), 1, "x") == (1, "x", 3)
+    # optimizer masks over a model: matrices and the embedding decay, vectors / norms do not; w0 is the 2x-rate leaf
+    model = R.initialize_model(0, R.tiny_config())
+    decay, w0 = decay_mask_fn(model), rwkv_w0_mask_fn(model)
+    assert decay["emb.weight"] and decay["layers.0.block.att.key.weight"] and not decay["layers.0.block.ln1.weight"]
+    assert not decay["layers.0.block.att.w0"] and w0["layers.0.block.att.w0"] and sum(w0.values()) == len(model.layers)
+    assert decay_mask_fn({"a": {"weight": torch.zeros(3)}}) == {"a.weight": False}
+    metrics = TrainMetrics.from_dict({"loss": torch.tensor(2.0), "total_loss": torch.tensor(2.5)})
+    assert float(metrics.loss) == 2.0 and float(metrics.rel_read_mean) == 0.0
+    assert flax_key_to_torch_key("blocks_0/att/key/kernel") == "blocks_0.att.key.kernel"
+    assert is_torch_available() and require_torch() is torch
+    # kernel settings record
+    assert WKVGPUConfig().takes_chunked_path(torch.zeros(1, 64, 1, 64, dtype=torch.bfloat16))
+    assert not WKVGPUConfig().takes_chunked_path(torch.zeros(1, 32, 1, 64, dtype=torch.bfloat16))
+    assert not WKVGPUConfig(impl="sequential").takes_chunked_path(torch.zeros(1, 64, 1, 64, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        WKVGPUConfig(impl="pallas")
+    # the evaluation step alone
+    cfg = R.tiny_config()
+    rt, ts = R.create_train_runtime(0, cfg, batch_size=2, total_steps=5)
+    batch = R.generate_toy_batch(1, 2, 6, cfg.vocab_size)
+    m, rs, ss = eval_step_data_parallel(ts, batch, rt.initial_rwkv_state, rt.initial_screen_state)
+    loss, _ = nnx_model_loss(ts.model, batch, rt.initial_rwkv_state, rt.initial_screen_state, phase="read_screening_only",
+                             include_l2wrap=False)
+    assert float(m["loss"]) == pytest.approx(float(loss.detach()), rel=1e-5) and ts.model.training
