@@ -236,3 +236,18 @@ def test_upstream_single_device_trainer_protocol(tiny_binidx, tmp_path):
     assert (out / "rwkv-6.pth").exists() and (out / "rwkv-final.pth").exists()
     assert json.loads((out / "run_summary.json").read_text())["status"] == "completed"
     assert last["tokens"] == 12 * 4 * 4
+
+
+def test_preset_execution_controls_are_opt_in_overrides():
+    """A preset brings its own recompute / chunking choices; the trainer's flags override each one in both directions
+    (scenario of the reference's tests/test_unified_model_scale.py:195-242)."""
+    from rwkv7m_b200.cli.common import build_config
+
+    base = ["--data-file", "unused", "--model-preset", "0.185b", "--ctx-len", "512", "--global-batch-size", "1", "--steps", "0"]
+    parse = train_binidx_distributed.parse_args
+    preset = build_config(parse(base))
+    assert (preset.remat_blocks, preset.sequence_chunk_size, preset.head_chunk_size) == (True, 128, None)
+    plain = build_config(parse(base + ["--no-remat-blocks", "--no-sequence-chunking", "--no-head-chunking"]))
+    assert (plain.remat_blocks, plain.sequence_chunk_size, plain.head_chunk_size) == (False, None, 512)
+    chosen = build_config(parse(base + ["--remat-blocks", "--sequence-chunk-size", "256", "--head-chunk-size", "512"]))
+    assert (chosen.remat_blocks, chosen.sequence_chunk_size, chosen.head_chunk_size) == (True, 256, 512)
