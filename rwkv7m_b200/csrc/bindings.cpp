@@ -237,6 +237,38 @@ std::vector<Tensor> gemm_ce_stats(const Tensor& A, const Tensor& B, const Tensor
   return {lse, maxv, argmax, nll};
 }
 
+// Up to four y_i = act_i(A_i B_i^T) with the same number of rows in one launch (bf16 in, bf16 out).  Returns false, having
+// launched nothing, when the set does not qualify; the caller then issues the products one by one.
+bool gemm_group(const std::vector<Tensor>& As, const std::vector<Tensor>& Bs, std::vector<Tensor> Ds,
+                const std::vector<int64_t>& acts) {
+  const size_t n = As.size();
+  TORCH_CHECK(n >= 1 && n <= 4 && Bs.size() == n && Ds.size() == n && acts.size() == n, "gemm_group: 1 to 4 problems");
+  c10::cuda::CUDAGuard guard(As[0].device());
+  rk::GemmArgs ps[4];
+  for (size_t i = 0; i < n; ++i) {
+    const Tensor &A = As[i], &B = Bs[i];
+    Tensor& D = Ds[i];
+    TORCH_CHECK(A.is_cuda() && B.is_cuda() && D.is_cuda(), "gemm_group: CUDA tensors required");
+    TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 && D.scalar_type() == at::kBFloat16,
+                "gemm_group: bf16 tensors required");
+    TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && D.dim() == 2 && A.stride(1) == 1 && B.stride(1) == 1 && D.stride(1) == 1,
+                "gemm_group: 2-D tensors with contiguous rows required");
+    TORCH_CHECK(B.size(1) == A.size(1) && D.size(0) == A.size(0) && D.size(1) == B.size(0), "gemm_group: shape mismatch");
+    TORCH_CHECK(acts[i] >= 0 && acts[i] <= 2, "gemm_group: activation selector out of range");
+    rk::GemmArgs p{};
+    p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = D.data_ptr();
+    p.lda = (int)A.stride(0); p.ldb = (int)B.stride(0); p.ldd = (int)D.stride(0);
+    p.M = (int)A.size(0); p.K = (int)A.size(1); p.N = (int)B.size(0);
+    p.layout = rk::kGemmTN; p.epilogue = rk::kEpiStoreBf16; p.act = (int)acts[i];
+    p.error_flag = gemm_error_flag(A.device()).data_ptr<int>();
+    ps[i] = p;
+  }
+  const int rc = rk::gemm_bf16_group(ps, (int)n, stream());
+  if (rc == 1) return false;
+  TORCH_CHECK(rc == 0, "gemm_bf16_group launch failed with code ", rc);
+  return true;
+}
+
 int64_t gemm_error(const Tensor& like) {
   return gemm_error_flag(like.device()).item<int>();
 }
@@ -868,6 +900,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat", &adamw_flat);
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("D"), py::arg("layout"), py::arg("epilogue"), py::arg("pair"),
         py::arg("aux") = py::none(), py::arg("act") = 0);
+  m.def("gemm_group", &gemm_group);
   m.def("gemm_error", &gemm_error);
   m.def("gemm_error_reset", &gemm_error_reset);
   m.def("layernorm_fwd", &layernorm_fwd);

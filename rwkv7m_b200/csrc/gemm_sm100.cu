@@ -499,6 +499,185 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Grouped variant: up to four y_i = act_i(x_i W_i^T) problems with the same number of rows in one persistent launch
+// (layout TN, bf16 store epilogue).  The low-rank pairs of the time-mix block are four skinny GEMMs of 30-40 us each; one
+// launch walks the tiles of all of them (problem after problem), so there is one ramp-up and one tail instead of four
+// and the short problems fill the SMs that the tail of a longer one leaves idle.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxGroup = 4;
+struct GroupProblem {
+  void* D;
+  int N, K, ldd, act;
+  int tiles_n, tile_begin, tma_out, pad;
+};
+struct GroupParams {
+  CUtensorMap tmA[kMaxGroup];
+  CUtensorMap tmB[kMaxGroup];
+  CUtensorMap tmD[kMaxGroup];
+  GroupProblem pr[kMaxGroup];
+  int count, M, total_tiles, raster_m;
+};
+
+__device__ __forceinline__ int group_find(const GroupParams& g, int work) {
+  int p = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxGroup; ++i)
+    if (i < g.count && work >= g.pr[i].tile_begin) p = i;
+  return p;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_group_kernel(const __grid_constant__ GroupParams g, int* __restrict__ err) {
+  using TL = Tile<BN>;
+  constexpr int kStages = TL::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint8_t* out_stage = smem + kStages * TL::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + 2 * kOutStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tfull_bar = bars + 2 * kStages;
+  uint64_t* tempty_bar = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int M = g.M;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int num_work = g.total_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull_bar[s], 1); mbar_init(&tempty_bar[s], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < g.count; ++i) {
+      tma_prefetch_desc(&g.tmA[i]); tma_prefetch_desc(&g.tmB[i]);
+      if (g.pr[i].tma_out) tma_prefetch_desc(&g.tmD[i]);
+    }
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TL::kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        const int p = group_find(g, work);
+        int tm, tn;
+        tile_coords(work - g.pr[p].tile_begin, tiles_m, g.pr[p].tiles_n, g.raster_m, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        const int num_kb = (g.pr[p].K + BK - 1) / BK;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * TL::kStageBytes;
+          uint8_t* sb = sa + TL::kABytes;
+          mbar_expect_tx(&full_bar[stage], TL::kStageBytes);
+          tma_load_2d(sa, &g.tmA[p], &full_bar[stage], kb * BK, m0);
+          tma_load_2d(sb, &g.tmB[p], &full_bar[stage], kb * BK, n0);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x10000 | 1); }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        const int num_kb = (g.pr[group_find(g, work)].K + BK - 1) / BK;
+        if (!wait_bar(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_bar(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * TL::kStageBytes);
+          const uint32_t sb = sa + TL::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16(d_tmem, umma_smem_desc_sw128(sa + k * 32, 16, 1024), umma_smem_desc_sw128(sb + k * 32, 16, 1024), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(err, 0x10000 | 2); }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool issuer = warp == 2 && lane == 0;
+    bool stored = false;
+    int obuf = 0;
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+      const int p = group_find(g, work);
+      const GroupProblem pr = g.pr[p];
+      int tm, tn;
+      tile_coords(work - pr.tile_begin, tiles_m, pr.tiles_n, g.raster_m, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      if (!wait_bar(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c += 2) {
+        if (n0 + c * 32 >= pr.N) break;   // the same for all 128 threads: nothing of this tile lies further right
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(t0 + c * 32, v0);
+        tmem_ld_32x32(t0 + c * 32 + 32, v1);
+        tmem_ld_wait();
+        if (pr.tma_out) {
+          uint8_t* buf = out_stage + obuf * kOutStageBytes;
+          stage_round<kEpiStoreBf16>(v0, v1, buf, q * 32 + lane, pr.act, nullptr);
+          if (issuer) tma_store_wait_read<0>();
+          epilogue_named_barrier();
+          if (issuer) { tma_store_2d(&g.tmD[p], buf, n0 + c * 32, m0); tma_store_commit(); stored = true; }
+          obuf ^= 1;
+        } else {
+          store_chunk<kEpiStoreBf16>(v0, pr.D, row, n0 + c * 32, M, pr.N, pr.ldd, false, nullptr, 0, pr.act);
+          store_chunk<kEpiStoreBf16>(v1, pr.D, row, n0 + c * 32 + 32, M, pr.N, pr.ldd, false, nullptr, 0, pr.act);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+    }
+    if (stored) tma_store_wait<0>();
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(err, 0x10000 | 3); }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) { }
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TL::kTmemCols); }
+}
+
+// ---------------------------------------------------------------------------------------------
 // CTA-pair variant: two CTAs of a cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2.
 // Each CTA loads only its own 128 rows of A and 128 columns of B per k-block (32 KB instead of the
 // 48 KB a lone 128 x 256 CTA needs for the same FLOPs) and keeps the 128 x 256 half of the accumulator
@@ -905,6 +1084,43 @@ int launch_layout(const GemmArgs& p, cudaStream_t st) {
   return 5;
 }
 
+template <int BN>
+int launch_group(const GemmArgs* ps, int count, cudaStream_t st) {
+  using TL = Tile<BN>;
+  alignas(64) GroupParams g;
+  memset(&g, 0, sizeof(g));
+  g.count = count;
+  g.M = ps[0].M;
+  g.raster_m = raster_rows(ps[0]);
+  const int tiles_m = (g.M + BM - 1) / BM;
+  int total = 0;
+  for (int i = 0; i < count; ++i) {
+    const GemmArgs& p = ps[i];
+    if (!make_map(&g.tmA[i], p.A, p.M, p.K, p.lda, BM)) return 2;
+    if (!make_map(&g.tmB[i], p.B, p.N, p.K, p.ldb, BN)) return 2;
+    g.tmD[i] = g.tmA[i];
+    GroupProblem& q = g.pr[i];
+    q.D = p.D; q.N = p.N; q.K = p.K; q.ldd = p.ldd; q.act = p.act;
+    q.tiles_n = (p.N + BN - 1) / BN;
+    q.tile_begin = total;
+    q.tma_out = 0;
+    if (tma_store_enabled() && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && p.ldd % 8 == 0)
+      q.tma_out = make_map(&g.tmD[i], p.D, p.M, p.N, p.ldd, BM) ? 1 : 0;
+    total += tiles_m * q.tiles_n;
+  }
+  for (int i = count; i < kMaxGroup; ++i) { g.tmA[i] = g.tmA[0]; g.tmB[i] = g.tmB[0]; g.tmD[i] = g.tmD[0]; g.pr[i].tile_begin = total; }
+  g.total_tiles = total;
+  auto kern = gemm_bf16_group_kernel<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::kSmemBytes) != cudaSuccess) return 3;
+    attr_set = true;
+  }
+  const int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, kThreads, TL::kSmemBytes, st>>>(g, ps[0].error_flag);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 template <int A_MN, int B_MN, int EPI>
 int launch_pair(const GemmArgs& p, cudaStream_t st) {
   using TL = PairTile;
@@ -1173,6 +1389,21 @@ bool tma_encode_bf16_3d(void* map, const void* ptr, unsigned long long d0, unsig
   return fn(reinterpret_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int gemm_bf16_group(const GemmArgs* ps, int count, cudaStream_t st) {
+  if (count < 1 || count > kMaxGroup) return 1;
+  int max_n = 0;
+  for (int i = 0; i < count; ++i) {
+    const GemmArgs& p = ps[i];
+    if (p.layout != kGemmTN || p.epilogue != kEpiStoreBf16 || p.M != ps[0].M || p.M <= 0 || p.N <= 0 || p.K <= 0) return 1;
+    if (p.K % 8 != 0 || p.lda % 8 != 0 || p.ldb % 8 != 0) return 1;
+    if ((reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B) | reinterpret_cast<uintptr_t>(p.D)) & 15) return 1;
+    if (p.ldd % 8 != 0 || p.error_flag == nullptr) return 1;
+    if (p.N > max_n) max_n = p.N;
+  }
+  // narrow outputs (the down-projections) take 128-column tiles, wide ones 256-column tiles
+  return max_n <= 256 ? launch_group<128>(ps, count, st) : launch_group<256>(ps, count, st);
 }
 
 bool gemm_decode_eligible(const GemmArgs& p) {

@@ -243,6 +243,9 @@ struct GemmArgs {
   int decode_kernel;   // non-zero: shapes with M <= 64 (layout kGemmTN) take the swap-AB cluster split-K kernel
 };
 int gemm_bf16(const GemmArgs& p, cudaStream_t st);
+// Up to four problems of layout kGemmTN with the bf16 store epilogue (each with its own activation) and the same M in one
+// persistent launch; returns 1 when the set does not qualify (the caller then launches them one by one).
+int gemm_bf16_group(const GemmArgs* ps, int count, cudaStream_t st);
 // Tiled tensor map (128 bytes at `map`, 64-byte aligned) over a bf16 array of logical shape [d2][d1][d0], d0 contiguous,
 // with byte strides stride1 / stride2 for the two outer dimensions; box = box0 x box1 x 1 elements, 128-byte swizzle,
 // zero fill outside the array.  Used for operand tiles that land in shared memory in the tensor cores' canonical layout.

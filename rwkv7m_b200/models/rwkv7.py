@@ -178,7 +178,11 @@ class RWKV7TimeMix(nn.Module):
         if self.fork is not None and T == 1 and x.is_cuda and not torch.is_grad_enabled():
             outs = self.fork.run(branches)
         else:
-            outs = [fn() for fn in branches]
+            outs = [fn() for fn in branches[:3]]
+            pairs = [(x_w, self.w1, self.w2, "tanh"), (x_a, self.a1, self.a2, "none"), (x_g, self.g1, self.g2, "sigmoid")]
+            if self.layer_idx > 0:
+                pairs.append((x_v, self.v1, self.v2, "none"))
+            outs += ops.lora_group(pairs)       # same order as the branches: decay, in-context rate, gate[, value residual]
         r, k, v, w_lora, a_lora, g = outs[:6]
         if self.layer_idx == 0:
             vg_lora, v_src, v0 = None, None, None

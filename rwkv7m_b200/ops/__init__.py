@@ -102,6 +102,14 @@ def lora(x, down, up, mid="none"):
     return reference.lora(x, down, up, None, mid=mid)
 
 
+def lora_group(items):
+    """Several low-rank paths on inputs of one shape: ``items`` are ``(x, down, up, mid)`` tuples, the result is the list of
+    outputs.  On the GPU the down-projections and the up-projections can each run as one grouped launch."""
+    if items and use_cuda(items[0][0]):
+        return _cuda().lora_group(items)
+    return [reference.lora(x, d, u, None, mid=mid) for x, d, u, mid in items]
+
+
 def tmix_pre(k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a, n_heads):
     """Everything between the projections and the recurrence, in one pass:
 
@@ -262,6 +270,7 @@ __all__ = [
     "linear",
     "linear_relu_sq",
     "lora",
+    "lora_group",
     "tmix_pre",
     "wkv7",
     "gn_bonus_gate",

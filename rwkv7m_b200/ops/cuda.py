@@ -686,6 +686,86 @@ def lora(x, down, up, mid="none"):
     return R.lora(x, down, up, mid=mid)
 
 
+# The low-rank pairs of a time-mix block (decay, in-context rate, gate and, past the first layer,
+# value residual) run their down-projections as one grouped GEMM launch and their up-projections as another
+# (RWKV7M_B200_LORA_GROUP=0: pair by pair).  Measured at 32768 x 2048, ranks 128 / 128 / 224 / 64: down-projections
+# 154 -> 131 us, up-projections 188 -> 194 us (write-bound; the grouping only removes three launches there).
+LORA_GROUP = os.environ.get("RWKV7M_B200_LORA_GROUP", "1") != "0"
+
+
+class LoraGroupFn(torch.autograd.Function):
+    """``n`` low-rank pairs on inputs of the same [.., C] shape in one autograd node: two grouped launches in forward (all
+    down-projections with their activations, then all up-projections); the backward of each pair is that of ``LoraFn``."""
+
+    @staticmethod
+    def forward(ctx, acts, n, *tensors):
+        xs, downs, ups = tensors[:n], tensors[n:2 * n], tensors[2 * n:3 * n]
+        dcs, ucs = [_compute_weight(d) for d in downs], [_compute_weight(u) for u in ups]
+        x2s = []
+        for x in xs:
+            x2 = x.reshape(-1, x.shape[-1])
+            x2s.append(x2 if x2.is_contiguous() else x2.contiguous())
+        M = x2s[0].shape[0]
+        dev = xs[0].device
+        hs = [torch.empty(M, dc.shape[0], dtype=torch.bfloat16, device=dev) for dc in dcs]
+        if _C.gemm_group(x2s, dcs, hs, list(acts)):
+            _count()
+        else:
+            for x2, dc, h, act in zip(x2s, dcs, hs, acts):
+                gemm(x2, dc, h, GEMM_TN, EPI_BF16, act=act)
+        ys = [torch.empty(M, uc.shape[0], dtype=torch.bfloat16, device=dev) for uc in ucs]
+        if _C.gemm_group(hs, ucs, ys, [ACT_NONE] * n):
+            _count()
+        else:
+            for h, uc, y in zip(hs, ucs, ys):
+                gemm(h, uc, y, GEMM_TN, EPI_BF16)
+        ctx.n, ctx.acts, ctx.downs, ctx.ups = n, tuple(acts), downs, ups
+        ctx.x_shapes = [x.shape for x in xs]
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(*x2s, *dcs, *ucs, *hs)
+        return tuple(y.view(*x.shape[:-1], uc.shape[0]) for y, x, uc in zip(ys, xs, ucs))
+
+    @staticmethod
+    def backward(ctx, *dys):
+        n = ctx.n
+        saved = ctx.saved_tensors
+        x2s, dcs, ucs, hs = saved[:n], saved[n:2 * n], saved[2 * n:3 * n], saved[3 * n:4 * n]
+        dxs, ddowns, dups = [None] * n, [None] * n, [None] * n
+        for i in range(n):
+            dy = dys[i]
+            if dy is None:
+                continue
+            x2, dc, uc, h, act = x2s[i], dcs[i], ucs[i], hs[i], ctx.acts[i]
+            d2 = dy.reshape(-1, uc.shape[0])
+            if not d2.is_contiguous():
+                d2 = d2.contiguous()
+            if ctx.needs_input_grad[2 + 2 * n + i]:
+                dups[i] = _wgrad(d2, h, ctx.ups[i])
+            dpre = torch.empty_like(h)
+            if act == ACT_NONE:
+                gemm(d2, uc, dpre, GEMM_NN, EPI_BF16)
+            else:
+                gemm(d2, uc, dpre, GEMM_NN, EPI_MUL2SQRT, aux=h, act=act)
+            if ctx.needs_input_grad[2 + i]:
+                dx = torch.empty(x2.shape[0], x2.shape[1], dtype=torch.bfloat16, device=dy.device)
+                gemm(dpre, dc, dx, GEMM_NN, EPI_BF16)
+                dxs[i] = dx.view(ctx.x_shapes[i])
+            if ctx.needs_input_grad[2 + n + i]:
+                ddowns[i] = _wgrad(dpre, x2, ctx.downs[i])
+        return (None, None, *dxs, *ddowns, *dups)
+
+
+def lora_group(items):
+    """``items``: ``(x, down, up, mid)`` tuples on inputs of one shape; returns the list of results.  One grouped launch
+    per half when the switch is on and every pair qualifies for the GEMM path, otherwise pair by pair."""
+    if LORA_GROUP and 2 <= len(items) <= 4 and all(_fused_linear_ok(x, d, u) for x, d, u, _ in items) \
+            and len({tuple(x.shape) for x, _, _, _ in items}) == 1:
+        n = len(items)
+        xs, downs, ups = [it[0] for it in items], [it[1] for it in items], [it[2] for it in items]
+        return list(LoraGroupFn.apply(tuple(_ACT[it[3]] for it in items), n, *xs, *downs, *ups))
+    return [lora(x, d, u, mid) for x, d, u, mid in items]
+
+
 class TmixPreFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, k, v, w_lora, a_lora, vg_lora, v_first, w0, a0, v0, k_k, k_a):

@@ -234,3 +234,77 @@ def test_decode_sized_gemm_matches_fp32(M, N, K, epi):
     finally:
         kk._C.set_decode_gemm(True)
     assert float((out.float() - out2.float()).abs().max()) < 2e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("M", [1000, 4096])
+def test_grouped_launch_matches_separate_products(M):
+    """Up to four y_i = act_i(x_i W_i^T) with one row count in one launch: the shapes of the low-rank pairs of a time-mix
+    block (ranks 128 / 128 / 224 / 64 down from 2048 columns with tanh / none / sigmoid / none, then back up), a row
+    count that is no multiple of the tile height, against an fp32 product of the same bf16 operands."""
+    from rwkv7m_b200.ops import cuda as K
+    from rwkv7m_b200.ops.build import load_extension
+
+    C_ext = load_extension()
+    torch.manual_seed(0)
+    C = 2048 if M > 1000 else 512
+    ranks, acts = [128, 128, 224, 64], [1, 0, 2, 0]
+    xs = [(torch.randn(M, C, device="cuda") * 0.5).bfloat16() for _ in ranks]
+    downs = [(torch.randn(r, C, device="cuda") / C ** 0.5).bfloat16() for r in ranks]
+    ups = [(torch.randn(C, r, device="cuda") / r ** 0.5).bfloat16() for r in ranks]
+    fn = {0: lambda t: t, 1: torch.tanh, 2: torch.sigmoid}
+    K.gemm_error_reset(xs[0])
+    for n in (4, 3, 1):
+        hs = [torch.full((M, r), float("nan"), device="cuda", dtype=torch.bfloat16) for r in ranks[:n]]
+        assert C_ext.gemm_group(xs[:n], downs[:n], hs, acts[:n])
+        for x, d, h, a in zip(xs, downs, hs, acts):
+            want = fn[a](x.float() @ d.float().t())
+            assert torch.isfinite(h.float()).all()
+            assert float((h.float() - want).abs().max()) < 2e-2 * float(want.abs().max()) + 1e-3
+            single = torch.empty_like(h)
+            K.gemm(x, d, single, K.GEMM_TN, K.EPI_BF16, act=a)
+            assert float((h.float() - single.float()).abs().max()) <= 1e-2 * float(want.abs().max())
+        ys = [torch.full((M, C), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+        assert C_ext.gemm_group(hs, ups[:n], ys, [0] * n)
+        for h, u, y in zip(hs, ups, ys):
+            want = h.float() @ u.float().t()
+            assert torch.isfinite(y.float()).all()
+            assert float((y.float() - want).abs().max()) < 2e-2 * float(want.abs().max()) + 1e-3
+    assert K.gemm_error_code(xs[0]) == 0
+    # a set that does not qualify (different row counts) launches nothing and says so
+    assert not C_ext.gemm_group([xs[0], xs[1][: M // 2]], downs[:2],
+                                [torch.empty(M, 128, device="cuda", dtype=torch.bfloat16),
+                                 torch.empty(M // 2, 128, device="cuda", dtype=torch.bfloat16)], [0, 0])
+
+
+def test_grouped_low_rank_pairs_match_pair_by_pair_in_a_block(monkeypatch):
+    """A time-mix block with the grouped launches switched on: outputs and every gradient equal the pair-by-pair path's
+    (the backward is the same code; the forward differs only in which launch computes a tile)."""
+    import rwkv7m_b200 as R
+    from rwkv7m_b200.ops import cuda as K
+
+    cfg = R.ModelConfig(d_model=256, d_ffn=512, n_layers=2, n_heads=4, head_size=64, vocab_size=512, max_seq_len=128,
+                        dtype="bfloat16", use_screening=False)
+    ids = torch.randint(0, 512, (2, 128), device="cuda", dtype=torch.int32)
+    batch = {"input_ids": ids, "target_ids": (ids + 1) % 512, "mask": torch.ones(2, 128, device="cuda")}
+
+    def run(grouped):
+        monkeypatch.setattr(K, "LORA_GROUP", grouped)
+        rt, ts = R.create_train_runtime(3, cfg, batch_size=2, total_steps=10, device="cuda")
+        gen = torch.Generator().manual_seed(5)
+        with torch.no_grad():      # the second halves of the pairs start at zero: move them so that every path carries signal
+            for name, p in ts.model.named_parameters():
+                if name.endswith((".w1", ".a1", ".v1", ".g1")):
+                    p.add_((torch.randn(p.shape, generator=gen) * 0.05).to(p))
+        ts.optimizer.flat.sync_compute()
+        before = K.LAUNCH_COUNT
+        ts, m = R.train_batch(ts, batch, rt)
+        launches = K.LAUNCH_COUNT - before
+        return float(m["loss"]), {n: p.detach().float().clone() for n, p in ts.model.named_parameters()}, launches
+
+    loss_a, params_a, launches_a = run(False)
+    loss_b, params_b, launches_b = run(True)
+    assert abs(loss_a - loss_b) < 1e-3 * abs(loss_a)
+    num = sum(float((params_a[n] - params_b[n]).pow(2).sum()) for n in params_a) ** 0.5
+    den = sum(float(params_a[n].pow(2).sum()) for n in params_a) ** 0.5
+    assert num / den < 1e-4, num / den
+    assert launches_a - launches_b == 2 * (3 + 4) - 2 * 2      # layer 0: 6 -> 2 forward launches, layer 1: 8 -> 2
