@@ -227,9 +227,49 @@ def bench_screening(B, T, iters=3, preset="0.185b", dtype=torch.bfloat16):
              "fwd_ms": tf["median_ms"], "fwd_bwd_ms": tb["median_ms"], "us_per_step_fwd": 1e3 * tf["median_ms"] / T}]
 
 
+def bench_lora_group(M, C, iters=10, ranks=(128, 128, 224, 64), acts=(1, 0, 2, 0)):
+    """The low-rank pairs of a time-mix block: four down-projections (with their activations) and four up-projections, each
+    set as four launches and as one grouped launch."""
+    from rwkv7m_b200.ops import cuda as K
+    from rwkv7m_b200.ops.build import load_extension
+
+    ext = load_extension()
+    dev = "cuda"
+    xs = [(torch.randn(M, C, device=dev) * 0.5).bfloat16() for _ in ranks]
+    downs = [(torch.randn(r, C, device=dev) / C ** 0.5).bfloat16() for r in ranks]
+    ups = [(torch.randn(C, r, device=dev) / r ** 0.5).bfloat16() for r in ranks]
+    hs = [torch.empty(M, r, device=dev, dtype=torch.bfloat16) for r in ranks]
+    ys = [torch.empty(M, C, device=dev, dtype=torch.bfloat16) for _ in ranks]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    acts, n = list(acts), len(ranks)
+
+    def down_separate():
+        for x, d, h, a in zip(xs, downs, hs, acts):
+            K.gemm(x, d, h, K.GEMM_TN, K.EPI_BF16, act=a)
+
+    def down_grouped():
+        if not ext.gemm_group(xs, downs, hs, acts):
+            raise RuntimeError("the down-projections did not qualify for the grouped launch")
+
+    def up_separate():
+        for h, u, y in zip(hs, ups, ys):
+            K.gemm(h, u, y, K.GEMM_TN, K.EPI_BF16)
+
+    def up_grouped():
+        if not ext.gemm_group(hs, ups, ys, [0] * n):
+            raise RuntimeError("the up-projections did not qualify for the grouped launch")
+
+    row = {"op": "lora_group", "M": M, "C": C, "ranks": list(ranks)}
+    for name, fn in (("down_separate", down_separate), ("down_grouped", down_grouped), ("up_separate", up_separate),
+                     ("up_grouped", up_grouped)):
+        row[f"{name}_us"] = _time(fn, iters=iters, flush=flush)["median_ms"] * 1000.0
+    row["gemm_error"] = K.gemm_error_code(xs[0])
+    return [row]
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="wkv,gemm", help="comma list of wkv, gemm, fused, optim, loss, screening")
+    ap.add_argument("--what", default="wkv,gemm", help="comma list of wkv, gemm, fused, optim, loss, screening, lora")
     ap.add_argument("--gemm-shape", default=None, help="M,N,K of a single GEMM case")
     ap.add_argument("--wkv-shape", default=None, help="T,B,H,N of a single WKV case")
     ap.add_argument("--wkv-impl", choices=["chunked", "sequential"], default=None)
@@ -265,6 +305,8 @@ def main(argv=None):
     if "screening" in args.what:
         steps = args.screen_steps or (256 if args.small else 4096)
         results += bench_screening(8, steps, iters=min(args.iters, 3), preset=args.screen_preset)
+    if "lora" in args.what:
+        results += bench_lora_group(4096 if args.small else 32768, 2048, iters=args.iters)
     if "optim" in args.what:
         results += bench_optimizer((64 if args.small else 512) * 1024 * 1024, iters=args.iters)
     for r in results:
