@@ -17,27 +17,46 @@ from ..data import MMapIndexedDataset, MMapIndexedDatasetBuilder, find_magic_pri
 from ..tokenizer import RWKVTokenizer, default_vocab_path
 
 
-def build_binidx(input_file, output_prefix, *, vocab_file=None, epochs=3, seed=42, dtype="uint16") -> dict:
+def build_binidx(input_file, output_prefix, *, vocab_file=None, epochs=3, seed=42, dtype="uint16", threads=0) -> dict:
+    """Tokenise every row once (in batches spread over ``threads`` workers when the native tokenizer is built; 0 means one
+    per core), then write ``epochs`` passes over the token arrays, each in a new order: the row list is shuffled again
+    before every pass, cumulatively and from ``seed``, so the document order equals that of shuffling and re-encoding the
+    text rows pass by pass.  Token arrays are smaller than the text they came from, so holding them costs less than the
+    row list itself."""
     tokenizer = RWKVTokenizer(vocab_file)
-    rng = random.Random(seed)
-    with open(input_file, "r", encoding="utf-8") as f:
-        rows = [line.strip() for line in f if line.strip()]
-    if not rows:
-        raise ValueError(f"no non-empty JSONL rows found in {input_file}")
     np_dtype = np.dtype(dtype)
+    texts = []
+    with open(input_file, "r", encoding="utf-8") as f:
+        for line in f:
+            line = line.strip()
+            if line:
+                texts.append(json.loads(line)["text"])
+    if not texts:
+        raise ValueError(f"no non-empty JSONL rows found in {input_file}")
+    limit = int(np.iinfo(np_dtype).max)
+    documents = []
+    for start in range(0, len(texts), 2048):
+        for ids in tokenizer.encode_batch(texts[start:start + 2048], add_eos=True, threads=threads):
+            arr = np.asarray(ids, dtype=np.int64)
+            if arr.size and int(arr.max()) > limit:
+                raise ValueError(f"token id {int(arr.max())} does not fit the {np_dtype.name} storage type")
+            documents.append(arr.astype(np_dtype))
+    del texts
+    order = list(range(len(documents)))
+    rng = random.Random(seed)
     builder = MMapIndexedDatasetBuilder(str(output_prefix) + ".bin", dtype=np_dtype)
     items = 0
     for _ in range(int(epochs)):
-        rng.shuffle(rows)
-        for line in rows:
-            tokens = tokenizer.encode(json.loads(line)["text"], add_eos=True)
-            builder.add_item(np.asarray(tokens, dtype=np_dtype))
+        rng.shuffle(order)
+        for i in order:
+            builder.add_item(documents[i])
             builder.end_document()
             items += 1
     builder.finalize(str(output_prefix) + ".idx")
     data = MMapIndexedDataset(str(output_prefix))
     try:
-        return {"items": items, "tokens": data.data_size, "dtype": np.dtype(data.dtype).name}
+        return {"items": items, "tokens": data.data_size, "dtype": np.dtype(data.dtype).name,
+                "native_tokenizer": tokenizer._native is not None}
     finally:
         data.close()
 
@@ -51,6 +70,7 @@ def parse_args(argv=None):
     p.add_argument("--ctx-len", type=int, default=512)
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--dtype", choices=["uint16", "uint32"], default="uint16")
+    p.add_argument("--threads", type=int, default=0, help="tokenizer workers (0: one per core; native tokenizer only)")
     return p.parse_args(argv)
 
 
@@ -58,7 +78,7 @@ def main(argv=None):
     args = parse_args(argv)
     prefix = args.output_prefix or str(Path(args.input_file).with_suffix(""))
     stats = build_binidx(args.input_file, prefix, vocab_file=args.vocab_file, epochs=args.epochs, seed=args.seed,
-                         dtype=args.dtype)
+                         dtype=args.dtype, threads=args.threads)
     print(f"wrote {prefix}.bin/.idx items={stats['items']} tokens={stats['tokens']} dtype={stats['dtype']}")
     if stats["tokens"] >= args.ctx_len + 1:
         print(f"magic_prime={find_magic_prime(stats['tokens'], args.ctx_len)} ctx_len={args.ctx_len}")

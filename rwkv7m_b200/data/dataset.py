@@ -142,6 +142,18 @@ class BinIdxBatchDataset:
     def _gather(self, offsets: np.ndarray) -> np.ndarray:
         return np.asarray(self.data._bin[offsets[:, None] + self._window[None, :]]).astype(np.int32)
 
+    def _gather_native(self, offsets: np.ndarray, pin_memory: bool):
+        """Inputs and targets of a step written by the native threaded gather straight into fresh (optionally pinned) int32
+        tensors: one pass over the memory-mapped stream, no intermediate index or widened copy."""
+        from ..utils import host_runtime
+
+        rows, ctx = int(offsets.shape[0]), self.config.ctx_len
+        pin = bool(pin_memory and torch.cuda.is_available())
+        inputs = torch.empty(rows, ctx, dtype=torch.int32, pin_memory=pin)
+        targets = torch.empty(rows, ctx, dtype=torch.int32, pin_memory=pin)
+        host_runtime.gather_rows(self.data._bin, offsets, ctx + 1, inputs.numpy(), targets.numpy(), threads=min(rows, 8))
+        return inputs, targets
+
     def get_sequence(self, sample_index, *, epoch=0):
         return self._gather(self.offsets([int(sample_index)], epoch=epoch))[0]
 
@@ -150,6 +162,14 @@ class BinIdxBatchDataset:
         return tokens[:-1], tokens[1:]
 
     def get_batch(self, step, *, epoch=0, pin_memory=False):
+        from ..utils import host_runtime
+
+        if host_runtime.available():
+            inputs, targets = self._gather_native(self.step_offsets(step, epoch=epoch), pin_memory)
+            mask = self._mask.clone()
+            if pin_memory and torch.cuda.is_available():
+                mask = mask.pin_memory()
+            return {"input_ids": inputs, "target_ids": targets, "mask": mask}
         tok = torch.from_numpy(self._gather(self.step_offsets(step, epoch=epoch)))
         batch = {"input_ids": tok[:, :-1].contiguous(), "target_ids": tok[:, 1:].contiguous(), "mask": self._mask.clone()}
         if pin_memory and torch.cuda.is_available():

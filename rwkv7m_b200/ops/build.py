@@ -1,4 +1,4 @@
-"""Builds the sm_100a extension in-tree (``rwkv7m_b200/_C*.so``).
+"""Builds the sm_100a extension in-tree (``rwkv7m_b200/_C*.so``) and the host runtime library (``rwkv7m_b200/_host.so``).
 
 The kernels are compiled with ``-gencode arch=compute_100a,code=sm_100a`` only;
 nvcc cross-compiles them without a GPU.  ``load_extension()`` imports the built
@@ -47,6 +47,9 @@ def _stale(so: Path) -> bool:
 def build_extension(verbose: bool = False, force: bool = False):
     """Compile (if needed) and import the extension.  Needs nvcc; no GPU required."""
     global _module
+    from ..utils.host_runtime import build_host_runtime
+
+    build_host_runtime(force=force)      # plain C++ (tokenizer trie, batch gather): one g++ call
     so = _so_path()
     if so is not None and not force and not _stale(so):
         return load_extension()

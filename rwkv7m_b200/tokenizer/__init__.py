@@ -1,3 +1,3 @@
-from .rwkv_tokenizer import RWKVTokenizer, default_vocab_path, tokenizer_metadata
+from .rwkv_tokenizer import RWKVTokenizer, Trie, default_vocab_path, tokenizer_metadata
 
-__all__ = ["RWKVTokenizer", "default_vocab_path", "tokenizer_metadata"]
+__all__ = ["RWKVTokenizer", "Trie", "default_vocab_path", "tokenizer_metadata"]
