@@ -172,12 +172,26 @@ def _check_checkpoints(issues, output_dir, s):
             continue
         if payload.get("format") != "rwkv7m_train_checkpoint":
             issues.add("error", "checkpoint_format_invalid", f"unexpected checkpoint format {payload.get('format')!r}", c)
-        if payload.get("step") != _checkpoint_step(c):
+        step = payload.get("step")
+        if isinstance(step, bool) or not isinstance(step, int) or step < 0:
+            issues.add("error", "checkpoint_step_invalid", f"checkpoint.json step is not a non-negative integer: {step!r}", c)
+            step = None
+        elif step != _checkpoint_step(c):
             issues.add("error", "checkpoint_step_mismatch",
-                       f"directory says step {_checkpoint_step(c)} but checkpoint.json says {payload.get('step')}", c)
+                       f"directory says step {_checkpoint_step(c)} but checkpoint.json says {step}", c)
+        position = payload.get("dataset_position")
+        if isinstance(position, dict) and position.get("step") is not None:
+            pos = position["step"]
+            if isinstance(pos, bool) or not isinstance(pos, int):
+                issues.add("error", "checkpoint_dataset_position_invalid", f"dataset_position step is not an integer: {pos!r}", c)
+            elif step is not None and pos != step:
+                issues.add("error", "checkpoint_dataset_position_mismatch",
+                           f"dataset_position says step {pos} but the checkpoint was taken at step {step}", c)
         if not (c / "model.safetensors").exists():
             issues.add("error", "checkpoint_model_missing", "model.safetensors is missing", c)
         backend = payload.get("backend", "single")
+        if backend not in ("single", "sharded"):
+            issues.add("error", "checkpoint_backend_unknown", f"checkpoint.json names an unknown backend {backend!r}", c)
         if not (c / "train_state.safetensors").exists():
             issues.add("error", "checkpoint_train_state_missing", "train_state.safetensors is missing", c)
         if backend == "sharded":

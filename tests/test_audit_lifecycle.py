@@ -77,7 +77,24 @@ def test_damaged_runs_are_flagged(finished_run, tmp_path):
     assert "summary_not_completed" in c and "run_config_invalid" in c and not rep.ok
     assert audit_cli.main([str(bad3), "--require-complete"]) == 1
 
-    # 4. empty directory
+    # 4. checkpoint.json that contradicts itself: an unknown backend, a step that is no integer, a dataset position that
+    #    is not the checkpoint's step
+    bad4 = tmp_path / "bad_payload"
+    shutil.copytree(finished_run, bad4)
+    ckpts = sorted(p for p in bad4.iterdir() if p.name.startswith("ckpt-"))
+    first = json.loads((ckpts[0] / "checkpoint.json").read_text())
+    first["backend"] = "tape"
+    first["dataset_position"] = {"step": int(first["step"]) + 1}
+    (ckpts[0] / "checkpoint.json").write_text(json.dumps(first))
+    last = json.loads((ckpts[-1] / "checkpoint.json").read_text())
+    last["step"] = "four"
+    last["dataset_position"] = {"step": 4.5}
+    (ckpts[-1] / "checkpoint.json").write_text(json.dumps(last))
+    c = codes(audit_distributed_run(bad4))
+    assert {"checkpoint_backend_unknown", "checkpoint_dataset_position_mismatch", "checkpoint_step_invalid",
+            "checkpoint_dataset_position_invalid"} <= c
+
+    # 5. empty directory
     empty = tmp_path / "empty"
     empty.mkdir()
     assert "run_summary_missing" in codes(audit_distributed_run(empty))
