@@ -5,7 +5,7 @@ Directory layout and ``checkpoint.json`` fields follow the reference
 onto this framework as follows: ``single`` (alias ``flax``) lets rank 0 write
 the complete train state after gathering any sharded Adam moments; ``sharded``
 (alias ``orbax``) lets every rank write its own optimizer shard and runtime
-state next to rank 0's model files, and needs the same world size to restore.
+state next to rank 0's model files; a restore may use another world size.
 """
 
 from __future__ import annotations
@@ -243,33 +243,37 @@ def restore_distributed_train_state(checkpoint_dir, train_state_template, proces
         return train_state_template, DistributedCheckpointPayload(
             config, payload, int(payload.get("step", 0)), payload.get("dataset_position"))
     if payload.get("backend", "single") == "sharded":
-        if int(payload.get("world_size", 1)) != world:
-            raise ValueError(
-                f"sharded checkpoint was written by {payload.get('world_size')} ranks; restore with the same count "
-                "or convert it by saving with the 'single' backend"
-            )
+        # Every rank of the saving run wrote the slice [begin, end) of both moments that it owned.  The restoring run may
+        # have another process count or another layout (replicated moments, or other slice bounds): each process reads
+        # the files whose ranges overlap what it needs.
+        saved_world = int(payload.get("world_size", 1))
         tensors = load_file(str(checkpoint_dir / TRAIN_STATE_FILE))
         from_portable(train_state_template.model,
                       {k[len("model/"):]: v for k, v in tensors.items() if k.startswith("model/")}, strict=True)
         opt.count = int(tensors["optimizer/count"].reshape(-1)[0])
-        part = load_file(str(checkpoint_dir / f"optimizer_shard.rank{rank:05d}.safetensors"))
-        begin, end = (int(x) for x in part["range"].tolist())
         if shard is not None:
-            m, v, b2, e2 = shard
-            if (b2, e2) != (begin, end):
-                raise ValueError("optimizer shard bounds differ from the checkpoint")
-            m.copy_(part["exp_avg"])
-            v.copy_(part["exp_avg_sq"])
+            dst_m, dst_v, need_b, need_e = shard
         else:
-            pieces_m = torch.zeros_like(opt.exp_avg)
-            pieces_v = torch.zeros_like(opt.exp_avg_sq)
-            for r in range(world):
-                p = load_file(str(checkpoint_dir / f"optimizer_shard.rank{r:05d}.safetensors"))
-                b, e = (int(x) for x in p["range"].tolist())
-                pieces_m[b:e].copy_(p["exp_avg"])
-                pieces_v[b:e].copy_(p["exp_avg_sq"])
-            opt.exp_avg.copy_(pieces_m)
-            opt.exp_avg_sq.copy_(pieces_v)
+            dst_m, dst_v, need_b, need_e = opt.exp_avg, opt.exp_avg_sq, 0, int(opt.exp_avg.numel())
+        dst_m.zero_()        # the flat store ends in padding up to a multiple of the process count: zeros on both sides
+        dst_v.zero_()
+        covered, saved_total = 0, 0
+        for r in range(saved_world):
+            path = checkpoint_dir / f"optimizer_shard.rank{r:05d}.safetensors"
+            if not path.exists():
+                raise FileNotFoundError(f"sharded checkpoint is missing {path.name}")
+            part = load_file(str(path))
+            b, e = (int(x) for x in part["range"].tolist())
+            saved_total = max(saved_total, e)
+            lo, hi = max(b, need_b), min(e, need_e)
+            if lo >= hi:
+                continue
+            dst_m[lo - need_b:hi - need_b].copy_(part["exp_avg"][lo - b:hi - b])
+            dst_v[lo - need_b:hi - need_b].copy_(part["exp_avg_sq"][lo - b:hi - b])
+            covered += hi - lo
+        expected = max(0, min(need_e, saved_total) - min(need_b, saved_total))
+        if covered != expected:
+            raise ValueError(f"the optimizer shards cover {covered} of the {expected} saved moment elements this process needs")
         opt.flat.sync_compute()
     else:
         if shard is not None:

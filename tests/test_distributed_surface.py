@@ -262,3 +262,44 @@ def test_placed_objects_on_two_processes_match_one_process(tmp_path, use_model_a
     assert res["first_eval"] == pytest.approx(first, rel=1e-4) and res["last_eval"] == pytest.approx(last, rel=1e-4)
     worst = max(float((ref[n] - res["params"][n]).abs().max()) for n in ref)
     assert worst < 5e-5, worst
+
+
+def _sharded_save_worker(rank, world, port, directory, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    batch = _batch()
+    rt, ts = R.create_train_runtime(3, _cfg(), batch_size=2, total_steps=20, shard_multiple=world * 8)
+    objects = P.replicate_train_objects(rt, ts)
+    for _ in range(2):
+        objects, _ = P.train_global_batch_data_parallel(objects, batch)
+    info = P.process_info()
+    P.save_orbax_train_state(directory, objects.train_state, process_info=info)
+    objects, m = P.train_global_batch_data_parallel(objects, batch)      # what a faithful restore has to reproduce
+    if rank == 0:
+        torch.save({"next_loss": float(m["loss"]), "exp_avg": objects.train_state.optimizer.exp_avg.clone()}, out)
+    dist.barrier()
+    os._exit(0)
+
+
+def test_sharded_train_state_restores_under_another_process_count(tmp_path):
+    """Two data-parallel processes save with the sharded backend (each writes half of both moments); one process restores
+    by reading both halves (its flat store is padded to another multiple, so the lengths differ by padding) and its next
+    step gives the loss that the saving run saw next."""
+    d, out = tmp_path / "ck", str(tmp_path / "w.pt")
+    mp.spawn(_sharded_save_worker, args=(2, _free_port(), str(d), out), nprocs=2, join=True)
+    saved = torch.load(out)
+    files = sorted(p.name for p in d.iterdir() if p.name.startswith("optimizer_shard"))
+    assert files == ["optimizer_shard.rank00000.safetensors", "optimizer_shard.rank00001.safetensors"]
+    rt, ts = R.create_train_runtime(9, _cfg(), batch_size=4, total_steps=20)      # other seed, other padding
+    ts = P.load_orbax_train_state(d, ts, process_info={"process_index": 0, "process_count": 1})
+    assert int(ts.step) == 2
+    objects = P.replicate_train_objects(rt, ts)
+    objects, m = P.train_global_batch_data_parallel(objects, _batch())
+    assert float(m["loss"]) == pytest.approx(saved["next_loss"], rel=1e-5)
+    n = min(ts.optimizer.exp_avg.numel(), saved["exp_avg"].numel())
+    assert torch.allclose(ts.optimizer.exp_avg[:n], saved["exp_avg"][:n], atol=1e-6)
+    # a missing shard file is an error, not zeros
+    (d / "optimizer_shard.rank00001.safetensors").unlink()
+    rt2, ts2 = R.create_train_runtime(9, _cfg(), batch_size=4, total_steps=20)
+    with pytest.raises(FileNotFoundError):
+        P.load_orbax_train_state(d, ts2, process_info={"process_index": 0, "process_count": 1})
