@@ -15,6 +15,7 @@ import torch
 from .config import ModelConfig, load_model_config, tiny_config
 from .data import BinIdxBatchDataset, create_binidx_dataset
 from .infer.generate import decode_one, generate, prefill
+from .io.names import PortableParams
 from .io.safetensors_io import load_params_into_model
 from .models.model import ScreenedRWKVModel, initialize_model
 from .state import init_rwkv_state, init_screen_state
@@ -59,7 +60,7 @@ def _make_runtime(model, config, batch_size):
                                      device=device)
     return RWKV7MRuntime(
         model=model,
-        variables={"params": dict(model.named_parameters())},
+        variables={"params": PortableParams(model)},
         rwkv_state=rwkv_state,
         screen_state=screen_state,
         config=config,
@@ -141,7 +142,7 @@ def load_runtime_params(runtime: RWKV7MRuntime, params):
     load_params_into_model(runtime.model, params)
     if not runtime.model.training:
         _attach_inference_weights(runtime.model)
-    runtime.variables = {"params": dict(runtime.model.named_parameters())}
+    runtime.variables = {"params": PortableParams(runtime.model)}
     return runtime
 
 

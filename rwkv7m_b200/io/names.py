@@ -14,6 +14,8 @@ Internally matrices are ``[out,in]`` and the six token-shift mixes are one
 
 from __future__ import annotations
 
+from collections.abc import Mapping
+
 import torch
 
 from ..config import ModelConfig
@@ -137,7 +139,7 @@ def flatten(tree: dict, prefix: str = "") -> dict:
     out = {}
     for key, value in tree.items():
         name = f"{prefix}/{key}" if prefix else str(key)
-        if isinstance(value, dict):
+        if isinstance(value, Mapping):
             out.update(flatten(value, name))
         else:
             out[name] = value
@@ -146,9 +148,9 @@ def flatten(tree: dict, prefix: str = "") -> dict:
 
 def _flat_portable(params: dict) -> dict:
     """A nested tree or a ``/``-joined mapping as the flat ``a/b/c -> tensor`` mapping (a top-level ``params`` is unwrapped)."""
-    if set(params) == {"params"} and isinstance(params["params"], dict):
+    if set(params) == {"params"} and isinstance(params["params"], Mapping):
         params = params["params"]
-    return flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
+    return flatten(params) if any(isinstance(v, Mapping) for v in params.values()) else dict(params)
 
 
 def assert_portable_parameter_contract(model, params: dict) -> None:
@@ -186,3 +188,36 @@ def load_portable_params(model, params: dict):
 def portable_params(model) -> dict:
     """The model's parameters as the nested portable tree."""
     return nest(to_portable(model))
+
+
+class PortableParams(Mapping):
+    """``runtime.variables["params"]``: the model's parameters as the nested portable tree (what the reference keeps in that
+    place, so ``save_model_safetensors(path, runtime.variables["params"], runtime.config)`` writes an exchangeable file).
+    The tree is built on first use (host copies of every tensor) and again after ``refresh()``; ``model`` stays reachable
+    for live access."""
+
+    def __init__(self, model):
+        self.model = model
+        self._tree = None
+
+    def _built(self) -> dict:
+        if self._tree is None:
+            self._tree = nest(to_portable(self.model))
+        return self._tree
+
+    def refresh(self):
+        self._tree = None
+        return self
+
+    def __getitem__(self, key):
+        return self._built()[key]
+
+    def __iter__(self):
+        return iter(self._built())
+
+    def __len__(self):
+        return len(self._built())
+
+    def named(self) -> dict:
+        """Live parameters under their internal names."""
+        return dict(self.model.named_parameters())

@@ -7,6 +7,8 @@ Header metadata keys match src/rwkv7m/io/safetensors.py:20-46 of the reference
 
 from __future__ import annotations
 
+from collections.abc import Mapping
+
 import json
 from pathlib import Path
 
@@ -55,7 +57,7 @@ def save_model_safetensors(path, params, config: ModelConfig, *, metadata=None, 
     if isinstance(params, torch.nn.Module):
         flat = to_portable(params)
     else:
-        flat = flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
+        flat = flatten(params) if any(isinstance(v, Mapping) for v in params.values()) else dict(params)
         flat = {k: torch.as_tensor(v).contiguous().cpu() for k, v in flat.items()}
     meta = standard_metadata(config, tokenizer_metadata)
     if metadata:
@@ -81,5 +83,5 @@ def load_model_safetensors(path):
 
 def load_params_into_model(model, params, *, strict=True):
     """Load a portable tree (nested or flat) into ``model`` in place."""
-    flat = flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
+    flat = flatten(params) if any(isinstance(v, Mapping) for v in params.values()) else dict(params)
     return from_portable(model, flat, strict=strict)

@@ -57,6 +57,19 @@ class Mesh:
     def size(self) -> int:
         return self.data_size * self.model_size
 
+    @property
+    def shape(self) -> dict:
+        """Axis name -> length, in axis order (what ``dict(mesh.shape)`` gives in the reference's reports)."""
+        lengths = {"data": self.data_size, "model": self.model_size}
+        return {name: lengths[name] for name in self.axis_names}
+
+    @property
+    def devices(self):
+        """Process ranks laid out as the ``data x model`` grid (a NumPy array; ``mesh.devices.size`` is the device count)."""
+        import numpy as np
+
+        return np.arange(self.size).reshape(self.data_size, self.model_size)
+
     def coords(self, rank: int) -> tuple:
         if not 0 <= rank < self.size:
             raise ValueError(f"rank {rank} outside mesh of {self.size}")

@@ -804,3 +804,28 @@ def test_small_helpers_under_the_reference_names():
     loss, _ = nnx_model_loss(ts.model, batch, rt.initial_rwkv_state, rt.initial_screen_state, phase="read_screening_only",
                              include_l2wrap=False)
     assert float(m["loss"]) == pytest.approx(float(loss.detach()), rel=1e-5) and ts.model.training
+
+
+def test_runtime_variables_hold_the_portable_tree(tmp_path):
+    """``runtime.variables["params"]`` is the nested portable tree, as in the reference's README: saved with
+    ``save_model_safetensors`` it loads into another runtime through ``load_model_safetensors`` + ``load_runtime_params``
+    and gives the same logits; after an update ``refresh()`` brings the snapshot up to date."""
+    cfg = R.tiny_config()
+    rt = R.create_runtime(0, cfg, batch_size=1)
+    tree = rt.variables["params"]
+    assert "token_embedding" in tree and tree["lm_head"]["kernel"].shape == (cfg.d_model, cfg.vocab_size)
+    assert set(tree.named()) == {n for n, _ in rt.model.named_parameters()}
+    path = tmp_path / "model.safetensors"
+    R.save_model_safetensors(path, rt.variables["params"], rt.config)
+    params, config, metadata = R.load_model_safetensors(path)
+    assert config.d_model == cfg.d_model and metadata["format"] == "rwkv7m"
+    other = R.load_runtime_params(R.create_runtime(5, cfg, batch_size=1), params)
+    ids = torch.tensor([[1, 2, 3, 4]], dtype=torch.int32)
+    a, _ = R.infer_prefill(rt, ids)
+    b, _ = R.infer_prefill(other, ids)
+    assert torch.equal(a, b)
+    assert torch.equal(other.variables["params"]["lm_head"]["kernel"], tree["lm_head"]["kernel"])
+    with torch.no_grad():
+        rt.model.head.weight.add_(1.0)
+    assert not torch.equal(tree["lm_head"]["kernel"], rt.model.head.weight.t().cpu())     # a snapshot ...
+    assert torch.equal(tree.refresh()["lm_head"]["kernel"], rt.model.head.weight.detach().t().cpu())   # ... until refreshed

@@ -303,3 +303,33 @@ def test_sharded_train_state_restores_under_another_process_count(tmp_path):
     rt2, ts2 = R.create_train_runtime(9, _cfg(), batch_size=4, total_steps=20)
     with pytest.raises(FileNotFoundError):
         P.load_orbax_train_state(d, ts2, process_info={"process_index": 0, "process_count": 1})
+
+
+def test_readme_skeleton_of_the_reference_runs_with_the_names_translated(tiny_binidx, tmp_path):
+    """The distributed example of the reference's README (its "TPU/distributed skeleton", "replicate_train_objects" and
+    "train_batch_data_parallel" snippets) with ``rwkv7m.distributed`` read as ``rwkv7m_b200.parallel``, plus the artifact
+    boundary ``rwkv7m.backends.torch`` -> ``rwkv7m_b200.backends.torch``."""
+    from rwkv7m_b200.parallel import (compute_batch_layout, create_host_binidx_dataset, data_parallel_sharding,
+                                      host_batch_to_global_arrays, make_1d_mesh, replicate_train_objects,
+                                      train_batch_data_parallel)
+
+    mesh = make_1d_mesh("data")
+    assert mesh.devices.size == 1 and dict(mesh.shape) == {"data": 1, "model": 1}
+    layout = compute_batch_layout(2, process_count=1, local_device_count=mesh.devices.size)
+    dataset = create_host_binidx_dataset(tiny_binidx, ctx_len=4, global_batch_size=2)
+    batch = host_batch_to_global_arrays(dataset.get_batch(0), data_parallel_sharding(mesh), dataset.layout)
+    assert batch["input_ids"].shape == (2, 4) and layout == dataset.layout
+    cfg = R.tiny_config(vocab_size=300, d_model=32, n_layers=2, n_heads=2, head_size=16)
+    runtime, train_state = R.create_train_runtime(0, cfg, batch_size=2, total_steps=5)
+    objects = replicate_train_objects(runtime, train_state, mesh=mesh)
+    objects, metrics = train_batch_data_parallel(objects, dataset.get_batch(0), dataset.layout)
+    assert float(metrics["loss"]) > 0 and int(objects.train_state.step) == 1
+    dataset.close()
+
+    from rwkv7m_b200.backends.torch import load_torch_safetensors
+
+    R.save_model_safetensors(tmp_path / "model.safetensors", runtime.variables["params"], runtime.config)
+    state_dict, config, metadata = load_torch_safetensors(tmp_path / "model.safetensors")
+    assert config.d_model == 32 and metadata["format"] == "rwkv7m" and all("/" not in k for k in state_dict)
+    raw, _, _ = load_torch_safetensors(tmp_path / "model.safetensors", rename_keys=False)
+    assert any("/" in k for k in raw)
