@@ -293,8 +293,6 @@ def run_distributed_training(args):
     if use_tp:
         if mode in ("fused", "zero3"):
             raise ValueError("--dp-mode fused / zero3 are not combined with a model axis; use allreduce")
-        if normalize_backend(args.checkpoint_backend) != "single":
-            raise ValueError("a tensor-parallel run writes checkpoints with --checkpoint-backend single")
         if args.ctx_len % mesh.model_size != 0:
             raise ValueError("--ctx-len must be divisible by the model axis (the residual stream is sharded over time)")
         from ..parallel.mesh import new_subgroups

@@ -91,6 +91,22 @@ def to_portable(model) -> dict:
     return out
 
 
+def internal_to_portable(named: dict, config: ModelConfig) -> dict:
+    """A mapping of full tensors under the model's internal names as the portable ``name -> tensor`` mapping (what
+    ``to_portable`` gives for a model; used where the full tensors exist only as gathered copies)."""
+    out = {}
+    for internal, portable, tf in portable_entries(config):
+        t = named[internal].detach()
+        if tf == "T":
+            t = t.t()
+        elif tf == "vec3":
+            t = t.reshape(1, 1, -1)
+        elif tf.startswith("mix:"):
+            t = t[int(tf[4:])]
+        out[portable] = t.contiguous().cpu()
+    return out
+
+
 def from_portable(model, tensors: dict, *, strict: bool = True):
     """Copy a portable mapping into the model in place.  Returns the list of
     portable names that were not consumed."""

@@ -139,10 +139,12 @@ def _save_checkpoint_dir(checkpoint_dir, train_state, config, process_info, *, b
     rank, world = _world(process_info)
     checkpoint_dir = Path(checkpoint_dir)
     tp = train_state.extras.get("tp")
+    if tp is not None and backend == "sharded":
+        return _save_tensor_parallel_shards(checkpoint_dir, train_state, config, process_info, tp, rng_key=rng_key,
+                                            dataset_position=dataset_position, metadata=metadata,
+                                            runtime_state=runtime_state)
     if tp is not None:
         # tensor-parallel shards are gathered into full tensors: the files are those of an un-sharded run
-        if backend != "single":
-            raise ValueError("a tensor-parallel train state is saved with the 'single' checkpoint backend")
         with tp.materialized(train_state):
             if rank == 0:
                 save_train_checkpoint(checkpoint_dir, train_state, config, rng_key=rng_key,
@@ -217,6 +219,74 @@ def _save_checkpoint_dir(checkpoint_dir, train_state, config, process_info, *, b
     return checkpoint_dir
 
 
+TP_SHARD_FILE = "tp_state.rank{rank:05d}.safetensors"
+
+
+def _save_tensor_parallel_shards(checkpoint_dir, train_state, config, process_info, tp, *, rng_key, dataset_position,
+                                 metadata, runtime_state):
+    """Sharded backend for a tensor-parallel train state: every rank of one model-parallel group writes its own flat fp32
+    master buffer and both moment buffers (``tp_state.rank<r>``, r = position on the model axis) without gathering
+    anything, so the resume is exact and needs the same model-axis size; rank 0 adds ``checkpoint.json`` and a gathered
+    ``model.safetensors`` for exchange with other runtimes.  With a data axis the groups hold identical state and only
+    the first one writes."""
+    rank, world = _world(process_info)
+    opt = train_state.optimizer
+    data_index = rank // tp.world
+    if rank == 0:
+        checkpoint_dir.mkdir(parents=True, exist_ok=True)
+    _barrier(process_info)
+    if data_index == 0:
+        tensors = {
+            "master": opt.flat.master.detach().contiguous().cpu(),
+            "exp_avg": opt.exp_avg.detach().contiguous().cpu(),
+            "exp_avg_sq": opt.exp_avg_sq.detach().contiguous().cpu(),
+            "count": torch.tensor([opt.count], dtype=torch.int64),
+        }
+        save_file(tensors, str(checkpoint_dir / TP_SHARD_FILE.format(rank=tp.rank)))
+    if runtime_state is not None:   # recurrent state holds this rank's heads and this data group's rows
+        save_runtime_state(checkpoint_dir / f"runtime_state.rank{rank:05d}.safetensors", runtime_state)
+    full = tp.gather_full_parameters(train_state.model)      # collective on every rank of a model-parallel group
+    if rank == 0:
+        from ..io.names import internal_to_portable
+
+        flat = internal_to_portable({k: v.detach().cpu() for k, v in full.items()}, config)
+        save_model_safetensors(checkpoint_dir / MODEL_SAFETENSORS, flat, config,
+                               metadata={"checkpoint_step": int(train_state.step), **(metadata or {})})
+        payload = {
+            "format": "rwkv7m_train_checkpoint", "format_version": 1, "backend": "sharded", "world_size": world,
+            "model_parallel": tp.world, "layout": "tensor_parallel", "vocab_parallel": bool(tp.vocab_parallel),
+            "step": int(train_state.step), "config": model_config_to_dict(config),
+            "rng_key": None if rng_key is None else [int(x) for x in torch.as_tensor(rng_key).reshape(-1).tolist()],
+            "dataset_position": dataset_position, "metadata": metadata or {},
+        }
+        with open(checkpoint_dir / CHECKPOINT_JSON, "w", encoding="utf-8") as f:
+            json.dump(payload, f, indent=2, sort_keys=True)
+            f.write("\n")
+    _barrier(process_info)
+    return checkpoint_dir
+
+
+def _restore_tensor_parallel_shards(checkpoint_dir, train_state, payload, tp):
+    if payload.get("layout") != "tensor_parallel":
+        raise ValueError("this sharded checkpoint was written by a data-parallel run; restore it without a model axis")
+    if int(payload.get("model_parallel", 0)) != tp.world or bool(payload.get("vocab_parallel", False)) != bool(tp.vocab_parallel):
+        raise ValueError(
+            f"tensor-parallel shards were written for a model axis of {payload.get('model_parallel')} "
+            f"(vocab_parallel={payload.get('vocab_parallel')}); restore with the same layout or save with the 'single' backend")
+    path = checkpoint_dir / TP_SHARD_FILE.format(rank=tp.rank)
+    if not path.exists():
+        raise FileNotFoundError(f"sharded checkpoint is missing {path.name}")
+    part = load_file(str(path))
+    opt = train_state.optimizer
+    if part["master"].numel() != opt.flat.master.numel():
+        raise ValueError("the flat parameter store of this rank has another size than the saved shard")
+    opt.flat.master.copy_(part["master"])
+    opt.exp_avg.copy_(part["exp_avg"])
+    opt.exp_avg_sq.copy_(part["exp_avg_sq"])
+    opt.count = int(part["count"].reshape(-1)[0])
+    opt.flat.sync_compute()
+
+
 def _patch_json(checkpoint_dir, extra: dict):
     path = Path(checkpoint_dir) / CHECKPOINT_JSON
     with open(path, "r", encoding="utf-8") as f:
@@ -236,12 +306,17 @@ def restore_distributed_train_state(checkpoint_dir, train_state_template, proces
     opt = train_state_template.optimizer
     shard = _moment_shard(train_state_template)
     tp = train_state_template.extras.get("tp")
+    if tp is not None and payload.get("backend", "single") == "sharded":
+        _restore_tensor_parallel_shards(checkpoint_dir, train_state_template, payload, tp)
+        return train_state_template, DistributedCheckpointPayload(
+            config, payload, int(payload.get("step", 0)), payload.get("dataset_position"))
     if tp is not None:
-        if payload.get("backend", "single") == "sharded":
-            raise ValueError("a tensor-parallel run restores from a 'single' checkpoint")
         tp.load_full_state(train_state_template, lambda ts: load_train_checkpoint(checkpoint_dir, ts))
         return train_state_template, DistributedCheckpointPayload(
             config, payload, int(payload.get("step", 0)), payload.get("dataset_position"))
+    if payload.get("backend", "single") == "sharded" and payload.get("layout") == "tensor_parallel":
+        raise ValueError("this checkpoint holds tensor-parallel shards; restore it on a model axis of "
+                         f"{payload.get('model_parallel')} or re-save it with the 'single' backend")
     if payload.get("backend", "single") == "sharded":
         # Every rank of the saving run wrote the slice [begin, end) of both moments that it owned.  The restoring run may
         # have another process count or another layout (replicated moments, or other slice bounds): each process reads
