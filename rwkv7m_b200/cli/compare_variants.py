@@ -14,6 +14,9 @@ Sub-commands:
               baseline's shape (``rwkv7m-train-upstream-single-gpu``)
   summarize   per-variant final / best eval loss, eval-loss AUC over tokens, first step / tokens /
               seconds at which each loss target is reached, mean tokens/s; CSV + JSON
+  matrix      the whole experiment in one command (``cli/compare_matrix.py``): size profile, one run directory per
+              seed with provenance files and replay commands, optional core-parity check, the reference-named
+              summary tables, and a cross-seed aggregate
 
 Nothing here needs network access: the official repository's own CUDA model is replaced by the plain-PyTorch x070
 network of ``backends/upstream_x070.py``.
@@ -139,16 +142,22 @@ def plan_variants(passthrough, mechanism_phase="read_write") -> dict:
     return {"variants": rows, "param_target": target, "screening_extra_params": mech - baseline}
 
 
-def run_variants(root, passthrough, *, mechanism_phase="read_write", variants=VARIANT_ORDER, with_upstream=False) -> dict:
+def write_parameter_counts(root, plan: dict):
     root = Path(root)
     root.mkdir(parents=True, exist_ok=True)
-    plan = plan_variants(passthrough, mechanism_phase)
     with open(root / "parameter_counts.csv", "w", newline="") as f:
         w = csv.writer(f)
         w.writerow(["variant", "trainable_params", "d_ffn", "use_screening", "phase", "note"])
         for name in VARIANT_ORDER:
             r = plan["variants"][name]
             w.writerow([name, r["trainable_params"], r["d_ffn"], r["use_screening"], r["phase"], r["note"]])
+
+
+def run_variants(root, passthrough, *, mechanism_phase="read_write", variants=VARIANT_ORDER, with_upstream=False) -> dict:
+    root = Path(root)
+    root.mkdir(parents=True, exist_ok=True)
+    plan = plan_variants(passthrough, mechanism_phase)
+    write_parameter_counts(root, plan)
     summaries = {}
     for name in variants:
         r = plan["variants"][name]
@@ -217,6 +226,8 @@ def summarize(root, *, tokens_per_step, loss_targets=()) -> dict:
             "train_steps": len(train), "final_train_loss": float(train[-1]["loss"]) if train else None,
             "final_eval_loss": float(evals[-1]["loss"]) if evals else None,
             "best_eval_loss": min((float(r["loss"]) for r in evals), default=None),
+            "first_eval_loss": float(evals[0]["loss"]) if evals else None,
+            "eval_token_span": (int(evals[-1]["step"]) - int(evals[0]["step"])) * tokens_per_step if len(evals) > 1 else None,
             "eval_loss_auc_over_tokens": auc, "eval_loss_auc_mean": auc_mean,
             "tokens_per_sec_median": statistics.median(tps) if tps else None, "train_seconds": total_seconds,
             "targets": {f"{t:g}": _first_hit(evals, float(t), seconds, tokens_per_step) for t in loss_targets},
@@ -245,7 +256,7 @@ def summarize(root, *, tokens_per_step, loss_targets=()) -> dict:
 
 def main(argv=None):
     p = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    p.add_argument("command", choices=["corpus", "plan", "run", "summarize"])
+    p.add_argument("command", choices=["corpus", "plan", "run", "summarize", "matrix"])
     p.add_argument("--corpus-file", default=None)
     p.add_argument("--validation-fraction", type=float, default=0.05)
     p.add_argument("--corpus-epochs", type=int, default=1)
@@ -256,6 +267,22 @@ def main(argv=None):
     p.add_argument("--loss-targets", type=float, nargs="*", default=[])
     p.add_argument("--tokens-per-step", type=int, default=None)
     args, passthrough = p.parse_known_args(argv)
+    if args.command == "matrix":
+        from .compare_matrix import add_matrix_arguments, run_matrix
+
+        # the matrix has flags of its own that the other sub-commands hand to the trainer untouched: parsed in a second step
+        mp = argparse.ArgumentParser(prog="rwkv7m-compare-variants matrix", description="The whole comparison in one command.")
+        add_matrix_arguments(mp)
+        margs, passthrough = mp.parse_known_args(passthrough)
+        for key, value in vars(margs).items():
+            setattr(args, key, value)
+        out = run_matrix(args, passthrough)
+        brief = {"run_id": out["run_id"], "seeds": {str(k): {"run_root": v["run_root"], "status": v.get("status")}
+                                                    for k, v in out["seeds"].items()}}
+        if "aggregate" in out:
+            brief["aggregate"] = {name: row["final_eval_loss"] for name, row in out["aggregate"].items()}
+        print(json.dumps(brief, indent=2))
+        return 0
     if args.command == "corpus":
         if args.corpus_file is None:
             p.error("corpus needs --corpus-file (JSONL with a text field, or one document per line)")

@@ -1,6 +1,8 @@
 """Command-line tools run in-process on tiny models (CPU)."""
 
+import csv
 import json
+import os
 from pathlib import Path
 
 import numpy as np
@@ -311,3 +313,56 @@ def test_model_axis_run_with_the_sharded_backend_resumes_exactly(tiny_binidx, tm
             "--print-every", "0", "--output-dir", str(tmp_path / "alone"), "--device", "cpu"] + tiny
     with pytest.raises(ValueError, match="tensor-parallel shards"):
         train_binidx_distributed.run_distributed_training(train_binidx_distributed.parse_args(argv))
+
+
+def test_comparison_matrix_profiles_seeds_provenance_and_tables(tiny_binidx, tmp_path, capsys):
+    """``rwkv7m-compare-variants matrix``: what the reference's wrapper scripts do (scripts/compare_minipile.sh,
+    comparison.sh:925-1245): a size profile with overrides, one run directory per seed with ``parameters.env``,
+    ``protocol.md``, replayable ``commands.sh`` and ``parameter_counts.csv``; ``--no-run`` stops there; a real run adds the
+    three summary tables, the core-parity report and the cross-seed aggregate."""
+    from rwkv7m_b200.cli import compare_matrix, compare_variants
+
+    assert compare_matrix.PROFILES["small"]["d_model"] == 768 and compare_matrix.PROFILES["smoke"]["steps"] == 50
+    tiny = ["--d-model", "32", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64", "--n-layers", "2", "--d-slot", "16",
+            "--d-k", "8", "--d-v", "8", "--n-slots", "4", "--device", "cpu"]
+    # 1. dry run of the full-size plan: nothing is trained, the provenance files and exact parameter counts exist
+    root = tmp_path / "plan_only"
+    assert compare_variants.main(["matrix", "--profile", "smoke", "--no-run", "--root", str(root), "--run-id", "dry",
+                                  "--seeds", "7"]) == 0
+    run = root / "dry-seed7"
+    assert {p.name for p in run.iterdir()} == {"parameters.env", "protocol.md", "commands.sh", "parameter_counts.csv"}
+    env = dict(l.split("=", 1) for l in (run / "parameters.env").read_text().splitlines())
+    assert env["PROFILE"] == "smoke" and env["SEED"] == "7" and "--d-model 256" in env["TRAINER_FLAGS"]
+    commands = (run / "commands.sh").read_text()
+    assert commands.count("rwkv7m-train-binidx-dp") == 4 and "--no-screening" in commands and os.access(run / "commands.sh", os.X_OK)
+    counts = {r["variant"]: int(r["trainable_params"]) for r in csv.DictReader(open(run / "parameter_counts.csv"))}
+    assert counts["local_param_control"] >= counts["local_mechanism"] > counts["local_core_baseline"]
+    capsys.readouterr()
+
+    # 2. two seeds of a tiny model, with the core-parity check
+    root = tmp_path / "runs"
+    argv = ["matrix", "--profile", "smoke", "--seeds", "1", "2", "--root", str(root), "--run-id", "t", "--data-file", tiny_binidx,
+            "--steps", "3", "--ctx-len", "4", "--global-batch-size", "2", "--vocab-size", "300", "--eval-every", "1",
+            "--eval-steps", "1", "--screened-layers", "1", "--loss-targets", "100", "--verify-core-parity"] + tiny
+    assert compare_variants.main(argv) == 0
+    capsys.readouterr()
+    for seed in (1, 2):
+        run = root / f"t-seed{seed}"
+        names = {p.name for p in run.iterdir()}
+        assert {"local_metric_summary.csv", "learning_speed_summary.csv", "learning_target_hits.csv", "summary.json",
+                "upstream_core_parity", *compare_variants.VARIANT_ORDER} <= names
+        assert json.loads((run / "upstream_core_parity" / "parity_report.json").read_text())["passed"] is True
+        rows = list(csv.DictReader(open(run / "local_metric_summary.csv")))
+        assert [r["variant"] for r in rows] == list(compare_variants.VARIANT_ORDER)
+        assert all(int(r["train_steps"]) == 3 and int(r["tokens_seen"]) == 3 * 8 and float(r["final_eval_loss"]) > 0 for r in rows)
+        speed = list(csv.DictReader(open(run / "learning_speed_summary.csv")))
+        assert all(float(r["best_eval_loss"]) <= float(r["final_eval_loss"]) + 1e-9 and float(r["eval_loss_auc_mean"]) > 0 for r in speed)
+        hits = list(csv.DictReader(open(run / "learning_target_hits.csv")))
+        assert {h["target"] for h in hits} >= {"100", "local_core_baseline_final", "local_param_control_final"}
+        assert all(h["hit"] == "1" and int(h["hit_step"]) >= 1 for h in hits if h["target"] == "100")
+    agg = list(csv.DictReader(open(root / "seed_aggregate.csv")))
+    row = next(r for r in agg if r["variant"] == "local_mechanism" and r["metric"] == "final_eval_loss")
+    assert row["n_seeds"] == "2" and float(row["std"]) >= 0 and float(row["mean"]) > 0
+    # the other sub-commands still hand trainer flags through untouched
+    plan = compare_variants.plan_variants(["--vocab-size", "300", "--screened-layers", "1"] + tiny)
+    assert plan["variants"]["local_mechanism"]["trainable_params"] > plan["variants"]["local_core_baseline"]["trainable_params"]
