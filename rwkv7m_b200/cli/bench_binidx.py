@@ -24,6 +24,9 @@ from .common import (
 )
 
 VARIANTS = ("baseline", "screening", "read_write")
+_INT_FLAGS = (("--ctx-len", 128), ("--batch-size", 1), ("--steps", 5), ("--seed", 42), ("--print-every", 1),
+              ("--vocab-size", 65536), ("--d-model", 64), ("--d-ffn", 128), ("--n-layers", 3), ("--n-heads", 4),
+              ("--head-size", 16), ("--d-slot", 32), ("--d-k", 16), ("--d-v", 16), ("--n-slots", 4))
 
 
 def build_config(args, variant) -> ModelConfig:
@@ -83,26 +86,13 @@ def parse_args(argv=None):
     p = argparse.ArgumentParser(description="Train small rwkv7m variants on a binidx file and report tokens/s.")
     p.add_argument("--data-file", required=True)
     add_model_source_args(p)
-    p.add_argument("--ctx-len", type=int, default=128)
-    p.add_argument("--batch-size", type=int, default=1)
-    p.add_argument("--steps", type=int, default=5)
+    add_execution_args(p)
+    for flag, default in _INT_FLAGS:     # run shape, then the hand-built model used when no preset / config file is given
+        p.add_argument(flag, type=int, default=default)
     p.add_argument("--magic-prime", type=int, default=None)
-    p.add_argument("--seed", type=int, default=42)
     p.add_argument("--variants", nargs="+", default=list(VARIANTS))
     p.add_argument("--dtype", choices=["float32", "bfloat16"], default="float32")
-    add_execution_args(p)
-    p.add_argument("--vocab-size", type=int, default=65536)
-    p.add_argument("--d-model", type=int, default=64)
-    p.add_argument("--d-ffn", type=int, default=128)
-    p.add_argument("--n-layers", type=int, default=3)
-    p.add_argument("--n-heads", type=int, default=4)
-    p.add_argument("--head-size", type=int, default=16)
-    p.add_argument("--d-slot", type=int, default=32)
-    p.add_argument("--d-k", type=int, default=16)
-    p.add_argument("--d-v", type=int, default=16)
-    p.add_argument("--n-slots", type=int, default=4)
     p.add_argument("--screened-layers", type=int, nargs="*", default=[])
-    p.add_argument("--print-every", type=int, default=1)
     p.add_argument("--trace-dir", default=None,
                    help="write a Chrome-trace timeline per variant here (torch.profiler; the reported time is then not a benchmark figure)")
     p.add_argument("--device", default="auto")

@@ -1,46 +1,124 @@
-"""``rwkv7m-generate``: text generation from a safetensors checkpoint
-(reference: src/rwkv7m/cli/generate.py:26-45)."""
+"""``rwkv7m-generate``: text generation from a safetensors checkpoint (reference: src/rwkv7m/cli/generate.py:26-45, whose
+flags are kept).  Beyond one prompt: ``--prompt`` may repeat, ``--prompt-file`` adds one prompt per non-empty line,
+``--num-samples`` draws several continuations per prompt (seeds ``seed, seed + 1, ...``), ``--json-out`` records every
+sample with its settings, and a tensor-parallel runtime is used when the command runs under a multi-process launcher with
+``--model-axis-size``."""
 
 from __future__ import annotations
 
 import argparse
+import json
+from pathlib import Path
 
-from ..api import create_runtime, generate_text, load_runtime_params
-from ..io import load_model_safetensors
-from ..tokenizer import RWKVTokenizer
-from .common import parse_args_with_config, pick_device
-from .eval_binidx import resolve_checkpoint_file
+_SAMPLING = (("max_new_tokens", int, 50), ("temperature", float, 1.0), ("top_p", float, 0.9), ("seed", int, 42))
 
 
 def parse_args(argv=None):
+    from .common import parse_args_with_config
+
     p = argparse.ArgumentParser(description="Generate text from an rwkv7m safetensors checkpoint.")
     p.add_argument("--checkpoint", required=True, help="checkpoint directory or model.safetensors file")
-    p.add_argument("--prompt", required=True)
-    p.add_argument("--max-new-tokens", type=int, default=50)
-    p.add_argument("--temperature", type=float, default=1.0)
-    p.add_argument("--top-p", type=float, default=0.9)
-    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--prompt", action="append", default=None, help="may be given several times")
+    p.add_argument("--prompt-file", default=None, help="text file with one prompt per non-empty line")
+    for name, kind, default in _SAMPLING:
+        p.add_argument("--" + name.replace("_", "-"), type=kind, default=default)
+    p.add_argument("--num-samples", type=int, default=1, help="continuations per prompt")
     p.add_argument("--phase", choices=["read_screening_only", "read_write"], default="read_screening_only")
-    p.add_argument("--continuation-only", action="store_true")
+    p.add_argument("--continuation-only", action="store_true", help="print the new text without the prompt")
     p.add_argument("--vocab-file", default=None)
     p.add_argument("--device", default="auto")
-    return parse_args_with_config(p, argv)
+    p.add_argument("--model-axis-size", type=int, default=1, help="tensor-parallel group size (under torch.distributed.run)")
+    p.add_argument("--json-out", default=None)
+    args = parse_args_with_config(p, argv)
+    if not args.prompt and not args.prompt_file:
+        p.error("give at least one --prompt or a --prompt-file")
+    if args.num_samples < 1:
+        p.error("--num-samples must be positive")
+    return args
 
 
-def main(argv=None):
-    args = parse_args(argv)
+def collect_prompts(args) -> list:
+    prompts = list(args.prompt or [])
+    if args.prompt_file:
+        prompts += [line.rstrip("\n") for line in Path(args.prompt_file).read_text(encoding="utf-8").splitlines() if line.strip()]
+    return prompts
+
+
+def build_runtime(args):
+    """A runtime holding the checkpoint's weights, sharded over the model axis when one is requested."""
+    from ..api import create_runtime, load_runtime_params
+    from ..io import load_model_safetensors
+    from .common import pick_device
+    from .eval_binidx import resolve_checkpoint_file
+
     params, config, _ = load_model_safetensors(resolve_checkpoint_file(args.checkpoint))
     if config is None:
         raise ValueError("checkpoint safetensors is missing rwkv7m config metadata")
+    sharding = None
+    if args.model_axis_size > 1:
+        from ..parallel.mesh import ShardingConfig, initialize_distributed, make_mesh
+
+        initialize_distributed()
+        sharding = ShardingConfig(make_mesh(("data", "model"), (-1, args.model_axis_size)))
+    if sharding is not None:
+        runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device), sharding=sharding)
+        return _load_sharded(runtime, params)
     runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device))
-    load_runtime_params(runtime, params)
-    text = generate_text(
-        runtime, args.prompt, tokenizer=RWKVTokenizer(args.vocab_file), max_new_tokens=args.max_new_tokens,
-        temperature=args.temperature, top_p=args.top_p, rng_key=args.seed, phase=args.phase,
-        include_prompt=not args.continuation_only,
-    )
-    print(text)
-    return text
+    return load_runtime_params(runtime, params)
+
+
+def _load_sharded(runtime, params):
+    """Load full portable tensors into a tensor-parallel runtime: fill an un-sharded model, then copy this rank's slices."""
+    from ..api import _attach_inference_weights
+    from ..io.safetensors_io import load_params_into_model
+    from ..models.model import initialize_model
+    from ..parallel.tp import shard_dim
+
+    tp = runtime.model.tp
+    full = initialize_model(0, runtime.config)
+    load_params_into_model(full, params)
+    named = dict(full.named_parameters())
+    import torch
+
+    with torch.no_grad():
+        for name, p in runtime.model.named_parameters():
+            src = named[name].detach()
+            d = shard_dim(name, tp.vocab_parallel)
+            if d is not None:
+                n = src.shape[d] // tp.world
+                src = src.narrow(d, tp.rank * n, n)
+            p.copy_(src.to(p.device, p.dtype))
+    _attach_inference_weights(runtime.model)
+    return runtime
+
+
+def main(argv=None):
+    from ..api import generate_text
+    from ..parallel.mesh import process_info
+    from ..tokenizer import RWKVTokenizer
+
+    args = parse_args(argv)
+    runtime = build_runtime(args)
+    tokenizer = RWKVTokenizer(args.vocab_file)
+    records = []
+    for prompt in collect_prompts(args):
+        for sample in range(args.num_samples):
+            seed = args.seed + sample
+            text = generate_text(runtime, prompt, tokenizer=tokenizer, max_new_tokens=args.max_new_tokens,
+                                 temperature=args.temperature, top_p=args.top_p, rng_key=seed, phase=args.phase,
+                                 include_prompt=not args.continuation_only)
+            records.append({"prompt": prompt, "sample": sample, "seed": seed, "text": text})
+    first = process_info()["process_index"] == 0
+    if first:
+        for r in records:
+            print(r["text"])
+        if args.json_out:
+            settings = {name: getattr(args, name) for name, _, _ in _SAMPLING}
+            settings.update(phase=args.phase, continuation_only=bool(args.continuation_only), checkpoint=str(args.checkpoint))
+            Path(args.json_out).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.json_out).write_text(json.dumps({"settings": settings, "samples": records}, indent=2, ensure_ascii=False) + "\n",
+                                           encoding="utf-8")
+    return records[0]["text"] if len(records) == 1 else [r["text"] for r in records]
 
 
 if __name__ == "__main__":

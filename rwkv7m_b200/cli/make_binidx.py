@@ -64,13 +64,12 @@ def build_binidx(input_file, output_prefix, *, vocab_file=None, epochs=3, seed=4
 def parse_args(argv=None):
     p = argparse.ArgumentParser(description="Convert JSONL text to RWKV .bin/.idx data.")
     p.add_argument("input_file")
-    p.add_argument("--output-prefix", default=None)
+    p.add_argument("--output-prefix", default=None, help="default: the input path without its suffix")
     p.add_argument("--vocab-file", default=str(default_vocab_path()))
-    p.add_argument("--epochs", type=int, default=3)
-    p.add_argument("--ctx-len", type=int, default=512)
-    p.add_argument("--seed", type=int, default=42)
+    for flag, default, text in (("--epochs", 3, "shuffled passes over the rows"), ("--ctx-len", 512, "context the magic prime is printed for"),
+                                ("--seed", 42, "shuffle seed"), ("--threads", 0, "tokenizer workers (0: one per core; native tokenizer only)")):
+        p.add_argument(flag, type=int, default=default, help=text)
     p.add_argument("--dtype", choices=["uint16", "uint32"], default="uint16")
-    p.add_argument("--threads", type=int, default=0, help="tokenizer workers (0: one per core; native tokenizer only)")
     return p.parse_args(argv)
 
 
@@ -79,9 +78,10 @@ def main(argv=None):
     prefix = args.output_prefix or str(Path(args.input_file).with_suffix(""))
     stats = build_binidx(args.input_file, prefix, vocab_file=args.vocab_file, epochs=args.epochs, seed=args.seed,
                          dtype=args.dtype, threads=args.threads)
-    print(f"wrote {prefix}.bin/.idx items={stats['items']} tokens={stats['tokens']} dtype={stats['dtype']}")
+    line = f"wrote {prefix}.bin/.idx items={stats['items']} tokens={stats['tokens']} dtype={stats['dtype']}"
     if stats["tokens"] >= args.ctx_len + 1:
-        print(f"magic_prime={find_magic_prime(stats['tokens'], args.ctx_len)} ctx_len={args.ctx_len}")
+        line += f"\nmagic_prime={find_magic_prime(stats['tokens'], args.ctx_len)} ctx_len={args.ctx_len}"
+    print(line)
     return stats
 
 

@@ -82,6 +82,33 @@ def test_make_binidx_and_generate(tmp_path, tiny_binidx):
     text = generate.main(["--checkpoint", str(ckpt), "--prompt", "hi", "--max-new-tokens", "3", "--temperature", "0",
                           "--device", "cpu"])
     assert text.startswith("hi")
+    # several prompts (flags and a file), several samples each, a JSON record of everything
+    (tmp_path / "prompts.txt").write_text("abc\n\nRWKV\n", encoding="utf-8")
+    texts = generate.main(["--checkpoint", str(ckpt), "--prompt", "hi", "--prompt", "yo", "--prompt-file",
+                           str(tmp_path / "prompts.txt"), "--num-samples", "2", "--max-new-tokens", "2", "--temperature", "0.7",
+                           "--continuation-only", "--json-out", str(tmp_path / "gen" / "out.json"), "--device", "cpu"])
+    record = json.loads((tmp_path / "gen" / "out.json").read_text(encoding="utf-8"))
+    assert len(texts) == 8 and [s["prompt"] for s in record["samples"]] == ["hi", "hi", "yo", "yo", "abc", "abc", "RWKV", "RWKV"]
+    assert [s["seed"] for s in record["samples"][:2]] == [42, 43] and record["settings"]["temperature"] == 0.7
+    with pytest.raises(SystemExit):
+        generate.parse_args(["--checkpoint", str(ckpt)])
+    # the same checkpoint served by two tensor-parallel processes gives the same greedy continuation
+    import socket
+    import subprocess
+    import sys
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    root = Path(__file__).resolve().parents[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "rwkv7m_b200.cli.generate", "--checkpoint", str(ckpt), "--prompt", "hi",
+           "--max-new-tokens", "3", "--temperature", "0", "--device", "cpu", "--model-axis-size", "2",
+           "--json-out", str(tmp_path / "tp.json")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(root),
+                         env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert json.loads((tmp_path / "tp.json").read_text(encoding="utf-8"))["samples"][0]["text"] == text
 
 
 def test_plan_scale_outputs_exact_counts(capsys):
