@@ -103,6 +103,45 @@ def wkv7(r, w, k, v, a, b, state0):
     return y, S
 
 
+def wkv7_chunked(r, w, k, v, a, b, state0, chunk_len: int = 64, dtype=torch.float64):
+    """The recurrence of :func:`wkv7` evaluated chunk by chunk with matrix products: the formulation that the tensor-core
+    kernels implement, stated in plain PyTorch (differentiable; ``dtype`` is the working precision).
+
+    Within a chunk of L steps let ``P_t`` be the product of the decays up to and including step t (per key column),
+    ``Pex_t = P_t / decay_t``, and scale the keys: ``a~_t = a_t * Pex_t``, ``r~_t = r_t * P_t``, ``b~_s = b_s / P_s``,
+    ``k~_s = k_s / P_s``.  The removal products ``u_t = S_{t-1} a_t`` then satisfy ``U = Z + tril(A~ B~^T, -1) U`` with
+    ``Z = A~ S_0^T + tril(A~ K~^T, -1) V``, a unit lower-triangular system; the outputs are
+    ``Y = R~ S_0^T + tril(R~ B~^T) U + tril(R~ K~^T) V`` and the state after the chunk is
+    ``S_L = (S_0 + U^T B~ + V^T K~) * P_L``.  ``1 / P_s`` grows like exp(0.61 L) at the strongest decay the model can
+    produce (w = -0.5), which is why the working precision defaults to float64 and the kernels rescale per chunk."""
+    B, T, H, N = r.shape
+    L = int(chunk_len)
+    rf, wf, kf, vf, af, bf = (t.to(dtype).permute(0, 2, 1, 3) for t in (r, w, k, v, a, b))      # [B, H, T, N]
+    S = state0.to(dtype)
+    ys = []
+    for c0 in range(0, T, L):
+        sl = slice(c0, min(c0 + L, T))
+        rc, wc, kc, vc, ac, bc = (t[:, :, sl] for t in (rf, wf, kf, vf, af, bf))
+        log_decay = -torch.exp(wc)
+        log_p = torch.cumsum(log_decay, dim=2)                     # inclusive
+        p_in, p_ex, p_inv = torch.exp(log_p), torch.exp(log_p - log_decay), torch.exp(-log_p)
+        a_s, r_s, b_s, k_s = ac * p_ex, rc * p_in, bc * p_inv, kc * p_inv
+        n = a_s.shape[2]
+        strict = torch.tril(torch.ones(n, n, dtype=torch.bool, device=r.device), -1)
+        incl = torch.tril(torch.ones(n, n, dtype=torch.bool, device=r.device))
+        a_ab = (a_s @ b_s.transpose(-1, -2)).masked_fill(~strict, 0)
+        a_ak = (a_s @ k_s.transpose(-1, -2)).masked_fill(~strict, 0)
+        z = a_s @ S.transpose(-1, -2) + a_ak @ vc                   # [B, H, n, N(value)]
+        eye = torch.eye(n, dtype=dtype, device=r.device)
+        u = torch.linalg.solve_triangular(eye - a_ab, z, upper=False, unitriangular=True)
+        r_b = (r_s @ b_s.transpose(-1, -2)).masked_fill(~incl, 0)
+        r_k = (r_s @ k_s.transpose(-1, -2)).masked_fill(~incl, 0)
+        ys.append(r_s @ S.transpose(-1, -2) + r_b @ u + r_k @ vc)
+        S = (S + u.transpose(-1, -2) @ b_s + vc.transpose(-1, -2) @ k_s) * p_in[:, :, -1].unsqueeze(-2)
+    y = torch.cat(ys, dim=2).permute(0, 2, 1, 3).to(r.dtype)
+    return y, S.to(torch.float32)
+
+
 def wkv_step(state, r_t, w_t, k_t, v_t, neg_kk_t, kka_t):
     """One step of the recurrence as a pure function (src/rwkv7m/model/rwkv_core.py:54-90): ``state`` [B,H,N,N],
     the six vectors [B,H,N]; returns ``(new_state, y_t)``, all math in fp32 whatever the storage dtype."""

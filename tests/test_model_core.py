@@ -119,3 +119,54 @@ def test_tiny_train_then_greedy_generate():
     ids = R.generate_ids(rt, [[1, 2, 3]], max_new_tokens=8, temperature=0.0)
     again = R.generate_ids(R.reset_runtime_state(rt, batch_size=1), [[1, 2, 3]], max_new_tokens=8, temperature=0.0)
     assert ids.shape == (1, 8) and torch.equal(ids, again)
+
+
+def test_chunked_wkv_formulation_equals_the_step_recurrence():
+    """The chunk-by-chunk matrix form that the tensor-core kernels implement, stated in PyTorch: same outputs, final state
+    and gradients as the step-by-step recurrence, for any chunk length (a ragged last chunk included) and at the
+    strongest decay the model can produce."""
+    import torch
+
+    from rwkv7m_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    B, T, H, N = 2, 70, 2, 8
+    f64 = dict(dtype=torch.float64)
+    r, k, v = (torch.randn(B, T, H, N, **f64) * 0.5 for _ in range(3))
+    w = -torch.nn.functional.softplus(-torch.randn(B, T, H, N, **f64)) - 0.5
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N, **f64), dim=-1)
+    a, b = -kk, kk * torch.sigmoid(torch.randn(B, T, H, N, **f64))
+    s0 = torch.randn(B, H, N, N, **f64) * 0.1
+    wy, ws = torch.randn(B, T, H, N, **f64), torch.randn(B, H, N, N, **f64)
+
+    def step_by_step(*xs):
+        r_, w_, k_, v_, a_, b_, S = xs
+        ys = []
+        for t in range(T):
+            S, y = _step64(S, r_[:, t], w_[:, t], k_[:, t], v_[:, t], a_[:, t], b_[:, t])
+            ys.append(y)
+        return torch.stack(ys, dim=1), S
+
+    def _step64(S, r_t, w_t, k_t, v_t, a_t, b_t):
+        sa = torch.einsum("bhij,bhj->bhi", S, a_t)
+        S = S * torch.exp(-torch.exp(w_t)).unsqueeze(-2) + sa.unsqueeze(-1) * b_t.unsqueeze(-2) + v_t.unsqueeze(-1) * k_t.unsqueeze(-2)
+        return S, torch.einsum("bhij,bhj->bhi", S, r_t)
+
+    def grads(fn, inputs):
+        leaves = [t.clone().requires_grad_(True) for t in inputs]
+        y, S = fn(*leaves)
+        ((y.double() * wy).sum() + (S.double() * ws).sum()).backward()
+        return y.detach().double(), S.detach().double(), [t.grad for t in leaves]
+
+    for weights in (w, torch.full_like(w, -0.5)):
+        inputs = (r, weights, k, v, a, b, s0)
+        y_ref, s_ref, g_ref = grads(step_by_step, inputs)
+        for chunk in (64, 16, 7):
+            y, s, g = grads(lambda *xs: ref.wkv7_chunked(*xs, chunk_len=chunk), inputs)
+            assert torch.allclose(y, y_ref, atol=1e-9) and torch.allclose(s, s_ref, atol=1e-6)   # the state is returned in fp32
+            for got, want in zip(g, g_ref):
+                assert torch.allclose(got, want, atol=1e-7, rtol=1e-6)
+    # and the fp32 oracle used everywhere else agrees with both
+    y32, s32 = ref.wkv7(*[t.float() for t in (r, w, k, v, a, b)], s0.float())
+    y64, _ = ref.wkv7_chunked(r, w, k, v, a, b, s0)
+    assert torch.allclose(y32.double(), y64, atol=1e-5)
