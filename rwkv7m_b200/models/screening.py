@@ -187,3 +187,91 @@ def screening_scan_reference(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, 
     stats["tau_w"] = tau_w.detach()
     new_state = LayerScreenState(slots=slots, ages=ages, usage_ema=usage)
     return torch.stack(hs, dim=1), new_state, stats
+
+
+def screening_scan_carried(mod, q_r, q_w, gate, delta_xh, delta_slot, h_base, state,
+                           *, tau_r, tau_w, lam, mu, write_enabled):
+    """The same scan in the formulation of the CUDA kernels, in plain fp32 PyTorch (differentiable).
+
+    The update moves every slot towards a target ``D_t[m] = tanh(dxh_t + dslot[m])`` that does not depend on the bank, and
+    the projections that a step needs (read key, value, write key: ``J = d_k + d_v + d_k`` columns) are linear in the
+    bank.  So instead of projecting the bank at every step, the projections themselves are carried:
+    ``P_{t+1}[m] = P_t[m] + s_t[m] (PD_t[m] - P_t[m])`` with ``PD = D W^T`` computed for all steps in one product.  The
+    sequential loop then touches ``J`` numbers per slot and no weight; the read-out normalisation, the output projection
+    and the bank itself (an independent scalar recurrence per element once the strengths are known) run outside it."""
+    cfg = mod.config
+    B, T, C = h_base.shape
+    M = state.slots.shape[1]
+    dk = mod.k_proj_r.weight.shape[0]
+    dv = mod.v_proj.weight.shape[0]
+    slots0, ages, usage = state.slots.float(), state.ages.float(), state.usage_ema.float()
+    embed = mod.slot_embed.float()
+    mats = [mod.k_proj_r.weight.float(), mod.v_proj.weight.float()]
+    if write_enabled:
+        mats.append(mod.k_proj_w.weight.float())
+    W = torch.cat(mats, dim=0)                                        # [J, ds]
+    shift = torch.zeros(M, W.shape[0], device=W.device)
+    if write_enabled:                                                 # the write key sees bank + slot identity
+        shift[:, dk + dv:] = embed @ mod.k_proj_w.weight.float().t()
+    D = torch.tanh(delta_xh.float().unsqueeze(2) + delta_slot.float())          # [B, T, M, ds]
+    PD = D @ W.t() + shift                                                        # [B, T, M, J]: one product for all steps
+    P = slots0 @ W.t() + shift                                                    # [B, M, J]
+    zs, strengths = [], []
+    acc = {k: 0.0 for k in STAT_KEYS}
+    for t in range(T):
+        k_r = R.unit_norm(P[..., :dk], eps=cfg.eps)
+        values = P[..., dk:dk + dv]
+        if cfg.use_value_unit_norm:
+            values = R.unit_norm(values, eps=cfg.eps)
+        sim_r = torch.einsum("bk,bmk->bm", q_r[:, t], k_r)
+        if cfg.use_leaky_warmup:
+            rel_r = (1.0 - cfg.leaky_alpha) * R.trim_square(sim_r, tau_r) + cfg.leaky_alpha * torch.sigmoid(
+                cfg.leaky_gamma * (sim_r - tau_r))
+        else:
+            rel_r = R.trim_square(sim_r, tau_r, eps=cfg.eps)
+        if cfg.use_age_mask:
+            rel_r = rel_r * R.compute_age_mask(ages, cfg)
+        z = torch.einsum("bm,bmv->bv", rel_r, values)
+        if write_enabled:
+            k_w = R.unit_norm(P[..., dk + dv:], eps=cfg.eps)
+            rel_w = R.trim_square(torch.einsum("bk,bmk->bm", q_w[:, t], k_w), tau_w, eps=cfg.eps)
+            strength = mu[None, :] * torch.clamp(rel_w, min=cfg.write_rel_floor)
+            ages = torch.where(rel_w > 1e-3, torch.zeros_like(ages), ages + 1.0)
+            activity = torch.maximum(rel_r, rel_w)
+        else:
+            rel_w = torch.zeros_like(rel_r)
+            strength = mu[None, :].expand(B, M)
+            activity = rel_r
+        usage = cfg.usage_ema_decay * usage + (1.0 - cfg.usage_ema_decay) * activity
+        P = P + strength.unsqueeze(-1) * (PD[:, t] - P)
+        zs.append(z)
+        strengths.append(strength)
+        with torch.no_grad():
+            acc["rel_read_mean"] += rel_r.mean()
+            acc["rel_read_max"] += rel_r.max()
+            acc["active_slots_mean"] += (rel_r > 1e-3).sum(-1).float().mean()
+            acc["z_norm_mean"] += z.norm(dim=-1).mean()
+            acc["rel_write_mean"] += rel_w.mean()
+            acc["rel_write_effective_mean"] += (torch.clamp(rel_w, min=cfg.write_rel_floor).mean() if write_enabled
+                                                else rel_w.mean())
+            acc["slot_usage_ema_mean"] += usage.mean()
+    z_all = torch.stack(zs, dim=1)                                               # everything below is parallel over steps
+    u = R.tanh_norm(z_all, cap=cfg.tanh_norm_cap, eps=cfg.eps)
+    read_out = R.linear(u, mod.out_proj.weight.float())
+    h = (h_base.float() + lam * gate.float() * read_out).to(h_base.dtype)
+    s_all = torch.stack(strengths, dim=1)                                        # [B, T, M]
+    # the bank: S_T = c_0 S_0 + sum_t c_{t+1} s_t D_t with c_t the product of (1 - s) over the steps from t on
+    keep = 1.0 - s_all
+    suffix = torch.flip(torch.cumprod(torch.flip(keep, dims=[1]), dim=1), dims=[1])          # c_t, t = 0 .. T-1
+    after = torch.cat([suffix[:, 1:], torch.ones_like(suffix[:, :1])], dim=1)                # c_{t+1}
+    slots = suffix[:, 0].unsqueeze(-1) * slots0 + ((after * s_all).unsqueeze(-1) * D).sum(dim=1)
+    with torch.no_grad():
+        acc["u_norm_mean"] = u.norm(dim=-1).mean(dim=0).sum()
+        bank = slots0
+        for t in range(T):                                                        # the statistic needs every intermediate bank
+            step = s_all[:, t].unsqueeze(-1) * (D[:, t] - bank)
+            acc["slot_update_norm_mean"] += step.norm(dim=-1).mean()
+            bank = bank + step
+    stats = {k: (v / T) for k, v in acc.items()}
+    stats["tau_r"], stats["lambda_screen"], stats["tau_w"] = tau_r.detach(), lam.detach(), tau_w.detach()
+    return h, LayerScreenState(slots=slots, ages=ages, usage_ema=usage), stats

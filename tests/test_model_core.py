@@ -170,3 +170,55 @@ def test_chunked_wkv_formulation_equals_the_step_recurrence():
     y32, s32 = ref.wkv7(*[t.float() for t in (r, w, k, v, a, b)], s0.float())
     y64, _ = ref.wkv7_chunked(r, w, k, v, a, b, s0)
     assert torch.allclose(y32.double(), y64, atol=1e-5)
+
+
+@pytest.mark.parametrize("write,age_mask,leaky", [(True, False, False), (True, True, True), (False, False, False), (False, True, True)])
+def test_carried_projection_scan_equals_the_step_scan(write, age_mask, leaky):
+    """The formulation of the screening kernels (projections carried through the slot recurrence, one product for all
+    targets, read-out and bank outside the sequential loop) stated in PyTorch: outputs, next state, statistics and every
+    gradient equal the step-by-step scan's."""
+    import torch
+
+    from rwkv7m_b200 import ops
+    from rwkv7m_b200.config import ScreeningConfig
+    from rwkv7m_b200.models import screening as SC
+    from rwkv7m_b200.state import LayerScreenState
+
+    torch.manual_seed(0)
+    C, B, T, M, ds = 32, 2, 9, 5, 24
+    cfg = ScreeningConfig(d_model=C, d_slot=ds, d_k=8, d_v=12, n_slots=M, screened_layers=(0,), bank_ids=(0, 0, 1, 1, 2),
+                          use_write_screening=write, use_age_mask=age_mask, write_rel_floor=1e-3, use_leaky_warmup=leaky,
+                          leaky_alpha=0.3 if leaky else 0.0)
+    mod = SC.StateLevelScreening(cfg)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.add_(torch.randn_like(p) * 0.2)
+        mod.lambda_raw.fill_(0.5)
+    x, h = torch.randn(B, T, C), torch.randn(B, T, C)
+    st = LayerScreenState(slots=torch.randn(B, M, ds) * 0.3, ages=torch.randint(0, 40, (B, M)).float(), usage_ema=torch.rand(B, M))
+    weights = torch.arange(float(ds))
+
+    def run(scan, monkey):
+        for p in mod.parameters():
+            p.grad = None
+        xs, hs = x.clone().requires_grad_(True), h.clone().requires_grad_(True)
+        s0 = LayerScreenState(st.slots.clone().requires_grad_(True), st.ages.clone(), st.usage_ema.clone())
+        original = ops.screening_scan
+        ops.screening_scan = scan
+        try:
+            out, ns, stats = mod(xs, hs, s0, phase="read_write" if write else "read_screening_only")
+        finally:
+            ops.screening_scan = original
+        (out.sum() + (ns.slots * weights).sum()).backward()
+        grads = {n: p.grad.clone() for n, p in mod.named_parameters() if p.grad is not None}
+        grads.update(x=xs.grad, h=hs.grad, slots0=s0.slots.grad)
+        return out.detach(), ns, stats, grads
+
+    o_ref, ns_ref, st_ref, g_ref = run(SC.screening_scan_reference, None)
+    o, ns, stt, g = run(SC.screening_scan_carried, None)
+    assert torch.allclose(o, o_ref, atol=2e-6) and torch.allclose(ns.slots, ns_ref.slots, atol=2e-6)
+    assert torch.equal(ns.ages, ns_ref.ages) and torch.allclose(ns.usage_ema, ns_ref.usage_ema, atol=1e-6)
+    assert set(stt) == set(st_ref) and all(abs(float(stt[k]) - float(st_ref[k])) < 1e-5 for k in st_ref)
+    assert set(g) == set(g_ref)
+    for name in g_ref:
+        assert torch.allclose(g[name], g_ref[name], atol=5e-5, rtol=1e-4), name
