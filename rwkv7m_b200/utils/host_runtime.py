@@ -48,7 +48,10 @@ def _load():
     _tried = True
     if os.environ.get("RWKV7M_B200_HOST_RUNTIME", "1") == "0" or not LIBRARY.exists():
         return None
-    lib = ctypes.CDLL(str(LIBRARY))
+    try:
+        lib = ctypes.CDLL(str(LIBRARY))
+    except OSError:          # built on another machine against another C++ runtime: the Python paths take over
+        return None
     c = ctypes
     lib.rk_tok_create.restype = c.c_void_p
     lib.rk_tok_create.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int32]
