@@ -758,7 +758,9 @@ class LoraGroupFn(torch.autograd.Function):
 def lora_group(items):
     """``items``: ``(x, down, up, mid)`` tuples on inputs of one shape; returns the list of results.  One grouped launch
     per half when the switch is on and every pair qualifies for the GEMM path, otherwise pair by pair."""
-    if LORA_GROUP and 2 <= len(items) <= 4 and all(_fused_linear_ok(x, d, u) for x, d, u, _ in items) \
+    # fewer than one tile of rows (prefill of a short prompt, eager decode): the decode-sized GEMM kernel serves each pair better
+    rows = items[0][0].numel() // max(items[0][0].shape[-1], 1) if items else 0
+    if LORA_GROUP and rows >= 128 and 2 <= len(items) <= 4 and all(_fused_linear_ok(x, d, u) for x, d, u, _ in items) \
             and len({tuple(x.shape) for x, _, _, _ in items}) == 1:
         n = len(items)
         xs, downs, ups = [it[0] for it in items], [it[1] for it in items], [it[2] for it in items]
