@@ -231,6 +231,8 @@ def train_step(train_state: TrainState, batch, rwkv_state, screen_state, *, phas
 def generate_toy_batch(seed, batch_size, seq_len, vocab_size, device=None):
     """Random ids with target = ids rolled by -1 (last target 0) and an all-ones mask
     (src/rwkv7m/train/train_loop.py:40-51)."""
+    if not isinstance(seed, int):      # a key in the reference's style ([0, seed] words): its last word is the seed
+        seed = 0 if seed is None else int(torch.as_tensor(seed).flatten()[-1].item())
     gen = torch.Generator().manual_seed(int(seed))
     ids = torch.randint(0, vocab_size, (batch_size, seq_len), generator=gen, dtype=torch.int64).to(torch.int32)
     targets = torch.roll(ids, shifts=-1, dims=1)
