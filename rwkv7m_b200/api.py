@@ -139,7 +139,26 @@ def create_train_runtime(rng_key, config, *, batch_size: int, total_steps: int =
 
 def load_runtime_params(runtime: RWKV7MRuntime, params):
     """Load a portable parameter tree (nested or ``/``-joined flat) into the runtime's model."""
-    load_params_into_model(runtime.model, params)
+    tp = getattr(runtime.model, "tp", None)
+    if tp is not None and tp.world > 1:
+        # full tensors into a tensor-parallel runtime: an un-sharded twin takes the tree (strict path and shape checks),
+        # this rank keeps its slices
+        from .models.model import initialize_model
+        from .parallel.tp import shard_dim
+
+        full = initialize_model(0, runtime.config)
+        load_params_into_model(full, params)
+        named = dict(full.named_parameters())
+        with torch.no_grad():
+            for name, p in runtime.model.named_parameters():
+                src = named[name].detach()
+                d = shard_dim(name, tp.vocab_parallel)
+                if d is not None:
+                    n = src.shape[d] // tp.world
+                    src = src.narrow(d, tp.rank * n, n)
+                p.copy_(src.to(p.device, p.dtype))
+    else:
+        load_params_into_model(runtime.model, params)
     if not runtime.model.training:
         _attach_inference_weights(runtime.model)
     runtime.variables = {"params": PortableParams(runtime.model)}

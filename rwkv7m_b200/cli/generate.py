@@ -60,36 +60,8 @@ def build_runtime(args):
 
         initialize_distributed()
         sharding = ShardingConfig(make_mesh(("data", "model"), (-1, args.model_axis_size)))
-    if sharding is not None:
-        runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device), sharding=sharding)
-        return _load_sharded(runtime, params)
-    runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device))
-    return load_runtime_params(runtime, params)
-
-
-def _load_sharded(runtime, params):
-    """Load full portable tensors into a tensor-parallel runtime: fill an un-sharded model, then copy this rank's slices."""
-    from ..api import _attach_inference_weights
-    from ..io.safetensors_io import load_params_into_model
-    from ..models.model import initialize_model
-    from ..parallel.tp import shard_dim
-
-    tp = runtime.model.tp
-    full = initialize_model(0, runtime.config)
-    load_params_into_model(full, params)
-    named = dict(full.named_parameters())
-    import torch
-
-    with torch.no_grad():
-        for name, p in runtime.model.named_parameters():
-            src = named[name].detach()
-            d = shard_dim(name, tp.vocab_parallel)
-            if d is not None:
-                n = src.shape[d] // tp.world
-                src = src.narrow(d, tp.rank * n, n)
-            p.copy_(src.to(p.device, p.dtype))
-    _attach_inference_weights(runtime.model)
-    return runtime
+    runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device), sharding=sharding)
+    return load_runtime_params(runtime, params)      # a tensor-parallel runtime keeps this rank's slices of the full tensors
 
 
 def main(argv=None):
