@@ -94,6 +94,8 @@ def parse_args(argv=None):
     p.add_argument("--mesh-axis-names", nargs="+", default=["data"])
     p.add_argument("--mesh-axis-sizes", type=int, nargs="+", default=None)
     p.add_argument("--param-axis-name", default=None)
+    p.add_argument("--no-health-gate", action="store_true",
+                   help="skip the host-side meeting before every step at which a peer's failure record stops the others")
     p.add_argument("--dp-mode", choices=["auto", "fused", "allreduce", "zero3"], default="auto",
                    help="fused: sharded optimizer step over NVLink (auto picks it on GPUs); allreduce: library "
                         "all-reduce (auto picks it on CPU); zero3: parameters, gradients and optimizer state "
@@ -397,6 +399,11 @@ def run_distributed_training(args):
     if args.disable_python_gc:
         gc.disable()
     eval_state = {}
+    health = None
+    if world > 1 and not args.no_health_gate:
+        from ..parallel.health import PeerHealth
+
+        health = PeerHealth(timeout_s=float(args.collective_timeout_s))
     try:
         say(f"data_tokens={dataset.data_size} magic_prime={dataset.magic_prime} ctx_len={args.ctx_len} "
             f"global_batch_size={args.global_batch_size} world={world} dp_mode={mode} start_step={start_step}")
@@ -406,8 +413,11 @@ def run_distributed_training(args):
             if args.carry_state and dataset.should_reset_state_before_step(step):
                 runtime.rwkv_state, runtime.screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
             if args.inject_failure_step is not None and step == args.inject_failure_step and rank == args.inject_failure_rank:
-                # between steps, nothing in flight: the other ranks learn of it through the collective timeout
+                # between steps, nothing in flight: the other ranks find the record at the gate below (or, without the
+                # gate, run into the collective timeout)
                 raise RuntimeError(f"injected failure on rank {rank} before step {step}")
+            if health is not None:
+                health.gate(step)
             if use_cuda:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -461,6 +471,8 @@ def run_distributed_training(args):
         summary.update(status="completed", ended_at=_now())
         _write_summary(args, info, summary)
     except BaseException as exc:
+        if health is not None:
+            health.report(exc)
         summary.update(status="failed", ended_at=_now(), error_type=type(exc).__name__, error_message=str(exc))
         _write_summary(args, info, summary)
         raise

@@ -37,6 +37,8 @@ def test_rank_failure_marks_run_failed_and_resume_recovers(tiny_binidx, tmp_path
     assert res.returncode != 0
     summary = json.loads((out / "run_summary.json").read_text())
     assert summary["status"] == "failed" and summary["error_type"] and summary["completed_steps"] == 3
+    # the surviving rank met the failure record at the gate of step 3: it names the peer instead of a collective timeout
+    assert summary["error_type"] == "PeerFailureError" and "rank 1 failed with RuntimeError" in summary["error_message"]
     rep = audit_distributed_run(out, require_complete=True)
     assert not rep.ok and "summary_not_completed" in {i.code for i in rep.issues}
     # recovery = resume from the last good checkpoint in a fresh single-process run

@@ -377,3 +377,46 @@ def test_sharding_keyword_builds_the_tensor_parallel_runtime(tmp_path):
     alone = R.create_runtime(3, _cfg(), batch_size=4, sharding=ShardingConfig(make_mesh(("data", "model"), (1, 1), world_size=1)))
     got, _ = R.infer_prefill(alone, _global_batch()["input_ids"])
     assert torch.equal(got, want)
+
+
+def _health_worker(rank, world, port, out):
+    _init(rank, world, port)
+    import time
+
+    from rwkv7m_b200.parallel.health import PeerFailureError, PeerHealth
+
+    health = PeerHealth(timeout_s=20.0)
+    result = {"rank": rank, "gates": 0}
+    try:
+        for step in range(5):
+            if rank == 1 and step == 3:
+                raise ValueError("disk full")          # between steps, nothing in flight
+            health.gate(step)
+            result["gates"] += 1
+            time.sleep(0.01 * (rank + 1))              # the ranks drift apart; the gate brings them together again
+    except BaseException as exc:
+        health.report(exc)
+        result.update(error=type(exc).__name__, message=str(exc), record=getattr(exc, "record", None))
+    with open(f"{out}.{rank}", "w") as f:
+        json.dump(result, f)
+    if rank == 0:
+        time.sleep(0.5)                                # rank 0 hosts the store: let the other process finish reading
+    sys_exit = os._exit
+    sys_exit(0)
+
+
+def test_peer_failure_is_seen_at_the_next_step_gate(tmp_path):
+    """A process that fails between steps posts a record in the job's store; the other one, waiting at the gate of the step
+    that the failed process never reaches, stops with the peer's rank and error instead of starting the step (and instead
+    of waiting for a collective timeout)."""
+    import time
+
+    out = str(tmp_path / "health")
+    t0 = time.monotonic()
+    mp.spawn(_health_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert time.monotonic() - t0 < 15          # far below the 20 s gate limit: the record ended the wait
+    survivor, failed = (json.load(open(f"{out}.{r}")) for r in (0, 1))
+    assert failed["error"] == "ValueError" and failed["gates"] == 3
+    assert survivor["error"] == "PeerFailureError" and survivor["gates"] == 3
+    assert survivor["record"] == {"rank": 1, "error": "ValueError", "message": "disk full"}
+    assert "rank 1 failed with ValueError: disk full" in survivor["message"]
