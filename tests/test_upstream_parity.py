@@ -68,3 +68,49 @@ def test_model_parallel_audit_world_of_one():
     assert rep["contract"]["has_row_parallel_kernel"] and rep["contract"]["has_column_parallel_kernel"]
     assert rep["parameters"]["layers.0.block.att.output.weight"]["shard_dim"] == 1
     assert rep["forward"]["collectives"]["calls"]["all_gather_into_tensor"] >= 4
+
+
+def test_convert_tool_round_trips_between_the_layouts(tmp_path):
+    """``rwkv7m-convert-upstream``: a portable file exported to the upstream layout and imported again gives the same
+    tensors and the same logits; the import infers the configuration from the shapes and reports full coverage; a model
+    with screened layers is refused for export; an upstream file with a stray tensor fails unless allowed."""
+    import json
+
+    import rwkv7m_b200 as R
+    from rwkv7m_b200.cli import convert_upstream
+
+    cfg = R.tiny_config(vocab_size=300, d_model=32, n_layers=2, n_heads=2, head_size=16, use_screening=False)
+    cfg.d_ffn = 64
+    rt = R.create_runtime(0, cfg, batch_size=1)
+    with torch.no_grad():      # the output projections start at zero: move them so that the logits depend on every tensor
+        for p in rt.model.parameters():
+            p.add_(torch.randn_like(p) * 0.02)
+    src = tmp_path / "model.safetensors"
+    R.save_model_safetensors(src, rt.model, cfg)
+    assert convert_upstream.main(["export", str(src), str(tmp_path / "up.pth")]) == 0
+    state = torch.load(tmp_path / "up.pth", weights_only=True)
+    assert "emb.weight" in state and "blocks.1.att.key.weight" in state and state["blocks.0.att.v0"].abs().sum() == 0
+    rc = convert_upstream.main(["import", str(tmp_path / "up.pth"), str(tmp_path / "back.safetensors"), "--head-size", "16",
+                                "--dtype", "float32", "--report", str(tmp_path / "report.json")])
+    assert rc == 0
+    report = json.loads((tmp_path / "report.json").read_text())
+    assert report["coverage"]["complete"] and report["spec"]["n_layers"] == 2 and report["spec"]["d_ffn"] == 64
+    params, config, meta = R.load_model_safetensors(tmp_path / "back.safetensors")
+    assert config.d_model == 32 and config.n_heads == 2 and not (config.use_screening and config.screening.screened_layers)
+    other = R.load_runtime_params(R.create_runtime(7, config, batch_size=1), params)
+    ids = torch.tensor([[1, 2, 3, 4, 5]], dtype=torch.int32)
+    a, _ = R.infer_prefill(rt, ids)
+    b, _ = R.infer_prefill(other, ids)
+    assert torch.allclose(a, b, atol=1e-6)
+    # the .safetensors flavour of the upstream layout, and a stray tensor
+    assert convert_upstream.main(["export", str(src), str(tmp_path / "up.safetensors")]) == 0
+    state["blocks.0.att.not_a_tensor"] = torch.zeros(3)
+    torch.save(state, tmp_path / "stray.pth")
+    with pytest.raises(ValueError, match="unexpected upstream tensors"):
+        convert_upstream.main(["import", str(tmp_path / "stray.pth"), str(tmp_path / "x.safetensors"), "--head-size", "16"])
+    assert convert_upstream.main(["import", str(tmp_path / "stray.pth"), str(tmp_path / "x.safetensors"), "--head-size", "16",
+                                  "--allow-unexpected-weights"]) == 0
+    screened = R.create_runtime(0, R.tiny_config(vocab_size=300, d_model=32, n_layers=2, n_heads=2, head_size=16), batch_size=1)
+    R.save_model_safetensors(tmp_path / "screened.safetensors", screened.model, screened.config)
+    with pytest.raises(ValueError, match="screening"):
+        convert_upstream.main(["export", str(tmp_path / "screened.safetensors"), str(tmp_path / "no.pth")])
