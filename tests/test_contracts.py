@@ -829,3 +829,16 @@ def test_runtime_variables_hold_the_portable_tree(tmp_path):
         rt.model.head.weight.add_(1.0)
     assert not torch.equal(tree["lm_head"]["kernel"], rt.model.head.weight.t().cpu())     # a snapshot ...
     assert torch.equal(tree.refresh()["lm_head"]["kernel"], rt.model.head.weight.detach().t().cpu())   # ... until refreshed
+
+
+def test_doctor_reports_what_the_installation_can_run(capsys):
+    from rwkv7m_b200.cli import doctor
+
+    rc = doctor.main(["--no-load"])
+    report = json.loads(capsys.readouterr().out)
+    assert rc == (0 if report["ok"] else 1)
+    assert {"cuda_extension", "host_runtime", "gpus", "process_group_backends"} <= set(report["checks"])
+    assert report["checks"]["process_group_backends"]["gloo"] is True and isinstance(report["problems"], list)
+    assert "torch" in report["environment"]["packages"]
+    if not torch.cuda.is_available():
+        assert report["checks"]["gpus"] == [] and report["ok"]
