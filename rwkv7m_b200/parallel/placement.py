@@ -15,7 +15,6 @@ from dataclasses import dataclass, replace
 import torch
 import torch.distributed as dist
 
-from ..state import ModelScreenState
 from .dp import DataParallelTrainer
 from .mesh import Mesh, make_mesh, mesh_groups
 from .metrics import aggregate_metrics
