@@ -8,8 +8,6 @@ import argparse
 import csv
 import sys
 
-import torch
-
 from ..api import create_train_runtime, train_batch
 from ..config import ModelConfig, ScreeningConfig
 from ..data import create_binidx_dataset

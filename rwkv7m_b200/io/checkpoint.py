@@ -24,7 +24,7 @@ from ..state import (
     screen_state_from_dict,
     screen_state_to_dict,
 )
-from .names import from_portable, portable_entries, to_portable
+from .names import from_portable, to_portable
 from .safetensors_io import save_model_safetensors
 
 CHECKPOINT_JSON = "checkpoint.json"

@@ -10,7 +10,6 @@ checkpoint layout (``[in, out]`` kernels, ``[1,1,C]`` vectors) is produced by
 
 from __future__ import annotations
 
-import contextlib
 import math
 
 import torch

@@ -25,7 +25,6 @@ from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
-from torch import nn
 
 from ..state import LayerRWKVState
 
