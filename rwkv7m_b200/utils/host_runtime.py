@@ -106,7 +106,10 @@ class NativeTrie:
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
         if handle:
-            self._lib.rk_tok_free(handle)
+            try:
+                self._lib.rk_tok_free(handle)
+            except Exception:      # interpreter shutdown: the library may already be gone
+                pass
 
     @staticmethod
     def _raise(code: int, base: int = 0):
