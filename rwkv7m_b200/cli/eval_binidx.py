@@ -45,7 +45,19 @@ def evaluate_binidx(args) -> dict:
             cfg = build_config(args)
     else:
         cfg = build_config(args)
-    runtime = create_runtime(args.seed, cfg, batch_size=args.batch_size, device=device)
+    sharding = None
+    if int(getattr(args, "model_axis_size", 1) or 1) > 1:
+        # under a multi-process launcher: every process holds its shard of the model and reads the same batches (the
+        # vocabulary-parallel loss of the 1b / 3b / 7b presets needs this)
+        from ..parallel.mesh import ShardingConfig, initialize_distributed, make_mesh
+
+        initialize_distributed()
+        sharding = ShardingConfig(make_mesh(("data", "model"), (-1, args.model_axis_size)))
+        if args.ctx_len % args.model_axis_size != 0:
+            raise ValueError("--ctx-len must be divisible by --model-axis-size (the residual stream is sharded over time)")
+    elif getattr(cfg, "vocab_parallel", False):
+        cfg.vocab_parallel = False       # one process evaluates the whole vocabulary itself
+    runtime = create_runtime(args.seed, cfg, batch_size=args.batch_size, device=device, sharding=sharding)
     if params is not None:
         load_runtime_params(runtime, params)
     dataset = create_binidx_dataset(
@@ -70,7 +82,7 @@ def evaluate_binidx(args) -> dict:
             count = float(batch["mask"].sum())
             total_nll += float(metrics["loss"]) * count
             total_count += count
-            if args.print_every and step % args.print_every == 0:
+            if args.print_every and step % args.print_every == 0 and _first_process():
                 print(f"eval_step={step} loss={float(metrics['loss']):.6f}")
     finally:
         dataset.close()
@@ -95,13 +107,22 @@ def parse_args(argv=None):
     add_execution_args(p)
     p.add_argument("--print-every", type=int, default=1)
     p.add_argument("--device", default="auto")
+    p.add_argument("--model-axis-size", type=int, default=1,
+                   help="tensor-parallel group size (under torch.distributed.run; every process prints nothing but rank 0)")
     return parse_args_with_config(p, argv)
+
+
+def _first_process() -> bool:
+    from ..parallel.mesh import process_info
+
+    return process_info()["process_index"] == 0
 
 
 def main(argv=None):
     args = parse_args(argv)
     m = evaluate_binidx(args)
-    print(f"eval tokens={m['tokens']} loss={m['loss']:.6f} perplexity={m['perplexity']:.6f}")
+    if _first_process():
+        print(f"eval tokens={m['tokens']} loss={m['loss']:.6f} perplexity={m['perplexity']:.6f}")
     return m
 
 

@@ -393,3 +393,34 @@ def test_comparison_matrix_profiles_seeds_provenance_and_tables(tiny_binidx, tmp
     # the other sub-commands still hand trainer flags through untouched
     plan = compare_variants.plan_variants(["--vocab-size", "300", "--screened-layers", "1"] + tiny)
     assert plan["variants"]["local_mechanism"]["trainable_params"] > plan["variants"]["local_core_baseline"]["trainable_params"]
+
+
+def test_evaluation_tool_on_a_model_axis_matches_one_process(tiny_binidx, tmp_path):
+    """``rwkv7m-eval-binidx --model-axis-size 2`` under a two-process launcher (each process holds half of the projections)
+    reports the loss that one process reports for the same checkpoint and batches."""
+    import socket
+    import subprocess
+    import sys
+
+    out = tmp_path / "run"
+    tiny = ["--vocab-size", "300", "--d-model", "32", "--d-ffn", "64", "--n-layers", "2", "--n-heads", "2", "--head-size", "16",
+            "--no-screening", "--device", "cpu"]
+    args = train_binidx.parse_args(["--data-file", tiny_binidx, "--ctx-len", "4", "--steps", "2", "--print-every", "0",
+                                    "--output-dir", str(out)] + tiny)
+    _, _, ckpt = train_binidx.run_training(args)
+    base = ["--data-file", tiny_binidx, "--checkpoint", str(ckpt), "--ctx-len", "4", "--batch-size", "2", "--steps", "3",
+            "--print-every", "0", "--device", "cpu"]
+    single = eval_binidx.evaluate_binidx(eval_binidx.parse_args(base))
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    root = Path(__file__).resolve().parents[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "rwkv7m_b200.cli.eval_binidx", "--model-axis-size", "2"] + base
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(root),
+                         env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.startswith("eval tokens=")]
+    assert len(lines) == 1                                        # only the first process reports
+    loss = float(lines[0].split("loss=")[1].split()[0])
+    assert loss == pytest.approx(single["loss"], rel=1e-4) and f"tokens={single['tokens']}" in lines[0]
