@@ -14,6 +14,7 @@ from .collectives import (CollectiveAudit, audit_collectives, audit_lowered_coll
                           ownership_table)
 from .dp import DataParallelTrainer
 from .environment import environment_manifest, runtime_version_manifest
+from .health import PeerFailureError, PeerHealth
 from .input_pipeline import (BatchLayout, HostBinIdxDataset, compute_batch_layout, create_host_binidx_dataset,
                              iter_prefetched_global_batches)
 from .lifecycle import (ShardingProbe, initialize_sharding_probe, restore_sharding_probe_checkpoint,
