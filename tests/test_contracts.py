@@ -842,3 +842,42 @@ def test_doctor_reports_what_the_installation_can_run(capsys):
     assert "torch" in report["environment"]["packages"]
     if not torch.cuda.is_available():
         assert report["checks"]["gpus"] == [] and report["ok"]
+
+
+def test_bench_clock_record_and_reference_arm(capsys, monkeypatch):
+    """The benchmark's clock record is the median SM clock, the highest maximum and the set of throttle reasons that were
+    active in any sample; malformed lines are skipped; without nvidia-smi the record says so.  The reference arm prints one
+    JSON line with ``impl: reference`` and exits normally when the reference cannot be imported."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("bench_module", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class FakeProc:
+        def terminate(self):
+            pass
+
+        def communicate(self, timeout=None):
+            return ("1755, 1965, 912.1, Not Active, Not Active, Not Active, Active\n"
+                    "1740, 1965, 998.7, Not Active, Not Active, Not Active, Active\n"
+                    "garbage line\n"
+                    "[N/A], 1965, 10.0, Not Active, Not Active, Not Active, Not Active\n"
+                    "1770, 1965, 640.0, Not Active, Not Active, Not Active, Not Active\n"), ""
+
+    sampler = bench.ClockSampler(0)
+    sampler.proc = FakeProc()
+    record = sampler.stop()
+    assert record["sm_mhz"] == 1755 and record["sm_max_mhz"] == 1965 and record["samples"] == 3
+    assert record["reasons"] == ["sw_power_cap"] and record["power_w_max"] == pytest.approx(998.7)
+    idle = bench.ClockSampler(0).stop()
+    assert idle["sm_mhz"] is None and idle["reasons"] == ["nvidia-smi unavailable"]
+
+    args = bench.parse_args(["--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"])
+    monkeypatch.setenv("RANK", "0")
+    bench.reference_arm(args)
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and ("unavailable" in line or "value" in line)
+    defaults = bench.parse_args([])
+    assert defaults.gpus == 1 and defaults.warmup >= 3 and defaults.remat == "off"
