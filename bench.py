@@ -194,6 +194,22 @@ def wkv7_kernel_figure(torch, device, T, B, H, iters=5):
             "convention": "9 N^2 FLOPs per token and head forward, backward 2.5x; autograd call of ops.wkv7, CUDA events"}
 
 
+def clock_verdict(record) -> str:
+    """How the clock record of a timed region reads: ``rejected: <reasons>`` when a hardware or thermal slowdown was active
+    in any sample, ``suspect: ...`` when the SM clock sat far below its maximum with no reason reported (a leftover clock
+    lock), ``ok`` otherwise (a software power cap alone is normal for a dense step on a 1 kW part) and ``unknown`` without
+    samples."""
+    if not isinstance(record, dict) or record.get("sm_mhz") is None:
+        return "unknown"
+    bad = [r for r in record.get("reasons", []) if r in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")]
+    if bad:
+        return "rejected: " + ", ".join(bad)
+    top = record.get("sm_max_mhz") or 0
+    if top and record["sm_mhz"] < 0.6 * top and not record.get("reasons"):
+        return f"suspect: median SM clock {record['sm_mhz']:.0f} MHz of {top:.0f} MHz with no throttle reason"
+    return "ok"
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
 
@@ -396,6 +412,11 @@ def main(argv=None):
     e1.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        try:
+            clocks["verdict"] = clock_verdict(clocks)
+        except Exception:      # never let the bookkeeping cost the measurement
+            clocks["verdict"] = "unknown"
     ms = e0.elapsed_time(e1)
     launches = K.LAUNCH_COUNT - launches0
     last_loss = float(metrics["loss"])

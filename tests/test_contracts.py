@@ -871,6 +871,10 @@ def test_bench_clock_record_and_reference_arm(capsys, monkeypatch):
     record = sampler.stop()
     assert record["sm_mhz"] == 1755 and record["sm_max_mhz"] == 1965 and record["samples"] == 3
     assert record["reasons"] == ["sw_power_cap"] and record["power_w_max"] == pytest.approx(998.7)
+    assert bench.clock_verdict(record) == "ok"                            # a software power cap alone is normal
+    assert bench.clock_verdict(dict(record, reasons=["hw_thermal_slowdown", "sw_power_cap"])) == "rejected: hw_thermal_slowdown"
+    assert bench.clock_verdict(dict(record, sm_mhz=600.0, reasons=[])).startswith("suspect")
+    assert bench.clock_verdict({"sm_mhz": None}) == "unknown" and bench.clock_verdict(None) == "unknown"
     idle = bench.ClockSampler(0).stop()
     assert idle["sm_mhz"] is None and idle["reasons"] == ["nvidia-smi unavailable"]
 
