@@ -189,6 +189,9 @@ def wkv7(r, w, k, v, a, b, state0):
         return backends.external_wkv7(r, w, k, v, a, b, state0)
     if use_cuda(r) and choice != "reference":
         return _cuda().wkv7(r, w, k, v, a, b, state0, impl=choice)
+    if choice == "chunked" and not r.is_cuda and not _FORCE_REFERENCE:
+        # the matrix formulation in float64: the same numbers as the step recurrence without a Python loop over the steps
+        return reference.wkv7_chunked(r, w, k, v, a, b, state0)
     return reference.wkv7(r, w, k, v, a, b, state0)
 
 

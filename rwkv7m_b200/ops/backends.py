@@ -28,7 +28,8 @@ def available_wkv_backends() -> tuple:
 def resolve_wkv_backend(requested: str | None = None, *, device_type: str | None = None) -> str:
     """Resolve an explicit or automatic backend.  ``auto`` is the chunked tensor-core form on CUDA devices (the scan
     kernels take over per call for head sizes other than 64, fp32 vectors and sequences shorter than one chunk) and
-    the PyTorch statement on CPU.  An external backend is never selected automatically."""
+    the PyTorch statement on CPU (an explicit ``chunked`` on CPU tensors runs the float64 matrix formulation of
+    ``reference.wkv7_chunked`` instead of the step loop).  An external backend is never selected automatically."""
     selected = requested if requested is not None else (_selected or os.environ.get("RWKV7M_B200_WKV_BACKEND", "auto"))
     selected = selected.strip().lower()
     if selected != "auto":

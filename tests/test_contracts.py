@@ -885,3 +885,38 @@ def test_bench_clock_record_and_reference_arm(capsys, monkeypatch):
     assert line["impl"] == "reference" and ("unavailable" in line or "value" in line)
     defaults = bench.parse_args([])
     assert defaults.gpus == 1 and defaults.warmup >= 3 and defaults.remat == "off"
+
+
+def test_chunked_backend_choice_on_cpu_uses_the_matrix_formulation(monkeypatch):
+    """``set_wkv_backend("chunked")`` on CPU tensors runs the float64 chunk formulation: same outputs and gradients as the
+    step recurrence, and much fewer Python-level steps for a long sequence."""
+    import time
+
+    from rwkv7m_b200 import ops
+
+    monkeypatch.delenv("RWKV7M_B200_WKV_BACKEND", raising=False)
+    torch.manual_seed(0)
+    B, T, H, N = 1, 512, 2, 16
+    r, k, v = (torch.randn(B, T, H, N) * 0.5 for _ in range(3))
+    w = -torch.nn.functional.softplus(-torch.randn(B, T, H, N)) - 0.5
+    kk = torch.nn.functional.normalize(torch.randn(B, T, H, N), dim=-1)
+    a, b = -kk, kk * torch.sigmoid(torch.randn(B, T, H, N))
+    s0 = torch.randn(B, H, N, N) * 0.1
+
+    def run():
+        leaves = [t.clone().requires_grad_(True) for t in (r, w, k, v, a, b, s0)]
+        t0 = time.perf_counter()
+        y, sT = ops.wkv7(*leaves)
+        (y.sum() + sT.sum()).backward()
+        return y.detach(), sT.detach(), [t.grad for t in leaves], time.perf_counter() - t0
+
+    y_ref, s_ref, g_ref, t_ref = run()
+    R.set_wkv_backend("chunked")
+    try:
+        y, s, g, t_chunked = run()
+    finally:
+        R.set_wkv_backend(None)
+    assert torch.allclose(y, y_ref, atol=2e-5) and torch.allclose(s, s_ref, atol=2e-5)
+    for got, want in zip(g, g_ref):
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-3)
+    assert t_chunked < t_ref
