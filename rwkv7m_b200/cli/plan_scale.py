@@ -21,6 +21,11 @@ def parse_args(argv=None):
                    default="config")
     p.add_argument("--optimizer-shards", type=int, default=1)
     p.add_argument("--tokens-per-device", type=int, default=0)
+    p.add_argument("--compare-modes", action="store_true",
+                   help="add a per-GPU memory table for data-parallel, fused, ZeRO-3 and tensor-parallel launches")
+    p.add_argument("--gpus", type=int, default=8)
+    p.add_argument("--hbm-gb", type=float, default=180.0)
+    p.add_argument("--recompute-layers", type=int, default=0)
     return p.parse_args(argv)
 
 
@@ -40,7 +45,14 @@ def build_report(args):
 def main(argv=None):
     args = parse_args(argv)
     est = build_estimate(args)
-    print(json.dumps({"environment": runtime_version_manifest(), "estimate": est.to_dict()}, indent=2, sort_keys=True))
+    report = {"environment": runtime_version_manifest(), "estimate": est.to_dict()}
+    if args.compare_modes:
+        from ..parallel.scaling import compare_parallelism_modes
+
+        cfg = load_model_config(args.model_config) if args.model_config else model_preset(args.model_preset)
+        report["modes"] = compare_parallelism_modes(cfg, gpus=args.gpus, tokens_per_device=args.tokens_per_device or 32768,
+                                                    hbm_bytes=int(args.hbm_gb * 10 ** 9), recompute_layers=args.recompute_layers)
+    print(json.dumps(report, indent=2, sort_keys=True))
     return est
 
 

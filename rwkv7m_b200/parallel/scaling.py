@@ -92,13 +92,53 @@ def abstract_parameter_summary(config: ModelConfig) -> ParameterSummary:
 
 def saved_activation_bytes_per_layer(config: ModelConfig, tokens: int) -> int:
     """bf16 [tokens, C] tensors a block keeps for backward (layer input, LN outputs, six mixed
-    inputs, r/k/v, four LoRA outputs, five recurrence inputs, y, gate product, FFN hidden) plus
-    the fp32 ``sa`` vectors and the every-16-steps state checkpoints of the recurrence."""
+    inputs, r/k/v, four LoRA outputs, five recurrence inputs, y, gate product, FFN hidden) plus what the
+    chunked recurrence saves: its removal products in bf16 and one fp32 state per 64-step chunk.
+    Calibration: 24 such layers plus 18 bytes per parameter give 131 GB for the 1.5B model at 8 x 4096 tokens; the
+    measured peak of that step is 127 GB."""
     C, F, N = config.d_model, config.ffn_dim, config.head_size
     units = 1 + 1 + 6 + 3 + 4 + 5 + 1 + 1 + 1 + 1 + 1  # [tokens, C] bf16 tensors
     act = tokens * C * 2 * units + tokens * F * 2
-    wkv = tokens * C * 4 + (tokens // 16 + 1) * C * N * 4
+    wkv = tokens * C * 2 + (tokens // 64 + 1) * C * N * 4
     return int(act + wkv)
+
+
+def compare_parallelism_modes(config: ModelConfig, *, gpus: int = 8, tokens_per_device: int = 32768,
+                              hbm_bytes: int = 180 * 10 ** 9, recompute_layers: int = 0, model_axis_sizes=(2, 4, 8)) -> list:
+    """Per-GPU memory of one training step under each way this framework can split a model over ``gpus`` GPUs, with the
+    storage scheme it really uses (fp32 master 4 B + bf16 compute copy 2 B + fp32 gradient 4 B + two fp32 moments 8 B per
+    parameter) and the activation estimate above.  An estimate for choosing a launch, not a fit guarantee: allocator
+    slack, GEMM workspaces, the LM-head chunk buffer and the communication buffers are not counted.
+
+    ``tokens_per_device`` is the batch of one data-parallel rank; under a model axis of M the M GPUs of a group share one
+    such batch (sequence-sharded residual stream), so activations divide by M."""
+    n = abstract_parameter_summary(config).total
+    L = config.n_layers
+    layer_params = n / max(L, 1)
+    kept = max(L - recompute_layers, 0)
+
+    def activations(tokens):
+        full = saved_activation_bytes_per_layer(config, int(tokens))
+        boundary = int(tokens) * config.d_model * 2                      # a recomputed layer keeps its input only
+        return kept * full + (L - kept) * boundary + (full if recompute_layers else 0)
+
+    rows = []
+
+    def add(mode, weights, act, note):
+        total = int(weights + act)
+        rows.append({"mode": mode, "weight_state_bytes": int(weights), "activation_bytes": int(act), "per_gpu_bytes": total,
+                     "fits": total <= hbm_bytes, "headroom_bytes": int(hbm_bytes - total), "note": note})
+
+    add("dp-allreduce", 18 * n, activations(tokens_per_device), "everything replicated; NCCL / gloo all-reduce")
+    add("dp-fused", 6 * n + 12 * n / gpus, activations(tokens_per_device),
+        "bf16 weights and fp32 gradients replicated, masters and moments of the bulk weights sharded")
+    add("zero3", 18 * n / gpus + 2 * layer_params * 2 + 3 * layer_params * 4, activations(tokens_per_device),
+        "parameters, gradients and optimizer state sharded; two gathered layers and three gradient buffers resident")
+    for m in model_axis_sizes:
+        if m <= gpus and gpus % m == 0 and config.n_heads % m == 0 and config.ffn_dim % m == 0:
+            add(f"tp{m}" + (f" x dp{gpus // m}" if gpus // m > 1 else ""), 18 * n / m, activations(tokens_per_device) / m,
+                "projections, heads and feed-forward width split over the model axis; replicated small leaves ignored")
+    return rows
 
 
 def estimate_training_memory(config: ModelConfig, dtype_policy: DTypePolicy, *, model_axis_size: int,

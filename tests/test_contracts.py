@@ -920,3 +920,27 @@ def test_chunked_backend_choice_on_cpu_uses_the_matrix_formulation(monkeypatch):
     for got, want in zip(g, g_ref):
         assert torch.allclose(got, want, atol=2e-4, rtol=1e-3)
     assert t_chunked < t_ref
+
+
+def test_parallelism_mode_comparison_is_calibrated_and_ordered(capsys):
+    """The launch planner's per-GPU table: for the 1.5B headline shape the replicated and the ZeRO-3 estimates sit within
+    10 % of the peaks measured on B200 (127 GB on one GPU, 102.5 GB per GPU on eight), sharding never raises the number,
+    the 7B preset at 16 x 4096 tokens per group only fits from a model axis of 4 on, and recompute lowers activations."""
+    from rwkv7m_b200.cli import plan_scale
+    from rwkv7m_b200.config import bench_config, model_preset
+    from rwkv7m_b200.parallel.scaling import compare_parallelism_modes
+
+    rows = {r["mode"]: r for r in compare_parallelism_modes(bench_config("1.5b"), gpus=8, tokens_per_device=32768)}
+    assert rows["dp-allreduce"]["per_gpu_bytes"] / 1e9 == pytest.approx(127.0, rel=0.10)
+    assert rows["zero3"]["per_gpu_bytes"] / 1e9 == pytest.approx(102.5, rel=0.10)
+    assert rows["dp-allreduce"]["per_gpu_bytes"] > rows["dp-fused"]["per_gpu_bytes"] > rows["zero3"]["per_gpu_bytes"]
+    assert rows["tp2 x dp4"]["per_gpu_bytes"] > rows["tp4 x dp2"]["per_gpu_bytes"] > rows["tp8"]["per_gpu_bytes"]
+    assert all(r["fits"] for r in rows.values())
+    big = {r["mode"]: r for r in compare_parallelism_modes(model_preset("7b"), gpus=8, tokens_per_device=65536)}
+    assert not big["zero3"]["fits"] and not big["tp2 x dp4"]["fits"] and big["tp4 x dp2"]["fits"] and big["tp8"]["fits"]
+    lean = {r["mode"]: r for r in compare_parallelism_modes(model_preset("7b"), gpus=8, tokens_per_device=65536,
+                                                              recompute_layers=32)}
+    assert lean["tp8"]["activation_bytes"] < 0.1 * big["tp8"]["activation_bytes"]
+    plan_scale.main(["--model-preset", "7b", "--model-axis-size", "8", "--compare-modes", "--tokens-per-device", "65536"])
+    report = json.loads(capsys.readouterr().out)
+    assert [r["mode"] for r in report["modes"]][:3] == ["dp-allreduce", "dp-fused", "zero3"] and "estimate" in report
