@@ -132,3 +132,25 @@ def test_corpus_converter_tokenises_once_and_keeps_the_document_order(tmp_path, 
         b.close()
     with pytest.raises(ValueError, match="does not fit"):
         make_binidx.build_binidx(src, tmp_path / "narrow", epochs=1, dtype="uint8")
+
+
+def test_native_runtime_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The C++ sources compiled with ``-fsanitize=address,undefined`` and driven by random inputs (tests/
+    host_runtime_fuzz.cpp): no report, and the batch encoder agrees with the single-document one."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    compiler = shutil.which("g++") or shutil.which("c++")
+    if compiler is None:
+        pytest.skip("no C++ compiler")
+    root = Path(__file__).resolve().parents[1]
+    exe = tmp_path / "fuzz"
+    build = subprocess.run([compiler, "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-omit-frame-pointer",
+                            "-pthread", str(root / "rwkv7m_b200" / "csrc" / "host_runtime.cpp"),
+                            str(root / "tests" / "host_runtime_fuzz.cpp"), "-o", str(exe)], capture_output=True, text=True)
+    if build.returncode != 0:
+        pytest.skip("sanitizer runtime not available: " + build.stderr[-200:])
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and "fuzz ok" in run.stdout, (run.stdout + run.stderr)[-2000:]
+    assert "runtime error" not in run.stderr and "AddressSanitizer" not in run.stderr
