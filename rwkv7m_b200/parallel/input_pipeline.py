@@ -110,10 +110,13 @@ def iter_prefetched_global_batches(host_dataset, device=None, *, start_step, ste
     q: queue.Queue = queue.Queue(maxsize=prefetch_size)
     copy_stream = torch.cuda.Stream(device=device) if use_cuda else None
     failure = []
+    cancelled = threading.Event()      # set when the consumer stops early: the worker must not read the rest of the run
 
     def worker():
         try:
             for step in range(start, stop):
+                if cancelled.is_set():
+                    break
                 host = host_dataset.get_batch(step, epoch=epoch, pin_memory=use_cuda)
                 if use_cuda:
                     with torch.cuda.stream(copy_stream):
@@ -140,6 +143,7 @@ def iter_prefetched_global_batches(host_dataset, device=None, *, start_step, ste
                 torch.cuda.current_stream(device).wait_event(event)
             yield step, batch
     finally:
+        cancelled.set()
         while thread.is_alive():
             try:
                 q.get(timeout=0.05)

@@ -944,3 +944,37 @@ def test_parallelism_mode_comparison_is_calibrated_and_ordered(capsys):
     plan_scale.main(["--model-preset", "7b", "--model-axis-size", "8", "--compare-modes", "--tokens-per-device", "65536"])
     report = json.loads(capsys.readouterr().out)
     assert [r["mode"] for r in report["modes"]][:3] == ["dp-allreduce", "dp-fused", "zero3"] and "estimate" in report
+
+
+def test_prefetch_thread_failures_and_early_exit_do_not_hang():
+    """A read error in the prefetch thread surfaces in the consumer after the batches that were already produced, and a
+    consumer that stops early (an exception in the training step) lets the worker thread end at once: it neither blocks on a
+    full queue nor reads the remaining batches of the run."""
+    import threading
+
+    from rwkv7m_b200.parallel.input_pipeline import iter_prefetched_global_batches
+
+    class Flaky:
+        def __init__(self, fail_at):
+            self.fail_at, self.calls = fail_at, 0
+
+        def get_batch(self, step, *, epoch=0, pin_memory=False):
+            self.calls += 1
+            if step == self.fail_at:
+                raise OSError("short read")
+            return {"input_ids": torch.full((1, 2), step, dtype=torch.int32)}
+
+    seen = []
+    with pytest.raises(OSError, match="short read"):
+        for step, batch in iter_prefetched_global_batches(Flaky(3), None, start_step=0, steps=6, prefetch_size=2):
+            seen.append((step, int(batch["input_ids"][0, 0])))
+    assert seen == [(0, 0), (1, 1), (2, 2)]
+
+    before = threading.active_count()
+    source = Flaky(fail_at=-1)
+    with pytest.raises(RuntimeError, match="step failed"):
+        for step, _ in iter_prefetched_global_batches(source, None, start_step=0, steps=50, prefetch_size=2):
+            if step == 1:
+                raise RuntimeError("step failed")
+    assert threading.active_count() == before          # the worker was drained and joined
+    assert source.calls <= 6                            # ... without reading the rest of the run first
