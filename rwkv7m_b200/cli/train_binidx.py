@@ -50,7 +50,8 @@ def parse_args(argv=None):
     p.add_argument("--print-every", type=int, default=10)
     p.add_argument("--output-dir", default=None)
     p.add_argument("--save-every", type=int, default=0)
-    p.add_argument("--resume", default=None, help="checkpoint directory to resume from")
+    p.add_argument("--resume", default=None,
+                   help="checkpoint directory, or 'auto': the newest complete checkpoint under --output-dir (a fresh start if none)")
     p.add_argument("--eval-every", type=int, default=0)
     p.add_argument("--eval-steps", type=int, default=1)
     p.add_argument("--device", default="auto")
@@ -103,6 +104,11 @@ def run_training(args):
         raise ValueError("gradient_accumulation_steps must be positive")
     if args.batch_size % args.gradient_accumulation_steps != 0:
         raise ValueError("batch_size must be divisible by gradient_accumulation_steps")
+    if args.resume == "auto":     # newest complete checkpoint of this output directory, or a fresh start
+        from ..parallel.checkpoint import latest_complete_checkpoint
+
+        found = latest_complete_checkpoint(args.output_dir)
+        args.resume = str(found) if found is not None else None
     if args.resume:
         cfg, payload = load_train_checkpoint_metadata(args.resume)
         start_step = int(payload.get("step", 0))

@@ -76,7 +76,8 @@ def parse_args(argv=None):
     p.add_argument("--save-every", type=int, default=0)
     p.add_argument("--keep-last-checkpoints", type=int, default=0)
     p.add_argument("--checkpoint-backend", choices=["flax", "orbax", "single", "sharded"], default="flax")
-    p.add_argument("--resume", default=None)
+    p.add_argument("--resume", default=None,
+                   help="checkpoint directory, or 'auto': the newest complete checkpoint under --output-dir (a fresh start if none)")
     p.add_argument("--prefetch-size", type=int, default=2)
     p.add_argument("--carry-state", action="store_true")
     p.add_argument("--eval-every", type=int, default=0)
@@ -260,6 +261,11 @@ def run_distributed_training(args):
         torch.cuda.set_device(device)
     else:
         device = pick_device(args.device)
+    if args.resume == "auto":     # newest complete checkpoint of this output directory, or a fresh start
+        from ..parallel.checkpoint import latest_complete_checkpoint
+
+        found = latest_complete_checkpoint(args.output_dir)
+        args.resume = str(found) if found is not None else None
     if args.resume:
         meta = load_distributed_checkpoint_metadata(args.resume)
         cfg, start_step = meta.config, meta.start_step

@@ -6,7 +6,8 @@ The names exported here are those of the reference's ``rwkv7m.distributed`` pack
 the classes that only exist here (trainers, engines) are exported next to them."""
 
 from .audit import DistributedRunAuditIssue, DistributedRunAuditReport, audit_distributed_run, audit_report_to_dict
-from .checkpoint import (DistributedCheckpointPayload, checkpoint_path, list_checkpoint_dirs,
+from .checkpoint import (DistributedCheckpointPayload, checkpoint_is_complete, checkpoint_path, latest_complete_checkpoint,
+                         list_checkpoint_dirs,
                          load_distributed_checkpoint_metadata, load_orbax_runtime_state, load_orbax_train_state,
                          restore_distributed_runtime_state, restore_distributed_train_state, rotate_checkpoints,
                          save_data_parallel_checkpoint, save_orbax_runtime_state, save_orbax_train_state)

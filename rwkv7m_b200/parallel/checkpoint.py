@@ -33,6 +33,7 @@ from ..io.checkpoint import (
 from ..io.names import from_portable, to_portable
 from ..io.safetensors_io import save_model_safetensors
 
+TP_SHARD_FILE = "tp_state.rank{rank:05d}.safetensors"
 BACKEND_ALIASES = {"flax": "single", "single": "single", "orbax": "sharded", "sharded": "sharded"}
 
 
@@ -65,6 +66,36 @@ def list_checkpoint_dirs(output_dir) -> list:
             if tail.isdigit():
                 found.append((int(tail), path))
     return [p for _, p in sorted(found)]
+
+
+def checkpoint_is_complete(checkpoint_dir) -> bool:
+    """True when the directory holds everything a restore reads: a parseable ``checkpoint.json`` (written last), the model
+    file, and the state files of its backend (one train-state file, or every rank's shard), none of them empty."""
+    checkpoint_dir = Path(checkpoint_dir)
+    try:
+        with open(checkpoint_dir / CHECKPOINT_JSON, "r", encoding="utf-8") as f:
+            payload = json.load(f)
+    except (OSError, ValueError):
+        return False
+    needed = [MODEL_SAFETENSORS]
+    if payload.get("backend", "single") == "sharded" and payload.get("layout") == "tensor_parallel":
+        needed += [TP_SHARD_FILE.format(rank=r) for r in range(int(payload.get("model_parallel", 1)))]
+    elif payload.get("backend", "single") == "sharded":
+        needed += [TRAIN_STATE_FILE] + [f"optimizer_shard.rank{r:05d}.safetensors" for r in range(int(payload.get("world_size", 1)))]
+    else:
+        needed.append(TRAIN_STATE_FILE)
+    return all((checkpoint_dir / name).is_file() and (checkpoint_dir / name).stat().st_size > 0 for name in needed)
+
+
+def latest_complete_checkpoint(output_dir):
+    """The newest ``ckpt-%08d`` directory under ``output_dir`` that a restore can use, or None: what ``--resume auto``
+    picks, so that a job restarted after a crash in the middle of a save falls back to the checkpoint before it."""
+    if output_dir is None:
+        return None
+    for path in reversed(list_checkpoint_dirs(output_dir)):
+        if checkpoint_is_complete(path):
+            return path
+    return None
 
 
 def load_distributed_checkpoint_raw_metadata(checkpoint_dir):
@@ -217,9 +248,6 @@ def _save_checkpoint_dir(checkpoint_dir, train_state, config, process_info, *, b
             f.write("\n")
     _barrier(process_info)
     return checkpoint_dir
-
-
-TP_SHARD_FILE = "tp_state.rank{rank:05d}.safetensors"
 
 
 def _save_tensor_parallel_shards(checkpoint_dir, train_state, config, process_info, tp, *, rng_key, dataset_position,

@@ -137,3 +137,29 @@ def test_bench_tool_times_variants_and_can_export_a_timeline(tiny_binidx, tmp_pa
     traces = sorted(p.name for p in (tmp_path / "tl").iterdir())
     assert traces == ["baseline.json", "read_write.json", "screening.json"]
     assert json.loads((tmp_path / "tl" / "baseline.json").read_text())["traceEvents"]
+
+
+def test_resume_auto_takes_the_newest_complete_checkpoint(tiny_binidx, tmp_path):
+    """``--resume auto``: a fresh start when the output directory has no checkpoint; after a crash in the middle of a save
+    (a directory without its ``checkpoint.json``, or with a zero-length state file) the run continues from the checkpoint
+    before it.  Both trainers."""
+    from rwkv7m_b200.cli import train_binidx
+    from rwkv7m_b200.parallel import checkpoint_is_complete, latest_complete_checkpoint
+
+    out = tmp_path / "auto"
+    _, _, s0 = _run(_argv(tiny_binidx, out, "--resume", "auto", "--save-every", "1", steps=3))
+    assert s0["start_step"] == 0 and latest_complete_checkpoint(out).name == "ckpt-00000003"
+    (out / "ckpt-00000003" / "checkpoint.json").unlink()                      # the newest save never finished
+    assert not checkpoint_is_complete(out / "ckpt-00000003") and latest_complete_checkpoint(out).name == "ckpt-00000002"
+    (out / "ckpt-00000002" / "train_state.safetensors").write_bytes(b"")      # and the one before lost its state file
+    assert latest_complete_checkpoint(out).name == "ckpt-00000001"
+    ts, _, s1 = _run(_argv(tiny_binidx, out, "--resume", "auto", steps=1))
+    assert s1["start_step"] == 1 and int(ts.step) == 2
+    assert latest_complete_checkpoint(tmp_path / "nowhere") is None and latest_complete_checkpoint(None) is None
+    # the single-process trainer takes the same word
+    single = tmp_path / "single"
+    base = ["--data-file", tiny_binidx, "--ctx-len", "4", "--print-every", "0", "--output-dir", str(single), "--save-every", "1",
+            "--resume", "auto"] + TINY
+    train_binidx.run_training(train_binidx.parse_args(base + ["--steps", "2"]))
+    ts2, _, _ = train_binidx.run_training(train_binidx.parse_args(base + ["--steps", "1"]))
+    assert int(ts2.step) == 3
