@@ -51,7 +51,9 @@ def parse_args(argv=None):
     p.add_argument("--output-dir", default=None)
     p.add_argument("--save-every", type=int, default=0)
     p.add_argument("--resume", default=None,
-                   help="checkpoint directory, or 'auto': the newest complete checkpoint under --output-dir (a fresh start if none)")
+                   help="checkpoint directory (then --steps counts further updates), or 'auto': the newest complete checkpoint "
+                        "under --output-dir, a fresh start if none (then --steps is the length of the whole run and a "
+                        "restarted command does what is left)")
     p.add_argument("--eval-every", type=int, default=0)
     p.add_argument("--eval-steps", type=int, default=1)
     p.add_argument("--device", default="auto")
@@ -109,6 +111,9 @@ def run_training(args):
 
         found = latest_complete_checkpoint(args.output_dir)
         args.resume = str(found) if found is not None else None
+        resumed_automatically = found is not None
+    else:
+        resumed_automatically = False
     if args.resume:
         cfg, payload = load_train_checkpoint_metadata(args.resume)
         start_step = int(payload.get("step", 0))
@@ -118,6 +123,9 @@ def run_training(args):
     else:
         cfg = build_config(args)
         start_step = 0
+    epoch_steps = max(args.steps, 1)
+    if resumed_automatically:   # --resume auto: --steps is the length of the whole run, this process does what is left
+        args.steps = max(args.steps - start_step, 0)
     if args.ctx_len > cfg.max_seq_len:
         raise ValueError(f"ctx_len={args.ctx_len} exceeds model max_seq_len={cfg.max_seq_len}")
     if cfg.vocab_parallel:
@@ -125,7 +133,7 @@ def run_training(args):
     device = pick_device(args.device)
     dataset = create_binidx_dataset(
         args.data_file, ctx_len=args.ctx_len, batch_size=args.batch_size, magic_prime=args.magic_prime,
-        epoch_steps=max(args.steps, 1), sampling_mode=args.sampling_mode,
+        epoch_steps=epoch_steps, sampling_mode=args.sampling_mode,
     )
     runtime, train_state = create_train_runtime(
         args.seed, cfg, batch_size=args.batch_size, total_steps=max(start_step + args.steps, 1), device=device

@@ -23,6 +23,7 @@ import argparse
 import gc
 import json
 import math
+import os
 import time
 from datetime import datetime, timezone
 from pathlib import Path
@@ -77,7 +78,9 @@ def parse_args(argv=None):
     p.add_argument("--keep-last-checkpoints", type=int, default=0)
     p.add_argument("--checkpoint-backend", choices=["flax", "orbax", "single", "sharded"], default="flax")
     p.add_argument("--resume", default=None,
-                   help="checkpoint directory, or 'auto': the newest complete checkpoint under --output-dir (a fresh start if none)")
+                   help="checkpoint directory (then --steps counts further updates), or 'auto': the newest complete checkpoint "
+                        "under --output-dir, a fresh start if none (then --steps is the length of the whole run and a "
+                        "restarted command does what is left)")
     p.add_argument("--prefetch-size", type=int, default=2)
     p.add_argument("--carry-state", action="store_true")
     p.add_argument("--eval-every", type=int, default=0)
@@ -266,6 +269,9 @@ def run_distributed_training(args):
 
         found = latest_complete_checkpoint(args.output_dir)
         args.resume = str(found) if found is not None else None
+        resumed_automatically = found is not None
+    else:
+        resumed_automatically = False
     if args.resume:
         meta = load_distributed_checkpoint_metadata(args.resume)
         cfg, start_step = meta.config, meta.start_step
@@ -274,6 +280,13 @@ def run_distributed_training(args):
                 raise ValueError("--model-config does not match the model config stored in --resume")
     else:
         cfg, start_step = build_config(args), 0
+    epoch_steps = max(args.steps, 1)
+    if resumed_automatically:
+        # With --resume auto the command line describes the WHOLE run, so that the same command, run again by a launcher's
+        # restart or a requeue, ends where the first launch would have: --steps counts from step 0 and this process does
+        # what is left (schedule and sampling see the same totals as an uninterrupted run).  --resume <dir> keeps
+        # "--steps further updates".
+        args.steps = max(args.steps - int(start_step), 0)
     if args.ctx_len > cfg.max_seq_len:
         raise ValueError(f"ctx_len={args.ctx_len} exceeds model max_seq_len={cfg.max_seq_len}")
     if cfg.vocab_parallel and not use_tp:
@@ -282,7 +295,7 @@ def run_distributed_training(args):
     # every rank of a model group reads the same rows: the data axis alone divides the global batch
     dataset = create_host_binidx_dataset(
         args.data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size,
-        magic_prime=args.magic_prime, epoch_steps=max(args.steps, 1), process_index=data_rank,
+        magic_prime=args.magic_prime, epoch_steps=epoch_steps, process_index=data_rank,
         process_count=mesh.data_size, sampling_mode=args.sampling_mode,
     )
     B = dataset.layout.process_batch_size
@@ -418,7 +431,8 @@ def run_distributed_training(args):
                                                           prefetch_size=args.prefetch_size):
             if args.carry_state and dataset.should_reset_state_before_step(step):
                 runtime.rwkv_state, runtime.screen_state = runtime.initial_rwkv_state, runtime.initial_screen_state
-            if args.inject_failure_step is not None and step == args.inject_failure_step and rank == args.inject_failure_rank:
+            if (args.inject_failure_step is not None and step == args.inject_failure_step and rank == args.inject_failure_rank
+                    and int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")) == 0):   # only the first attempt of a launch
                 # between steps, nothing in flight: the other ranks find the record at the gate below (or, without the
                 # gate, run into the collective timeout)
                 raise RuntimeError(f"injected failure on rank {rank} before step {step}")

@@ -40,6 +40,14 @@ def initialize_distributed(backend: str | None = None, timeout_s: float = 600.0)
     if backend == "nccl":
         torch.cuda.set_device(local)
         kwargs["device_id"] = torch.device("cuda", local)
+    attempt = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0"))
+    if attempt > 0 and os.environ.get("TORCHELASTIC_USE_AGENT_STORE") == "True":
+        # A launcher with a fixed endpoint keeps ONE store over its restarts, so the addresses, barrier counts and failure
+        # records that the previous attempt's workers left there would be read as this attempt's: give every restart its
+        # own key space.
+        store = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), world, is_master=False,
+                              timeout=kwargs["timeout"])
+        kwargs.update(store=dist.PrefixStore(f"restart_{attempt}", store), rank=int(os.environ["RANK"]), world_size=world)
     dist.init_process_group(backend, **kwargs)
     return process_info()
 

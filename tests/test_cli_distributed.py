@@ -153,13 +153,16 @@ def test_resume_auto_takes_the_newest_complete_checkpoint(tiny_binidx, tmp_path)
     assert not checkpoint_is_complete(out / "ckpt-00000003") and latest_complete_checkpoint(out).name == "ckpt-00000002"
     (out / "ckpt-00000002" / "train_state.safetensors").write_bytes(b"")      # and the one before lost its state file
     assert latest_complete_checkpoint(out).name == "ckpt-00000001"
-    ts, _, s1 = _run(_argv(tiny_binidx, out, "--resume", "auto", steps=1))
-    assert s1["start_step"] == 1 and int(ts.step) == 2
+    # under "auto" --steps is the length of the whole run: the same command again does what is left of it
+    ts, _, s1 = _run(_argv(tiny_binidx, out, "--resume", "auto", "--save-every", "1", steps=3))
+    assert s1["start_step"] == 1 and int(ts.step) == 3 and s1["completed_steps"] == 2
+    ts, _, s1 = _run(_argv(tiny_binidx, out, "--resume", "auto", "--save-every", "1", steps=3))      # nothing left to do
+    assert s1["start_step"] == 3 and int(ts.step) == 3 and s1["completed_steps"] == 0 and s1["status"] == "completed"
     assert latest_complete_checkpoint(tmp_path / "nowhere") is None and latest_complete_checkpoint(None) is None
     # the single-process trainer takes the same word
     single = tmp_path / "single"
     base = ["--data-file", tiny_binidx, "--ctx-len", "4", "--print-every", "0", "--output-dir", str(single), "--save-every", "1",
             "--resume", "auto"] + TINY
     train_binidx.run_training(train_binidx.parse_args(base + ["--steps", "2"]))
-    ts2, _, _ = train_binidx.run_training(train_binidx.parse_args(base + ["--steps", "1"]))
+    ts2, _, _ = train_binidx.run_training(train_binidx.parse_args(base + ["--steps", "3"]))
     assert int(ts2.step) == 3

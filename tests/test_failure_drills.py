@@ -118,3 +118,36 @@ def test_dp_barrier_limit_is_a_parameter_and_a_failed_wait_makes_the_reduce_a_no
         assert float(g0.sum()) == 3.0 * 1024                                      # with a clean word it does
     finally:
         C.dp_set_wait_limit_ms(old)
+
+
+def test_launcher_restart_with_resume_auto_finishes_the_planned_run(tiny_binidx, tmp_path):
+    """Self-healing launch: ``torch.distributed.run --max-restarts 1`` with ``--resume auto``.  Rank 1 fails before step 3
+    of 6 on the first attempt; the launcher restarts both workers, they pick up ``ckpt-00000003`` by themselves and finish
+    the run at step 6 (the steps that were planned, not six more) with the losses of a run that was never interrupted, and
+    the artefacts pass the strict audit."""
+    out = tmp_path / "elastic"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--max-restarts=1",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m", "rwkv7m_b200.cli.train_binidx_distributed",
+           "--steps", "6", "--resume", "auto", "--collective-timeout-s", "30", "--inject-failure-step", "3",
+           "--inject-failure-rank", "1", "--data-file", tiny_binidx, "--ctx-len", "4", "--global-batch-size", "2",
+           "--print-every", "0", "--output-dir", str(out), "--save-every", "1", "--summary-every", "1", "--device", "cpu"] + TINY
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env, cwd=str(ROOT))
+    assert res.returncode == 0, res.stderr[-3000:]
+    summary = json.loads((out / "run_summary.json").read_text())
+    assert summary["status"] == "completed" and summary["start_step"] == 3 and summary["current_step"] == 6
+    assert sorted(p.name for p in out.iterdir() if p.name.startswith("ckpt-"))[-1] == "ckpt-00000006"
+    steps = [json.loads(l)["step"] for l in (out / "metrics.jsonl").read_text().splitlines() if '"train"' in l]
+    assert steps == [1, 2, 3, 4, 5, 6]
+    assert audit_distributed_run(out, require_complete=True).ok
+    # schedule, sampling and optimizer state continue as if nothing had happened: same loss curve as one 6-step process
+    # pair (the all-reduce of two ranks is a two-term sum, so the arithmetic is the same in both runs)
+    whole = tmp_path / "whole"
+    cmd2 = [a for a in cmd if a != "--max-restarts=1"]
+    cmd2[cmd2.index("--master-port") + 1] = str(_free_port())
+    cmd2[cmd2.index("--output-dir") + 1] = str(whole)
+    cmd2[cmd2.index("--inject-failure-step") + 1] = "99"
+    res = subprocess.run(cmd2, capture_output=True, text=True, timeout=400, env=env, cwd=str(ROOT))
+    assert res.returncode == 0, res.stderr[-3000:]
+    losses = lambda d: [json.loads(l)["loss"] for l in (d / "metrics.jsonl").read_text().splitlines() if '"train"' in l]
+    assert losses(out) == losses(whole)
