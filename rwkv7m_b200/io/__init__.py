@@ -7,8 +7,10 @@ from .checkpoint import (
     load_train_checkpoint,
     load_train_checkpoint_metadata,
     load_train_runtime_state,
+    safetensors_file_is_whole,
     save_runtime_state,
     save_train_checkpoint,
+    write_json_atomic,
 )
 from .names import flatten, from_portable, nest, portable_entries, to_portable
 from .safetensors_io import (

@@ -12,6 +12,7 @@ in portable names under ``model/``, both Adam moments and the update count.
 from __future__ import annotations
 
 import json
+import os
 from pathlib import Path
 
 import torch
@@ -74,10 +75,48 @@ def save_train_checkpoint(checkpoint_dir, train_state, config: ModelConfig, *, r
         "dataset_position": dataset_position,
         "metadata": {} if metadata is None else metadata,
     }
-    with open(checkpoint_dir / CHECKPOINT_JSON, "w", encoding="utf-8") as f:
+    write_json_atomic(checkpoint_dir / CHECKPOINT_JSON, payload)
+    return checkpoint_dir
+
+
+def write_json_atomic(path, payload) -> None:
+    """Write under a temporary name in the same directory and rename: a reader sees the old file or the whole new one,
+    never a prefix.  ``checkpoint.json`` marks a checkpoint as finished, so it must not exist half-written."""
+    path = Path(path)
+    tmp = path.with_name(path.name + f".tmp{os.getpid()}")
+    with open(tmp, "w", encoding="utf-8") as f:
         json.dump(payload, f, indent=2, sort_keys=True)
         f.write("\n")
-    return checkpoint_dir
+        f.flush()
+        os.fsync(f.fileno())
+    os.replace(tmp, path)
+
+
+def safetensors_file_is_whole(path) -> bool:
+    """True when the file's length is what its own header promises (8-byte header length, JSON header, tensor data up to
+    the largest ``data_offsets`` end): a save that was cut short fails this without any tensor being read."""
+    path = Path(path)
+    try:
+        size = path.stat().st_size
+        with open(path, "rb") as f:
+            head = f.read(8)
+            if len(head) != 8:
+                return False
+            n = int.from_bytes(head, "little")
+            if n <= 0 or 8 + n > size:
+                return False
+            header = json.loads(f.read(n).decode("utf-8"))
+    except (OSError, ValueError, UnicodeDecodeError):
+        return False
+    end = 0
+    for name, entry in header.items():
+        if name == "__metadata__":
+            continue
+        try:
+            end = max(end, int(entry["data_offsets"][1]))
+        except (KeyError, TypeError, IndexError, ValueError):
+            return False
+    return size == 8 + n + end
 
 
 def load_train_checkpoint_metadata(checkpoint_dir):

@@ -27,8 +27,10 @@ from ..io.checkpoint import (
     TRAIN_STATE_FILE,
     load_train_checkpoint,
     load_train_runtime_state,
+    safetensors_file_is_whole,
     save_runtime_state,
     save_train_checkpoint,
+    write_json_atomic,
 )
 from ..io.names import from_portable, to_portable
 from ..io.safetensors_io import save_model_safetensors
@@ -70,7 +72,8 @@ def list_checkpoint_dirs(output_dir) -> list:
 
 def checkpoint_is_complete(checkpoint_dir) -> bool:
     """True when the directory holds everything a restore reads: a parseable ``checkpoint.json`` (written last), the model
-    file, and the state files of its backend (one train-state file, or every rank's shard), none of them empty."""
+    file, and the state files of its backend (one train-state file, or every rank's shard; per-rank runtime state: all ranks'
+    or none), each as long as its own header says (a file cut short by a crash fails without a tensor being read)."""
     checkpoint_dir = Path(checkpoint_dir)
     try:
         with open(checkpoint_dir / CHECKPOINT_JSON, "r", encoding="utf-8") as f:
@@ -84,7 +87,11 @@ def checkpoint_is_complete(checkpoint_dir) -> bool:
         needed += [TRAIN_STATE_FILE] + [f"optimizer_shard.rank{r:05d}.safetensors" for r in range(int(payload.get("world_size", 1)))]
     else:
         needed.append(TRAIN_STATE_FILE)
-    return all((checkpoint_dir / name).is_file() and (checkpoint_dir / name).stat().st_size > 0 for name in needed)
+    for r in range(int(payload.get("world_size", 1))):     # carried runtime state, where the run saved one per rank
+        if (checkpoint_dir / f"runtime_state.rank{r:05d}.safetensors").exists():
+            needed += [f"runtime_state.rank{q:05d}.safetensors" for q in range(int(payload.get("world_size", 1)))]
+            break
+    return all(safetensors_file_is_whole(checkpoint_dir / name) for name in needed)
 
 
 def latest_complete_checkpoint(output_dir):
@@ -243,9 +250,9 @@ def _save_checkpoint_dir(checkpoint_dir, train_state, config, process_info, *, b
             "rng_key": None if rng_key is None else [int(x) for x in torch.as_tensor(rng_key).reshape(-1).tolist()],
             "dataset_position": dataset_position, "metadata": metadata or {},
         }
-        with open(checkpoint_dir / CHECKPOINT_JSON, "w", encoding="utf-8") as f:
-            json.dump(payload, f, indent=2, sort_keys=True)
-            f.write("\n")
+    _barrier(process_info)      # every rank's shard is on disk before the file that marks the checkpoint as finished
+    if rank == 0:
+        write_json_atomic(checkpoint_dir / CHECKPOINT_JSON, payload)
     _barrier(process_info)
     return checkpoint_dir
 
@@ -287,9 +294,9 @@ def _save_tensor_parallel_shards(checkpoint_dir, train_state, config, process_in
             "rng_key": None if rng_key is None else [int(x) for x in torch.as_tensor(rng_key).reshape(-1).tolist()],
             "dataset_position": dataset_position, "metadata": metadata or {},
         }
-        with open(checkpoint_dir / CHECKPOINT_JSON, "w", encoding="utf-8") as f:
-            json.dump(payload, f, indent=2, sort_keys=True)
-            f.write("\n")
+    _barrier(process_info)      # every rank's shard is on disk before the file that marks the checkpoint as finished
+    if rank == 0:
+        write_json_atomic(checkpoint_dir / CHECKPOINT_JSON, payload)
     _barrier(process_info)
     return checkpoint_dir
 
@@ -320,9 +327,7 @@ def _patch_json(checkpoint_dir, extra: dict):
     with open(path, "r", encoding="utf-8") as f:
         payload = json.load(f)
     payload.update(extra)
-    with open(path, "w", encoding="utf-8") as f:
-        json.dump(payload, f, indent=2, sort_keys=True)
-        f.write("\n")
+    write_json_atomic(path, payload)
 
 
 def restore_distributed_train_state(checkpoint_dir, train_state_template, process_info=None):

@@ -151,7 +151,10 @@ def test_resume_auto_takes_the_newest_complete_checkpoint(tiny_binidx, tmp_path)
     assert s0["start_step"] == 0 and latest_complete_checkpoint(out).name == "ckpt-00000003"
     (out / "ckpt-00000003" / "checkpoint.json").unlink()                      # the newest save never finished
     assert not checkpoint_is_complete(out / "ckpt-00000003") and latest_complete_checkpoint(out).name == "ckpt-00000002"
-    (out / "ckpt-00000002" / "train_state.safetensors").write_bytes(b"")      # and the one before lost its state file
+    blob = (out / "ckpt-00000002" / "train_state.safetensors").read_bytes()
+    (out / "ckpt-00000002" / "train_state.safetensors").write_bytes(blob[: len(blob) - 64])   # the one before was cut short
+    assert not checkpoint_is_complete(out / "ckpt-00000002")       # shorter than its own header says: no tensor is read
+    (out / "ckpt-00000002" / "train_state.safetensors").write_bytes(b"")
     assert latest_complete_checkpoint(out).name == "ckpt-00000001"
     # under "auto" --steps is the length of the whole run: the same command again does what is left of it
     ts, _, s1 = _run(_argv(tiny_binidx, out, "--resume", "auto", "--save-every", "1", steps=3))
