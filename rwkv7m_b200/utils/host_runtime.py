@@ -32,7 +32,7 @@ def build_host_runtime(force: bool = False) -> Path:
     compiler = shutil.which(os.environ.get("CXX", "g++")) or shutil.which("c++")
     if compiler is None:
         raise RuntimeError("no C++ compiler found for the host runtime (set CXX)")
-    tmp = LIBRARY.with_suffix(".so.tmp")
+    tmp = LIBRARY.with_suffix(f".so.tmp{os.getpid()}")      # several processes may build at once: last rename wins
     subprocess.run([compiler, "-O3", "-std=c++17", "-shared", "-fPIC", "-pthread", "-Wall", "-o", str(tmp), str(SOURCE)],
                    check=True)
     os.replace(tmp, LIBRARY)
