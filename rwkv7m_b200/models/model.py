@@ -107,16 +107,24 @@ class ScreenedRWKVModel(nn.Module):
         new_rwkv = list(rwkv_state)
         new_screen = list(screen_state.layers) if screen_state is not None else []
         all_stats = []
+        # context parallelism: ``input_ids`` is this rank's time slice; every layer starts from the state that the rank
+        # before it reached and hands its own on (outside the recomputed region, so a recompute does not communicate)
+        cp = getattr(self, "cp", None)
         for idx, layer in enumerate(self.layers):
             scr = screen_state.layers[screened_idx[idx]] if idx in screened_idx else None
+            rwkv_in = rwkv_state[idx]
+            if cp is not None:
+                rwkv_in, scr = cp.enter(idx, rwkv_in, scr)
             if hook is not None:
                 hook.pre_forward(hook.unit_of_layer(idx))
                 x = hook.mark_enter(x, hook.unit_of_layer(idx))
             with nvtx_range(f"layer.{idx}"):
                 if (cfg.remat_blocks or idx < self.remat_layer_count) and torch.is_grad_enabled():
-                    x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_state[idx], scr, phase)
+                    x, v_first, rwkv_l, scr_l, stats = _remat_layer(layer, x, v_first, rwkv_in, scr, phase)
                 else:
-                    x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_state[idx], scr, phase)
+                    x, v_first, rwkv_l, scr_l, stats = layer(x, v_first, rwkv_in, scr, phase)
+            if cp is not None:
+                cp.leave(idx, rwkv_l, scr_l)
             check_finite(f"layer.{idx} output", x, rwkv_l.wkv)
             if hook is not None:
                 x = hook.mark_leave(x, hook.unit_of_layer(idx))
@@ -129,7 +137,11 @@ class ScreenedRWKVModel(nn.Module):
         if all_stats:
             for key in all_stats[0]:
                 agg[key] = torch.stack([torch.as_tensor(s[key]).float() for s in all_stats]).mean()
-        return x, tuple(new_rwkv), ModelScreenState(layers=tuple(new_screen)), agg
+        out_rwkv, out_screen = tuple(new_rwkv), ModelScreenState(layers=tuple(new_screen))
+        if cp is not None:
+            x = cp.tie(x)
+            out_rwkv, out_screen = cp.final_state(out_rwkv, out_screen)     # the state after the whole sequence, everywhere
+        return x, out_rwkv, out_screen, agg
 
     def compute_logits(self, hidden):
         if hidden.shape[-1] != self.config.d_model:

@@ -13,6 +13,7 @@ from .checkpoint import (DistributedCheckpointPayload, checkpoint_is_complete, c
                          save_data_parallel_checkpoint, save_orbax_runtime_state, save_orbax_train_state)
 from .collectives import (CollectiveAudit, audit_collectives, audit_lowered_collectives, compiler_ir_text, count_collectives,
                           ownership_table)
+from .context import ContextParallel
 from .dp import DataParallelTrainer
 from .environment import environment_manifest, runtime_version_manifest
 from .health import PeerFailureError, PeerHealth

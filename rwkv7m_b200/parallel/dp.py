@@ -128,6 +128,11 @@ class DataParallelTrainer:
         model.train()
         if self.mode != "fused":
             opt.zero_grad()
+        cp = getattr(model, "cp", None)
+        if cp is not None:
+            # context parallelism: this rank trains on its time slice of the rows; for the loss weights and the gradient
+            # exchange it is one more data-parallel rank
+            batch = cp.slice_batch(batch)
         scale = (1.0, 1.0) if self.world == 1 else self._loss_scale(batch)
         events = None
         if self.record_phases and opt.flat.master.is_cuda:

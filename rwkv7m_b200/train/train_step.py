@@ -86,6 +86,10 @@ def model_loss(model, batch, rwkv_state, screen_state, *, phase, include_l2wrap=
     T = int(input_ids.shape[1])
     rchunk = min(int(cfg.sequence_chunk_size or T), T)
     hchunk = min(int(cfg.head_chunk_size or cfg.sequence_chunk_size or T), T)
+    if getattr(model, "cp", None) is not None and rchunk < T:
+        # the ranks hand the state over once per layer and call; a second chunk of the same slice would receive again
+        raise ValueError("sequence_chunk_size must cover this rank's time slice under context parallelism "
+                         "(the context axis already divides the working set)")
     hidden_chunks = []
     stats_total = None
     cur_rwkv, cur_screen = rwkv_state, screen_state
