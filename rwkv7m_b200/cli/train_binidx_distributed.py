@@ -100,6 +100,10 @@ def parse_args(argv=None):
     p.add_argument("--param-axis-name", default=None)
     p.add_argument("--no-health-gate", action="store_true",
                    help="skip the host-side meeting before every step at which a peer's failure record stops the others")
+    p.add_argument("--context-parallel-size", type=int, default=1,
+                   help="split every sequence along time over this many adjacent ranks; the recurrent state is handed from "
+                        "rank to rank per layer and its gradient handed back, so the result is that of the unsplit "
+                        "sequence with 1/P of the activations per GPU (the remaining ranks form the data axis)")
     p.add_argument("--dp-mode", choices=["auto", "fused", "allreduce", "zero3"], default="auto",
                    help="fused: sharded optimizer step over NVLink (auto picks it on GPUs); allreduce: library "
                         "all-reduce (auto picks it on CPU); zero3: parameters, gradients and optimizer state "
@@ -211,6 +215,8 @@ def run_validation(args, model, cfg, device, info, eval_state):
             else:
                 rs = init_rwkv_state(B, cfg, device=device)
                 ss = init_screen_state(B, cfg.screening if cfg.screening_active else _empty(cfg), device=device)
+            if getattr(model, "cp", None) is not None:
+                batch = model.cp.slice_batch(batch)
             _, (metrics, nr, ns) = model_loss(model, batch, rs, ss, phase=args.phase, include_l2wrap=False)
             if args.carry_state:
                 eval_state["rwkv"], eval_state["screen"] = tuple(s.detach() for s in nr), ns.detach()
@@ -257,8 +263,20 @@ def run_distributed_training(args):
     mesh = make_mesh(tuple(args.mesh_axis_names), args.mesh_axis_sizes, world_size=world)
     use_tp = mesh.model_size > 1
     data_rank, _ = mesh.coords(rank)
-    info = dict(info, data_index=data_rank, data_count=mesh.data_size)
-    validate_args(args, mesh.data_size)
+    data_count = mesh.data_size
+    cp_size = int(args.context_parallel_size)
+    if cp_size > 1:
+        # context ranks read the same rows and keep their own time slice; for sampling they are one data rank, for the
+        # gradient exchange each of them is a data-parallel rank
+        if use_tp:
+            raise ValueError("--context-parallel-size is not combined with a model axis")
+        if world % cp_size != 0 or args.ctx_len % cp_size != 0:
+            raise ValueError("--context-parallel-size must divide the number of processes and --ctx-len")
+        if args.dp_mode == "zero3":
+            raise ValueError("--context-parallel-size is not combined with --dp-mode zero3")
+        data_rank, data_count = rank // cp_size, world // cp_size
+    info = dict(info, data_index=data_rank, data_count=data_count)
+    validate_args(args, data_count)
     if torch.cuda.is_available() and args.device in ("auto", None):
         device = torch.device("cuda", info["local_rank"])
         torch.cuda.set_device(device)
@@ -296,7 +314,7 @@ def run_distributed_training(args):
     dataset = create_host_binidx_dataset(
         args.data_file, ctx_len=args.ctx_len, global_batch_size=args.global_batch_size,
         magic_prime=args.magic_prime, epoch_steps=epoch_steps, process_index=data_rank,
-        process_count=mesh.data_size, sampling_mode=args.sampling_mode,
+        process_count=data_count, sampling_mode=args.sampling_mode,
     )
     B = dataset.layout.process_batch_size
     alloc = None
@@ -344,6 +362,15 @@ def run_distributed_training(args):
         trainer = DataParallelTrainer(train_state, mode="allreduce" if zero3 else mode)
     if getattr(trainer, "fused", None) is not None:
         train_state.extras["fused_optimizer"] = trainer.fused
+    if cp_size > 1:
+        from ..parallel.context import ContextParallel
+
+        context_group = None
+        for d in range(data_count):      # collective on all ranks: every group is created everywhere
+            g = torch.distributed.new_group(list(range(d * cp_size, (d + 1) * cp_size)))
+            if d == data_rank:
+                context_group = g
+        train_state.model.cp = ContextParallel(context_group)
     if args.resume:
         train_state, _ = restore_distributed_train_state(args.resume, train_state, info)
         if args.carry_state:
@@ -371,7 +398,8 @@ def run_distributed_training(args):
         "tokens_seen": 0, "checkpoint_backend": args.checkpoint_backend, "sampling_mode": args.sampling_mode,
         "carry_state": args.carry_state, "latest_checkpoint": None, "best_eval": None, "last_train": None,
         "last_eval": None, "process_info": dict(info), "dp_mode": mode,
-        "mesh": {"data": mesh.data_size, "model": mesh.model_size}, "device_error_words": {},
+        "mesh": {"data": data_count, "model": mesh.model_size, **({"context": cp_size} if cp_size > 1 else {})},
+        "device_error_words": {},
     }
     if args.output_dir is not None and rank == 0:
         _write_json(Path(args.output_dir) / "run_config.json", {

@@ -111,7 +111,8 @@ def compare_parallelism_modes(config: ModelConfig, *, gpus: int = 8, tokens_per_
     slack, GEMM workspaces, the LM-head chunk buffer and the communication buffers are not counted.
 
     ``tokens_per_device`` is the batch of one data-parallel rank; under a model axis of M the M GPUs of a group share one
-    such batch (sequence-sharded residual stream), so activations divide by M."""
+    such batch (sequence-sharded residual stream), so activations divide by M; the same holds for a context axis of C
+    (``parallel.context``), which keeps the weights replicated and sends the recurrent state from GPU to GPU instead."""
     n = abstract_parameter_summary(config).total
     L = config.n_layers
     layer_params = n / max(L, 1)
@@ -138,6 +139,14 @@ def compare_parallelism_modes(config: ModelConfig, *, gpus: int = 8, tokens_per_
         if m <= gpus and gpus % m == 0 and config.n_heads % m == 0 and config.ffn_dim % m == 0:
             add(f"tp{m}" + (f" x dp{gpus // m}" if gpus // m > 1 else ""), 18 * n / m, activations(tokens_per_device) / m,
                 "projections, heads and feed-forward width split over the model axis; replicated small leaves ignored")
+    for c in model_axis_sizes:
+        if c <= gpus and gpus % c == 0:
+            # a sequence split along time over c GPUs: the per-layer state crosses the link (bytes below), not activations
+            state = (config.n_heads * config.head_size ** 2 + 2 * config.d_model) * 4
+            add(f"cp{c}" + (f" x dp{gpus // c}" if gpus // c > 1 else ""), 6 * n + 12 * n / gpus,
+                activations(tokens_per_device) / c,
+                f"weights as dp-fused, each sequence split along time over {c} GPUs; hand-off per layer and batch row "
+                f"{state / 1e6:.2f} MB forward and the same backward")
     return rows
 
 

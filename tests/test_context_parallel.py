@@ -71,3 +71,37 @@ def test_context_split_needs_a_divisible_length_and_one_chunk():
         assert torch.equal(loss_cp, loss)
     finally:
         dist.destroy_process_group()
+
+
+def test_trainer_flag_reproduces_the_single_process_run(tiny_binidx, tmp_path):
+    """``--context-parallel-size 2`` on two ranks (with evaluation, carried state and a resume in the middle) logs the loss
+    curve of one process that reads the same rows with whole sequences."""
+    tiny = ["--d-model", "32", "--n-layers", "2", "--n-heads", "2", "--head-size", "16", "--d-ffn", "64", "--vocab-size", "300"]
+    common = ["--data-file", tiny_binidx, "--ctx-len", "8", "--global-batch-size", "2", "--print-every", "0", "--device", "cpu",
+              "--save-every", "2", "--summary-every", "1", "--lr-init", "0.001", "--lr-final", "0.001", "--warmup-steps", "0",
+              "--sampling-mode", "sequential", "--carry-state", "--eval-every", "2", "--eval-steps", "1"] + tiny
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+
+    def launch(out, nproc, extra):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), "-m", "rwkv7m_b200.cli.train_binidx_distributed",
+               "--output-dir", str(out)] + common + extra
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+        assert res.returncode == 0, res.stderr[-3000:]
+
+    def curve(out, split):
+        rows = [json.loads(l) for l in (out / "metrics.jsonl").read_text().splitlines()]
+        return [(r["step"], r["loss"]) for r in rows if r.get("split") == split]
+
+    split, whole = tmp_path / "split", tmp_path / "whole"
+    launch(split, 2, ["--context-parallel-size", "2", "--steps", "2"])
+    launch(split, 2, ["--context-parallel-size", "2", "--steps", "4", "--resume", "auto"])      # steps 3-4 after a restart
+    launch(whole, 1, ["--steps", "4"])
+    summary = json.loads((split / "run_summary.json").read_text())
+    assert summary["status"] == "completed" and summary["mesh"] == {"data": 1, "model": 1, "context": 2}
+    got, want = curve(split, "train"), curve(whole, "train")
+    assert [s for s, _ in got] == [1, 2, 3, 4]
+    for (_, a), (_, b) in zip(got, want):
+        assert a == pytest.approx(b, rel=1e-5)
+    # the evaluation before the restart (the one after it starts from a fresh carried evaluation state in the split run)
+    assert curve(split, "eval")[0][0] == 2 and curve(split, "eval")[0][1] == pytest.approx(curve(whole, "eval")[0][1], rel=1e-5)
