@@ -60,6 +60,21 @@ def evaluate_binidx(args) -> dict:
     runtime = create_runtime(args.seed, cfg, batch_size=args.batch_size, device=device, sharding=sharding)
     if params is not None:
         load_runtime_params(runtime, params)
+    cp = None
+    if int(getattr(args, "context_parallel_size", 1) or 1) > 1:
+        # very long contexts: every process holds the whole model and evaluates its time slice of the same rows, starting
+        # each layer from the state that the process before it reached
+        import torch.distributed as dist
+
+        from ..parallel.context import ContextParallel
+        from ..parallel.mesh import initialize_distributed
+
+        if sharding is not None:
+            raise ValueError("--context-parallel-size is not combined with --model-axis-size")
+        initialize_distributed()
+        if not dist.is_initialized() or dist.get_world_size() != args.context_parallel_size:
+            raise ValueError("--context-parallel-size must equal the number of launched processes")
+        cp = runtime.model.cp = ContextParallel()
     dataset = create_binidx_dataset(
         args.data_file, ctx_len=args.ctx_len, batch_size=args.batch_size, magic_prime=args.magic_prime,
         epoch_steps=max(args.steps, 1), sampling_mode=args.sampling_mode,
@@ -76,6 +91,8 @@ def evaluate_binidx(args) -> dict:
                 rs, ss = runtime.rwkv_state, runtime.screen_state
             else:
                 rs, ss = runtime.initial_rwkv_state, runtime.initial_screen_state
+            if cp is not None:
+                batch = cp.slice_batch(batch)
             _, (metrics, nr, ns) = model_loss(model, batch, rs, ss, phase=args.phase, include_l2wrap=False)
             if args.carry_state:
                 runtime.rwkv_state, runtime.screen_state = tuple(s.detach() for s in nr), ns.detach()
@@ -86,6 +103,12 @@ def evaluate_binidx(args) -> dict:
                 print(f"eval_step={step} loss={float(metrics['loss']):.6f}")
     finally:
         dataset.close()
+    if cp is not None:      # the slices' sums make the sequence's mean
+        import torch.distributed as dist
+
+        both = torch.tensor([total_nll, total_count], dtype=torch.float64, device=device)
+        dist.all_reduce(both)
+        total_nll, total_count = float(both[0]), float(both[1])
     mean = total_nll / max(total_count, 1.0)
     return {"loss": mean, "perplexity": math.exp(min(mean, 20.0)), "tokens": int(total_count), "steps": args.steps}
 
@@ -109,6 +132,9 @@ def parse_args(argv=None):
     p.add_argument("--device", default="auto")
     p.add_argument("--model-axis-size", type=int, default=1,
                    help="tensor-parallel group size (under torch.distributed.run; every process prints nothing but rank 0)")
+    p.add_argument("--context-parallel-size", type=int, default=1,
+                   help="split every sequence along time over this many processes (under torch.distributed.run), the "
+                        "recurrent state handed from process to process: long contexts with 1/P of the activations each")
     return parse_args_with_config(p, argv)
 
 

@@ -424,3 +424,13 @@ def test_evaluation_tool_on_a_model_axis_matches_one_process(tiny_binidx, tmp_pa
     assert len(lines) == 1                                        # only the first process reports
     loss = float(lines[0].split("loss=")[1].split()[0])
     assert loss == pytest.approx(single["loss"], rel=1e-4) and f"tokens={single['tokens']}" in lines[0]
+    # the same rows with every sequence split along time over the two processes (whole model on each, state handed over)
+    cmd = cmd[:cmd.index("--model-axis-size")] + ["--context-parallel-size", "2", "--carry-state", "--sampling-mode", "sequential"] + base
+    cmd[cmd.index("--master-port") + 1] = str(port + 1 if port < 65000 else port - 1)
+    carried = eval_binidx.evaluate_binidx(eval_binidx.parse_args(base + ["--carry-state", "--sampling-mode", "sequential"]))
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(root),
+                         env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.startswith("eval tokens=")]
+    assert len(lines) == 1 and f"tokens={carried['tokens']}" in lines[0]
+    assert float(lines[0].split("loss=")[1].split()[0]) == pytest.approx(carried["loss"], rel=1e-5)
