@@ -33,6 +33,8 @@ class RWKV7MRuntime:
     batch_size: int
     initial_rwkv_state: tuple
     initial_screen_state: object
+    # a parallel.context.ContextParallel: generation splits the prefill of a prompt over its processes
+    context_parallel: object = None
 
     @property
     def device(self):
@@ -200,6 +202,7 @@ def generate_ids(runtime: RWKV7MRuntime, prompt_ids, *, max_new_tokens=50, tempe
     ids, runtime.rwkv_state, runtime.screen_state = generate(
         runtime.model, _ids(runtime, prompt_ids), runtime.rwkv_state, runtime.screen_state,
         max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p, rng_key=rng_key, phase=phase,
+        context_parallel=runtime.context_parallel,
     )
     return ids
 

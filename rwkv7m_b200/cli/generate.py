@@ -28,6 +28,9 @@ def parse_args(argv=None):
     p.add_argument("--vocab-file", default=None)
     p.add_argument("--device", default="auto")
     p.add_argument("--model-axis-size", type=int, default=1, help="tensor-parallel group size (under torch.distributed.run)")
+    p.add_argument("--context-parallel-size", type=int, default=1,
+                   help="split the prefill of the prompt along time over this many processes (under torch.distributed.run); "
+                        "all of them then decode the same continuation and the first one prints it")
     p.add_argument("--json-out", default=None)
     args = parse_args_with_config(p, argv)
     if not args.prompt and not args.prompt_file:
@@ -61,6 +64,19 @@ def build_runtime(args):
         initialize_distributed()
         sharding = ShardingConfig(make_mesh(("data", "model"), (-1, args.model_axis_size)))
     runtime = create_runtime(args.seed, config, batch_size=1, device=pick_device(args.device), sharding=sharding)
+    if args.context_parallel_size > 1:
+        # long prompts: every process holds the whole model, the prefill is split along time over the processes
+        import torch.distributed as dist
+
+        from ..parallel.context import ContextParallel
+        from ..parallel.mesh import initialize_distributed
+
+        if sharding is not None:
+            raise ValueError("--context-parallel-size is not combined with --model-axis-size")
+        initialize_distributed()
+        if not dist.is_initialized() or dist.get_world_size() != args.context_parallel_size:
+            raise ValueError("--context-parallel-size must equal the number of launched processes")
+        runtime.context_parallel = ContextParallel()
     return load_runtime_params(runtime, params)      # a tensor-parallel runtime keeps this rank's slices of the full tensors
 
 

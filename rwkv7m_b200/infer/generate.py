@@ -47,10 +47,27 @@ def sample_next(last_logits, temperature, top_p, generator=None):
 
 
 @torch.no_grad()
-def prefill_last(model, prompt_ids, rwkv_state, screen_state, *, phase="read_screening_only"):
+def prefill_last(model, prompt_ids, rwkv_state, screen_state, *, phase="read_screening_only", context_parallel=None):
     """Prefill that projects only the last position onto the vocabulary (the [B, T, V] logits of a long
-    prompt are never materialised).  Returns (last logits [B, V], rwkv_state, screen_state)."""
+    prompt are never materialised).  Returns (last logits [B, V], rwkv_state, screen_state).
+
+    ``context_parallel`` (a ``parallel.context.ContextParallel`` over P processes that all hold the model and the
+    prompt): the longest prefix whose length is a multiple of P and leaves at least one token is split along time over
+    the processes, the state handed from one to the next layer by layer; every process then runs the short tail from the
+    shared state, so all of them end with the same logits and state and can decode in step."""
     model.eval()
+    cp = context_parallel
+    if cp is not None and cp.world > 1:
+        T = int(prompt_ids.shape[1])
+        main = ((T - 1) // cp.world) * cp.world
+        if main > 0:
+            model.cp = cp
+            try:
+                _, rwkv_state, screen_state, _ = model.compute_recurrent_hidden(
+                    cp.local_time_slice(prompt_ids[:, :main]).contiguous(), rwkv_state, screen_state, phase=phase)
+            finally:
+                del model.cp
+            prompt_ids = prompt_ids[:, main:]
     hidden, rwkv_state, screen_state, _ = model.compute_recurrent_hidden(prompt_ids, rwkv_state, screen_state, phase=phase)
     return model.compute_logits(hidden[:, -1:])[:, -1, :], rwkv_state, screen_state
 
@@ -135,15 +152,17 @@ def _graph_ok(model, prompt_ids):
 
 @torch.no_grad()
 def generate(model, prompt_ids, rwkv_state, screen_state, *, max_new_tokens=50, temperature=1.0,
-             top_p=0.9, rng_key=None, phase="read_screening_only", use_cuda_graph=None):
-    """Returns (new ids [B, max_new_tokens], rwkv_state, screen_state)."""
+             top_p=0.9, rng_key=None, phase="read_screening_only", use_cuda_graph=None, context_parallel=None):
+    """Returns (new ids [B, max_new_tokens], rwkv_state, screen_state).  ``context_parallel``: split the prefill of a long
+    prompt over the processes of that group (see ``prefill_last``); they all decode the same continuation."""
     if rng_key is None:
         rng_key = 0
     if isinstance(rng_key, torch.Generator):
         generator = rng_key
     else:
         generator = torch.Generator().manual_seed(int(torch.as_tensor(rng_key).flatten()[-1].item()))
-    last, rwkv_state, screen_state = prefill_last(model, prompt_ids, rwkv_state, screen_state, phase=phase)
+    last, rwkv_state, screen_state = prefill_last(model, prompt_ids, rwkv_state, screen_state, phase=phase,
+                                                  context_parallel=context_parallel)
     if use_cuda_graph is None:
         use_cuda_graph = max_new_tokens >= 8 and _graph_ok(model, prompt_ids)
     out = []

@@ -144,7 +144,10 @@ class RWKVTokenizer:
         return out
 
     def decode_bytes(self, tokens) -> bytes:
-        return b"".join(self.idx2token[int(t)] for t in tokens)
+        """Bytes of the ids.  The end-of-document id (0) has no entry in the vocabulary file and decodes to nothing, so a
+        continuation in which the model emitted it still prints; any other unknown id is an error."""
+        table, eos = self.idx2token, self.EOS
+        return b"".join(table[t] for t in map(int, tokens) if t != eos or t in table)
 
     def encode(self, text: str, *, add_eos: bool = False) -> list:
         tokens = self.encode_bytes(text.encode("utf-8"))

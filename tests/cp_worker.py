@@ -80,6 +80,16 @@ def main():
         state_diff=float((wkv_cp - torch.stack([l.wkv for l in rs1])).abs().max()),
         hidden_diff=float((hid_cp.float() - hid_full[:, rank * n:(rank + 1) * n].float()).abs().max()),
     )
+    # ---- generation: prefill of an 11-token prompt split over the ranks, then every rank decodes the same continuation
+    from rwkv7m_b200.infer.generate import generate
+
+    prompt = generate_toy_batch(9, B, 11, cfg.vocab_size)["input_ids"]
+    ts_g, rs_g, ss_g = fresh()
+    ids_cp, st_cp, _ = generate(ts_g.model, prompt, rs_g, ss_g, max_new_tokens=5, temperature=0.0, context_parallel=ContextParallel())
+    ids_one, st_one, _ = generate(ts_g.model, prompt, rs_g, ss_g, max_new_tokens=5, temperature=0.0)
+    record["generated_equal"] = bool(torch.equal(ids_cp, ids_one))
+    record["generated_state_diff"] = float((st_cp[-1].wkv - st_one[-1].wkv).abs().max())
+    record["cp_detached_after_prefill"] = not hasattr(ts_g.model, "cp")
     if screening:
         record["slot_diff"] = float((ss.layers[0].slots - ss1.layers[0].slots).abs().max())
     with open(f"{out_path}.rank{rank}.json", "w") as f:

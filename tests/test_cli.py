@@ -109,6 +109,18 @@ def test_make_binidx_and_generate(tmp_path, tiny_binidx):
                          env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
     assert res.returncode == 0, res.stderr[-2000:]
     assert json.loads((tmp_path / "tp.json").read_text(encoding="utf-8"))["samples"][0]["text"] == text
+    # and with the prefill of a longer prompt split along time over two processes that each hold the whole model
+    prompt = "hello world, hello world"
+    want = generate.main(["--checkpoint", str(ckpt), "--prompt", prompt, "--max-new-tokens", "3", "--temperature", "0",
+                          "--device", "cpu"])
+    cmd = cmd[:cmd.index("--checkpoint")] + ["--checkpoint", str(ckpt), "--prompt", prompt, "--max-new-tokens", "3",
+                                             "--temperature", "0", "--device", "cpu", "--context-parallel-size", "2",
+                                             "--json-out", str(tmp_path / "cp.json")]
+    cmd[cmd.index("--master-port") + 1] = str(port + 1 if port < 65000 else port - 1)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(root),
+                         env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert json.loads((tmp_path / "cp.json").read_text(encoding="utf-8"))["samples"][0]["text"] == want
 
 
 def test_plan_scale_outputs_exact_counts(capsys):

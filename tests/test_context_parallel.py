@@ -37,6 +37,8 @@ def test_time_split_training_matches_the_unsplit_sequence(tmp_path, world, scree
         assert rec["hidden_diff"] <= 1e-6           # evaluation path (no autograd): this rank's slice of the hidden states
         if screening:
             assert rec["slot_diff"] <= 1e-6
+        # split prefill of a prompt whose length the ranks do not divide, then the same greedy continuation on every rank
+        assert rec["generated_equal"] and rec["generated_state_diff"] <= 1e-6 and rec["cp_detached_after_prefill"]
 
 
 def test_context_split_needs_a_divisible_length_and_one_chunk():

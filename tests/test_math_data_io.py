@@ -114,6 +114,11 @@ def test_tokenizer_round_trip_ascii_and_japanese():
         ids = tok.encode(text)
         assert ids and tok.decode(ids) == text
     assert tok.encode("a", add_eos=True)[-1] == 0
+    # the end-of-document id has no vocabulary entry: it decodes to nothing (a continuation that contains it still prints),
+    # any other unknown id is an error
+    assert tok.decode(tok.encode("ab", add_eos=True) + tok.encode("cd")) == "abcd"
+    with pytest.raises(KeyError):
+        tok.decode([max(tok.idx2token) + 7])
     assert len(R.tokenizer_metadata()["tokenizer_vocab_sha256"]) == 64
 
 
