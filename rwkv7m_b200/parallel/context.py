@@ -69,7 +69,8 @@ class _Send(torch.autograd.Function):
     stream, so that backward reaches this node.  Backward: receives the cotangents from the next rank."""
 
     @staticmethod
-    def forward(ctx, cp, tag, *tensors):
+    def forward(ctx, cp, tag, anchor, *tensors):
+        del anchor          # as in _Receive: the node is recorded whenever gradients are enabled, on both sides alike
         ctx.cp, ctx.tag = cp, tag
         ctx.meta = [(t.shape, t.dtype, t.device) for t in tensors]
         for t in tensors:
@@ -84,7 +85,7 @@ class _Send(torch.autograd.Function):
             buf = torch.empty(shape, dtype=dtype, device=device)
             dist.recv(buf, src=cp.next_global, group=cp.group, tag=ctx.tag)
             grads.append(buf)
-        return (None, None) + tuple(grads)
+        return (None, None, None) + tuple(grads)
 
 
 class ContextParallel:
@@ -132,6 +133,8 @@ class ContextParallel:
 
     def enter(self, idx: int, rwkv_l, scr_l):
         """State with which this rank starts layer ``idx``: the caller's on the first rank, the previous rank's otherwise."""
+        if idx == 0:
+            self._tokens = []          # a forward that was abandoned half way leaves nothing behind
         if self.rank == 0:
             return rwkv_l, scr_l
         templates = _pack(rwkv_l, scr_l)
@@ -150,10 +153,10 @@ class ContextParallel:
         if self.rank == self.world - 1:
             return
         tensors = _pack(rwkv_l, scr_l)
-        if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+        if torch.is_grad_enabled():
             # every tensor goes through the node (also those without a graph of their own), so that both sides exchange
             # the same number of cotangents in backward
-            self._tokens.append(_Send.apply(self, idx, *tensors))
+            self._tokens.append(_Send.apply(self, idx, self._anchor_for(tensors[0].device), *tensors))
         else:
             for t in tensors:
                 dist.send(t.detach().contiguous(), dst=self.next_global, group=self.group, tag=idx)
