@@ -361,3 +361,13 @@ def test_example_scripts_run(tiny_binidx, capsys):
     assert res.returncode == 0, res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("mesh=")][-1]
     assert "'model': 2" in line and f"{losses[0]:.4f}"[:5] in line
+    # a sequence shared by two processes (context parallelism): the losses of one process on the whole sequence
+    one = runpy.run_path(str(root / "examples" / "context_parallel.py"))["main"](["--ctx-len", "16", "--steps", "2"])
+    capsys.readouterr()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), str(root / "examples" / "context_parallel.py"), "--ctx-len", "16", "--steps", "2"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(root),
+                         env=dict(os.environ, PYTHONPATH=str(root), CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("processes=2")][-1]
+    assert all(f"{x:.5f}"[:6] in line for x in one)
