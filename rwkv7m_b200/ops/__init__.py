@@ -180,7 +180,9 @@ def _check_wkv_inputs(r, w, k, v, a, b, state0):
 
 
 def wkv7(r, w, k, v, a, b, state0):
-    """WKV7 recurrence on [B,T,H,N] vectors with an fp32 [B,H,N,N] initial state."""
+    """WKV7 recurrence on [B,T,H,N] vectors with an fp32 [B,H,N,N] initial state.  The kernels implement reverse-mode
+    differentiation only (a hand-written backward, as the reference's custom VJP, src/rwkv7m/model/wkv.py); forward-mode
+    differentiation through a CUDA call raises in autograd, the PyTorch statement on CPU supports both."""
     _check_wkv_inputs(r, w, k, v, a, b, state0)
     from . import backends
 
