@@ -941,6 +941,10 @@ def test_parallelism_mode_comparison_is_calibrated_and_ordered(capsys):
     lean = {r["mode"]: r for r in compare_parallelism_modes(model_preset("7b"), gpus=8, tokens_per_device=65536,
                                                               recompute_layers=32)}
     assert lean["tp8"]["activation_bytes"] < 0.1 * big["tp8"]["activation_bytes"]
+    # a context axis divides the activations like a model axis and keeps the weight state of the fused data-parallel step
+    assert big["cp8"]["activation_bytes"] == pytest.approx(big["dp-fused"]["activation_bytes"] / 8, rel=1e-6)
+    assert big["cp8"]["weight_state_bytes"] == big["dp-fused"]["weight_state_bytes"] and big["cp8"]["fits"]
+    assert not big["cp2 x dp4"]["fits"] and "MB forward" in big["cp4 x dp2"]["note"]
     plan_scale.main(["--model-preset", "7b", "--model-axis-size", "8", "--compare-modes", "--tokens-per-device", "65536"])
     report = json.loads(capsys.readouterr().out)
     assert [r["mode"] for r in report["modes"]][:3] == ["dp-allreduce", "dp-fused", "zero3"] and "estimate" in report
